@@ -1,0 +1,117 @@
+// Embedding gather, RMSNorm, SiLU-gate and bias kernels.  The residual stream is 32-bit in both
+// engine dtypes; T is the storage type of weights and activations (float or bf16).
+//
+// What each replaces in libmir: embedding_bf16.cu:3-19, rms_norm_bf16.cu:3-36,
+// elementwise_bf16.cu:42-70 (packed gate|up), select_row_bf16.cu (row gather, folded into the norm).
+#include "common.cuh"
+
+using namespace mir;
+
+// out[r, :] = float(table[ids[r], :]) * scale.  An id outside [0, vocab) gives a row of zeros;
+// the host rejects such ids before the launch.
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+                             int hidden, int vocab, float scale) {
+  const int row = blockIdx.x;
+  const int id = ids[row];
+  const bool ok = id >= 0 && id < vocab;
+  const T* src = table + (size_t)(ok ? id : 0) * hidden;
+  float* dst = out + (size_t)row * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = ok ? to_float(src[c]) * scale : 0.0f;
+}
+
+// y[r, :] = x[src(r), :] * rsqrt(mean(x^2) + eps) * w, src(r) = rows ? rows[r] : r.
+// Sum of squares and scaling in 32-bit with a fixed reduction tree.
+template <typename Tout>
+__global__ void rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ weight,
+                                Tout* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[32];
+  const int row = blockIdx.x;
+  const float* src = x + (size_t)(rows ? rows[row] : row) * hidden;
+  float sum = 0.0f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float v = src[c];
+    sum = fmaf(v, v, sum);
+  }
+  sum = block_sum(sum, scratch);
+  const float inverse = rsqrtf(sum / (float)hidden + eps);
+  Tout* dst = out + (size_t)row * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = from_float<Tout>(src[c] * inverse * weight[c]);
+}
+
+// out[r, c] = silu(gu[r, c]) * gu[r, inter + c]; gu rows are [gate | up].
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+  const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index >= total) return;
+  const size_t row = index / inter;
+  const int col = (int)(index - row * inter);
+  const float g = to_float(gu[row * 2 * inter + col]);
+  const float u = to_float(gu[row * 2 * inter + inter + col]);
+  out[index] = from_float<T>(g / (1.0f + expf(-g)) * u);
+}
+
+// x[r, c] += bias[c]  (32-bit residual; used when a projection that accumulates into the residual has a bias).
+template <typename T>
+__global__ void add_bias_kernel(float* __restrict__ x, const T* __restrict__ bias, int cols, size_t total) {
+  const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index >= total) return;
+  x[index] += to_float(bias[index % cols]);
+}
+
+// dst[i] = T(src[i]) for the load-time casts (dense_cast.cu:4-18) and for copying logits rows.
+template <typename Tin, typename Tout>
+__global__ void cast_kernel(const Tin* __restrict__ src, Tout* __restrict__ dst, size_t total) {
+  const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index < total) dst[index] = from_float<Tout>(to_float(src[index]));
+}
+
+#define LAUNCH_1D(kernel, total, ...)                                                      \
+  do {                                                                                     \
+    const size_t n_ = (total);                                                             \
+    if (n_ == 0) return MIR_OK;                                                            \
+    kernel<<<(unsigned)((n_ + 255) / 256), 256, 0, stream>>>(__VA_ARGS__);                 \
+  } while (0)
+
+MIR_EXPORT int mir_embed(int bf16, const void* table, const int* ids, float* out, int rows, int hidden, int vocab,
+                         float scale, cudaStream_t stream) {
+  if (rows == 0) return MIR_OK;
+  if (rows < 0 || hidden <= 0 || vocab <= 0) { mir_set_error("embed: bad sizes"); return MIR_BAD_ARGUMENT; }
+  if (bf16) embed_kernel<<<rows, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, scale);
+  else embed_kernel<<<rows, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab, scale);
+  return mir_check_launch("embed");
+}
+
+MIR_EXPORT int mir_rms_norm(int bf16, const float* x, const float* weight, void* out, const int* rows, int n_rows,
+                            int hidden, float eps, cudaStream_t stream) {
+  if (n_rows == 0) return MIR_OK;
+  if (n_rows < 0 || hidden <= 0) { mir_set_error("rms_norm: bad sizes"); return MIR_BAD_ARGUMENT; }
+  const int threads = hidden >= 2048 ? 512 : 256;
+  if (bf16) rms_norm_kernel<<<n_rows, threads, 0, stream>>>(x, weight, (__nv_bfloat16*)out, rows, hidden, eps);
+  else rms_norm_kernel<<<n_rows, threads, 0, stream>>>(x, weight, (float*)out, rows, hidden, eps);
+  return mir_check_launch("rms_norm");
+}
+
+MIR_EXPORT int mir_silu_mul(int bf16, const void* gu, void* out, int rows, int inter, cudaStream_t stream) {
+  if (rows < 0 || inter <= 0) { mir_set_error("silu_mul: bad sizes"); return MIR_BAD_ARGUMENT; }
+  const size_t total = (size_t)rows * inter;
+  if (bf16) LAUNCH_1D(silu_mul_kernel, total, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
+  else LAUNCH_1D(silu_mul_kernel, total, (const float*)gu, (float*)out, inter, total);
+  return mir_check_launch("silu_mul");
+}
+
+MIR_EXPORT int mir_add_bias(int bf16, float* x, const void* bias, int rows, int cols, cudaStream_t stream) {
+  if (rows < 0 || cols <= 0) { mir_set_error("add_bias: bad sizes"); return MIR_BAD_ARGUMENT; }
+  const size_t total = (size_t)rows * cols;
+  if (bf16) LAUNCH_1D(add_bias_kernel, total, x, (const __nv_bfloat16*)bias, cols, total);
+  else LAUNCH_1D(add_bias_kernel, total, x, (const float*)bias, cols, total);
+  return mir_check_launch("add_bias");
+}
+
+// kind: 0 f32->bf16, 1 bf16->f32.
+MIR_EXPORT int mir_cast(int kind, const void* src, void* dst, size_t total, cudaStream_t stream) {
+  if (kind == 0) LAUNCH_1D(cast_kernel, total, (const float*)src, (__nv_bfloat16*)dst, total);
+  else if (kind == 1) LAUNCH_1D(cast_kernel, total, (const __nv_bfloat16*)src, (float*)dst, total);
+  else { mir_set_error("cast: unknown kind %d", kind); return MIR_BAD_ARGUMENT; }
+  return mir_check_launch("cast");
+}

@@ -1,0 +1,108 @@
+"""What a step hands to the parts: the packed rows' metadata on the device, and scratch memory.
+
+Nothing here is specific to a mixer.  The packed-row description follows libmir's PagedPrefillBatch
+(cuda/src/backend/kv/prefill_batch/mod.rs:82-139): per row of the batch (one request's portion)
+query_starts, context length after the step, block table; per token its request row, absolute
+position and cache slot.  A decoded token is a portion of one token (cuda/src/engine/model/generation/
+graph.rs:112-121).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import kernels
+
+
+class Arena:
+    """Scratch memory of a step: a bump allocator over buffers that are kept between steps.
+
+    `reset` starts a new step.  When a step needs more than the arena holds, another buffer is added
+    (a device allocation) and kept, so steps of a size seen before allocate nothing; shapes replayed
+    from a CUDA graph always find the addresses they were captured with because allocation order is
+    deterministic.
+    """
+
+    ALIGN = 256
+
+    def __init__(self, device: torch.device, chunk_bytes: int = 64 << 20):
+        self.device = device
+        self.chunk_bytes = chunk_bytes
+        self.chunks: List[torch.Tensor] = []
+        self.chunk = 0
+        self.offset = 0
+
+    def reset(self) -> None:
+        self.chunk = 0
+        self.offset = 0
+
+    def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        count = 1
+        for dim in shape:
+            count *= int(dim)
+        nbytes = count * torch.empty((), dtype=dtype).element_size()
+        padded = -(-max(nbytes, 1) // self.ALIGN) * self.ALIGN
+        while True:
+            if self.chunk >= len(self.chunks):
+                self.chunks.append(torch.empty(max(self.chunk_bytes, padded), dtype=torch.uint8, device=self.device))
+            buffer = self.chunks[self.chunk]
+            if self.offset + padded <= buffer.numel():
+                view = buffer[self.offset:self.offset + nbytes].view(dtype).view(*shape)
+                self.offset += padded
+                return view
+            self.chunk += 1
+            self.offset = 0
+
+    def bytes(self) -> int:
+        return sum(chunk.numel() for chunk in self.chunks)
+
+
+@dataclass
+class GroupContext:
+    """Per cache group: where each token's key/value goes and each row's block table."""
+
+    block_table: torch.Tensor           # int32 [rows, width]; -1 where a page was released
+    slot_mapping: torch.Tensor          # int32 [tokens]; page * page_size + position % page_size, -1 = no write
+    table_width: int = 0
+
+
+@dataclass
+class StepContext:
+    num_tokens: int
+    num_rows: int
+    tokens: torch.Tensor                # int32 [T]
+    positions: torch.Tensor             # int32 [T] absolute position of each token in its request
+    row_of_token: torch.Tensor          # int32 [T]
+    query_starts: torch.Tensor          # int32 [R + 1]
+    context_lens: torch.Tensor          # int32 [R] tokens of the request cached after this step
+    state_slots: torch.Tensor           # int32 [R] the request's fixed-size state slot
+    groups: List[GroupContext]
+    views: Dict[int, object]            # schedule entry -> CacheView
+    arena: Arena
+    dtype: torch.dtype
+    # host copies, for launch geometry and for parts that walk requests on the host
+    host_query_starts: Sequence[int] = ()
+    host_start_positions: Sequence[int] = ()
+    host_state_slots: Sequence[int] = ()
+    max_context: int = 0
+    max_portion: int = 0
+    decode_only: bool = False
+    page_size: int = 0
+
+    def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        return self.arena.alloc(shape, dtype)
+
+    def cache_view(self, entry: int):
+        return self.views.get(entry)
+
+    def cast_residual(self, residual: torch.Tensor) -> torch.Tensor:
+        """The 32-bit residual in the engine's dtype (for an arrangement without a norm)."""
+        if self.dtype == torch.float32:
+            return residual
+        out = self.alloc(residual.shape, self.dtype)
+        kernels.cast(residual, out)
+        return out

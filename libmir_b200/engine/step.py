@@ -1,0 +1,209 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+One path for every mix: portions of prompts beside single decoded tokens, cut anywhere.  A step runs
+only the tokens it is given, reads everything older from the cache, and returns 32-bit logits at the
+requested places.  libmir's equivalent is CudaEngine::execute_generation_step ->
+CudaMoeModelSession::prefill_packed_chunk + finish_packed_prefill_rows
+(cuda/src/engine/execution/step.rs:14-88, cuda/src/backend/model/session/prefill/packed.rs:23-89,
+output.rs:112-178), which returns only last-position results; here any position may be asked for.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, CacheStorage
+from ..errors import KernelError, KvCachePressure, KvCapacity, SchedulerError
+from .context import Arena, GroupContext, StepContext
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the local places whose logits are wanted."""
+
+    request_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class StepResult:
+    logits: Optional[torch.Tensor]          # float32 [wanted, vocab] on the device; valid until the next step
+    rows: List[tuple]                       # (request_id, local index) for each logits row, in order
+    num_tokens: int = 0
+
+
+class StepRunner:
+    """Owns the device state of one loaded model: cache storage, scratch, staging buffers."""
+
+    def __init__(self, model, manager: CacheManager, storage: CacheStorage, device: torch.device,
+                 decode_graphs: bool = False):
+        self.model = model
+        self.manager = manager
+        self.storage = storage
+        self.device = device
+        self.decode_graphs = decode_graphs
+        self.arena = Arena(device)
+        self._staging: List[Optional[torch.Tensor]] = [None, None]
+        self._staging_events: List[Optional[torch.cuda.Event]] = [None, None]
+        self._device_meta: Optional[torch.Tensor] = None
+        self._flip = 0
+        self.steps = 0
+        self.tokens_run = 0
+
+    # -- metadata ------------------------------------------------------------------
+    def _stage(self, arrays: List[np.ndarray]) -> List[torch.Tensor]:
+        """Copy int32 arrays to the device through one pinned buffer and one transfer."""
+        sizes = [a.size for a in arrays]
+        offsets, total = [], 0
+        for size in sizes:
+            offsets.append(total)
+            total += -(-max(size, 1) // 4) * 4          # keep every array 16-byte aligned
+        self._flip ^= 1
+        staging = self._staging[self._flip]
+        if staging is None or staging.numel() < total:
+            staging = torch.empty(max(total, 4096), dtype=torch.int32, pin_memory=True)
+            self._staging[self._flip] = staging
+            self._staging_events[self._flip] = None
+        event = self._staging_events[self._flip]
+        if event is not None:
+            event.synchronize()
+        if self._device_meta is None or self._device_meta.numel() < total:
+            self._device_meta = torch.empty(max(total, 4096), dtype=torch.int32, device=self.device)
+        host = staging.numpy()
+        for array, offset in zip(arrays, offsets):
+            host[offset:offset + array.size] = array.reshape(-1)
+        self._device_meta[:total].copy_(staging[:total], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self._staging_events[self._flip] = event
+        return [self._device_meta[offset:offset + size] for offset, size in zip(offsets, sizes)]
+
+    def build_context(self, entries: Sequence[StepEntry], sequences) -> tuple:
+        manager = self.manager
+        page = manager.page_size
+        counts = [len(e.tokens) for e in entries]
+        total = sum(counts)
+        rows = len(entries)
+        tokens = np.empty(total, dtype=np.int32)
+        positions = np.empty(total, dtype=np.int32)
+        row_of_token = np.empty(total, dtype=np.int32)
+        query_starts = np.zeros(rows + 1, dtype=np.int32)
+        context_lens = np.empty(rows, dtype=np.int32)
+        state_slots = np.empty(rows, dtype=np.int32)
+        want_rows: List[int] = []
+        want_keys: List[tuple] = []
+        vocab = self.model.spec.vocab_size
+        cursor = 0
+        for r, (entry, seq, count) in enumerate(zip(entries, sequences, counts)):
+            ids = np.asarray(entry.tokens, dtype=np.int64)
+            if ids.size and (ids.min() < 0 or ids.max() >= vocab):
+                raise SchedulerError(f"request {entry.request_id!r}: token id outside [0, {vocab})")
+            tokens[cursor:cursor + count] = ids
+            positions[cursor:cursor + count] = np.arange(seq.length, seq.length + count, dtype=np.int32)
+            row_of_token[cursor:cursor + count] = r
+            query_starts[r + 1] = cursor + count
+            context_lens[r] = seq.length + count
+            state_slots[r] = seq.slot
+            for local in entry.want:
+                if not 0 <= local < count:
+                    raise SchedulerError(f"request {entry.request_id!r}: wanted place {local} is outside its "
+                                         f"{count} tokens")
+                want_rows.append(cursor + local)
+                want_keys.append((entry.request_id, local))
+            cursor += count
+        arrays = [tokens, positions, row_of_token, query_starts, context_lens, state_slots,
+                  np.asarray(want_rows, dtype=np.int32)]
+        widths = []
+        for g, group in enumerate(manager.groups):
+            width = max(1, max(len(seq.tables[g]) for seq in sequences))
+            widths.append(width)
+            table = np.full((rows, width), -1, dtype=np.int32)
+            slots = np.empty(total, dtype=np.int32)
+            for r, seq in enumerate(sequences):
+                blocks = seq.tables[g]
+                table[r, :len(blocks)] = blocks
+                begin, end = query_starts[r], query_starts[r + 1]
+                pos = positions[begin:end]
+                pages = table[r, pos // page]
+                slots[begin:end] = np.where(pages >= 0, pages * page + pos % page, -1)
+            arrays += [table, slots]
+        staged = self._stage(arrays)
+        groups = []
+        for g, width in enumerate(widths):
+            groups.append(GroupContext(block_table=staged[7 + 2 * g].view(rows, width),
+                                       slot_mapping=staged[8 + 2 * g], table_width=width))
+        ctx = StepContext(
+            num_tokens=total, num_rows=rows, tokens=staged[0], positions=staged[1], row_of_token=staged[2],
+            query_starts=staged[3], context_lens=staged[4], state_slots=staged[5], groups=groups,
+            views=self.storage.views, arena=self.arena, dtype=self.model.env.dtype,
+            host_query_starts=query_starts.tolist(), host_start_positions=[seq.length for seq in sequences],
+            host_state_slots=state_slots.tolist(), max_context=int(context_lens.max()) if rows else 0,
+            max_portion=max(counts) if counts else 0, decode_only=all(c == 1 for c in counts),
+            page_size=page)
+        return ctx, staged[6], want_keys
+
+    # -- the step ----------------------------------------------------------------------
+    def reserve(self, entries: Sequence[StepEntry]):
+        """Host side of a step: check the batch and take the pages it needs, all or none.
+
+        Raises KvCapacity when one request alone exceeds a pool, KvCachePressure when the pages are not
+        free right now (nothing is taken in either case)."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        manager = self.manager
+        seen = set()
+        sequences = []
+        for entry in entries:
+            if entry.request_id in seen:
+                raise SchedulerError(f"request {entry.request_id!r} appears twice in one step")
+            seen.add(entry.request_id)
+            seq = manager.live.get(entry.request_id)
+            if seq is None:
+                raise SchedulerError(f"request {entry.request_id!r} is not live: admit it first")
+            sequences.append(seq)
+        limit = self.model.spec.max_positions
+        for entry, seq in zip(entries, sequences):
+            if seq.length + len(entry.tokens) > limit:
+                raise SchedulerError(f"request {entry.request_id!r} would reach {seq.length + len(entry.tokens)} "
+                                     f"tokens, max_position_embeddings is {limit}")
+        needs = [manager.pages_needed(seq, seq.length + len(e.tokens)) for e, seq in zip(entries, sequences)]
+        for g, group in enumerate(manager.groups):
+            total_need = sum(n[g] for n in needs)
+            if total_need <= group.pool.free:
+                continue
+            for need, seq in zip(needs, sequences):     # a request too large for the whole pool is a hard error
+                alone = sum(1 for p in seq.tables[g] if p >= 0) + need[g]
+                if alone > group.pool.count:
+                    raise KvCapacity(alone, group.pool.count, f"group {g}")
+            raise KvCachePressure(total_need, group.pool.free, f"group {g}")
+        for entry, seq in zip(entries, sequences):
+            manager.grow(seq, seq.length + len(entry.tokens))
+        return entries, sequences
+
+    def execute(self, entries: Sequence[StepEntry], sequences) -> StepResult:
+        """Device side of a step: run the tokens from the cache and return logits at the wanted places."""
+        self.storage.zero_slots(self.manager.take_fresh_slots())
+        self.arena.reset()
+        ctx, want_rows, want_keys = self.build_context(entries, sequences)
+        residual = self.model.forward(ctx)
+        logits = self.model.logits(ctx, residual, want_rows) if want_keys else None
+        return StepResult(logits, want_keys, ctx.num_tokens)
+
+    def commit(self, entries: Sequence[StepEntry], sequences) -> None:
+        for entry, seq in zip(entries, sequences):
+            self.manager.commit(seq, seq.length + len(entry.tokens))
+
+    def step(self, entries: Sequence[StepEntry]) -> StepResult:
+        """Run one batch: reserve pages, run the tokens, commit the new lengths."""
+        entries, sequences = self.reserve(entries)
+        if not entries:
+            return StepResult(None, [], 0)
+        result = self.execute(entries, sequences)
+        self.commit(entries, sequences)
+        self.steps += 1
+        self.tokens_run += result.num_tokens
+        return result

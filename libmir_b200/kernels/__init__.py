@@ -1,0 +1,294 @@
+"""Python launchers of the sm_100a kernels in libmir_b200/csrc.
+
+Every function takes torch CUDA tensors, checks what the kernel cannot check itself (device, dtype,
+contiguity), and launches on torch's current stream, so launches are captured when a CUDA graph is
+being recorded.  There is no fallback: if the native library cannot be built or loaded, or a kernel
+refuses its sizes, a KernelError is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_double, c_float, c_int, c_longlong, c_size_t, c_void_p
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..csrc import build as _build
+from ..errors import KernelError
+
+_LIBS: dict = {}
+_VERBOSE_BUILD = True
+
+_SIGNATURES = {
+    "core": {
+        "mir_embed": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+        "mir_rms_norm": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+        "mir_silu_mul": [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "mir_add_bias": [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "mir_cast": [c_int, c_void_p, c_void_p, c_size_t, c_void_p],
+        "mir_qk_rope_store": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "mir_paged_attention_generic": [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                        c_void_p],
+        "mir_gemm_f32": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                         c_void_p],
+        "mir_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
+        "mir_repetition_penalty": [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    },
+    "bf16": {
+        "mir_gemm_bf16_lt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                             c_float, c_void_p, c_size_t, c_void_p],
+    },
+}
+
+
+def set_build_verbosity(verbose: bool) -> None:
+    global _VERBOSE_BUILD
+    _VERBOSE_BUILD = verbose
+
+
+def library(name: str) -> ctypes.CDLL:
+    """The loaded native library `name`, compiled first if its sources changed or it was never built."""
+    lib = _LIBS.get(name)
+    if lib is not None:
+        return lib
+    path = _build.build(name, verbose=_VERBOSE_BUILD)
+    try:
+        lib = ctypes.CDLL(str(path), mode=ctypes.RTLD_LOCAL)
+    except OSError as error:
+        raise KernelError(f"cannot load {path}: {error}") from error
+    lib.mir_last_error.restype = ctypes.c_char_p
+    lib.mir_last_error.argtypes = []
+    for symbol, argtypes in _SIGNATURES.get(name, {}).items():
+        function = getattr(lib, symbol)
+        function.argtypes = argtypes
+        function.restype = c_int
+    _LIBS[name] = lib
+    return lib
+
+
+def loaded_libraries() -> dict:
+    """Paths of the native libraries this process has loaded (for reports)."""
+    return {name: lib._name for name, lib in _LIBS.items()}
+
+
+def _check(lib: ctypes.CDLL, status: int) -> None:
+    if status != 0:
+        raise KernelError(lib.mir_last_error().decode(errors="replace") or f"kernel launch failed with status {status}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(tensor: Optional[torch.Tensor]) -> Optional[int]:
+    return None if tensor is None else tensor.data_ptr()
+
+
+def _is_bf16(tensor: torch.Tensor) -> int:
+    if tensor.dtype == torch.bfloat16:
+        return 1
+    if tensor.dtype == torch.float32:
+        return 0
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {tensor.dtype}")
+
+
+def _require(condition: bool, message: str) -> None:
+    if not condition:
+        raise KernelError(message)
+
+
+def _cuda(*tensors) -> None:
+    for tensor in tensors:
+        if tensor is not None and not tensor.is_cuda:
+            raise KernelError("kernels take CUDA tensors only: there is no CPU path")
+
+
+# --------------------------------------------------------------------------- elementwise
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[r] = float(table[ids[r]]) * scale; out is the 32-bit residual [rows, hidden]."""
+    _cuda(table, ids, out)
+    rows, hidden = out.shape
+    _require(table.is_contiguous() and out.is_contiguous() and ids.dtype == torch.int32 and ids.numel() == rows
+             and out.dtype == torch.float32 and table.shape[1] == hidden, "embed: bad arguments")
+    lib = library("core")
+    _check(lib, lib.mir_embed(_is_bf16(table), table.data_ptr(), ids.data_ptr(), out.data_ptr(), rows, hidden,
+                              table.shape[0], scale, _stream()))
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+             rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = rmsnorm(x[rows[r] if rows else r]) * weight; x and weight are 32-bit."""
+    _cuda(x, weight, out, rows)
+    n_rows, hidden = out.shape
+    _require(x.dtype == torch.float32 and weight.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+             and x.shape[1] == hidden and weight.numel() == hidden, "rms_norm: bad arguments")
+    if rows is not None:
+        _require(rows.dtype == torch.int32 and rows.numel() == n_rows, "rms_norm: bad row index")
+    else:
+        _require(x.shape[0] >= n_rows, "rms_norm: fewer input rows than output rows")
+    lib = library("core")
+    _check(lib, lib.mir_rms_norm(_is_bf16(out), x.data_ptr(), weight.data_ptr(), out.data_ptr(), _ptr(rows), n_rows,
+                                 hidden, eps, _stream()))
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r, c] = silu(gate_up[r, c]) * gate_up[r, I + c]."""
+    _cuda(gate_up, out)
+    rows, inter = out.shape
+    _require(gate_up.shape == (rows, 2 * inter) and gate_up.is_contiguous() and out.is_contiguous()
+             and gate_up.dtype == out.dtype, "silu_mul: bad arguments")
+    lib = library("core")
+    _check(lib, lib.mir_silu_mul(_is_bf16(out), gate_up.data_ptr(), out.data_ptr(), rows, inter, _stream()))
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
+    _cuda(x, bias)
+    rows, cols = x.shape
+    _require(x.dtype == torch.float32 and x.is_contiguous() and bias.numel() == cols, "add_bias: bad arguments")
+    lib = library("core")
+    _check(lib, lib.mir_add_bias(_is_bf16(bias), x.data_ptr(), bias.data_ptr(), rows, cols, _stream()))
+
+
+def cast(src: torch.Tensor, dst: torch.Tensor) -> None:
+    """float32 <-> bfloat16 copy of equal shapes (load-time cast, libmir dense_cast.cu)."""
+    _cuda(src, dst)
+    _require(src.is_contiguous() and dst.is_contiguous() and src.numel() == dst.numel(), "cast: bad arguments")
+    kinds = {(torch.float32, torch.bfloat16): 0, (torch.bfloat16, torch.float32): 1}
+    kind = kinds.get((src.dtype, dst.dtype))
+    _require(kind is not None, f"cast: {src.dtype} -> {dst.dtype} is not supported")
+    lib = library("core")
+    _check(lib, lib.mir_cast(kind, src.data_ptr(), dst.data_ptr(), src.numel(), _stream()))
+
+
+# --------------------------------------------------------------------------- attention
+def qk_rope_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+                  inv_freq: Optional[torch.Tensor], q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
+                  k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], heads: int, kv_heads: int,
+                  head_dim: int, rotary_dim: int, eps: float, write_kv: bool = True) -> None:
+    """q/k-norm + rotary on the packed qkv rows in place for q, k and v into their pages."""
+    _cuda(qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages)
+    tokens = qkv.shape[0]
+    _require(qkv.is_contiguous() and qkv.shape[1] == (heads + 2 * kv_heads) * head_dim, "qk_rope_store: bad qkv")
+    _require(positions.dtype == torch.int32 and positions.numel() >= tokens, "qk_rope_store: bad positions")
+    _require(head_dim % 8 == 0, f"qk_rope_store: head_dim {head_dim} is not a multiple of 8")
+    if rotary_dim:
+        _require(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
+                 "qk_rope_store: the angle table must hold rotary_dim / 2 float32 values")
+    for norm in (q_norm, k_norm):
+        _require(norm is None or (norm.dtype == torch.float32 and norm.numel() == head_dim),
+                 "qk_rope_store: q/k norm weights must be float32 [head_dim]")
+    if write_kv:
+        _require(slot_mapping is not None and slot_mapping.dtype == torch.int32 and k_pages is not None
+                 and v_pages is not None and k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype,
+                 "qk_rope_store: cache pages of the activations' dtype and a slot mapping are needed")
+    lib = library("core")
+    _check(lib, lib.mir_qk_rope_store(_is_bf16(qkv), qkv.data_ptr(), positions.data_ptr(), _ptr(slot_mapping),
+                                      _ptr(inv_freq), _ptr(q_norm), _ptr(k_norm), _ptr(k_pages), _ptr(v_pages),
+                                      tokens, heads, kv_heads, head_dim, rotary_dim, eps, int(write_kv), _stream()))
+
+
+def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                            block_table: torch.Tensor, row_of_token: torch.Tensor, positions: torch.Tensor,
+                            page_size: int, heads: int, kv_heads: int, head_dim: int, scale: float,
+                            window: Optional[int]) -> None:
+    """out[t, h] = softmax over the visible cached keys of token t's request; q is read from the packed qkv rows."""
+    _cuda(qkv, out, k_pages, v_pages, block_table, row_of_token, positions)
+    tokens = out.shape[0]
+    _require(out.is_contiguous() and out.shape[1] == heads * head_dim and qkv.dtype == out.dtype
+             and k_pages.dtype == out.dtype and v_pages.dtype == out.dtype, "paged_attention: bad tensors")
+    _require(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous()
+             and row_of_token.dtype == torch.int32 and positions.dtype == torch.int32, "paged_attention: bad metadata")
+    lib = library("core")
+    _check(lib, lib.mir_paged_attention_generic(
+        _is_bf16(out), qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], row_of_token.data_ptr(), positions.data_ptr(), tokens,
+        page_size, heads, kv_heads, head_dim, scale, int(window or 0), _stream()))
+
+
+# --------------------------------------------------------------------------- matrix products
+_LT_WORKSPACE: dict = {}
+LT_WORKSPACE_BYTES = 64 * 1024 * 1024
+
+
+def _lt_workspace(device) -> torch.Tensor:
+    key = (device.type, device.index)
+    buffer = _LT_WORKSPACE.get(key)
+    if buffer is None:
+        buffer = torch.empty(LT_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+        _LT_WORKSPACE[key] = buffer
+    return buffer
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           accumulate: bool = False) -> None:
+    """out = (out if accumulate) + x . weight^T (+ bias).
+
+    float32 tensors: the 32-bit FMA kernel.  bfloat16 x and weight: cuBLASLt with 32-bit accumulation,
+    out bfloat16 or float32.  x and out may be row-strided views; weight is [out_features, in_features].
+    """
+    _cuda(x, weight, out, bias)
+    m, k = x.shape
+    n = weight.shape[0]
+    _require(weight.shape[1] == k and out.shape == (m, n) and x.stride(1) == 1 and out.stride(1) == 1
+             and weight.is_contiguous(), "linear: shapes or strides do not fit")
+    beta = 1.0 if accumulate else 0.0
+    if x.dtype == torch.float32:
+        _require(weight.dtype == torch.float32 and out.dtype == torch.float32
+                 and (bias is None or bias.dtype == torch.float32), "linear: float32 takes float32 everywhere")
+        lib = library("core")
+        _check(lib, lib.mir_gemm_f32(x.data_ptr(), x.stride(0), weight.data_ptr(), k, _ptr(bias), out.data_ptr(),
+                                     out.stride(0), m, n, k, beta, _stream()))
+        return
+    _require(x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16, "linear: x and weight must share a dtype")
+    if bias is not None and bias.dtype != out.dtype:
+        _require(out.dtype == torch.float32 and accumulate, "linear: bias dtype must match out")
+        add_bias(out, bias)
+        bias = None
+    lib = library("bf16")
+    workspace = _lt_workspace(x.device)
+    _check(lib, lib.mir_gemm_bf16_lt(x.data_ptr(), x.stride(0), weight.data_ptr(), k, _ptr(bias), out.data_ptr(),
+                                     out.stride(0), int(out.dtype == torch.float32), m, n, k, beta,
+                                     workspace.data_ptr(), workspace.numel(), _stream()))
+
+
+# --------------------------------------------------------------------------- sampling
+SAMPLE_OPTIONS = np.dtype([("draw", "<f8"), ("temperature", "<f4"), ("top_p", "<f4"), ("top_k", "<i4"),
+                           ("pad", "<i4")])
+
+
+def ranked_scratch_keys(rows: int, vocab: int) -> int:
+    """How many 64-bit keys of scratch top-k / top-p sampling needs for `rows` rows."""
+    padded = 1
+    while padded < vocab:
+        padded <<= 1
+    return rows * padded
+
+
+def sample(logits: torch.Tensor, options: torch.Tensor, tokens: torch.Tensor,
+           sort_keys: Optional[torch.Tensor] = None, needs_ranked: bool = False) -> None:
+    """tokens[r] = one token from row r of the 32-bit logits; options is a uint8 view of SAMPLE_OPTIONS records."""
+    _cuda(logits, options, tokens, sort_keys)
+    rows, vocab = logits.shape
+    _require(logits.dtype == torch.float32 and logits.stride(1) == 1 and tokens.dtype == torch.int32
+             and tokens.numel() >= rows and options.numel() * options.element_size() >= rows * SAMPLE_OPTIONS.itemsize,
+             "sample: bad arguments")
+    capacity = 0 if sort_keys is None else sort_keys.numel() * sort_keys.element_size() // 8
+    lib = library("core")
+    _check(lib, lib.mir_sample(logits.data_ptr(), logits.stride(0), rows, vocab, options.data_ptr(), _ptr(sort_keys),
+                               capacity, int(needs_ranked), tokens.data_ptr(), _stream()))
+
+
+def repetition_penalty(logits: torch.Tensor, ids: torch.Tensor, id_rows: torch.Tensor,
+                       penalties: torch.Tensor) -> None:
+    _cuda(logits, ids, id_rows, penalties)
+    rows, vocab = logits.shape
+    _require(logits.dtype == torch.float32 and ids.dtype == torch.int32 and id_rows.dtype == torch.int32
+             and penalties.dtype == torch.float32 and penalties.numel() >= rows and ids.numel() == id_rows.numel(),
+             "repetition_penalty: bad arguments")
+    lib = library("core")
+    _check(lib, lib.mir_repetition_penalty(logits.data_ptr(), logits.stride(0), vocab, ids.data_ptr(),
+                                           id_rows.data_ptr(), penalties.data_ptr(), ids.numel(), _stream()))

@@ -1,0 +1,89 @@
+"""Grouped-query softmax attention over the paged cache.
+
+input [T, H] -> one packed projection [T, (Hq + 2 Hkv) D] (weights row-stacked [Wq; Wk; Wv] as libmir's
+CUDA loader packs them, cuda/src/backend/linear/pack.rs:35-76) -> per-head q/k RMSNorm and rotary,
+K and V written to their pages (one kernel) -> attention over the request's pages -> output projection
+accumulated into the 32-bit residual.  Formulas: metal/src/engine/dense/swiglu/attention.rs:14-112.
+Options, all from the spec: q/k-norm, q/k/v bias and output bias, window, scale, position encoding.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import kernels
+from ..config.spec import PagedKv, ParamSpec
+from ..registry import build_part
+from .base import Mixer
+
+
+class SoftmaxAttention(Mixer):
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        s = spec
+        if s.heads % s.kv_heads:
+            raise ValueError("heads must be divisible by kv_heads")
+        self.q_width = s.heads * s.head_dim
+        self.kv_width = s.kv_heads * s.head_dim
+        self.position = build_part(s.position, env) if s.position is not None else None
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_norm = self.k_norm = None
+
+    def cache_requirement(self):
+        return PagedKv(self.spec.kv_heads, self.spec.head_dim, self.spec.window)
+
+    def parameters(self):
+        s = self.spec
+        table = {
+            "q_proj.weight": ParamSpec((self.q_width, s.hidden_size)),
+            "k_proj.weight": ParamSpec((self.kv_width, s.hidden_size)),
+            "v_proj.weight": ParamSpec((self.kv_width, s.hidden_size)),
+            "o_proj.weight": ParamSpec((s.hidden_size, self.q_width)),
+        }
+        if s.qkv_bias:
+            table["q_proj.bias"] = ParamSpec((self.q_width,))
+            table["k_proj.bias"] = ParamSpec((self.kv_width,))
+            table["v_proj.bias"] = ParamSpec((self.kv_width,))
+        if s.out_bias:
+            table["o_proj.bias"] = ParamSpec((s.hidden_size,))
+        if s.qk_norm:
+            table["q_norm.weight"] = ParamSpec((s.head_dim,), init="ones", store="float32")
+            table["k_norm.weight"] = ParamSpec((s.head_dim,), init="ones", store="float32")
+        return table
+
+    def bind(self, tensors):
+        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]], dim=0)
+        self.w_o = tensors["o_proj.weight"].contiguous()
+        if self.spec.qkv_bias:
+            self.b_qkv = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]], dim=0)
+        if self.spec.out_bias:
+            self.b_o = tensors["o_proj.bias"].contiguous()
+        if self.spec.qk_norm:
+            self.q_norm = tensors["q_norm.weight"].contiguous()
+            self.k_norm = tensors["k_norm.weight"].contiguous()
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o, self.b_qkv, self.b_o) if t is not None)
+
+    def forward(self, ctx, cache, x, residual):
+        s = self.spec
+        tokens = x.shape[0]
+        qkv = ctx.alloc((tokens, self.q_width + 2 * self.kv_width), self.env.dtype)
+        kernels.linear(x, self.w_qkv, qkv, self.b_qkv)
+        group = ctx.groups[cache.group]
+        kernels.qk_rope_store(
+            qkv, ctx.positions, group.slot_mapping,
+            self.position.table if self.position is not None else None, self.q_norm, self.k_norm,
+            cache.k_pages, cache.v_pages, s.heads, s.kv_heads, s.head_dim,
+            self.position.rotary_dim if self.position is not None else 0, s.qk_norm_eps, write_kv=cache.writes)
+        mixed = ctx.alloc((tokens, self.q_width), self.env.dtype)
+        self.attend(ctx, group, cache, qkv, mixed)
+        kernels.linear(mixed, self.w_o, residual, self.b_o, accumulate=True)
+
+    def attend(self, ctx, group, cache, qkv, out):
+        """Attention of every packed row over its request's pages; the kernel is chosen by size."""
+        s = self.spec
+        kernels.paged_attention_generic(qkv, out, cache.k_pages, cache.v_pages, group.block_table, ctx.row_of_token,
+                                        ctx.positions, cache.page_size, s.heads, s.kv_heads, s.head_dim, s.scale,
+                                        s.window)
