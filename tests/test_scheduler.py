@@ -1,0 +1,200 @@
+"""The scheduler's decisions with the real cache manager and a step function that runs nothing (no GPU)."""
+
+import pytest
+import torch
+
+from libmir_b200 import KvCapacity, SchedulerError, build_spec
+from libmir_b200.cache import CacheManager
+from libmir_b200.config import GenerationSettings, SchedulerConfig
+from libmir_b200.engine.scheduler import Request, Scheduler
+from libmir_b200.engine.step import StepResult, StepRunner
+from libmir_b200.models.decoder import DecoderModel
+from libmir_b200.parts.base import BuildEnv
+from libmir_b200.sampling import RequestSampler
+from tiny_configs import TINY_A, TINY_C
+
+
+class HostOnlyRunner(StepRunner):
+    """The real reserve/commit on the host; the device part is replaced by a record of what ran."""
+
+    def __init__(self, model, manager):
+        super().__init__(model, manager, None, torch.device("cpu"))
+        self.ran = []
+
+    def execute(self, entries, sequences):
+        self.ran.append([(e.request_id, seq.length, len(e.tokens), list(e.want)) for e, seq in zip(entries, sequences)])
+        keys = [(e.request_id, w) for e in entries for w in e.want]
+        return StepResult(None, keys, sum(len(e.tokens) for e in entries))
+
+
+def build(config=TINY_A, pages=64, page_size=4, **scheduler_options):
+    model = DecoderModel(build_spec(config), BuildEnv(torch.float32, torch.device("meta")))
+    options = SchedulerConfig(**scheduler_options)
+    manager = CacheManager(model.cache_plan(), page_size, pages, options.max_batch_requests)
+    runner = HostOnlyRunner(model, manager)
+    counter = {"n": 0}
+
+    def sample(result, samplers):
+        out = []
+        for _ in samplers:
+            counter["n"] += 1
+            out.append(100 + counter["n"] % 50)
+        return out
+
+    scheduler = Scheduler(manager, options, model.spec.max_positions, runner.step, sample)
+    return scheduler, runner, manager
+
+
+def request(name, prompt_len, max_tokens, stop=(), **kw):
+    settings = GenerationSettings(max_tokens=max_tokens, stop_token_ids=tuple(stop), **kw)
+    return Request(name, list(range(1, prompt_len + 1)), settings, RequestSampler())
+
+
+def test_prompt_is_cut_into_portions_under_the_token_budget():
+    scheduler, runner, manager = build(max_batch_tokens=16, prefill_chunk_tokens=10)
+    scheduler.submit(request("a", 23, 2))
+    scheduler.run()
+    portions = [[(rid, start, count) for rid, start, count, _ in step] for step in runner.ran]
+    assert portions == [[("a", 0, 10)], [("a", 10, 10)], [("a", 20, 3)], [("a", 23, 1)]]
+    assert runner.ran[1][0][3] == [] and runner.ran[2][0][3] == [2]      # logits only where the prompt ends
+    assert scheduler.finished[0].finish_reason == "length" and len(scheduler.finished[0].output) == 2
+    assert manager.groups[0].pool.free == 64 and manager.free_slots == 16
+    manager.check()
+
+
+def test_decode_rows_come_first_and_prompts_get_the_rest():
+    scheduler, runner, _ = build(max_batch_tokens=12, prefill_chunk_tokens=100)
+    scheduler.submit(request("a", 5, 6))
+    scheduler.step()                                  # a's whole prompt
+    scheduler.submit(request("b", 30, 2))
+    scheduler.step()
+    assert runner.ran[1] == [("a", 5, 1, [0]), ("b", 0, 11, [])]        # budget 12 - 1 decode row
+    scheduler.step()
+    assert runner.ran[2] == [("a", 6, 1, [0]), ("b", 11, 11, [])]
+    scheduler.step()
+    assert runner.ran[3] == [("a", 7, 1, [0]), ("b", 22, 8, [7])]
+    scheduler.step()
+    assert [e[:3] for e in runner.ran[4]] == [("a", 8, 1), ("b", 30, 1)]
+
+
+def test_completion_first_oldest_prompt_takes_the_budget():
+    scheduler, runner, _ = build(max_batch_tokens=20, prefill_chunk_tokens=100)
+    scheduler.submit(request("a", 30, 1))
+    scheduler.submit(request("b", 8, 1))
+    scheduler.step()
+    assert runner.ran[0] == [("a", 0, 20, [])]
+    scheduler.step()
+    assert runner.ran[1] == [("a", 20, 10, [9]), ("b", 0, 8, [7])]
+
+
+def test_stop_token_min_tokens_and_ignore_eos():
+    scheduler, _, _ = build()
+    scheduler.sample = lambda result, samplers: [7 for _ in samplers]
+    scheduler.submit(request("stops", 3, 10, stop=[7]))
+    scheduler.submit(request("min", 3, 10, stop=[7], min_tokens=4))
+    scheduler.submit(request("ignores", 3, 5, stop=[7], ignore_eos=True))
+    scheduler.run()
+    by_name = {r.request_id: r for r in scheduler.finished}
+    assert (by_name["stops"].finish_reason, len(by_name["stops"].output)) == ("stop", 1)
+    assert (by_name["min"].finish_reason, len(by_name["min"].output)) == ("stop", 4)
+    assert (by_name["ignores"].finish_reason, len(by_name["ignores"].output)) == ("length", 5)
+
+
+def test_requests_beyond_the_slots_wait_their_turn_in_order():
+    scheduler, runner, manager = build(max_batch_requests=2)
+    for name in "abcd":
+        scheduler.submit(request(name, 4, 2))
+    scheduler.run()
+    assert [r.request_id for r in scheduler.finished] == ["a", "b", "c", "d"]
+    first_seen = {}
+    for index, step in enumerate(runner.ran):
+        assert len(step) <= 2
+        for rid, *_ in step:
+            first_seen.setdefault(rid, index)
+    assert first_seen["a"] == first_seen["b"] < first_seen["c"] == first_seen["d"]
+    manager.check()
+
+
+def test_a_request_that_can_never_fit_is_refused_at_submission():
+    scheduler, _, _ = build(pages=4, page_size=4)
+    with pytest.raises(KvCapacity):
+        scheduler.submit(request("big", 40, 1))
+    with pytest.raises(SchedulerError, match="at least one prompt token"):
+        scheduler.submit(request("empty", 0, 1))
+    with pytest.raises(SchedulerError, match="max_position_embeddings"):
+        scheduler.submit(request("long", 128, 1))
+
+
+def test_waiting_request_is_admitted_only_when_its_prompt_fits():
+    scheduler, runner, manager = build(pages=10, page_size=4)
+    scheduler.submit(request("a", 30, 3))                 # 8 pages, 9 with its decoded tokens
+    scheduler.submit(request("b", 12, 2))                 # 3 pages: does not fit beside a
+    scheduler.run()
+    first_b = next(i for i, step in enumerate(runner.ran) if any(e[0] == "b" for e in step))
+    last_a = max(i for i, step in enumerate(runner.ran) if any(e[0] == "a" for e in step))
+    assert first_b > last_a                               # b ran on a's pages after a had finished
+    assert manager.groups[0].pool.reused > 0
+    assert {r.request_id: r.finish_reason for r in scheduler.finished} == {"a": "length", "b": "length"}
+
+
+def test_out_of_pages_preempts_the_youngest_and_recomputes_it():
+    scheduler, runner, manager = build(pages=6, page_size=4, out_of_pages="preempt")
+    scheduler.submit(request("old", 8, 12))               # grows to 20 tokens = 5 pages
+    scheduler.submit(request("young", 7, 12))             # 2 pages at admission: both fit at first
+    scheduler.run()
+    by_name = {r.request_id: r for r in scheduler.finished}
+    assert by_name["young"].preemptions >= 1 and by_name["old"].preemptions == 0
+    assert len(by_name["old"].output) == 12 and len(by_name["young"].output) == 12
+    assert by_name["old"].finish_reason == by_name["young"].finish_reason == "length"
+    # after the preemption young was fed again from position 0, with the tokens it had produced
+    restarts = [step for step in runner.ran for e in step if e[0] == "young" and e[1] == 0]
+    assert len(restarts) >= 2
+    assert manager.groups[0].pool.free == 6
+    manager.check()
+
+
+def test_out_of_pages_finish_policy_and_lonely_request():
+    scheduler, _, manager = build(pages=6, page_size=4, out_of_pages="finish")
+    scheduler.submit(request("old", 8, 12))
+    scheduler.submit(request("young", 7, 12))
+    scheduler.run()
+    by_name = {r.request_id: r for r in scheduler.finished}
+    assert by_name["young"].finish_reason == "out_of_pages" and by_name["old"].finish_reason == "length"
+    scheduler, _, manager = build(pages=3, page_size=4)
+    scheduler.submit(request("alone", 8, 30))             # can never hold 38 tokens in 12 slots
+    scheduler.run()
+    lonely = scheduler.finished[0]
+    assert lonely.finish_reason == "out_of_pages" and 0 < len(lonely.output) < 30
+    assert manager.groups[0].pool.free == 3
+    manager.check()
+
+
+def test_cancel_frees_everything():
+    scheduler, _, manager = build()
+    scheduler.submit(request("a", 6, 50))
+    scheduler.submit(request("b", 6, 3))
+    scheduler.step()
+    scheduler.cancel("a")
+    scheduler.run()
+    assert {r.request_id: r.finish_reason for r in scheduler.finished} == {"a": "cancelled", "b": "length"}
+    assert manager.groups[0].pool.free == 64 and manager.free_slots == 16
+
+
+def test_windowed_model_runs_long_requests_in_few_pages():
+    scheduler, runner, manager = build(TINY_C, pages=12, page_size=8, prefill_chunk_tokens=16)
+    scheduler.submit(request("w", 60, 30))                # 90 tokens: 12 pages in the full group
+    scheduler.run()
+    assert scheduler.finished[0].finish_reason == "length"
+    full, windowed = manager.groups
+    assert full.pool.high_water == 12 and windowed.pool.high_water <= (40 + 16) // 8 + 2
+    manager.check()
+
+
+def test_deterministic_schedule():
+    def schedule():
+        scheduler, runner, _ = build(pages=12, page_size=4, max_batch_tokens=9, prefill_chunk_tokens=7)
+        for name, n, m in (("a", 9, 5), ("b", 17, 4), ("c", 3, 8), ("d", 11, 2)):
+            scheduler.submit(request(name, n, m))
+        scheduler.run()
+        return runner.ran
+    assert schedule() == schedule()
