@@ -278,29 +278,26 @@ def sample(logits, draw: float, temperature: float, top_k: int = 0, top_p: float
     if temperature <= np.finfo(np.float32).eps or top_k == 1:
         return greedy(values)
     if top_p >= 1.0 and top_k == 0:
-        weights = np.exp((values - values.max()).astype(np.float64) / temperature)
-        threshold = draw * weights.sum()
-        for token, weight in enumerate(weights):
-            threshold -= weight
-            if threshold <= 0.0:
-                return token
-        return len(weights) - 1
-    order = np.argsort(-values.astype(np.float64), kind="stable")
+        finite = np.isfinite(values)
+        weights = np.where(finite, np.exp((values - values[finite].max()).astype(np.float64) / temperature), 0.0)
+        return _first_reaching(weights, draw * weights.sum())
+    candidates = np.flatnonzero(np.isfinite(values))
+    order = candidates[np.argsort(-values[candidates].astype(np.float64), kind="stable")]
     weights = np.exp((values[order] - values[order[0]]).astype(np.float64) / temperature)
-    total = weights.sum()
     keep = len(order)
-    cumulative = 0.0
-    for rank, weight in enumerate(weights):
-        cumulative += weight / total
-        if cumulative >= top_p:
-            keep = rank + 1
-            break
+    if top_p < 1.0:
+        keep = _first_reaching(weights / weights.sum(), top_p) + 1
     if top_k > 0:
         keep = min(keep, top_k)
     weights, order = weights[:keep], order[:keep]
-    threshold = draw * weights.sum()
-    for token, weight in zip(order, weights):
-        threshold -= weight
-        if threshold <= 0.0:
-            return int(token)
-    return int(order[-1])
+    return int(order[_first_reaching(weights, draw * weights.sum())])
+
+
+def _first_reaching(weights, threshold: float) -> int:
+    """The walk `threshold -= w; stop when threshold <= 0` of runtime/src/sampling/mod.rs:104-113,226-238:
+    the first index whose running sum (accumulated in order, in float64) reaches the threshold; the last
+    index if rounding leaves none."""
+    if threshold <= 0.0:
+        return 0
+    reached = np.flatnonzero(np.cumsum(weights) >= threshold)
+    return int(reached[0]) if reached.size else len(weights) - 1

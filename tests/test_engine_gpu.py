@@ -1,0 +1,172 @@
+"""The engine in-process against the plain implementation: the first tokens of a sequence, long
+decoding, a page's edge, greedy and sampled generation through the entry point."""
+
+import numpy as np
+import pytest
+import torch
+
+import plain_impl
+from helpers import TOL, make_folder, plain_logits, random_ids
+from tiny_configs import ALL, TINY_A, TINY_B, TINY_C
+
+pytestmark = pytest.mark.gpu
+
+
+def load(folder, dtype, pages=64, page_size=16, **scheduler):
+    from libmir_b200 import CacheConfig, Library, RuntimeConfig, SchedulerConfig
+    return Library(RuntimeConfig(kv_cache=CacheConfig(block_size=page_size, block_count=pages),
+                                 scheduler=SchedulerConfig(**scheduler), dtype=dtype)).load(folder)
+
+
+def check(got, want, tol, label):
+    error = float(np.abs(got - want).max())
+    scale = max(1.0, float(np.abs(want).max()))
+    assert np.isfinite(got).all() and error <= tol * scale, f"{label}: max |diff| {error:.3e} > {tol * scale:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_first_tokens_of_a_sequence_one_by_one(tmp_path, name, dtype):
+    from libmir_b200 import StepEntry
+    config = ALL[name]
+    folder = make_folder(tmp_path, config, seed=3, dtype=dtype, sharpen=6.0)
+    ids = random_ids(np.random.default_rng(0), config["vocab_size"], 20)
+    reference = plain_logits(folder, ids)
+    model = load(folder, dtype, page_size=4)
+    model.admit("r")
+    for position, token in enumerate(ids):
+        result = model.step([StepEntry("r", [token], [0])])
+        check(result.logits.cpu().numpy()[0], reference[position], TOL[dtype], f"{name}/{dtype} position {position}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_with_windows_and_small_pages(tmp_path, dtype):
+    """700 tokens decoded one by one after a 60-token prompt on the model with sliding-window layers:
+    the window (40) passes many pages (8 tokens each), which go back to the pool and are used again."""
+    from libmir_b200 import StepEntry
+    folder = make_folder(tmp_path, TINY_C, seed=4, dtype=dtype, sharpen=6.0)
+    ids = random_ids(np.random.default_rng(1), TINY_C["vocab_size"], 760)
+    reference = plain_logits(folder, ids)
+    model = load(folder, dtype, pages=100, page_size=8)
+    model.admit("r")
+    result = model.step([StepEntry("r", ids[:60], [59])])
+    check(result.logits.cpu().numpy()[0], reference[59], TOL[dtype], "prompt")
+    for position in range(60, 760):
+        result = model.step([StepEntry("r", [ids[position]], [0])])
+        if position % 7 == 0 or position > 740:
+            check(result.logits.cpu().numpy()[0], reference[position], TOL[dtype], f"{dtype} position {position}")
+    full, windowed = model.cache_stats()["groups"]
+    assert full["high_water"] == 95 and windowed["high_water"] <= 8
+    model.release("r")
+    model.admit("again")                                    # the next request runs on pages used before
+    result = model.step([StepEntry("again", ids[:100], [99])])
+    check(result.logits.cpu().numpy()[0], reference[99], TOL[dtype], "reused pages")
+    assert model.cache_stats()["groups"][0]["reused"] > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_portion_that_ends_and_starts_at_a_pages_edge(tmp_path, dtype):
+    from libmir_b200 import StepEntry
+    folder = make_folder(tmp_path, TINY_B, seed=6, dtype=dtype, sharpen=6.0)
+    ids = random_ids(np.random.default_rng(2), TINY_B["vocab_size"], 50)
+    reference = plain_logits(folder, ids)
+    model = load(folder, dtype, page_size=8)
+    model.admit("r")
+    cursor = 0
+    for size in (8, 8, 1, 7, 16, 2, 8):                     # edges at 8, 16, 24, 40, 48
+        result = model.step([StepEntry("r", ids[cursor:cursor + size], range(size))])
+        check(result.logits.cpu().numpy(), reference[cursor:cursor + size], TOL[dtype], f"portion at {cursor}")
+        cursor += size
+
+
+def test_float32_logits_do_not_depend_on_the_cut_or_the_batch_at_all(tmp_path):
+    """In 32-bit every reduction's order is fixed by the token's own position, so the same position
+    gives bit-identical logits whole, decoded, in portions and beside other requests."""
+    from libmir_b200 import StepEntry
+    folder = make_folder(tmp_path, TINY_C, seed=8, dtype="float32", sharpen=6.0)
+    rng = np.random.default_rng(3)
+    ids, other = (random_ids(rng, TINY_C["vocab_size"], n) for n in (90, 70))
+    model = load(folder, "float32", page_size=8)
+    model.admit("whole")
+    whole = model.step([StepEntry("whole", ids, range(90))]).logits.cpu().numpy()
+    model.admit("cut"); model.admit("other")
+    rows = []
+    cursor = 0
+    for size in (13, 2, 30, 1, 1, 20, 23):
+        entries = [StepEntry("cut", ids[cursor:cursor + size], range(size))]
+        if cursor < 60:
+            entries.insert(0, StepEntry("other", other[cursor:cursor + 9], [0]))
+        result = model.step(entries)
+        rows.append(result.logits.cpu().numpy()[-size:])
+        cursor += size
+    assert np.array_equal(np.concatenate(rows), whole)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
+    """BASELINE workloads: prompts of 5/11/17 (A) and 1/9/33/64 (B) tokens, greedy, against the plain
+    implementation decoding the same way (whole sequence recomputed for every token)."""
+    from libmir_b200 import GenerationOverrides, GenerationRequest
+    config = ALL[name]
+    folder = make_folder(tmp_path, config, seed=0 if name == "A" else 1, dtype=dtype, sharpen=6.0)
+    rng = np.random.default_rng(7)
+    lengths = [5, 11, 17] if name == "A" else [1, 9, 33, 64]
+    prompts = [random_ids(rng, config["vocab_size"], n) for n in lengths]
+    model = load(folder, dtype, page_size=16 if name == "A" else 8, prefill_chunk_tokens=16)
+    outputs = model.generate_batch([GenerationRequest(p, GenerationOverrides(max_tokens=8)) for p in prompts])
+    plain_config, weights = plain_impl.read_model(folder)
+    for prompt, output in zip(prompts, outputs):
+        assert output.finish_reason == "length" and len(output.token_ids) == 8
+        tokens = list(prompt)
+        for step, token in enumerate(output.token_ids):
+            logits = plain_impl.forward(plain_config, weights, tokens)[-1].numpy()
+            best = plain_impl.greedy(logits)
+            if token != best:                                  # allowed only on a near-tie in bfloat16
+                margin = logits[best] - logits[token]
+                assert dtype == "bfloat16" and margin <= 2 * TOL[dtype] * max(1.0, np.abs(logits).max()), (
+                    f"{name}/{dtype}: token {step} is {token}, plain says {best} (margin {margin:.3e})")
+            tokens.append(token)
+    assert model.cache_stats()["groups"][0]["free"] == 64
+
+
+def test_sampled_generation_follows_the_plain_sampler(tmp_path):
+    """Temperature 0.7, top-k/top-p and a repetition penalty: with the same seed the engine must pick the
+    token the plain sampler picks from the plain logits, draw by draw (32-bit)."""
+    from libmir_b200 import GenerationOverrides, GenerationRequest
+    folder = make_folder(tmp_path, TINY_B, seed=1, dtype="float32", sharpen=6.0)
+    rng = np.random.default_rng(9)
+    prompts = [random_ids(rng, TINY_B["vocab_size"], n) for n in (1, 9, 33, 64)]
+    options = [GenerationOverrides(max_tokens=12, temperature=0.7),
+               GenerationOverrides(max_tokens=12, temperature=0.7, top_k=5),
+               GenerationOverrides(max_tokens=12, temperature=1.3, top_p=0.8),
+               GenerationOverrides(max_tokens=12, temperature=0.9, top_k=40, top_p=0.9, repetition_penalty=1.3)]
+    model = load(folder, "float32", page_size=8, prefill_chunk_tokens=16)
+    outputs = model.generate_batch([GenerationRequest(p, o, seed=100 + i)
+                                    for i, (p, o) in enumerate(zip(prompts, options))])
+    plain_config, weights = plain_impl.read_model(folder)
+    for index, (prompt, option, output) in enumerate(zip(prompts, options, outputs)):
+        generator = plain_impl.SplitMix64(100 + index)
+        tokens = list(prompt)
+        for step, token in enumerate(output.token_ids):
+            logits = plain_impl.forward(plain_config, weights, tokens)[-1].numpy()
+            expected = plain_impl.sample(logits, generator.next_unit(), option.temperature, option.top_k or 0,
+                                         option.top_p or 1.0, option.repetition_penalty or 1.0, tokens)
+            assert token == expected, f"request {index} token {step}: engine {token}, plain sampler {expected}"
+            tokens.append(token)
+
+
+def test_session_prefill_and_decode(tmp_path):
+    from libmir_b200 import SamplingLogits
+    folder = make_folder(tmp_path, TINY_A, seed=2, dtype="float32")
+    ids = random_ids(np.random.default_rng(4), 256, 12)
+    reference = plain_logits(folder, ids)
+    model = load(folder, "float32")
+    with model.session() as session:
+        out = session.prefill(ids[:8], SamplingLogits.FULL)
+        check(out.logits, reference[7], TOL["float32"], "session prefill")
+        assert out.cached_tokens == 8
+        out = session.decode(ids[8], SamplingLogits.TOKEN)
+        assert out.next_token == plain_impl.greedy(reference[8]) and session.cache_stats()["cached_tokens"] == 9
+    assert model.cache_stats()["live_requests"] == 0
+    model.unload()

@@ -1,0 +1,339 @@
+"""Each kernel alone against its plain reference, at other sizes than the engine's tiny models use."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_impl
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 1e-5, torch.bfloat16: 1.6e-2}      # relative to the largest reference value
+
+
+def cuda(t, dtype=None):
+    return t.to("cuda", dtype) if dtype is not None else t.to("cuda")
+
+
+def close(got, want, dtype, scale=None, factor=1.0):
+    want = want.double().cpu()
+    got = got.double().cpu()
+    bound = TOL[dtype] * factor * max(1.0, float(want.abs().max()) if scale is None else scale)
+    error = float((got - want).abs().max())
+    assert torch.isfinite(got).all() and error <= bound, f"max |diff| {error:.3e} > {bound:.3e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(dtype):
+    from libmir_b200 import kernels
+    torch.manual_seed(0)
+    table = torch.randn(1000, 200).to(dtype)
+    ids = torch.tensor([0, 999, 17, 17, 500], dtype=torch.int32)
+    out = torch.empty(5, 200, device="cuda")
+    kernels.embed(cuda(table), cuda(ids), out, 1.7)
+    expected = plain_impl.embedding(table, ids.tolist(), 1.7)
+    close(out, expected, torch.float32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [72, 5000])
+def test_rms_norm_with_and_without_row_gather(dtype, hidden):
+    from libmir_b200 import kernels
+    torch.manual_seed(1)
+    x = torch.randn(9, hidden) * 3
+    weight = torch.randn(hidden)
+    out = torch.empty(9, hidden, device="cuda", dtype=dtype)
+    kernels.rms_norm(cuda(x), cuda(weight), 1e-3, out)
+    close(out, plain_impl.rms_norm(x.double(), weight, 1e-3), dtype)
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32)
+    out = torch.empty(3, hidden, device="cuda", dtype=dtype)
+    kernels.rms_norm(cuda(x), cuda(weight), 1e-3, out, cuda(rows))
+    close(out, plain_impl.rms_norm(x.double()[rows.long()], weight, 1e-3), dtype)
+
+
+def test_rms_norm_is_exact_to_bf16_rounding():
+    """libmir's own kernel test asserts exact bf16 equality with the host formula
+    (cuda/src/kernels/decoder/tests/mod.rs:10-33); the same here up to one bf16 ulp of the float64 result."""
+    from libmir_b200 import kernels
+    torch.manual_seed(2)
+    x, weight = torch.randn(4, 256), torch.randn(256)
+    out = torch.empty(4, 256, device="cuda", dtype=torch.bfloat16)
+    kernels.rms_norm(cuda(x), cuda(weight), 1e-5, out)
+    exact = plain_impl.rms_norm(x.double(), weight, 1e-5)
+    rounded = exact.to(torch.bfloat16)
+    different = (out.cpu() != rounded)
+    assert different.float().mean() < 0.01            # only values that sit on a rounding boundary
+    assert ((out.cpu().double() - exact).abs() <= exact.abs() * 2 ** -7).all()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    from libmir_b200 import kernels
+    torch.manual_seed(3)
+    gate_up = (torch.randn(7, 2 * 333) * 4).to(dtype)
+    out = torch.empty(7, 333, device="cuda", dtype=dtype)
+    kernels.silu_mul(cuda(gate_up), out)
+    g, u = gate_up.double()[:, :333], gate_up.double()[:, 333:]
+    close(out, plain_impl.silu(g) * u, dtype)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 101, 77), (37, 130, 200), (130, 64, 16), (65, 3, 1000)])
+def test_gemm_f32_is_true_32_bit(m, n, k):
+    from libmir_b200 import kernels
+    torch.manual_seed(4)
+    x, w, bias = torch.randn(m, k), torch.randn(n, k), torch.randn(n)
+    out = torch.empty(m, n, device="cuda")
+    kernels.linear(cuda(x), cuda(w), out, cuda(bias))
+    exact = plain_impl.linear(x.double(), w, bias)
+    # float32 FMA chain over k terms: error ~ k * 6e-8 * |terms|; TF32 (10-bit mantissa) would be ~1e-3
+    assert float((out.double().cpu() - exact).abs().max()) <= 2e-7 * k * float(exact.abs().max() + 1)
+    base = torch.randn(m, n)
+    out = cuda(base.clone())
+    kernels.linear(cuda(x), cuda(w), out, accumulate=True)
+    close(out, base.double() + plain_impl.linear(x.double(), w), torch.float32, factor=3)
+    # a strided view as input (the q part of packed rows) and as output
+    wide = torch.randn(m, k + 24)
+    out_wide = torch.zeros(m, n + 8, device="cuda")
+    kernels.linear(cuda(wide)[:, 8:8 + k], cuda(w), out_wide[:, :n])
+    close(out_wide[:, :n], plain_impl.linear(wide.double()[:, 8:8 + k], w), torch.float32, factor=3)
+    assert float(out_wide[:, n:].abs().max()) == 0.0
+
+
+def test_gemm_f32_rows_do_not_depend_on_the_batch():
+    from libmir_b200 import kernels
+    torch.manual_seed(5)
+    x, w = cuda(torch.randn(150, 333)), cuda(torch.randn(97, 333))
+    whole = torch.empty(150, 97, device="cuda")
+    kernels.linear(x, w, whole)
+    for begin, end in ((0, 1), (63, 66), (149, 150), (10, 140)):
+        part = torch.empty(end - begin, 97, device="cuda")
+        kernels.linear(x[begin:end], w, part)
+        assert torch.equal(part, whole[begin:end])
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 136, 264), (8, 200, 72), (50, 136, 264), (300, 520, 128)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_bf16(m, n, k, out_dtype):
+    from libmir_b200 import kernels
+    torch.manual_seed(6)
+    x, w = torch.randn(m, k).bfloat16(), torch.randn(n, k).bfloat16()
+    bias = torch.randn(n).to(out_dtype)
+    out = torch.empty(m, n, device="cuda", dtype=out_dtype)
+    kernels.linear(cuda(x), cuda(w), out, cuda(bias))
+    exact = plain_impl.linear(x.double(), w, bias)
+    close(out, exact, out_dtype if out_dtype == torch.bfloat16 else torch.float32, factor=4)
+    if out_dtype == torch.float32:                         # the residual epilogue: out += x w^T
+        base = torch.randn(m, n)
+        out = cuda(base.clone())
+        kernels.linear(cuda(x), cuda(w), out, accumulate=True)
+        close(out, base.double() + plain_impl.linear(x.double(), w), torch.float32, factor=4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,dim,rotary,norm", [(3, 1, 48, 24, True), (4, 4, 16, 16, False),
+                                                           (10, 5, 128, 128, True), (2, 1, 256, 64, False)])
+def test_qk_norm_rope_and_cache_write(dtype, heads, kv_heads, dim, rotary, norm):
+    from libmir_b200 import kernels
+    torch.manual_seed(7)
+    tokens, page, pages = 11, 4, 9
+    qkv = torch.randn(tokens, (heads + 2 * kv_heads) * dim).to(dtype)
+    positions = torch.tensor([0, 1, 2, 3, 4, 900, 901, 7, 8, 9, 10], dtype=torch.int32)
+    slots = torch.tensor([4, 5, 6, 7, 20, 21, -1, 0, 1, 2, 3], dtype=torch.int32)
+    frequencies = plain_impl.rope_inverse_frequencies(rotary, 50000.0, None)
+    q_weight = torch.randn(dim) if norm else None
+    k_weight = torch.randn(dim) if norm else None
+    k_pages = torch.full((pages * page, kv_heads, dim), 7.0, device="cuda", dtype=dtype)
+    v_pages = torch.full((pages * page, kv_heads, dim), 7.0, device="cuda", dtype=dtype)
+    device_qkv = cuda(qkv.clone())
+    kernels.qk_rope_store(device_qkv, cuda(positions), cuda(slots), cuda(frequencies),
+                          None if q_weight is None else cuda(q_weight), None if k_weight is None else cuda(k_weight),
+                          k_pages, v_pages, heads, kv_heads, dim, rotary, 1e-4)
+    wide = qkv.double()
+    q = wide[:, :heads * dim].reshape(tokens, heads, dim)
+    k = wide[:, heads * dim:(heads + kv_heads) * dim].reshape(tokens, kv_heads, dim)
+    v = wide[:, (heads + kv_heads) * dim:].reshape(tokens, kv_heads, dim)
+    if norm:
+        q, k = plain_impl.rms_norm(q, q_weight, 1e-4), plain_impl.rms_norm(k, k_weight, 1e-4)
+    q, k = plain_impl.rope(q, positions, frequencies), plain_impl.rope(k, positions, frequencies)
+    close(device_qkv[:, :heads * dim].reshape(tokens, heads, dim), q, dtype)
+    close(device_qkv[:, heads * dim:], wide[:, heads * dim:], dtype)          # k and v columns are not touched
+    for token, slot in enumerate(slots.tolist()):
+        if slot < 0:
+            continue
+        close(k_pages[slot], k[token], dtype)
+        close(v_pages[slot], v[token], dtype)
+    untouched = sorted(set(range(pages * page)) - set(s for s in slots.tolist() if s >= 0))
+    assert torch.all(k_pages[untouched] == 7.0) and torch.all(v_pages[untouched] == 7.0)
+
+
+def paged(k, v, page, pages_total, rng):
+    """Scatter one request's keys/values [S, H, D] into shuffled pages; returns pages and its table."""
+    seq = k.shape[0]
+    blocks = -(-seq // page)
+    order = rng.permutation(pages_total)[:blocks]
+    k_pages = torch.randn(pages_total * page, *k.shape[1:], dtype=k.dtype) * 50     # garbage elsewhere
+    v_pages = torch.randn(pages_total * page, *v.shape[1:], dtype=v.dtype) * 50
+    for block, physical in enumerate(order):
+        chunk = slice(block * page, min(seq, (block + 1) * page))
+        n = chunk.stop - chunk.start
+        k_pages[physical * page: physical * page + n] = k[chunk]
+        v_pages[physical * page: physical * page + n] = v[chunk]
+    return k_pages, v_pages, order
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,dim,page,window", [
+    (6, 3, 48, 4, None), (4, 1, 16, 16, None), (8, 8, 80, 8, 37), (32, 8, 128, 16, None), (2, 1, 256, 16, 100),
+    (5, 5, 64, 1, None), (16, 2, 128, 16, 64)])
+def test_paged_attention_prompt_portions_and_decoded_tokens(dtype, heads, kv_heads, dim, page, window):
+    """Two requests in one batch: a portion of 40 tokens that starts at position 150 (history in the
+    cache), and one decoded token at position 299.  Pages are shuffled and the rest of the pool holds
+    large garbage, so a wrong page or slot shows."""
+    from libmir_b200 import kernels
+    rng = np.random.default_rng(0)
+    torch.manual_seed(8)
+    lengths = [190, 300]
+    starts = [150, 299]
+    scale = 0.7 / math.sqrt(dim)
+    qs, ks, vs = [], [], []
+    for n in lengths:
+        qs.append((torch.randn(n, heads, dim) * 2).to(dtype))
+        ks.append((torch.randn(n, kv_heads, dim) * 2).to(dtype))
+        vs.append(torch.randn(n, kv_heads, dim).to(dtype))
+    total_pages = 2 * (300 // page + 2)
+    k_pool = torch.randn(total_pages * page, kv_heads, dim).to(dtype) * 50
+    v_pool = torch.randn(total_pages * page, kv_heads, dim).to(dtype) * 50
+    order = rng.permutation(total_pages)
+    width = -(-300 // page)
+    table = torch.full((2, width), -1, dtype=torch.int32)
+    cursor = 0
+    for r, n in enumerate(lengths):
+        blocks = -(-n // page)
+        for block in range(blocks):
+            physical = int(order[cursor]); cursor += 1
+            table[r, block] = physical
+            chunk = slice(block * page, min(n, (block + 1) * page))
+            k_pool[physical * page: physical * page + chunk.stop - chunk.start] = ks[r][chunk]
+            v_pool[physical * page: physical * page + chunk.stop - chunk.start] = vs[r][chunk]
+    q_rows = torch.cat([qs[0][150:190], qs[1][299:300]]).reshape(41, heads * dim)
+    packed = torch.cat([q_rows, torch.randn(41, 2 * kv_heads * dim).to(dtype)], dim=1).contiguous()
+    positions = torch.tensor(list(range(150, 190)) + [299], dtype=torch.int32)
+    rows = torch.tensor([0] * 40 + [1], dtype=torch.int32)
+    out = torch.empty(41, heads * dim, device="cuda", dtype=dtype)
+    kernels.paged_attention_generic(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table), cuda(rows),
+                                    cuda(positions), page, heads, kv_heads, dim, scale, window)
+    expected = torch.cat([
+        plain_impl.attention_scores_softmax_values(qs[0].double(), ks[0].double(), vs[0].double(), scale, window)[150:190],
+        plain_impl.attention_scores_softmax_values(qs[1].double(), ks[1].double(), vs[1].double(), scale, window)[299:300]])
+    close(out.reshape(41, heads, dim), expected, dtype, factor=2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_sees_one_far_key_among_hundreds_and_the_windows_edge(dtype):
+    """Scores are made so that ONE key dominates: the output must be that key's value.  Placed at the
+    first key, at a page's first and last slot, at the first key inside the window and (invisible) at the
+    last key outside it."""
+    from libmir_b200 import kernels
+    heads, kv_heads, dim, page, n = 4, 2, 64, 16, 600
+    torch.manual_seed(9)
+    direction = torch.randn(dim)
+    direction /= direction.norm()
+
+    def run(strong_key, window):
+        k = torch.randn(n, kv_heads, dim) * 0.05
+        k[strong_key] = direction * 8.0
+        v = torch.randn(n, kv_heads, dim)
+        q = direction.repeat(1, heads, 1) * 8.0                      # score 64 * scale at the strong key
+        k, v, q = k.to(dtype), v.to(dtype), q.to(dtype)
+        table = torch.arange(-(-n // page), dtype=torch.int32).flip(0).reshape(1, -1).contiguous()
+        k_pool = torch.zeros(table.numel() * page, kv_heads, dim, dtype=dtype)
+        v_pool = torch.zeros_like(k_pool)
+        for block in range(table.numel()):
+            physical = int(table[0, block])
+            chunk = slice(block * page, min(n, (block + 1) * page))
+            k_pool[physical * page: physical * page + chunk.stop - chunk.start] = k[chunk]
+            v_pool[physical * page: physical * page + chunk.stop - chunk.start] = v[chunk]
+        packed = torch.cat([q.reshape(1, -1), torch.zeros(1, 2 * kv_heads * dim, dtype=dtype)], dim=1)
+        out = torch.empty(1, heads * dim, device="cuda", dtype=dtype)
+        kernels.paged_attention_generic(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table),
+                                        cuda(torch.zeros(1, dtype=torch.int32)),
+                                        cuda(torch.tensor([n - 1], dtype=torch.int32)), page, heads, kv_heads, dim,
+                                        1.0, window)
+        return out.reshape(heads, dim).float().cpu(), v.float()
+
+    for strong in (0, 15, 16, 31, 300, n - 1):
+        out, v = run(strong, None)
+        for head in range(heads):
+            assert torch.allclose(out[head], v[strong, head // 2], atol=2e-2), f"key {strong} was not seen"
+    window = 100                                                      # visible keys: n - 100 .. n - 1
+    out, v = run(n - window, window)
+    assert torch.allclose(out[0], v[n - window, 0], atol=2e-2), "the first key inside the window was not seen"
+    out, v = run(n - window - 1, window)
+    assert not torch.allclose(out[0], v[n - window - 1, 0], atol=0.3), "a key outside the window was seen"
+
+
+def test_kernels_refuse_sizes_they_do_not_take():
+    from libmir_b200 import KernelError, kernels
+    q = torch.zeros(1, 3 * 20, device="cuda")
+    with pytest.raises(KernelError, match="head_dim 20"):
+        kernels.paged_attention_generic(q, torch.zeros(1, 20, device="cuda"), torch.zeros(4, 1, 20, device="cuda"),
+                                        torch.zeros(4, 1, 20, device="cuda"),
+                                        torch.zeros(1, 1, dtype=torch.int32, device="cuda"),
+                                        torch.zeros(1, dtype=torch.int32, device="cuda"),
+                                        torch.zeros(1, dtype=torch.int32, device="cuda"), 4, 1, 1, 20, 1.0, None)
+    with pytest.raises(KernelError, match="CUDA tensors only"):
+        kernels.silu_mul(torch.zeros(1, 4), torch.zeros(1, 2))
+    with pytest.raises(KernelError, match="shapes or strides"):
+        kernels.linear(torch.zeros(2, 8, device="cuda"), torch.zeros(4, 9, device="cuda"),
+                       torch.zeros(2, 4, device="cuda"))
+
+
+# ------------------------------------------------------------------------------ sampling
+def device_sample(logits, options):
+    from libmir_b200 import kernels
+    rows = logits.shape[0]
+    host = np.zeros(rows, dtype=kernels.SAMPLE_OPTIONS)
+    for r, (draw, temperature, top_k, top_p) in enumerate(options):
+        host[r] = (draw, temperature, top_p, top_k, 0)
+    tokens = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ranked = any(t > 1.2e-7 and k != 1 and not (k == 0 and p >= 1.0) for _, t, k, p in options)
+    keys = torch.empty(kernels.ranked_scratch_keys(rows, logits.shape[1]), dtype=torch.int64, device="cuda")
+    kernels.sample(cuda(logits), torch.from_numpy(host.view(np.uint8)).cuda(), tokens, keys if ranked else None,
+                   ranked)
+    return tokens.cpu().tolist()
+
+
+def test_greedy_ties_go_to_the_lowest_id():
+    logits = torch.full((3, 5003), -1.0)
+    logits[0, [4000, 17, 2500]] = 3.0
+    logits[1, 5002] = 0.5
+    logits[2, 0] = float("inf")
+    logits[2, 9] = 2.0                                            # non-finite logits are not candidates
+    assert device_sample(logits, [(0.0, 0.0, 0, 1.0)] * 3) == [17, 5002, 9]
+    assert device_sample(logits, [(0.7, 0.9, 1, 1.0)] * 3) == [17, 5002, 9]       # top_k == 1 is greedy
+
+
+@pytest.mark.parametrize("vocab", [5, 384, 151936])
+def test_sampling_picks_what_the_plain_sampler_picks(vocab):
+    rng = np.random.default_rng(vocab)
+    rows = 12
+    logits = torch.from_numpy(rng.normal(0, 2.5, size=(rows, vocab)).astype(np.float32))
+    modes = [(0.7, 0, 1.0), (1.0, 0, 1.0), (0.3, 0, 1.0), (0.7, 5, 1.0), (0.7, 0, 0.8), (1.5, 50, 0.9),
+             (0.9, 3, 0.5), (2.0, 0, 0.3), (0.7, 1000000, 0.95), (1.0, 2, 1.0), (0.5, 0, 0.999), (1.0, 64, 0.1)]
+    for draws in ([0.0] * rows, rng.random(rows).tolist(), rng.random(rows).tolist(), [0.999999] * rows):
+        options = [(draw, t, k, p) for draw, (t, k, p) in zip(draws, modes)]
+        got = device_sample(logits, options)
+        want = [plain_impl.sample(logits[r].numpy(), draw, t, k, p) for r, (draw, t, k, p) in enumerate(options)]
+        assert got == want
+
+
+def test_repetition_penalty_rewrites_the_rows_logits():
+    from libmir_b200 import kernels
+    logits = torch.tensor([[2.0, -1.0, 0.5, 3.0], [1.0, 1.0, -2.0, 0.0]])
+    device = cuda(logits.clone())
+    kernels.repetition_penalty(device, cuda(torch.tensor([3, 1, 2], dtype=torch.int32)),
+                               cuda(torch.tensor([0, 0, 1], dtype=torch.int32)), cuda(torch.tensor([2.0, 1.5])))
+    assert device.cpu().tolist() == [[2.0, -2.0, 0.5, 1.5], [1.0, 1.0, -3.0, 0.0]]
