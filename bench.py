@@ -1,0 +1,299 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Qwen3-4B sizes on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  `value` is decoded tokens per second at batch 8 with 2,048 tokens of context
+per request, timed on the device over exactly K decode steps that run back to back (each step's
+sampled token is the next step's input on the device).  `e2e` is the same through the Python entry
+point with host token ids in and out every step.  `prefill` is one 2,048-token prompt in one step.
+`points` has decode at batch 1 and 64.  Weights are random (N(0, 0.02), seeded), token ids are seeded
+uniform random, and the cache of the decode runs is filled with random keys and values of the stated
+context length (a decode step's cost does not depend on the values).
+
+The engine runs on one GPU: for --gpus N > 1 a line says so and the exit code is 2.
+The reference (mirmir-tech/libmir) is a Rust workspace with crates.io-only dependencies; it cannot be
+installed offline with pip, so `--impl reference` prints an `unavailable` line and exits 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_4B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "hidden_size": 2560, "intermediate_size": 9728, "num_hidden_layers": 36,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 151936,
+    "max_position_embeddings": 40960, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "tie_word_embeddings": True, "hidden_act": "silu",
+}
+PROMPT_TOKENS = 2048
+GENERATED_TOKENS = 256
+PAGE_SIZE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            data = json.load(open(path))
+            flat = {}
+
+            def walk(node):
+                if isinstance(node, dict):
+                    for key, value in node.items():
+                        if isinstance(value, (int, float)) and key in FALLBACK_PEAKS:
+                            flat.setdefault(key, float(value))
+                        else:
+                            walk(value)
+            walk(data)
+            if "hbm_gbs" in flat and "bf16_tflops" in flat:
+                return {**FALLBACK_PEAKS, **flat}, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.index = index
+        self.samples = []
+        self.process = None
+
+    def __enter__(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.process = None
+        return self
+
+    def _read(self):
+        for line in self.process.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.process is not None:
+            self.process.terminate()
+            try:
+                self.process.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.process.kill()
+
+    def summary(self):
+        clocks, reasons, maximum = [], set(), None
+        for sm, sm_max, hw, hw_thermal, sw_thermal, power in self.samples:
+            try:
+                clocks.append(float(sm))
+                maximum = float(sm_max)
+            except ValueError:
+                continue
+            for name, value in (("hw_slowdown", hw), ("hw_thermal_slowdown", hw_thermal),
+                                ("sw_thermal_slowdown", sw_thermal), ("sw_power_cap", power)):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": maximum,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--skip-points", action="store_true", help="only the batch-8 decode and the prefill")
+    args = parser.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "mirmir-tech/libmir is a Rust workspace (no setup.py/pyproject; cargo, rustc and its "
+                          "crates.io dependencies mircuda/mirtal/mircup are absent offline): pip cannot install it"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on ONE GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import numpy as np
+    import torch
+
+    from libmir_b200 import CacheConfig, CudaConfig, Library, RuntimeConfig, SchedulerConfig, StepEntry, kernels
+    from libmir_b200.sampling import RequestSampler
+
+    peaks, peaks_kind = read_peaks()
+    config = dict(QWEN3_4B)
+    layers_full = config["num_hidden_layers"]
+    if args.layers:
+        config["num_hidden_layers"] = args.layers
+    layers = config["num_hidden_layers"]
+    max_batch = max(64, args.batch)
+    context_limit = PROMPT_TOKENS + GENERATED_TOKENS + args.steps + args.warmup + 64
+    pages = max_batch * (-(-context_limit // PAGE_SIZE)) + 64
+    runtime = RuntimeConfig(kv_cache=CacheConfig(block_size=PAGE_SIZE, block_count=pages),
+                            scheduler=SchedulerConfig(max_batch_requests=max_batch, max_batch_tokens=8192,
+                                                      prefill_chunk_tokens=4096),
+                            cuda=CudaConfig(decode_graphs=True), dtype="bfloat16")
+    torch.cuda.set_device(0)
+    model = Library(runtime).load_random(config, seed=0)
+    rng = np.random.default_rng(0)
+    vocab = config["vocab_size"]
+    for buffer in model.storage.buffers:                      # synthetic cache content
+        buffer.normal_(0.0, 0.5)
+    kv_bytes_per_token = sum(len(g.entries) * 2 * g.requirement.kv_heads * g.requirement.head_dim * 2
+                             for g in model.cache.groups)
+    weight_bytes = model.decoder.weight_bytes_per_step()
+
+    def fill(batch):
+        ids = []
+        for index in range(batch):
+            request_id = f"d{batch}-{index}"
+            seq = model.cache.admit(request_id)
+            model.cache.grow(seq, PROMPT_TOKENS)
+            model.cache.commit(seq, PROMPT_TOKENS)
+            ids.append(request_id)
+        return ids
+
+    def release(ids):
+        for request_id in ids:
+            model.release(request_id)
+
+    def event_pair():
+        return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def decode_device(batch, steps, warmup):
+        """K back-to-back decode steps on the device; returns (tokens/s, ms per step, launches, clocks)."""
+        ids = fill(batch)
+        samplers = [RequestSampler() for _ in ids]
+        tokens = rng.integers(0, vocab, size=batch).tolist()
+        entries = [StepEntry(i, [t], [0]) for i, t in zip(ids, tokens)]
+        out = model.decode_many(entries, samplers, warmup)
+        entries = [StepEntry(i, [int(t)], [0]) for i, t in zip(ids, out[-1].tolist())]
+        torch.cuda.synchronize()
+        launches = kernels.LAUNCHES
+        start, stop = event_pair()
+        with ClockSampler() as clocks:
+            torch.cuda.synchronize()
+            start.record()
+            model.decode_many(entries, samplers, steps)
+            stop.record()
+            torch.cuda.synchronize()
+        ms = start.elapsed_time(stop)
+        launches = kernels.LAUNCHES - launches
+        context = PROMPT_TOKENS + warmup + steps / 2.0
+        release(ids)
+        return batch * steps / (ms / 1e3), ms / steps, launches, clocks.summary(), context
+
+    def decode_e2e(batch, steps, warmup):
+        """The same through Model.step: host ids in, sampled ids out, every step."""
+        ids = fill(batch)
+        samplers = [RequestSampler() for _ in ids]
+        tokens = rng.integers(0, vocab, size=batch).tolist()
+        h2d = d2h = 0
+        started = None
+        for step in range(warmup + steps):
+            if step == warmup:
+                torch.cuda.synchronize()
+                started = time.perf_counter()
+            result = model.step([StepEntry(i, [t], [0]) for i, t in zip(ids, tokens)], samplers)
+            tokens = result.tokens.cpu().tolist()
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - started
+        graphs = model.runner._graphs.graphs if model.runner._graphs else {}
+        for graph in graphs.values():
+            if graph.rows >= batch:
+                h2d = max(h2d, graph.staging.numel() * 4)
+        d2h = batch * 4
+        release(ids)
+        return batch * steps / seconds, h2d, d2h
+
+    def prefill(repeats=5):
+        tokens = rng.integers(0, vocab, size=PROMPT_TOKENS).tolist()
+        times = []
+        for index in range(repeats + 2):
+            request_id = f"p{index}"
+            model.admit(request_id)
+            start, stop = event_pair()
+            torch.cuda.synchronize()
+            start.record()
+            result = model.step([StepEntry(request_id, tokens, [PROMPT_TOKENS - 1])], [RequestSampler()])
+            stop.record()
+            torch.cuda.synchronize()
+            result.tokens.cpu()
+            model.release(request_id)
+            if index >= 2:
+                times.append(start.elapsed_time(stop))
+        return statistics.median(times)
+
+    hidden, inter, heads, kv_heads, dim = (config[k] for k in ("hidden_size", "intermediate_size",
+                                                               "num_attention_heads", "num_key_value_heads",
+                                                               "head_dim"))
+    per_layer = hidden * (heads + 2 * kv_heads) * dim + heads * dim * hidden + 3 * hidden * inter
+    gemm_flops = 2.0 * PROMPT_TOKENS * per_layer * layers + 2.0 * hidden * vocab
+    attention_flops = 4.0 * heads * dim * (PROMPT_TOKENS * (PROMPT_TOKENS + 1) / 2.0) * layers
+    prefill_flops = gemm_flops + attention_flops
+
+    value, ms_per_step, launches, clocks, context = decode_device(args.batch, args.steps, args.warmup)
+    step_bytes = weight_bytes + args.batch * context * kv_bytes_per_token
+    achieved_gbs = step_bytes / (ms_per_step / 1e3) / 1e9
+    e2e_value, h2d, d2h = decode_e2e(args.batch, args.steps, args.warmup)
+    prefill_ms = prefill()
+    points = {}
+    if not args.skip_points:
+        for batch in (1, 64):
+            points[f"decode_b{batch}"] = round(decode_device(batch, args.steps, args.warmup)[0], 1)
+
+    line = {
+        "metric": "decode tok/s at batch 8 (Qwen3-4B sizes, 2,048-token context, 1 B200)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random token ids, random N(0,0.02) weights, random cache",
+        "config": {
+            "model": "Qwen3-4B sizes (BASELINE.json configs[2])", "layers": layers, "layers_of_config": layers_full,
+            "hidden": hidden, "heads": heads, "kv_heads": kv_heads, "head_dim": dim, "intermediate": inter,
+            "vocab": vocab, "global_batch": args.batch, "seq_len": PROMPT_TOKENS + GENERATED_TOKENS,
+            "context_at_decode": round(context, 1), "page_size": PAGE_SIZE, "tied_embeddings": True,
+            "parallelism": "1 GPU", "l2": "inputs larger than L2 (a step reads every weight and the cache)",
+            "peaks": peaks_kind,
+        },
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "prefill": {"value": round(PROMPT_TOKENS / (prefill_ms / 1e3), 1), "tokens": PROMPT_TOKENS,
+                    "ms": round(prefill_ms, 3),
+                    "frac": round(prefill_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved_gbs / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "native_libraries": sorted(os.path.basename(p) for p in kernels.loaded_libraries().values()),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -87,7 +87,7 @@ __global__ void paged_attention_generic_kernel(
   }
 
   T* out_row = out + ((size_t)token * heads + head) * head_dim;
-  const float inverse = 1.0f / denominator;
+  const float inverse = denominator > 0.0f ? 1.0f / denominator : 0.0f;   // a padded row has no keys
 #pragma unroll
   for (int i = 0; i < kMaxHeadDim / 32; ++i) {
     const int d = lane + 32 * i;

@@ -115,3 +115,53 @@ MIR_EXPORT int mir_cast(int kind, const void* src, void* dst, size_t total, cuda
   else { mir_set_error("cast: unknown kind %d", kind); return MIR_BAD_ARGUMENT; }
   return mir_check_launch("cast");
 }
+
+// ---- decode batches that run as a captured graph -------------------------------------------------
+// Before the layers: where each row's new key/value goes, from its position and block table.  A row
+// with a negative position is padding (the batch is smaller than the captured size): no cache write.
+__global__ void decode_prepare_kernel(const int* __restrict__ positions, const int* __restrict__ block_table,
+                                      int table_width, int page_size, int* __restrict__ slot_mapping,
+                                      int* __restrict__ context_lens, int rows) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  const int position = positions[row];
+  int slot = -1;
+  if (position >= 0) {
+    const int block = position / page_size;
+    const int page = block < table_width ? block_table[(size_t)row * table_width + block] : -1;
+    if (page >= 0) slot = page * page_size + position % page_size;
+  }
+  slot_mapping[row] = slot;
+  context_lens[row] = position >= 0 ? position + 1 : 0;
+}
+
+// After sampling: the sampled token is the next step's input, positions move on by one, and the token is
+// appended to a log so that several steps can run without the host reading each one.
+__global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __restrict__ tokens,
+                                      int* __restrict__ positions, int* __restrict__ token_log, int log_steps,
+                                      int* __restrict__ step_counter, int rows) {
+  const int step = *step_counter;
+  __syncthreads();
+  for (int row = threadIdx.x; row < rows; row += blockDim.x) {
+    const int token = sampled[row];
+    tokens[row] = token;
+    if (positions[row] >= 0) positions[row] += 1;
+    if (step < log_steps) token_log[(size_t)step * rows + row] = token;
+  }
+  if (threadIdx.x == 0) *step_counter = step + 1;
+}
+
+MIR_EXPORT int mir_decode_prepare(const int* positions, const int* block_table, int table_width, int page_size,
+                                  int* slot_mapping, int* context_lens, int rows, cudaStream_t stream) {
+  if (rows <= 0) return MIR_OK;
+  decode_prepare_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(positions, block_table, table_width, page_size,
+                                                               slot_mapping, context_lens, rows);
+  return mir_check_launch("decode_prepare");
+}
+
+MIR_EXPORT int mir_decode_advance(const int* sampled, int* tokens, int* positions, int* token_log, int log_steps,
+                                  int* step_counter, int rows, cudaStream_t stream) {
+  if (rows <= 0) return MIR_OK;
+  decode_advance_kernel<<<1, 256, 0, stream>>>(sampled, tokens, positions, token_log, log_steps, step_counter, rows);
+  return mir_check_launch("decode_advance");
+}

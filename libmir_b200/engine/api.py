@@ -144,7 +144,7 @@ class Model:
             self.storage = CacheStorage(self.cache, plan, decoder.env.dtype, self.device)
             self.runner = StepRunner(decoder, self.cache, self.storage, self.device,
                                      decode_graphs=runtime.cuda.decode_graphs)
-            self.sampler = DeviceSampler(self.device, self.spec.vocab_size)
+        self.sampler = self.runner.sampler
         self._ids = itertools.count()
         self._unloaded = False
 
@@ -155,10 +155,16 @@ class Model:
     def release(self, request_id) -> None:
         self.cache.release(request_id)
 
-    def step(self, entries: Sequence[StepEntry]) -> StepResult:
-        """Run one batch of (request, next tokens); every request must have been admitted."""
+    def step(self, entries: Sequence[StepEntry], samplers: Optional[Sequence[RequestSampler]] = None) -> StepResult:
+        """Run one batch of (request, next tokens); every request must have been admitted.  With
+        `samplers`, one per wanted row, the result also carries the sampled tokens."""
         with torch.cuda.device(self.device):
-            return self.runner.step(entries)
+            return self.runner.step(entries, samplers)
+
+    def decode_many(self, entries: Sequence[StepEntry], samplers: Sequence[RequestSampler], steps: int):
+        """Several greedy decode steps back to back on the device; see StepRunner.decode_many."""
+        with torch.cuda.device(self.device):
+            return self.runner.decode_many(entries, samplers, steps)
 
     # -- generation ----------------------------------------------------------------------
     def _settings(self, options: Optional[GenerationOverrides]) -> GenerationSettings:
@@ -168,13 +174,12 @@ class Model:
             for key in GenerationOverrides.__dataclass_fields__})
         return self.generation_config.resolve(merged)
 
-    def _sample_fn(self, result: StepResult, samplers: Sequence[RequestSampler]) -> List[int]:
-        tokens = self.sampler.sample(result.logits, samplers)
-        return tokens.cpu().tolist()
+    def _run_and_sample(self, entries: Sequence[StepEntry], samplers: Sequence[RequestSampler]) -> List[int]:
+        result = self.step(entries, samplers)
+        return result.tokens.cpu().tolist() if result.tokens is not None else []
 
     def _scheduler(self) -> Scheduler:
-        return Scheduler(self.cache, self.library.config.scheduler, self.spec.max_positions, self.step,
-                         self._sample_fn)
+        return Scheduler(self.cache, self.library.config.scheduler, self.spec.max_positions, self._run_and_sample)
 
     def generate_batch(self, requests: Sequence[GenerationRequest],
                        on_token: Optional[Callable[[object, int], None]] = None) -> List[GenerationOutput]:
@@ -247,13 +252,15 @@ class Session:
         if not self._open:
             raise SchedulerError("the session is closed")
         tokens = [int(t) for t in tokens]
-        result = self.model.step([StepEntry(self.request_id, tokens, [len(tokens) - 1])])
-        cached = self.model.cache.live[self.request_id].length
+        entry = StepEntry(self.request_id, tokens, [len(tokens) - 1])
         if want == SamplingLogits.FULL:
+            result = self.model.step([entry])
+            cached = self.model.cache.live[self.request_id].length
             return PrefillOutput(logits=result.logits[0].float().cpu().numpy(), cached_tokens=cached)
         self.sampler.observe(tokens)
-        token = int(self.model.sampler.sample(result.logits, [self.sampler]).cpu()[0])
-        return PrefillOutput(next_token=token, cached_tokens=cached)
+        result = self.model.step([entry], [self.sampler])
+        cached = self.model.cache.live[self.request_id].length
+        return PrefillOutput(next_token=int(result.tokens.cpu()[0]), cached_tokens=cached)
 
     def prefill(self, prompt_ids: Sequence[int], sampling: str = SamplingLogits.TOKEN,
                 settings: Optional[GenerationSettings] = None, seed: Optional[int] = None) -> PrefillOutput:

@@ -1,0 +1,200 @@
+"""Decode-only steps as captured CUDA graphs.
+
+A step in which every request brings exactly one token and wants its logits sampled has a fixed shape
+once the number of rows and the width of the block tables are rounded up to a bucket, so the whole
+forward (cache-slot computation, embedding, layers, final norm, head, sampling, and moving the sampled
+token into the next step's input) is captured once per bucket and replayed.  Per step the host copies
+one small block (tokens, positions, slots, block tables, sampling options) to the device and reads the
+sampled tokens back; `run_many` replays several steps without any host work in between.
+
+libmir captures decode per bucket of rows {1, 2, 4, 5, 8, 10, 16, ...} and re-captures when split
+attention's partition counts change (cuda/src/engine/batch/mod.rs:18-32,108-131,
+cuda/src/backend/model/batch/capture.rs:26-54), and chains batch-1 decode on the device-resident token
+(cuda/src/backend/model/graph/mod.rs:54-100, session/mod.rs:152-160).  Here nothing is re-captured when
+contexts grow: kernels read lengths and tables from device memory, and a bucket is keyed by
+(rows, table width, ranked sampling).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import kernels
+from .context import GroupContext, StepContext
+
+LOG_STEPS = 512            # sampled tokens kept on the device between host reads
+
+
+def _bucket(n: int, floor: int = 1) -> int:
+    size = floor
+    while size < n:
+        size *= 2
+    return size
+
+
+class DecodeGraph:
+    def __init__(self, runner, rows: int, widths: Sequence[int], ranked: bool):
+        self.runner = runner
+        self.rows = rows
+        self.widths = list(widths)
+        self.ranked = ranked
+        device = runner.device
+        groups = len(widths)
+        options_ints = rows * kernels.SAMPLE_OPTIONS.itemsize // 4
+        # host-written block: sampling options (first: they hold 64-bit values and the block starts on a
+        # 256-byte boundary), tokens, positions, state slots, one table per group
+        sizes = [options_ints, rows, rows, rows] + [rows * w for w in widths]
+        self._offsets = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+        upload = int(self._offsets[-1])
+        # device-computed block: slot mapping per group, context lengths, and the constant index arrays
+        self.meta = torch.zeros(upload + groups * rows + rows + rows + (rows + 1) + rows, dtype=torch.int32,
+                                device=device)
+        self.staging = torch.zeros(upload, dtype=torch.int32, pin_memory=True)
+        self._host = self.staging.numpy()
+        self._upload = upload
+        cut = lambda index: self.meta[int(self._offsets[index]):int(self._offsets[index + 1])]
+        self.options = cut(0).view(torch.uint8)
+        self.tokens, self.positions, self.state_slots = cut(1), cut(2), cut(3)
+        self.tables = [cut(4 + g).view(rows, widths[g]) for g in range(groups)]
+        cursor = upload
+        self.slot_mappings = []
+        for _ in range(groups):
+            self.slot_mappings.append(self.meta[cursor:cursor + rows])
+            cursor += rows
+        self.context_lens = self.meta[cursor:cursor + rows]; cursor += rows
+        self.row_of_token = self.meta[cursor:cursor + rows]; cursor += rows
+        self.query_starts = self.meta[cursor:cursor + rows + 1]; cursor += rows + 1
+        self.want_rows = self.meta[cursor:cursor + rows]
+        self.row_of_token.copy_(torch.arange(rows, dtype=torch.int32))
+        self.query_starts.copy_(torch.arange(rows + 1, dtype=torch.int32))
+        self.want_rows.copy_(torch.arange(rows, dtype=torch.int32))
+        self.sampled = torch.zeros(rows, dtype=torch.int32, device=device)
+        self.token_log = torch.zeros(LOG_STEPS, rows, dtype=torch.int32, device=device)
+        self.step_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.logits: Optional[torch.Tensor] = None
+        self.sort_keys = None
+        if ranked:
+            self.sort_keys = torch.empty(kernels.ranked_scratch_keys(rows, runner.model.spec.vocab_size),
+                                         dtype=torch.int64, device=device)
+        self.host_tokens = torch.zeros(rows, dtype=torch.int32, pin_memory=True)
+        self.launches_per_replay = 0
+        self._copied = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._capture()
+
+    # -- host views of the upload block --------------------------------------------------
+    def _host_part(self, index: int) -> np.ndarray:
+        return self._host[int(self._offsets[index]):int(self._offsets[index + 1])]
+
+    def _context(self) -> StepContext:
+        runner = self.runner
+        groups = [GroupContext(block_table=self.tables[g], slot_mapping=self.slot_mappings[g],
+                               table_width=self.widths[g]) for g in range(len(self.widths))]
+        page = runner.manager.page_size
+        return StepContext(
+            num_tokens=self.rows, num_rows=self.rows, tokens=self.tokens, positions=self.positions,
+            row_of_token=self.row_of_token, query_starts=self.query_starts, context_lens=self.context_lens,
+            state_slots=self.state_slots, groups=groups, views=runner.storage.views, arena=runner.arena,
+            dtype=runner.model.env.dtype, host_query_starts=list(range(self.rows + 1)),
+            host_start_positions=[0] * self.rows, host_state_slots=[0] * self.rows,
+            max_context=max(self.widths) * page if self.widths else 0, max_portion=1, decode_only=True,
+            page_size=page)
+
+    def _body(self) -> None:
+        runner = self.runner
+        runner.arena.reset()
+        ctx = self._context()
+        for g in range(len(self.widths)):
+            kernels.decode_prepare(self.positions, self.tables[g], runner.manager.page_size, self.slot_mappings[g],
+                                   self.context_lens)
+        residual = runner.model.forward(ctx)
+        self.logits = runner.model.logits(ctx, residual, self.want_rows)
+        kernels.sample(self.logits, self.options, self.sampled, self.sort_keys, self.ranked)
+        kernels.decode_advance(self.sampled, self.tokens, self.positions, self.token_log, self.step_counter)
+
+    def _capture(self) -> None:
+        # every row is padding while warming up and capturing: nothing is written to the cache
+        self._host[:] = 0
+        self._host_part(2)[:] = -1
+        greedy = np.zeros(self.rows, dtype=kernels.SAMPLE_OPTIONS)
+        greedy["top_p"] = 1.0
+        self._host_part(0)[:] = greedy.view(np.int32)
+        self.meta[:self._upload].copy_(self.staging)
+        stream = torch.cuda.Stream(device=self.runner.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                self._body()                       # builds library plans and grows the arena before capture
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        before = kernels.LAUNCHES
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._body()
+        self.launches_per_replay = kernels.LAUNCHES - before
+        self.graph = graph
+        self.step_counter.zero_()
+
+    # -- running -----------------------------------------------------------------------------
+    def load(self, tokens: Sequence[int], sequences, options: Optional[np.ndarray]) -> None:
+        """Fill the upload block for the live rows (the rest is padding) and copy it to the device."""
+        n = len(tokens)
+        if self._copied is not None:
+            self._copied.synchronize()             # the previous copy has read the pinned block
+        host_tokens, host_positions, host_slots = self._host_part(1), self._host_part(2), self._host_part(3)
+        host_tokens[:n] = tokens
+        host_tokens[n:] = 0
+        host_positions[:n] = [seq.length for seq in sequences]
+        host_positions[n:] = -1
+        host_slots[:n] = [seq.slot for seq in sequences]
+        host_slots[n:] = 0
+        records = self._host_part(0).view(kernels.SAMPLE_OPTIONS)
+        if options is None:
+            records["draw"], records["temperature"], records["top_p"], records["top_k"] = 0.0, 0.0, 1.0, 0
+        else:
+            records[:n] = options
+        for g, width in enumerate(self.widths):
+            table = self._host_part(4 + g).reshape(self.rows, width)
+            table[n:] = 0
+            for r, seq in enumerate(sequences):
+                blocks = seq.tables[g]
+                table[r, :len(blocks)] = blocks
+                table[r, len(blocks):] = -1
+        self.meta[:self._upload].copy_(self.staging, non_blocking=True)
+        self._copied = torch.cuda.Event()
+        self._copied.record()
+
+    def replay(self) -> None:
+        self.graph.replay()
+        kernels.LAUNCHES += self.launches_per_replay
+
+
+class DecodeGraphs:
+    """The buckets captured so far for one StepRunner."""
+
+    def __init__(self, runner):
+        self.runner = runner
+        self.graphs: Dict[Tuple, DecodeGraph] = {}
+
+    def usable(self) -> bool:
+        """Every mixer must read the batch from device memory only (graph_safe), since a replay cannot
+        see what the host knew at capture time."""
+        from ..parts.base import Mixer
+        return all(part.graph_safe for part in self.runner.model.parts() if isinstance(part, Mixer))
+
+    def get(self, rows: int, sequences, extra_tokens: int, ranked: bool) -> DecodeGraph:
+        page = self.runner.manager.page_size
+        widths = []
+        for g in range(len(self.runner.manager.groups)):
+            need = max(-(-(seq.length + extra_tokens) // page) for seq in sequences)
+            need = max(need, max(len(seq.tables[g]) for seq in sequences))
+            widths.append(_bucket(need, 8))
+        key = (_bucket(rows), tuple(widths), ranked)
+        graph = self.graphs.get(key)
+        if graph is None:
+            graph = DecodeGraph(self.runner, key[0], widths, ranked)
+            self.graphs[key] = graph
+        return graph

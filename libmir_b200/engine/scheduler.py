@@ -71,14 +71,14 @@ class PlannedEntry:
 
 class Scheduler:
     def __init__(self, manager: CacheManager, config: SchedulerConfig, max_positions: int,
-                 run_step: Callable[[Sequence[StepEntry]], object],
-                 sample: Callable[[object, Sequence[RequestSampler]], List[int]]):
+                 run_step: Callable[[Sequence[StepEntry], Sequence[RequestSampler]], List[int]]):
+        """`run_step(entries, samplers)` runs one batch and returns the sampled token of every entry
+        that wants one (those with a non-empty `want`), in order, as host integers."""
         config.validate()
         self.manager = manager
         self.config = config
         self.max_positions = max_positions
         self.run_step = run_step
-        self.sample = sample
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []
         self.finished: List[Request] = []
@@ -244,11 +244,10 @@ class Scheduler:
         for item in planned:
             tokens = item.request.tokens[item.start:item.start + item.count]
             entries.append(StepEntry(item.request.request_id, tokens, [item.count - 1] if item.samples else []))
-        result = self.run_step(entries)
         samplers = [item.request.sampler for item in planned if item.samples]
+        sampled = self.run_step(entries, samplers)
         for item in planned:
             item.request.fed += item.count
-        sampled = self.sample(result, samplers) if samplers else []
         self.log.append({"step": self.steps, "tokens": sum(i.count for i in planned),
                          "decode_rows": sum(1 for i in planned if i.count == 1 and i.start >= len(i.request.prompt)),
                          "entries": [(i.request.request_id, i.start, i.count) for i in planned]})

@@ -35,6 +35,7 @@ class StepResult:
     logits: Optional[torch.Tensor]          # float32 [wanted, vocab] on the device; valid until the next step
     rows: List[tuple]                       # (request_id, local index) for each logits row, in order
     num_tokens: int = 0
+    tokens: Optional[torch.Tensor] = None   # int32 [wanted] sampled tokens on the device, if samplers were given
 
 
 class StepRunner:
@@ -47,6 +48,12 @@ class StepRunner:
         self.storage = storage
         self.device = device
         self.decode_graphs = decode_graphs
+        self._graphs = None
+        self._graphs_usable = False
+        self.sampler = None
+        if storage is not None:
+            from ..sampling.sampler import DeviceSampler
+            self.sampler = DeviceSampler(device, model.spec.vocab_size)
         self.arena = Arena(device)
         self._staging: List[Optional[torch.Tensor]] = [None, None]
         self._staging_events: List[Optional[torch.cuda.Event]] = [None, None]
@@ -184,26 +191,89 @@ class StepRunner:
             manager.grow(seq, seq.length + len(entry.tokens))
         return entries, sequences
 
-    def execute(self, entries: Sequence[StepEntry], sequences) -> StepResult:
-        """Device side of a step: run the tokens from the cache and return logits at the wanted places."""
+    def _graph_eligible(self, entries, samplers) -> bool:
+        if not self.decode_graphs or samplers is None or len(samplers) != len(entries):
+            return False
+        if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
+            return False
+        if any(s.repetition_penalty > 1.0 for s in samplers):
+            return False
+        if self._graphs is None:
+            from .decode_graph import DecodeGraphs
+            self._graphs = DecodeGraphs(self)
+            self._graphs_usable = self._graphs.usable()
+        return self._graphs_usable
+
+    def _options(self, samplers) -> Optional[np.ndarray]:
+        if all(s.greedy for s in samplers):
+            return None
+        from .. import kernels
+        options = np.zeros(len(samplers), dtype=kernels.SAMPLE_OPTIONS)
+        for r, s in enumerate(samplers):
+            options[r] = (s.next_draw(), s.temperature, s.top_p, s.top_k, 0)
+        return options
+
+    def execute(self, entries: Sequence[StepEntry], sequences, samplers=None) -> StepResult:
+        """Device side of a step: run the tokens from the cache, return logits at the wanted places
+        and, when `samplers` has one sampler per wanted row, the sampled tokens."""
         self.storage.zero_slots(self.manager.take_fresh_slots())
+        if self._graph_eligible(entries, samplers):
+            graph = self._graphs.get(len(entries), sequences, 1, any(s.ranked for s in samplers))
+            graph.load([e.tokens[0] for e in entries], sequences, self._options(samplers))
+            graph.replay()
+            rows = len(entries)
+            keys = [(e.request_id, 0) for e in entries]
+            return StepResult(graph.logits[:rows], keys, rows, graph.sampled[:rows])
         self.arena.reset()
         ctx, want_rows, want_keys = self.build_context(entries, sequences)
         residual = self.model.forward(ctx)
         logits = self.model.logits(ctx, residual, want_rows) if want_keys else None
-        return StepResult(logits, want_keys, ctx.num_tokens)
+        tokens = None
+        if samplers is not None and logits is not None:
+            tokens = self.sampler.sample(logits, samplers)
+        return StepResult(logits, want_keys, ctx.num_tokens, tokens)
 
     def commit(self, entries: Sequence[StepEntry], sequences) -> None:
         for entry, seq in zip(entries, sequences):
             self.manager.commit(seq, seq.length + len(entry.tokens))
 
-    def step(self, entries: Sequence[StepEntry]) -> StepResult:
-        """Run one batch: reserve pages, run the tokens, commit the new lengths."""
+    def step(self, entries: Sequence[StepEntry], samplers=None) -> StepResult:
+        """Run one batch: reserve pages, run the tokens, commit the new lengths.  With `samplers` (one
+        per wanted row, in order) the result also holds the sampled tokens."""
         entries, sequences = self.reserve(entries)
         if not entries:
             return StepResult(None, [], 0)
-        result = self.execute(entries, sequences)
+        result = self.execute(entries, sequences, samplers)
         self.commit(entries, sequences)
         self.steps += 1
         self.tokens_run += result.num_tokens
         return result
+
+    def decode_many(self, entries: Sequence[StepEntry], samplers, steps: int) -> torch.Tensor:
+        """`steps` decode steps for the same requests with no host work in between: each step's sampled
+        token is the next step's input on the device.  Pages for all the steps are taken first.  Returns
+        the sampled tokens [steps, rows] (int32, host).  Greedy or seeded sampling without penalty only;
+        stopping rules are the caller's to apply afterwards."""
+        from .decode_graph import LOG_STEPS
+        if steps > LOG_STEPS:
+            raise SchedulerError(f"decode_many takes at most {LOG_STEPS} steps at a time")
+        entries = list(entries)
+        if not self._graph_eligible(entries, samplers):
+            raise SchedulerError("decode_many needs decode graphs, one token per request and samplers "
+                                 "without a repetition penalty")
+        if any(not s.greedy for s in samplers):
+            raise SchedulerError("decode_many draws nothing on the host: greedy samplers only")
+        ahead = [StepEntry(e.request_id, list(e.tokens) + [0] * (steps - 1), []) for e in entries]
+        ahead, sequences = self.reserve(ahead)
+        self.storage.zero_slots(self.manager.take_fresh_slots())
+        graph = self._graphs.get(len(entries), sequences, steps, False)
+        graph.load([e.tokens[0] for e in entries], sequences, None)
+        graph.step_counter.zero_()
+        for _ in range(steps):
+            graph.replay()
+        tokens = graph.token_log[:steps, :len(entries)].cpu()
+        graph.step_counter.zero_()
+        self.commit(ahead, sequences)
+        self.steps += steps
+        self.tokens_run += steps * len(entries)
+        return tokens

@@ -37,6 +37,8 @@ _SIGNATURES = {
                          c_void_p],
         "mir_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
         "mir_repetition_penalty": [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+        "mir_decode_prepare": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+        "mir_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p],
     },
     "bf16": {
         "mir_gemm_bf16_lt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -75,7 +77,12 @@ def loaded_libraries() -> dict:
     return {name: lib._name for name, lib in _LIBS.items()}
 
 
+LAUNCHES = 0        # kernels (and library matrix products) launched through this module, for reports
+
+
 def _check(lib: ctypes.CDLL, status: int) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if status != 0:
         raise KernelError(lib.mir_last_error().decode(errors="replace") or f"kernel launch failed with status {status}")
 
@@ -162,6 +169,23 @@ def cast(src: torch.Tensor, dst: torch.Tensor) -> None:
     _require(kind is not None, f"cast: {src.dtype} -> {dst.dtype} is not supported")
     lib = library("core")
     _check(lib, lib.mir_cast(kind, src.data_ptr(), dst.data_ptr(), src.numel(), _stream()))
+
+
+def decode_prepare(positions, block_table, page_size, slot_mapping, context_lens) -> None:
+    """slot_mapping[r] and context_lens[r] of a decode batch from positions and block tables (on the device)."""
+    rows = positions.numel()
+    lib = library("core")
+    _check(lib, lib.mir_decode_prepare(positions.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
+                                       slot_mapping.data_ptr(), context_lens.data_ptr(), rows, _stream()))
+
+
+def decode_advance(sampled, tokens, positions, token_log, step_counter) -> None:
+    """tokens <- sampled, positions += 1, token_log[step] <- sampled, step += 1 (on the device)."""
+    rows = tokens.numel()
+    lib = library("core")
+    _check(lib, lib.mir_decode_advance(sampled.data_ptr(), tokens.data_ptr(), positions.data_ptr(),
+                                       token_log.data_ptr(), token_log.shape[0], step_counter.data_ptr(), rows,
+                                       _stream()))
 
 
 # --------------------------------------------------------------------------- attention

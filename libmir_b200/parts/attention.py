@@ -20,6 +20,8 @@ from .base import Mixer
 
 
 class SoftmaxAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, spec, env):
         super().__init__(spec, env)
         s = spec

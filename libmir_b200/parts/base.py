@@ -61,6 +61,8 @@ class Norm(Part):
 
 
 class Mixer(Part):
+    graph_safe = False     # True if forward reads the batch only from device tensors of the context
+
     def cache_requirement(self) -> CacheRequirement:
         return None
 

@@ -21,7 +21,7 @@ class HostOnlyRunner(StepRunner):
         super().__init__(model, manager, None, torch.device("cpu"))
         self.ran = []
 
-    def execute(self, entries, sequences):
+    def execute(self, entries, sequences, samplers=None):
         self.ran.append([(e.request_id, seq.length, len(e.tokens), list(e.want)) for e, seq in zip(entries, sequences)])
         keys = [(e.request_id, w) for e in entries for w in e.want]
         return StepResult(None, keys, sum(len(e.tokens) for e in entries))
@@ -41,7 +41,12 @@ def build(config=TINY_A, pages=64, page_size=4, **scheduler_options):
             out.append(100 + counter["n"] % 50)
         return out
 
-    scheduler = Scheduler(manager, options, model.spec.max_positions, runner.step, sample)
+    def run_step(entries, samplers):
+        runner.step(entries)
+        return run_step.sample(None, samplers)
+
+    run_step.sample = sample
+    scheduler = Scheduler(manager, options, model.spec.max_positions, run_step)
     return scheduler, runner, manager
 
 
@@ -89,7 +94,7 @@ def test_completion_first_oldest_prompt_takes_the_budget():
 
 def test_stop_token_min_tokens_and_ignore_eos():
     scheduler, _, _ = build()
-    scheduler.sample = lambda result, samplers: [7 for _ in samplers]
+    scheduler.run_step.sample = lambda result, samplers: [7 for _ in samplers]
     scheduler.submit(request("stops", 3, 10, stop=[7]))
     scheduler.submit(request("min", 3, 10, stop=[7], min_tokens=4))
     scheduler.submit(request("ignores", 3, 5, stop=[7], ignore_eos=True))
