@@ -1,0 +1,576 @@
+// Tensor-core paged attention for bf16 (head_dim 64 or 128), two kernels:
+//
+//   decode   one token per request.  Split over the keys (flash-decoding): a CTA takes one
+//            (request, kv head, partition of the keys) and serves the whole group of query heads that
+//            share the kv head, so keys and values are read from HBM once per group, not once per head.
+//            Each of its 4 warps streams its own 16-key tiles through a cp.async double buffer; partial
+//            results (unnormalised output, running maximum, denominator) are merged by a second kernel.
+//            Replaces libmir's paged_attention_batch_split_bf16.cu:24-424 (SIMT / wmma 16x16x16).
+//   prefill  portions of prompts (and any mixed batch).  FlashAttention-2 style: a CTA takes 64
+//            consecutive tokens of one request's portion and one query head; keys/values of the
+//            request's history AND of the portion itself come from the cache pages (the portion's were
+//            written by the kernel that ran before).  Replaces the per-token kernel
+//            paged_prefill_attention_batch_bf16.cu:14-124 and the opaque FmhaBf16Plan.
+//
+// Both use mma.sync.m16n8k16 (bf16 in, 32-bit accumulate) with ldmatrix from padded shared-memory rows
+// (row stride head_dim + 8 elements: an odd number of 16-byte chunks, so ldmatrix is conflict-free).
+// Scores, maxima, exponentials and sums are 32-bit.  Keys outside [first visible, position] are masked
+// before the maximum is taken; a tile's tail beyond the context is zero-filled, never read.
+#include <cfloat>
+#include "common.cuh"
+
+using namespace mir;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;   // 0 bytes read: the 16 bytes of shared memory are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+// Copy `keys` rows of head_dim bf16 (one kv head) from the pages into padded shared-memory rows.
+// Row i holds key `first_key + i`; rows whose key is >= limit are zero-filled.  THREADS threads cooperate.
+template <int D, int THREADS>
+__device__ __forceinline__ void load_rows(bf16* dst, const bf16* __restrict__ pages, const int* __restrict__ table,
+                                          int page_size, int kv_heads, int kv_head, int first_key, int keys,
+                                          int limit, int thread) {
+  constexpr int CHUNKS = D / 8;          // 16-byte chunks per row
+  constexpr int STRIDE = D + 8;
+  for (int c = thread; c < keys * CHUNKS; c += THREADS) {
+    const int r = c / CHUNKS, chunk = c % CHUNKS;
+    const int key = first_key + r;
+    const bool valid = key < limit;
+    const bf16* src = pages;
+    if (valid) {
+      const int page = table[key / page_size];
+      src = pages + (((size_t)page * page_size + key % page_size) * kv_heads + kv_head) * D + chunk * 8;
+    }
+    cp_async16(smem_u32(dst + r * STRIDE + chunk * 8), src, valid);
+  }
+}
+
+// S[16 x 16 keys] += Q[16 x D] . K^T for one 16-key tile (two n-tiles of 8 keys).
+template <int D>
+__device__ __forceinline__ void scores_16(float (&s)[2][4], const uint32_t (&qa)[D / 16][4], const bf16* k_tile,
+                                          int lane) {
+  constexpr int STRIDE = D + 8;
+  const int mat = lane >> 3, rowin = lane & 7;
+  const bf16* base = k_tile + ((mat >> 1) * 8 + rowin) * STRIDE + (mat & 1) * 8;
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    uint32_t b[4];
+    ldmatrix_x4(b, smem_u32(base + ks * 16));
+    mma_bf16(s[0], qa[ks], b[0], b[1]);
+    mma_bf16(s[1], qa[ks], b[2], b[3]);
+  }
+}
+
+// O[16 x D] += P[16 x 16 keys] . V for one 16-key tile.
+template <int D>
+__device__ __forceinline__ void values_16(float (&o)[D / 8][4], const uint32_t (&pa)[4], const bf16* v_tile, int lane) {
+  constexpr int STRIDE = D + 8;
+  const int mat = lane >> 3, rowin = lane & 7;
+  const bf16* base = v_tile + ((mat & 1) * 8 + rowin) * STRIDE + (mat >> 1) * 8;
+#pragma unroll
+  for (int np = 0; np < D / 16; ++np) {
+    uint32_t b[4];
+    ldmatrix_x4_trans(b, smem_u32(base + np * 16));
+    mma_bf16(o[2 * np], pa, b[0], b[1]);
+    mma_bf16(o[2 * np + 1], pa, b[2], b[3]);
+  }
+}
+
+// Online-softmax update of one 16-row block with the scores of 16 keys (already scaled to log2 units and
+// masked with -inf).  m/l are per thread for its two rows (lane/4 and lane/4 + 8); l is a per-thread partial
+// sum that the caller reduces over the quad at the end.
+template <int D>
+__device__ __forceinline__ void softmax_16(float (&s)[2][4], float (&m)[2], float (&l)[2], float (&o)[D / 8][4],
+                                           uint32_t (&pa)[4]) {
+  float mx0 = quad_max(fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1])));
+  float mx1 = quad_max(fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3])));
+  const float new0 = fmaxf(m[0], mx0), new1 = fmaxf(m[1], mx1);
+  const float ref0 = new0 == -INFINITY ? 0.0f : new0, ref1 = new1 == -INFINITY ? 0.0f : new1;
+  const float corr0 = exp2f(m[0] - ref0), corr1 = exp2f(m[1] - ref1);
+  m[0] = new0;
+  m[1] = new1;
+  float p[2][4];
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    p[nt][0] = exp2f(s[nt][0] - ref0);
+    p[nt][1] = exp2f(s[nt][1] - ref0);
+    p[nt][2] = exp2f(s[nt][2] - ref1);
+    p[nt][3] = exp2f(s[nt][3] - ref1);
+  }
+  l[0] = l[0] * corr0 + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
+  l[1] = l[1] * corr1 + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) {
+    o[nt][0] *= corr0;
+    o[nt][1] *= corr0;
+    o[nt][2] *= corr1;
+    o[nt][3] *= corr1;
+  }
+  pa[0] = pack_bf16(p[0][0], p[0][1]);
+  pa[1] = pack_bf16(p[0][2], p[0][3]);
+  pa[2] = pack_bf16(p[1][0], p[1][1]);
+  pa[3] = pack_bf16(p[1][2], p[1][3]);
+}
+
+// ------------------------------------------------------------------------------------------------ decode
+constexpr int kDecodeWarps = 4;
+constexpr int kDecodeTile = 16;
+
+template <int D>
+__global__ void __launch_bounds__(kDecodeWarps * 32)
+decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* __restrict__ k_pages,
+                        const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
+                        const int* __restrict__ positions, int page_size, int heads, int kv_heads, float scale_log2,
+                        int window, int partition, int num_partitions, float* __restrict__ partial_o,
+                        float* __restrict__ partial_ml, bf16* __restrict__ out) {
+  constexpr int STRIDE = D + 8;
+  constexpr int TILE_ELEMS = kDecodeTile * STRIDE;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int part = blockIdx.x, row = blockIdx.z;
+  const int group = heads / kv_heads;
+  const int group_tiles = (group + 15) / 16;
+  const int kv_head = blockIdx.y / group_tiles;
+  const int head0 = kv_head * group + (blockIdx.y % group_tiles) * 16;
+  const int valid_rows = min(16, kv_head * group + group - head0);
+  const int position = positions[row];
+  if (position < 0) return;                                   // padding row of a captured batch
+  const int context = position + 1;
+  const int first_key = (window > 0 && context > window) ? context - window : 0;
+  const int part_begin = part * partition;
+  const int part_end = min(context, part_begin + partition);
+  const int begin = max(part_begin, first_key / kDecodeTile * kDecodeTile);
+  if (begin >= part_end) return;                              // the merge skips this partition the same way
+
+  // this warp's buffers: [stage][K | V][16 rows][STRIDE]
+  bf16* stage_base = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * 2 * 2 * TILE_ELEMS;
+  const int* table = block_table + (size_t)row * table_width;
+
+  // Q fragments of the 16 (padded) heads of the group
+  uint32_t qa[D / 16][4];
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8, c = (lane & 3) * 2;
+    const bf16* q_row0 = q + (size_t)row * q_stride + (size_t)(head0 + r0) * D;
+    const bf16* q_row1 = q + (size_t)row * q_stride + (size_t)(head0 + r1) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qa[ks][0] = r0 < valid_rows ? *reinterpret_cast<const uint32_t*>(q_row0 + ks * 16 + c) : 0u;
+      qa[ks][1] = r1 < valid_rows ? *reinterpret_cast<const uint32_t*>(q_row1 + ks * 16 + c) : 0u;
+      qa[ks][2] = r0 < valid_rows ? *reinterpret_cast<const uint32_t*>(q_row0 + ks * 16 + 8 + c) : 0u;
+      qa[ks][3] = r1 < valid_rows ? *reinterpret_cast<const uint32_t*>(q_row1 + ks * 16 + 8 + c) : 0u;
+    }
+  }
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+
+  const int stride_keys = kDecodeWarps * kDecodeTile;
+  int tile = begin + warp * kDecodeTile;
+  if (tile < part_end) {
+    load_rows<D, 32>(stage_base, k_pages, table, page_size, kv_heads, kv_head, tile, kDecodeTile, part_end, lane);
+    load_rows<D, 32>(stage_base + TILE_ELEMS, v_pages, table, page_size, kv_heads, kv_head, tile, kDecodeTile,
+                     part_end, lane);
+  }
+  cp_async_commit();
+  int stage = 0;
+  for (; tile < part_end; tile += stride_keys, stage ^= 1) {
+    const int next = tile + stride_keys;
+    if (next < part_end) {
+      bf16* dst = stage_base + (stage ^ 1) * 2 * TILE_ELEMS;
+      load_rows<D, 32>(dst, k_pages, table, page_size, kv_heads, kv_head, next, kDecodeTile, part_end, lane);
+      load_rows<D, 32>(dst + TILE_ELEMS, v_pages, table, page_size, kv_heads, kv_head, next, kDecodeTile, part_end,
+                       lane);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+    const bf16* k_tile = stage_base + stage * 2 * TILE_ELEMS;
+    const bf16* v_tile = k_tile + TILE_ELEMS;
+    float s[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+    scores_16<D>(s, qa, k_tile, lane);
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = tile + nt * 8 + (lane & 3) * 2 + (e & 1);
+        s[nt][e] = (key >= first_key && key <= position) ? s[nt][e] * scale_log2 : -INFINITY;
+      }
+    uint32_t pa[4];
+    softmax_16<D>(s, m, l, o, pa);
+    values_16<D>(o, pa, v_tile, lane);
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+  l[0] = quad_sum(l[0]);
+  l[1] = quad_sum(l[1]);
+  __syncthreads();                                            // every warp is done with its pipeline buffers
+
+  // combine the 4 warps through shared memory
+  float* o_sm = reinterpret_cast<float*>(smem_raw);           // [warps][16][D]
+  float* m_sm = o_sm + kDecodeWarps * 16 * D;                 // [warps][16]
+  float* l_sm = m_sm + kDecodeWarps * 16;
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8, c = (lane & 3) * 2;
+    float* mine = o_sm + (size_t)warp * 16 * D;
+#pragma unroll
+    for (int nt = 0; nt < D / 8; ++nt) {
+      mine[r0 * D + nt * 8 + c] = o[nt][0];
+      mine[r0 * D + nt * 8 + c + 1] = o[nt][1];
+      mine[r1 * D + nt * 8 + c] = o[nt][2];
+      mine[r1 * D + nt * 8 + c + 1] = o[nt][3];
+    }
+    if ((lane & 3) == 0) {
+      m_sm[warp * 16 + r0] = m[0];
+      m_sm[warp * 16 + r1] = m[1];
+      l_sm[warp * 16 + r0] = l[0];
+      l_sm[warp * 16 + r1] = l[1];
+    }
+  }
+  __syncthreads();
+  for (int index = threadIdx.x; index < valid_rows * D; index += kDecodeWarps * 32) {
+    const int r = index / D, d = index % D;
+    float top = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) top = fmaxf(top, m_sm[w * 16 + r]);
+    float acc = 0.0f, denom = 0.0f;
+    if (top != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < kDecodeWarps; ++w) {
+        const float weight = exp2f(m_sm[w * 16 + r] - top);
+        acc += o_sm[((size_t)w * 16 + r) * D + d] * weight;
+        denom += l_sm[w * 16 + r] * weight;
+      }
+    }
+    const size_t head = (size_t)row * heads + head0 + r;
+    if (num_partitions == 1) {
+      out[head * D + d] = __float2bfloat16_rn(denom > 0.0f ? acc / denom : 0.0f);
+    } else {
+      partial_o[(head * num_partitions + part) * D + d] = acc;
+      if (d == 0) {
+        partial_ml[(head * num_partitions + part) * 2] = top;
+        partial_ml[(head * num_partitions + part) * 2 + 1] = denom;
+      }
+    }
+  }
+}
+
+template <int D>
+__global__ void decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
+                                    const int* __restrict__ positions, int heads, int window, int partition,
+                                    int num_partitions, bf16* __restrict__ out) {
+  const int head = blockIdx.x, row = blockIdx.y;
+  const int position = positions[row];
+  const size_t index = (size_t)row * heads + head;
+  if (position < 0) {
+    for (int d = threadIdx.x; d < D; d += blockDim.x) out[index * D + d] = __float2bfloat16_rn(0.0f);
+    return;
+  }
+  const int context = position + 1;
+  const int first_key = (window > 0 && context > window) ? context - window : 0;
+  const int first_part = (first_key / kDecodeTile * kDecodeTile) / partition;
+  const int last_part = position / partition;
+  float top = -INFINITY;
+  for (int p = first_part; p <= last_part; ++p) top = fmaxf(top, partial_ml[(index * num_partitions + p) * 2]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.0f, denom = 0.0f;
+    for (int p = first_part; p <= last_part; ++p) {
+      const float weight = exp2f(partial_ml[(index * num_partitions + p) * 2] - top);
+      acc += partial_o[(index * num_partitions + p) * D + d] * weight;
+      denom += partial_ml[(index * num_partitions + p) * 2 + 1] * weight;
+    }
+    out[index * D + d] = __float2bfloat16_rn(denom > 0.0f ? acc / denom : 0.0f);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ prefill
+constexpr int kPrefillWarps = 4;
+constexpr int kQueryTile = kPrefillWarps * 16;     // 64 tokens per CTA
+constexpr int kKeyTile = 64;
+
+template <int D>
+__global__ void __launch_bounds__(kPrefillWarps * 32)
+prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __restrict__ out,
+                         const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                         const int* __restrict__ block_table, int table_width, const int* __restrict__ query_starts,
+                         const int* __restrict__ context_lens, int num_rows, int page_size, int heads, int kv_heads,
+                         float scale_log2, int window) {
+  constexpr int STRIDE = D + 8;
+  constexpr int TILE_ELEMS = kKeyTile * STRIDE;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* buffers = reinterpret_cast<bf16*>(smem_raw);          // [stage][K | V][64][STRIDE]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int kv_head = head / (heads / kv_heads);
+
+  // which request row and which 64-token tile of its portion this CTA has
+  int row = -1, local_tile = 0;
+  {
+    int remaining = blockIdx.x;
+    for (int r = 0; r < num_rows; ++r) {
+      const int tiles = (query_starts[r + 1] - query_starts[r] + kQueryTile - 1) / kQueryTile;
+      if (remaining < tiles) { row = r; local_tile = remaining; break; }
+      remaining -= tiles;
+    }
+  }
+  if (row < 0) return;
+  const int q_begin = query_starts[row];
+  const int count = query_starts[row + 1] - q_begin;
+  const int start_position = context_lens[row] - count;
+  const int local0 = local_tile * kQueryTile;
+  const int tile_rows = min(kQueryTile, count - local0);
+  const int first_position = start_position + local0;
+  const int last_position = first_position + tile_rows - 1;
+  const int* table = block_table + (size_t)row * table_width;
+
+  // this warp's 16 query rows
+  const int r0 = lane >> 2, r1 = r0 + 8, c = (lane & 3) * 2;
+  const int local_r0 = warp * 16 + r0, local_r1 = warp * 16 + r1;
+  const bool valid0 = local_r0 < tile_rows, valid1 = local_r1 < tile_rows;
+  const int pos0 = min(first_position + local_r0, last_position), pos1 = min(first_position + local_r1, last_position);
+  uint32_t qa[D / 16][4];
+  {
+    const bf16* q_row0 = q + (size_t)(q_begin + local0 + local_r0) * q_stride + (size_t)head * D;
+    const bf16* q_row1 = q + (size_t)(q_begin + local0 + local_r1) * q_stride + (size_t)head * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qa[ks][0] = valid0 ? *reinterpret_cast<const uint32_t*>(q_row0 + ks * 16 + c) : 0u;
+      qa[ks][1] = valid1 ? *reinterpret_cast<const uint32_t*>(q_row1 + ks * 16 + c) : 0u;
+      qa[ks][2] = valid0 ? *reinterpret_cast<const uint32_t*>(q_row0 + ks * 16 + 8 + c) : 0u;
+      qa[ks][3] = valid1 ? *reinterpret_cast<const uint32_t*>(q_row1 + ks * 16 + 8 + c) : 0u;
+    }
+  }
+  float o[D / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+
+  const int first_key = (window > 0 && first_position + 1 > window) ? first_position + 1 - window : 0;
+  const int key_begin = first_key / kKeyTile * kKeyTile;
+  const int key_end = last_position + 1;                       // exclusive
+  const int warp_last = min(first_position + warp * 16 + 15, last_position);
+  const int warp_first = min(first_position + warp * 16, last_position);
+  const int warp_first_key = (window > 0 && warp_first + 1 > window) ? warp_first + 1 - window : 0;
+
+  load_rows<D, kPrefillWarps * 32>(buffers, k_pages, table, page_size, kv_heads, kv_head, key_begin, kKeyTile, key_end,
+                                   threadIdx.x);
+  load_rows<D, kPrefillWarps * 32>(buffers + TILE_ELEMS, v_pages, table, page_size, kv_heads, kv_head, key_begin,
+                                   kKeyTile, key_end, threadIdx.x);
+  cp_async_commit();
+  int stage = 0;
+  for (int key0 = key_begin; key0 < key_end; key0 += kKeyTile, stage ^= 1) {
+    const int next = key0 + kKeyTile;
+    if (next < key_end) {
+      bf16* dst = buffers + (stage ^ 1) * 2 * TILE_ELEMS;
+      load_rows<D, kPrefillWarps * 32>(dst, k_pages, table, page_size, kv_heads, kv_head, next, kKeyTile, key_end,
+                                       threadIdx.x);
+      load_rows<D, kPrefillWarps * 32>(dst + TILE_ELEMS, v_pages, table, page_size, kv_heads, kv_head, next, kKeyTile,
+                                       key_end, threadIdx.x);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const bf16* k_tile = buffers + stage * 2 * TILE_ELEMS;
+    const bf16* v_tile = k_tile + TILE_ELEMS;
+    // this warp needs the tile only if some key of it is visible to some of its rows
+    if (key0 <= warp_last && key0 + kKeyTile > warp_first_key) {
+      const bool needs_mask = key0 + kKeyTile - 1 > warp_first || (window > 0 && key0 < warp_last + 1 - window + 15);
+#pragma unroll
+      for (int sub = 0; sub < kKeyTile / 16; ++sub) {
+        const int sub0 = key0 + sub * 16;
+        if (sub0 > warp_last) break;
+        float s[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+        scores_16<D>(s, qa, k_tile + sub * 16 * STRIDE, lane);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = sub0 + nt * 8 + c + (e & 1);
+            const int pos = (e < 2) ? pos0 : pos1;
+            bool visible = true;
+            if (needs_mask) visible = key <= pos && (window <= 0 || key > pos - window);
+            s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+          }
+        uint32_t pa[4];
+        softmax_16<D>(s, m, l, o, pa);
+        values_16<D>(o, pa, v_tile + sub * 16 * STRIDE, lane);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  l[0] = quad_sum(l[0]);
+  l[1] = quad_sum(l[1]);
+  const float inv0 = l[0] > 0.0f ? 1.0f / l[0] : 0.0f, inv1 = l[1] > 0.0f ? 1.0f / l[1] : 0.0f;
+  bf16* out0 = out + ((size_t)(q_begin + local0 + local_r0) * heads + head) * D;
+  bf16* out1 = out + ((size_t)(q_begin + local0 + local_r1) * heads + head) * D;
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) {
+    if (valid0) *reinterpret_cast<uint32_t*>(out0 + nt * 8 + c) = pack_bf16(o[nt][0] * inv0, o[nt][1] * inv0);
+    if (valid1) *reinterpret_cast<uint32_t*>(out1 + nt * 8 + c) = pack_bf16(o[nt][2] * inv1, o[nt][3] * inv1);
+  }
+}
+
+// Opt in to more than 48 KB of dynamic shared memory, once per kernel.
+template <typename Kernel>
+int set_smem(Kernel kernel, size_t bytes, const char* what) {
+  static bool done = false;          // one instance of this function, and of the flag, per kernel type
+  if (bytes <= 48 * 1024 || done) return MIR_OK;
+  done = true;
+  const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (err != cudaSuccess) {
+    mir_set_error("%s: cannot reserve %zu bytes of shared memory: %s", what, bytes, cudaGetErrorString(err));
+    return MIR_CUDA_ERROR;
+  }
+  return MIR_OK;
+}
+
+template <int D>
+int launch_decode(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages, const bf16* v_pages,
+                  const int* block_table, int table_width, const int* positions, int rows, int page_size, int heads,
+                  int kv_heads, float scale, int window, int partition, int num_partitions, float* partial_o,
+                  float* partial_ml, cudaStream_t stream) {
+  const size_t pipeline = (size_t)kDecodeWarps * 2 * 2 * kDecodeTile * (D + 8) * sizeof(bf16);
+  const size_t combine = (size_t)kDecodeWarps * 16 * (D + 2) * sizeof(float);
+  const size_t smem = pipeline > combine ? pipeline : combine;
+  int status = set_smem(decode_attention_kernel<D>, smem, "decode_attention");
+  if (status != MIR_OK) return status;
+  const int group = heads / kv_heads;
+  const dim3 grid(num_partitions, kv_heads * ((group + 15) / 16), rows);
+  decode_attention_kernel<D><<<grid, kDecodeWarps * 32, smem, stream>>>(
+      q, q_stride, k_pages, v_pages, block_table, table_width, positions, page_size, heads, kv_heads,
+      scale * 1.4426950408889634f, window, partition, num_partitions, partial_o, partial_ml, out);
+  status = mir_check_launch("decode_attention");
+  if (status != MIR_OK || num_partitions == 1) return status;
+  decode_merge_kernel<D><<<dim3(heads, rows), D <= 64 ? 64 : 128, 0, stream>>>(partial_o, partial_ml, positions, heads,
+                                                                             window, partition, num_partitions, out);
+  return mir_check_launch("decode_merge");
+}
+
+template <int D>
+int launch_prefill(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages, const bf16* v_pages,
+                   const int* block_table, int table_width, const int* query_starts, const int* context_lens,
+                   int num_rows, int tokens, int page_size, int heads, int kv_heads, float scale, int window,
+                   cudaStream_t stream) {
+  const size_t smem = (size_t)2 * 2 * kKeyTile * (D + 8) * sizeof(bf16);
+  int status = set_smem(prefill_attention_kernel<D>, smem, "prefill_attention");
+  if (status != MIR_OK) return status;
+  const int tiles = (tokens + kQueryTile - 1) / kQueryTile + num_rows;   // an upper bound; spare CTAs return
+  prefill_attention_kernel<D><<<dim3(tiles, heads), kPrefillWarps * 32, smem, stream>>>(
+      q, q_stride, out, k_pages, v_pages, block_table, table_width, query_starts, context_lens, num_rows, page_size,
+      heads, kv_heads, scale * 1.4426950408889634f, window);
+  return mir_check_launch("prefill_attention");
+}
+
+bool bad_common(const char* what, int heads, int kv_heads, int head_dim, int page_size, int table_width, int window) {
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || page_size <= 0 || table_width <= 0 || window < 0) {
+    mir_set_error("%s: bad sizes (heads %d, kv heads %d, page %d, table width %d)", what, heads, kv_heads, page_size,
+                  table_width);
+    return true;
+  }
+  if (head_dim != 64 && head_dim != 128) {
+    mir_set_error("%s: head_dim %d is not one of 64, 128 (the reference kernel takes the other sizes)", what, head_dim);
+    return true;
+  }
+  return false;
+}
+
+}  // namespace
+
+// How many floats of scratch decode attention needs: partial outputs and (maximum, denominator) pairs.
+MIR_EXPORT long long mir_decode_attention_scratch_floats(int rows, int heads, int head_dim, int num_partitions) {
+  return num_partitions <= 1 ? 0 : (long long)rows * heads * num_partitions * (head_dim + 2);
+}
+
+// One token per row.  `partition` (a multiple of 64) is how many keys one CTA takes; num_partitions must be
+// >= ceil(longest context / partition).  scratch holds mir_decode_attention_scratch_floats floats.
+MIR_EXPORT int mir_decode_attention_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                         const void* v_pages, const int* block_table, int table_width,
+                                         const int* positions, int rows, int page_size, int heads, int kv_heads,
+                                         int head_dim, float scale, int window, int partition, int num_partitions,
+                                         float* scratch, long long scratch_floats, cudaStream_t stream) {
+  if (rows == 0) return MIR_OK;
+  if (bad_common("decode_attention", heads, kv_heads, head_dim, page_size, table_width, window)) return MIR_BAD_ARGUMENT;
+  if (rows < 0 || rows > 65535 || partition <= 0 || partition % 64 || num_partitions <= 0) {
+    mir_set_error("decode_attention: bad rows %d, partition %d or partition count %d", rows, partition, num_partitions);
+    return MIR_BAD_ARGUMENT;
+  }
+  const long long need = mir_decode_attention_scratch_floats(rows, heads, head_dim, num_partitions);
+  if (need > 0 && (scratch == nullptr || scratch_floats < need)) {
+    mir_set_error("decode_attention: scratch of %lld floats is needed, got %lld", need, scratch_floats);
+    return MIR_BAD_ARGUMENT;
+  }
+  float* partial_o = scratch;
+  float* partial_ml = scratch ? scratch + (size_t)rows * heads * num_partitions * head_dim : nullptr;
+  if (head_dim == 64)
+    return launch_decode<64>((const bf16*)q, (size_t)q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages,
+                             block_table, table_width, positions, rows, page_size, heads, kv_heads, scale, window,
+                             partition, num_partitions, partial_o, partial_ml, stream);
+  return launch_decode<128>((const bf16*)q, (size_t)q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages,
+                            block_table, table_width, positions, rows, page_size, heads, kv_heads, scale, window,
+                            partition, num_partitions, partial_o, partial_ml, stream);
+}
+
+// Any mix of portions: row r has tokens query_starts[r] .. query_starts[r+1]-1 of the packed batch, and its
+// request holds context_lens[r] tokens after this step (so the portion starts at context_lens[r] - count).
+MIR_EXPORT int mir_prefill_attention_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                          const void* v_pages, const int* block_table, int table_width,
+                                          const int* query_starts, const int* context_lens, int num_rows, int tokens,
+                                          int page_size, int heads, int kv_heads, int head_dim, float scale,
+                                          int window, cudaStream_t stream) {
+  if (tokens == 0 || num_rows == 0) return MIR_OK;
+  if (bad_common("prefill_attention", heads, kv_heads, head_dim, page_size, table_width, window)) return MIR_BAD_ARGUMENT;
+  if (tokens < 0 || num_rows < 0 || heads > 65535) {
+    mir_set_error("prefill_attention: bad tokens %d, rows %d or heads %d", tokens, num_rows, heads);
+    return MIR_BAD_ARGUMENT;
+  }
+  if (head_dim == 64)
+    return launch_prefill<64>((const bf16*)q, (size_t)q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages,
+                              block_table, table_width, query_starts, context_lens, num_rows, tokens, page_size, heads,
+                              kv_heads, scale, window, stream);
+  return launch_prefill<128>((const bf16*)q, (size_t)q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages,
+                             block_table, table_width, query_starts, context_lens, num_rows, tokens, page_size, heads,
+                             kv_heads, scale, window, stream);
+}

@@ -36,7 +36,7 @@ LIBRARIES = {
         "link": [],
     },
     "bf16": {
-        "sources": ["runtime.cu", "gemm_lt.cu"],
+        "sources": ["runtime.cu", "gemm_lt.cu", "attention_mma.cu"],
         "link": ["-lcublasLt"],
     },
 }

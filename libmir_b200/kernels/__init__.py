@@ -41,6 +41,11 @@ _SIGNATURES = {
         "mir_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p],
     },
     "bf16": {
+        "mir_decode_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                      c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p,
+                                      c_longlong, c_void_p],
+        "mir_prefill_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "mir_gemm_bf16_lt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_void_p, c_size_t, c_void_p],
     },
@@ -231,6 +236,69 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
         _is_bf16(out), qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], row_of_token.data_ptr(), positions.data_ptr(), tokens,
         page_size, heads, kv_heads, head_dim, scale, int(window or 0), _stream()))
+
+
+FAST_HEAD_DIMS = (64, 128)      # what the tensor-core attention kernels take; other sizes use the reference kernel
+SM_COUNT = 148
+
+
+def decode_partitioning(rows: int, kv_heads: int, max_context: int) -> tuple:
+    """(keys per partition, partitions) for split decode attention: the largest partition that still gives
+    about two CTAs per SM, so that long contexts at small batch spread over the whole GPU."""
+    partition = 512
+    while True:
+        count = max(1, -(-max_context // partition))
+        if rows * kv_heads * count >= 2 * SM_COUNT or partition == 64:
+            return partition, count
+        partition //= 2
+
+
+def decode_attention_scratch_floats(rows: int, heads: int, head_dim: int, num_partitions: int) -> int:
+    return 0 if num_partitions <= 1 else rows * heads * num_partitions * (head_dim + 2)
+
+
+def decode_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                     block_table: torch.Tensor, positions: torch.Tensor, page_size: int, heads: int, kv_heads: int,
+                     head_dim: int, scale: float, window: Optional[int], partition: int, num_partitions: int,
+                     scratch: Optional[torch.Tensor]) -> None:
+    """bf16 split-KV attention for a batch of single tokens (row r of qkv belongs to request row r)."""
+    _cuda(qkv, out, k_pages, v_pages, block_table, positions, scratch)
+    rows = out.shape[0]
+    _require(qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
+             and v_pages.dtype == torch.bfloat16 and out.is_contiguous() and out.shape[1] == heads * head_dim,
+             "decode_attention: bfloat16 tensors are needed")
+    _require(block_table.dtype == torch.int32 and block_table.is_contiguous() and positions.dtype == torch.int32
+             and positions.numel() >= rows and block_table.shape[0] >= rows, "decode_attention: bad metadata")
+    _require(scratch is None or scratch.dtype == torch.float32, "decode_attention: scratch must be float32")
+    lib = library("bf16")
+    _check(lib, lib.mir_decode_attention_bf16(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], positions.data_ptr(), rows, page_size, heads, kv_heads, head_dim, scale,
+        int(window or 0), partition, num_partitions, _ptr(scratch), 0 if scratch is None else scratch.numel(),
+        _stream()))
+    global LAUNCHES
+    LAUNCHES += 1 if num_partitions > 1 else 0
+
+
+def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      block_table: torch.Tensor, query_starts: torch.Tensor, context_lens: torch.Tensor,
+                      page_size: int, heads: int, kv_heads: int, head_dim: int, scale: float,
+                      window: Optional[int]) -> None:
+    """bf16 tensor-core attention for any mix of portions (row r owns tokens query_starts[r]..query_starts[r+1])."""
+    _cuda(qkv, out, k_pages, v_pages, block_table, query_starts, context_lens)
+    tokens = out.shape[0]
+    rows = context_lens.numel()
+    _require(qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
+             and v_pages.dtype == torch.bfloat16 and out.is_contiguous() and out.shape[1] == heads * head_dim,
+             "prefill_attention: bfloat16 tensors are needed")
+    _require(block_table.dtype == torch.int32 and block_table.is_contiguous() and query_starts.dtype == torch.int32
+             and context_lens.dtype == torch.int32 and query_starts.numel() == rows + 1
+             and block_table.shape[0] >= rows, "prefill_attention: bad metadata")
+    lib = library("bf16")
+    _check(lib, lib.mir_prefill_attention_bf16(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], query_starts.data_ptr(), context_lens.data_ptr(), rows, tokens, page_size, heads,
+        kv_heads, head_dim, scale, int(window or 0), _stream()))
 
 
 # --------------------------------------------------------------------------- matrix products

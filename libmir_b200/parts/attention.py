@@ -84,8 +84,23 @@ class SoftmaxAttention(Mixer):
         kernels.linear(mixed, self.w_o, residual, self.b_o, accumulate=True)
 
     def attend(self, ctx, group, cache, qkv, out):
-        """Attention of every packed row over its request's pages; the kernel is chosen by size."""
+        """Attention of every packed row over its request's pages; the kernel is chosen by dtype and size:
+        bfloat16 with head_dim 64 or 128 runs on tensor cores (split over the keys when every row is a
+        single decoded token), everything else runs the reference kernel."""
         s = self.spec
+        if self.env.dtype == torch.bfloat16 and s.head_dim in kernels.FAST_HEAD_DIMS:
+            if ctx.decode_only:
+                partition, count = kernels.decode_partitioning(ctx.num_rows, s.kv_heads, ctx.max_context)
+                floats = kernels.decode_attention_scratch_floats(ctx.num_rows, s.heads, s.head_dim, count)
+                scratch = ctx.alloc((floats,), torch.float32) if floats else None
+                kernels.decode_attention(qkv, out, cache.k_pages, cache.v_pages, group.block_table, ctx.positions,
+                                         cache.page_size, s.heads, s.kv_heads, s.head_dim, s.scale, s.window,
+                                         partition, count, scratch)
+            else:
+                kernels.prefill_attention(qkv, out, cache.k_pages, cache.v_pages, group.block_table,
+                                          ctx.query_starts, ctx.context_lens, cache.page_size, s.heads, s.kv_heads,
+                                          s.head_dim, s.scale, s.window)
+            return
         kernels.paged_attention_generic(qkv, out, cache.k_pages, cache.v_pages, group.block_table, ctx.row_of_token,
                                         ctx.positions, cache.page_size, s.heads, s.kv_heads, s.head_dim, s.scale,
                                         s.window)

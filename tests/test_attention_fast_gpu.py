@@ -1,0 +1,198 @@
+"""The tensor-core attention kernels (bf16, head_dim 64/128) alone against plain attention: decode split
+over partitions of the keys, and portions of prompts; shuffled pages, garbage elsewhere in the pool,
+windows, groups of 1 to 20 query heads per kv head, one dominant far key, the window's edge."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_impl
+
+pytestmark = pytest.mark.gpu
+
+BF16 = torch.bfloat16
+
+
+def cuda(t):
+    return t.to("cuda")
+
+
+def build_pool(ks, vs, page, rng, garbage=50.0):
+    """Scatter each request's keys/values into shuffled pages of one pool; returns pools and the tables."""
+    kv_heads, dim = ks[0].shape[1:]
+    blocks = [-(-k.shape[0] // page) for k in ks]
+    total = sum(blocks) + 5
+    order = rng.permutation(total)
+    k_pool = (torch.randn(total * page, kv_heads, dim) * garbage).to(BF16)
+    v_pool = (torch.randn(total * page, kv_heads, dim) * garbage).to(BF16)
+    table = torch.full((len(ks), max(blocks)), -1, dtype=torch.int32)
+    cursor = 0
+    for r, (k, v) in enumerate(zip(ks, vs)):
+        for block in range(blocks[r]):
+            physical = int(order[cursor]); cursor += 1
+            table[r, block] = physical
+            chunk = slice(block * page, min(k.shape[0], (block + 1) * page))
+            n = chunk.stop - chunk.start
+            k_pool[physical * page: physical * page + n] = k[chunk]
+            v_pool[physical * page: physical * page + n] = v[chunk]
+    return k_pool, v_pool, table
+
+
+def expect(q, k, v, scale, window, rows):
+    full = plain_impl.attention_scores_softmax_values(q.double(), k.double(), v.double(), scale, window)
+    return full[rows]
+
+
+def close(got, want, tol=2e-2):
+    want, got = want.double().cpu(), got.double().cpu()
+    bound = tol * max(1.0, float(want.abs().max()))
+    error = float((got - want).abs().max())
+    assert torch.isfinite(got).all() and error <= bound, f"max |diff| {error:.3e} > {bound:.3e}"
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,page,window,partition", [
+    (32, 8, 128, 16, None, 512), (32, 8, 128, 16, None, 64), (8, 8, 64, 8, None, 128), (16, 1, 128, 16, 300, 256),
+    (40, 2, 64, 4, None, 64), (6, 3, 128, 32, 70, 64), (4, 4, 128, 1, None, 192), (64, 8, 128, 16, None, 128)])
+def test_decode_attention(heads, kv_heads, dim, page, window, partition):
+    from libmir_b200 import kernels
+    rng = np.random.default_rng(heads + dim)
+    torch.manual_seed(heads * dim)
+    lengths = [700, 1, 64, 65, 513, 16]
+    scale = 0.8 / math.sqrt(dim)
+    qs = [(torch.randn(n, heads, dim) * 2).to(BF16) for n in lengths]
+    ks = [(torch.randn(n, kv_heads, dim) * 2).to(BF16) for n in lengths]
+    vs = [torch.randn(n, kv_heads, dim).to(BF16) for n in lengths]
+    k_pool, v_pool, table = build_pool(ks, vs, page, rng)
+    rows = len(lengths) + 2                                      # two padding rows, as in a captured batch
+    q_rows = torch.cat([q[-1:] for q in qs] + [torch.zeros(2, heads, dim, dtype=BF16)]).reshape(rows, heads * dim)
+    packed = torch.cat([q_rows, torch.randn(rows, 2 * kv_heads * dim).to(BF16)], dim=1).contiguous()
+    positions = torch.tensor([n - 1 for n in lengths] + [-1, -1], dtype=torch.int32)
+    table = torch.cat([table, torch.zeros(2, table.shape[1], dtype=torch.int32)])
+    count = -(-max(lengths) // partition)
+    floats = kernels.decode_attention_scratch_floats(rows, heads, dim, count)
+    scratch = torch.full((max(floats, 1),), float("nan"), device="cuda")
+    out = torch.full((rows, heads * dim), 9.0, device="cuda", dtype=BF16)
+    kernels.decode_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table), cuda(positions), page, heads,
+                             kv_heads, dim, scale, window, partition, count, scratch if floats else None)
+    expected = torch.cat([expect(q, k, v, scale, window, slice(n - 1, n)) for q, k, v, n in zip(qs, ks, vs, lengths)])
+    close(out[:len(lengths)].reshape(len(lengths), heads, dim), expected)
+    if count > 1:
+        assert float(out[len(lengths):].abs().max()) == 0.0     # padding rows give zeros
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,page,window", [
+    (8, 2, 128, 16, None), (4, 4, 64, 8, None), (6, 1, 128, 16, 100), (3, 3, 64, 4, 17), (32, 8, 128, 16, None)])
+def test_prefill_attention_mixed_portions(heads, kv_heads, dim, page, window):
+    """Four rows in one batch: a whole 200-token prompt, a 70-token portion that starts at 333, a single
+    decoded token at 129, and a 2-token portion at 64 (a page's and a tile's edge)."""
+    from libmir_b200 import kernels
+    rng = np.random.default_rng(dim + heads)
+    torch.manual_seed(dim + heads)
+    spans = [(0, 200), (333, 403), (129, 130), (64, 66)]
+    scale = 0.8 / math.sqrt(dim)
+    qs = [(torch.randn(end, heads, dim) * 2).to(BF16) for _, end in spans]
+    ks = [(torch.randn(end, kv_heads, dim) * 2).to(BF16) for _, end in spans]
+    vs = [torch.randn(end, kv_heads, dim).to(BF16) for _, end in spans]
+    k_pool, v_pool, table = build_pool(ks, vs, page, rng)
+    q_rows = torch.cat([q[start:end] for q, (start, end) in zip(qs, spans)])
+    tokens = q_rows.shape[0]
+    packed = torch.cat([q_rows.reshape(tokens, -1), torch.randn(tokens, 2 * kv_heads * dim).to(BF16)], dim=1).contiguous()
+    starts = np.cumsum([0] + [end - start for start, end in spans])
+    out = torch.full((tokens, heads * dim), 9.0, device="cuda", dtype=BF16)
+    kernels.prefill_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table),
+                              cuda(torch.tensor(starts, dtype=torch.int32)),
+                              cuda(torch.tensor([end for _, end in spans], dtype=torch.int32)), page, heads, kv_heads,
+                              dim, scale, window)
+    expected = torch.cat([expect(q, k, v, scale, window, slice(start, end))
+                          for q, k, v, (start, end) in zip(qs, ks, vs, spans)])
+    close(out.reshape(tokens, heads, dim), expected)
+
+
+@pytest.mark.parametrize("kind", ["decode", "prefill"])
+def test_one_far_key_among_hundreds_and_the_windows_edge(kind):
+    from libmir_b200 import kernels
+    heads, kv_heads, dim, page, n = 8, 2, 128, 16, 1100
+    torch.manual_seed(11)
+    direction = torch.randn(dim)
+    direction /= direction.norm()
+
+    def run(strong_key, window):
+        k = torch.randn(n, kv_heads, dim) * 0.05
+        k[strong_key] = direction * 8.0
+        v = torch.randn(n, kv_heads, dim)
+        q = (direction.repeat(1, heads, 1) * 8.0).to(BF16)
+        k, v = k.to(BF16), v.to(BF16)
+        k_pool, v_pool, table = build_pool([k], [v], page, np.random.default_rng(strong_key), garbage=0.0)
+        packed = torch.cat([q.reshape(1, -1), torch.zeros(1, 2 * kv_heads * dim, dtype=BF16)], dim=1)
+        out = torch.empty(1, heads * dim, device="cuda", dtype=BF16)
+        if kind == "decode":
+            count = -(-n // 128)
+            scratch = torch.empty(kernels.decode_attention_scratch_floats(1, heads, dim, count), device="cuda")
+            kernels.decode_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table),
+                                     cuda(torch.tensor([n - 1], dtype=torch.int32)), page, heads, kv_heads, dim, 1.0,
+                                     window, 128, count, scratch)
+        else:
+            kernels.prefill_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table),
+                                      cuda(torch.tensor([0, 1], dtype=torch.int32)),
+                                      cuda(torch.tensor([n], dtype=torch.int32)), page, heads, kv_heads, dim, 1.0,
+                                      window)
+        return out.reshape(heads, dim).float().cpu(), v.float()
+
+    for strong in (0, 15, 16, 63, 64, 127, 128, 600, n - 1):
+        out, v = run(strong, None)
+        for head in range(heads):
+            assert torch.allclose(out[head], v[strong, head // 4], atol=3e-2), f"{kind}: key {strong} was not seen"
+    window = 333                                                       # visible keys: n - 333 .. n - 1
+    out, v = run(n - window, window)
+    assert torch.allclose(out[0], v[n - window, 0], atol=3e-2), "the first key inside the window was not seen"
+    out, v = run(n - window - 1, window)
+    assert not torch.allclose(out[0], v[n - window - 1, 0], atol=0.3), "a key outside the window was seen"
+
+
+def test_fast_kernels_refuse_other_head_sizes():
+    from libmir_b200 import KernelError, kernels
+    z = lambda *shape: torch.zeros(*shape, device="cuda", dtype=BF16)
+    meta = lambda *shape: torch.zeros(*shape, device="cuda", dtype=torch.int32)
+    with pytest.raises(KernelError, match="head_dim 48 is not one of 64, 128"):
+        kernels.decode_attention(z(1, 3 * 48), z(1, 48), z(16, 1, 48), z(16, 1, 48), meta(1, 1), meta(1), 16, 1, 1, 48,
+                                 1.0, None, 64, 1, None)
+    with pytest.raises(KernelError, match="head_dim 80 is not one of 64, 128"):
+        kernels.prefill_attention(z(1, 3 * 80), z(1, 80), z(16, 1, 80), z(16, 1, 80), meta(1, 1), meta(2), meta(1), 16,
+                                  1, 1, 80, 1.0, None)
+
+
+def test_engine_uses_the_fast_kernels_and_matches_the_plain_model(tmp_path):
+    """A model with head_dim 64 in bfloat16: prompt portions, mixed steps and graph-captured decode steps
+    all run the tensor-core kernels; logits against the plain implementation."""
+    from helpers import TOL, make_folder, plain_logits, random_ids
+    from libmir_b200 import CacheConfig, Library, RuntimeConfig, StepEntry
+    from libmir_b200.sampling import RequestSampler
+    config = {"architectures": ["Qwen3ForCausalLM"], "hidden_size": 128, "intermediate_size": 320,
+              "num_hidden_layers": 2, "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 64,
+              "vocab_size": 500, "max_position_embeddings": 2048, "rms_norm_eps": 1e-6, "rope_theta": 1e6,
+              "tie_word_embeddings": True}
+    folder = make_folder(tmp_path, config, seed=5, dtype="bfloat16", sharpen=4.0)
+    rng = np.random.default_rng(0)
+    first, second = random_ids(rng, 500, 900), random_ids(rng, 500, 300)
+    ref_first, ref_second = plain_logits(folder, first), plain_logits(folder, second)
+    model = Library(RuntimeConfig(kv_cache=CacheConfig(block_size=16, block_count=128), dtype="bfloat16")).load(folder)
+    model.admit("a"); model.admit("b")
+
+    def check(got, want, label):
+        error = float(np.abs(got - want).max())
+        assert error <= TOL["bfloat16"] * max(1.0, float(np.abs(want).max())), f"{label}: {error:.3e}"
+
+    result = model.step([StepEntry("a", first[:700], [0, 350, 699])])
+    check(result.logits.cpu().numpy(), ref_first[[0, 350, 699]], "whole portion")
+    result = model.step([StepEntry("a", first[700:701], [0]), StepEntry("b", second[:250], [249])])
+    check(result.logits.cpu().numpy(), np.stack([ref_first[700], ref_second[249]]), "mixed step")
+    samplers = [RequestSampler(), RequestSampler()]
+    for offset in range(40):                                           # captured decode steps, two requests
+        result = model.step([StepEntry("a", [first[701 + offset]], [0]), StepEntry("b", [second[250 + offset]], [0])],
+                            samplers)
+        check(result.logits.cpu().numpy(), np.stack([ref_first[701 + offset], ref_second[250 + offset]]),
+              f"decode step {offset}")
+        assert result.tokens.cpu().tolist() == [int(np.argmax(l)) for l in result.logits.cpu().numpy()]
+    assert model.runner._graphs is not None and len(model.runner._graphs.graphs) >= 1
