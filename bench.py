@@ -126,6 +126,10 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--skip-points", action="store_true", help="only the batch-8 decode and the prefill")
+    parser.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
+                        help="decode / prefill: run only that phase, bracketed by cudaProfilerStart/Stop (for ncu "
+                             "--profile-from-start off); the JSON line then holds only that phase")
+    parser.add_argument("--no-graphs", action="store_true", help="decode steps as plain launches, not as CUDA graphs")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -156,7 +160,7 @@ def main() -> int:
     runtime = RuntimeConfig(kv_cache=CacheConfig(block_size=PAGE_SIZE, block_count=pages),
                             scheduler=SchedulerConfig(max_batch_requests=max_batch, max_batch_tokens=8192,
                                                       prefill_chunk_tokens=4096),
-                            cuda=CudaConfig(decode_graphs=True), dtype="bfloat16")
+                            cuda=CudaConfig(decode_graphs=not args.no_graphs), dtype="bfloat16")
     torch.cuda.set_device(0)
     model = Library(runtime).load_random(config, seed=0)
     rng = np.random.default_rng(0)
@@ -207,7 +211,7 @@ def main() -> int:
         release(ids)
         return batch * steps / (ms / 1e3), ms / steps, launches, clocks.summary(), context
 
-    def decode_e2e(batch, steps, warmup):
+    def decode_e2e(batch, steps, warmup, profile=False):
         """The same through Model.step: host ids in, sampled ids out, every step."""
         ids = fill(batch)
         samplers = [RequestSampler() for _ in ids]
@@ -217,11 +221,15 @@ def main() -> int:
         for step in range(warmup + steps):
             if step == warmup:
                 torch.cuda.synchronize()
+                if profile:
+                    torch.cuda.profiler.start()
                 started = time.perf_counter()
             result = model.step([StepEntry(i, [t], [0]) for i, t in zip(ids, tokens)], samplers)
             tokens = result.tokens.cpu().tolist()
         torch.cuda.synchronize()
         seconds = time.perf_counter() - started
+        if profile:
+            torch.cuda.profiler.stop()
         graphs = model.runner._graphs.graphs if model.runner._graphs else {}
         for graph in graphs.values():
             if graph.rows >= batch:
@@ -230,7 +238,7 @@ def main() -> int:
         release(ids)
         return batch * steps / seconds, h2d, d2h
 
-    def prefill(repeats=5):
+    def prefill(repeats=5, profile=False):
         tokens = rng.integers(0, vocab, size=PROMPT_TOKENS).tolist()
         times = []
         for index in range(repeats + 2):
@@ -238,6 +246,8 @@ def main() -> int:
             model.admit(request_id)
             start, stop = event_pair()
             torch.cuda.synchronize()
+            if profile and index == 2:
+                torch.cuda.profiler.start()
             start.record()
             result = model.step([StepEntry(request_id, tokens, [PROMPT_TOKENS - 1])], [RequestSampler()])
             stop.record()
@@ -246,6 +256,8 @@ def main() -> int:
             model.release(request_id)
             if index >= 2:
                 times.append(start.elapsed_time(stop))
+        if profile:
+            torch.cuda.profiler.stop()
         return statistics.median(times)
 
     hidden, inter, heads, kv_heads, dim = (config[k] for k in ("hidden_size", "intermediate_size",
@@ -255,6 +267,16 @@ def main() -> int:
     gemm_flops = 2.0 * PROMPT_TOKENS * per_layer * layers + 2.0 * hidden * vocab
     attention_flops = 4.0 * heads * dim * (PROMPT_TOKENS * (PROMPT_TOKENS + 1) / 2.0) * layers
     prefill_flops = gemm_flops + attention_flops
+
+    if args.phase == "decode":
+        tokens_per_second, _, _ = decode_e2e(args.batch, args.steps, args.warmup, profile=True)
+        print(json.dumps({"phase": "decode", "batch": args.batch, "steps": args.steps, "layers": layers,
+                          "graphs": not args.no_graphs, "tokens_per_second": round(tokens_per_second, 1)}))
+        return 0
+    if args.phase == "prefill":
+        ms = prefill(repeats=max(1, min(args.steps, 5)), profile=True)
+        print(json.dumps({"phase": "prefill", "tokens": PROMPT_TOKENS, "layers": layers, "ms": round(ms, 3)}))
+        return 0
 
     value, ms_per_step, launches, clocks, context = decode_device(args.batch, args.steps, args.warmup)
     step_bytes = weight_bytes + args.batch * context * kv_bytes_per_token

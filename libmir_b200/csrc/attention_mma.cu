@@ -65,81 +65,106 @@ __device__ __forceinline__ float quad_sum(float v) {
   return v + __shfl_xor_sync(0xffffffffu, v, 2);
 }
 
-// Copy `keys` rows of head_dim bf16 (one kv head) from the pages into padded shared-memory rows.
-// Row i holds key `first_key + i`; rows whose key is >= limit are zero-filled.  THREADS threads cooperate.
-template <int D, int THREADS>
-__device__ __forceinline__ void load_rows(bf16* dst, const bf16* __restrict__ pages, const int* __restrict__ table,
-                                          int page_size, int kv_heads, int kv_head, int first_key, int keys,
-                                          int limit, int thread) {
-  constexpr int CHUNKS = D / 8;          // 16-byte chunks per row
+// Copy ROWS consecutive keys and their values (one kv head, head_dim bf16 each) from the pages into padded
+// shared-memory rows.  Row i holds key `first_key + i`; rows whose key is >= limit are zero-filled.  Two
+// threads share a row (half a row each), so a thread looks its page up ONCE and then issues head_dim / 16
+// 16-byte copies for the key and as many for the value, which lie at the same slot of their pools.
+template <int D, int ROWS>
+__device__ __forceinline__ void load_tile(bf16* k_dst, bf16* v_dst, const bf16* __restrict__ k_pages,
+                                          const bf16* __restrict__ v_pages, const int* __restrict__ table,
+                                          int page_size, int kv_heads, int kv_head, int first_key, int limit,
+                                          int thread) {
   constexpr int STRIDE = D + 8;
-  for (int c = thread; c < keys * CHUNKS; c += THREADS) {
-    const int r = c / CHUNKS, chunk = c % CHUNKS;
-    const int key = first_key + r;
-    const bool valid = key < limit;
-    const bf16* src = pages;
-    if (valid) {
-      const int page = table[key / page_size];
-      src = pages + (((size_t)page * page_size + key % page_size) * kv_heads + kv_head) * D + chunk * 8;
-    }
-    cp_async16(smem_u32(dst + r * STRIDE + chunk * 8), src, valid);
+  constexpr int HALF = D / 2;            // elements per thread
+  const int r = thread >> 1, half = thread & 1;
+  if (r >= ROWS) return;
+  const int key = first_key + r;
+  const bool valid = key < limit;
+  size_t offset = 0;
+  if (valid) {
+    const int block = key / page_size;
+    const int page = table[block];
+    offset = (((size_t)page * page_size + (key - block * page_size)) * kv_heads + kv_head) * D + half * HALF;
   }
+  const bf16* k_src = k_pages + offset;
+  const bf16* v_src = v_pages + offset;
+  const uint32_t k_smem = smem_u32(k_dst + r * STRIDE + half * HALF);
+  const uint32_t v_smem = smem_u32(v_dst + r * STRIDE + half * HALF);
+#pragma unroll
+  for (int j = 0; j < HALF / 8; ++j) cp_async16(k_smem + j * 16, k_src + j * 8, valid);
+#pragma unroll
+  for (int j = 0; j < HALF / 8; ++j) cp_async16(v_smem + j * 16, v_src + j * 8, valid);
 }
 
-// S[16 x 16 keys] += Q[16 x D] . K^T for one 16-key tile (two n-tiles of 8 keys).
-template <int D>
-__device__ __forceinline__ void scores_16(float (&s)[2][4], const uint32_t (&qa)[D / 16][4], const bf16* k_tile,
-                                          int lane) {
+// S[16 x NT*8 keys] += Q[16 x D] . K^T for NT n-tiles of 8 keys (NT even).
+template <int D, int NT>
+__device__ __forceinline__ void scores(float (&s)[NT][4], const uint32_t (&qa)[D / 16][4], const bf16* k_tile,
+                                       int lane) {
   constexpr int STRIDE = D + 8;
   const int mat = lane >> 3, rowin = lane & 7;
   const bf16* base = k_tile + ((mat >> 1) * 8 + rowin) * STRIDE + (mat & 1) * 8;
 #pragma unroll
   for (int ks = 0; ks < D / 16; ++ks) {
-    uint32_t b[4];
-    ldmatrix_x4(b, smem_u32(base + ks * 16));
-    mma_bf16(s[0], qa[ks], b[0], b[1]);
-    mma_bf16(s[1], qa[ks], b[2], b[3]);
+#pragma unroll
+    for (int pair = 0; pair < NT / 2; ++pair) {
+      uint32_t b[4];
+      ldmatrix_x4(b, smem_u32(base + pair * 16 * STRIDE + ks * 16));
+      mma_bf16(s[2 * pair], qa[ks], b[0], b[1]);
+      mma_bf16(s[2 * pair + 1], qa[ks], b[2], b[3]);
+    }
   }
 }
 
-// O[16 x D] += P[16 x 16 keys] . V for one 16-key tile.
-template <int D>
-__device__ __forceinline__ void values_16(float (&o)[D / 8][4], const uint32_t (&pa)[4], const bf16* v_tile, int lane) {
+// O[16 x D] += P[16 x NT*8 keys] . V.
+template <int D, int NT>
+__device__ __forceinline__ void values(float (&o)[D / 8][4], const uint32_t (&pa)[NT / 2][4], const bf16* v_tile,
+                                       int lane) {
   constexpr int STRIDE = D + 8;
   const int mat = lane >> 3, rowin = lane & 7;
   const bf16* base = v_tile + ((mat & 1) * 8 + rowin) * STRIDE + (mat >> 1) * 8;
 #pragma unroll
-  for (int np = 0; np < D / 16; ++np) {
-    uint32_t b[4];
-    ldmatrix_x4_trans(b, smem_u32(base + np * 16));
-    mma_bf16(o[2 * np], pa, b[0], b[1]);
-    mma_bf16(o[2 * np + 1], pa, b[2], b[3]);
+  for (int kk = 0; kk < NT / 2; ++kk) {
+#pragma unroll
+    for (int np = 0; np < D / 16; ++np) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, smem_u32(base + kk * 16 * STRIDE + np * 16));
+      mma_bf16(o[2 * np], pa[kk], b[0], b[1]);
+      mma_bf16(o[2 * np + 1], pa[kk], b[2], b[3]);
+    }
   }
 }
 
-// Online-softmax update of one 16-row block with the scores of 16 keys (already scaled to log2 units and
+// Online-softmax update of one 16-row block with the scores of NT*8 keys (already scaled to log2 units and
 // masked with -inf).  m/l are per thread for its two rows (lane/4 and lane/4 + 8); l is a per-thread partial
 // sum that the caller reduces over the quad at the end.
-template <int D>
-__device__ __forceinline__ void softmax_16(float (&s)[2][4], float (&m)[2], float (&l)[2], float (&o)[D / 8][4],
-                                           uint32_t (&pa)[4]) {
-  float mx0 = quad_max(fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1])));
-  float mx1 = quad_max(fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3])));
+template <int D, int NT>
+__device__ __forceinline__ void softmax(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&o)[D / 8][4],
+                                        uint32_t (&pa)[NT / 2][4]) {
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+    mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+  }
+  mx0 = quad_max(mx0);
+  mx1 = quad_max(mx1);
   const float new0 = fmaxf(m[0], mx0), new1 = fmaxf(m[1], mx1);
   const float ref0 = new0 == -INFINITY ? 0.0f : new0, ref1 = new1 == -INFINITY ? 0.0f : new1;
   const float corr0 = exp2f(m[0] - ref0), corr1 = exp2f(m[1] - ref1);
   m[0] = new0;
   m[1] = new1;
-  float p[2][4];
+  float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-  for (int nt = 0; nt < 2; ++nt) {
-    p[nt][0] = exp2f(s[nt][0] - ref0);
-    p[nt][1] = exp2f(s[nt][1] - ref0);
-    p[nt][2] = exp2f(s[nt][2] - ref1);
-    p[nt][3] = exp2f(s[nt][3] - ref1);
+  for (int nt = 0; nt < NT; ++nt) {
+    s[nt][0] = exp2f(s[nt][0] - ref0);
+    s[nt][1] = exp2f(s[nt][1] - ref0);
+    s[nt][2] = exp2f(s[nt][2] - ref1);
+    s[nt][3] = exp2f(s[nt][3] - ref1);
+    sum0 += s[nt][0] + s[nt][1];
+    sum1 += s[nt][2] + s[nt][3];
   }
-  l[0] = l[0] * corr0 + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
-  l[1] = l[1] * corr1 + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
+  l[0] = l[0] * corr0 + sum0;
+  l[1] = l[1] * corr1 + sum1;
 #pragma unroll
   for (int nt = 0; nt < D / 8; ++nt) {
     o[nt][0] *= corr0;
@@ -147,10 +172,13 @@ __device__ __forceinline__ void softmax_16(float (&s)[2][4], float (&m)[2], floa
     o[nt][2] *= corr1;
     o[nt][3] *= corr1;
   }
-  pa[0] = pack_bf16(p[0][0], p[0][1]);
-  pa[1] = pack_bf16(p[0][2], p[0][3]);
-  pa[2] = pack_bf16(p[1][0], p[1][1]);
-  pa[3] = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; ++kk) {
+    pa[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    pa[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    pa[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    pa[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------ decode
@@ -209,20 +237,17 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
 
   const int stride_keys = kDecodeWarps * kDecodeTile;
   int tile = begin + warp * kDecodeTile;
-  if (tile < part_end) {
-    load_rows<D, 32>(stage_base, k_pages, table, page_size, kv_heads, kv_head, tile, kDecodeTile, part_end, lane);
-    load_rows<D, 32>(stage_base + TILE_ELEMS, v_pages, table, page_size, kv_heads, kv_head, tile, kDecodeTile,
-                     part_end, lane);
-  }
+  if (tile < part_end)
+    load_tile<D, kDecodeTile>(stage_base, stage_base + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads,
+                              kv_head, tile, part_end, lane);
   cp_async_commit();
   int stage = 0;
   for (; tile < part_end; tile += stride_keys, stage ^= 1) {
     const int next = tile + stride_keys;
     if (next < part_end) {
       bf16* dst = stage_base + (stage ^ 1) * 2 * TILE_ELEMS;
-      load_rows<D, 32>(dst, k_pages, table, page_size, kv_heads, kv_head, next, kDecodeTile, part_end, lane);
-      load_rows<D, 32>(dst + TILE_ELEMS, v_pages, table, page_size, kv_heads, kv_head, next, kDecodeTile, part_end,
-                       lane);
+      load_tile<D, kDecodeTile>(dst, dst + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head, next,
+                                part_end, lane);
     }
     cp_async_commit();
     cp_async_wait<1>();
@@ -230,7 +255,7 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
     const bf16* k_tile = stage_base + stage * 2 * TILE_ELEMS;
     const bf16* v_tile = k_tile + TILE_ELEMS;
     float s[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
-    scores_16<D>(s, qa, k_tile, lane);
+    scores<D, 2>(s, qa, k_tile, lane);
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -238,9 +263,9 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
         const int key = tile + nt * 8 + (lane & 3) * 2 + (e & 1);
         s[nt][e] = (key >= first_key && key <= position) ? s[nt][e] * scale_log2 : -INFINITY;
       }
-    uint32_t pa[4];
-    softmax_16<D>(s, m, l, o, pa);
-    values_16<D>(o, pa, v_tile, lane);
+    uint32_t pa[1][4];
+    softmax<D, 2>(s, m, l, o, pa);
+    values<D, 2>(o, pa, v_tile, lane);
     __syncwarp();
   }
   cp_async_wait<0>();
@@ -331,7 +356,7 @@ constexpr int kQueryTile = kPrefillWarps * 16;     // 64 tokens per CTA
 constexpr int kKeyTile = 64;
 
 template <int D>
-__global__ void __launch_bounds__(kPrefillWarps * 32)
+__global__ void __launch_bounds__(kPrefillWarps * 32, 3)
 prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __restrict__ out,
                          const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                          const int* __restrict__ block_table, int table_width, const int* __restrict__ query_starts,
@@ -348,7 +373,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
   // which request row and which 64-token tile of its portion this CTA has
   int row = -1, local_tile = 0;
   {
-    int remaining = blockIdx.x;
+    int remaining = gridDim.x - 1 - blockIdx.x;              // late tiles see the most keys: start them first
     for (int r = 0; r < num_rows; ++r) {
       const int tiles = (query_starts[r + 1] - query_starts[r] + kQueryTile - 1) / kQueryTile;
       if (remaining < tiles) { row = r; local_tile = remaining; break; }
@@ -394,20 +419,16 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
   const int warp_first = min(first_position + warp * 16, last_position);
   const int warp_first_key = (window > 0 && warp_first + 1 > window) ? warp_first + 1 - window : 0;
 
-  load_rows<D, kPrefillWarps * 32>(buffers, k_pages, table, page_size, kv_heads, kv_head, key_begin, kKeyTile, key_end,
-                                   threadIdx.x);
-  load_rows<D, kPrefillWarps * 32>(buffers + TILE_ELEMS, v_pages, table, page_size, kv_heads, kv_head, key_begin,
-                                   kKeyTile, key_end, threadIdx.x);
+  load_tile<D, kKeyTile>(buffers, buffers + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head,
+                         key_begin, key_end, threadIdx.x);
   cp_async_commit();
   int stage = 0;
   for (int key0 = key_begin; key0 < key_end; key0 += kKeyTile, stage ^= 1) {
     const int next = key0 + kKeyTile;
     if (next < key_end) {
       bf16* dst = buffers + (stage ^ 1) * 2 * TILE_ELEMS;
-      load_rows<D, kPrefillWarps * 32>(dst, k_pages, table, page_size, kv_heads, kv_head, next, kKeyTile, key_end,
-                                       threadIdx.x);
-      load_rows<D, kPrefillWarps * 32>(dst + TILE_ELEMS, v_pages, table, page_size, kv_heads, kv_head, next, kKeyTile,
-                                       key_end, threadIdx.x);
+      load_tile<D, kKeyTile>(dst, dst + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head, next,
+                             key_end, threadIdx.x);
     }
     cp_async_commit();
     cp_async_wait<1>();
@@ -417,26 +438,26 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
     // this warp needs the tile only if some key of it is visible to some of its rows
     if (key0 <= warp_last && key0 + kKeyTile > warp_first_key) {
       const bool needs_mask = key0 + kKeyTile - 1 > warp_first || (window > 0 && key0 < warp_last + 1 - window + 15);
+      constexpr int NT = kKeyTile / 8;
+      float s[NT][4];
 #pragma unroll
-      for (int sub = 0; sub < kKeyTile / 16; ++sub) {
-        const int sub0 = key0 + sub * 16;
-        if (sub0 > warp_last) break;
-        float s[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
-        scores_16<D>(s, qa, k_tile + sub * 16 * STRIDE, lane);
+      for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+      scores<D, NT>(s, qa, k_tile, lane);
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int key = sub0 + nt * 8 + c + (e & 1);
+        for (int e = 0; e < 4; ++e) {
+          bool visible = true;
+          if (needs_mask) {
+            const int key = key0 + nt * 8 + c + (e & 1);
             const int pos = (e < 2) ? pos0 : pos1;
-            bool visible = true;
-            if (needs_mask) visible = key <= pos && (window <= 0 || key > pos - window);
-            s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+            visible = key <= pos && (window <= 0 || key > pos - window);
           }
-        uint32_t pa[4];
-        softmax_16<D>(s, m, l, o, pa);
-        values_16<D>(o, pa, v_tile + sub * 16 * STRIDE, lane);
-      }
+          s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+        }
+      uint32_t pa[NT / 2][4];
+      softmax<D, NT>(s, m, l, o, pa);
+      values<D, NT>(o, pa, v_tile, lane);
     }
     __syncthreads();
   }

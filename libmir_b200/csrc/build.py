@@ -36,7 +36,7 @@ LIBRARIES = {
         "link": [],
     },
     "bf16": {
-        "sources": ["runtime.cu", "gemm_lt.cu", "attention_mma.cu"],
+        "sources": ["runtime.cu", "gemm_lt.cu", "attention_mma.cu", "gemm_skinny.cu"],
         "link": ["-lcublasLt"],
     },
 }

@@ -51,6 +51,26 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
   out[index] = from_float<T>(g / (1.0f + expf(-g)) * u);
 }
 
+// The same, 8 columns per thread with 16-byte loads and stores (inter a multiple of 8, bf16).
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                                       int inter, size_t total8) {
+  const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index >= total8) return;
+  const int per_row = inter / 8;
+  const size_t row = index / per_row;
+  const int col = (int)(index - row * per_row) * 8;
+  float g[8], u[8];
+  load8(gu + row * 2 * inter + col, g);
+  load8(gu + row * 2 * inter + inter + col, u);
+  uint4 packed;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    h[i] = __floats2bfloat162_rn(g[2 * i] / (1.0f + expf(-g[2 * i])) * u[2 * i],
+                                 g[2 * i + 1] / (1.0f + expf(-g[2 * i + 1])) * u[2 * i + 1]);
+  *reinterpret_cast<uint4*>(out + row * inter + col) = packed;
+}
+
 // x[r, c] += bias[c]  (32-bit residual; used when a projection that accumulates into the residual has a bias).
 template <typename T>
 __global__ void add_bias_kernel(float* __restrict__ x, const T* __restrict__ bias, int cols, size_t total) {
@@ -95,7 +115,9 @@ MIR_EXPORT int mir_rms_norm(int bf16, const float* x, const float* weight, void*
 MIR_EXPORT int mir_silu_mul(int bf16, const void* gu, void* out, int rows, int inter, cudaStream_t stream) {
   if (rows < 0 || inter <= 0) { mir_set_error("silu_mul: bad sizes"); return MIR_BAD_ARGUMENT; }
   const size_t total = (size_t)rows * inter;
-  if (bf16) LAUNCH_1D(silu_mul_kernel, total, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
+  if (bf16 && inter % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0)
+    LAUNCH_1D(silu_mul_bf16x8_kernel, total / 8, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total / 8);
+  else if (bf16) LAUNCH_1D(silu_mul_kernel, total, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
   else LAUNCH_1D(silu_mul_kernel, total, (const float*)gu, (float*)out, inter, total);
   return mir_check_launch("silu_mul");
 }

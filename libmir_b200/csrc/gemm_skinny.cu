@@ -1,0 +1,222 @@
+// Matrix products with few rows (1 to 64 tokens) in bf16: the decode step's projections.
+//
+//   out[M, N] = epilogue(x[M, K] . w[N, K]^T)
+// With so few tokens the product is a stream of the weights: the work is to read w once at the speed of
+// HBM.  The roles are swapped for the tensor cores: 16 rows of w are the M side of mma.m16n8k16 and 8
+// tokens are the N side.  A CTA owns a strip of rows of w; its 8 warps split K between them (every warp
+// takes every 8th block of 32 k), each lane reading 16 bytes of a row at a time, and the 8 partial
+// sums are added in shared memory in warp order, so the result is deterministic and needs no atomics.
+//
+// No data is rearranged for the fragments: inside one mma the order of k does not matter as long as
+// both operands use the same order, so a lane keeps the 8 consecutive k it loaded from a row of w and
+// the same 8 consecutive k of its token of x, and feeds them as (k, k+1 | k+4, k+5) and
+// (k+2, k+3 | k+6, k+7) of two mma steps.
+//
+// Epilogues (fused so that no extra kernel or round trip of the result is needed):
+//   STORE   out bf16 = acc (+ bias)                       QKV projection, output head in bf16
+//   ACCUM   out float += acc (+ bias)                     output and down projections into the residual
+//   F32     out float = acc (+ bias)                      output head (32-bit logits)
+//   SWIGLU  out bf16 = silu(acc_gate) * acc_up            w holds [gate rows; up rows]: one launch, and
+//                                                         the gate|up intermediate is never written
+// libmir plans a GEMV only for one token (DenseVectorPlan, cuda/src/backend/linear/autotune/
+// candidate.rs:92-98) and otherwise a library GEMM followed by separate add / gate kernels
+// (cuda/kernels/elementwise_bf16.cu:3-11,42-70).
+#include "common.cuh"
+
+using namespace mir;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+constexpr int kWarps = 8;
+enum Epilogue : int { STORE = 0, ACCUM = 1, F32 = 2, SWIGLU = 3 };
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 load_stream(const bf16* p, bool valid) {
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if (valid) v = __ldcs(reinterpret_cast<const uint4*>(p));      // read once: do not keep in L1
+  return v;
+}
+__device__ __forceinline__ uint4 load_cached(const bf16* p, bool valid) {
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if (valid) v = __ldg(reinterpret_cast<const uint4*>(p));
+  return v;
+}
+
+// RS row sets of 16 rows of w per warp (for SWIGLU: RS/2 gate sets then RS/2 up sets), NT tiles of 8 tokens,
+// U blocks of 32 k loaded before their products are issued.
+template <int RS, int NT, int U, int MODE>
+__global__ void __launch_bounds__(kWarps * 32)
+skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, const void* __restrict__ bias,
+                   void* __restrict__ out, int ldo, int m, int n, int k, int up_offset) {
+  constexpr int SETS = MODE == SWIGLU ? RS / 2 : RS;       // row sets that become distinct output columns
+  extern __shared__ float reduce[];                        // [warps][RS][16][NT * 8]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int quad = lane & 3, group = lane >> 2;
+  const int n0 = blockIdx.x * 16 * SETS;
+
+  const bf16* w_lo[RS];
+  const bf16* w_hi[RS];
+  bool ok_lo[RS], ok_hi[RS];
+#pragma unroll
+  for (int rs = 0; rs < RS; ++rs) {
+    const int set = MODE == SWIGLU ? rs % SETS : rs;
+    const int base = (MODE == SWIGLU && rs >= SETS) ? up_offset : 0;
+    const int row = n0 + set * 16 + group;
+    ok_lo[rs] = row < n;
+    ok_hi[rs] = row + 8 < n;
+    w_lo[rs] = w + (size_t)(base + row) * k + quad * 8;
+    w_hi[rs] = w + (size_t)(base + row + 8) * k + quad * 8;
+  }
+  const bf16* x_row[NT];
+  bool ok_x[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int token = nt * 8 + group;
+    ok_x[nt] = token < m;
+    x_row[nt] = x + (size_t)token * ldx + quad * 8;
+  }
+
+  float acc[RS][NT][4];
+#pragma unroll
+  for (int rs = 0; rs < RS; ++rs)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[rs][nt][0] = acc[rs][nt][1] = acc[rs][nt][2] = acc[rs][nt][3] = 0.0f;
+
+  const int blocks = (k + 31) / 32;
+  for (int block0 = warp; block0 < blocks; block0 += kWarps * U) {
+    uint4 a_lo[U][RS], a_hi[U][RS], b[U][NT];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int block = block0 + u * kWarps;
+      const int offset = block * 32;
+      const bool in_k = block < blocks && offset + quad * 8 + 8 <= k;
+#pragma unroll
+      for (int rs = 0; rs < RS; ++rs) {
+        a_lo[u][rs] = load_stream(w_lo[rs] + offset, in_k && ok_lo[rs]);
+        a_hi[u][rs] = load_stream(w_hi[rs] + offset, in_k && ok_hi[rs]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) b[u][nt] = load_cached(x_row[nt] + offset, in_k && ok_x[nt]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int rs = 0; rs < RS; ++rs)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          mma_bf16(acc[rs][nt], a_lo[u][rs].x, a_hi[u][rs].x, a_lo[u][rs].z, a_hi[u][rs].z, b[u][nt].x, b[u][nt].z);
+          mma_bf16(acc[rs][nt], a_lo[u][rs].y, a_hi[u][rs].y, a_lo[u][rs].w, a_hi[u][rs].w, b[u][nt].y, b[u][nt].w);
+        }
+  }
+
+  // partial sums of the 8 warps -> shared memory
+  constexpr int TOKENS = NT * 8;
+  float* mine = reduce + (size_t)warp * RS * 16 * TOKENS;
+#pragma unroll
+  for (int rs = 0; rs < RS; ++rs)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int token = nt * 8 + quad * 2;
+      float* base = mine + (size_t)rs * 16 * TOKENS;
+      base[group * TOKENS + token] = acc[rs][nt][0];
+      base[group * TOKENS + token + 1] = acc[rs][nt][1];
+      base[(group + 8) * TOKENS + token] = acc[rs][nt][2];
+      base[(group + 8) * TOKENS + token + 1] = acc[rs][nt][3];
+    }
+  __syncthreads();
+  // outputs of the CTA: SETS * 16 columns x m tokens; consecutive threads take consecutive columns
+  const int columns = SETS * 16;
+  for (int index = threadIdx.x; index < columns * m; index += kWarps * 32) {
+    const int token = index / columns, local = index % columns;
+    const int column = n0 + local;
+    if (column >= n) continue;
+    const int set = local / 16, row = local % 16;
+    float value = 0.0f, other = 0.0f;
+#pragma unroll
+    for (int wp = 0; wp < kWarps; ++wp) {
+      const float* base = reduce + (size_t)wp * RS * 16 * TOKENS;
+      value += base[((size_t)set * 16 + row) * TOKENS + token];
+      if (MODE == SWIGLU) other += base[((size_t)(set + SETS) * 16 + row) * TOKENS + token];
+    }
+    if (MODE == SWIGLU) {
+      reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
+          __float2bfloat16_rn(value / (1.0f + expf(-value)) * other);
+    } else if (MODE == STORE) {
+      if (bias) value += __bfloat162float(reinterpret_cast<const bf16*>(bias)[column]);
+      reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(value);
+    } else {
+      if (bias) value += reinterpret_cast<const float*>(bias)[column];
+      float* dst = reinterpret_cast<float*>(out) + (size_t)token * ldo + column;
+      *dst = MODE == ACCUM ? *dst + value : value;
+    }
+  }
+}
+
+template <int RS, int NT, int U, int MODE>
+int launch(const bf16* x, int ldx, const bf16* w, const void* bias, void* out, int ldo, int m, int n, int k,
+           int up_offset, cudaStream_t stream) {
+  constexpr int SETS = MODE == SWIGLU ? RS / 2 : RS;
+  const size_t smem = (size_t)kWarps * RS * 16 * NT * 8 * sizeof(float);
+  static bool configured = false;
+  if (smem > 48 * 1024 && !configured) {
+    const cudaError_t err = cudaFuncSetAttribute(skinny_gemm_kernel<RS, NT, U, MODE>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) {
+      mir_set_error("skinny_gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+      return MIR_CUDA_ERROR;
+    }
+    configured = true;
+  }
+  const int grid = (n + 16 * SETS - 1) / (16 * SETS);
+  skinny_gemm_kernel<RS, NT, U, MODE><<<grid, kWarps * 32, smem, stream>>>(x, ldx, w, bias, out, ldo, m, n, k,
+                                                                          up_offset);
+  return mir_check_launch("skinny_gemm");
+}
+
+template <int MODE>
+int dispatch(const bf16* x, int ldx, const bf16* w, const void* bias, void* out, int ldo, int m, int n, int k,
+             int up_offset, cudaStream_t stream) {
+  constexpr int P = MODE == SWIGLU ? 2 : 1;      // SWIGLU streams two row sets per output set
+  if (m <= 8) return launch<P, 1, 4, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
+  if (m <= 16) return launch<P, 2, 4, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
+  if (m <= 32) return launch<P, 4, 2, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
+  return launch<2, 8, 1, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
+}
+
+}  // namespace
+
+MIR_EXPORT int mir_skinny_gemm_max_rows() { return 64; }
+
+// mode: 0 out bf16 = x w^T (+bias bf16); 1 out float += x w^T (+bias float); 2 out float = x w^T (+bias float);
+// 3 out bf16 [m, n] = silu(x w[0:n]^T) * (x w[up_offset : up_offset + n]^T).
+// Needs m <= 64, k a multiple of 8, ldx a multiple of 8, and x and w on 16-byte boundaries.
+MIR_EXPORT int mir_gemm_skinny_bf16(int mode, const void* x, int ldx, const void* w, const void* bias, void* out,
+                                    int ldo, int m, int n, int k, int up_offset, cudaStream_t stream) {
+  if (m == 0 || n == 0) return MIR_OK;
+  if (m < 0 || m > 64 || n < 0 || k <= 0 || (k % 8) || (ldx % 8) || ldx < k || ldo < n ||
+      ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) {
+    mir_set_error("skinny_gemm: needs 1..64 rows, k and the row stride multiples of 8 and 16-byte aligned operands "
+                  "(m %d n %d k %d ldx %d ldo %d)", m, n, k, ldx, ldo);
+    return MIR_BAD_ARGUMENT;
+  }
+  const bf16* xx = (const bf16*)x;
+  const bf16* ww = (const bf16*)w;
+  switch (mode) {
+    case STORE: return dispatch<STORE>(xx, ldx, ww, bias, out, ldo, m, n, k, 0, stream);
+    case ACCUM: return dispatch<ACCUM>(xx, ldx, ww, bias, out, ldo, m, n, k, 0, stream);
+    case F32: return dispatch<F32>(xx, ldx, ww, bias, out, ldo, m, n, k, 0, stream);
+    case SWIGLU:
+      if (bias) { mir_set_error("skinny_gemm: the SwiGLU epilogue takes no bias"); return MIR_BAD_ARGUMENT; }
+      return dispatch<SWIGLU>(xx, ldx, ww, nullptr, out, ldo, m, n, k, up_offset, stream);
+  }
+  mir_set_error("skinny_gemm: unknown mode %d", mode);
+  return MIR_BAD_ARGUMENT;
+}

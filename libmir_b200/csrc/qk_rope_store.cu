@@ -21,8 +21,8 @@ __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict_
                                      int head_dim, int rotary_dim, float eps, int write_kv) {
   const int token = blockIdx.x;
   const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
-  const int warps = blockDim.x >> 5;
+  const int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int warps = gridDim.y * (blockDim.x >> 5);
   const int units = heads + 2 * kv_heads;
   const size_t row_width = (size_t)units * head_dim;
   T* row = qkv + (size_t)token * row_width;
@@ -83,14 +83,16 @@ MIR_EXPORT int mir_qk_rope_store(int bf16, void* qkv, const int* positions, cons
                   head_dim, rotary_dim);
     return MIR_BAD_ARGUMENT;
   }
+  // one warp per head (query, key or value) of a token: 4 warps per CTA, enough CTAs per token to cover them
   const int units = heads + 2 * kv_heads;
-  const int threads = units >= 8 ? 256 : 32 * units;
+  const int threads = 128;
+  const dim3 grid(tokens, (units + 3) / 4);
   if (bf16)
-    qk_rope_store_kernel<<<tokens, threads, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, q_norm,
+    qk_rope_store_kernel<<<grid, threads, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, q_norm,
                                                          k_norm, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,
                                                          heads, kv_heads, head_dim, rotary_dim, eps, write_kv);
   else
-    qk_rope_store_kernel<<<tokens, threads, 0, stream>>>((float*)qkv, positions, slot_mapping, inv_freq, q_norm, k_norm,
+    qk_rope_store_kernel<<<grid, threads, 0, stream>>>((float*)qkv, positions, slot_mapping, inv_freq, q_norm, k_norm,
                                                          (float*)k_pages, (float*)v_pages, heads, kv_heads, head_dim,
                                                          rotary_dim, eps, write_kv);
   return mir_check_launch("qk_rope_store");

@@ -46,6 +46,8 @@ _SIGNATURES = {
                                       c_longlong, c_void_p],
         "mir_prefill_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "mir_gemm_skinny_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                 c_int, c_void_p],
         "mir_gemm_bf16_lt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_void_p, c_size_t, c_void_p],
     },
@@ -341,10 +343,45 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optio
         add_bias(out, bias)
         bias = None
     lib = library("bf16")
+    if _skinny_ok(x, m, k) and (out.dtype == torch.float32 or not accumulate):
+        mode = SKINNY_STORE if out.dtype == torch.bfloat16 else (SKINNY_ACCUM if accumulate else SKINNY_F32)
+        _check(lib, lib.mir_gemm_skinny_bf16(mode, x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias),
+                                             out.data_ptr(), out.stride(0), m, n, k, 0, _stream()))
+        return
     workspace = _lt_workspace(x.device)
     _check(lib, lib.mir_gemm_bf16_lt(x.data_ptr(), x.stride(0), weight.data_ptr(), k, _ptr(bias), out.data_ptr(),
                                      out.stride(0), int(out.dtype == torch.float32), m, n, k, beta,
                                      workspace.data_ptr(), workspace.numel(), _stream()))
+
+
+SKINNY_MAX_ROWS = 64
+SKINNY_STORE, SKINNY_ACCUM, SKINNY_F32, SKINNY_SWIGLU = 0, 1, 2, 3
+
+
+def _skinny_ok(x: torch.Tensor, m: int, k: int) -> bool:
+    """Whether the few-rows kernel takes this product: up to 64 rows, 16-byte aligned rows of 8-element multiples."""
+    return (0 < m <= SKINNY_MAX_ROWS and k % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
+
+
+def gate_up_silu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -> None:
+    """out[M, I] = silu(x w_gate^T) * (x w_up^T) with w_gate_up = [w_gate; w_up] of shape [2 I, K].
+
+    Up to 64 bfloat16 rows: one kernel, the [M, 2 I] intermediate is never written.  Otherwise the product
+    (library or 32-bit kernel) followed by the SiLU-multiply kernel; `scratch_alloc(shape, dtype)` provides
+    the intermediate."""
+    _cuda(x, w_gate_up, out)
+    m, k = x.shape
+    inter = out.shape[1]
+    _require(w_gate_up.shape == (2 * inter, k) and out.shape[0] == m and out.is_contiguous()
+             and w_gate_up.is_contiguous() and x.stride(1) == 1, "gate_up_silu: shapes do not fit")
+    if x.dtype == torch.bfloat16 and _skinny_ok(x, m, k):
+        lib = library("bf16")
+        _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_SWIGLU, x.data_ptr(), x.stride(0), w_gate_up.data_ptr(), None,
+                                             out.data_ptr(), out.stride(0), m, inter, k, inter, _stream()))
+        return
+    gate_up = scratch_alloc((m, 2 * inter), x.dtype)
+    linear(x, w_gate_up, gate_up)
+    silu_mul(gate_up, out)
 
 
 # --------------------------------------------------------------------------- sampling

@@ -37,8 +37,6 @@ class SwiGlu(FeedForward):
     def forward(self, ctx, x, residual):
         s = self.spec
         tokens = x.shape[0]
-        gate_up = ctx.alloc((tokens, 2 * s.intermediate_size), self.env.dtype)
-        kernels.linear(x, self.w_gate_up, gate_up)
         hidden = ctx.alloc((tokens, s.intermediate_size), self.env.dtype)
-        kernels.silu_mul(gate_up, hidden)
+        kernels.gate_up_silu(x, self.w_gate_up, hidden, ctx.alloc)
         kernels.linear(hidden, self.w_down, residual, accumulate=True)

@@ -337,3 +337,42 @@ def test_repetition_penalty_rewrites_the_rows_logits():
     kernels.repetition_penalty(device, cuda(torch.tensor([3, 1, 2], dtype=torch.int32)),
                                cuda(torch.tensor([0, 0, 1], dtype=torch.int32)), cuda(torch.tensor([2.0, 1.5])))
     assert device.cpu().tolist() == [[2.0, -2.0, 0.5, 1.5], [1.0, 1.0, -3.0, 0.0]]
+
+
+@pytest.mark.parametrize("m", [1, 5, 8, 9, 16, 17, 32, 33, 64, 65])
+@pytest.mark.parametrize("n,k", [(136, 264), (50, 72), (2560, 1024)])
+def test_few_rows_products_and_their_epilogues(m, n, k):
+    """1 to 64 bf16 rows run the weight-streaming kernel (65 the library): store, accumulate into the 32-bit
+    residual, 32-bit output, bias, and a strided view as input."""
+    from libmir_b200 import kernels
+    torch.manual_seed(m * n + k)
+    x, w = torch.randn(m, k).bfloat16(), (torch.randn(n, k) * 0.3).bfloat16()
+    exact = plain_impl.linear(x.double(), w)
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(n).bfloat16()
+    kernels.linear(cuda(x), cuda(w), out, cuda(bias))
+    close(out, exact + bias.double(), torch.bfloat16, factor=2)
+    base = torch.randn(m, n)
+    residual = cuda(base.clone())
+    kernels.linear(cuda(x), cuda(w), residual, accumulate=True)
+    close(residual, base.double() + exact, torch.float32, factor=40)       # bf16 products, 32-bit sums
+    logits = torch.empty(m, n, device="cuda")
+    kernels.linear(cuda(x), cuda(w), logits)
+    close(logits, exact, torch.float32, factor=40)
+    wide = cuda(torch.randn(m, k + 40).bfloat16())
+    kernels.linear(wide[:, 16:16 + k], cuda(w), logits)
+    close(logits, plain_impl.linear(wide[:, 16:16 + k].double().cpu(), w), torch.float32, factor=40)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,inter,k", [(1, 333, 72), (8, 9728 // 8, 320), (40, 200, 136), (64, 176, 264), (70, 96, 64)])
+def test_gate_up_silu(dtype, m, inter, k):
+    from libmir_b200 import kernels
+    torch.manual_seed(m + inter)
+    x = torch.randn(m, k).to(dtype)
+    w = (torch.randn(2 * inter, k) * 0.2).to(dtype)
+    out = torch.empty(m, inter, device="cuda", dtype=dtype)
+    kernels.gate_up_silu(cuda(x), cuda(w), out, lambda shape, dt: torch.empty(shape, device="cuda", dtype=dt))
+    gate = plain_impl.linear(x.double(), w[:inter])
+    up = plain_impl.linear(x.double(), w[inter:])
+    close(out, plain_impl.silu(gate) * up, dtype, factor=2)
