@@ -96,6 +96,23 @@ __device__ __forceinline__ void load_tile(bf16* k_dst, bf16* v_dst, const bf16* 
   for (int j = 0; j < HALF / 8; ++j) cp_async16(v_smem + j * 16, v_src + j * 8, valid);
 }
 
+// The same for one row whose place in the pools is already known (offset in elements, half a row per thread).
+template <int D>
+__device__ __forceinline__ void load_row_at(bf16* k_dst, bf16* v_dst, const bf16* __restrict__ k_pages,
+                                            const bf16* __restrict__ v_pages, size_t offset, bool valid, int thread) {
+  constexpr int STRIDE = D + 8;
+  constexpr int HALF = D / 2;
+  const int r = thread >> 1, half = thread & 1;
+  const bf16* k_src = k_pages + (valid ? offset : 0);
+  const bf16* v_src = v_pages + (valid ? offset : 0);
+  const uint32_t k_smem = smem_u32(k_dst + r * STRIDE + half * HALF);
+  const uint32_t v_smem = smem_u32(v_dst + r * STRIDE + half * HALF);
+#pragma unroll
+  for (int j = 0; j < HALF / 8; ++j) cp_async16(k_smem + j * 16, k_src + j * 8, valid);
+#pragma unroll
+  for (int j = 0; j < HALF / 8; ++j) cp_async16(v_smem + j * 16, v_src + j * 8, valid);
+}
+
 // S[16 x NT*8 keys] += Q[16 x D] . K^T for NT n-tiles of 8 keys (NT even).
 template <int D, int NT>
 __device__ __forceinline__ void scores(float (&s)[NT][4], const uint32_t (&qa)[D / 16][4], const bf16* k_tile,
@@ -184,6 +201,9 @@ __device__ __forceinline__ void softmax(float (&s)[NT][4], float (&m)[2], float 
 // ------------------------------------------------------------------------------------------------ decode
 constexpr int kDecodeWarps = 4;
 constexpr int kDecodeTile = 16;
+constexpr int kDecodeStages = 3;
+constexpr int kDecodeMaxPartition = 512;
+constexpr int kDecodeMaxTiles = kDecodeMaxPartition / (kDecodeWarps * kDecodeTile);   // tiles per warp
 
 template <int D>
 __global__ void __launch_bounds__(kDecodeWarps * 32)
@@ -212,8 +232,27 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
   if (begin >= part_end) return;                              // the merge skips this partition the same way
 
   // this warp's buffers: [stage][K | V][16 rows][STRIDE]
-  bf16* stage_base = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * 2 * 2 * TILE_ELEMS;
+  bf16* stage_base = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * kDecodeStages * 2 * TILE_ELEMS;
   const int* table = block_table + (size_t)row * table_width;
+
+  // Where this lane's row of each of the warp's tiles lies in the pools.  All the block-table reads are
+  // issued here, together, so that no tile's copy waits for a table read of its own.
+  const int stride_keys = kDecodeWarps * kDecodeTile;
+  const int my_begin = begin + warp * kDecodeTile;
+  const int my_tiles = my_begin < part_end ? (part_end - my_begin + stride_keys - 1) / stride_keys : 0;
+  size_t place[kDecodeMaxTiles];
+  bool present[kDecodeMaxTiles];
+#pragma unroll
+  for (int j = 0; j < kDecodeMaxTiles; ++j) {
+    const int key = my_begin + j * stride_keys + (lane >> 1);
+    present[j] = j < my_tiles && key < part_end;
+    place[j] = 0;
+    if (present[j]) {
+      const int block = key / page_size;
+      const int page = table[block];
+      place[j] = (((size_t)page * page_size + (key - block * page_size)) * kv_heads + kv_head) * D + (lane & 1) * (D / 2);
+    }
+  }
 
   // Q fragments of the 16 (padded) heads of the group
   uint32_t qa[D / 16][4];
@@ -235,24 +274,29 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
   for (int nt = 0; nt < D / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
 
-  const int stride_keys = kDecodeWarps * kDecodeTile;
-  int tile = begin + warp * kDecodeTile;
-  if (tile < part_end)
-    load_tile<D, kDecodeTile>(stage_base, stage_base + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads,
-                              kv_head, tile, part_end, lane);
-  cp_async_commit();
-  int stage = 0;
-  for (; tile < part_end; tile += stride_keys, stage ^= 1) {
-    const int next = tile + stride_keys;
-    if (next < part_end) {
-      bf16* dst = stage_base + (stage ^ 1) * 2 * TILE_ELEMS;
-      load_tile<D, kDecodeTile>(dst, dst + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head, next,
-                                part_end, lane);
+  // prologue: the first kDecodeStages - 1 tiles are on their way before any is used
+#pragma unroll
+  for (int j = 0; j < kDecodeStages - 1; ++j) {
+    if (j < my_tiles) {
+      bf16* dst = stage_base + j * 2 * TILE_ELEMS;
+      load_row_at<D>(dst, dst + TILE_ELEMS, k_pages, v_pages, place[j], present[j], lane);
     }
     cp_async_commit();
-    cp_async_wait<1>();
+  }
+#pragma unroll
+  for (int j = 0; j < kDecodeMaxTiles; ++j) {
+    if (j >= my_tiles) break;
+    constexpr int kAhead = kDecodeStages - 1;
+    if (j + kAhead < kDecodeMaxTiles && j + kAhead < my_tiles) {
+      bf16* dst = stage_base + ((j + kAhead) % kDecodeStages) * 2 * TILE_ELEMS;
+      load_row_at<D>(dst, dst + TILE_ELEMS, k_pages, v_pages, place[(j + kAhead) % kDecodeMaxTiles],
+                     present[(j + kAhead) % kDecodeMaxTiles], lane);
+    }
+    cp_async_commit();
+    cp_async_wait<kDecodeStages - 1>();
     __syncwarp();
-    const bf16* k_tile = stage_base + stage * 2 * TILE_ELEMS;
+    const int tile = my_begin + j * stride_keys;
+    const bf16* k_tile = stage_base + (j % kDecodeStages) * 2 * TILE_ELEMS;
     const bf16* v_tile = k_tile + TILE_ELEMS;
     float s[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
     scores<D, 2>(s, qa, k_tile, lane);
@@ -493,7 +537,7 @@ int launch_decode(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages
                   const int* block_table, int table_width, const int* positions, int rows, int page_size, int heads,
                   int kv_heads, float scale, int window, int partition, int num_partitions, float* partial_o,
                   float* partial_ml, cudaStream_t stream) {
-  const size_t pipeline = (size_t)kDecodeWarps * 2 * 2 * kDecodeTile * (D + 8) * sizeof(bf16);
+  const size_t pipeline = (size_t)kDecodeWarps * kDecodeStages * 2 * kDecodeTile * (D + 8) * sizeof(bf16);
   const size_t combine = (size_t)kDecodeWarps * 16 * (D + 2) * sizeof(float);
   const size_t smem = pipeline > combine ? pipeline : combine;
   int status = set_smem(decode_attention_kernel<D>, smem, "decode_attention");
@@ -554,7 +598,8 @@ MIR_EXPORT int mir_decode_attention_bf16(const void* q, long long q_stride, void
                                          float* scratch, long long scratch_floats, cudaStream_t stream) {
   if (rows == 0) return MIR_OK;
   if (bad_common("decode_attention", heads, kv_heads, head_dim, page_size, table_width, window)) return MIR_BAD_ARGUMENT;
-  if (rows < 0 || rows > 65535 || partition <= 0 || partition % 64 || num_partitions <= 0) {
+  if (rows < 0 || rows > 65535 || partition <= 0 || partition % 64 || partition > kDecodeMaxPartition ||
+      num_partitions <= 0) {
     mir_set_error("decode_attention: bad rows %d, partition %d or partition count %d", rows, partition, num_partitions);
     return MIR_BAD_ARGUMENT;
   }

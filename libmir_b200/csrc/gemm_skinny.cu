@@ -1,11 +1,14 @@
-// Matrix products with few rows (1 to 64 tokens) in bf16: the decode step's projections.
+// Matrix products with few rows (1 to 16 tokens) in bf16: the decode step's projections.
 //
 //   out[M, N] = epilogue(x[M, K] . w[N, K]^T)
 // With so few tokens the product is a stream of the weights: the work is to read w once at the speed of
 // HBM.  The roles are swapped for the tensor cores: 16 rows of w are the M side of mma.m16n8k16 and 8
 // tokens are the N side.  A CTA owns a strip of rows of w; its 8 warps split K between them (every warp
 // takes every 8th block of 32 k), each lane reading 16 bytes of a row at a time, and the 8 partial
-// sums are added in shared memory in warp order, so the result is deterministic and needs no atomics.
+// sums are added in shared memory in warp order.  When a matrix has too few rows to fill the GPU that
+// way, K is also split over the CTAs of a thread-block cluster, whose leader adds the partial sums of
+// its peers, in rank order, straight out of their shared memory (distributed shared memory).  The
+// result is deterministic and needs neither atomics nor scratch in global memory.
 //
 // No data is rearranged for the fragments: inside one mma the order of k does not matter as long as
 // both operands use the same order, so a lane keeps the 8 consecutive k it loaded from a row of w and
@@ -21,7 +24,10 @@
 // libmir plans a GEMV only for one token (DenseVectorPlan, cuda/src/backend/linear/autotune/
 // candidate.rs:92-98) and otherwise a library GEMM followed by separate add / gate kernels
 // (cuda/kernels/elementwise_bf16.cu:3-11,42-70).
+#include <cooperative_groups.h>
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 using namespace mir;
 typedef __nv_bfloat16 bf16;
@@ -57,7 +63,12 @@ __global__ void __launch_bounds__(kWarps * 32)
 skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, const void* __restrict__ bias,
                    void* __restrict__ out, int ldo, int m, int n, int k, int up_offset) {
   constexpr int SETS = MODE == SWIGLU ? RS / 2 : RS;       // row sets that become distinct output columns
-  extern __shared__ float reduce[];                        // [warps][RS][16][NT * 8]
+  constexpr int TOKENS = NT * 8;
+  constexpr int PARTIAL = RS * 16 * TOKENS;                // floats of one CTA's partial result
+  extern __shared__ float shared[];                        // [warps][PARTIAL] then [PARTIAL] (the CTA's sum)
+  float* cta_sum = shared + kWarps * PARTIAL;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int splits = gridDim.y, split = blockIdx.y;        // the cluster spans gridDim.y: K is cut into `splits`
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int quad = lane & 3, group = lane >> 2;
   const int n0 = blockIdx.x * 16 * SETS;
@@ -91,13 +102,15 @@ skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
     for (int nt = 0; nt < NT; ++nt) acc[rs][nt][0] = acc[rs][nt][1] = acc[rs][nt][2] = acc[rs][nt][3] = 0.0f;
 
   const int blocks = (k + 31) / 32;
-  for (int block0 = warp; block0 < blocks; block0 += kWarps * U) {
+  const int per_split = (blocks + splits - 1) / splits;
+  const int block_begin = split * per_split, block_end = min(blocks, block_begin + per_split);
+  for (int block0 = block_begin + warp; block0 < block_end; block0 += kWarps * U) {
     uint4 a_lo[U][RS], a_hi[U][RS], b[U][NT];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int block = block0 + u * kWarps;
       const int offset = block * 32;
-      const bool in_k = block < blocks && offset + quad * 8 + 8 <= k;
+      const bool in_k = block < block_end && offset + quad * 8 + 8 <= k;
 #pragma unroll
       for (int rs = 0; rs < RS; ++rs) {
         a_lo[u][rs] = load_stream(w_lo[rs] + offset, in_k && ok_lo[rs]);
@@ -117,9 +130,8 @@ skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
         }
   }
 
-  // partial sums of the 8 warps -> shared memory
-  constexpr int TOKENS = NT * 8;
-  float* mine = reduce + (size_t)warp * RS * 16 * TOKENS;
+  // partial sums of the 8 warps -> shared memory -> one sum per CTA
+  float* mine = shared + (size_t)warp * PARTIAL;
 #pragma unroll
   for (int rs = 0; rs < RS; ++rs)
 #pragma unroll
@@ -132,78 +144,100 @@ skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
       base[(group + 8) * TOKENS + token + 1] = acc[rs][nt][3];
     }
   __syncthreads();
-  // outputs of the CTA: SETS * 16 columns x m tokens; consecutive threads take consecutive columns
-  const int columns = SETS * 16;
-  for (int index = threadIdx.x; index < columns * m; index += kWarps * 32) {
-    const int token = index / columns, local = index % columns;
-    const int column = n0 + local;
-    if (column >= n) continue;
-    const int set = local / 16, row = local % 16;
-    float value = 0.0f, other = 0.0f;
+  for (int index = threadIdx.x; index < PARTIAL; index += kWarps * 32) {
+    float total = 0.0f;
 #pragma unroll
-    for (int wp = 0; wp < kWarps; ++wp) {
-      const float* base = reduce + (size_t)wp * RS * 16 * TOKENS;
-      value += base[((size_t)set * 16 + row) * TOKENS + token];
-      if (MODE == SWIGLU) other += base[((size_t)(set + SETS) * 16 + row) * TOKENS + token];
-    }
-    if (MODE == SWIGLU) {
-      reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
-          __float2bfloat16_rn(value / (1.0f + expf(-value)) * other);
-    } else if (MODE == STORE) {
-      if (bias) value += __bfloat162float(reinterpret_cast<const bf16*>(bias)[column]);
-      reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(value);
-    } else {
-      if (bias) value += reinterpret_cast<const float*>(bias)[column];
-      float* dst = reinterpret_cast<float*>(out) + (size_t)token * ldo + column;
-      *dst = MODE == ACCUM ? *dst + value : value;
+    for (int wp = 0; wp < kWarps; ++wp) total += shared[(size_t)wp * PARTIAL + index];
+    cta_sum[index] = total;
+  }
+  cluster.sync();                                          // every CTA's sum is in its shared memory
+  if (split == 0) {
+    // outputs of the cluster: SETS * 16 columns x m tokens; consecutive threads take consecutive columns
+    const int columns = SETS * 16;
+    for (int index = threadIdx.x; index < columns * m; index += kWarps * 32) {
+      const int token = index / columns, local = index % columns;
+      const int column = n0 + local;
+      if (column >= n) continue;
+      const int set = local / 16, row = local % 16;
+      const int at = (set * 16 + row) * TOKENS + token;
+      float value = 0.0f, other = 0.0f;
+      for (int rank = 0; rank < splits; ++rank) {
+        const float* peer = cluster.map_shared_rank(cta_sum, rank);
+        value += peer[at];
+        if (MODE == SWIGLU) other += peer[at + SETS * 16 * TOKENS];
+      }
+      if (MODE == SWIGLU) {
+        reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
+            __float2bfloat16_rn(value / (1.0f + expf(-value)) * other);
+      } else if (MODE == STORE) {
+        if (bias) value += __bfloat162float(reinterpret_cast<const bf16*>(bias)[column]);
+        reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(value);
+      } else {
+        if (bias) value += reinterpret_cast<const float*>(bias)[column];
+        float* dst = reinterpret_cast<float*>(out) + (size_t)token * ldo + column;
+        *dst = MODE == ACCUM ? *dst + value : value;
+      }
     }
   }
+  cluster.sync();                                          // peers keep their shared memory until it was read
 }
+
+constexpr int kTargetCtas = 4 * 148;
 
 template <int RS, int NT, int U, int MODE>
 int launch(const bf16* x, int ldx, const bf16* w, const void* bias, void* out, int ldo, int m, int n, int k,
            int up_offset, cudaStream_t stream) {
   constexpr int SETS = MODE == SWIGLU ? RS / 2 : RS;
-  const size_t smem = (size_t)kWarps * RS * 16 * NT * 8 * sizeof(float);
-  static bool configured = false;
-  if (smem > 48 * 1024 && !configured) {
-    const cudaError_t err = cudaFuncSetAttribute(skinny_gemm_kernel<RS, NT, U, MODE>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) {
-      mir_set_error("skinny_gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
-      return MIR_CUDA_ERROR;
-    }
-    configured = true;
+  const size_t smem = (size_t)(kWarps + 1) * RS * 16 * NT * 8 * sizeof(float);
+  const int tiles = (n + 16 * SETS - 1) / (16 * SETS);
+  const int blocks = (k + 31) / 32;
+  int splits = 1;                                          // cut K over a cluster until the GPU is full
+  while (splits < 8 && tiles * splits < kTargetCtas && blocks / (splits * 2 * kWarps) >= 2) splits *= 2;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(tiles, splits, 1);
+  config.blockDim = dim3(kWarps * 32, 1, 1);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = 1;
+  attribute[0].val.clusterDim.y = splits;
+  attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  const cudaError_t err = cudaLaunchKernelEx(&config, skinny_gemm_kernel<RS, NT, U, MODE>, x, ldx, w, bias, out, ldo,
+                                             m, n, k, up_offset);
+  if (err != cudaSuccess) {
+    mir_set_error("skinny_gemm: launch failed: %s", cudaGetErrorString(err));
+    return MIR_CUDA_ERROR;
   }
-  const int grid = (n + 16 * SETS - 1) / (16 * SETS);
-  skinny_gemm_kernel<RS, NT, U, MODE><<<grid, kWarps * 32, smem, stream>>>(x, ldx, w, bias, out, ldo, m, n, k,
-                                                                          up_offset);
   return mir_check_launch("skinny_gemm");
 }
 
 template <int MODE>
 int dispatch(const bf16* x, int ldx, const bf16* w, const void* bias, void* out, int ldo, int m, int n, int k,
              int up_offset, cudaStream_t stream) {
-  constexpr int P = MODE == SWIGLU ? 2 : 1;      // SWIGLU streams two row sets per output set
-  if (m <= 8) return launch<P, 1, 4, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
-  if (m <= 16) return launch<P, 2, 4, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
-  if (m <= 32) return launch<P, 4, 2, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
-  return launch<2, 8, 1, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
+  if (MODE == SWIGLU) {                          // two row sets (gate, up) per output set
+    if (m <= 8) return launch<2, 1, 4, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
+    return launch<2, 2, 4, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
+  }
+  if (m <= 8) return launch<1, 1, 8, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
+  return launch<1, 2, 8, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
 }
 
 }  // namespace
 
-MIR_EXPORT int mir_skinny_gemm_max_rows() { return 64; }
+MIR_EXPORT int mir_skinny_gemm_max_rows() { return 16; }
 
 // mode: 0 out bf16 = x w^T (+bias bf16); 1 out float += x w^T (+bias float); 2 out float = x w^T (+bias float);
 // 3 out bf16 [m, n] = silu(x w[0:n]^T) * (x w[up_offset : up_offset + n]^T).
-// Needs m <= 64, k a multiple of 8, ldx a multiple of 8, and x and w on 16-byte boundaries.
+// Needs m <= 16, k a multiple of 8, ldx a multiple of 8, and x and w on 16-byte boundaries.
 MIR_EXPORT int mir_gemm_skinny_bf16(int mode, const void* x, int ldx, const void* w, const void* bias, void* out,
                                     int ldo, int m, int n, int k, int up_offset, cudaStream_t stream) {
   if (m == 0 || n == 0) return MIR_OK;
-  if (m < 0 || m > 64 || n < 0 || k <= 0 || (k % 8) || (ldx % 8) || ldx < k || ldo < n ||
+  if (m < 0 || m > 16 || n < 0 || k <= 0 || (k % 8) || (ldx % 8) || ldx < k || ldo < n ||
       ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) {
-    mir_set_error("skinny_gemm: needs 1..64 rows, k and the row stride multiples of 8 and 16-byte aligned operands "
+    mir_set_error("skinny_gemm: needs 1..16 rows, k and the row stride multiples of 8 and 16-byte aligned operands "
                   "(m %d n %d k %d ldx %d ldo %d)", m, n, k, ldx, ldo);
     return MIR_BAD_ARGUMENT;
   }

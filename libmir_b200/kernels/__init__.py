@@ -354,19 +354,19 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optio
                                      workspace.data_ptr(), workspace.numel(), _stream()))
 
 
-SKINNY_MAX_ROWS = 64
+SKINNY_MAX_ROWS = 16
 SKINNY_STORE, SKINNY_ACCUM, SKINNY_F32, SKINNY_SWIGLU = 0, 1, 2, 3
 
 
 def _skinny_ok(x: torch.Tensor, m: int, k: int) -> bool:
-    """Whether the few-rows kernel takes this product: up to 64 rows, 16-byte aligned rows of 8-element multiples."""
+    """Whether the few-rows kernel takes this product: up to 16 rows, 16-byte aligned rows of 8-element multiples."""
     return (0 < m <= SKINNY_MAX_ROWS and k % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
 
 
 def gate_up_silu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -> None:
     """out[M, I] = silu(x w_gate^T) * (x w_up^T) with w_gate_up = [w_gate; w_up] of shape [2 I, K].
 
-    Up to 64 bfloat16 rows: one kernel, the [M, 2 I] intermediate is never written.  Otherwise the product
+    Up to 16 bfloat16 rows: one kernel, the [M, 2 I] intermediate is never written.  Otherwise the product
     (library or 32-bit kernel) followed by the SiLU-multiply kernel; `scratch_alloc(shape, dtype)` provides
     the intermediate."""
     _cuda(x, w_gate_up, out)
