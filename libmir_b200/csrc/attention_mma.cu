@@ -66,51 +66,55 @@ __device__ __forceinline__ float quad_sum(float v) {
 }
 
 // Copy ROWS consecutive keys and their values (one kv head, head_dim bf16 each) from the pages into padded
-// shared-memory rows.  Row i holds key `first_key + i`; rows whose key is >= limit are zero-filled.  Two
-// threads share a row (half a row each), so a thread looks its page up ONCE and then issues head_dim / 16
-// 16-byte copies for the key and as many for the value, which lie at the same slot of their pools.
-template <int D, int ROWS>
+// shared-memory rows with THREADS threads.  Row i holds key `first_key + i`; rows whose key is >= limit
+// are zero-filled.  One instruction of a warp copies whole rows: head_dim / 8 consecutive lanes take the
+// consecutive 16-byte pieces of a row, so every 32-byte sector that is requested is used in full (a lane
+// that walked along its own row would ask for each sector twice, once per half).  The rows of one
+// instruction are GROUP consecutive keys; when the page size is a multiple of GROUP they lie in one page
+// and the block table is read once for all of them (the same address for every lane).
+template <int D, int ROWS, int THREADS>
 __device__ __forceinline__ void load_tile(bf16* k_dst, bf16* v_dst, const bf16* __restrict__ k_pages,
                                           const bf16* __restrict__ v_pages, const int* __restrict__ table,
                                           int page_size, int kv_heads, int kv_head, int first_key, int limit,
                                           int thread) {
   constexpr int STRIDE = D + 8;
-  constexpr int HALF = D / 2;            // elements per thread
-  const int r = thread >> 1, half = thread & 1;
-  if (r >= ROWS) return;
-  const int key = first_key + r;
-  const bool valid = key < limit;
-  size_t offset = 0;
-  if (valid) {
-    const int block = key / page_size;
-    const int page = table[block];
-    offset = (((size_t)page * page_size + (key - block * page_size)) * kv_heads + kv_head) * D + half * HALF;
+  constexpr int CHUNKS = D / 8;                    // 16-byte pieces per row
+  constexpr int GROUP = THREADS / CHUNKS;          // rows per instruction
+  static_assert(ROWS % GROUP == 0, "tile rows must be a multiple of the rows one instruction copies");
+  const int sub = thread / CHUNKS, piece = thread % CHUNKS;
+  if (page_size % ROWS == 0 && first_key % ROWS == 0) {
+    // the whole tile lies in one page: one table read, then constant strides
+    const int block = first_key / page_size;
+    const int page = first_key < limit ? table[block] : 0;
+    const size_t row_stride = (size_t)kv_heads * D;
+    const size_t base = ((size_t)page * page_size + (first_key - block * page_size)) * row_stride + (size_t)kv_head * D +
+                        piece * 8;
+#pragma unroll
+    for (int i = 0; i < ROWS / GROUP; ++i) {
+      const int r = i * GROUP + sub;
+      const bool valid = first_key + r < limit;
+      const size_t offset = valid ? base + r * row_stride : 0;
+      cp_async16(smem_u32(k_dst + r * STRIDE + piece * 8), k_pages + offset, valid);
+      cp_async16(smem_u32(v_dst + r * STRIDE + piece * 8), v_pages + offset, valid);
+    }
+    return;
   }
-  const bf16* k_src = k_pages + offset;
-  const bf16* v_src = v_pages + offset;
-  const uint32_t k_smem = smem_u32(k_dst + r * STRIDE + half * HALF);
-  const uint32_t v_smem = smem_u32(v_dst + r * STRIDE + half * HALF);
+  const bool one_page = page_size % GROUP == 0 && first_key % GROUP == 0;
 #pragma unroll
-  for (int j = 0; j < HALF / 8; ++j) cp_async16(k_smem + j * 16, k_src + j * 8, valid);
-#pragma unroll
-  for (int j = 0; j < HALF / 8; ++j) cp_async16(v_smem + j * 16, v_src + j * 8, valid);
-}
-
-// The same for one row whose place in the pools is already known (offset in elements, half a row per thread).
-template <int D>
-__device__ __forceinline__ void load_row_at(bf16* k_dst, bf16* v_dst, const bf16* __restrict__ k_pages,
-                                            const bf16* __restrict__ v_pages, size_t offset, bool valid, int thread) {
-  constexpr int STRIDE = D + 8;
-  constexpr int HALF = D / 2;
-  const int r = thread >> 1, half = thread & 1;
-  const bf16* k_src = k_pages + (valid ? offset : 0);
-  const bf16* v_src = v_pages + (valid ? offset : 0);
-  const uint32_t k_smem = smem_u32(k_dst + r * STRIDE + half * HALF);
-  const uint32_t v_smem = smem_u32(v_dst + r * STRIDE + half * HALF);
-#pragma unroll
-  for (int j = 0; j < HALF / 8; ++j) cp_async16(k_smem + j * 16, k_src + j * 8, valid);
-#pragma unroll
-  for (int j = 0; j < HALF / 8; ++j) cp_async16(v_smem + j * 16, v_src + j * 8, valid);
+  for (int i = 0; i < ROWS / GROUP; ++i) {
+    const int r = i * GROUP + sub;
+    const int key = first_key + r;
+    const bool valid = key < limit;
+    size_t offset = 0;
+    if (valid) {
+      const int lookup_key = one_page ? first_key + i * GROUP : key;
+      const int block = lookup_key / page_size;
+      const int page = table[block];
+      offset = (((size_t)page * page_size + (key - block * page_size)) * kv_heads + kv_head) * D + piece * 8;
+    }
+    cp_async16(smem_u32(k_dst + r * STRIDE + piece * 8), k_pages + offset, valid);
+    cp_async16(smem_u32(v_dst + r * STRIDE + piece * 8), v_pages + offset, valid);
+  }
 }
 
 // S[16 x NT*8 keys] += Q[16 x D] . K^T for NT n-tiles of 8 keys (NT even).
@@ -201,10 +205,15 @@ __device__ __forceinline__ void softmax(float (&s)[NT][4], float (&m)[2], float 
 // ------------------------------------------------------------------------------------------------ decode
 constexpr int kDecodeWarps = 4;
 constexpr int kDecodeTile = 16;
-constexpr int kDecodeStages = 3;
+constexpr int kDecodeStages = 2;
+constexpr int kDecodeHeads = 8;                 // query heads one CTA serves (rows 8..15 of the tile are padding)
 constexpr int kDecodeMaxPartition = 512;
 constexpr int kDecodeMaxTiles = kDecodeMaxPartition / (kDecodeWarps * kDecodeTile);   // tiles per warp
 
+// One CTA: one request, one kv head (up to 8 of its query heads), one partition of the keys.
+// Per 16-key tile a warp computes S = Q K^T (heads on the M side, 8 real rows), the softmax update of its
+// 8 heads, and O^T += V^T P^T (head_dim on the M side, heads on the N side: the padding rows cost nothing
+// here, and P^T in the layout the product wants is exactly the layout S came out in).
 template <int D>
 __global__ void __launch_bounds__(kDecodeWarps * 32)
 decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* __restrict__ k_pages,
@@ -216,12 +225,13 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
   constexpr int TILE_ELEMS = kDecodeTile * STRIDE;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int quad = lane & 3, group_row = lane >> 2;
   const int part = blockIdx.x, row = blockIdx.z;
   const int group = heads / kv_heads;
-  const int group_tiles = (group + 15) / 16;
+  const int group_tiles = (group + kDecodeHeads - 1) / kDecodeHeads;
   const int kv_head = blockIdx.y / group_tiles;
-  const int head0 = kv_head * group + (blockIdx.y % group_tiles) * 16;
-  const int valid_rows = min(16, kv_head * group + group - head0);
+  const int head0 = kv_head * group + (blockIdx.y % group_tiles) * kDecodeHeads;
+  const int valid_rows = min(kDecodeHeads, kv_head * group + group - head0);
   const int position = positions[row];
   if (position < 0) return;                                   // padding row of a captured batch
   const int context = position + 1;
@@ -234,63 +244,49 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
   // this warp's buffers: [stage][K | V][16 rows][STRIDE]
   bf16* stage_base = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * kDecodeStages * 2 * TILE_ELEMS;
   const int* table = block_table + (size_t)row * table_width;
-
-  // Where this lane's row of each of the warp's tiles lies in the pools.  All the block-table reads are
-  // issued here, together, so that no tile's copy waits for a table read of its own.
   const int stride_keys = kDecodeWarps * kDecodeTile;
   const int my_begin = begin + warp * kDecodeTile;
   const int my_tiles = my_begin < part_end ? (part_end - my_begin + stride_keys - 1) / stride_keys : 0;
-  size_t place[kDecodeMaxTiles];
-  bool present[kDecodeMaxTiles];
-#pragma unroll
-  for (int j = 0; j < kDecodeMaxTiles; ++j) {
-    const int key = my_begin + j * stride_keys + (lane >> 1);
-    present[j] = j < my_tiles && key < part_end;
-    place[j] = 0;
-    if (present[j]) {
-      const int block = key / page_size;
-      const int page = table[block];
-      place[j] = (((size_t)page * page_size + (key - block * page_size)) * kv_heads + kv_head) * D + (lane & 1) * (D / 2);
-    }
-  }
 
-  // Q fragments of the 16 (padded) heads of the group
-  uint32_t qa[D / 16][4];
-  {
-    const int r0 = lane >> 2, r1 = r0 + 8, c = (lane & 3) * 2;
-    const bf16* q_row0 = q + (size_t)row * q_stride + (size_t)(head0 + r0) * D;
-    const bf16* q_row1 = q + (size_t)row * q_stride + (size_t)(head0 + r1) * D;
-#pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-      qa[ks][0] = r0 < valid_rows ? *reinterpret_cast<const uint32_t*>(q_row0 + ks * 16 + c) : 0u;
-      qa[ks][1] = r1 < valid_rows ? *reinterpret_cast<const uint32_t*>(q_row1 + ks * 16 + c) : 0u;
-      qa[ks][2] = r0 < valid_rows ? *reinterpret_cast<const uint32_t*>(q_row0 + ks * 16 + 8 + c) : 0u;
-      qa[ks][3] = r1 < valid_rows ? *reinterpret_cast<const uint32_t*>(q_row1 + ks * 16 + 8 + c) : 0u;
-    }
-  }
-
-  float o[D / 8][4];
-#pragma unroll
-  for (int nt = 0; nt < D / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-
-  // prologue: the first kDecodeStages - 1 tiles are on their way before any is used
+  // the first copies are on their way before anything else is done
 #pragma unroll
   for (int j = 0; j < kDecodeStages - 1; ++j) {
     if (j < my_tiles) {
       bf16* dst = stage_base + j * 2 * TILE_ELEMS;
-      load_row_at<D>(dst, dst + TILE_ELEMS, k_pages, v_pages, place[j], present[j], lane);
+      load_tile<D, kDecodeTile, 32>(dst, dst + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head,
+                                    my_begin + j * stride_keys, part_end, lane);
     }
     cp_async_commit();
   }
+
+  // Q fragments: rows 0..7 are the heads of the group, rows 8..15 are zero
+  uint32_t qa[D / 16][4];
+  {
+    const int c = quad * 2;
+    const bf16* q_row = q + (size_t)row * q_stride + (size_t)(head0 + group_row) * D;
+    const bool real = group_row < valid_rows;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qa[ks][0] = real ? *reinterpret_cast<const uint32_t*>(q_row + ks * 16 + c) : 0u;
+      qa[ks][1] = 0u;
+      qa[ks][2] = real ? *reinterpret_cast<const uint32_t*>(q_row + ks * 16 + 8 + c) : 0u;
+      qa[ks][3] = 0u;
+    }
+  }
+
+  float ot[D / 16][4];                                         // O^T: [d = mt*16 + lane/4 (+8)][head = quad*2 (+1)]
+#pragma unroll
+  for (int mt = 0; mt < D / 16; ++mt) ot[mt][0] = ot[mt][1] = ot[mt][2] = ot[mt][3] = 0.0f;
+  float m = -INFINITY, l = 0.0f;                               // of head lane/4 (l: this lane's share)
+
 #pragma unroll
   for (int j = 0; j < kDecodeMaxTiles; ++j) {
     if (j >= my_tiles) break;
     constexpr int kAhead = kDecodeStages - 1;
-    if (j + kAhead < kDecodeMaxTiles && j + kAhead < my_tiles) {
+    if (j + kAhead < my_tiles) {
       bf16* dst = stage_base + ((j + kAhead) % kDecodeStages) * 2 * TILE_ELEMS;
-      load_row_at<D>(dst, dst + TILE_ELEMS, k_pages, v_pages, place[(j + kAhead) % kDecodeMaxTiles],
-                     present[(j + kAhead) % kDecodeMaxTiles], lane);
+      load_tile<D, kDecodeTile, 32>(dst, dst + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head,
+                                    my_begin + (j + kAhead) * stride_keys, part_end, lane);
     }
     cp_async_commit();
     cp_async_wait<kDecodeStages - 1>();
@@ -300,42 +296,70 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
     const bf16* v_tile = k_tile + TILE_ELEMS;
     float s[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
     scores<D, 2>(s, qa, k_tile, lane);
+    float v00 = s[0][0] * scale_log2, v01 = s[0][1] * scale_log2, v10 = s[1][0] * scale_log2, v11 = s[1][1] * scale_log2;
+    if (tile + kDecodeTile > context || tile < first_key) {     // only the edge tiles need a mask
+      const int key = tile + quad * 2;
+      if (key < first_key || key > position) v00 = -INFINITY;
+      if (key + 1 < first_key || key + 1 > position) v01 = -INFINITY;
+      if (key + 8 < first_key || key + 8 > position) v10 = -INFINITY;
+      if (key + 9 < first_key || key + 9 > position) v11 = -INFINITY;
+    }
+    const float tile_max = quad_max(fmaxf(fmaxf(v00, v01), fmaxf(v10, v11)));
+    const float next = fmaxf(m, tile_max);
+    const float ref = next == -INFINITY ? 0.0f : next;
+    const float corr = exp2f(m - ref);
+    m = next;
+    v00 = exp2f(v00 - ref);
+    v01 = exp2f(v01 - ref);
+    v10 = exp2f(v10 - ref);
+    v11 = exp2f(v11 - ref);
+    l = l * corr + (v00 + v01 + v10 + v11);
+    if (__any_sync(0xffffffffu, corr != 1.0f)) {                // the maximum moved for some head: rescale O^T
+      const float corr_a = __shfl_sync(0xffffffffu, corr, quad * 8);        // head quad*2   lives in lanes 8*quad..
+      const float corr_b = __shfl_sync(0xffffffffu, corr, quad * 8 + 4);    // head quad*2+1
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = tile + nt * 8 + (lane & 3) * 2 + (e & 1);
-        s[nt][e] = (key >= first_key && key <= position) ? s[nt][e] * scale_log2 : -INFINITY;
+      for (int mt = 0; mt < D / 16; ++mt) {
+        ot[mt][0] *= corr_a;
+        ot[mt][1] *= corr_b;
+        ot[mt][2] *= corr_a;
+        ot[mt][3] *= corr_b;
       }
-    uint32_t pa[1][4];
-    softmax<D, 2>(s, m, l, o, pa);
-    values<D, 2>(o, pa, v_tile, lane);
+    }
+    const uint32_t pb0 = pack_bf16(v00, v01), pb1 = pack_bf16(v10, v11);   // P^T: keys 0..7 and 8..15 of the tile
+    {
+      const int mat = lane >> 3, rowin = lane & 7;
+      const bf16* base = v_tile + ((mat >> 1) * 8 + rowin) * STRIDE + (mat & 1) * 8;
+#pragma unroll
+      for (int mt = 0; mt < D / 16; ++mt) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, smem_u32(base + mt * 16));
+        mma_bf16(ot[mt], a, pb0, pb1);
+      }
+    }
     __syncwarp();
   }
   cp_async_wait<0>();
-  l[0] = quad_sum(l[0]);
-  l[1] = quad_sum(l[1]);
+  l = quad_sum(l);
   __syncthreads();                                            // every warp is done with its pipeline buffers
 
   // combine the 4 warps through shared memory
-  float* o_sm = reinterpret_cast<float*>(smem_raw);           // [warps][16][D]
-  float* m_sm = o_sm + kDecodeWarps * 16 * D;                 // [warps][16]
-  float* l_sm = m_sm + kDecodeWarps * 16;
+  float* o_sm = reinterpret_cast<float*>(smem_raw);           // [warps][8 heads][D]
+  float* m_sm = o_sm + kDecodeWarps * kDecodeHeads * D;       // [warps][8]
+  float* l_sm = m_sm + kDecodeWarps * kDecodeHeads;
   {
-    const int r0 = lane >> 2, r1 = r0 + 8, c = (lane & 3) * 2;
-    float* mine = o_sm + (size_t)warp * 16 * D;
+    float* mine = o_sm + (size_t)warp * kDecodeHeads * D;
+    const int head_a = quad * 2, head_b = head_a + 1;
 #pragma unroll
-    for (int nt = 0; nt < D / 8; ++nt) {
-      mine[r0 * D + nt * 8 + c] = o[nt][0];
-      mine[r0 * D + nt * 8 + c + 1] = o[nt][1];
-      mine[r1 * D + nt * 8 + c] = o[nt][2];
-      mine[r1 * D + nt * 8 + c + 1] = o[nt][3];
+    for (int mt = 0; mt < D / 16; ++mt) {
+      const int d = mt * 16 + group_row;
+      mine[head_a * D + d] = ot[mt][0];
+      mine[head_b * D + d] = ot[mt][1];
+      mine[head_a * D + d + 8] = ot[mt][2];
+      mine[head_b * D + d + 8] = ot[mt][3];
     }
-    if ((lane & 3) == 0) {
-      m_sm[warp * 16 + r0] = m[0];
-      m_sm[warp * 16 + r1] = m[1];
-      l_sm[warp * 16 + r0] = l[0];
-      l_sm[warp * 16 + r1] = l[1];
+    if (quad == 0) {
+      m_sm[warp * kDecodeHeads + group_row] = m;
+      l_sm[warp * kDecodeHeads + group_row] = l;
     }
   }
   __syncthreads();
@@ -343,14 +367,14 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
     const int r = index / D, d = index % D;
     float top = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kDecodeWarps; ++w) top = fmaxf(top, m_sm[w * 16 + r]);
+    for (int w = 0; w < kDecodeWarps; ++w) top = fmaxf(top, m_sm[w * kDecodeHeads + r]);
     float acc = 0.0f, denom = 0.0f;
     if (top != -INFINITY) {
 #pragma unroll
       for (int w = 0; w < kDecodeWarps; ++w) {
-        const float weight = exp2f(m_sm[w * 16 + r] - top);
-        acc += o_sm[((size_t)w * 16 + r) * D + d] * weight;
-        denom += l_sm[w * 16 + r] * weight;
+        const float weight = exp2f(m_sm[w * kDecodeHeads + r] - top);
+        acc += o_sm[((size_t)w * kDecodeHeads + r) * D + d] * weight;
+        denom += l_sm[w * kDecodeHeads + r] * weight;
       }
     }
     const size_t head = (size_t)row * heads + head0 + r;
@@ -463,7 +487,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
   const int warp_first = min(first_position + warp * 16, last_position);
   const int warp_first_key = (window > 0 && warp_first + 1 > window) ? warp_first + 1 - window : 0;
 
-  load_tile<D, kKeyTile>(buffers, buffers + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head,
+  load_tile<D, kKeyTile, kPrefillWarps * 32>(buffers, buffers + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head,
                          key_begin, key_end, threadIdx.x);
   cp_async_commit();
   int stage = 0;
@@ -471,7 +495,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
     const int next = key0 + kKeyTile;
     if (next < key_end) {
       bf16* dst = buffers + (stage ^ 1) * 2 * TILE_ELEMS;
-      load_tile<D, kKeyTile>(dst, dst + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head, next,
+      load_tile<D, kKeyTile, kPrefillWarps * 32>(dst, dst + TILE_ELEMS, k_pages, v_pages, table, page_size, kv_heads, kv_head, next,
                              key_end, threadIdx.x);
     }
     cp_async_commit();
@@ -518,17 +542,16 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
   }
 }
 
-// Opt in to more than 48 KB of dynamic shared memory, once per kernel.
+// Opt in to more than 48 KB of dynamic shared memory.  `done` is the caller's flag for this one kernel.
 template <typename Kernel>
-int set_smem(Kernel kernel, size_t bytes, const char* what) {
-  static bool done = false;          // one instance of this function, and of the flag, per kernel type
+int set_smem(Kernel kernel, size_t bytes, const char* what, bool& done) {
   if (bytes <= 48 * 1024 || done) return MIR_OK;
-  done = true;
   const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
   if (err != cudaSuccess) {
     mir_set_error("%s: cannot reserve %zu bytes of shared memory: %s", what, bytes, cudaGetErrorString(err));
     return MIR_CUDA_ERROR;
   }
+  done = true;
   return MIR_OK;
 }
 
@@ -538,12 +561,13 @@ int launch_decode(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages
                   int kv_heads, float scale, int window, int partition, int num_partitions, float* partial_o,
                   float* partial_ml, cudaStream_t stream) {
   const size_t pipeline = (size_t)kDecodeWarps * kDecodeStages * 2 * kDecodeTile * (D + 8) * sizeof(bf16);
-  const size_t combine = (size_t)kDecodeWarps * 16 * (D + 2) * sizeof(float);
+  const size_t combine = (size_t)kDecodeWarps * kDecodeHeads * (D + 2) * sizeof(float);
   const size_t smem = pipeline > combine ? pipeline : combine;
-  int status = set_smem(decode_attention_kernel<D>, smem, "decode_attention");
+  static bool smem_set = false;                               // per head size: this function is a template
+  int status = set_smem(decode_attention_kernel<D>, smem, "decode_attention", smem_set);
   if (status != MIR_OK) return status;
   const int group = heads / kv_heads;
-  const dim3 grid(num_partitions, kv_heads * ((group + 15) / 16), rows);
+  const dim3 grid(num_partitions, kv_heads * ((group + kDecodeHeads - 1) / kDecodeHeads), rows);
   decode_attention_kernel<D><<<grid, kDecodeWarps * 32, smem, stream>>>(
       q, q_stride, k_pages, v_pages, block_table, table_width, positions, page_size, heads, kv_heads,
       scale * 1.4426950408889634f, window, partition, num_partitions, partial_o, partial_ml, out);
@@ -560,7 +584,8 @@ int launch_prefill(const bf16* q, size_t q_stride, bf16* out, const bf16* k_page
                    int num_rows, int tokens, int page_size, int heads, int kv_heads, float scale, int window,
                    cudaStream_t stream) {
   const size_t smem = (size_t)2 * 2 * kKeyTile * (D + 8) * sizeof(bf16);
-  int status = set_smem(prefill_attention_kernel<D>, smem, "prefill_attention");
+  static bool smem_set = false;
+  int status = set_smem(prefill_attention_kernel<D>, smem, "prefill_attention", smem_set);
   if (status != MIR_OK) return status;
   const int tiles = (tokens + kQueryTile - 1) / kQueryTile + num_rows;   // an upper bound; spare CTAs return
   prefill_attention_kernel<D><<<dim3(tiles, heads), kPrefillWarps * 32, smem, stream>>>(
