@@ -170,3 +170,37 @@ def test_session_prefill_and_decode(tmp_path):
         assert out.next_token == plain_impl.greedy(reference[8]) and session.cache_stats()["cached_tokens"] == 9
     assert model.cache_stats()["live_requests"] == 0
     model.unload()
+
+
+def test_generate_command_line(tmp_path):
+    """bin/generate as a user runs it: a folder written by --write-random-model, then greedy tokens that match
+    the plain implementation, the `finish_reason=` line, and the batch form."""
+    import json
+    import subprocess
+    import sys
+    from helpers import ROOT
+    config_path = tmp_path / "tiny.json"
+    config_path.write_text(json.dumps(TINY_A))
+    folder = tmp_path / "model"
+    run = lambda *args: subprocess.run([sys.executable, str(ROOT / "bin" / "generate"), *args], capture_output=True,
+                                       text=True, timeout=300)
+    done = run("--random-weights", str(config_path), "--write-random-model", str(folder), "--dtype", "float32",
+               "--weights-seed", "5")
+    assert done.returncode == 0 and (folder / "model.safetensors").is_file(), done.stderr[-2000:]
+    done = run(str(folder), "--prompt-ids", "5,17,3,200,9", "--max-tokens", "6", "--dtype", "float32",
+               "--block-count", "32")
+    assert done.returncode == 0, done.stderr[-2000:]
+    lines = done.stdout.strip().splitlines()
+    assert lines[-1] == "finish_reason=length"
+    tokens = [int(t) for t in lines[0].split()]
+    plain_config, weights = plain_impl.read_model(folder)
+    sequence = [5, 17, 3, 200, 9]
+    for token in tokens:
+        assert token == plain_impl.greedy(plain_impl.forward(plain_config, weights, sequence)[-1].numpy())
+        sequence.append(token)
+    assert len(tokens) == 6
+    done = run(str(folder), "--prompt-ids", "5,17,3;9,9", "--max-tokens", "3", "--dtype", "float32", "--temperature",
+               "0.8", "--seed", "7", "--block-count", "32")
+    assert done.returncode == 0, done.stderr[-2000:]
+    records = [json.loads(line) for line in done.stdout.strip().splitlines()]
+    assert [r["request"] for r in records] == [0, 1] and all(len(r["token_ids"]) == 3 for r in records)
