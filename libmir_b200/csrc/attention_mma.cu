@@ -665,3 +665,70 @@ MIR_EXPORT int mir_prefill_attention_bf16(const void* q, long long q_stride, voi
                              block_table, table_width, query_starts, context_lens, num_rows, tokens, page_size, heads,
                              kv_heads, scale, window, stream);
 }
+
+// ------------------------------------------------------------------------------------------------
+// The variant for callers that cannot allocate (declared and explained in no_alloc.h): the partial
+// results live in an array that is part of this library's device image.
+#include <mutex>
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_static_decode_scratch[MIR_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_address[kMaxDevices] = {};      // device address of the array, per device, once known
+std::mutex g_static_scratch_mutex;
+
+// In host code the array's name only stands for the symbol; the address a kernel can use has to be asked
+// for, with the device that will run the kernel current.  Done once per device.
+int static_scratch_for_current_device(float** address) {
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess || device < 0 || device >= kMaxDevices) {
+    mir_set_error("decode_attention_static: cannot identify the current device: %s", cudaGetErrorString(err));
+    return MIR_CUDA_ERROR;
+  }
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_address[device] == nullptr) {
+    void* found = nullptr;
+    err = cudaGetSymbolAddress(&found, g_static_decode_scratch);
+    if (err != cudaSuccess || found == nullptr) {
+      mir_set_error("decode_attention_static: cudaGetSymbolAddress failed on device %d: %s", device,
+                    cudaGetErrorString(err));
+      return MIR_CUDA_ERROR;
+    }
+    g_static_scratch_address[device] = static_cast<float*>(found);
+  }
+  *address = g_static_scratch_address[device];
+  return MIR_OK;
+}
+}  // namespace
+
+MIR_EXPORT int mir_decode_attention_bf16_static(const void* q, long long q_stride, void* out, const void* k_pages,
+                                                const void* v_pages, const int* block_table, int table_width,
+                                                const int* positions, int rows, int page_size, int heads,
+                                                int kv_heads, int head_dim, float scale, int window, int partition,
+                                                int num_partitions, cudaStream_t stream) {
+  if (rows == 0) return MIR_OK;
+  if (rows < 0 || heads <= 0 || head_dim <= 0 || num_partitions <= 0) {
+    mir_set_error("decode_attention_static: bad rows %d, heads %d, head_dim %d or partition count %d", rows, heads,
+                  head_dim, num_partitions);
+    return MIR_BAD_ARGUMENT;
+  }
+  const long long need = mir_decode_attention_scratch_floats(rows, heads, head_dim, num_partitions);
+  if (need > (long long)MIR_STATIC_SCRATCH_FLOATS) {
+    mir_set_error("decode_attention_static: this call needs %lld floats of scratch (rows %d x heads %d x partitions "
+                  "%d x (head_dim %d + 2)), the built-in array holds %u; use fewer rows or partitions per call, or "
+                  "mir_decode_attention_bf16 with scratch of your own",
+                  need, rows, heads, num_partitions, head_dim, (unsigned)MIR_STATIC_SCRATCH_FLOATS);
+    return MIR_BAD_ARGUMENT;
+  }
+  float* scratch = nullptr;
+  if (need > 0) {
+    const int status = static_scratch_for_current_device(&scratch);
+    if (status != MIR_OK) return status;
+  }
+  return mir_decode_attention_bf16(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows,
+                                   page_size, heads, kv_heads, head_dim, scale, window, partition, num_partitions,
+                                   scratch, need, stream);
+}

@@ -37,6 +37,7 @@ LIBRARIES = {
     },
     "bf16": {
         "sources": ["runtime.cu", "gemm_lt.cu", "attention_mma.cu", "gemm_skinny.cu"],
+        "headers": ["no_alloc.h"],
         "link": ["-lcublasLt"],
     },
 }
