@@ -232,6 +232,8 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
   const int kv_head = blockIdx.y / group_tiles;
   const int head0 = kv_head * group + (blockIdx.y % group_tiles) * kDecodeHeads;
   const int valid_rows = min(kDecodeHeads, kv_head * group + group - head0);
+  grid_launch_dependents();
+  grid_dependency_wait();                                     // the newest key was written by the kernel before
   const int position = positions[row];
   if (position < 0) return;                                   // padding row of a captured batch
   const int context = position + 1;
@@ -395,6 +397,8 @@ __global__ void decode_merge_kernel(const float* __restrict__ partial_o, const f
                                     const int* __restrict__ positions, int heads, int window, int partition,
                                     int num_partitions, bf16* __restrict__ out) {
   const int head = blockIdx.x, row = blockIdx.y;
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int position = positions[row];
   const size_t index = (size_t)row * heads + head;
   if (position < 0) {
@@ -438,6 +442,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
   const int head = blockIdx.y;
   const int kv_head = head / (heads / kv_heads);
 
+  grid_launch_dependents();
+  grid_dependency_wait();
   // which request row and which 64-token tile of its portion this CTA has
   int row = -1, local_tile = 0;
   {
@@ -568,14 +574,13 @@ int launch_decode(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages
   if (status != MIR_OK) return status;
   const int group = heads / kv_heads;
   const dim3 grid(num_partitions, kv_heads * ((group + kDecodeHeads - 1) / kDecodeHeads), rows);
-  decode_attention_kernel<D><<<grid, kDecodeWarps * 32, smem, stream>>>(
-      q, q_stride, k_pages, v_pages, block_table, table_width, positions, page_size, heads, kv_heads,
-      scale * 1.4426950408889634f, window, partition, num_partitions, partial_o, partial_ml, out);
-  status = mir_check_launch("decode_attention");
+  status = mir_launch("decode_attention", decode_attention_kernel<D>, grid, dim3(kDecodeWarps * 32), smem, stream, 0,
+                      q, q_stride, k_pages, v_pages, block_table, table_width, positions, page_size, heads, kv_heads,
+                      scale * 1.4426950408889634f, window, partition, num_partitions, partial_o, partial_ml, out);
   if (status != MIR_OK || num_partitions == 1) return status;
-  decode_merge_kernel<D><<<dim3(heads, rows), D <= 64 ? 64 : 128, 0, stream>>>(partial_o, partial_ml, positions, heads,
-                                                                             window, partition, num_partitions, out);
-  return mir_check_launch("decode_merge");
+  return mir_launch("decode_merge", decode_merge_kernel<D>, dim3(heads, rows), dim3(D <= 64 ? 64 : 128), 0, stream, 0,
+                    (const float*)partial_o, (const float*)partial_ml, positions, heads, window, partition,
+                    num_partitions, out);
 }
 
 template <int D>
@@ -588,10 +593,9 @@ int launch_prefill(const bf16* q, size_t q_stride, bf16* out, const bf16* k_page
   int status = set_smem(prefill_attention_kernel<D>, smem, "prefill_attention", smem_set);
   if (status != MIR_OK) return status;
   const int tiles = (tokens + kQueryTile - 1) / kQueryTile + num_rows;   // an upper bound; spare CTAs return
-  prefill_attention_kernel<D><<<dim3(tiles, heads), kPrefillWarps * 32, smem, stream>>>(
-      q, q_stride, out, k_pages, v_pages, block_table, table_width, query_starts, context_lens, num_rows, page_size,
-      heads, kv_heads, scale * 1.4426950408889634f, window);
-  return mir_check_launch("prefill_attention");
+  return mir_launch("prefill_attention", prefill_attention_kernel<D>, dim3(tiles, heads), dim3(kPrefillWarps * 32),
+                    smem, stream, 0, q, q_stride, out, k_pages, v_pages, block_table, table_width, query_starts,
+                    context_lens, num_rows, page_size, heads, kv_heads, scale * 1.4426950408889634f, window);
 }
 
 bool bad_common(const char* what, int heads, int kv_heads, int head_dim, int page_size, int table_width, int window) {

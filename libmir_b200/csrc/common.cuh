@@ -18,7 +18,50 @@ enum MirStatus : int {
 void mir_set_error(const char* fmt, ...);
 int mir_check_launch(const char* what);
 
+// Programmatic dependent launch: a kernel launched this way may be scheduled while the kernel before it in
+// the stream is still draining.  Its CTAs run up to mir::grid_dependency_wait() (prefetching what does not
+// depend on the earlier kernel, e.g. weights) and block there until the earlier kernel has completed and
+// its writes are visible.  Every kernel launched through mir_launch calls grid_dependency_wait() before it
+// reads an activation or writes anything, so the order of memory effects is the order of the stream.
+bool mir_pdl_enabled();
+
+template <typename... KernelArgs, typename... Args>
+int mir_launch(const char* what, void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+               cudaStream_t stream, int cluster_y, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  int count = 0;
+  if (cluster_y > 0) {
+    attributes[count].id = cudaLaunchAttributeClusterDimension;
+    attributes[count].val.clusterDim.x = 1;
+    attributes[count].val.clusterDim.y = (unsigned)cluster_y;
+    attributes[count].val.clusterDim.z = 1;
+    ++count;
+  }
+  if (mir_pdl_enabled()) {
+    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  config.attrs = attributes;
+  config.numAttrs = count;
+  const cudaError_t err = cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+  if (err != cudaSuccess) {
+    mir_set_error("%s: launch failed: %s", what, cudaGetErrorString(err));
+    return MIR_CUDA_ERROR;
+  }
+  return mir_check_launch(what);
+}
+
 namespace mir {
+
+// See mir_launch.  Both are no-ops in a kernel that was launched without the attribute.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" :::); }
 
 template <typename T> __device__ __forceinline__ float to_float(T v);
 template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }

@@ -12,6 +12,8 @@ using namespace mir;
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                              int hidden, int vocab, float scale) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int row = blockIdx.x;
   const int id = ids[row];
   const bool ok = id >= 0 && id < vocab;
@@ -26,6 +28,9 @@ template <typename Tout>
 __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ weight,
                                 Tout* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[32];
+  grid_launch_dependents();
+  grid_dependency_wait();
+
   const int row = blockIdx.x;
   const float* src = x + (size_t)(rows ? rows[row] : row) * hidden;
   float sum = 0.0f;
@@ -97,9 +102,11 @@ MIR_EXPORT int mir_embed(int bf16, const void* table, const int* ids, float* out
                          float scale, cudaStream_t stream) {
   if (rows == 0) return MIR_OK;
   if (rows < 0 || hidden <= 0 || vocab <= 0) { mir_set_error("embed: bad sizes"); return MIR_BAD_ARGUMENT; }
-  if (bf16) embed_kernel<<<rows, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, scale);
-  else embed_kernel<<<rows, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab, scale);
-  return mir_check_launch("embed");
+  if (bf16)
+    return mir_launch("embed", embed_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, 0,
+                      (const __nv_bfloat16*)table, ids, out, hidden, vocab, scale);
+  return mir_launch("embed", embed_kernel<float>, dim3(rows), dim3(256), 0, stream, 0, (const float*)table, ids, out,
+                    hidden, vocab, scale);
 }
 
 MIR_EXPORT int mir_rms_norm(int bf16, const float* x, const float* weight, void* out, const int* rows, int n_rows,
@@ -107,9 +114,11 @@ MIR_EXPORT int mir_rms_norm(int bf16, const float* x, const float* weight, void*
   if (n_rows == 0) return MIR_OK;
   if (n_rows < 0 || hidden <= 0) { mir_set_error("rms_norm: bad sizes"); return MIR_BAD_ARGUMENT; }
   const int threads = hidden >= 2048 ? 512 : 256;
-  if (bf16) rms_norm_kernel<<<n_rows, threads, 0, stream>>>(x, weight, (__nv_bfloat16*)out, rows, hidden, eps);
-  else rms_norm_kernel<<<n_rows, threads, 0, stream>>>(x, weight, (float*)out, rows, hidden, eps);
-  return mir_check_launch("rms_norm");
+  if (bf16)
+    return mir_launch("rms_norm", rms_norm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, 0, x, weight,
+                      (__nv_bfloat16*)out, rows, hidden, eps);
+  return mir_launch("rms_norm", rms_norm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, 0, x, weight,
+                    (float*)out, rows, hidden, eps);
 }
 
 MIR_EXPORT int mir_silu_mul(int bf16, const void* gu, void* out, int rows, int inter, cudaStream_t stream) {
@@ -144,6 +153,8 @@ MIR_EXPORT int mir_cast(int kind, const void* src, void* dst, size_t total, cuda
 __global__ void decode_prepare_kernel(const int* __restrict__ positions, const int* __restrict__ block_table,
                                       int table_width, int page_size, int* __restrict__ slot_mapping,
                                       int* __restrict__ context_lens, int rows) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= rows) return;
   const int position = positions[row];
@@ -162,6 +173,8 @@ __global__ void decode_prepare_kernel(const int* __restrict__ positions, const i
 __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __restrict__ tokens,
                                       int* __restrict__ positions, int* __restrict__ token_log, int log_steps,
                                       int* __restrict__ step_counter, int rows) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int step = *step_counter;
   __syncthreads();
   for (int row = threadIdx.x; row < rows; row += blockDim.x) {
@@ -176,14 +189,13 @@ __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __re
 MIR_EXPORT int mir_decode_prepare(const int* positions, const int* block_table, int table_width, int page_size,
                                   int* slot_mapping, int* context_lens, int rows, cudaStream_t stream) {
   if (rows <= 0) return MIR_OK;
-  decode_prepare_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(positions, block_table, table_width, page_size,
-                                                               slot_mapping, context_lens, rows);
-  return mir_check_launch("decode_prepare");
+  return mir_launch("decode_prepare", decode_prepare_kernel, dim3((rows + 127) / 128), dim3(128), 0, stream, 0,
+                    positions, block_table, table_width, page_size, slot_mapping, context_lens, rows);
 }
 
 MIR_EXPORT int mir_decode_advance(const int* sampled, int* tokens, int* positions, int* token_log, int log_steps,
                                   int* step_counter, int rows, cudaStream_t stream) {
   if (rows <= 0) return MIR_OK;
-  decode_advance_kernel<<<1, 256, 0, stream>>>(sampled, tokens, positions, token_log, log_steps, step_counter, rows);
-  return mir_check_launch("decode_advance");
+  return mir_launch("decode_advance", decode_advance_kernel, dim3(1), dim3(256), 0, stream, 0, sampled, tokens,
+                    positions, token_log, log_steps, step_counter, rows);
 }

@@ -19,6 +19,8 @@ __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const float* __restrict__ q_norm, const float* __restrict__ k_norm,
                                      T* __restrict__ k_pages, T* __restrict__ v_pages, int heads, int kv_heads,
                                      int head_dim, int rotary_dim, float eps, int write_kv) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int token = blockIdx.x;
   const int lane = threadIdx.x & 31;
   const int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -88,12 +90,10 @@ MIR_EXPORT int mir_qk_rope_store(int bf16, void* qkv, const int* positions, cons
   const int threads = 128;
   const dim3 grid(tokens, (units + 3) / 4);
   if (bf16)
-    qk_rope_store_kernel<<<grid, threads, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, q_norm,
-                                                         k_norm, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,
-                                                         heads, kv_heads, head_dim, rotary_dim, eps, write_kv);
-  else
-    qk_rope_store_kernel<<<grid, threads, 0, stream>>>((float*)qkv, positions, slot_mapping, inv_freq, q_norm, k_norm,
-                                                         (float*)k_pages, (float*)v_pages, heads, kv_heads, head_dim,
-                                                         rotary_dim, eps, write_kv);
-  return mir_check_launch("qk_rope_store");
+    return mir_launch("qk_rope_store", qk_rope_store_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, 0,
+                      (__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, (__nv_bfloat16*)k_pages,
+                      (__nv_bfloat16*)v_pages, heads, kv_heads, head_dim, rotary_dim, eps, write_kv);
+  return mir_launch("qk_rope_store", qk_rope_store_kernel<float>, grid, dim3(threads), 0, stream, 0, (float*)qkv,
+                    positions, slot_mapping, inv_freq, q_norm, k_norm, (float*)k_pages, (float*)v_pages, heads,
+                    kv_heads, head_dim, rotary_dim, eps, write_kv);
 }

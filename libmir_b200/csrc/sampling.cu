@@ -125,6 +125,8 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
   __shared__ double s_sum[32];
   __shared__ double chunk_sums[kThreads];
   __shared__ int found;
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int row = blockIdx.x;
   const SampleOptions opt = options[row];
   const float* l = logits + (size_t)row * ld;
@@ -225,9 +227,9 @@ MIR_EXPORT int mir_sample(const float* logits, long long ld, int rows, int vocab
                   sort_keys_capacity);
     return MIR_BAD_ARGUMENT;
   }
-  sample_kernel<<<rows, kThreads, 0, stream>>>(logits, (size_t)ld, vocab, (const SampleOptions*)options,
-                                               needs_ranked ? (unsigned long long*)sort_keys : nullptr, padded, tokens);
-  return mir_check_launch("sample");
+  return mir_launch("sample", sample_kernel, dim3(rows), dim3(kThreads), 0, stream, 0, logits, (size_t)ld, vocab,
+                    (const SampleOptions*)options, needs_ranked ? (unsigned long long*)sort_keys : nullptr, padded,
+                    tokens);
 }
 
 MIR_EXPORT int mir_repetition_penalty(float* logits, long long ld, int vocab, const int* ids, const int* id_rows,

@@ -79,6 +79,16 @@ def library(name: str) -> ctypes.CDLL:
     return lib
 
 
+def set_programmatic_launch(enabled: bool) -> None:
+    """Launch kernels with programmatic stream serialization (a kernel's start overlaps the previous kernel's
+    end; every kernel waits for its predecessor before it touches activations) or plainly."""
+    for name in ("core", "bf16"):
+        lib = library(name)
+        lib.mir_set_pdl.argtypes = [c_int]
+        lib.mir_set_pdl.restype = None
+        lib.mir_set_pdl(int(enabled))
+
+
 def loaded_libraries() -> dict:
     """Paths of the native libraries this process has loaded (for reports)."""
     return {name: lib._name for name, lib in _LIBS.items()}
@@ -361,6 +371,14 @@ SKINNY_STORE, SKINNY_ACCUM, SKINNY_F32, SKINNY_SWIGLU = 0, 1, 2, 3
 def _skinny_ok(x: torch.Tensor, m: int, k: int) -> bool:
     """Whether the few-rows kernel takes this product: up to 16 rows, 16-byte aligned rows of 8-element multiples."""
     return (0 < m <= SKINNY_MAX_ROWS and k % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
+
+
+def stream_gemm_error() -> int:
+    """1 if a CTA of the few-rows product ever gave up waiting for its weights, else 0 (synchronises)."""
+    lib = library("bf16")
+    lib.mir_stream_gemm_error.restype = c_int
+    lib.mir_stream_gemm_error.argtypes = []
+    return lib.mir_stream_gemm_error()
 
 
 def gate_up_silu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -> None:
