@@ -130,6 +130,10 @@ def main() -> int:
                         help="decode / prefill: run only that phase, bracketed by cudaProfilerStart/Stop (for ncu "
                              "--profile-from-start off); the JSON line then holds only that phase")
     parser.add_argument("--no-graphs", action="store_true", help="decode steps as plain launches, not as CUDA graphs")
+    parser.add_argument("--library-modes", default="", help="few-rows epilogues (store,accum,f32,swiglu) to run "
+                        "through the library product instead (an experiment switch)")
+    parser.add_argument("--pdl", type=int, default=None, choices=[0, 1],
+                        help="launch kernels with (1) or without (0) programmatic stream serialization")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -148,6 +152,12 @@ def main() -> int:
     from libmir_b200 import CacheConfig, CudaConfig, Library, RuntimeConfig, SchedulerConfig, StepEntry, kernels
     from libmir_b200.sampling import RequestSampler
 
+    if args.library_modes:
+        kernels.SKINNY_MODES -= set(args.library_modes.split(","))
+    if os.environ.get("MIR_EXPERIMENT_SKIP_NORM"):
+        kernels._EXPERIMENT_SKIP_NORM = True
+    if args.pdl is not None:
+        kernels.set_programmatic_launch(bool(args.pdl))
     peaks, peaks_kind = read_peaks()
     config = dict(QWEN3_4B)
     layers_full = config["num_hidden_layers"]

@@ -2,30 +2,30 @@
 //
 //   out[M, N] = epilogue(x[M, K] . w[N, K]^T)
 // With so few tokens the product is a stream of the weights: the work is to read w once at the speed of
-// HBM.  A CTA owns 16 rows of w (32 for the SwiGLU epilogue) over a slice of K.  One warp asks the copy
-// engine for each row's slice with a single bulk copy (cp.async.bulk, completion counted by an mbarrier),
-// so the CTA's whole share of the weights is in flight after a few dozen instructions and no thread
-// spends registers or address arithmetic on it.  When the bytes have landed the 8 warps take every 8th
-// block of 32 k: 16 rows of w are the M side of mma.m16n8k16, 8 tokens the N side.  The partial sums of
-// the warps are added in shared memory in warp order; K is cut over the CTAs of a thread-block cluster
-// (so that matrices with few rows still fill the GPU, and so that a slice fits in shared memory), whose
-// leader adds its peers' sums, in rank order, straight out of their shared memory.  The result is
-// deterministic and needs neither atomics nor scratch in global memory.
+// HBM.  The roles are swapped for the tensor cores: 16 rows of w are the M side of mma.m16n8k16 and 8
+// tokens are the N side.  A CTA owns a strip of rows of w; its 8 warps split K between them (every warp
+// takes every 8th block of 32 k), each lane reading 16 bytes of a row at a time, and the 8 partial
+// sums are added in shared memory in warp order.  When a matrix has too few rows to fill the GPU that
+// way, K is also split over the CTAs of a thread-block cluster, whose leader adds the partial sums of
+// its peers, in rank order, straight out of their shared memory (distributed shared memory).  The
+// result is deterministic and needs neither atomics nor scratch in global memory.
 //
 // No data is rearranged for the fragments: inside one mma the order of k does not matter as long as
-// both operands use the same order, so a lane takes 8 consecutive k of a row of w (16 bytes of shared
-// memory) and the same 8 consecutive k of its token of x, and feeds them as (k, k+1 | k+4, k+5) and
-// (k+2, k+3 | k+6, k+7) of two mma steps.  Rows in shared memory are padded so that the 16-byte reads of
-// a warp fall on different banks.
+// both operands use the same order, so a lane keeps the 8 consecutive k it loaded from a row of w and
+// the same 8 consecutive k of its token of x, and feeds them as (k, k+1 | k+4, k+5) and
+// (k+2, k+3 | k+6, k+7) of two mma steps.
 //
 // Epilogues (fused so that no extra kernel or round trip of the result is needed):
-//   STORE   out bf16 = acc (+ bias)                       QKV projection
+//   STORE   out bf16 = acc (+ bias)                       QKV projection, output head in bf16
 //   ACCUM   out float += acc (+ bias)                     output and down projections into the residual
 //   F32     out float = acc (+ bias)                      output head (32-bit logits)
 //   SWIGLU  out bf16 = silu(acc_gate) * acc_up            w holds [gate rows; up rows]: one launch, and
 //                                                         the gate|up intermediate is never written
-// Waits on the mbarrier are bounded: a CTA that gives up raises a flag that mir_stream_gemm_error()
-// reads, and carries on (its output is then wrong, but nothing hangs).
+// Two more fusions remove the RMSNorm kernel between products.  The ACCUM epilogue can also write, per token,
+// the sum of squares of the 16 residual values it has just produced (`sumsq_out[tile][token]`); a later STORE
+// or SWIGLU product can take the 32-bit residual itself as its input together with those partial sums: it
+// adds them up in tile order, forms rsqrt(mean + eps), and normalises and rounds the values it reads on the
+// fly, exactly as the norm kernel would have (NormFusion below).
 // libmir plans a GEMV only for one token (DenseVectorPlan, cuda/src/backend/linear/autotune/
 // candidate.rs:92-98) and otherwise a library GEMM followed by separate add / gate kernels
 // (cuda/kernels/elementwise_bf16.cu:3-11,42-70).
@@ -50,166 +50,150 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ uint4 load_stream(const bf16* p, bool valid) {
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if (valid) v = __ldcs(reinterpret_cast<const uint4*>(p));      // read once: do not keep in L1
+  return v;
+}
 __device__ __forceinline__ uint4 load_cached(const bf16* p, bool valid) {
   uint4 v = make_uint4(0u, 0u, 0u, 0u);
   if (valid) v = __ldg(reinterpret_cast<const uint4*>(p));
   return v;
 }
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// Optional fusion of the RMSNorm before (residual != nullptr) or after (sumsq_out != nullptr) the product.
+struct NormFusion {
+  const float* residual;   // [m, ld_residual] 32-bit input to normalise instead of x
+  int ld_residual;
+  const float* weight;     // [k] norm weight
+  float eps;
+  const float* sumsq;      // [sumsq_tiles][16]: partial sums of squares of the residual's rows
+  int sumsq_tiles;
+  float* sumsq_out;        // ACCUM: [tiles][16] partial sums of squares of the rows this product updates
+};
 
-__device__ int g_stream_gemm_error = 0;                    // set when a bounded wait gave up
-
-constexpr unsigned long long kWaitNanoseconds = 200ull * 1000ull * 1000ull;   // a copy of a few KB takes microseconds
-
-__device__ __forceinline__ unsigned long long global_nanoseconds() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// Wait for the phase with the given parity; false if the time limit ran out.  test_wait never blocks.
-__device__ __forceinline__ bool wait_barrier(uint32_t barrier, uint32_t parity) {
-  const unsigned long long start = global_nanoseconds();
-  for (;;) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred P1;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, P1;\n\t}"
-        : "=r"(done)
-        : "r"(barrier), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if (global_nanoseconds() - start > kWaitNanoseconds) return false;
-    __nanosleep(64);
-  }
-}
-
-// RS row sets of 16 rows of w per CTA (for SWIGLU: RS/2 gate sets then RS/2 up sets), NT tiles of 8 tokens.
-// Dynamic shared memory: [barrier, 128 bytes][RS*16 rows of w, row_bytes each][warps][PARTIAL][PARTIAL].
-template <int RS, int NT, int MODE>
+// RS row sets of 16 rows of w per warp (for SWIGLU: RS/2 gate sets then RS/2 up sets), NT tiles of 8 tokens,
+// U blocks of 32 k loaded before their products are issued.
+template <int RS, int NT, int U, int MODE, bool FUSED>
 __global__ void __launch_bounds__(kWarps * 32)
 skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, const void* __restrict__ bias,
-                   void* __restrict__ out, int ldo, int m, int n, int k, int up_offset, int k_per_split,
-                   int row_bytes) {
+                   void* __restrict__ out, int ldo, int m, int n, int k, int up_offset, NormFusion norm) {
   constexpr int SETS = MODE == SWIGLU ? RS / 2 : RS;       // row sets that become distinct output columns
-  constexpr int ROWS = RS * 16;
   constexpr int TOKENS = NT * 8;
   constexpr int PARTIAL = RS * 16 * TOKENS;                // floats of one CTA's partial result
-  extern __shared__ __align__(128) unsigned char smem[];
-  const uint32_t barrier = smem_u32(smem);
-  unsigned char* w_rows = smem + 128;
-  float* reduce = reinterpret_cast<float*>(w_rows + (size_t)ROWS * row_bytes);
-  float* cta_sum = reduce + kWarps * PARTIAL;
+  extern __shared__ float shared[];                        // [warps][PARTIAL] then [PARTIAL] (the CTA's sum)
+  float* cta_sum = shared + kWarps * PARTIAL;
+  __shared__ float inverse_rms[16];
   cg::cluster_group cluster = cg::this_cluster();
   const int splits = gridDim.y, split = blockIdx.y;        // the cluster spans gridDim.y: K is cut into `splits`
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int quad = lane & 3, group = lane >> 2;
   const int n0 = blockIdx.x * 16 * SETS;
-  const int k0 = split * k_per_split;
-  const int k_len = max(0, min(k - k0, k_per_split));      // this CTA's slice of K (a multiple of 8)
-  const uint32_t slice_bytes = (uint32_t)k_len * 2u;
-
-  if (threadIdx.x == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(barrier) : "memory");
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncthreads();
-  if (warp == 0) {
-    // which global row each shared-memory row holds; rows past the end of w are left out and read as zero
-    int valid_rows = 0;
-    for (int r = lane; r < ROWS; r += 32) {
-      const int rs = r / 16;
-      const int set = MODE == SWIGLU ? rs % SETS : rs;
-      if (n0 + set * 16 + (r % 16) < n) ++valid_rows;
-    }
-    valid_rows = __reduce_add_sync(0xffffffffu, valid_rows);
-    if (lane == 0)
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(barrier),
-                   "r"(slice_bytes * (uint32_t)valid_rows)
-                   : "memory");
-    __syncwarp();
-    if (slice_bytes > 0) {
-      for (int r = lane; r < ROWS; r += 32) {
-        const int rs = r / 16;
-        const int set = MODE == SWIGLU ? rs % SETS : rs;
-        const int base = (MODE == SWIGLU && rs >= SETS) ? up_offset : 0;
-        const int row = n0 + set * 16 + (r % 16);
-        if (row >= n) continue;
-        const bf16* src = w + (size_t)(base + row) * k + k0;
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                         smem_u32(w_rows + (size_t)r * row_bytes)),
-                     "l"(src), "r"(slice_bytes), "r"(barrier)
-                     : "memory");
-      }
-    }
-  }
-
-  // The weights do not depend on the kernel before this one: their copies are under way.  Everything from
-  // here on reads activations or writes results, so it waits for that kernel to be complete.
   grid_launch_dependents();
-  grid_dependency_wait();
 
+  const bf16* w_lo[RS];
+  const bf16* w_hi[RS];
+  bool ok_lo[RS], ok_hi[RS];
+#pragma unroll
+  for (int rs = 0; rs < RS; ++rs) {
+    const int set = MODE == SWIGLU ? rs % SETS : rs;
+    const int base = (MODE == SWIGLU && rs >= SETS) ? up_offset : 0;
+    const int row = n0 + set * 16 + group;
+    ok_lo[rs] = row < n;
+    ok_hi[rs] = row + 8 < n;
+    w_lo[rs] = w + (size_t)(base + row) * k + quad * 8;
+    w_hi[rs] = w + (size_t)(base + row + 8) * k + quad * 8;
+  }
   const bf16* x_row[NT];
   bool ok_x[NT];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int token = nt * 8 + group;
     ok_x[nt] = token < m;
-    x_row[nt] = x + (size_t)token * ldx + k0 + quad * 8;
+    x_row[nt] = x + (size_t)token * ldx + quad * 8;
   }
-  bool ok_lo[RS], ok_hi[RS];
-#pragma unroll
-  for (int rs = 0; rs < RS; ++rs) {
-    const int set = MODE == SWIGLU ? rs % SETS : rs;
-    ok_lo[rs] = n0 + set * 16 + group < n;
-    ok_hi[rs] = n0 + set * 16 + group + 8 < n;
-  }
+
   float acc[RS][NT][4];
 #pragma unroll
   for (int rs = 0; rs < RS; ++rs)
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[rs][nt][0] = acc[rs][nt][1] = acc[rs][nt][2] = acc[rs][nt][3] = 0.0f;
 
-  if (!wait_barrier(barrier, 0)) {
-    g_stream_gemm_error = 1;
-    wait_barrier(barrier, 0);                              // once more, so that no copy lands after the CTA left
+  grid_dependency_wait();                                  // x and out belong to the kernels before this one
+  constexpr bool fused_norm = FUSED;           // compiled apart: the plain product keeps its registers
+  if (fused_norm) {
+    // 16 threads per token add the tiles' partial sums in a fixed order
+    const int token = threadIdx.x >> 4, part = threadIdx.x & 15;
+    float sum = 0.0f;
+    if (token < m)
+      for (int tile = part; tile < norm.sumsq_tiles; tile += 16) sum += norm.sumsq[tile * 16 + token];
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (part == 0) inverse_rms[token] = rsqrtf(sum / (float)k + norm.eps);
+    __syncthreads();
   }
-
-  const int blocks = (k_len + 31) / 32;
-  constexpr int U = 4;
-  for (int block0 = warp; block0 < blocks; block0 += kWarps * U) {
-    uint4 b[U][NT];
+  float inv[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) inv[nt] = fused_norm ? inverse_rms[nt * 8 + group] : 1.0f;
+  const int blocks = (k + 31) / 32;
+  const int per_split = (blocks + splits - 1) / splits;
+  const int block_begin = split * per_split, block_end = min(blocks, block_begin + per_split);
+  for (int block0 = block_begin + warp; block0 < block_end; block0 += kWarps * U) {
+    uint4 a_lo[U][RS], a_hi[U][RS], b[U][NT];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int offset = (block0 + u * kWarps) * 32;
-      const bool in_k = offset + quad * 8 + 8 <= k_len;
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) b[u][nt] = load_cached(x_row[nt] + offset, in_k && ok_x[nt]);
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int offset = (block0 + u * kWarps) * 32;
-      if (offset >= k_len) continue;                       // the same for the whole warp: mma.sync needs all lanes
-      const bool in_k = offset + quad * 8 + 8 <= k_len;    // a lane past the end of the slice feeds zeros
+      const int block = block0 + u * kWarps;
+      const int offset = block * 32;
+      const bool in_k = block < block_end && offset + quad * 8 + 8 <= k;
 #pragma unroll
       for (int rs = 0; rs < RS; ++rs) {
-        const unsigned char* lo = w_rows + (size_t)(rs * 16 + group) * row_bytes + (size_t)offset * 2 + quad * 16;
-        uint4 a_lo = make_uint4(0u, 0u, 0u, 0u), a_hi = make_uint4(0u, 0u, 0u, 0u);
-        if (in_k && ok_lo[rs]) a_lo = *reinterpret_cast<const uint4*>(lo);
-        if (in_k && ok_hi[rs]) a_hi = *reinterpret_cast<const uint4*>(lo + (size_t)8 * row_bytes);
+        a_lo[u][rs] = load_stream(w_lo[rs] + offset, in_k && ok_lo[rs]);
+        a_hi[u][rs] = load_stream(w_hi[rs] + offset, in_k && ok_hi[rs]);
+      }
+      if (!fused_norm) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) b[u][nt] = load_cached(x_row[nt] + offset, in_k && ok_x[nt]);
+      } else {
+        // normalise 8 values of the 32-bit residual: x * rsqrt(mean(x^2) + eps) * weight, rounded to bf16
+        float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
+        if (in_k) {
+          w0 = __ldg(reinterpret_cast<const float4*>(norm.weight + offset + quad * 8));
+          w1 = __ldg(reinterpret_cast<const float4*>(norm.weight + offset + quad * 8 + 4));
+        }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          mma_bf16(acc[rs][nt], a_lo.x, a_hi.x, a_lo.z, a_hi.z, b[u][nt].x, b[u][nt].z);
-          mma_bf16(acc[rs][nt], a_lo.y, a_hi.y, a_lo.w, a_hi.w, b[u][nt].y, b[u][nt].w);
+          b[u][nt] = make_uint4(0u, 0u, 0u, 0u);
+          if (in_k && ok_x[nt]) {
+            const float* row = norm.residual + (size_t)(nt * 8 + group) * norm.ld_residual + offset + quad * 8;
+            const float4 r0 = __ldg(reinterpret_cast<const float4*>(row));
+            const float4 r1 = __ldg(reinterpret_cast<const float4*>(row + 4));
+            const float s = inv[nt];
+            b[u][nt].x = pack2(r0.x * s * w0.x, r0.y * s * w0.y);
+            b[u][nt].y = pack2(r0.z * s * w0.z, r0.w * s * w0.w);
+            b[u][nt].z = pack2(r1.x * s * w1.x, r1.y * s * w1.y);
+            b[u][nt].w = pack2(r1.z * s * w1.z, r1.w * s * w1.w);
+          }
         }
       }
     }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int rs = 0; rs < RS; ++rs)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          mma_bf16(acc[rs][nt], a_lo[u][rs].x, a_hi[u][rs].x, a_lo[u][rs].z, a_hi[u][rs].z, b[u][nt].x, b[u][nt].z);
+          mma_bf16(acc[rs][nt], a_lo[u][rs].y, a_hi[u][rs].y, a_lo[u][rs].w, a_hi[u][rs].w, b[u][nt].y, b[u][nt].w);
+        }
   }
 
   // partial sums of the 8 warps -> shared memory -> one sum per CTA
-  float* mine = reduce + (size_t)warp * PARTIAL;
+  float* mine = shared + (size_t)warp * PARTIAL;
 #pragma unroll
   for (int rs = 0; rs < RS; ++rs)
 #pragma unroll
@@ -225,35 +209,47 @@ skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
   for (int index = threadIdx.x; index < PARTIAL; index += kWarps * 32) {
     float total = 0.0f;
 #pragma unroll
-    for (int wp = 0; wp < kWarps; ++wp) total += reduce[(size_t)wp * PARTIAL + index];
+    for (int wp = 0; wp < kWarps; ++wp) total += shared[(size_t)wp * PARTIAL + index];
     cta_sum[index] = total;
   }
   cluster.sync();                                          // every CTA's sum is in its shared memory
   if (split == 0) {
     // outputs of the cluster: SETS * 16 columns x m tokens; consecutive threads take consecutive columns
     const int columns = SETS * 16;
-    for (int index = threadIdx.x; index < columns * m; index += kWarps * 32) {
+    const int passes = (columns * TOKENS + kWarps * 32 - 1) / (kWarps * 32);
+    for (int pass = 0; pass < passes; ++pass) {
+      const int index = pass * kWarps * 32 + threadIdx.x;
       const int token = index / columns, local = index % columns;
       const int column = n0 + local;
-      if (column >= n) continue;
-      const int set = local / 16, row = local % 16;
-      const int at = (set * 16 + row) * TOKENS + token;
+      const bool active = token < m && column < n;
       float value = 0.0f, other = 0.0f;
-      for (int rank = 0; rank < splits; ++rank) {
-        const float* peer = cluster.map_shared_rank(cta_sum, rank);
-        value += peer[at];
-        if (MODE == SWIGLU) other += peer[at + SETS * 16 * TOKENS];
+      if (active) {
+        const int set = local / 16, row = local % 16;
+        const int at = (set * 16 + row) * TOKENS + token;
+        for (int rank = 0; rank < splits; ++rank) {
+          const float* peer = cluster.map_shared_rank(cta_sum, rank);
+          value += peer[at];
+          if (MODE == SWIGLU) other += peer[at + SETS * 16 * TOKENS];
+        }
+        if (MODE == SWIGLU) {
+          reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
+              __float2bfloat16_rn(value / (1.0f + expf(-value)) * other);
+        } else if (MODE == STORE) {
+          if (bias) value += __bfloat162float(reinterpret_cast<const bf16*>(bias)[column]);
+          reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(value);
+        } else {
+          if (bias) value += reinterpret_cast<const float*>(bias)[column];
+          float* dst = reinterpret_cast<float*>(out) + (size_t)token * ldo + column;
+          value = MODE == ACCUM ? *dst + value : value;
+          *dst = value;
+        }
       }
-      if (MODE == SWIGLU) {
-        reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
-            __float2bfloat16_rn(value / (1.0f + expf(-value)) * other);
-      } else if (MODE == STORE) {
-        if (bias) value += __bfloat162float(reinterpret_cast<const bf16*>(bias)[column]);
-        reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(value);
-      } else {
-        if (bias) value += reinterpret_cast<const float*>(bias)[column];
-        float* dst = reinterpret_cast<float*>(out) + (size_t)token * ldo + column;
-        *dst = MODE == ACCUM ? *dst + value : value;
+      if (MODE == ACCUM && norm.sumsq_out != nullptr) {
+        // sum of squares of this tile's 16 new residual values of each token (16 consecutive lanes per token)
+        float square = active ? value * value : 0.0f;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
+        if (local == 0 && token < m) norm.sumsq_out[(size_t)blockIdx.x * 16 + token] = square;
       }
     }
   }
@@ -261,86 +257,90 @@ skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
 }
 
 constexpr int kTargetCtas = 4 * 148;
-constexpr int kSliceBudget = 80 * 1024;                    // bytes of weights one CTA holds (two CTAs fit an SM)
 
-template <int RS, int NT, int MODE>
+template <int RS, int NT, int U, int MODE, bool FUSED>
 int launch(const bf16* x, int ldx, const bf16* w, const void* bias, void* out, int ldo, int m, int n, int k,
-           int up_offset, cudaStream_t stream) {
+           int up_offset, const NormFusion& norm, cudaStream_t stream) {
   constexpr int SETS = MODE == SWIGLU ? RS / 2 : RS;
-  constexpr int ROWS = RS * 16;
+  const size_t smem = (size_t)(kWarps + 1) * RS * 16 * NT * 8 * sizeof(float);
   const int tiles = (n + 16 * SETS - 1) / (16 * SETS);
-  // cut K: first until a slice fits in shared memory, then further while the GPU is not full
-  int splits = 1;
-  auto per_split = [&](int s) { return ((k + s - 1) / s + 31) / 32 * 32; };
-  while (splits < 8 && (size_t)ROWS * per_split(splits) * 2 > (size_t)kSliceBudget) splits *= 2;
-  if ((size_t)ROWS * per_split(splits) * 2 > (size_t)200 * 1024) {
-    mir_set_error("skinny_gemm: k %d is too long for this kernel (a slice of %d rows must fit in shared memory)", k,
-                  ROWS);
-    return MIR_BAD_ARGUMENT;
-  }
-  while (splits < 8 && tiles * splits < kTargetCtas && per_split(splits * 2) >= 512) splits *= 2;
-  const int k_per_split = per_split(splits);
-  int row_bytes = k_per_split * 2;
-  if ((row_bytes / 16) % 2 == 0) row_bytes += 16;          // an odd number of 16-byte units: no bank conflicts
-  const size_t smem = 128 + (size_t)ROWS * row_bytes + (size_t)(kWarps + 1) * RS * 16 * NT * 8 * sizeof(float);
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    const cudaError_t err = cudaFuncSetAttribute(skinny_gemm_kernel<RS, NT, MODE>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) {
-      mir_set_error("skinny_gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
-      return MIR_CUDA_ERROR;
-    }
-    configured = smem;
-  }
-  return mir_launch("skinny_gemm", skinny_gemm_kernel<RS, NT, MODE>, dim3(tiles, splits, 1), dim3(kWarps * 32), smem,
-                    stream, splits, x, ldx, w, bias, out, ldo, m, n, k, up_offset, k_per_split, row_bytes);
+  const int blocks = (k + 31) / 32;
+  int splits = 1;                                          // cut K over a cluster until the GPU is full
+  while (splits < 8 && tiles * splits < kTargetCtas && blocks / (splits * 2 * kWarps) >= 2) splits *= 2;
+  return mir_launch("skinny_gemm", skinny_gemm_kernel<RS, NT, U, MODE, FUSED>, dim3(tiles, splits, 1), dim3(kWarps * 32), smem,
+                    stream, splits, x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm);
 }
 
 template <int MODE>
 int dispatch(const bf16* x, int ldx, const bf16* w, const void* bias, void* out, int ldo, int m, int n, int k,
-             int up_offset, cudaStream_t stream) {
+             int up_offset, const NormFusion& norm, cudaStream_t stream) {
+  const bool fused = norm.residual != nullptr;
   if (MODE == SWIGLU) {                          // two row sets (gate, up) per output set
-    if (m <= 8) return launch<2, 1, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
-    return launch<2, 2, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
+    if (fused) {
+      if (m <= 8) return launch<2, 1, 4, MODE, true>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
+      return launch<2, 2, 2, MODE, true>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
+    }
+    if (m <= 8) return launch<2, 1, 4, MODE, false>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
+    return launch<2, 2, 4, MODE, false>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
   }
-  if (m <= 8) return launch<1, 1, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
-  return launch<1, 2, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, stream);
+  if (fused && MODE == STORE) {
+    if (m <= 8) return launch<1, 1, 4, MODE, true>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
+    return launch<1, 2, 4, MODE, true>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
+  }
+  if (fused) {
+    mir_set_error("skinny_gemm: the fused norm input is built for the store and SwiGLU epilogues");
+    return MIR_BAD_ARGUMENT;
+  }
+  if (m <= 8) return launch<1, 1, 8, MODE, false>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
+  return launch<1, 2, 8, MODE, false>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
 }
 
 }  // namespace
 
 MIR_EXPORT int mir_skinny_gemm_max_rows() { return 16; }
 
-// 1 if a CTA of the few-rows product ever gave up waiting for its weights (then its output was wrong), else 0.
-// Synchronises the device.
-MIR_EXPORT int mir_stream_gemm_error() {
-  int flag = 0;
-  if (cudaMemcpyFromSymbol(&flag, g_stream_gemm_error, sizeof(int)) != cudaSuccess) return -1;
-  return flag;
-}
-
 // mode: 0 out bf16 = x w^T (+bias bf16); 1 out float += x w^T (+bias float); 2 out float = x w^T (+bias float);
 // 3 out bf16 [m, n] = silu(x w[0:n]^T) * (x w[up_offset : up_offset + n]^T).
 // Needs m <= 16, k a multiple of 8, ldx a multiple of 8, and x and w on 16-byte boundaries.
+// Norm fusion (all optional, see NormFusion): with `residual` the input is rmsnorm(residual) * norm_weight
+// computed on the fly from the partial sums `sumsq` [sumsq_tiles][16] (x is then ignored and may be null);
+// with `sumsq_out` (mode 1 only) the product also writes the partial sums of squares of the rows it updates,
+// [ceil(n / 16)][16] floats.
 MIR_EXPORT int mir_gemm_skinny_bf16(int mode, const void* x, int ldx, const void* w, const void* bias, void* out,
-                                    int ldo, int m, int n, int k, int up_offset, cudaStream_t stream) {
+                                    int ldo, int m, int n, int k, int up_offset, const float* residual,
+                                    int ld_residual, const float* norm_weight, float eps, const float* sumsq,
+                                    int sumsq_tiles, float* sumsq_out, cudaStream_t stream) {
   if (m == 0 || n == 0) return MIR_OK;
-  if (m < 0 || m > 16 || n < 0 || k <= 0 || (k % 8) || (ldx % 8) || ldx < k || ldo < n ||
-      ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) {
+  const bool fused = residual != nullptr;
+  if (m < 0 || m > 16 || n < 0 || k <= 0 || (k % 8) || ldo < n || ((uintptr_t)w & 15) ||
+      (!fused && ((ldx % 8) || ldx < k || ((uintptr_t)x & 15) || x == nullptr)) ||
+      (fused && ((ld_residual % 4) || ld_residual < k || ((uintptr_t)residual & 15) || norm_weight == nullptr ||
+                 ((uintptr_t)norm_weight & 15) || sumsq == nullptr || sumsq_tiles <= 0))) {
     mir_set_error("skinny_gemm: needs 1..16 rows, k and the row stride multiples of 8 and 16-byte aligned operands "
-                  "(m %d n %d k %d ldx %d ldo %d)", m, n, k, ldx, ldo);
+                  "(m %d n %d k %d ldx %d ldo %d, fused norm %d)", m, n, k, ldx, ldo, (int)fused);
     return MIR_BAD_ARGUMENT;
   }
+  if (sumsq_out != nullptr && mode != ACCUM) {
+    mir_set_error("skinny_gemm: sums of squares are written by the accumulate epilogue only");
+    return MIR_BAD_ARGUMENT;
+  }
+  NormFusion norm;
+  norm.residual = residual;
+  norm.ld_residual = ld_residual;
+  norm.weight = norm_weight;
+  norm.eps = eps;
+  norm.sumsq = sumsq;
+  norm.sumsq_tiles = sumsq_tiles;
+  norm.sumsq_out = sumsq_out;
   const bf16* xx = (const bf16*)x;
   const bf16* ww = (const bf16*)w;
   switch (mode) {
-    case STORE: return dispatch<STORE>(xx, ldx, ww, bias, out, ldo, m, n, k, 0, stream);
-    case ACCUM: return dispatch<ACCUM>(xx, ldx, ww, bias, out, ldo, m, n, k, 0, stream);
-    case F32: return dispatch<F32>(xx, ldx, ww, bias, out, ldo, m, n, k, 0, stream);
+    case STORE: return dispatch<STORE>(xx, ldx, ww, bias, out, ldo, m, n, k, 0, norm, stream);
+    case ACCUM: return dispatch<ACCUM>(xx, ldx, ww, bias, out, ldo, m, n, k, 0, norm, stream);
+    case F32: return dispatch<F32>(xx, ldx, ww, bias, out, ldo, m, n, k, 0, norm, stream);
     case SWIGLU:
       if (bias) { mir_set_error("skinny_gemm: the SwiGLU epilogue takes no bias"); return MIR_BAD_ARGUMENT; }
-      return dispatch<SWIGLU>(xx, ldx, ww, nullptr, out, ldo, m, n, k, up_offset, stream);
+      return dispatch<SWIGLU>(xx, ldx, ww, nullptr, out, ldo, m, n, k, up_offset, norm, stream);
   }
   mir_set_error("skinny_gemm: unknown mode %d", mode);
   return MIR_BAD_ARGUMENT;

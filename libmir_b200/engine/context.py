@@ -92,9 +92,21 @@ class StepContext:
     max_portion: int = 0
     decode_only: bool = False
     page_size: int = 0
+    residual_stats: Optional[tuple] = None     # (residual data_ptr, rows, sums-of-squares tensor, tiles) or None
 
     def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
         return self.arena.alloc(shape, dtype)
+
+    def note_residual_stats(self, residual: torch.Tensor, sumsq: Optional[torch.Tensor], tiles: int) -> None:
+        """Remember (or forget, with None) that `sumsq` holds the sums of squares of `residual` as it is now.
+        Whoever changes the residual calls this; a norm may then be fused into the product that follows."""
+        self.residual_stats = None if sumsq is None else (residual.data_ptr(), residual.shape[0], sumsq, tiles)
+
+    def stats_for(self, residual: torch.Tensor):
+        stats = self.residual_stats
+        if stats is not None and stats[0] == residual.data_ptr() and stats[1] == residual.shape[0]:
+            return stats[2], stats[3]
+        return None
 
     def cache_view(self, entry: int):
         return self.views.get(entry)

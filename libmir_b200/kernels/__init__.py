@@ -47,7 +47,7 @@ _SIGNATURES = {
         "mir_prefill_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "mir_gemm_skinny_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                 c_int, c_void_p],
+                                 c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p],
         "mir_gemm_bf16_lt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_void_p, c_size_t, c_void_p],
     },
@@ -94,6 +94,7 @@ def loaded_libraries() -> dict:
     return {name: lib._name for name, lib in _LIBS.items()}
 
 
+_EXPERIMENT_SKIP_NORM = False
 LAUNCHES = 0        # kernels (and library matrix products) launched through this module, for reports
 
 
@@ -150,6 +151,8 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
     n_rows, hidden = out.shape
     _require(x.dtype == torch.float32 and weight.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
              and x.shape[1] == hidden and weight.numel() == hidden, "rms_norm: bad arguments")
+    if _EXPERIMENT_SKIP_NORM:
+        return
     if rows is not None:
         _require(rows.dtype == torch.int32 and rows.numel() == n_rows, "rms_norm: bad row index")
     else:
@@ -327,13 +330,56 @@ def _lt_workspace(device) -> torch.Tensor:
     return buffer
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           accumulate: bool = False) -> None:
+class NormedResidual:
+    """RMSNorm of the 32-bit residual stream that has not been computed yet: the few-rows products take it as
+    their input and normalise the values as they read them (one kernel less per norm).  `sumsq` holds, per
+    16-column tile of the residual and per token, the sum of squares that the product which last updated the
+    residual wrote.  Anything else that needs the normed rows calls `materialize`."""
+
+    def __init__(self, residual: torch.Tensor, weight: torch.Tensor, eps: float, sumsq: torch.Tensor, tiles: int,
+                 dtype: torch.dtype):
+        self.residual, self.weight, self.eps, self.sumsq, self.tiles, self.dtype = residual, weight, eps, sumsq, tiles, dtype
+        self.shape = residual.shape
+
+    def materialize(self, alloc) -> torch.Tensor:
+        out = alloc(tuple(self.residual.shape), self.dtype)
+        rms_norm(self.residual, self.weight, self.eps, out)
+        return out
+
+
+def sumsq_tiles(columns: int) -> int:
+    """How many 16-column tiles the accumulate epilogue writes sums of squares for."""
+    return -(-columns // 16)
+
+
+def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           accumulate: bool = False, sumsq_out: Optional[torch.Tensor] = None, alloc=None) -> bool:
     """out = (out if accumulate) + x . weight^T (+ bias).
 
-    float32 tensors: the 32-bit FMA kernel.  bfloat16 x and weight: cuBLASLt with 32-bit accumulation,
-    out bfloat16 or float32.  x and out may be row-strided views; weight is [out_features, in_features].
-    """
+    float32 tensors: the 32-bit FMA kernel.  bfloat16 x and weight: up to 16 rows run the weight-streaming
+    kernel, more run cuBLASLt, both with 32-bit accumulation; out is bfloat16 or float32.  x and out may be
+    row-strided views; weight is [out_features, in_features].  x may be a NormedResidual (then `alloc` must be
+    given in case it has to be materialised).  With `sumsq_out` (float32 [ceil(N / 16), 16]) an accumulating
+    few-rows product also writes the sums of squares of the rows it updates; the return value says whether it
+    did."""
+    lazy = x if isinstance(x, NormedResidual) else None
+    if lazy is not None:
+        m, k = lazy.shape
+        fits = (weight.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and not accumulate
+                and 0 < m <= SKINNY_MAX_ROWS and k % 8 == 0 and "store" in SKINNY_MODES
+                and lazy.residual.stride(0) % 4 == 0)
+        if fits:
+            _cuda(lazy.residual, weight, out, bias)
+            n = weight.shape[0]
+            _require(weight.shape[1] == k and out.shape == (m, n) and out.stride(1) == 1 and weight.is_contiguous(),
+                     "linear: shapes or strides do not fit")
+            lib = library("bf16")
+            _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_STORE, None, 0, weight.data_ptr(), _ptr(bias), out.data_ptr(),
+                                                 out.stride(0), m, n, k, 0, lazy.residual.data_ptr(),
+                                                 lazy.residual.stride(0), lazy.weight.data_ptr(), lazy.eps,
+                                                 lazy.sumsq.data_ptr(), lazy.tiles, None, _stream()))
+            return False
+        x = lazy.materialize(alloc)
     _cuda(x, weight, out, bias)
     m, k = x.shape
     n = weight.shape[0]
@@ -346,25 +392,31 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optio
         lib = library("core")
         _check(lib, lib.mir_gemm_f32(x.data_ptr(), x.stride(0), weight.data_ptr(), k, _ptr(bias), out.data_ptr(),
                                      out.stride(0), m, n, k, beta, _stream()))
-        return
+        return False
     _require(x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16, "linear: x and weight must share a dtype")
     if bias is not None and bias.dtype != out.dtype:
         _require(out.dtype == torch.float32 and accumulate, "linear: bias dtype must match out")
         add_bias(out, bias)
         bias = None
     lib = library("bf16")
-    if _skinny_ok(x, m, k) and (out.dtype == torch.float32 or not accumulate):
+    mode_name = "store" if out.dtype == torch.bfloat16 else ("accum" if accumulate else "f32")
+    if _skinny_ok(x, m, k) and (out.dtype == torch.float32 or not accumulate) and mode_name in SKINNY_MODES:
         mode = SKINNY_STORE if out.dtype == torch.bfloat16 else (SKINNY_ACCUM if accumulate else SKINNY_F32)
+        stats = sumsq_out if (mode == SKINNY_ACCUM and sumsq_out is not None
+                              and sumsq_out.numel() >= sumsq_tiles(n) * 16) else None
         _check(lib, lib.mir_gemm_skinny_bf16(mode, x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias),
-                                             out.data_ptr(), out.stride(0), m, n, k, 0, _stream()))
-        return
+                                             out.data_ptr(), out.stride(0), m, n, k, 0, None, 0, None, 0.0, None, 0,
+                                             _ptr(stats), _stream()))
+        return stats is not None
     workspace = _lt_workspace(x.device)
     _check(lib, lib.mir_gemm_bf16_lt(x.data_ptr(), x.stride(0), weight.data_ptr(), k, _ptr(bias), out.data_ptr(),
                                      out.stride(0), int(out.dtype == torch.float32), m, n, k, beta,
                                      workspace.data_ptr(), workspace.numel(), _stream()))
+    return False
 
 
 SKINNY_MAX_ROWS = 16
+SKINNY_MODES = {"store", "accum", "f32", "swiglu"}     # the few-rows epilogues in use; the rest go to the library
 SKINNY_STORE, SKINNY_ACCUM, SKINNY_F32, SKINNY_SWIGLU = 0, 1, 2, 3
 
 
@@ -373,29 +425,35 @@ def _skinny_ok(x: torch.Tensor, m: int, k: int) -> bool:
     return (0 < m <= SKINNY_MAX_ROWS and k % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
 
 
-def stream_gemm_error() -> int:
-    """1 if a CTA of the few-rows product ever gave up waiting for its weights, else 0 (synchronises)."""
-    lib = library("bf16")
-    lib.mir_stream_gemm_error.restype = c_int
-    lib.mir_stream_gemm_error.argtypes = []
-    return lib.mir_stream_gemm_error()
-
-
-def gate_up_silu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -> None:
+def gate_up_silu(x, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -> None:
     """out[M, I] = silu(x w_gate^T) * (x w_up^T) with w_gate_up = [w_gate; w_up] of shape [2 I, K].
 
-    Up to 16 bfloat16 rows: one kernel, the [M, 2 I] intermediate is never written.  Otherwise the product
-    (library or 32-bit kernel) followed by the SiLU-multiply kernel; `scratch_alloc(shape, dtype)` provides
-    the intermediate."""
-    _cuda(x, w_gate_up, out)
+    Up to 16 bfloat16 rows: one kernel, the [M, 2 I] intermediate is never written, and x may be a
+    NormedResidual that is normalised on the fly.  Otherwise the product (library or 32-bit kernel) followed by
+    the SiLU-multiply kernel; `scratch_alloc(shape, dtype)` provides the intermediate."""
+    lazy = x if isinstance(x, NormedResidual) else None
     m, k = x.shape
     inter = out.shape[1]
     _require(w_gate_up.shape == (2 * inter, k) and out.shape[0] == m and out.is_contiguous()
-             and w_gate_up.is_contiguous() and x.stride(1) == 1, "gate_up_silu: shapes do not fit")
-    if x.dtype == torch.bfloat16 and _skinny_ok(x, m, k):
+             and w_gate_up.is_contiguous(), "gate_up_silu: shapes do not fit")
+    few = (w_gate_up.dtype == torch.bfloat16 and 0 < m <= SKINNY_MAX_ROWS and k % 8 == 0 and "swiglu" in SKINNY_MODES)
+    if lazy is not None:
+        if few and lazy.residual.stride(0) % 4 == 0:
+            _cuda(lazy.residual, w_gate_up, out)
+            lib = library("bf16")
+            _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_SWIGLU, None, 0, w_gate_up.data_ptr(), None, out.data_ptr(),
+                                                 out.stride(0), m, inter, k, inter, lazy.residual.data_ptr(),
+                                                 lazy.residual.stride(0), lazy.weight.data_ptr(), lazy.eps,
+                                                 lazy.sumsq.data_ptr(), lazy.tiles, None, _stream()))
+            return
+        x = lazy.materialize(scratch_alloc)
+    _cuda(x, w_gate_up, out)
+    _require(x.stride(1) == 1, "gate_up_silu: x rows must be contiguous")
+    if few and x.dtype == torch.bfloat16 and _skinny_ok(x, m, k):
         lib = library("bf16")
         _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_SWIGLU, x.data_ptr(), x.stride(0), w_gate_up.data_ptr(), None,
-                                             out.data_ptr(), out.stride(0), m, inter, k, inter, _stream()))
+                                             out.data_ptr(), out.stride(0), m, inter, k, inter, None, 0, None, 0.0,
+                                             None, 0, None, _stream()))
         return
     gate_up = scratch_alloc((m, 2 * inter), x.dtype)
     linear(x, w_gate_up, gate_up)

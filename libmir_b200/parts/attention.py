@@ -21,6 +21,7 @@ from .base import Mixer
 
 class SoftmaxAttention(Mixer):
     graph_safe = True
+    takes_normed_residual = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -72,7 +73,7 @@ class SoftmaxAttention(Mixer):
         s = self.spec
         tokens = x.shape[0]
         qkv = ctx.alloc((tokens, self.q_width + 2 * self.kv_width), self.env.dtype)
-        kernels.linear(x, self.w_qkv, qkv, self.b_qkv)
+        kernels.linear(x, self.w_qkv, qkv, self.b_qkv, alloc=ctx.alloc)
         group = ctx.groups[cache.group]
         kernels.qk_rope_store(
             qkv, ctx.positions, group.slot_mapping,
@@ -81,7 +82,16 @@ class SoftmaxAttention(Mixer):
             self.position.rotary_dim if self.position is not None else 0, s.qk_norm_eps, write_kv=cache.writes)
         mixed = ctx.alloc((tokens, self.q_width), self.env.dtype)
         self.attend(ctx, group, cache, qkv, mixed)
-        kernels.linear(mixed, self.w_o, residual, self.b_o, accumulate=True)
+        note = getattr(ctx, "note_residual_stats", None)
+        if note is None:
+            kernels.linear(mixed, self.w_o, residual, self.b_o, accumulate=True)
+        else:
+            # a few-rows product also leaves the sums of squares of the new residual, so that the next norm
+            # can be computed inside the product that follows it
+            tiles = kernels.sumsq_tiles(s.hidden_size)
+            sumsq = ctx.alloc((tiles, 16), torch.float32)
+            wrote = kernels.linear(mixed, self.w_o, residual, self.b_o, accumulate=True, sumsq_out=sumsq)
+            note(residual, sumsq if wrote else None, tiles)
 
     def attend(self, ctx, group, cache, qkv, out):
         """Attention of every packed row over its request's pages; the kernel is chosen by dtype and size:

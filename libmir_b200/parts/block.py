@@ -30,12 +30,31 @@ class PreNormBlock(Block):
         return self.mixer.cache_requirement()
 
     def forward(self, ctx, cache, residual):
-        x = self.mixer_norm.forward(ctx, residual) if self.mixer_norm is not None else ctx.cast_residual(residual)
+        # A part that sets `takes_normed_residual` accepts a kernels.NormedResidual as x (a norm that its first
+        # product computes on the fly); every other part gets the normed tensor.
+        x = (self._norm(self.mixer_norm, self.mixer, ctx, residual) if self.mixer_norm is not None
+             else ctx.cast_residual(residual))
+        self._forget_stats(ctx)              # the mixer changes the residual; it may note new sums of squares
         self.mixer.forward(ctx, cache, x, residual)
         if self.feed_forward is not None:
-            x = (self.feed_forward_norm.forward(ctx, residual) if self.feed_forward_norm is not None
-                 else ctx.cast_residual(residual))
+            x = (self._norm(self.feed_forward_norm, self.feed_forward, ctx, residual)
+                 if self.feed_forward_norm is not None else ctx.cast_residual(residual))
+            self._forget_stats(ctx)
             self.feed_forward.forward(ctx, x, residual)
+
+    @staticmethod
+    def _forget_stats(ctx):
+        if hasattr(ctx, "residual_stats"):
+            ctx.residual_stats = None
+
+    @staticmethod
+    def _norm(norm, consumer, ctx, residual):
+        if getattr(consumer, "takes_normed_residual", False) and getattr(norm, "forward", None) is not None:
+            try:
+                return norm.forward(ctx, residual, lazy=True)
+            except TypeError:                 # a norm part without the `lazy` option
+                pass
+        return norm.forward(ctx, residual)
 
 
 ARRANGEMENTS = {"pre_norm": PreNormBlock}

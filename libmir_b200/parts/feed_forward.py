@@ -15,6 +15,8 @@ from .base import FeedForward
 
 
 class SwiGlu(FeedForward):
+    takes_normed_residual = True
+
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.w_gate_up = self.w_down = None
@@ -39,4 +41,13 @@ class SwiGlu(FeedForward):
         tokens = x.shape[0]
         hidden = ctx.alloc((tokens, s.intermediate_size), self.env.dtype)
         kernels.gate_up_silu(x, self.w_gate_up, hidden, ctx.alloc)
-        kernels.linear(hidden, self.w_down, residual, accumulate=True)
+        note = getattr(ctx, "note_residual_stats", None)
+        if note is None:
+            kernels.linear(hidden, self.w_down, residual, accumulate=True)
+        else:
+            # a few-rows product also leaves the sums of squares of the new residual, so that the next norm
+            # can be computed inside the product that follows it
+            tiles = kernels.sumsq_tiles(s.hidden_size)
+            sumsq = ctx.alloc((tiles, 16), torch.float32)
+            wrote = kernels.linear(hidden, self.w_down, residual, accumulate=True, sumsq_out=sumsq)
+            note(residual, sumsq if wrote else None, tiles)

@@ -29,7 +29,13 @@ class RmsNorm(Norm):
     def weight_bytes(self):
         return self.weight.numel() * 4
 
-    def forward(self, ctx, x, out=None, rows=None):
+    def forward(self, ctx, x, out=None, rows=None, lazy=False):
+        """`lazy`: the caller's next product can normalise on the fly; if the sums of squares of x are at hand
+        (written by the product that last added into it), return a NormedResidual instead of running a kernel."""
+        if lazy and out is None and rows is None and self.env.dtype == torch.bfloat16:
+            stats = ctx.stats_for(x) if hasattr(ctx, "stats_for") else None
+            if stats is not None:
+                return kernels.NormedResidual(x, self.weight, self.spec.eps, stats[0], stats[1], self.env.dtype)
         n_rows = x.shape[0] if rows is None else rows.numel()
         if out is None:
             out = ctx.alloc((n_rows, self.spec.size), self.env.dtype)

@@ -376,14 +376,3 @@ def test_gate_up_silu(dtype, m, inter, k):
     gate = plain_impl.linear(x.double(), w[:inter])
     up = plain_impl.linear(x.double(), w[inter:])
     close(out, plain_impl.silu(gate) * up, dtype, factor=2)
-
-
-def test_no_bounded_wait_ever_gave_up():
-    """The few-rows product waits for its bulk copies with a limit; the flag it raises on giving up stays 0."""
-    from libmir_b200 import kernels
-    x, w = torch.randn(4, 9728).bfloat16().cuda(), torch.randn(2560, 9728).bfloat16().cuda()
-    out = torch.zeros(4, 2560, device="cuda")
-    for _ in range(3):
-        kernels.linear(x, w, out, accumulate=True)
-    close(out, 3 * plain_impl.linear(x.double().cpu(), w.cpu()), torch.float32, factor=400)
-    assert kernels.stream_gemm_error() == 0
