@@ -154,8 +154,6 @@ def main() -> int:
 
     if args.library_modes:
         kernels.SKINNY_MODES -= set(args.library_modes.split(","))
-    if os.environ.get("MIR_EXPERIMENT_SKIP_NORM"):
-        kernels._EXPERIMENT_SKIP_NORM = True
     if args.pdl is not None:
         kernels.set_programmatic_launch(bool(args.pdl))
     peaks, peaks_kind = read_peaks()

@@ -32,7 +32,8 @@ class RmsNorm(Norm):
     def forward(self, ctx, x, out=None, rows=None, lazy=False):
         """`lazy`: the caller's next product can normalise on the fly; if the sums of squares of x are at hand
         (written by the product that last added into it), return a NormedResidual instead of running a kernel."""
-        if lazy and out is None and rows is None and self.env.dtype == torch.bfloat16:
+        if (lazy and kernels.FUSE_NORM_INTO_PRODUCT and out is None and rows is None
+                and self.env.dtype == torch.bfloat16):
             stats = ctx.stats_for(x) if hasattr(ctx, "stats_for") else None
             if stats is not None:
                 return kernels.NormedResidual(x, self.weight, self.spec.eps, stats[0], stats[1], self.env.dtype)

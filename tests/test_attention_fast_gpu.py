@@ -163,12 +163,15 @@ def test_fast_kernels_refuse_other_head_sizes():
                                   1, 1, 80, 1.0, None)
 
 
-def test_engine_uses_the_fast_kernels_and_matches_the_plain_model(tmp_path):
+@pytest.mark.parametrize("fuse_norm", [False, True])
+def test_engine_uses_the_fast_kernels_and_matches_the_plain_model(tmp_path, fuse_norm, monkeypatch):
     """A model with head_dim 64 in bfloat16: prompt portions, mixed steps and graph-captured decode steps
     all run the tensor-core kernels; logits against the plain implementation."""
     from helpers import TOL, make_folder, plain_logits, random_ids
-    from libmir_b200 import CacheConfig, Library, RuntimeConfig, StepEntry
+    from libmir_b200 import CacheConfig, Library, RuntimeConfig, StepEntry, kernels
     from libmir_b200.sampling import RequestSampler
+    # with fuse_norm the decode steps leave each RMSNorm to the product after it (kernels.NormedResidual)
+    monkeypatch.setattr(kernels, "FUSE_NORM_INTO_PRODUCT", fuse_norm)
     config = {"architectures": ["Qwen3ForCausalLM"], "hidden_size": 128, "intermediate_size": 320,
               "num_hidden_layers": 2, "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 64,
               "vocab_size": 500, "max_position_embeddings": 2048, "rms_norm_eps": 1e-6, "rope_theta": 1e6,
