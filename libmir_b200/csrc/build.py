@@ -36,7 +36,7 @@ LIBRARIES = {
         "link": [],
     },
     "bf16": {
-        "sources": ["runtime.cu", "gemm_lt.cu", "attention_mma.cu", "gemm_skinny.cu"],
+        "sources": ["runtime.cu", "gemm_lt.cu", "attention_mma.cu", "gemm_skinny.cu", "gemm_tc.cu"],
         "headers": ["no_alloc.h"],
         "link": ["-lcublasLt"],
     },

@@ -48,6 +48,10 @@ _SIGNATURES = {
                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "mir_gemm_skinny_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                  c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p],
+        "mir_gemm_tc_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                             c_void_p],
+        "mir_gemm_tc_set_stages": [c_int, c_int],
+        "mir_gemm_tc_error": [],
         "mir_gemm_bf16_lt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_void_p, c_size_t, c_void_p],
     },
@@ -414,6 +418,37 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
                                      out.stride(0), int(out.dtype == torch.float32), m, n, k, beta,
                                      workspace.data_ptr(), workspace.numel(), _stream()))
     return False
+
+
+def tensor_core_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
+                       bias: Optional[torch.Tensor] = None, accumulate: bool = False, swiglu: bool = False) -> None:
+    """The tcgen05 product for many bfloat16 rows: out = x . weight^T (+ bias) as bfloat16, or as float32
+    (added to out if `accumulate`); with `swiglu`, weight is [gate rows; up rows] and
+    out[M, I] = silu(x w_gate^T) * (x w_up^T) in one kernel."""
+    _cuda(x, weight, out, bias)
+    m, k = x.shape
+    _require(x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.is_contiguous()
+             and weight.shape[1] == k and x.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == m,
+             "tensor_core_linear: bfloat16 x [M, K] and weight [N, K] are needed")
+    lib = library("bf16")
+    if swiglu:
+        inter = out.shape[1]
+        _require(weight.shape[0] == 2 * inter and out.dtype == torch.bfloat16 and bias is None and not accumulate,
+                 "tensor_core_linear: the SwiGLU epilogue takes [2 I, K] weights, no bias, and writes bfloat16")
+        mode, n, up_offset = SKINNY_SWIGLU, inter, inter
+    else:
+        n, up_offset = weight.shape[0], 0
+        _require(out.shape[1] == n and (bias is None or bias.dtype == out.dtype)
+                 and (out.dtype == torch.float32 or not accumulate),
+                 "tensor_core_linear: out must be [M, N]; bias shares its dtype; only float32 accumulates")
+        mode = SKINNY_STORE if out.dtype == torch.bfloat16 else (SKINNY_ACCUM if accumulate else SKINNY_F32)
+    _check(lib, lib.mir_gemm_tc_bf16(mode, x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias), out.data_ptr(),
+                                     out.stride(0), m, n, k, up_offset, _stream()))
+
+
+def tensor_core_linear_error() -> int:
+    """0, or which role of the tcgen05 product gave up a bounded wait (synchronises the device)."""
+    return int(library("bf16").mir_gemm_tc_error())
 
 
 SKINNY_MAX_ROWS = 16
