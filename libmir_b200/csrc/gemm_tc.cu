@@ -2,33 +2,40 @@
 //
 //   out[M, N] = epilogue(x[M, K] . w[N, K]^T)          x, w row-major bf16 ("K-major" for both operands)
 //
-// One CTA computes a 128-token x 128-feature tile of the output (for the SwiGLU epilogue: 128 gate features
-// and the 128 up features that belong to them, 256 accumulator columns).  Three roles, one warp or more each:
+// One CTA per SM walks over tiles of the output: 128 tokens x `width` accumulator columns (for the SwiGLU
+// epilogue width / 2 gate features and the width / 2 up features that belong to them); width is 256 unless
+// the product has fewer columns.  Three roles:
 //
 //   producer   one thread.  Per 64-wide step of K it asks the TMA unit for the x box (128 rows x 64) and the
-//              w box(es) (128 rows x 64) with cp.async.bulk.tensor.2d into a ring of shared-memory stages laid
-//              out with the 128-byte swizzle that tcgen05.mma reads.  Out-of-range rows and k arrive as zeros,
-//              so M, N and K need not be multiples of the tile.  An mbarrier per stage counts the bytes in.
-//   issuer     one thread.  When a stage is full it issues four tcgen05.mma (128 x N x 16 each, operands
+//              w box(es) with cp.async.bulk.tensor.2d into a ring of shared-memory stages laid out with the
+//              128-byte swizzle that tcgen05.mma reads.  Out-of-range rows and k arrive as zeros, so M, N and K
+//              need not be multiples of the tile.  An mbarrier per stage counts the bytes in.
+//   issuer     one thread.  When a stage is full it issues four tcgen05.mma (128 x width x 16 each, operands
 //              straight from shared memory through matrix descriptors, accumulator in tensor memory) and then
 //              tcgen05.commit, which arrives on the stage's "empty" barrier once the tensor cores have read the
-//              stage, so the producer can refill it.  After the last step a commit arrives on the "done" barrier.
-//   epilogue   four warps; warp i owns accumulator lanes 32 i .. 32 i + 31 (one token row per thread).  They
-//              wait for "done", read the accumulator with tcgen05.ld (32 columns at a time), apply the epilogue
-//              and write the row to global memory.
+//              stage, so the producer can refill it.  After a tile's last step a commit arrives on the
+//              accumulator's "full" barrier.  Two accumulators alternate: the products of the next tile run
+//              while the epilogue reads the last one.
+//   epilogue   eight warps; warp i may read accumulator lanes 32 (i mod 4) .. + 31 (one token row per thread),
+//              and the two warps of a quarter take alternate chunks of 32 columns.  They
+//              wait for "full", read the accumulator with tcgen05.ld (32 columns at a time), hand the
+//              accumulator back ("free" barrier) as soon as its last columns are in registers, apply the
+//              epilogue and write the row to global memory.
 //
 // Epilogues:  STORE  out bf16 = acc (+ bias)
 //             ACCUM  out float += acc (+ bias)            the residual stream
 //             F32    out float = acc (+ bias)
 //             SWIGLU out bf16 = silu(acc_gate) * acc_up   w holds [gate rows; up rows]; the [M, 2 I] intermediate
 //                                                         of the two-kernel formulation is never written
-// Tensor memory: 128 lanes x 128 (or 256) 32-bit columns, allocated by one warp and freed by the same warp.
+// Tensor memory: all 512 columns (two accumulators of 128 lanes x 256 columns), allocated by one warp and freed
+// by the same warp; the shared-memory ring leaves room for one CTA per SM only.
 // Every wait is bounded in time; a role whose wait runs out raises g_tc_gemm_error and stops waiting, the CTA
 // still frees its tensor memory and returns.
 // libmir takes these products from a library (DenseMatmulPlan / CublasLtBf16Plan of the mircuda crate,
 // cuda/src/backend/linear/mod.rs:141-194) and applies the gate in a second kernel
 // (cuda/kernels/elementwise_bf16.cu:42-70).
 #include <cuda.h>
+#include <algorithm>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -40,10 +47,12 @@ typedef __nv_bfloat16 bf16;
 namespace {
 
 constexpr int kTileM = 128;                 // tokens per CTA
-constexpr int kTileN = 128;                 // features per accumulator half
 constexpr int kStepK = 64;                  // k per stage: 128 bytes, one swizzle row
-constexpr int kBoxBytes = 128 * kStepK * 2; // 16 KB: a 128-row x 64-k box
-constexpr int kThreads = 6 * 32;            // producer warp, issuer warp, four epilogue warps
+constexpr int kStages = 4;                  // shared-memory ring
+constexpr int kStageStride = (kTileM + 256) * 128;   // 48 KB: 128 token rows and up to 256 weight rows of 128 bytes
+constexpr int kEpilogueWarps = 8;          // two per quarter of the accumulator lanes; they share its columns
+constexpr int kThreads = (2 + kEpilogueWarps) * 32;  // producer warp, issuer warp, epilogue warps
+constexpr uint32_t kTmemColumns = 512;      // two accumulators of up to 256 columns
 enum Epilogue : int { STORE = 0, ACCUM = 1, F32 = 2, SWIGLU = 3 };
 
 __device__ int g_tc_gemm_error = 0;
@@ -131,37 +140,42 @@ __device__ __forceinline__ void tmem_load_32(uint32_t address, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// STAGES stages of [x box | w box (| second w box)]; dynamic shared memory starts on a 1024-byte boundary.
+// One CTA per SM walks over output tiles (token tile fastest, so CTAs that run together share weight rows in
+// L2).  A tile is 128 tokens x `width` accumulator columns (width a multiple of 16, at most 256; with the SwiGLU
+// epilogue width / 2 gate columns followed by width / 2 up columns).  Two accumulators of 256 columns alternate,
+// so the epilogue of one tile overlaps the products of the next.
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
                const void* __restrict__ bias, void* __restrict__ out, int ldo, int m, int n, int k, int up_offset,
-               int stages) {
-  constexpr int HALVES = MODE == SWIGLU ? 2 : 1;            // accumulator halves of 128 columns
-  constexpr int STAGE_BYTES = (1 + HALVES) * kBoxBytes;
-  constexpr uint32_t TMEM_COLUMNS = HALVES * kTileN;
+               int width, int token_tiles, int tiles) {
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long barriers[2 * 8 + 1];   // full[8], empty[8], done
+  __shared__ __align__(8) unsigned long long barriers[2 * kStages + 4];   // full, empty, accumulator full[2], free[2]
   __shared__ uint32_t tmem_base_slot;
   if (*reinterpret_cast<volatile int*>(&g_tc_gemm_error) != 0) return;   // an earlier wait ran out: do not queue up more
   // the swizzle pattern repeats every 1024 bytes; the stages start on such a boundary
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kTileM, n0 = blockIdx.x * kTileN;
-  const uint32_t full0 = smem_u32(&barriers[0]), empty0 = smem_u32(&barriers[8]), done = smem_u32(&barriers[16]);
+  const uint32_t full0 = smem_u32(&barriers[0]), empty0 = smem_u32(&barriers[kStages]);
+  const uint32_t acc_full0 = smem_u32(&barriers[2 * kStages]), acc_free0 = smem_u32(&barriers[2 * kStages + 2]);
   const int steps = (k + kStepK - 1) / kStepK;
+  const int out_width = MODE == SWIGLU ? width / 2 : width;  // output columns of a tile
+  const uint32_t stage_bytes = (uint32_t)(kTileM + width) * 128u;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(full0 + 8 * s) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(empty0 + 8 * s) : "memory");
     }
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(done) : "memory");
+    for (int b = 0; b < 2; ++b) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(acc_full0 + 8 * b) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(acc_free0 + 8 * b), "r"(kEpilogueWarps) : "memory");
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {                                          // this warp owns the tensor memory allocation
+  if (warp == 1) {                                          // this warp owns the tensor memory: all 512 columns
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
-                 "r"(TMEM_COLUMNS)
+                 "r"(kTmemColumns)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -176,74 +190,98 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
       const uint64_t xm = reinterpret_cast<uint64_t>(&x_map), wm = reinterpret_cast<uint64_t>(&w_map);
-      for (int step = 0; step < steps; ++step) {
-        const int stage = step % stages;
-        const uint32_t parity = (uint32_t)(step / stages) & 1u;
-        if (!wait_barrier(empty0 + 8 * stage, parity ^ 1u)) { g_tc_gemm_error = 1; break; }
-        const uint32_t barrier = full0 + 8 * stage;
-        const uint32_t dst = smem_u32(smem + (size_t)stage * STAGE_BYTES);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(barrier), "r"((uint32_t)STAGE_BYTES) : "memory");
-        asm volatile(
-            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
-                "r"(dst), "l"(xm), "r"(barrier), "r"(step * kStepK), "r"(m0)
-            : "memory");
-        asm volatile(
-            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
-                "r"(dst + kBoxBytes), "l"(wm), "r"(barrier), "r"(step * kStepK), "r"(n0)
-            : "memory");
-        if (MODE == SWIGLU)
+      uint32_t count = 0;                                    // stages filled so far, over all tiles
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
+        const int m0 = (tile % token_tiles) * kTileM, n0 = (tile / token_tiles) * out_width;
+        for (int step = 0; step < steps; ++step, ++count) {
+          const uint32_t stage = count % kStages, parity = (count / kStages) & 1u;
+          if (!wait_barrier(empty0 + 8 * stage, parity ^ 1u)) { g_tc_gemm_error = 1; alive = false; break; }
+          const uint32_t barrier = full0 + 8 * stage;
+          const uint32_t dst = smem_u32(smem + (size_t)stage * kStageStride);
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(barrier), "r"(stage_bytes) : "memory");
           asm volatile(
               "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
-                  "r"(dst + 2 * kBoxBytes), "l"(wm), "r"(barrier), "r"(step * kStepK), "r"(up_offset + n0)
+                  "r"(dst), "l"(xm), "r"(barrier), "r"(step * kStepK), "r"(m0)
               : "memory");
+          // the weight map's box has out_width rows: one box, or a gate box and an up box behind it
+          asm volatile(
+              "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+                  "r"(dst + kTileM * 128), "l"(wm), "r"(barrier), "r"(step * kStepK), "r"(n0)
+              : "memory");
+          if (MODE == SWIGLU)
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+                    "r"(dst + (kTileM + out_width) * 128), "l"(wm), "r"(barrier), "r"(step * kStepK), "r"(up_offset + n0)
+                : "memory");
+        }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = instruction_descriptor(kTileM, HALVES * kTileN);
+      const uint32_t idesc = instruction_descriptor(kTileM, width);
+      uint32_t count = 0, local = 0;                         // stages consumed; tiles of this CTA
       bool alive = true;
-      for (int step = 0; step < steps; ++step) {
-        const int stage = step % stages;
-        const uint32_t parity = (uint32_t)(step / stages) & 1u;
-        if (alive && !wait_barrier(full0 + 8 * stage, parity)) { g_tc_gemm_error = 2; alive = false; }
+      for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+        const uint32_t buffer = local & 1u, use = (local >> 1) & 1u;
+        // the epilogue must have read this accumulator's previous tile
+        if (alive && !wait_barrier(acc_free0 + 8 * buffer, use ^ 1u)) { g_tc_gemm_error = 2; alive = false; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_base = smem_u32(smem + (size_t)stage * STAGE_BYTES);
-        const uint32_t b_base = a_base + kBoxBytes;          // gate rows then, for SwiGLU, up rows: 256 rows of B
+        const uint32_t accumulator = tmem_base + buffer * 256u;
+        for (int step = 0; step < steps; ++step, ++count) {
+          const uint32_t stage = count % kStages, parity = (count / kStages) & 1u;
+          if (alive && !wait_barrier(full0 + 8 * stage, parity)) { g_tc_gemm_error = 2; alive = false; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_base = smem_u32(smem + (size_t)stage * kStageStride);
+          const uint32_t b_base = a_base + kTileM * 128;
 #pragma unroll
-        for (int kk = 0; kk < kStepK / 16; ++kk) {
-          // 16 k = 32 bytes further along the swizzled rows: the start address moves by 32 bytes
-          const uint64_t a_desc = operand_descriptor(a_base + kk * 32);
-          const uint64_t b_desc = operand_descriptor(b_base + kk * 32);
-          mma_bf16_ss(tmem_base, a_desc, b_desc, idesc, (step > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kStepK / 16; ++kk) {
+            // 16 k = 32 bytes further along the swizzled rows: the start address moves by 32 bytes
+            mma_bf16_ss(accumulator, operand_descriptor(a_base + kk * 32), operand_descriptor(b_base + kk * 32), idesc,
+                        (step > 0 || kk > 0) ? 1u : 0u);
+          }
+          mma_commit(empty0 + 8 * stage);                    // the stage is free once these have read it
         }
-        mma_commit(empty0 + 8 * stage);                      // the stage is free once these have read it
+        mma_commit(acc_full0 + 8 * buffer);                  // this tile's accumulator is complete
       }
-      mma_commit(done);                                      // the accumulator is complete
     }
   } else {
     // ------------------------------------------------------------------ epilogue: one token row per thread
     const int quarter = warp & 3;                            // the accumulator lanes this warp may read
-    const int row = m0 + quarter * 32 + lane;
-    const bool alive = wait_barrier(done, 0);
-    if (!alive) g_tc_gemm_error = 3;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    if (alive) {
+    const int half = (warp - 2) >> 2;                        // which of every two 32-column chunks it takes
+    uint32_t local = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x, ++local) {
+      const uint32_t buffer = local & 1u, use = (local >> 1) & 1u;
+      const int m0 = (tile % token_tiles) * kTileM, n0 = (tile / token_tiles) * out_width;
+      const int row = m0 + quarter * 32 + lane;
+      if (!wait_barrier(acc_full0 + 8 * buffer, use)) { g_tc_gemm_error = 3; alive = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t lane_base = tmem_base + buffer * 256u + ((uint32_t)(quarter * 32) << 16);
+      bool released = false;
+      auto release = [&]() {                                 // this warp has read all it needs of the accumulator
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_free0 + 8 * buffer) : "memory");
+        released = true;
+      };
 #pragma unroll 1
-      for (int c0 = 0; c0 < kTileN; c0 += 32) {
+      for (int c0 = half * 32; c0 < out_width; c0 += 64) {
         float v[32];
         tmem_load_32(lane_base + c0, v);
         if (MODE == SWIGLU) {
           float u[32];
-          tmem_load_32(lane_base + kTileN + c0, u);
+          tmem_load_32(lane_base + out_width + c0, u);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + __expf(-v[i])) * u[i];
+          for (int i = 0; i < 32; ++i) v[i] = __fdividef(v[i], 1.0f + __expf(-v[i])) * u[i];
         }
+        if (c0 + 64 >= out_width) release();                 // the last columns are in registers
+        const int limit = min(n, n0 + out_width);            // columns of this tile that exist
         if (row < m) {
           if (MODE == STORE || MODE == SWIGLU) {
             bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)row * ldo + n0 + c0;
-            if (n0 + c0 + 32 <= n && (ldo % 8) == 0) {
+            if (n0 + c0 + 32 <= limit && (ldo % 8) == 0) {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
                 float b8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -258,16 +296,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
                 *reinterpret_cast<uint4*>(dst + i) = packed;
               }
             } else {
+#pragma unroll
               for (int i = 0; i < 32; ++i) {
-                if (n0 + c0 + i >= n) break;
-                float value = v[i];
-                if (MODE == STORE && bias) value += __bfloat162float(reinterpret_cast<const bf16*>(bias)[n0 + c0 + i]);
-                dst[i] = __float2bfloat16_rn(value);
+                if (n0 + c0 + i < limit) {
+                  float value = v[i];
+                  if (MODE == STORE && bias) value += __bfloat162float(reinterpret_cast<const bf16*>(bias)[n0 + c0 + i]);
+                  dst[i] = __float2bfloat16_rn(value);
+                }
               }
             }
           } else {
             float* dst = reinterpret_cast<float*>(out) + (size_t)row * ldo + n0 + c0;
-            if (n0 + c0 + 32 <= n && (ldo % 4) == 0 && bias == nullptr) {
+            if (n0 + c0 + 32 <= limit && (ldo % 4) == 0 && bias == nullptr) {
 #pragma unroll
               for (int i = 0; i < 32; i += 4) {
                 float4 value = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
@@ -277,23 +317,27 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
                 }
                 *reinterpret_cast<float4*>(dst + i) = value;
               }
-            } else
-            for (int i = 0; i < 32; ++i) {
-              if (n0 + c0 + i >= n) break;
-              float value = v[i];
-              if (bias) value += reinterpret_cast<const float*>(bias)[n0 + c0 + i];
-              dst[i] = MODE == ACCUM ? dst[i] + value : value;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                if (n0 + c0 + i < limit) {
+                  float value = v[i];
+                  if (bias) value += reinterpret_cast<const float*>(bias)[n0 + c0 + i];
+                  dst[i] = MODE == ACCUM ? dst[i] + value : value;
+                }
+              }
             }
           }
         }
       }
+      if (!released) release();                              // a tile too narrow to give this warp any columns
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLUMNS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns) : "memory");
   }
 }
 
@@ -302,15 +346,15 @@ typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, v
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 std::mutex g_mutex;
-int g_stages_swiglu = 4, g_stages_other = 6;
 EncodeTiled g_encode = nullptr;
-std::map<std::tuple<const void*, int, int, int>, CUtensorMap> g_maps;
+std::map<std::tuple<const void*, int, int, int, int>, CUtensorMap> g_maps;
+int g_forced_width = 0;                                      // for measurements: 0 = choose
 
-// Tensor map of a row-major bf16 matrix [rows, k] with row stride ld: boxes of 128 rows x 64 k, 128-byte
+// Tensor map of a row-major bf16 matrix [rows, k] with row stride ld: boxes of box_rows rows x 64 k, 128-byte
 // swizzle, out-of-range elements read as zero.
-int tensor_map_for(const void* base, int rows, int k, int ld, CUtensorMap* map) {
+int tensor_map_for(const void* base, int rows, int k, int ld, int box_rows, CUtensorMap* map) {
   std::lock_guard<std::mutex> lock(g_mutex);
-  const auto key = std::make_tuple(base, rows, k, ld);
+  const auto key = std::make_tuple(base, rows, k, ld, box_rows);
   auto found = g_maps.find(key);
   if (found != g_maps.end()) {
     *map = found->second;
@@ -328,7 +372,7 @@ int tensor_map_for(const void* base, int rows, int k, int ld, CUtensorMap* map) 
   }
   const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)kStepK, 128u};
+  const cuuint32_t box[2] = {(cuuint32_t)kStepK, (cuuint32_t)box_rows};
   const cuuint32_t element_strides[2] = {1, 1};
   CUtensorMap made;
   const CUresult status = g_encode(&made, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
@@ -345,31 +389,53 @@ int tensor_map_for(const void* base, int rows, int k, int ld, CUtensorMap* map) 
   return MIR_OK;
 }
 
+int sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) count = 148;
+  }
+  return count;
+}
+
+// Accumulator columns of a tile.  Measured on B200 (2,048 tokens, K 2,560 to 9,728): a step of K takes about
+// 0.4 us whether the tile is 192, 224 or 256 columns wide (the ring of four stages is bound by the latency of
+// its refills, not by the products), so the widest tile is the fastest even where a narrower one would fill the
+// last round of tiles better.  `columns` is the number of accumulator columns over all tiles (2 n with the
+// SwiGLU epilogue), `step` what the width must be a multiple of.
+int choose_width(long long columns, int step) {
+  if (g_forced_width >= step && g_forced_width <= 256 && g_forced_width % step == 0) return g_forced_width;
+  const long long rounded = (columns + step - 1) / step * step;
+  return (int)std::min<long long>(256, rounded);
+}
+
 template <int MODE>
 int launch(const void* x, int ldx, const void* w, const void* bias, void* out, int ldo, int m, int n, int k,
            int up_offset, cudaStream_t stream) {
-  constexpr int HALVES = MODE == SWIGLU ? 2 : 1;
-  constexpr int STAGE_BYTES = (1 + HALVES) * kBoxBytes;
+  const int token_tiles = (m + kTileM - 1) / kTileM;
+  const int width = MODE == SWIGLU ? choose_width(2ll * n, 32) : choose_width(n, 16);
+  const int out_width = MODE == SWIGLU ? width / 2 : width;
   CUtensorMap x_map, w_map;
-  int status = tensor_map_for(x, m, k, ldx, &x_map);
+  int status = tensor_map_for(x, m, k, ldx, kTileM, &x_map);
   if (status != MIR_OK) return status;
-  status = tensor_map_for(w, MODE == SWIGLU ? up_offset + n : n, k, k, &w_map);
+  status = tensor_map_for(w, MODE == SWIGLU ? up_offset + n : n, k, k, out_width, &w_map);
   if (status != MIR_OK) return status;
-  const int stages = MODE == SWIGLU ? g_stages_swiglu : g_stages_other;
-  const size_t smem = (size_t)stages * STAGE_BYTES + 1024;
+  const size_t smem = (size_t)kStages * kStageStride + 1024;
   static bool configured = false;
   if (!configured) {
-    const cudaError_t err = cudaFuncSetAttribute(tc_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 (MODE == SWIGLU ? 4 : 6) * STAGE_BYTES + 1024);
+    const cudaError_t err = cudaFuncSetAttribute(tc_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) {
       mir_set_error("tc_gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
       return MIR_CUDA_ERROR;
     }
     configured = true;
   }
-  const dim3 grid((n + kTileN - 1) / kTileN, (m + kTileM - 1) / kTileM);
+  const long long tiles = (long long)((n + out_width - 1) / out_width) * token_tiles;
+  if (tiles > 0x7fffffffll) { mir_set_error("tc_gemm: too many tiles"); return MIR_BAD_ARGUMENT; }
+  const dim3 grid((unsigned)std::min<long long>(tiles, sm_count()));
   return mir_launch("tc_gemm", tc_gemm_kernel<MODE>, grid, dim3(kThreads), smem, stream, 0, x_map, w_map, bias, out, ldo,
-                    m, n, k, up_offset, stages);
+                    m, n, k, up_offset, width, token_tiles, (int)tiles);
 }
 
 }  // namespace
@@ -382,15 +448,14 @@ MIR_EXPORT int mir_gemm_tc_error() {
   return flag;
 }
 
-// Stages of the shared-memory ring (1..4 with the SwiGLU epilogue, 1..6 otherwise).  Fewer stages let two CTAs
-// share an SM, so that one's epilogue overlaps the other's products.
-MIR_EXPORT int mir_gemm_tc_set_stages(int swiglu, int other) {
-  if (swiglu < 1 || swiglu > 4 || other < 1 || other > 6) {
-    mir_set_error("tc_gemm: stages out of range");
+// For measurements: fix the accumulator width of a tile (a multiple of 32, 32..256), or 0 to let the launcher
+// choose.
+MIR_EXPORT int mir_gemm_tc_set_width(int width) {
+  if (width != 0 && (width < 32 || width > 256 || width % 32)) {
+    mir_set_error("tc_gemm: the width must be 0 or a multiple of 32 up to 256");
     return MIR_BAD_ARGUMENT;
   }
-  g_stages_swiglu = swiglu;
-  g_stages_other = other;
+  g_forced_width = width;
   return MIR_OK;
 }
 

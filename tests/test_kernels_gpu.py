@@ -365,7 +365,8 @@ def test_few_rows_products_and_their_epilogues(m, n, k):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("m,inter,k", [(1, 333, 72), (8, 9728 // 8, 320), (40, 200, 136), (64, 176, 264), (70, 96, 64)])
+@pytest.mark.parametrize("m,inter,k", [(1, 333, 72), (8, 9728 // 8, 320), (40, 200, 136), (64, 176, 264), (70, 96, 64),
+                                       (130, 200, 136), (256, 333, 72), (300, 1216, 320)])
 def test_gate_up_silu(dtype, m, inter, k):
     from libmir_b200 import kernels
     torch.manual_seed(m + inter)
@@ -376,3 +377,44 @@ def test_gate_up_silu(dtype, m, inter, k):
     gate = plain_impl.linear(x.double(), w[:inter])
     up = plain_impl.linear(x.double(), w[inter:])
     close(out, plain_impl.silu(gate) * up, dtype, factor=2)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 328, 520), (77, 100, 72), (300, 272, 1032), (129, 48, 8),
+                                   (640, 1000, 264)])
+def test_tensor_core_product_and_its_epilogues(m, n, k):
+    """The tcgen05 product (TMA ring, accumulator in tensor memory): store with bias, accumulate into the 32-bit
+    residual, 32-bit output, a strided view as input, and the SwiGLU epilogue, at sizes that are no multiples of
+    its tiles; none of its bounded waits may have run out."""
+    from libmir_b200 import kernels
+    torch.manual_seed(m + n + k)
+    x, w = torch.randn(m, k).bfloat16(), (torch.randn(n, k) * 0.3).bfloat16()
+    exact = plain_impl.linear(x.double(), w)
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(n).bfloat16()
+    kernels.tensor_core_linear(cuda(x), cuda(w), out, cuda(bias))
+    close(out, exact + bias.double(), torch.bfloat16, factor=2)
+    base = torch.randn(m, n)
+    residual = cuda(base.clone())
+    kernels.tensor_core_linear(cuda(x), cuda(w), residual, accumulate=True)
+    close(residual, base.double() + exact, torch.float32, factor=40)       # bf16 products, 32-bit sums
+    logits = torch.empty(m, n, device="cuda")
+    float_bias = torch.randn(n)
+    kernels.tensor_core_linear(cuda(x), cuda(w), logits, cuda(float_bias))
+    close(logits, exact + float_bias.double(), torch.float32, factor=40)
+    wide = cuda(torch.randn(m, k + 40).bfloat16())
+    kernels.tensor_core_linear(wide[:, 16:16 + k], cuda(w), logits)
+    close(logits, plain_impl.linear(wide[:, 16:16 + k].double().cpu(), w), torch.float32, factor=40)
+    if n % 2 == 0:
+        inter = n // 2
+        gated = torch.empty(m, inter, device="cuda", dtype=torch.bfloat16)
+        kernels.tensor_core_linear(cuda(x), cuda(w), gated, swiglu=True)
+        close(gated, plain_impl.silu(exact[:, :inter]) * exact[:, inter:], torch.bfloat16, factor=2)
+    assert kernels.tensor_core_linear_error() == 0
+
+
+def test_tensor_core_product_refuses_what_it_cannot_take():
+    from libmir_b200 import kernels
+    from libmir_b200.errors import KernelError
+    x, w = cuda(torch.randn(128, 20).bfloat16()), cuda(torch.randn(64, 20).bfloat16())
+    with pytest.raises(KernelError, match="multiples of 8"):
+        kernels.tensor_core_linear(x, w, torch.empty(128, 64, device="cuda", dtype=torch.bfloat16))
