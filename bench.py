@@ -126,6 +126,9 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--skip-points", action="store_true", help="only the batch-8 decode and the prefill")
+    parser.add_argument("--no-fold-norm", action="store_true",
+                        help="run every RMSNorm as a kernel of its own instead of folding it into the few-rows "
+                             "products around it")
     parser.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
                         help="decode / prefill: run only that phase, bracketed by cudaProfilerStart/Stop (for ncu "
                              "--profile-from-start off); the JSON line then holds only that phase")
@@ -156,6 +159,8 @@ def main() -> int:
         kernels.SKINNY_MODES -= set(args.library_modes.split(","))
     if args.pdl is not None:
         kernels.set_programmatic_launch(bool(args.pdl))
+    if args.no_fold_norm:
+        kernels.FUSE_NORM_INTO_PRODUCT = False
     peaks, peaks_kind = read_peaks()
     config = dict(QWEN3_4B)
     layers_full = config["num_hidden_layers"]
@@ -277,9 +282,12 @@ def main() -> int:
     prefill_flops = gemm_flops + attention_flops
 
     if args.phase == "decode":
+        device_value, device_ms, launches, _, _ = decode_device(args.batch, args.steps, args.warmup)
         tokens_per_second, _, _ = decode_e2e(args.batch, args.steps, args.warmup, profile=True)
         print(json.dumps({"phase": "decode", "batch": args.batch, "steps": args.steps, "layers": layers,
-                          "graphs": not args.no_graphs, "tokens_per_second": round(tokens_per_second, 1)}))
+                          "graphs": not args.no_graphs, "tokens_per_second": round(tokens_per_second, 1),
+                          "device_tokens_per_second": round(device_value, 1), "device_ms_per_step": round(device_ms, 4),
+                          "launches_per_step": launches / max(1, args.steps)}))
         return 0
     if args.phase == "prefill":
         ms = prefill(repeats=max(1, min(args.steps, 5)), profile=True)

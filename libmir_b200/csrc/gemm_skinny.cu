@@ -61,15 +61,21 @@ __device__ __forceinline__ uint4 load_cached(const bf16* p, bool valid) {
   return v;
 }
 
-// Optional fusion of the RMSNorm before (residual != nullptr) or after (sumsq_out != nullptr) the product.
+// Optional fusion of an RMSNorm into the products around it, without work in the inner loop:
+//   - an accumulating product (it updates the residual r) also writes, per 16-column tile and token, the sum of
+//     squares of the new values (`sumsq_out`), and the new values times the NEXT norm's weight, rounded to bf16
+//     (`weighted_out` = bf16(r * g));
+//   - the product after that norm takes `weighted_out` as its x and multiplies each token's results by
+//     rsqrt(sum of squares / k + eps) (`sumsq`): W (r g s) = s W (r g), since s is one number per token.
+// Each value is rounded to bf16 once, as when the norm runs as a kernel of its own.
 struct NormFusion {
-  const float* residual;   // [m, ld_residual] 32-bit input to normalise instead of x
-  int ld_residual;
-  const float* weight;     // [k] norm weight
-  float eps;
-  const float* sumsq;      // [sumsq_tiles][16]: partial sums of squares of the residual's rows
+  const float* sumsq;        // consumer: [sumsq_tiles][16] partial sums of squares of x's rows before weighting
   int sumsq_tiles;
-  float* sumsq_out;        // ACCUM: [tiles][16] partial sums of squares of the rows this product updates
+  float eps;
+  float* sumsq_out;          // producer (ACCUM): [tiles][16] partial sums of squares of the rows it updates
+  const float* next_weight;  // producer: [n] weight of the norm that follows, or null
+  bf16* weighted_out;        // producer: [m, ld_weighted] bf16(new residual * next_weight)
+  int ld_weighted;
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -79,7 +85,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 // RS row sets of 16 rows of w per warp (for SWIGLU: RS/2 gate sets then RS/2 up sets), NT tiles of 8 tokens,
 // U blocks of 32 k loaded before their products are issued.
-template <int RS, int NT, int U, int MODE, bool FUSED>
+template <int RS, int NT, int U, int MODE>
 __global__ void __launch_bounds__(kWarps * 32)
 skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, const void* __restrict__ bias,
                    void* __restrict__ out, int ldo, int m, int n, int k, int up_offset, NormFusion norm) {
@@ -125,21 +131,6 @@ skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
     for (int nt = 0; nt < NT; ++nt) acc[rs][nt][0] = acc[rs][nt][1] = acc[rs][nt][2] = acc[rs][nt][3] = 0.0f;
 
   grid_dependency_wait();                                  // x and out belong to the kernels before this one
-  constexpr bool fused_norm = FUSED;           // compiled apart: the plain product keeps its registers
-  if (fused_norm) {
-    // 16 threads per token add the tiles' partial sums in a fixed order
-    const int token = threadIdx.x >> 4, part = threadIdx.x & 15;
-    float sum = 0.0f;
-    if (token < m)
-      for (int tile = part; tile < norm.sumsq_tiles; tile += 16) sum += norm.sumsq[tile * 16 + token];
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (part == 0) inverse_rms[token] = rsqrtf(sum / (float)k + norm.eps);
-    __syncthreads();
-  }
-  float inv[NT];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) inv[nt] = fused_norm ? inverse_rms[nt * 8 + group] : 1.0f;
   const int blocks = (k + 31) / 32;
   const int per_split = (blocks + splits - 1) / splits;
   const int block_begin = split * per_split, block_end = min(blocks, block_begin + per_split);
@@ -155,31 +146,8 @@ skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
         a_lo[u][rs] = load_stream(w_lo[rs] + offset, in_k && ok_lo[rs]);
         a_hi[u][rs] = load_stream(w_hi[rs] + offset, in_k && ok_hi[rs]);
       }
-      if (!fused_norm) {
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) b[u][nt] = load_cached(x_row[nt] + offset, in_k && ok_x[nt]);
-      } else {
-        // normalise 8 values of the 32-bit residual: x * rsqrt(mean(x^2) + eps) * weight, rounded to bf16
-        float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
-        if (in_k) {
-          w0 = __ldg(reinterpret_cast<const float4*>(norm.weight + offset + quad * 8));
-          w1 = __ldg(reinterpret_cast<const float4*>(norm.weight + offset + quad * 8 + 4));
-        }
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          b[u][nt] = make_uint4(0u, 0u, 0u, 0u);
-          if (in_k && ok_x[nt]) {
-            const float* row = norm.residual + (size_t)(nt * 8 + group) * norm.ld_residual + offset + quad * 8;
-            const float4 r0 = __ldg(reinterpret_cast<const float4*>(row));
-            const float4 r1 = __ldg(reinterpret_cast<const float4*>(row + 4));
-            const float s = inv[nt];
-            b[u][nt].x = pack2(r0.x * s * w0.x, r0.y * s * w0.y);
-            b[u][nt].y = pack2(r0.z * s * w0.z, r0.w * s * w0.w);
-            b[u][nt].z = pack2(r1.x * s * w1.x, r1.y * s * w1.y);
-            b[u][nt].w = pack2(r1.z * s * w1.z, r1.w * s * w1.w);
-          }
-        }
-      }
+      for (int nt = 0; nt < NT; ++nt) b[u][nt] = load_cached(x_row[nt] + offset, in_k && ok_x[nt]);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u)
@@ -192,6 +160,19 @@ skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
         }
   }
 
+  // one scale per token: 1, or the folded norm's rsqrt(mean of squares + eps); read after the syncs below
+  if (threadIdx.x < 16) inverse_rms[threadIdx.x] = 1.0f;
+  if (norm.sumsq != nullptr) {
+    // 16 threads per token add the tiles' partial sums in a fixed order
+    __syncthreads();
+    const int token = threadIdx.x >> 4, part = threadIdx.x & 15;
+    float sum = 0.0f;
+    if (token < m)
+      for (int tile = part; tile < norm.sumsq_tiles; tile += 16) sum += norm.sumsq[tile * 16 + token];
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (part == 0 && token < 16) inverse_rms[token] = rsqrtf(sum / (float)k + norm.eps);
+  }
   // partial sums of the 8 warps -> shared memory -> one sum per CTA
   float* mine = shared + (size_t)warp * PARTIAL;
 #pragma unroll
@@ -231,6 +212,9 @@ skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
           value += peer[at];
           if (MODE == SWIGLU) other += peer[at + SETS * 16 * TOKENS];
         }
+        const float scale = inverse_rms[token];              // 1 unless a norm is folded into this product
+        value *= scale;
+        other *= scale;
         if (MODE == SWIGLU) {
           reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
               __float2bfloat16_rn(value / (1.0f + expf(-value)) * other);
@@ -242,6 +226,9 @@ skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
           float* dst = reinterpret_cast<float*>(out) + (size_t)token * ldo + column;
           value = MODE == ACCUM ? *dst + value : value;
           *dst = value;
+          if (MODE == ACCUM && norm.weighted_out != nullptr)
+            norm.weighted_out[(size_t)token * norm.ld_weighted + column] =
+                __float2bfloat16_rn(value * norm.next_weight[column]);
         }
       }
       if (MODE == ACCUM && norm.sumsq_out != nullptr) {
@@ -258,7 +245,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
 
 constexpr int kTargetCtas = 4 * 148;
 
-template <int RS, int NT, int U, int MODE, bool FUSED>
+template <int RS, int NT, int U, int MODE>
 int launch(const bf16* x, int ldx, const bf16* w, const void* bias, void* out, int ldo, int m, int n, int k,
            int up_offset, const NormFusion& norm, cudaStream_t stream) {
   constexpr int SETS = MODE == SWIGLU ? RS / 2 : RS;
@@ -267,32 +254,19 @@ int launch(const bf16* x, int ldx, const bf16* w, const void* bias, void* out, i
   const int blocks = (k + 31) / 32;
   int splits = 1;                                          // cut K over a cluster until the GPU is full
   while (splits < 8 && tiles * splits < kTargetCtas && blocks / (splits * 2 * kWarps) >= 2) splits *= 2;
-  return mir_launch("skinny_gemm", skinny_gemm_kernel<RS, NT, U, MODE, FUSED>, dim3(tiles, splits, 1), dim3(kWarps * 32), smem,
+  return mir_launch("skinny_gemm", skinny_gemm_kernel<RS, NT, U, MODE>, dim3(tiles, splits, 1), dim3(kWarps * 32), smem,
                     stream, splits, x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm);
 }
 
 template <int MODE>
 int dispatch(const bf16* x, int ldx, const bf16* w, const void* bias, void* out, int ldo, int m, int n, int k,
              int up_offset, const NormFusion& norm, cudaStream_t stream) {
-  const bool fused = norm.residual != nullptr;
   if (MODE == SWIGLU) {                          // two row sets (gate, up) per output set
-    if (fused) {
-      if (m <= 8) return launch<2, 1, 4, MODE, true>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
-      return launch<2, 2, 2, MODE, true>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
-    }
-    if (m <= 8) return launch<2, 1, 4, MODE, false>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
-    return launch<2, 2, 4, MODE, false>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
+    if (m <= 8) return launch<2, 1, 4, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
+    return launch<2, 2, 4, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
   }
-  if (fused && MODE == STORE) {
-    if (m <= 8) return launch<1, 1, 4, MODE, true>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
-    return launch<1, 2, 4, MODE, true>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
-  }
-  if (fused) {
-    mir_set_error("skinny_gemm: the fused norm input is built for the store and SwiGLU epilogues");
-    return MIR_BAD_ARGUMENT;
-  }
-  if (m <= 8) return launch<1, 1, 8, MODE, false>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
-  return launch<1, 2, 8, MODE, false>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
+  if (m <= 8) return launch<1, 1, 8, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
+  return launch<1, 2, 8, MODE>(x, ldx, w, bias, out, ldo, m, n, k, up_offset, norm, stream);
 }
 
 }  // namespace
@@ -302,36 +276,41 @@ MIR_EXPORT int mir_skinny_gemm_max_rows() { return 16; }
 // mode: 0 out bf16 = x w^T (+bias bf16); 1 out float += x w^T (+bias float); 2 out float = x w^T (+bias float);
 // 3 out bf16 [m, n] = silu(x w[0:n]^T) * (x w[up_offset : up_offset + n]^T).
 // Needs m <= 16, k a multiple of 8, ldx a multiple of 8, and x and w on 16-byte boundaries.
-// Norm fusion (all optional, see NormFusion): with `residual` the input is rmsnorm(residual) * norm_weight
-// computed on the fly from the partial sums `sumsq` [sumsq_tiles][16] (x is then ignored and may be null);
-// with `sumsq_out` (mode 1 only) the product also writes the partial sums of squares of the rows it updates,
-// [ceil(n / 16)][16] floats.
+// Norm fusion (all optional, see NormFusion): with `sumsq` [sumsq_tiles][16] each token's results are
+// multiplied by rsqrt(sum / k + eps) (modes 0 and 3); with `sumsq_out` (mode 1 only) the product also writes the
+// partial sums of squares of the rows it updates, [ceil(n / 16)][16] floats, and with `weighted_out` and
+// `next_weight` the new rows times that weight as bf16.
 MIR_EXPORT int mir_gemm_skinny_bf16(int mode, const void* x, int ldx, const void* w, const void* bias, void* out,
-                                    int ldo, int m, int n, int k, int up_offset, const float* residual,
-                                    int ld_residual, const float* norm_weight, float eps, const float* sumsq,
-                                    int sumsq_tiles, float* sumsq_out, cudaStream_t stream) {
+                                    int ldo, int m, int n, int k, int up_offset, const float* sumsq, int sumsq_tiles,
+                                    float eps, float* sumsq_out, const float* next_weight, void* weighted_out,
+                                    int ld_weighted, cudaStream_t stream) {
   if (m == 0 || n == 0) return MIR_OK;
-  const bool fused = residual != nullptr;
-  if (m < 0 || m > 16 || n < 0 || k <= 0 || (k % 8) || ldo < n || ((uintptr_t)w & 15) ||
-      (!fused && ((ldx % 8) || ldx < k || ((uintptr_t)x & 15) || x == nullptr)) ||
-      (fused && ((ld_residual % 4) || ld_residual < k || ((uintptr_t)residual & 15) || norm_weight == nullptr ||
-                 ((uintptr_t)norm_weight & 15) || sumsq == nullptr || sumsq_tiles <= 0))) {
+  if (m < 0 || m > 16 || n < 0 || k <= 0 || (k % 8) || ldo < n || ((uintptr_t)w & 15) || (ldx % 8) || ldx < k ||
+      ((uintptr_t)x & 15) || x == nullptr) {
     mir_set_error("skinny_gemm: needs 1..16 rows, k and the row stride multiples of 8 and 16-byte aligned operands "
-                  "(m %d n %d k %d ldx %d ldo %d, fused norm %d)", m, n, k, ldx, ldo, (int)fused);
+                  "(m %d n %d k %d ldx %d ldo %d)", m, n, k, ldx, ldo);
     return MIR_BAD_ARGUMENT;
   }
-  if (sumsq_out != nullptr && mode != ACCUM) {
-    mir_set_error("skinny_gemm: sums of squares are written by the accumulate epilogue only");
+  if ((sumsq_out != nullptr || weighted_out != nullptr) && mode != ACCUM) {
+    mir_set_error("skinny_gemm: sums of squares and weighted rows are written by the accumulate epilogue only");
+    return MIR_BAD_ARGUMENT;
+  }
+  if (sumsq != nullptr && (sumsq_tiles <= 0 || (mode != STORE && mode != SWIGLU))) {
+    mir_set_error("skinny_gemm: a folded norm needs its partial sums, and the store or SwiGLU epilogue");
+    return MIR_BAD_ARGUMENT;
+  }
+  if (weighted_out != nullptr && (next_weight == nullptr || sumsq_out == nullptr || ld_weighted < n)) {
+    mir_set_error("skinny_gemm: weighted rows need the next norm's weight, a row stride >= n, and sums of squares");
     return MIR_BAD_ARGUMENT;
   }
   NormFusion norm;
-  norm.residual = residual;
-  norm.ld_residual = ld_residual;
-  norm.weight = norm_weight;
-  norm.eps = eps;
   norm.sumsq = sumsq;
   norm.sumsq_tiles = sumsq_tiles;
+  norm.eps = eps;
   norm.sumsq_out = sumsq_out;
+  norm.next_weight = next_weight;
+  norm.weighted_out = (bf16*)weighted_out;
+  norm.ld_weighted = ld_weighted;
   const bf16* xx = (const bf16*)x;
   const bf16* ww = (const bf16*)w;
   switch (mode) {

@@ -92,21 +92,52 @@ class StepContext:
     max_portion: int = 0
     decode_only: bool = False
     page_size: int = 0
-    residual_stats: Optional[tuple] = None     # (residual data_ptr, rows, sums-of-squares tensor, tiles) or None
+    # (residual data_ptr, rows, sums-of-squares tensor, tiles, weighted rows, norm weight data_ptr) or None
+    residual_stats: Optional[tuple] = None
+    # The norm that will be applied to the residual right after the part that runs now has added into it (set by
+    # the block), and the one that the next block in the schedule starts with (set by the model); None if unknown.
+    upcoming_norm: Optional[object] = None
+    norm_after_block: Optional[object] = None
 
     def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
         return self.arena.alloc(shape, dtype)
 
-    def note_residual_stats(self, residual: torch.Tensor, sumsq: Optional[torch.Tensor], tiles: int) -> None:
-        """Remember (or forget, with None) that `sumsq` holds the sums of squares of `residual` as it is now.
-        Whoever changes the residual calls this; a norm may then be fused into the product that follows."""
-        self.residual_stats = None if sumsq is None else (residual.data_ptr(), residual.shape[0], sumsq, tiles)
+    def note_residual_stats(self, residual: torch.Tensor, sumsq: Optional[torch.Tensor], tiles: int,
+                            weighted: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None) -> None:
+        """Remember (or forget, with None) that `sumsq` holds the sums of squares of `residual` as it is now and
+        `weighted` its rows times `norm_weight`.  Whoever changes the residual calls this; the norm with that
+        weight may then be folded into the product that follows it."""
+        if sumsq is None or weighted is None or norm_weight is None:
+            self.residual_stats = None
+        else:
+            self.residual_stats = (residual.data_ptr(), residual.shape[0], sumsq, tiles, weighted,
+                                   norm_weight.data_ptr())
 
-    def stats_for(self, residual: torch.Tensor):
+    def stats_for(self, residual: torch.Tensor, norm_weight: torch.Tensor):
         stats = self.residual_stats
-        if stats is not None and stats[0] == residual.data_ptr() and stats[1] == residual.shape[0]:
-            return stats[2], stats[3]
+        if (stats is not None and stats[0] == residual.data_ptr() and stats[1] == residual.shape[0]
+                and stats[5] == norm_weight.data_ptr()):
+            return stats[2], stats[3], stats[4]
         return None
+
+    def accumulate_with_stats(self, x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor,
+                              bias: Optional[torch.Tensor] = None) -> None:
+        """residual += x . weight^T (+ bias).  If a norm is known to follow (`upcoming_norm`, with a float32
+        `weight` and a `foldable` flag) and the product can do it, it also leaves what that norm needs to be
+        folded into the next product."""
+        norm = self.upcoming_norm
+        norm_weight = getattr(norm, "weight", None) if getattr(norm, "foldable", False) else None
+        if (not kernels.FUSE_NORM_INTO_PRODUCT or norm_weight is None or self.dtype != torch.bfloat16
+                or residual.shape[0] > kernels.SKINNY_MAX_ROWS or norm_weight.numel() != residual.shape[1]):
+            kernels.linear(x, weight, residual, bias, accumulate=True)
+            self.residual_stats = None
+            return
+        tiles = kernels.sumsq_tiles(residual.shape[1])
+        sumsq = self.alloc((tiles, 16), torch.float32)
+        weighted = self.alloc(tuple(residual.shape), torch.bfloat16)
+        wrote = kernels.linear(x, weight, residual, bias, accumulate=True, sumsq_out=sumsq,
+                               weighted_out=(weighted, norm_weight))
+        self.note_residual_stats(residual, sumsq if wrote else None, tiles, weighted, norm_weight)
 
     def cache_view(self, entry: int):
         return self.views.get(entry)

@@ -47,7 +47,7 @@ _SIGNATURES = {
         "mir_prefill_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "mir_gemm_skinny_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                 c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p],
+                                 c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mir_gemm_tc_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_void_p],
         "mir_gemm_tc_set_width": [c_int],
@@ -98,10 +98,10 @@ def loaded_libraries() -> dict:
     return {name: lib._name for name, lib in _LIBS.items()}
 
 
-# Whether an RMSNorm may be left to the few-rows product that follows it (NormedResidual).  Measured on B200 at
-# Qwen3-4B sizes, 8 rows: 73 kernels fewer per step but the step takes 4.19 ms instead of 3.81 ms (the on-the-fly
-# normalisation reads 32-bit values and costs the product more than the norm kernel it saves), so it is off.
-FUSE_NORM_INTO_PRODUCT = False
+# Whether an RMSNorm between two few-rows products is folded into them (NormedResidual): the product before it
+# leaves the sums of squares and the weighted rows, the product after it scales its results.  Two kernels fewer
+# per layer in a decode step.
+FUSE_NORM_INTO_PRODUCT = True
 LAUNCHES = 0        # kernels (and library matrix products) launched through this module, for reports
 
 
@@ -336,14 +336,16 @@ def _lt_workspace(device) -> torch.Tensor:
 
 
 class NormedResidual:
-    """RMSNorm of the 32-bit residual stream that has not been computed yet: the few-rows products take it as
-    their input and normalise the values as they read them (one kernel less per norm).  `sumsq` holds, per
-    16-column tile of the residual and per token, the sum of squares that the product which last updated the
-    residual wrote.  Anything else that needs the normed rows calls `materialize`."""
+    """An RMSNorm of the 32-bit residual stream that is folded into the few-rows products around it.
+    `weighted` holds bf16(residual * norm weight) and `sumsq`, per 16-column tile of the residual and per token,
+    the sum of squares; both were written by the product that last updated the residual.  The product that takes
+    this as its x multiplies each token's results by rsqrt(mean of squares + eps).  Anything else that needs the
+    normed rows calls `materialize`."""
 
     def __init__(self, residual: torch.Tensor, weight: torch.Tensor, eps: float, sumsq: torch.Tensor, tiles: int,
-                 dtype: torch.dtype):
+                 dtype: torch.dtype, weighted: torch.Tensor):
         self.residual, self.weight, self.eps, self.sumsq, self.tiles, self.dtype = residual, weight, eps, sumsq, tiles, dtype
+        self.weighted = weighted
         self.shape = residual.shape
 
     def materialize(self, alloc) -> torch.Tensor:
@@ -358,31 +360,33 @@ def sumsq_tiles(columns: int) -> int:
 
 
 def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           accumulate: bool = False, sumsq_out: Optional[torch.Tensor] = None, alloc=None) -> bool:
+           accumulate: bool = False, sumsq_out: Optional[torch.Tensor] = None, alloc=None,
+           weighted_out: Optional[tuple] = None) -> bool:
     """out = (out if accumulate) + x . weight^T (+ bias).
 
     float32 tensors: the 32-bit FMA kernel.  bfloat16 x and weight: up to 16 rows run the weight-streaming
     kernel, more run cuBLASLt, both with 32-bit accumulation; out is bfloat16 or float32.  x and out may be
     row-strided views; weight is [out_features, in_features].  x may be a NormedResidual (then `alloc` must be
     given in case it has to be materialised).  With `sumsq_out` (float32 [ceil(N / 16), 16]) an accumulating
-    few-rows product also writes the sums of squares of the rows it updates; the return value says whether it
-    did."""
+    few-rows product also writes the sums of squares of the rows it updates, and with
+    `weighted_out` = (bfloat16 [M, N], float32 norm weight [N]) those rows times the weight; the return value
+    says whether it did."""
     lazy = x if isinstance(x, NormedResidual) else None
     if lazy is not None:
         m, k = lazy.shape
+        xw = lazy.weighted
         fits = (weight.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and not accumulate
-                and 0 < m <= SKINNY_MAX_ROWS and k % 8 == 0 and "store" in SKINNY_MODES
-                and lazy.residual.stride(0) % 4 == 0)
+                and "store" in SKINNY_MODES and _skinny_ok(xw, m, k))
         if fits:
-            _cuda(lazy.residual, weight, out, bias)
+            _cuda(xw, weight, out, bias, lazy.sumsq)
             n = weight.shape[0]
-            _require(weight.shape[1] == k and out.shape == (m, n) and out.stride(1) == 1 and weight.is_contiguous(),
-                     "linear: shapes or strides do not fit")
+            _require(weight.shape[1] == k and out.shape == (m, n) and out.stride(1) == 1 and weight.is_contiguous()
+                     and xw.shape == (m, k) and xw.stride(1) == 1, "linear: shapes or strides do not fit")
             lib = library("bf16")
-            _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_STORE, None, 0, weight.data_ptr(), _ptr(bias), out.data_ptr(),
-                                                 out.stride(0), m, n, k, 0, lazy.residual.data_ptr(),
-                                                 lazy.residual.stride(0), lazy.weight.data_ptr(), lazy.eps,
-                                                 lazy.sumsq.data_ptr(), lazy.tiles, None, _stream()))
+            _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_STORE, xw.data_ptr(), xw.stride(0), weight.data_ptr(),
+                                                 _ptr(bias), out.data_ptr(), out.stride(0), m, n, k, 0,
+                                                 lazy.sumsq.data_ptr(), lazy.tiles, lazy.eps, None, None, None, 0,
+                                                 _stream()))
             return False
         x = lazy.materialize(alloc)
     _cuda(x, weight, out, bias)
@@ -409,9 +413,16 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
         mode = SKINNY_STORE if out.dtype == torch.bfloat16 else (SKINNY_ACCUM if accumulate else SKINNY_F32)
         stats = sumsq_out if (mode == SKINNY_ACCUM and sumsq_out is not None
                               and sumsq_out.numel() >= sumsq_tiles(n) * 16) else None
+        rows, next_weight = weighted_out if (stats is not None and weighted_out is not None) else (None, None)
+        if rows is not None:
+            _cuda(rows, next_weight)
+            _require(rows.dtype == torch.bfloat16 and rows.shape == (m, n) and rows.stride(1) == 1
+                     and next_weight.dtype == torch.float32 and next_weight.numel() == n
+                     and next_weight.is_contiguous(), "linear: weighted rows are bfloat16 [M, N], the weight float32 [N]")
         _check(lib, lib.mir_gemm_skinny_bf16(mode, x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias),
-                                             out.data_ptr(), out.stride(0), m, n, k, 0, None, 0, None, 0.0, None, 0,
-                                             _ptr(stats), _stream()))
+                                             out.data_ptr(), out.stride(0), m, n, k, 0, None, 0, 0.0, _ptr(stats),
+                                             _ptr(next_weight), _ptr(rows), rows.stride(0) if rows is not None else 0,
+                                             _stream()))
         return stats is not None
     workspace = _lt_workspace(x.device)
     _check(lib, lib.mir_gemm_bf16_lt(x.data_ptr(), x.stride(0), weight.data_ptr(), k, _ptr(bias), out.data_ptr(),
@@ -474,8 +485,8 @@ def _skinny_ok(x: torch.Tensor, m: int, k: int) -> bool:
 def gate_up_silu(x, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -> None:
     """out[M, I] = silu(x w_gate^T) * (x w_up^T) with w_gate_up = [w_gate; w_up] of shape [2 I, K].
 
-    Up to 16 bfloat16 rows (the weight-streaming kernel; x may be a NormedResidual that is normalised on the
-    fly) and from TENSOR_CORE_MIN_ROWS bfloat16 rows (the tcgen05 kernel): one kernel, the [M, 2 I] intermediate is never written.
+    Up to 16 bfloat16 rows (the weight-streaming kernel; x may be a NormedResidual, a norm folded into this
+    product) and from TENSOR_CORE_MIN_ROWS bfloat16 rows (the tcgen05 kernel): one kernel, the [M, 2 I] intermediate is never written.
     Otherwise the product (library or 32-bit kernel) followed by the SiLU-multiply kernel;
     `scratch_alloc(shape, dtype)` provides the intermediate."""
     lazy = x if isinstance(x, NormedResidual) else None
@@ -485,13 +496,14 @@ def gate_up_silu(x, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -
              and w_gate_up.is_contiguous(), "gate_up_silu: shapes do not fit")
     few = (w_gate_up.dtype == torch.bfloat16 and 0 < m <= SKINNY_MAX_ROWS and k % 8 == 0 and "swiglu" in SKINNY_MODES)
     if lazy is not None:
-        if few and lazy.residual.stride(0) % 4 == 0:
-            _cuda(lazy.residual, w_gate_up, out)
+        xw = lazy.weighted
+        if few and _skinny_ok(xw, m, k):
+            _cuda(xw, w_gate_up, out, lazy.sumsq)
             lib = library("bf16")
-            _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_SWIGLU, None, 0, w_gate_up.data_ptr(), None, out.data_ptr(),
-                                                 out.stride(0), m, inter, k, inter, lazy.residual.data_ptr(),
-                                                 lazy.residual.stride(0), lazy.weight.data_ptr(), lazy.eps,
-                                                 lazy.sumsq.data_ptr(), lazy.tiles, None, _stream()))
+            _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_SWIGLU, xw.data_ptr(), xw.stride(0), w_gate_up.data_ptr(), None,
+                                                 out.data_ptr(), out.stride(0), m, inter, k, inter,
+                                                 lazy.sumsq.data_ptr(), lazy.tiles, lazy.eps, None, None, None, 0,
+                                                 _stream()))
             return
         x = lazy.materialize(scratch_alloc)
     _cuda(x, w_gate_up, out)
@@ -499,8 +511,8 @@ def gate_up_silu(x, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -
     if few and x.dtype == torch.bfloat16 and _skinny_ok(x, m, k):
         lib = library("bf16")
         _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_SWIGLU, x.data_ptr(), x.stride(0), w_gate_up.data_ptr(), None,
-                                             out.data_ptr(), out.stride(0), m, inter, k, inter, None, 0, None, 0.0,
-                                             None, 0, None, _stream()))
+                                             out.data_ptr(), out.stride(0), m, inter, k, inter, None, 0, 0.0, None,
+                                             None, None, 0, _stream()))
         return
     if (x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and m >= TENSOR_CORE_MIN_ROWS
             and _tensor_core_ok(x, k)):

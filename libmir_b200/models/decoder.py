@@ -111,6 +111,11 @@ class DecoderModel:
         residual = ctx.alloc((ctx.num_tokens, spec.hidden_size), torch.float32)
         kernels.embed(self.embedding, ctx.tokens, residual, spec.embedding.multiplier)
         for index, entry in enumerate(spec.schedule):
+            if hasattr(ctx, "norm_after_block"):
+                # the norm that the next block in the schedule starts with: this block's last product may prepare it
+                following = (self.blocks[spec.schedule[index + 1].layer] if index + 1 < len(spec.schedule) else None)
+                first_norm = getattr(following, "first_norm", None)
+                ctx.norm_after_block = first_norm() if first_norm is not None else None
             self.blocks[entry.layer].forward(ctx, ctx.cache_view(index), residual)
         return residual
 

@@ -82,16 +82,11 @@ class SoftmaxAttention(Mixer):
             self.position.rotary_dim if self.position is not None else 0, s.qk_norm_eps, write_kv=cache.writes)
         mixed = ctx.alloc((tokens, self.q_width), self.env.dtype)
         self.attend(ctx, group, cache, qkv, mixed)
-        note = getattr(ctx, "note_residual_stats", None)
-        if note is None:
+        accumulate = getattr(ctx, "accumulate_with_stats", None)
+        if accumulate is None:
             kernels.linear(mixed, self.w_o, residual, self.b_o, accumulate=True)
         else:
-            # a few-rows product also leaves the sums of squares of the new residual, so that the next norm
-            # can be computed inside the product that follows it
-            tiles = kernels.sumsq_tiles(s.hidden_size)
-            sumsq = ctx.alloc((tiles, 16), torch.float32)
-            wrote = kernels.linear(mixed, self.w_o, residual, self.b_o, accumulate=True, sumsq_out=sumsq)
-            note(residual, sumsq if wrote else None, tiles)
+            accumulate(mixed, self.w_o, residual, self.b_o)      # may also prepare the norm that follows
 
     def attend(self, ctx, group, cache, qkv, out):
         """Attention of every packed row over its request's pages; the kernel is chosen by dtype and size:

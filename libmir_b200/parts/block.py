@@ -29,18 +29,32 @@ class PreNormBlock(Block):
     def cache_requirement(self):
         return self.mixer.cache_requirement()
 
+    def first_norm(self):
+        """The norm this block applies to the incoming residual before anything else, or None."""
+        return self.mixer_norm
+
     def forward(self, ctx, cache, residual):
-        # A part that sets `takes_normed_residual` accepts a kernels.NormedResidual as x (a norm that its first
-        # product computes on the fly); every other part gets the normed tensor.
+        # A part that sets `takes_normed_residual` accepts a kernels.NormedResidual as x (a norm folded into the
+        # products around it); every other part gets the normed tensor.  Before a part runs, the context is told
+        # which norm follows it, so that its last product can prepare that norm.
+        after = getattr(ctx, "norm_after_block", None)
         x = (self._norm(self.mixer_norm, self.mixer, ctx, residual) if self.mixer_norm is not None
              else ctx.cast_residual(residual))
         self._forget_stats(ctx)              # the mixer changes the residual; it may note new sums of squares
+        self._announce(ctx, self.feed_forward_norm if self.feed_forward is not None else after)
         self.mixer.forward(ctx, cache, x, residual)
         if self.feed_forward is not None:
             x = (self._norm(self.feed_forward_norm, self.feed_forward, ctx, residual)
                  if self.feed_forward_norm is not None else ctx.cast_residual(residual))
             self._forget_stats(ctx)
+            self._announce(ctx, after)
             self.feed_forward.forward(ctx, x, residual)
+        self._announce(ctx, None)
+
+    @staticmethod
+    def _announce(ctx, norm):
+        if hasattr(ctx, "upcoming_norm"):
+            ctx.upcoming_norm = norm
 
     @staticmethod
     def _forget_stats(ctx):

@@ -41,13 +41,8 @@ class SwiGlu(FeedForward):
         tokens = x.shape[0]
         hidden = ctx.alloc((tokens, s.intermediate_size), self.env.dtype)
         kernels.gate_up_silu(x, self.w_gate_up, hidden, ctx.alloc)
-        note = getattr(ctx, "note_residual_stats", None)
-        if note is None:
+        accumulate = getattr(ctx, "accumulate_with_stats", None)
+        if accumulate is None:
             kernels.linear(hidden, self.w_down, residual, accumulate=True)
         else:
-            # a few-rows product also leaves the sums of squares of the new residual, so that the next norm
-            # can be computed inside the product that follows it
-            tiles = kernels.sumsq_tiles(s.hidden_size)
-            sumsq = ctx.alloc((tiles, 16), torch.float32)
-            wrote = kernels.linear(hidden, self.w_down, residual, accumulate=True, sumsq_out=sumsq)
-            note(residual, sumsq if wrote else None, tiles)
+            accumulate(hidden, self.w_down, residual)            # may also prepare the norm that follows

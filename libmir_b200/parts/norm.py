@@ -16,6 +16,8 @@ from .base import Norm
 
 
 class RmsNorm(Norm):
+    foldable = True       # y = x * s * w with one s per row: the products around it can take it over
+
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.weight: Optional[torch.Tensor] = None
@@ -30,13 +32,15 @@ class RmsNorm(Norm):
         return self.weight.numel() * 4
 
     def forward(self, ctx, x, out=None, rows=None, lazy=False):
-        """`lazy`: the caller's next product can normalise on the fly; if the sums of squares of x are at hand
-        (written by the product that last added into it), return a NormedResidual instead of running a kernel."""
+        """`lazy`: the caller's next product can take over this norm; if what it needs is at hand (the sums of
+        squares of x and its rows times this norm's weight, written by the product that last added into x),
+        return a NormedResidual instead of running a kernel."""
         if (lazy and kernels.FUSE_NORM_INTO_PRODUCT and out is None and rows is None
                 and self.env.dtype == torch.bfloat16):
-            stats = ctx.stats_for(x) if hasattr(ctx, "stats_for") else None
+            stats = ctx.stats_for(x, self.weight) if hasattr(ctx, "stats_for") else None
             if stats is not None:
-                return kernels.NormedResidual(x, self.weight, self.spec.eps, stats[0], stats[1], self.env.dtype)
+                return kernels.NormedResidual(x, self.weight, self.spec.eps, stats[0], stats[1], self.env.dtype,
+                                              stats[2])
         n_rows = x.shape[0] if rows is None else rows.numel()
         if out is None:
             out = ctx.alloc((n_rows, self.spec.size), self.env.dtype)

@@ -418,3 +418,46 @@ def test_tensor_core_product_refuses_what_it_cannot_take():
     x, w = cuda(torch.randn(128, 20).bfloat16()), cuda(torch.randn(64, 20).bfloat16())
     with pytest.raises(KernelError, match="multiples of 8"):
         kernels.tensor_core_linear(x, w, torch.empty(128, 64, device="cuda", dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("m", [1, 8, 13])
+def test_norm_folded_into_the_few_rows_products_around_it(m):
+    """The accumulating product leaves the sums of squares of the new residual and its rows times the next
+    norm's weight; the product after the norm scales its results: together they equal norm then product."""
+    from libmir_b200 import kernels
+    torch.manual_seed(m)
+    hidden, inner, wide, eps = 264, 136, 200, 1e-5
+    x = torch.randn(m, inner).bfloat16()
+    w_in = (torch.randn(hidden, inner) * 0.3).bfloat16()
+    gain = torch.rand(hidden) + 0.5
+    base = torch.randn(m, hidden) * 3.0
+    residual = cuda(base.clone())
+    tiles = kernels.sumsq_tiles(hidden)
+    sumsq = torch.zeros(tiles, 16, device="cuda")
+    weighted = torch.zeros(m, hidden, device="cuda", dtype=torch.bfloat16)
+    wrote = kernels.linear(cuda(x), cuda(w_in), residual, accumulate=True, sumsq_out=sumsq,
+                           weighted_out=(weighted, cuda(gain)))
+    assert wrote
+    new_residual = base.double() + plain_impl.linear(x.double(), w_in)
+    close(residual, new_residual, torch.float32, factor=40)
+    normed = plain_impl.rms_norm(new_residual, gain, eps)
+    lazy = kernels.NormedResidual(residual, cuda(gain), eps, sumsq, tiles, torch.bfloat16, weighted)
+    w_out = (torch.randn(wide, hidden) * 0.2).bfloat16()
+    out = torch.empty(m, wide, device="cuda", dtype=torch.bfloat16)
+    kernels.linear(lazy, cuda(w_out), out, alloc=lambda shape, dt: torch.empty(shape, device="cuda", dtype=dt))
+    close(out, plain_impl.linear(normed, w_out), torch.bfloat16, factor=2)
+    w_gate_up = (torch.randn(2 * wide, hidden) * 0.2).bfloat16()
+    gated = torch.empty(m, wide, device="cuda", dtype=torch.bfloat16)
+    kernels.gate_up_silu(lazy, cuda(w_gate_up), gated, lambda shape, dt: torch.empty(shape, device="cuda", dtype=dt))
+    both = plain_impl.linear(normed, w_gate_up)
+    close(gated, plain_impl.silu(both[:, :wide]) * both[:, wide:], torch.bfloat16, factor=2)
+    # what cannot be folded falls back to the norm kernel
+    assert torch.equal(lazy.materialize(lambda shape, dt: torch.empty(shape, device="cuda", dtype=dt)).cpu(),
+                       _rms_norm_kernel(residual, gain, eps).cpu())
+
+
+def _rms_norm_kernel(residual, gain, eps):
+    from libmir_b200 import kernels
+    out = torch.empty(residual.shape, device="cuda", dtype=torch.bfloat16)
+    kernels.rms_norm(residual, cuda(gain), eps, out)
+    return out
