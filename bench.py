@@ -126,6 +126,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--skip-points", action="store_true", help="only the batch-8 decode and the prefill")
+    parser.add_argument("--decode-ctas-per-sm", type=int, default=None,
+                        help="CTAs per SM that split decode attention aims for when it picks the partition size")
     parser.add_argument("--no-fold-norm", action="store_true",
                         help="run every RMSNorm as a kernel of its own instead of folding it into the few-rows "
                              "products around it")
@@ -161,6 +163,8 @@ def main() -> int:
         kernels.set_programmatic_launch(bool(args.pdl))
     if args.no_fold_norm:
         kernels.FUSE_NORM_INTO_PRODUCT = False
+    if args.decode_ctas_per_sm is not None:
+        kernels.DECODE_CTAS_PER_SM = args.decode_ctas_per_sm
     peaks, peaks_kind = read_peaks()
     config = dict(QWEN3_4B)
     layers_full = config["num_hidden_layers"]

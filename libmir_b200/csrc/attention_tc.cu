@@ -1,0 +1,372 @@
+// Causal attention of prompt portions over the paged cache on the 5th-generation tensor cores (tcgen05),
+// head_dim 128, bf16:
+//
+//   out[i] = softmax_j(scale q_i . k_j) v_j     over the keys j <= position(i) (and inside the window, if any)
+//
+// One CTA takes 128 consecutive query tokens of one request and one head, and walks over the request's keys in
+// tiles of 128.  Per tile:  S = Q K^T  (tcgen05.mma, 128 x 128 x 128, accumulator in tensor memory),
+// P = exp2(scale S - m) by the softmax threads (one query row per thread, read with tcgen05.ld, written to
+// shared memory as the bf16 A operand of the next product),  O += P V  (tcgen05.mma, accumulator stays in tensor
+// memory for the whole row of tiles).  Roles:
+//
+//   loader    one warp.  Q once, then per tile the pages that hold its keys and values: one TMA box per page and
+//             64-wide half of the head (cp.async.bulk.tensor.2d through a tensor map over the cache, 128-byte
+//             swizzle), into two-stage rings for K and V.  Pages the block table does not have (-1) are skipped.
+//   issuer    one thread.  S(t+1) = Q K(t+1)^T is issued before O += P(t) V(t), so that the tensor cores work on
+//             the next scores while the softmax threads are busy with the current ones (two S accumulators).
+//   softmax   four warps, thread r owns query row r = accumulator lane r.  The running maximum is only raised when
+//             a tile's maximum exceeds it by more than 2^8 (then O and the denominator are rescaled, O by
+//             tcgen05.ld / tcgen05.st), so most tiles need no pass over O.
+//
+// V is read as an MN-major operand (rows of keys, 64 head elements per 128-byte row) exactly as the cache stores
+// it; nothing is transposed.  Masked keys get probability 0 by selection, never by arithmetic on what the cache
+// holds there, and the V ring starts zeroed, so a skipped page cannot inject a NaN (0 x NaN) into O.
+// Every wait is bounded in time; a role whose wait runs out raises g_tc_attention_error and stops waiting, the
+// CTA still frees its tensor memory and returns.
+// libmir computes prompt attention with a library (flash-attention style kernels in cuda/kernels/attention_bf16.cu
+// for decode; cuda/src/backend/attention/mod.rs chooses); the formula is metal/src/engine/attention/mod.rs:60-140.
+#include <algorithm>
+#include "tcgen05.cuh"
+
+using namespace mir;
+using namespace mir::tc;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+constexpr int kRows = 128;                  // query tokens per CTA
+constexpr int kKeys = 128;                  // keys per tile
+constexpr int kDim = 128;                   // head_dim
+constexpr int kHalf = 128 * 128;            // bytes of a 128-row x 64-element half tile
+constexpr int kTile = 2 * kHalf;            // 32 KB
+constexpr int kOffQ = 0, kOffK = kTile, kOffV = 3 * kTile, kOffP = 5 * kTile;
+constexpr int kSmemBytes = 6 * kTile + 1024;
+constexpr int kThreads = 6 * 32;            // loader warp, issuer warp, four softmax warps
+constexpr uint32_t kTmemColumns = 512;      // S0 at 0, S1 at 128, O at 256
+constexpr float kRescaleThreshold = 8.0f;   // log2 of how far a tile's maximum may exceed the running one
+
+// barrier indices
+enum { Q_FULL = 0, K_FULL = 1, K_FREE = 3, V_FULL = 5, V_FREE = 7, S_FULL = 9, S_FREE = 11, P_READY = 13, PV_DONE = 14,
+       BARRIERS = 15 };
+
+__device__ int g_tc_attention_error = 0;
+
+__global__ void __launch_bounds__(kThreads, 1)
+tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                            const __grid_constant__ CUtensorMap v_map, bf16* __restrict__ out,
+                            const int* __restrict__ block_table, int table_width, const int* __restrict__ query_starts,
+                            const int* __restrict__ context_lens, int num_rows, int page_size, int heads, int kv_heads,
+                            float scale_log2, int window) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long barriers[BARRIERS];
+  __shared__ uint32_t tmem_base_slot;
+  if (*reinterpret_cast<volatile int*>(&g_tc_attention_error) != 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int kv_head = head / (heads / kv_heads);
+
+  grid_launch_dependents();
+  grid_dependency_wait();
+  // which request row and which 128-token tile of its portion this CTA has
+  int row = -1, local_tile = 0;
+  {
+    int remaining = gridDim.x - 1 - blockIdx.x;              // late tiles see the most keys: start them first
+    for (int r = 0; r < num_rows; ++r) {
+      const int tiles = (query_starts[r + 1] - query_starts[r] + kRows - 1) / kRows;
+      if (remaining < tiles) { row = r; local_tile = remaining; break; }
+      remaining -= tiles;
+    }
+  }
+  if (row < 0) return;                                        // a spare CTA (uniform for the whole CTA)
+  const int q_begin = query_starts[row];
+  const int count = query_starts[row + 1] - q_begin;
+  const int start_position = context_lens[row] - count;
+  const int local0 = local_tile * kRows;
+  const int tile_rows = min(kRows, count - local0);
+  const int first_position = start_position + local0;
+  const int last_position = first_position + tile_rows - 1;
+  const int* table = block_table + (size_t)row * table_width;
+  const int first_key = (window > 0 && first_position + 1 > window) ? first_position + 1 - window : 0;
+  const int key_begin = first_key / kKeys * kKeys;
+  const int key_end = last_position + 1;                      // exclusive
+  const int tiles = (key_end - key_begin + kKeys - 1) / kKeys;
+
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar0 = smem_u32(&barriers[0]);
+  auto bar = [&](int index) { return bar0 + 8u * (uint32_t)index; };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < BARRIERS; ++i) {
+      const bool many = i == S_FREE || i == S_FREE + 1 || i == P_READY;   // every softmax thread arrives
+      barrier_init(bar(i), many ? 128u : 1u);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // the V ring starts as zeros (see the note on skipped pages above)
+  for (int i = threadIdx.x; i < 2 * kTile / 16; i += kThreads)
+    *reinterpret_cast<uint4*>(smem + kOffV + (size_t)i * 16) = make_uint4(0u, 0u, 0u, 0u);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"(kTmemColumns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tensor_fence_before_sync();
+  __syncthreads();
+  tensor_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+  const uint32_t tmem_o = tmem_base + 256u;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ loader
+    if (lane == 0) {
+      barrier_expect_bytes(bar(Q_FULL), kTile);
+      tma_load_2d(smem_base + kOffQ, &q_map, bar(Q_FULL), head * kDim, q_begin + local0);
+      tma_load_2d(smem_base + kOffQ + kHalf, &q_map, bar(Q_FULL), head * kDim + 64, q_begin + local0);
+    }
+    const int pages_per_tile = kKeys / page_size;
+    const uint32_t box_bytes = (uint32_t)page_size * 128u;
+    bool alive = true;
+    for (int t = 0; t < tiles && alive; ++t) {
+      const int stage = t & 1;
+      const uint32_t parity = (uint32_t)(t >> 1) & 1u;
+      const int key0 = key_begin + t * kKeys;
+#pragma unroll 1
+      for (int which = 0; which < 2 && alive; ++which) {      // 0: keys, 1: values
+        const uint32_t full = bar((which ? V_FULL : K_FULL) + stage), free_bar = bar((which ? V_FREE : K_FREE) + stage);
+        int ok = 1;
+        if (lane == 0) ok = wait_barrier(free_bar, parity ^ 1u) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { if (lane == 0) g_tc_attention_error = 1; alive = false; break; }
+        const uint32_t dst = smem_base + (which ? kOffV : kOffK) + (uint32_t)stage * kTile;
+        // lane l loads half (l & 1) of page slot (l >> 1): at most 16 pages of 8 keys, so one round of 32 lanes
+        const int slot = lane >> 1, half = lane & 1;
+        const int key = key0 + slot * page_size;
+        int page = -1;
+        if (lane < 2 * pages_per_tile && key < key_end && key + page_size > first_key) page = table[key / page_size];
+        const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
+        if (lane == 0) barrier_expect_bytes(full, (uint32_t)__popc(valid) * box_bytes);
+        __syncwarp();
+        if (page >= 0)
+          tma_load_2d(dst + (uint32_t)half * kHalf + (uint32_t)(slot * page_size) * 128u, which ? &v_map : &k_map, full,
+                      kv_head * kDim + half * 64, page * page_size);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = instruction_descriptor(kRows, kKeys, false);
+      constexpr uint32_t idesc_pv = instruction_descriptor(kRows, kDim, true);
+      bool alive = wait_barrier(bar(Q_FULL), 0);
+      if (!alive) g_tc_attention_error = 2;
+      auto issue_scores = [&](int t) {
+        const int stage = t & 1;
+        const uint32_t parity = (uint32_t)(t >> 1) & 1u;
+        if (alive && !wait_barrier(bar(K_FULL + stage), parity)) { g_tc_attention_error = 2; alive = false; }
+        if (alive && !wait_barrier(bar(S_FREE + stage), parity ^ 1u)) { g_tc_attention_error = 2; alive = false; }
+        tensor_fence_after_sync();
+        const uint32_t a = smem_base + kOffQ, b = smem_base + kOffK + (uint32_t)stage * kTile;
+#pragma unroll
+        for (int kk = 0; kk < kDim / 16; ++kk) {
+          const uint32_t offset = (uint32_t)(kk >> 2) * kHalf + (uint32_t)(kk & 3) * 32u;
+          mma_bf16_ss(tmem_base + (uint32_t)stage * 128u, operand_descriptor(a + offset), operand_descriptor(b + offset),
+                      idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(bar(S_FULL + stage));
+        mma_commit(bar(K_FREE + stage));
+      };
+      issue_scores(0);
+      for (int t = 0; t < tiles; ++t) {
+        if (t + 1 < tiles) issue_scores(t + 1);
+        const int stage = t & 1;
+        const uint32_t parity = (uint32_t)(t >> 1) & 1u;
+        if (alive && !wait_barrier(bar(V_FULL + stage), parity)) { g_tc_attention_error = 2; alive = false; }
+        if (alive && !wait_barrier(bar(P_READY), (uint32_t)t & 1u)) { g_tc_attention_error = 2; alive = false; }
+        tensor_fence_after_sync();
+        const uint32_t a = smem_base + kOffP, b = smem_base + kOffV + (uint32_t)stage * kTile;
+#pragma unroll
+        for (int kk = 0; kk < kKeys / 16; ++kk) {
+          // P: 16 keys further along its 128-byte rows; V: 16 rows of keys further down
+          const uint32_t a_offset = (uint32_t)(kk >> 2) * kHalf + (uint32_t)(kk & 3) * 32u;
+          mma_bf16_ss(tmem_o, operand_descriptor(a + a_offset), operand_descriptor_mn_major(b + (uint32_t)kk * 2048u, kHalf),
+                      idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
+        }
+        mma_commit(bar(PV_DONE));
+        mma_commit(bar(V_FREE + stage));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax: one query row per thread
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const bool valid_row = r < tile_rows;
+    const int position = first_position + min(r, tile_rows - 1);
+    const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
+    float reference = -INFINITY, denominator = 0.0f;          // running maximum (scaled, log2 domain) and sum
+    bool alive = true;
+    for (int t = 0; t < tiles && alive; ++t) {
+      const int stage = t & 1;
+      const uint32_t parity = (uint32_t)(t >> 1) & 1u;
+      const int key0 = key_begin + t * kKeys;
+      if (!wait_barrier(bar(S_FULL + stage), parity)) { g_tc_attention_error = 3; alive = false; break; }
+      tensor_fence_after_sync();
+      const uint32_t scores = tmem_base + (uint32_t)stage * 128u + lane_bits;
+      // keys of this tile that row r may see: [low, high]
+      const int high = position - key0;                       // last visible column, may be >= 128 or < 0
+      const int low = window > 0 ? position - window + 1 - key0 : -1;
+      // pass 1: the row's maximum over the visible keys
+      float maximum = -INFINITY;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kKeys; c0 += 32) {
+        float v[32];
+        tmem_load_32(scores + c0, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int c = c0 + i;
+          if (c <= high && c >= low) maximum = fmaxf(maximum, v[i]);
+        }
+      }
+      maximum *= scale_log2;                                  // scale > 0
+      const bool grow = maximum > reference + kRescaleThreshold;
+      const float next_reference = grow ? maximum : reference;
+      const float factor = grow ? exp2f(reference - maximum) : 1.0f;   // 0 when nothing was seen before
+      // pass 2: probabilities, packed to bf16
+      uint32_t packed[kKeys / 2];
+      float sum = 0.0f;
+#pragma unroll
+      for (int c0 = 0; c0 < kKeys; c0 += 32) {
+        float v[32];
+        tmem_load_32(scores + c0, v);
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int c = c0 + i;
+          const float p0 = (c <= high && c >= low) ? exp2f(fmaf(v[i], scale_log2, -next_reference)) : 0.0f;
+          const float p1 = (c + 1 <= high && c + 1 >= low) ? exp2f(fmaf(v[i + 1], scale_log2, -next_reference)) : 0.0f;
+          sum += p0 + p1;
+          const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+          packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&pair);
+        }
+      }
+      tensor_fence_before_sync();
+      barrier_arrive(bar(S_FREE + stage));                    // the scores are in registers
+      denominator = denominator * factor + sum;
+      reference = next_reference;
+      // the product with the previous tile's P must be over before P or O change
+      if (t > 0) {
+        if (!wait_barrier(bar(PV_DONE), (uint32_t)(t - 1) & 1u)) { g_tc_attention_error = 3; alive = false; break; }
+        tensor_fence_after_sync();
+        if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < kDim; c0 += 32) {
+            float o[32];
+            tmem_load_32(tmem_o + lane_bits + c0, o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= factor;
+            tmem_store_32(tmem_o + lane_bits + c0, o);
+          }
+          tmem_store_wait();
+        }
+      }
+      // P as the A operand: rows of 128 bytes (64 keys), 16-byte chunks swizzled by the row
+      unsigned char* p_row = smem + kOffP + (size_t)r * 128;
+#pragma unroll
+      for (int chunk = 0; chunk < 16; ++chunk) {
+        const int where = (chunk & 7) ^ (r & 7);
+        *reinterpret_cast<uint4*>(p_row + (size_t)(chunk >> 3) * kHalf + where * 16) =
+            make_uint4(packed[4 * chunk], packed[4 * chunk + 1], packed[4 * chunk + 2], packed[4 * chunk + 3]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tensor_fence_before_sync();
+      barrier_arrive(bar(P_READY));
+    }
+    if (alive && !wait_barrier(bar(PV_DONE), (uint32_t)(tiles - 1) & 1u)) { g_tc_attention_error = 3; alive = false; }
+    tensor_fence_after_sync();
+    if (alive) {
+      const float inverse = denominator > 0.0f ? 1.0f / denominator : 0.0f;
+      bf16* dst = out + ((size_t)(q_begin + local0 + r) * heads + head) * kDim;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kDim; c0 += 32) {
+        float o[32];
+        tmem_load_32(tmem_o + lane_bits + c0, o);
+        if (valid_row) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 packed_out;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed_out);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(o[i + 2 * j] * inverse, o[i + 2 * j + 1] * inverse);
+            *reinterpret_cast<uint4*>(dst + c0 + i) = packed_out;
+          }
+        }
+      }
+    }
+    tensor_fence_before_sync();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tensor_fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns) : "memory");
+  }
+}
+
+}  // namespace
+
+// 0 if no bounded wait of the tcgen05 attention ever ran out; else which role gave up last (1 loader, 2 issuer,
+// 3 softmax).  Synchronises the device.
+MIR_EXPORT int mir_prefill_attention_tc_error() {
+  int flag = 0;
+  if (cudaMemcpyFromSymbol(&flag, g_tc_attention_error, sizeof(int)) != cudaSuccess) return -1;
+  return flag;
+}
+
+// Whether the tcgen05 kernel takes these sizes (head_dim 128, pages of 8 to 128 keys that divide 128).
+MIR_EXPORT int mir_prefill_attention_tc_takes(int head_dim, int page_size) {
+  return head_dim == kDim && page_size >= 8 && page_size <= kKeys && kKeys % page_size == 0 && page_size % 8 == 0;
+}
+
+// Any mix of portions: row r has tokens query_starts[r] .. query_starts[r+1]-1 of the packed batch, and its
+// context_lens[r] cached tokens include them.  q is the packed [tokens, q_stride] buffer whose first
+// heads * 128 columns are the rotated queries; out is [tokens, heads * 128]; k_pages and v_pages are
+// [cache_rows, kv_heads, 128].
+MIR_EXPORT int mir_prefill_attention_tc_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                             const void* v_pages, long long cache_rows, const int* block_table,
+                                             int table_width, const int* query_starts, const int* context_lens,
+                                             int num_rows, int tokens, int page_size, int heads, int kv_heads,
+                                             int head_dim, float scale, int window, cudaStream_t stream) {
+  if (num_rows == 0 || tokens == 0) return MIR_OK;
+  if (!mir_prefill_attention_tc_takes(head_dim, page_size) || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
+      table_width <= 0 || window < 0 || num_rows < 0 || tokens < 0 || heads > 65535 || scale <= 0.0f ||
+      (q_stride % 8) || q_stride < (long long)heads * kDim || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) ||
+      ((uintptr_t)v_pages & 15) || ((uintptr_t)out & 15) || cache_rows <= 0 || cache_rows > 0x7fffffffll ||
+      q_stride > 0x7fffffffll) {
+    mir_set_error("prefill_attention_tc: takes head_dim 128, pages of 8..128 keys that divide 128, a positive scale "
+                  "and 16-byte aligned tensors (head_dim %d, page %d, heads %d, kv heads %d)", head_dim, page_size,
+                  heads, kv_heads);
+    return MIR_BAD_ARGUMENT;
+  }
+  CUtensorMap q_map, k_map, v_map;
+  int status = tensor_map_for(q, tokens, (int)q_stride, (int)q_stride, kRows, &q_map);
+  if (status != MIR_OK) return status;
+  status = tensor_map_for(k_pages, (int)cache_rows, kv_heads * kDim, kv_heads * kDim, page_size, &k_map);
+  if (status != MIR_OK) return status;
+  status = tensor_map_for(v_pages, (int)cache_rows, kv_heads * kDim, kv_heads * kDim, page_size, &v_map);
+  if (status != MIR_OK) return status;
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t err = cudaFuncSetAttribute(tc_prefill_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 kSmemBytes);
+    if (err != cudaSuccess) {
+      mir_set_error("prefill_attention_tc: cannot reserve %d bytes of shared memory: %s", kSmemBytes,
+                    cudaGetErrorString(err));
+      return MIR_CUDA_ERROR;
+    }
+    configured = true;
+  }
+  const int tiles = (tokens + kRows - 1) / kRows + num_rows;   // an upper bound; spare CTAs return
+  return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel, dim3(tiles, heads), dim3(kThreads),
+                    (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, (bf16*)out, block_table, table_width,
+                    query_starts, context_lens, num_rows, page_size, heads, kv_heads,
+                    scale * 1.4426950408889634f, window);
+}

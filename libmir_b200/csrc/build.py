@@ -36,8 +36,8 @@ LIBRARIES = {
         "link": [],
     },
     "bf16": {
-        "sources": ["runtime.cu", "gemm_lt.cu", "attention_mma.cu", "gemm_skinny.cu", "gemm_tc.cu"],
-        "headers": ["no_alloc.h"],
+        "sources": ["runtime.cu", "gemm_lt.cu", "attention_mma.cu", "gemm_skinny.cu", "gemm_tc.cu", "attention_tc.cu"],
+        "headers": ["no_alloc.h", "tcgen05.cuh"],
         "link": ["-lcublasLt"],
     },
 }

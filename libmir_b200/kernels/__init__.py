@@ -46,6 +46,11 @@ _SIGNATURES = {
                                       c_longlong, c_void_p],
         "mir_prefill_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "mir_prefill_attention_tc_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int,
+                                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                          c_void_p],
+        "mir_prefill_attention_tc_takes": [c_int, c_int],
+        "mir_prefill_attention_tc_error": [],
         "mir_gemm_skinny_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                  c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mir_gemm_tc_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -260,6 +265,7 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
 
 FAST_HEAD_DIMS = (64, 128)      # what the tensor-core attention kernels take; other sizes use the reference kernel
 SM_COUNT = 148
+DECODE_CTAS_PER_SM = 2      # how many CTAs per SM split decode attention aims for
 
 
 def decode_partitioning(rows: int, kv_heads: int, max_context: int) -> tuple:
@@ -268,7 +274,7 @@ def decode_partitioning(rows: int, kv_heads: int, max_context: int) -> tuple:
     partition = 512
     while True:
         count = max(1, -(-max_context // partition))
-        if rows * kv_heads * count >= 2 * SM_COUNT or partition == 64:
+        if rows * kv_heads * count >= DECODE_CTAS_PER_SM * SM_COUNT or partition == 64:
             return partition, count
         partition //= 2
 
@@ -300,11 +306,18 @@ def decode_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor
     LAUNCHES += 1 if num_partitions > 1 else 0
 
 
+# Whether prompt portions run the tcgen05 attention kernel where it takes the sizes (head_dim 128, pages of 8 to
+# 128 keys that divide 128) and the portions average at least PREFILL_TENSOR_CORE_MIN_PORTION tokens.
+PREFILL_TENSOR_CORES = True
+PREFILL_TENSOR_CORE_MIN_PORTION = 32
+
+
 def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       block_table: torch.Tensor, query_starts: torch.Tensor, context_lens: torch.Tensor,
                       page_size: int, heads: int, kv_heads: int, head_dim: int, scale: float,
-                      window: Optional[int]) -> None:
-    """bf16 tensor-core attention for any mix of portions (row r owns tokens query_starts[r]..query_starts[r+1])."""
+                      window: Optional[int], tensor_cores: Optional[bool] = None) -> None:
+    """bf16 tensor-core attention for any mix of portions (row r owns tokens query_starts[r]..query_starts[r+1]).
+    `tensor_cores`: True runs the tcgen05 kernel, False the mma.sync kernel, None chooses."""
     _cuda(qkv, out, k_pages, v_pages, block_table, query_starts, context_lens)
     tokens = out.shape[0]
     rows = context_lens.numel()
@@ -315,10 +328,27 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
              and context_lens.dtype == torch.int32 and query_starts.numel() == rows + 1
              and block_table.shape[0] >= rows, "prefill_attention: bad metadata")
     lib = library("bf16")
+    if tensor_cores is None:
+        tensor_cores = (PREFILL_TENSOR_CORES and tokens >= PREFILL_TENSOR_CORE_MIN_PORTION * rows
+                        and bool(lib.mir_prefill_attention_tc_takes(head_dim, page_size))
+                        and k_pages.is_contiguous() and v_pages.is_contiguous() and scale > 0)
+    if tensor_cores:
+        _require(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape == v_pages.shape,
+                 "prefill_attention: the tcgen05 kernel reads contiguous [rows, kv_heads, head_dim] pages")
+        _check(lib, lib.mir_prefill_attention_tc_bf16(
+            qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
+            block_table.data_ptr(), block_table.shape[1], query_starts.data_ptr(), context_lens.data_ptr(), rows, tokens,
+            page_size, heads, kv_heads, head_dim, scale, int(window or 0), _stream()))
+        return
     _check(lib, lib.mir_prefill_attention_bf16(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], query_starts.data_ptr(), context_lens.data_ptr(), rows, tokens, page_size, heads,
         kv_heads, head_dim, scale, int(window or 0), _stream()))
+
+
+def prefill_attention_error() -> int:
+    """0, or which role of the tcgen05 attention gave up a bounded wait (synchronises the device)."""
+    return int(library("bf16").mir_prefill_attention_tc_error())
 
 
 # --------------------------------------------------------------------------- matrix products

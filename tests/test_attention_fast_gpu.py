@@ -110,7 +110,38 @@ def test_prefill_attention_mixed_portions(heads, kv_heads, dim, page, window):
     close(out.reshape(tokens, heads, dim), expected)
 
 
-@pytest.mark.parametrize("kind", ["decode", "prefill"])
+@pytest.mark.parametrize("heads,kv_heads,page,window", [
+    (8, 2, 16, None), (4, 4, 8, None), (6, 1, 32, 100), (3, 3, 128, 300), (32, 8, 16, None), (2, 1, 64, 129)])
+def test_prefill_attention_on_tcgen05(heads, kv_heads, page, window):
+    """The tcgen05 kernel (head_dim 128): a whole 700-token prompt, a 300-token portion that starts at 333, a
+    single decoded token at 129, a 2-token portion at 64, and a 130-token portion that ends on a tile's edge."""
+    from libmir_b200 import kernels
+    dim = 128
+    rng = np.random.default_rng(page + heads)
+    torch.manual_seed(page + heads)
+    spans = [(0, 700), (333, 633), (129, 130), (64, 66), (126, 256)]
+    scale = 0.8 / math.sqrt(dim)
+    qs = [(torch.randn(end, heads, dim) * 2).to(BF16) for _, end in spans]
+    ks = [(torch.randn(end, kv_heads, dim) * 2).to(BF16) for _, end in spans]
+    vs = [torch.randn(end, kv_heads, dim).to(BF16) for _, end in spans]
+    k_pool, v_pool, table = build_pool(ks, vs, page, rng)
+    q_rows = torch.cat([q[start:end] for q, (start, end) in zip(qs, spans)])
+    tokens = q_rows.shape[0]
+    packed = torch.cat([q_rows.reshape(tokens, -1), torch.randn(tokens, 2 * kv_heads * dim).to(BF16)], dim=1).contiguous()
+    starts = np.cumsum([0] + [end - start for start, end in spans])
+    out = torch.full((tokens, heads * dim), 9.0, device="cuda", dtype=BF16)
+    kernels.prefill_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table),
+                              cuda(torch.tensor(starts, dtype=torch.int32)),
+                              cuda(torch.tensor([end for _, end in spans], dtype=torch.int32)), page, heads, kv_heads,
+                              dim, scale, window, tensor_cores=True)
+    torch.cuda.synchronize()
+    assert kernels.prefill_attention_error() == 0
+    expected = torch.cat([expect(q, k, v, scale, window, slice(start, end))
+                          for q, k, v, (start, end) in zip(qs, ks, vs, spans)])
+    close(out.reshape(tokens, heads, dim), expected)
+
+
+@pytest.mark.parametrize("kind", ["decode", "prefill", "prefill_tcgen05"])
 def test_one_far_key_among_hundreds_and_the_windows_edge(kind):
     from libmir_b200 import kernels
     heads, kv_heads, dim, page, n = 8, 2, 128, 16, 1100
@@ -137,7 +168,7 @@ def test_one_far_key_among_hundreds_and_the_windows_edge(kind):
             kernels.prefill_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table),
                                       cuda(torch.tensor([0, 1], dtype=torch.int32)),
                                       cuda(torch.tensor([n], dtype=torch.int32)), page, heads, kv_heads, dim, 1.0,
-                                      window)
+                                      window, tensor_cores=(kind == "prefill_tcgen05"))
         return out.reshape(heads, dim).float().cpu(), v.float()
 
     for strong in (0, 15, 16, 63, 64, 127, 128, 600, n - 1):
