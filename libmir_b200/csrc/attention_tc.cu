@@ -9,14 +9,15 @@
 // shared memory as the bf16 A operand of the next product),  O += P V  (tcgen05.mma, accumulator stays in tensor
 // memory for the whole row of tiles).  Roles:
 //
-//   loader    one warp.  Q once, then per tile the pages that hold its keys and values: one TMA box per page and
-//             64-wide half of the head (cp.async.bulk.tensor.2d through a tensor map over the cache, 128-byte
-//             swizzle), into two-stage rings for K and V.  Pages the block table does not have (-1) are skipped.
+//   loaders   one warp for keys (and Q, once), one for values.  Per tile the pages that hold it: one TMA box per
+//             page and 64-wide half of the head (cp.async.bulk.tensor.2d through a tensor map over the cache,
+//             128-byte swizzle), into two-stage rings.  Pages the block table does not have (-1) are skipped.
 //   issuer    one thread.  S(t+1) = Q K(t+1)^T is issued before O += P(t) V(t), so that the tensor cores work on
 //             the next scores while the softmax threads are busy with the current ones (two S accumulators).
-//   softmax   four warps, thread r owns query row r = accumulator lane r.  The running maximum is only raised when
-//             a tile's maximum exceeds it by more than 2^8 (then O and the denominator are rescaled, O by
-//             tcgen05.ld / tcgen05.st), so most tiles need no pass over O.
+//   softmax   eight warps: query row r = accumulator lane r belongs to two threads, which take 64 columns each
+//             (of the scores, of P and of O) and share the row's maximum through shared memory.  The running
+//             maximum is only raised when a tile's maximum exceeds it by more than 2^8 (then O and the
+//             denominator are rescaled, O by tcgen05.ld / tcgen05.st), so most tiles need no pass over O.
 //
 // V is read as an MN-major operand (rows of keys, 64 head elements per 128-byte row) exactly as the cache stores
 // it; nothing is transposed.  Masked keys get probability 0 by selection, never by arithmetic on what the cache
@@ -41,7 +42,7 @@ constexpr int kHalf = 128 * 128;            // bytes of a 128-row x 64-element h
 constexpr int kTile = 2 * kHalf;            // 32 KB
 constexpr int kOffQ = 0, kOffK = kTile, kOffV = 3 * kTile, kOffP = 5 * kTile;
 constexpr int kSmemBytes = 6 * kTile + 1024;
-constexpr int kThreads = 6 * 32;            // loader warp, issuer warp, four softmax warps
+constexpr int kThreads = 11 * 32;           // key loader, issuer, eight softmax warps, value loader
 constexpr uint32_t kTmemColumns = 512;      // S0 at 0, S1 at 128, O at 256
 constexpr float kRescaleThreshold = 8.0f;   // log2 of how far a tile's maximum may exceed the running one
 
@@ -50,6 +51,74 @@ enum { Q_FULL = 0, K_FULL = 1, K_FREE = 3, V_FULL = 5, V_FREE = 7, S_FULL = 9, S
        BARRIERS = 15 };
 
 __device__ int g_tc_attention_error = 0;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 32 consecutive accumulator columns of this thread's lane, without waiting for them (tmem_load_wait()).
+__device__ __forceinline__ void tmem_load_32_nowait(uint32_t address, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(address)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+constexpr int kCols = kKeys / 2;             // columns of a tile that one softmax thread handles
+
+// One tile of the softmax for this thread's half (64 columns starting at `first`) of its row: the scores are
+// read once (two loads in flight, one wait), then the visible maximum (columns low..high of the tile; all if
+// !MASKED), which the two threads of a row exchange through `mine` / `other` and the named barrier `pair`; then
+// the decision whether the running maximum rises, and p = exp2(scale s - reference) packed to bf16.  Returns
+// the sum of this thread's p.
+template <bool MASKED>
+__device__ __forceinline__ float softmax_tile(uint32_t scores, int first, int low, int high, float scale_log2,
+                                              float& reference, float& factor, bool& grow, uint32_t (&packed)[kCols / 2],
+                                              float* mine, const float* other, int pair) {
+  float v[kCols];
+#pragma unroll
+  for (int c0 = 0; c0 < kCols; c0 += 32) tmem_load_32_nowait(scores + first + c0, v + c0);
+  tmem_load_wait();
+#pragma unroll
+  for (int c = 0; c < kCols; ++c) asm volatile("" : "+f"(v[c])::"memory");   // no use of v moves above the wait
+  float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};        // four chains instead of one
+#pragma unroll
+  for (int c = 0; c < kCols; ++c)
+    if (!MASKED || (first + c <= high && first + c >= low)) best[c & 3] = fmaxf(best[c & 3], v[c]);
+  float maximum = fmaxf(fmaxf(best[0], best[1]), fmaxf(best[2], best[3]));
+  *mine = maximum;
+  asm volatile("bar.sync %0, 64;" ::"r"(pair) : "memory");
+  maximum = fmaxf(maximum, *other) * scale_log2;                       // scale > 0
+  grow = maximum > reference + kRescaleThreshold;
+  factor = grow ? fast_exp2(reference - maximum) : 1.0f;               // 0 when nothing was seen before
+  reference = grow ? maximum : reference;
+  float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+  for (int c = 0; c < kCols; c += 2) {
+    float p0 = fast_exp2(fmaf(v[c], scale_log2, -reference));
+    float p1 = fast_exp2(fmaf(v[c + 1], scale_log2, -reference));
+    if (MASKED) {
+      p0 = (first + c <= high && first + c >= low) ? p0 : 0.0f;
+      p1 = (first + c + 1 <= high && first + c + 1 >= low) ? p1 : 0.0f;
+    }
+    sums[(c >> 1) & 3] += p0 + p1;
+    const __nv_bfloat162 pair2 = __floats2bfloat162_rn(p0, p1);
+    packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&pair2);
+  }
+  return (sums[0] + sums[1]) + (sums[2] + sums[3]);
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
@@ -60,6 +129,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long barriers[BARRIERS];
   __shared__ uint32_t tmem_base_slot;
+  __shared__ float exchange[2][2][kRows];                    // [tile parity][half][row]: what a row's two threads share
   if (*reinterpret_cast<volatile int*>(&g_tc_attention_error) != 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y;
@@ -99,7 +169,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   if (threadIdx.x == 0) {
     for (int i = 0; i < BARRIERS; ++i) {
       const bool many = i == S_FREE || i == S_FREE + 1 || i == P_READY;   // every softmax thread arrives
-      barrier_init(bar(i), many ? 128u : 1u);
+      barrier_init(bar(i), many ? 256u : 1u);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -119,40 +189,42 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   const uint32_t tmem_base = tmem_base_slot;
   const uint32_t tmem_o = tmem_base + 256u;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ loader
-    if (lane == 0) {
+  if (warp == 0 || warp == kThreads / 32 - 1) {
+    // ------------------------------------------------------------------ loaders: warp 0 keys, the last warp values
+    // (apart, so that the keys of a later tile do not queue behind values whose stage is still being read)
+    const int which = warp == 0 ? 0 : 1;
+    if (which == 0 && lane == 0) {
       barrier_expect_bytes(bar(Q_FULL), kTile);
       tma_load_2d(smem_base + kOffQ, &q_map, bar(Q_FULL), head * kDim, q_begin + local0);
       tma_load_2d(smem_base + kOffQ + kHalf, &q_map, bar(Q_FULL), head * kDim + 64, q_begin + local0);
     }
     const int pages_per_tile = kKeys / page_size;
     const uint32_t box_bytes = (uint32_t)page_size * 128u;
-    bool alive = true;
-    for (int t = 0; t < tiles && alive; ++t) {
+    // lane l loads half (l & 1) of page slot (l >> 1): at most 16 pages of 8 keys, so one round of 32 lanes
+    const int slot = lane >> 1, half = lane & 1;
+    auto page_of = [&](int t) {
+      const int key = key_begin + t * kKeys + slot * page_size;
+      return (t < tiles && lane < 2 * pages_per_tile && key < key_end && key + page_size > first_key)
+                 ? table[key / page_size] : -1;
+    };
+    int page = page_of(0);
+    for (int t = 0; t < tiles; ++t) {
       const int stage = t & 1;
       const uint32_t parity = (uint32_t)(t >> 1) & 1u;
-      const int key0 = key_begin + t * kKeys;
-#pragma unroll 1
-      for (int which = 0; which < 2 && alive; ++which) {      // 0: keys, 1: values
-        const uint32_t full = bar((which ? V_FULL : K_FULL) + stage), free_bar = bar((which ? V_FREE : K_FREE) + stage);
-        int ok = 1;
-        if (lane == 0) ok = wait_barrier(free_bar, parity ^ 1u) ? 1 : 0;
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) { if (lane == 0) g_tc_attention_error = 1; alive = false; break; }
-        const uint32_t dst = smem_base + (which ? kOffV : kOffK) + (uint32_t)stage * kTile;
-        // lane l loads half (l & 1) of page slot (l >> 1): at most 16 pages of 8 keys, so one round of 32 lanes
-        const int slot = lane >> 1, half = lane & 1;
-        const int key = key0 + slot * page_size;
-        int page = -1;
-        if (lane < 2 * pages_per_tile && key < key_end && key + page_size > first_key) page = table[key / page_size];
-        const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
-        if (lane == 0) barrier_expect_bytes(full, (uint32_t)__popc(valid) * box_bytes);
-        __syncwarp();
-        if (page >= 0)
-          tma_load_2d(dst + (uint32_t)half * kHalf + (uint32_t)(slot * page_size) * 128u, which ? &v_map : &k_map, full,
-                      kv_head * kDim + half * 64, page * page_size);
-      }
+      const int next_page = page_of(t + 1);                   // on its way while this tile's stage is awaited
+      const uint32_t full = bar((which ? V_FULL : K_FULL) + stage), free_bar = bar((which ? V_FREE : K_FREE) + stage);
+      int ok = 1;
+      if (lane == 0) ok = wait_barrier(free_bar, parity ^ 1u) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { if (lane == 0) g_tc_attention_error = 1; break; }
+      const uint32_t dst = smem_base + (which ? kOffV : kOffK) + (uint32_t)stage * kTile;
+      const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
+      if (lane == 0) barrier_expect_bytes(full, (uint32_t)__popc(valid) * box_bytes);
+      __syncwarp();
+      if (page >= 0)
+        tma_load_2d(dst + (uint32_t)half * kHalf + (uint32_t)(slot * page_size) * 128u, which ? &v_map : &k_map, full,
+                    kv_head * kDim + half * 64, page * page_size);
+      page = next_page;
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ issuer
@@ -198,98 +270,82 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax: one query row per thread
-    const int quarter = warp & 3;
+    // ------------------------------------------------------------------ softmax: two threads per query row (warps 2..9)
+    const int quarter = warp & 3;                             // the accumulator lanes this warp may touch
+    const int half = (warp - 2) >> 2;                         // which 64 columns of the row (and of O) it takes
     const int r = quarter * 32 + lane;
     const bool valid_row = r < tile_rows;
     const int position = first_position + min(r, tile_rows - 1);
     const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
-    float reference = -INFINITY, denominator = 0.0f;          // running maximum (scaled, log2 domain) and sum
+    const int first = half * kCols;
+    float reference = -INFINITY, denominator = 0.0f;          // running maximum (scaled, log2 domain), partial sum
     bool alive = true;
-    for (int t = 0; t < tiles && alive; ++t) {
+    // (a thread whose wait ran out keeps walking the tiles without waiting, so that the pair's named barrier
+    // still sees both of its threads)
+    for (int t = 0; t < tiles; ++t) {
       const int stage = t & 1;
       const uint32_t parity = (uint32_t)(t >> 1) & 1u;
       const int key0 = key_begin + t * kKeys;
-      if (!wait_barrier(bar(S_FULL + stage), parity)) { g_tc_attention_error = 3; alive = false; break; }
+      if (alive && !wait_barrier(bar(S_FULL + stage), parity)) { g_tc_attention_error = 3; alive = false; }
       tensor_fence_after_sync();
       const uint32_t scores = tmem_base + (uint32_t)stage * 128u + lane_bits;
-      // keys of this tile that row r may see: [low, high]
+      // keys of this tile that row r may see: columns [low, high]; most tiles are visible to every row
       const int high = position - key0;                       // last visible column, may be >= 128 or < 0
       const int low = window > 0 ? position - window + 1 - key0 : -1;
-      // pass 1: the row's maximum over the visible keys
-      float maximum = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kKeys; c0 += 32) {
-        float v[32];
-        tmem_load_32(scores + c0, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int c = c0 + i;
-          if (c <= high && c >= low) maximum = fmaxf(maximum, v[i]);
-        }
-      }
-      maximum *= scale_log2;                                  // scale > 0
-      const bool grow = maximum > reference + kRescaleThreshold;
-      const float next_reference = grow ? maximum : reference;
-      const float factor = grow ? exp2f(reference - maximum) : 1.0f;   // 0 when nothing was seen before
-      // pass 2: probabilities, packed to bf16
-      uint32_t packed[kKeys / 2];
-      float sum = 0.0f;
-#pragma unroll
-      for (int c0 = 0; c0 < kKeys; c0 += 32) {
-        float v[32];
-        tmem_load_32(scores + c0, v);
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int c = c0 + i;
-          const float p0 = (c <= high && c >= low) ? exp2f(fmaf(v[i], scale_log2, -next_reference)) : 0.0f;
-          const float p1 = (c + 1 <= high && c + 1 >= low) ? exp2f(fmaf(v[i + 1], scale_log2, -next_reference)) : 0.0f;
-          sum += p0 + p1;
-          const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
-          packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&pair);
-        }
-      }
+      const bool every = key0 + kKeys - 1 <= first_position && (window == 0 || last_position - window + 1 <= key0);
+      uint32_t packed[kCols / 2];
+      bool grow;
+      float factor;
+      float* mine = &exchange[stage][half][r];
+      const float* other = &exchange[stage][half ^ 1][r];
+      const float sum = every ? softmax_tile<false>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
+                                                    mine, other, 1 + quarter)
+                              : softmax_tile<true>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
+                                                   mine, other, 1 + quarter);
       tensor_fence_before_sync();
       barrier_arrive(bar(S_FREE + stage));                    // the scores are in registers
       denominator = denominator * factor + sum;
-      reference = next_reference;
       // the product with the previous tile's P must be over before P or O change
       if (t > 0) {
-        if (!wait_barrier(bar(PV_DONE), (uint32_t)(t - 1) & 1u)) { g_tc_attention_error = 3; alive = false; break; }
+        if (alive && !wait_barrier(bar(PV_DONE), (uint32_t)(t - 1) & 1u)) { g_tc_attention_error = 3; alive = false; }
         tensor_fence_after_sync();
         if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-          for (int c0 = 0; c0 < kDim; c0 += 32) {
+          for (int c0 = 0; c0 < kDim / 2; c0 += 32) {
             float o[32];
-            tmem_load_32(tmem_o + lane_bits + c0, o);
+            tmem_load_32(tmem_o + lane_bits + first + c0, o);
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] *= factor;
-            tmem_store_32(tmem_o + lane_bits + c0, o);
+            tmem_store_32(tmem_o + lane_bits + first + c0, o);
           }
           tmem_store_wait();
         }
       }
-      // P as the A operand: rows of 128 bytes (64 keys), 16-byte chunks swizzled by the row
-      unsigned char* p_row = smem + kOffP + (size_t)r * 128;
+      // P as the A operand: rows of 128 bytes (64 keys, this thread's half), 16-byte chunks swizzled by the row
+      unsigned char* p_row = smem + kOffP + (size_t)half * kHalf + (size_t)r * 128;
 #pragma unroll
-      for (int chunk = 0; chunk < 16; ++chunk) {
-        const int where = (chunk & 7) ^ (r & 7);
-        *reinterpret_cast<uint4*>(p_row + (size_t)(chunk >> 3) * kHalf + where * 16) =
+      for (int chunk = 0; chunk < 8; ++chunk) {
+        const int where = chunk ^ (r & 7);
+        *reinterpret_cast<uint4*>(p_row + where * 16) =
             make_uint4(packed[4 * chunk], packed[4 * chunk + 1], packed[4 * chunk + 2], packed[4 * chunk + 3]);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tensor_fence_before_sync();
       barrier_arrive(bar(P_READY));
     }
+    // the row's denominator is the sum of its two threads' parts
+    exchange[0][half][r] = denominator;
+    asm volatile("bar.sync %0, 64;" ::"r"(5 + quarter) : "memory");
+    denominator += exchange[0][half ^ 1][r];
     if (alive && !wait_barrier(bar(PV_DONE), (uint32_t)(tiles - 1) & 1u)) { g_tc_attention_error = 3; alive = false; }
     tensor_fence_after_sync();
     if (alive) {
       const float inverse = denominator > 0.0f ? 1.0f / denominator : 0.0f;
-      bf16* dst = out + ((size_t)(q_begin + local0 + r) * heads + head) * kDim;
+      bf16* dst = out + ((size_t)(q_begin + local0 + r) * heads + head) * kDim + first;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kDim; c0 += 32) {
+      for (int c0 = 0; c0 < kDim / 2; c0 += 32) {
         float o[32];
-        tmem_load_32(tmem_o + lane_bits + c0, o);
+        tmem_load_32(tmem_o + lane_bits + first + c0, o);
         if (valid_row) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
