@@ -44,6 +44,41 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __rest
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = from_float<Tout>(src[c] * inverse * weight[c]);
 }
 
+// The same with 16-byte loads (hidden a multiple of 4); the second pass finds the row in L1.
+template <typename Tout>
+__global__ void rms_norm_vec4_kernel(const float* __restrict__ x, const float* __restrict__ weight,
+                                     Tout* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[32];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int row = blockIdx.x;
+  const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[row] : row) * hidden);
+  const float4* w4 = reinterpret_cast<const float4*>(weight);
+  const int quads = hidden >> 2;
+  float sum = 0.0f;
+  for (int c = threadIdx.x; c < quads; c += blockDim.x) {
+    const float4 v = src[c];
+    sum = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, sum))));
+  }
+  sum = block_sum(sum, scratch);
+  const float inverse = rsqrtf(sum / (float)hidden + eps);
+  Tout* dst = out + (size_t)row * hidden;
+  for (int c = threadIdx.x; c < quads; c += blockDim.x) {
+    const float4 v = src[c];
+    const float4 w = __ldg(w4 + c);
+    const float a = v.x * inverse * w.x, b = v.y * inverse * w.y, d = v.z * inverse * w.z, e = v.w * inverse * w.w;
+    if (sizeof(Tout) == 4) {
+      reinterpret_cast<float4*>(dst)[c] = make_float4(a, b, d, e);
+    } else {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(d, e);
+      uint2 packed;
+      packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(dst)[c] = packed;
+    }
+  }
+}
+
 // out[r, c] = silu(gu[r, c]) * gu[r, inter + c]; gu rows are [gate | up].
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
@@ -113,6 +148,14 @@ MIR_EXPORT int mir_rms_norm(int bf16, const float* x, const float* weight, void*
                             int hidden, float eps, cudaStream_t stream) {
   if (n_rows == 0) return MIR_OK;
   if (n_rows < 0 || hidden <= 0) { mir_set_error("rms_norm: bad sizes"); return MIR_BAD_ARGUMENT; }
+  if ((hidden & 3) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)weight & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    const int vec_threads = hidden >= 1024 ? 256 : 128;
+    if (bf16)
+      return mir_launch("rms_norm", rms_norm_vec4_kernel<__nv_bfloat16>, dim3(n_rows), dim3(vec_threads), 0, stream, 0,
+                        x, weight, (__nv_bfloat16*)out, rows, hidden, eps);
+    return mir_launch("rms_norm", rms_norm_vec4_kernel<float>, dim3(n_rows), dim3(vec_threads), 0, stream, 0, x, weight,
+                      (float*)out, rows, hidden, eps);
+  }
   const int threads = hidden >= 2048 ? 512 : 256;
   if (bf16)
     return mir_launch("rms_norm", rms_norm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, 0, x, weight,

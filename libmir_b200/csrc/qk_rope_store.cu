@@ -13,31 +13,53 @@
 
 using namespace mir;
 
-template <typename T>
+// Two consecutive elements as floats, and back.
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load2(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ void store2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store2(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+// One CTA per (token, slice of the token's heads): the token's cosines and sines are computed once into shared
+// memory, then each warp takes heads (query, key or value) of the slice.  PAIRED: head_dim is even and
+// rotary_dim a multiple of 4, so every lane works on two neighbouring elements (4- or 8-byte accesses).
+template <typename T, bool PAIRED>
 __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                      const int* __restrict__ slot_mapping, const float* __restrict__ inv_freq,
                                      const float* __restrict__ q_norm, const float* __restrict__ k_norm,
                                      T* __restrict__ k_pages, T* __restrict__ v_pages, int heads, int kv_heads,
-                                     int head_dim, int rotary_dim, float eps, int write_kv) {
+                                     int head_dim, int rotary_dim, float eps, int write_kv, int units_per_cta) {
+  extern __shared__ float angles[];                 // [half] cosines then [half] sines of this token
   grid_launch_dependents();
   grid_dependency_wait();
   const int token = blockIdx.x;
   const int lane = threadIdx.x & 31;
-  const int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int warps = gridDim.y * (blockDim.x >> 5);
+  const int warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int units = heads + 2 * kv_heads;
   const size_t row_width = (size_t)units * head_dim;
   T* row = qkv + (size_t)token * row_width;
   const float position = (float)positions[token];
   const int slot = slot_mapping ? slot_mapping[token] : -1;
   const int half = rotary_dim / 2;
+  for (int pair = threadIdx.x; pair < half; pair += blockDim.x)
+    sincosf(position * inv_freq[pair], &angles[half + pair], &angles[pair]);
+  __syncthreads();
+  const int unit_begin = blockIdx.y * units_per_cta, unit_end = min(units, unit_begin + units_per_cta);
 
-  for (int unit = warp; unit < units; unit += warps) {
+  for (int unit = unit_begin + warp; unit < unit_end; unit += warps) {
     T* src = row + (size_t)unit * head_dim;
     if (unit >= heads + kv_heads) {                 // a value head: copy to its page
       if (!write_kv || slot < 0) continue;
       T* dst = v_pages + ((size_t)slot * kv_heads + (unit - heads - kv_heads)) * head_dim;
-      for (int d = lane; d < head_dim; d += 32) dst[d] = src[d];
+      if ((head_dim * sizeof(T)) % 16 == 0 && ((uintptr_t)src & 15) == 0 && ((uintptr_t)dst & 15) == 0) {
+        const int chunks = head_dim * (int)sizeof(T) / 16;
+        for (int c = lane; c < chunks; c += 32) reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+      } else {
+        for (int d = lane; d < head_dim; d += 32) dst[d] = src[d];
+      }
       continue;
     }
     const bool is_query = unit < heads;
@@ -46,32 +68,79 @@ __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict_
     float inverse = 1.0f;
     if (norm) {
       float sum = 0.0f;
-      for (int d = lane; d < head_dim; d += 32) {
-        const float v = to_float(src[d]);
-        sum = fmaf(v, v, sum);
+      if (PAIRED) {
+        for (int d = 2 * lane; d < head_dim; d += 64) {
+          const float2 v = load2(src + d);
+          sum = fmaf(v.x, v.x, fmaf(v.y, v.y, sum));
+        }
+      } else {
+        for (int d = lane; d < head_dim; d += 32) {
+          const float v = to_float(src[d]);
+          sum = fmaf(v, v, sum);
+        }
       }
       sum = warp_sum(sum);
       inverse = rsqrtf(sum / (float)head_dim + eps);
     }
     T* dst = is_query ? src : k_pages + ((size_t)slot * kv_heads + (unit - heads)) * head_dim;
-    for (int pair = lane; pair < half; pair += 32) {
-      float first = to_float(src[pair]);
-      float second = to_float(src[pair + half]);
-      if (norm) {
-        first = first * inverse * norm[pair];
-        second = second * inverse * norm[pair + half];
+    if (PAIRED) {
+      for (int pair = 2 * lane; pair < half; pair += 64) {
+        float2 first = load2(src + pair), second = load2(src + pair + half);
+        if (norm) {
+          first.x *= inverse * norm[pair]; first.y *= inverse * norm[pair + 1];
+          second.x *= inverse * norm[pair + half]; second.y *= inverse * norm[pair + half + 1];
+        }
+        const float c0 = angles[pair], c1 = angles[pair + 1], s0 = angles[half + pair], s1 = angles[half + pair + 1];
+        store2(dst + pair, first.x * c0 - second.x * s0, first.y * c1 - second.y * s1);
+        store2(dst + pair + half, first.x * s0 + second.x * c0, first.y * s1 + second.y * c1);
       }
-      float sine, cosine;
-      sincosf(position * inv_freq[pair], &sine, &cosine);
-      dst[pair] = from_float<T>(first * cosine - second * sine);
-      dst[pair + half] = from_float<T>(first * sine + second * cosine);
-    }
-    for (int d = rotary_dim + lane; d < head_dim; d += 32) {
-      float v = to_float(src[d]);
-      if (norm) v = v * inverse * norm[d];
-      dst[d] = from_float<T>(v);
+      for (int d = rotary_dim + 2 * lane; d < head_dim; d += 64) {
+        float2 v = load2(src + d);
+        if (norm) { v.x *= inverse * norm[d]; v.y *= inverse * norm[d + 1]; }
+        store2(dst + d, v.x, v.y);
+      }
+    } else {
+      for (int pair = lane; pair < half; pair += 32) {
+        float first = to_float(src[pair]);
+        float second = to_float(src[pair + half]);
+        if (norm) {
+          first = first * inverse * norm[pair];
+          second = second * inverse * norm[pair + half];
+        }
+        const float cosine = angles[pair], sine = angles[half + pair];
+        dst[pair] = from_float<T>(first * cosine - second * sine);
+        dst[pair + half] = from_float<T>(first * sine + second * cosine);
+      }
+      for (int d = rotary_dim + lane; d < head_dim; d += 32) {
+        float v = to_float(src[d]);
+        if (norm) v = v * inverse * norm[d];
+        dst[d] = from_float<T>(v);
+      }
     }
   }
+}
+
+template <typename T>
+int launch_rope(T* qkv, const int* positions, const int* slot_mapping, const float* inv_freq, const float* q_norm,
+                const float* k_norm, T* k_pages, T* v_pages, int tokens, int heads, int kv_heads, int head_dim,
+                int rotary_dim, float eps, int write_kv, cudaStream_t stream) {
+  // few tokens: 4 warps per CTA and enough CTAs per token to give every head a warp; many tokens: one CTA of 8
+  // warps per token, so that the token's angles are computed once
+  const int units = heads + 2 * kv_heads;
+  const bool many = tokens >= 64;
+  const int threads = many ? 256 : 128;
+  const int units_per_cta = many ? units : 4;
+  const dim3 grid(tokens, (units + units_per_cta - 1) / units_per_cta);
+  const size_t smem = (size_t)rotary_dim * sizeof(float);
+  const bool paired = (head_dim % 2 == 0) && (rotary_dim % 4 == 0) && ((uintptr_t)qkv % (2 * sizeof(T)) == 0) &&
+                      ((uintptr_t)k_pages % (2 * sizeof(T)) == 0);
+  if (paired)
+    return mir_launch("qk_rope_store", qk_rope_store_kernel<T, true>, grid, dim3(threads), smem, stream, 0, qkv, positions,
+                      slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages, heads, kv_heads, head_dim, rotary_dim,
+                      eps, write_kv, units_per_cta);
+  return mir_launch("qk_rope_store", qk_rope_store_kernel<T, false>, grid, dim3(threads), smem, stream, 0, qkv, positions,
+                    slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages, heads, kv_heads, head_dim, rotary_dim, eps,
+                    write_kv, units_per_cta);
 }
 
 MIR_EXPORT int mir_qk_rope_store(int bf16, void* qkv, const int* positions, const int* slot_mapping,
@@ -85,15 +154,10 @@ MIR_EXPORT int mir_qk_rope_store(int bf16, void* qkv, const int* positions, cons
                   head_dim, rotary_dim);
     return MIR_BAD_ARGUMENT;
   }
-  // one warp per head (query, key or value) of a token: 4 warps per CTA, enough CTAs per token to cover them
-  const int units = heads + 2 * kv_heads;
-  const int threads = 128;
-  const dim3 grid(tokens, (units + 3) / 4);
+  if (rotary_dim > 8192) { mir_set_error("qk_rope_store: rotary_dim %d is too large", rotary_dim); return MIR_BAD_ARGUMENT; }
   if (bf16)
-    return mir_launch("qk_rope_store", qk_rope_store_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, 0,
-                      (__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, (__nv_bfloat16*)k_pages,
-                      (__nv_bfloat16*)v_pages, heads, kv_heads, head_dim, rotary_dim, eps, write_kv);
-  return mir_launch("qk_rope_store", qk_rope_store_kernel<float>, grid, dim3(threads), 0, stream, 0, (float*)qkv,
-                    positions, slot_mapping, inv_freq, q_norm, k_norm, (float*)k_pages, (float*)v_pages, heads,
-                    kv_heads, head_dim, rotary_dim, eps, write_kv);
+    return launch_rope((__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, (__nv_bfloat16*)k_pages,
+                       (__nv_bfloat16*)v_pages, tokens, heads, kv_heads, head_dim, rotary_dim, eps, write_kv, stream);
+  return launch_rope((float*)qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, (float*)k_pages, (float*)v_pages,
+                     tokens, heads, kv_heads, head_dim, rotary_dim, eps, write_kv, stream);
 }
