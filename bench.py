@@ -286,7 +286,9 @@ def main() -> int:
     prefill_flops = gemm_flops + attention_flops
 
     if args.phase == "decode":
-        device_value, device_ms, launches, _, _ = decode_device(args.batch, args.steps, args.warmup)
+        device_value = device_ms = launches = 0.0
+        if not args.no_graphs:
+            device_value, device_ms, launches, _, _ = decode_device(args.batch, args.steps, args.warmup)
         tokens_per_second, _, _ = decode_e2e(args.batch, args.steps, args.warmup, profile=True)
         print(json.dumps({"phase": "decode", "batch": args.batch, "steps": args.steps, "layers": layers,
                           "graphs": not args.no_graphs, "tokens_per_second": round(tokens_per_second, 1),

@@ -1,0 +1,365 @@
+// bf16 matrix products for FEW rows (1 to 128 tokens: decode steps and short portions) on tcgen05, built to
+// stream the weights at memory speed:
+//
+//   out[M, N] = epilogue(x[M, K] . w[N, K]^T)
+//
+// The roles of the operands are swapped against the many-rows kernel: a tile of 128 weight rows is the A operand
+// (M = 128 of the instruction), the tokens are the B operand (N = tokens rounded up to 16), so the tensor cores
+// are fed whole 16 KB boxes of weights and a few hundred bytes of activations per step, and the accumulator
+// D[128 features, tokens] in tensor memory is the transposed output tile.
+//
+//   producer   one thread: per 64-wide step of K one TMA box of weights (128 rows x 64; with the SwiGLU epilogue 64
+//              gate rows and the 64 up rows that belong to them) and one of activations into a ring of stages.
+//   issuer     one thread: four tcgen05.mma (128 x tokens x 16) per stage, tcgen05.commit frees the stage.
+//   epilogue   four warps: read the accumulator (lane = feature), transpose it through shared memory.
+//
+// K is cut over a cluster of 1, 2, 4 or 8 CTAs so that 150 to 444 CTAs run whatever the shape (three fit on an SM;
+// what counts is that together they keep enough bytes in flight, not how they spread over the SMs).  Each
+// CTA of the cluster then finishes a share of the tokens: it adds the partial tiles over distributed shared
+// memory in rank order and applies the epilogue: store bf16 / accumulate into the 32-bit residual / 32-bit store / SwiGLU, bias, and the two halves
+// of a folded RMSNorm (scale each token's results by rsqrt(mean of squares + eps) of its input; leave the sums
+// of squares and the weighted bf16 copy of the rows it updates).  Waits on mbarriers are bounded in time.
+// libmir takes these products from a library (cuda/src/backend/linear/mod.rs:141-194).
+#include <algorithm>
+#include <cooperative_groups.h>
+#include "tcgen05.cuh"
+
+namespace cg = cooperative_groups;
+using namespace mir;
+using namespace mir::tc;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+constexpr int kStepK = 64;
+constexpr int kWeightBytes = 128 * 128;     // a stage's weights: 128 rows of 128 bytes
+constexpr int kMaxStages = 8;
+constexpr int kThreads = 6 * 32;            // producer warp, issuer warp, four epilogue warps
+constexpr int kRingBytes = 72 * 1024;       // per CTA, so that three CTAs fit on an SM
+int g_ring_bytes = kRingBytes;               // for measurements
+enum Epilogue : int { STORE = 0, ACCUM = 1, F32 = 2, SWIGLU = 3 };
+
+__device__ int g_tc_stream_error = 0;
+
+struct StreamNorm {
+  const float* sumsq;        // consumer: [sumsq_tiles][16] partial sums of squares of x's rows before weighting
+  int sumsq_tiles;
+  float eps;
+  float* sumsq_out;          // producer (ACCUM): [ceil(n / 16)][16] partial sums of squares of the rows it updates
+  const float* next_weight;  // producer: [n] weight of the norm that follows, or null
+  bf16* weighted_out;        // producer: [m, ld_weighted] bf16(new residual * next_weight)
+  int ld_weighted;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 3)
+tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
+                 const void* __restrict__ bias, void* __restrict__ out, int ldo, int m, int n, int k, int up_offset,
+                 int tokens, int stages, int stage_stride, uint32_t tmem_columns, StreamNorm norm) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long barriers[2 * kMaxStages + 1];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ float scale[16];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int splits = gridDim.y, split = blockIdx.y;           // the cluster spans gridDim.y
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int TILE_ROWS = MODE == SWIGLU ? 64 : 128;        // output features per CTA
+  const int n0 = blockIdx.x * TILE_ROWS;
+  const int total_steps = (k + kStepK - 1) / kStepK;
+  const int per_split = (total_steps + splits - 1) / splits;
+  const int step_begin = split * per_split;
+  const int my_steps = max(0, min(total_steps, step_begin + per_split) - step_begin);
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t full0 = smem_u32(&barriers[0]), empty0 = smem_u32(&barriers[kMaxStages]);
+  const uint32_t done = smem_u32(&barriers[2 * kMaxStages]);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      barrier_init(full0 + 8 * s, 1);
+      barrier_init(empty0 + 8 * s, 1);
+    }
+    barrier_init(done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"(tmem_columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tensor_fence_before_sync();
+  __syncthreads();
+  tensor_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+  grid_launch_dependents();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      const uint32_t stage_bytes = (uint32_t)kWeightBytes + (uint32_t)tokens * 128u;
+      bool waited = false;
+      for (int i = 0; i < my_steps; ++i) {
+        const int stage = i % stages;
+        const uint32_t parity = (uint32_t)(i / stages) & 1u;
+        if (!wait_barrier(empty0 + 8 * stage, parity ^ 1u)) { g_tc_stream_error = 1; break; }
+        const uint32_t barrier = full0 + 8 * stage;
+        const uint32_t dst = smem_base + (uint32_t)stage * (uint32_t)stage_stride;
+        const int k0 = (step_begin + i) * kStepK;
+        barrier_expect_bytes(barrier, stage_bytes);
+        if (MODE == SWIGLU) {
+          tma_load_2d(dst, &w_map, barrier, k0, n0);
+          tma_load_2d(dst + kWeightBytes / 2, &w_map, barrier, k0, up_offset + n0);
+        } else {
+          tma_load_2d(dst, &w_map, barrier, k0, n0);
+        }
+        // the weights belong to no kernel; the activations come from the kernel before this one
+        if (!waited) { grid_dependency_wait(); waited = true; }
+        tma_load_2d(dst + kWeightBytes, &x_map, barrier, k0, 0);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ issuer
+    if (lane == 0) {
+      const uint32_t idesc = instruction_descriptor(128, tokens);
+      bool alive = true;
+      for (int i = 0; i < my_steps; ++i) {
+        const int stage = i % stages;
+        const uint32_t parity = (uint32_t)(i / stages) & 1u;
+        if (alive && !wait_barrier(full0 + 8 * stage, parity)) { g_tc_stream_error = 2; alive = false; }
+        tensor_fence_after_sync();
+        const uint32_t a_base = smem_base + (uint32_t)stage * (uint32_t)stage_stride;
+        const uint32_t b_base = a_base + kWeightBytes;
+#pragma unroll
+        for (int kk = 0; kk < kStepK / 16; ++kk)
+          mma_bf16_ss(tmem_base, operand_descriptor(a_base + kk * 32), operand_descriptor(b_base + kk * 32), idesc,
+                      (i > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(empty0 + 8 * stage);
+      }
+      mma_commit(done);
+    }
+  }
+  // ---------------------------------------------------------------------- the tile, transposed, into shared memory
+  // (the ring is free once `done` has completed: every box has landed and every product has read it)
+  float* tile = reinterpret_cast<float*>(smem);               // [tokens][128]
+  if (warp >= 2) {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                      // feature row of the tile = accumulator lane
+    const bool alive = wait_barrier(done, 0);
+    if (!alive) g_tc_stream_error = 3;
+    tensor_fence_after_sync();
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+    for (int c0 = 0; c0 < tokens; c0 += 16) {
+      float v[16];
+      tmem_load_16(lane_base + c0, v);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) tile[(size_t)(c0 + i) * 128 + row] = (alive && my_steps > 0) ? v[i] : 0.0f;
+    }
+    tensor_fence_before_sync();
+  }
+  grid_dependency_wait();                                     // `out` (residual) and the sums belong to earlier kernels
+  cluster.sync();                                             // every CTA's partial tile is in its shared memory
+  // Every CTA of the cluster finishes a share of the tokens (token = split, split + splits, ...): it adds the
+  // cluster's partial tiles over distributed shared memory in rank order and applies the epilogue.
+  if (warp >= 2) {
+    const int tid = threadIdx.x - 64;                         // 0..127
+    // per token: 1, or the folded norm's rsqrt(mean of squares + eps): 8 threads per token add the tiles' sums
+    if (tid < 16) scale[tid] = 1.0f;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (norm.sumsq != nullptr) {
+      const int token = tid >> 3, part = tid & 7;
+      float sum = 0.0f;
+      if (token < m)
+        for (int t = part; t < norm.sumsq_tiles; t += 8) sum += norm.sumsq[t * 16 + token];
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (part == 0) scale[token] = rsqrtf(sum / (float)k + norm.eps);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+    const float* peers[8];
+#pragma unroll
+    for (int rank = 0; rank < 8; ++rank) peers[rank] = cluster.map_shared_rank(tile, rank < splits ? rank : 0);
+    auto cluster_sum = [&](int token, int row) {
+      float parts[8];
+#pragma unroll
+      for (int rank = 0; rank < 8; ++rank) parts[rank] = rank < splits ? peers[rank][(size_t)token * 128 + row] : 0.0f;
+      float total = parts[0];
+#pragma unroll
+      for (int rank = 1; rank < 8; ++rank) total += parts[rank];
+      return total;
+    };
+    // four tokens at a time, so that their loads (partial tiles, the old residual) are in flight together
+    constexpr int BATCH = 4;
+    if (MODE == SWIGLU) {
+      // 64 features per tile: the two halves of the threads take alternate tokens of this CTA's share
+      const int feature = tid & 63, column = n0 + feature;
+      const int stride = 2 * splits;
+      for (int token0 = split + splits * (tid >> 6); token0 < m; token0 += BATCH * stride) {
+        float gate[BATCH], up[BATCH];
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) {
+          const int token = token0 + j * stride;
+          gate[j] = token < m ? cluster_sum(token, feature) : 0.0f;
+          up[j] = token < m ? cluster_sum(token, 64 + feature) : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) {
+          const int token = token0 + j * stride;
+          if (token < m && column < n) {
+            const float s = token < 16 ? scale[token] : 1.0f;
+            const float g = gate[j] * s;
+            reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * (up[j] * s));
+          }
+        }
+      }
+    } else {
+      const int column = n0 + tid;
+      const bool in_range = column < n;
+      float extra = 0.0f;
+      if (bias != nullptr && in_range)
+        extra = MODE == STORE ? __bfloat162float(reinterpret_cast<const bf16*>(bias)[column]) : reinterpret_cast<const float*>(bias)[column];
+      for (int token0 = split; token0 < m; token0 += BATCH * splits) {
+        float value[BATCH], old[BATCH];
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) {
+          const int token = token0 + j * splits;
+          value[j] = token < m ? cluster_sum(token, tid) : 0.0f;
+          old[j] = (MODE == ACCUM && token < m && in_range) ? reinterpret_cast<const float*>(out)[(size_t)token * ldo + column] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) {
+          const int token = token0 + j * splits;
+          if (token >= m) break;                              // the same for every thread
+          const float result = value[j] * (token < 16 ? scale[token] : 1.0f) + extra + old[j];
+          if (in_range) {
+            if (MODE == STORE) {
+              reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(result);
+            } else {
+              reinterpret_cast<float*>(out)[(size_t)token * ldo + column] = result;
+              if (MODE == ACCUM && norm.weighted_out != nullptr)
+                norm.weighted_out[(size_t)token * norm.ld_weighted + column] = __float2bfloat16_rn(result * norm.next_weight[column]);
+            }
+          }
+          if (MODE == ACCUM && norm.sumsq_out != nullptr && token < 16) {
+            // sum of squares of 16 neighbouring new residual values of this token (16 consecutive lanes)
+            float square = in_range ? result * result : 0.0f;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
+            if ((tid & 15) == 0 && column < n) norm.sumsq_out[(size_t)(column >> 4) * 16 + token] = square;
+          }
+        }
+      }
+    }
+  }
+  cluster.sync();                                             // peers keep their shared memory until it was read
+  __syncthreads();
+  if (warp == 1) {
+    tensor_fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_columns) : "memory");
+  }
+}
+
+int g_forced_splits = 0;                                      // for measurements: 0 = choose
+
+template <int MODE>
+int launch(const void* x, int ldx, const void* w, const void* bias, void* out, int ldo, int m, int n, int k,
+           int up_offset, const StreamNorm& norm, cudaStream_t stream) {
+  constexpr int TILE_ROWS = MODE == SWIGLU ? 64 : 128;
+  const int tokens = (m + 15) / 16 * 16;
+  CUtensorMap w_map, x_map;
+  int status = tensor_map_for(w, MODE == SWIGLU ? up_offset + n : n, k, k, TILE_ROWS, &w_map);
+  if (status != MIR_OK) return status;
+  status = tensor_map_for(x, m, k, ldx, tokens, &x_map);
+  if (status != MIR_OK) return status;
+  const int stage_stride = (kWeightBytes + tokens * 128 + 1023) / 1024 * 1024;
+  const int tile_bytes = tokens * 128 * 4;                    // the transposed tile reuses the ring
+  int stages = std::max(2, std::min(kMaxStages, g_ring_bytes / stage_stride));
+  while (stages * stage_stride < tile_bytes) ++stages;        // at most 4 (128 tokens: 32 KB stages, 64 KB tile)
+  const size_t smem = (size_t)stages * stage_stride + 1024;
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t err = cudaFuncSetAttribute(tc_stream_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 225 * 1024);
+    if (err != cudaSuccess) {
+      mir_set_error("tc_stream: cannot reserve shared memory: %s", cudaGetErrorString(err));
+      return MIR_CUDA_ERROR;
+    }
+    configured = true;
+  }
+  const int tiles = (n + TILE_ROWS - 1) / TILE_ROWS;
+  const int total_steps = (k + kStepK - 1) / kStepK;
+  int splits = 1;                                             // 1, 2, 4 or 8 CTAs share K: up to 444 CTAs, one wave
+  while (splits < 8 && tiles * splits * 2 <= 3 * 148 && total_steps / (splits * 2) >= 4) splits *= 2;
+  if (g_forced_splits > 0) splits = g_forced_splits;
+  uint32_t tmem_columns = 32;
+  while ((int)tmem_columns < tokens) tmem_columns *= 2;
+  return mir_launch("tc_stream", tc_stream_kernel<MODE>, dim3(tiles, splits), dim3(kThreads), smem, stream, splits, w_map,
+                    x_map, bias, out, ldo, m, n, k, up_offset, tokens, stages, stage_stride, tmem_columns, norm);
+}
+
+}  // namespace
+
+MIR_EXPORT int mir_gemm_tc_stream_error() {
+  int flag = 0;
+  if (cudaMemcpyFromSymbol(&flag, g_tc_stream_error, sizeof(int)) != cudaSuccess) return -1;
+  return flag;
+}
+
+MIR_EXPORT int mir_gemm_tc_stream_max_rows() { return 128; }
+
+// For measurements: 1, 2, 4 or 8 CTAs per cluster (0: the launcher chooses), and the ring's size in KB.
+MIR_EXPORT int mir_gemm_tc_stream_set_splits(int splits, int ring_kb) {
+  if ((splits != 0 && splits != 1 && splits != 2 && splits != 4 && splits != 8) || ring_kb < 32 || ring_kb > 200) {
+    mir_set_error("tc_stream: splits must be 0, 1, 2, 4 or 8 and the ring 32..200 KB");
+    return MIR_BAD_ARGUMENT;
+  }
+  g_forced_splits = splits;
+  g_ring_bytes = ring_kb * 1024;
+  return MIR_OK;
+}
+
+// Modes and the folded-norm arguments as in mir_gemm_skinny_bf16; 1 <= m <= 128, k and ldx multiples of 8, x and
+// w 16-byte aligned.  The sums of squares and the weighted rows are defined for up to 16 tokens.
+MIR_EXPORT int mir_gemm_tc_stream_bf16(int mode, const void* x, int ldx, const void* w, const void* bias, void* out,
+                                       int ldo, int m, int n, int k, int up_offset, const float* sumsq,
+                                       int sumsq_tiles, float eps, float* sumsq_out, const float* next_weight,
+                                       void* weighted_out, int ld_weighted, cudaStream_t stream) {
+  if (m == 0 || n == 0) return MIR_OK;
+  if (m < 0 || m > 128 || n < 0 || k <= 0 || (k % 8) || ldo < n || ((uintptr_t)w & 15) || (ldx % 8) || ldx < k ||
+      ((uintptr_t)x & 15) || x == nullptr) {
+    mir_set_error("tc_stream: needs 1..128 rows, k and the row stride multiples of 8 and 16-byte aligned operands "
+                  "(m %d n %d k %d ldx %d ldo %d)", m, n, k, ldx, ldo);
+    return MIR_BAD_ARGUMENT;
+  }
+  if ((sumsq_out != nullptr || weighted_out != nullptr) && (mode != ACCUM || m > 16)) {
+    mir_set_error("tc_stream: sums of squares and weighted rows are written by the accumulate epilogue for up to 16 rows");
+    return MIR_BAD_ARGUMENT;
+  }
+  if (sumsq != nullptr && (sumsq_tiles <= 0 || m > 16 || (mode != STORE && mode != SWIGLU))) {
+    mir_set_error("tc_stream: a folded norm needs its partial sums, up to 16 rows, and the store or SwiGLU epilogue");
+    return MIR_BAD_ARGUMENT;
+  }
+  if (weighted_out != nullptr && (next_weight == nullptr || sumsq_out == nullptr || ld_weighted < n)) {
+    mir_set_error("tc_stream: weighted rows need the next norm's weight, a row stride >= n, and sums of squares");
+    return MIR_BAD_ARGUMENT;
+  }
+  StreamNorm norm;
+  norm.sumsq = sumsq;
+  norm.sumsq_tiles = sumsq_tiles;
+  norm.eps = eps;
+  norm.sumsq_out = sumsq_out;
+  norm.next_weight = next_weight;
+  norm.weighted_out = (bf16*)weighted_out;
+  norm.ld_weighted = ld_weighted;
+  switch (mode) {
+    case STORE: return launch<STORE>(x, ldx, w, bias, out, ldo, m, n, k, 0, norm, stream);
+    case ACCUM: return launch<ACCUM>(x, ldx, w, bias, out, ldo, m, n, k, 0, norm, stream);
+    case F32: return launch<F32>(x, ldx, w, bias, out, ldo, m, n, k, 0, norm, stream);
+    case SWIGLU:
+      if (bias) { mir_set_error("tc_stream: the SwiGLU epilogue takes no bias"); return MIR_BAD_ARGUMENT; }
+      return launch<SWIGLU>(x, ldx, w, nullptr, out, ldo, m, n, k, up_offset, norm, stream);
+  }
+  mir_set_error("tc_stream: unknown mode %d", mode);
+  return MIR_BAD_ARGUMENT;
+}

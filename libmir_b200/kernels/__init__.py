@@ -53,6 +53,10 @@ _SIGNATURES = {
         "mir_prefill_attention_tc_error": [],
         "mir_gemm_skinny_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                  c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+        "mir_gemm_tc_stream_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                    c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+        "mir_gemm_tc_stream_error": [],
+        "mir_gemm_tc_stream_set_splits": [c_int, c_int],
         "mir_gemm_tc_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_void_p],
         "mir_gemm_tc_set_width": [c_int],
@@ -412,6 +416,9 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
             n = weight.shape[0]
             _require(weight.shape[1] == k and out.shape == (m, n) and out.stride(1) == 1 and weight.is_contiguous()
                      and xw.shape == (m, k) and xw.stride(1) == 1, "linear: shapes or strides do not fit")
+            if _few_rows_kernel(m, "store") == "stream":
+                stream_linear(xw, weight, out, bias, folded=lazy)
+                return False
             lib = library("bf16")
             _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_STORE, xw.data_ptr(), xw.stride(0), weight.data_ptr(),
                                                  _ptr(bias), out.data_ptr(), out.stride(0), m, n, k, 0,
@@ -449,6 +456,10 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
             _require(rows.dtype == torch.bfloat16 and rows.shape == (m, n) and rows.stride(1) == 1
                      and next_weight.dtype == torch.float32 and next_weight.numel() == n
                      and next_weight.is_contiguous(), "linear: weighted rows are bfloat16 [M, N], the weight float32 [N]")
+        if _few_rows_kernel(m, mode_name) == "stream":
+            stream_linear(x, weight, out, bias, accumulate=accumulate, sumsq_out=stats,
+                          weighted_out=(rows, next_weight) if rows is not None else None)
+            return stats is not None
         _check(lib, lib.mir_gemm_skinny_bf16(mode, x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias),
                                              out.data_ptr(), out.stride(0), m, n, k, 0, None, 0, 0.0, _ptr(stats),
                                              _ptr(next_weight), _ptr(rows), rows.stride(0) if rows is not None else 0,
@@ -497,6 +508,47 @@ def _tensor_core_ok(x: torch.Tensor, k: int) -> bool:
     return k % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and x.stride(1) == 1
 
 
+def stream_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                  accumulate: bool = False, swiglu: bool = False, folded: Optional["NormedResidual"] = None,
+                  sumsq_out: Optional[torch.Tensor] = None, weighted_out: Optional[tuple] = None) -> None:
+    """The tcgen05 weight-streaming product for 1 to 128 bfloat16 rows (see tensor_core_linear for the modes).
+    `folded`: x is folded.weighted and each token's results are scaled by the folded norm; `sumsq_out`,
+    `weighted_out` as in linear (accumulate, up to 16 rows)."""
+    if folded is not None:
+        x = folded.weighted
+    _cuda(x, weight, out, bias)
+    m, k = x.shape
+    _require(x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.is_contiguous()
+             and weight.shape[1] == k and x.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == m
+             and 0 < m <= STREAM_MAX_ROWS, "stream_linear: 1..128 bfloat16 rows x [M, K] and weight [N, K] are needed")
+    lib = library("bf16")
+    if swiglu:
+        inter = out.shape[1]
+        _require(weight.shape[0] == 2 * inter and out.dtype == torch.bfloat16 and bias is None and not accumulate,
+                 "stream_linear: the SwiGLU epilogue takes [2 I, K] weights, no bias, and writes bfloat16")
+        mode, n, up_offset = SKINNY_SWIGLU, inter, inter
+    else:
+        n, up_offset = weight.shape[0], 0
+        _require(out.shape[1] == n and (bias is None or bias.dtype == out.dtype)
+                 and (out.dtype == torch.float32 or not accumulate),
+                 "stream_linear: out must be [M, N]; bias shares its dtype; only float32 accumulates")
+        mode = SKINNY_STORE if out.dtype == torch.bfloat16 else (SKINNY_ACCUM if accumulate else SKINNY_F32)
+    rows, next_weight = weighted_out if weighted_out is not None else (None, None)
+    _check(lib, lib.mir_gemm_tc_stream_bf16(
+        mode, x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias), out.data_ptr(), out.stride(0), m, n, k,
+        up_offset, folded.sumsq.data_ptr() if folded is not None else None, folded.tiles if folded is not None else 0,
+        folded.eps if folded is not None else 0.0, _ptr(sumsq_out), _ptr(next_weight), _ptr(rows),
+        rows.stride(0) if rows is not None else 0, _stream()))
+
+
+STREAM_MAX_ROWS = 128
+
+
+def stream_linear_error() -> int:
+    """0, or which role of the weight-streaming product gave up a bounded wait (synchronises the device)."""
+    return int(library("bf16").mir_gemm_tc_stream_error())
+
+
 def tensor_core_linear_error() -> int:
     """0, or which role of the tcgen05 product gave up a bounded wait (synchronises the device)."""
     return int(library("bf16").mir_gemm_tc_error())
@@ -505,6 +557,21 @@ def tensor_core_linear_error() -> int:
 SKINNY_MAX_ROWS = 16
 SKINNY_MODES = {"store", "accum", "f32", "swiglu"}     # the few-rows epilogues in use; the rest go to the library
 SKINNY_STORE, SKINNY_ACCUM, SKINNY_F32, SKINNY_SWIGLU = 0, 1, 2, 3
+
+
+# Which of the two few-rows kernels runs a product of up to 16 rows.  Measured on B200 inside a CUDA graph at
+# Qwen3-4B sizes (us, tcgen05 weight-streaming kernel against the mma.sync kernel), 8 rows: QKV 10.7 / 13.5,
+# gate-up with SwiGLU 21.6 / 27.0, output head 123 / 179, but the accumulating products 9.3 / 8.7 and 14.3 / 13.9;
+# 16 rows: 10.3 / 15.3, 15.0 / 25.1, 11.7 / 19.7, 25.5 / 37.5.
+FEW_ROWS_KERNEL = {"store": "stream", "f32": "stream", "swiglu": "stream", "accum": "auto"}
+STREAM_ACCUM_MIN_ROWS = 9
+
+
+def _few_rows_kernel(m: int, mode_name: str) -> str:
+    choice = FEW_ROWS_KERNEL.get(mode_name, "skinny")
+    if choice == "auto":
+        return "stream" if m >= STREAM_ACCUM_MIN_ROWS else "skinny"
+    return choice
 
 
 def _skinny_ok(x: torch.Tensor, m: int, k: int) -> bool:
@@ -529,6 +596,9 @@ def gate_up_silu(x, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -
         xw = lazy.weighted
         if few and _skinny_ok(xw, m, k):
             _cuda(xw, w_gate_up, out, lazy.sumsq)
+            if _few_rows_kernel(m, "swiglu") == "stream":
+                stream_linear(xw, w_gate_up, out, swiglu=True, folded=lazy)
+                return
             lib = library("bf16")
             _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_SWIGLU, xw.data_ptr(), xw.stride(0), w_gate_up.data_ptr(), None,
                                                  out.data_ptr(), out.stride(0), m, inter, k, inter,
@@ -539,6 +609,9 @@ def gate_up_silu(x, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -
     _cuda(x, w_gate_up, out)
     _require(x.stride(1) == 1, "gate_up_silu: x rows must be contiguous")
     if few and x.dtype == torch.bfloat16 and _skinny_ok(x, m, k):
+        if _few_rows_kernel(m, "swiglu") == "stream":
+            stream_linear(x, w_gate_up, out, swiglu=True)
+            return
         lib = library("bf16")
         _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_SWIGLU, x.data_ptr(), x.stride(0), w_gate_up.data_ptr(), None,
                                              out.data_ptr(), out.stride(0), m, inter, k, inter, None, 0, 0.0, None,

@@ -461,3 +461,35 @@ def _rms_norm_kernel(residual, gain, eps):
     out = torch.empty(residual.shape, device="cuda", dtype=torch.bfloat16)
     kernels.rms_norm(residual, cuda(gain), eps, out)
     return out
+
+
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 77, 128])
+@pytest.mark.parametrize("n,k", [(136, 264), (50, 72), (2560, 1024), (1000, 4104)])
+def test_weight_streaming_product_and_its_epilogues(m, n, k):
+    """The tcgen05 product for 1 to 128 rows (weights as the A operand, K cut over a cluster): store with bias,
+    accumulate into the 32-bit residual, 32-bit output, a strided view as input, the SwiGLU epilogue; sizes that
+    are no multiples of its tiles; none of its bounded waits may have run out."""
+    from libmir_b200 import kernels
+    torch.manual_seed(m * n + k)
+    x, w = torch.randn(m, k).bfloat16(), (torch.randn(n, k) * 0.3).bfloat16()
+    exact = plain_impl.linear(x.double(), w)
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(n).bfloat16()
+    kernels.stream_linear(cuda(x), cuda(w), out, cuda(bias))
+    close(out, exact + bias.double(), torch.bfloat16, factor=2)
+    base = torch.randn(m, n)
+    residual = cuda(base.clone())
+    kernels.stream_linear(cuda(x), cuda(w), residual, accumulate=True)
+    close(residual, base.double() + exact, torch.float32, factor=40)       # bf16 products, 32-bit sums
+    logits = torch.empty(m, n, device="cuda")
+    float_bias = torch.randn(n)
+    kernels.stream_linear(cuda(x), cuda(w), logits, cuda(float_bias))
+    close(logits, exact + float_bias.double(), torch.float32, factor=40)
+    wide = cuda(torch.randn(m, k + 40).bfloat16())
+    kernels.stream_linear(wide[:, 16:16 + k], cuda(w), logits)
+    close(logits, plain_impl.linear(wide[:, 16:16 + k].double().cpu(), w), torch.float32, factor=40)
+    inter = n // 2
+    gated = torch.empty(m, inter, device="cuda", dtype=torch.bfloat16)
+    kernels.stream_linear(cuda(x), cuda(w[:2 * inter]), gated, swiglu=True)
+    close(gated, plain_impl.silu(exact[:, :inter]) * exact[:, inter:2 * inter], torch.bfloat16, factor=2)
+    assert kernels.stream_linear_error() == 0
