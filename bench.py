@@ -128,6 +128,8 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="only the batch-8 decode and the prefill")
     parser.add_argument("--decode-ctas-per-sm", type=int, default=None,
                         help="CTAs per SM that split decode attention aims for when it picks the partition size")
+    parser.add_argument("--set", action="append", default=[], metavar="NAME=VALUE",
+                        help="set a tuning constant of libmir_b200.kernels (an integer), e.g. STREAM_ACCUM_MIN_ROWS=1")
     parser.add_argument("--no-fold-norm", action="store_true",
                         help="run every RMSNorm as a kernel of its own instead of folding it into the few-rows "
                              "products around it")
@@ -137,7 +139,7 @@ def main() -> int:
     parser.add_argument("--no-graphs", action="store_true", help="decode steps as plain launches, not as CUDA graphs")
     parser.add_argument("--library-modes", default="", help="few-rows epilogues (store,accum,f32,swiglu) to run "
                         "through the library product instead (an experiment switch)")
-    parser.add_argument("--pdl", type=int, default=None, choices=[0, 1],
+    parser.add_argument("--pdl", type=int, default=None, choices=[0, 1, 2],
                         help="launch kernels with (1) or without (0) programmatic stream serialization")
     args = parser.parse_args()
 
@@ -160,9 +162,14 @@ def main() -> int:
     if args.library_modes:
         kernels.SKINNY_MODES -= set(args.library_modes.split(","))
     if args.pdl is not None:
-        kernels.set_programmatic_launch(bool(args.pdl))
+        kernels.set_programmatic_launch(args.pdl)
     if args.no_fold_norm:
         kernels.FUSE_NORM_INTO_PRODUCT = False
+    for item in args.set:
+        name, _, value = item.partition("=")
+        if not hasattr(kernels, name):
+            parser.error(f"libmir_b200.kernels has no constant {name}")
+        setattr(kernels, name, int(value))
     if args.decode_ctas_per_sm is not None:
         kernels.DECODE_CTAS_PER_SM = args.decode_ctas_per_sm
     peaks, peaks_kind = read_peaks()

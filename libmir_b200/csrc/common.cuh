@@ -24,10 +24,11 @@ int mir_check_launch(const char* what);
 // its writes are visible.  Every kernel launched through mir_launch calls grid_dependency_wait() before it
 // reads an activation or writes anything, so the order of memory effects is the order of the stream.
 bool mir_pdl_enabled();
+bool mir_pdl_for_streaming();   // also true in the mode that launches only the weight-streaming kernels this way
 
 template <typename... KernelArgs, typename... Args>
-int mir_launch(const char* what, void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
-               cudaStream_t stream, int cluster_y, Args... args) {
+int mir_launch_with(bool programmatic, const char* what, void (*kernel)(KernelArgs...), dim3 grid, dim3 block,
+                    size_t smem, cudaStream_t stream, int cluster_y, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
@@ -42,7 +43,7 @@ int mir_launch(const char* what, void (*kernel)(KernelArgs...), dim3 grid, dim3 
     attributes[count].val.clusterDim.z = 1;
     ++count;
   }
-  if (mir_pdl_enabled()) {
+  if (programmatic) {
     attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attributes[count].val.programmaticStreamSerializationAllowed = 1;
     ++count;
@@ -55,6 +56,12 @@ int mir_launch(const char* what, void (*kernel)(KernelArgs...), dim3 grid, dim3 
     return MIR_CUDA_ERROR;
   }
   return mir_check_launch(what);
+}
+
+template <typename... KernelArgs, typename... Args>
+int mir_launch(const char* what, void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+               cudaStream_t stream, int cluster_y, Args... args) {
+  return mir_launch_with(mir_pdl_enabled(), what, kernel, grid, block, smem, stream, cluster_y, args...);
 }
 
 namespace mir {

@@ -142,9 +142,33 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
   // ---------------------------------------------------------------------- the tile, transposed, into shared memory
   // (the ring is free once `done` has completed: every box has landed and every product has read it)
   float* tile = reinterpret_cast<float*>(smem);               // [tokens][128]
+  constexpr int BATCH = 4;                                    // tokens whose loads are in flight together
+  float old_first[BATCH] = {0.0f, 0.0f, 0.0f, 0.0f};          // ACCUM: the residual under this thread's first tokens
   if (warp >= 2) {
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;                      // feature row of the tile = accumulator lane
+    const int tid = threadIdx.x - 64;                         // 0..127
+    // While the products run: what the epilogue needs from earlier kernels.  Per token 1, or the folded norm's
+    // rsqrt(mean of squares + eps) (8 threads per token add the tiles' sums); and the old residual values.
+    grid_dependency_wait();
+    if (tid < 16) scale[tid] = 1.0f;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (norm.sumsq != nullptr) {
+      const int token = tid >> 3, part = tid & 7;
+      float sum = 0.0f;
+      if (token < m)
+        for (int t = part; t < norm.sumsq_tiles; t += 8) sum += norm.sumsq[t * 16 + token];
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (part == 0) scale[token] = rsqrtf(sum / (float)k + norm.eps);
+    }
+    if (MODE == ACCUM && n0 + tid < n) {
+#pragma unroll
+      for (int j = 0; j < BATCH; ++j) {
+        const int token = split + j * splits;
+        if (token < m) old_first[j] = reinterpret_cast<const float*>(out)[(size_t)token * ldo + n0 + tid];
+      }
+    }
     const bool alive = wait_barrier(done, 0);
     if (!alive) g_tc_stream_error = 3;
     tensor_fence_after_sync();
@@ -158,25 +182,11 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
     }
     tensor_fence_before_sync();
   }
-  grid_dependency_wait();                                     // `out` (residual) and the sums belong to earlier kernels
   cluster.sync();                                             // every CTA's partial tile is in its shared memory
   // Every CTA of the cluster finishes a share of the tokens (token = split, split + splits, ...): it adds the
   // cluster's partial tiles over distributed shared memory in rank order and applies the epilogue.
   if (warp >= 2) {
     const int tid = threadIdx.x - 64;                         // 0..127
-    // per token: 1, or the folded norm's rsqrt(mean of squares + eps): 8 threads per token add the tiles' sums
-    if (tid < 16) scale[tid] = 1.0f;
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (norm.sumsq != nullptr) {
-      const int token = tid >> 3, part = tid & 7;
-      float sum = 0.0f;
-      if (token < m)
-        for (int t = part; t < norm.sumsq_tiles; t += 8) sum += norm.sumsq[t * 16 + token];
-#pragma unroll
-      for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-      if (part == 0) scale[token] = rsqrtf(sum / (float)k + norm.eps);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-    }
     const float* peers[8];
 #pragma unroll
     for (int rank = 0; rank < 8; ++rank) peers[rank] = cluster.map_shared_rank(tile, rank < splits ? rank : 0);
@@ -190,7 +200,6 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
       return total;
     };
     // four tokens at a time, so that their loads (partial tiles, the old residual) are in flight together
-    constexpr int BATCH = 4;
     if (MODE == SWIGLU) {
       // 64 features per tile: the two halves of the threads take alternate tokens of this CTA's share
       const int feature = tid & 63, column = n0 + feature;
@@ -225,7 +234,8 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
         for (int j = 0; j < BATCH; ++j) {
           const int token = token0 + j * splits;
           value[j] = token < m ? cluster_sum(token, tid) : 0.0f;
-          old[j] = (MODE == ACCUM && token < m && in_range) ? reinterpret_cast<const float*>(out)[(size_t)token * ldo + column] : 0.0f;
+          old[j] = token0 == split ? old_first[j]
+                   : ((MODE == ACCUM && token < m && in_range) ? reinterpret_cast<const float*>(out)[(size_t)token * ldo + column] : 0.0f);
         }
 #pragma unroll
         for (int j = 0; j < BATCH; ++j) {
@@ -294,7 +304,7 @@ int launch(const void* x, int ldx, const void* w, const void* bias, void* out, i
   if (g_forced_splits > 0) splits = g_forced_splits;
   uint32_t tmem_columns = 32;
   while ((int)tmem_columns < tokens) tmem_columns *= 2;
-  return mir_launch("tc_stream", tc_stream_kernel<MODE>, dim3(tiles, splits), dim3(kThreads), smem, stream, splits, w_map,
+  return mir_launch_with(mir_pdl_for_streaming(), "tc_stream", tc_stream_kernel<MODE>, dim3(tiles, splits), dim3(kThreads), smem, stream, splits, w_map,
                     x_map, bias, out, ldo, m, n, k, up_offset, tokens, stages, stage_stride, tmem_columns, norm);
 }
 

@@ -23,10 +23,13 @@ MIR_EXPORT const char* mir_last_error() { return g_error; }
 
 MIR_EXPORT int mir_abi_version() { return 1; }
 
-static bool g_pdl = false;   // measured: inside captured decode steps it costs more than it hides
+// 0 off, 1 every kernel, 2 only the kernels that stream weights before they wait.  Measured inside captured
+// decode steps (Qwen3-4B sizes, batch 8): 3.37 ms off, 3.42 ms for every kernel, 3.25 ms for the streaming ones.
+static int g_pdl = 2;
 
-bool mir_pdl_enabled() { return g_pdl; }
+bool mir_pdl_enabled() { return g_pdl == 1; }
+bool mir_pdl_for_streaming() { return g_pdl >= 1; }
 
-// 1: kernels are launched with programmatic stream serialization; 0 (the default): plainly.
-MIR_EXPORT void mir_set_pdl(int enabled) { g_pdl = enabled != 0; }
-MIR_EXPORT int mir_get_pdl() { return g_pdl ? 1 : 0; }
+// Which kernels are launched with programmatic stream serialization: see g_pdl.
+MIR_EXPORT void mir_set_pdl(int mode) { g_pdl = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
+MIR_EXPORT int mir_get_pdl() { return g_pdl; }

@@ -92,14 +92,16 @@ def library(name: str) -> ctypes.CDLL:
     return lib
 
 
-def set_programmatic_launch(enabled: bool) -> None:
-    """Launch kernels with programmatic stream serialization (a kernel's start overlaps the previous kernel's
-    end; every kernel waits for its predecessor before it touches activations) or plainly."""
+def set_programmatic_launch(mode) -> None:
+    """How kernels are launched: 0 / False plainly; 1 / True all with programmatic stream serialization (a
+    kernel's start overlaps the previous kernel's end; every kernel waits for its predecessor before it touches
+    activations); 2 only the weight-streaming products, whose first weights are then on their way while the
+    kernel before them drains."""
     for name in ("core", "bf16"):
         lib = library(name)
         lib.mir_set_pdl.argtypes = [c_int]
         lib.mir_set_pdl.restype = None
-        lib.mir_set_pdl(int(enabled))
+        lib.mir_set_pdl(int(mode))
 
 
 def loaded_libraries() -> dict:
@@ -501,7 +503,7 @@ def tensor_core_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
 # From how many rows the tcgen05 kernel computes the gated feed-forward product.  Measured on B200 at K 2,560,
 # I 9,728: 2,048 rows 153 us against 175 us for the library product and the SiLU-multiply kernel, 512 rows 55
 # against 59, 128 rows 26 against 37, 32 rows 25 against 26.
-TENSOR_CORE_MIN_ROWS = 32
+TENSOR_CORE_MIN_ROWS = 128
 
 
 def _tensor_core_ok(x: torch.Tensor, k: int) -> bool:
