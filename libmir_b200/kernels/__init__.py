@@ -561,12 +561,15 @@ SKINNY_MODES = {"store", "accum", "f32", "swiglu"}     # the few-rows epilogues 
 SKINNY_STORE, SKINNY_ACCUM, SKINNY_F32, SKINNY_SWIGLU = 0, 1, 2, 3
 
 
-# Which of the two few-rows kernels runs a product of up to 16 rows.  Measured on B200 inside a CUDA graph at
-# Qwen3-4B sizes (us, tcgen05 weight-streaming kernel against the mma.sync kernel), 8 rows: QKV 10.7 / 13.5,
-# gate-up with SwiGLU 21.6 / 27.0, output head 123 / 179, but the accumulating products 9.3 / 8.7 and 14.3 / 13.9;
-# 16 rows: 10.3 / 15.3, 15.0 / 25.1, 11.7 / 19.7, 25.5 / 37.5.
+# Which of the two few-rows kernels runs a product of up to 16 rows: "stream" (tcgen05, TMA ring, launched so
+# that its weights load while the kernel before it drains) or "skinny" (mma.sync from registers).  Measured on
+# B200 inside a CUDA graph at Qwen3-4B sizes, 8 rows, each kernel alone (us, stream / skinny): QKV 10.6 / 13.5,
+# gate-up with SwiGLU 21.5 / 27.0, output head 122 / 179, output projection 9.0 / 8.7, down projection
+# 14.1 / 13.9; 16 rows: 10.3 / 15.3, 15.0 / 25.1, 11.7 / 19.7, 25.5 / 37.5.  In the whole decode step, where the
+# streaming kernel's early start counts, batch 8 takes 3.12 ms with it everywhere against 3.25 ms with the
+# accumulating products on the other kernel, and 3.73 ms without it.
 FEW_ROWS_KERNEL = {"store": "stream", "f32": "stream", "swiglu": "stream", "accum": "auto"}
-STREAM_ACCUM_MIN_ROWS = 9
+STREAM_ACCUM_MIN_ROWS = 1
 
 
 def _few_rows_kernel(m: int, mode_name: str) -> str:

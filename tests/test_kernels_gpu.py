@@ -339,12 +339,15 @@ def test_repetition_penalty_rewrites_the_rows_logits():
     assert device.cpu().tolist() == [[2.0, -2.0, 0.5, 1.5], [1.0, 1.0, -3.0, 0.0]]
 
 
+@pytest.mark.parametrize("which", ["stream", "skinny"])
 @pytest.mark.parametrize("m", [1, 5, 8, 9, 16, 17, 32, 33, 64, 65])
 @pytest.mark.parametrize("n,k", [(136, 264), (50, 72), (2560, 1024)])
-def test_few_rows_products_and_their_epilogues(m, n, k):
-    """1 to 64 bf16 rows run the weight-streaming kernel (65 the library): store, accumulate into the 32-bit
-    residual, 32-bit output, bias, and a strided view as input."""
+def test_few_rows_products_and_their_epilogues(m, n, k, which, monkeypatch):
+    """Up to 16 bf16 rows run one of the two few-rows kernels (tcgen05 weight streaming, or mma.sync from
+    registers), more run the library: store, accumulate into the 32-bit residual, 32-bit output, bias, and a
+    strided view as input."""
     from libmir_b200 import kernels
+    monkeypatch.setattr(kernels, "FEW_ROWS_KERNEL", {mode: which for mode in kernels.FEW_ROWS_KERNEL})
     torch.manual_seed(m * n + k)
     x, w = torch.randn(m, k).bfloat16(), (torch.randn(n, k) * 0.3).bfloat16()
     exact = plain_impl.linear(x.double(), w)
@@ -364,11 +367,15 @@ def test_few_rows_products_and_their_epilogues(m, n, k):
     close(logits, plain_impl.linear(wide[:, 16:16 + k].double().cpu(), w), torch.float32, factor=40)
 
 
+@pytest.mark.parametrize("which", ["stream", "skinny"])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("m,inter,k", [(1, 333, 72), (8, 9728 // 8, 320), (40, 200, 136), (64, 176, 264), (70, 96, 64),
                                        (130, 200, 136), (256, 333, 72), (300, 1216, 320)])
-def test_gate_up_silu(dtype, m, inter, k):
+def test_gate_up_silu(dtype, m, inter, k, which, monkeypatch):
     from libmir_b200 import kernels
+    if which == "skinny" and (m > 16 or dtype != torch.bfloat16):
+        pytest.skip("the choice of the few-rows kernel only matters for up to 16 bfloat16 rows")
+    monkeypatch.setattr(kernels, "FEW_ROWS_KERNEL", {mode: which for mode in kernels.FEW_ROWS_KERNEL})
     torch.manual_seed(m + inter)
     x = torch.randn(m, k).to(dtype)
     w = (torch.randn(2 * inter, k) * 0.2).to(dtype)
@@ -420,11 +427,13 @@ def test_tensor_core_product_refuses_what_it_cannot_take():
         kernels.tensor_core_linear(x, w, torch.empty(128, 64, device="cuda", dtype=torch.bfloat16))
 
 
+@pytest.mark.parametrize("which", ["stream", "skinny"])
 @pytest.mark.parametrize("m", [1, 8, 13])
-def test_norm_folded_into_the_few_rows_products_around_it(m):
+def test_norm_folded_into_the_few_rows_products_around_it(m, which, monkeypatch):
     """The accumulating product leaves the sums of squares of the new residual and its rows times the next
     norm's weight; the product after the norm scales its results: together they equal norm then product."""
     from libmir_b200 import kernels
+    monkeypatch.setattr(kernels, "FEW_ROWS_KERNEL", {mode: which for mode in kernels.FEW_ROWS_KERNEL})
     torch.manual_seed(m)
     hidden, inner, wide, eps = 264, 136, 200, 1e-5
     x = torch.randn(m, inner).bfloat16()
