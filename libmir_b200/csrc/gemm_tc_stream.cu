@@ -13,7 +13,7 @@
 //   issuer     one thread: four tcgen05.mma (128 x tokens x 16) per stage, tcgen05.commit frees the stage.
 //   epilogue   four warps: read the accumulator (lane = feature), transpose it through shared memory.
 //
-// K is cut over a cluster of 1, 2, 4 or 8 CTAs so that 150 to 444 CTAs run whatever the shape (three fit on an SM;
+// K is cut over a cluster of 1, 2, 4 or 8 CTAs so that up to 444 CTAs run whatever the shape (three fit on an SM;
 // what counts is that together they keep enough bytes in flight, not how they spread over the SMs).  Each
 // CTA of the cluster then finishes a share of the tokens: it adds the partial tiles over distributed shared
 // memory in rank order and applies the epilogue: store bf16 / accumulate into the 32-bit residual / 32-bit store / SwiGLU, bias, and the two halves
@@ -55,7 +55,7 @@ template <int MODE>
 __global__ void __launch_bounds__(kThreads, 3)
 tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                  const void* __restrict__ bias, void* __restrict__ out, int ldo, int m, int n, int k, int up_offset,
-                 int tokens, int stages, int stage_stride, uint32_t tmem_columns, StreamNorm norm) {
+                 int tokens, int tile_rows, int stages, int stage_stride, uint32_t tmem_columns, StreamNorm norm) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long barriers[2 * kMaxStages + 1];
   __shared__ uint32_t tmem_base_slot;
@@ -63,8 +63,11 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
   cg::cluster_group cluster = cg::this_cluster();
   const int splits = gridDim.y, split = blockIdx.y;           // the cluster spans gridDim.y
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int TILE_ROWS = MODE == SWIGLU ? 64 : 128;        // output features per CTA
-  const int n0 = blockIdx.x * TILE_ROWS;
+  // tile_rows output features per CTA (128, 64 or 32; with the SwiGLU epilogue 64 gate and 64 up rows).  The A
+  // operand always spans 128 rows of shared memory: rows beyond the tile hold whatever was there, and the
+  // accumulator rows they produce are never read.
+  const int n0 = blockIdx.x * tile_rows;
+  const uint32_t weight_bytes = (MODE == SWIGLU ? 128u : (uint32_t)tile_rows) * 128u;
   const int total_steps = (k + kStepK - 1) / kStepK;
   const int per_split = (total_steps + splits - 1) / splits;
   const int step_begin = split * per_split;
@@ -97,7 +100,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      const uint32_t stage_bytes = (uint32_t)kWeightBytes + (uint32_t)tokens * 128u;
+      const uint32_t stage_bytes = weight_bytes + (uint32_t)tokens * 128u;
       bool waited = false;
       for (int i = 0; i < my_steps; ++i) {
         const int stage = i % stages;
@@ -115,7 +118,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
         }
         // the weights belong to no kernel; the activations come from the kernel before this one
         if (!waited) { grid_dependency_wait(); waited = true; }
-        tma_load_2d(dst + kWeightBytes, &x_map, barrier, k0, 0);
+        tma_load_2d(dst + weight_bytes, &x_map, barrier, k0, 0);
       }
     }
   } else if (warp == 1) {
@@ -129,7 +132,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
         if (alive && !wait_barrier(full0 + 8 * stage, parity)) { g_tc_stream_error = 2; alive = false; }
         tensor_fence_after_sync();
         const uint32_t a_base = smem_base + (uint32_t)stage * (uint32_t)stage_stride;
-        const uint32_t b_base = a_base + kWeightBytes;
+        const uint32_t b_base = a_base + weight_bytes;
 #pragma unroll
         for (int kk = 0; kk < kStepK / 16; ++kk)
           mma_bf16_ss(tmem_base, operand_descriptor(a_base + kk * 32), operand_descriptor(b_base + kk * 32), idesc,
@@ -162,7 +165,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
       for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
       if (part == 0) scale[token] = rsqrtf(sum / (float)k + norm.eps);
     }
-    if (MODE == ACCUM && n0 + tid < n) {
+    if (MODE == ACCUM && tid < tile_rows && n0 + tid < n) {
 #pragma unroll
       for (int j = 0; j < BATCH; ++j) {
         const int token = split + j * splits;
@@ -224,7 +227,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
       }
     } else {
       const int column = n0 + tid;
-      const bool in_range = column < n;
+      const bool in_range = tid < tile_rows && column < n;
       float extra = 0.0f;
       if (bias != nullptr && in_range)
         extra = MODE == STORE ? __bfloat162float(reinterpret_cast<const bf16*>(bias)[column]) : reinterpret_cast<const float*>(bias)[column];
@@ -233,7 +236,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
 #pragma unroll
         for (int j = 0; j < BATCH; ++j) {
           const int token = token0 + j * splits;
-          value[j] = token < m ? cluster_sum(token, tid) : 0.0f;
+          value[j] = (token < m && in_range) ? cluster_sum(token, tid) : 0.0f;
           old[j] = token0 == split ? old_first[j]
                    : ((MODE == ACCUM && token < m && in_range) ? reinterpret_cast<const float*>(out)[(size_t)token * ldo + column] : 0.0f);
         }
@@ -256,7 +259,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
             float square = in_range ? result * result : 0.0f;
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
-            if ((tid & 15) == 0 && column < n) norm.sumsq_out[(size_t)(column >> 4) * 16 + token] = square;
+            if ((tid & 15) == 0 && in_range) norm.sumsq_out[(size_t)(column >> 4) * 16 + token] = square;
           }
         }
       }
@@ -272,21 +275,42 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
 
 int g_forced_splits = 0;                                      // for measurements: 0 = choose
 
+int g_forced_rows = 0;
+
+// Tile height and how many CTAs share K.  Measured on B200 (8 rows, inside a CUDA graph, us): whole 128-row tiles
+// beat 64- and 32-row tiles at every shape (QKV 9.0 / 15.5 / 18.1, output projection 7.7 / 10.5 / 11.5), and K is
+// best cut as far as one wave of CTAs allows (three fit on an SM): output projection 7.7 with 8 CTAs per tile,
+// 10.4 with 4, 16.8 with 2.
+void choose_shape(int n, int total_steps, bool swiglu, int* tile_rows, int* splits) {
+  const int rows = swiglu ? 64 : 128;
+  const int tiles = (n + rows - 1) / rows;
+  int s = 1;
+  while (s < 8 && tiles * s * 2 <= 3 * 148 && total_steps / (s * 2) >= 4) s *= 2;
+  *tile_rows = rows;
+  *splits = s;
+}
+
 template <int MODE>
 int launch(const void* x, int ldx, const void* w, const void* bias, void* out, int ldo, int m, int n, int k,
            int up_offset, const StreamNorm& norm, cudaStream_t stream) {
-  constexpr int TILE_ROWS = MODE == SWIGLU ? 64 : 128;
   const int tokens = (m + 15) / 16 * 16;
+  const int total_steps = (k + kStepK - 1) / kStepK;
+  int tile_rows, splits;
+  choose_shape(n, total_steps, MODE == SWIGLU, &tile_rows, &splits);
+  if (g_forced_splits > 0) splits = g_forced_splits;
+  if (g_forced_rows > 0 && MODE != SWIGLU) tile_rows = g_forced_rows;
   CUtensorMap w_map, x_map;
-  int status = tensor_map_for(w, MODE == SWIGLU ? up_offset + n : n, k, k, TILE_ROWS, &w_map);
+  int status = tensor_map_for(w, MODE == SWIGLU ? up_offset + n : n, k, k, tile_rows, &w_map);
   if (status != MIR_OK) return status;
   status = tensor_map_for(x, m, k, ldx, tokens, &x_map);
   if (status != MIR_OK) return status;
-  const int stage_stride = (kWeightBytes + tokens * 128 + 1023) / 1024 * 1024;
+  const int weight_bytes = (MODE == SWIGLU ? 128 : tile_rows) * 128;
+  const int stage_stride = (weight_bytes + tokens * 128 + 1023) / 1024 * 1024;
   const int tile_bytes = tokens * 128 * 4;                    // the transposed tile reuses the ring
   int stages = std::max(2, std::min(kMaxStages, g_ring_bytes / stage_stride));
-  while (stages * stage_stride < tile_bytes) ++stages;        // at most 4 (128 tokens: 32 KB stages, 64 KB tile)
-  const size_t smem = (size_t)stages * stage_stride + 1024;
+  while (stages * stage_stride < tile_bytes) ++stages;
+  // the A operand of the last stage reads 128 rows whatever the tile's height: room for that behind the ring
+  const size_t smem = (size_t)stages * stage_stride + std::max(0, kWeightBytes - stage_stride) + 1024;
   static bool configured = false;
   if (!configured) {
     const cudaError_t err = cudaFuncSetAttribute(tc_stream_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -297,15 +321,11 @@ int launch(const void* x, int ldx, const void* w, const void* bias, void* out, i
     }
     configured = true;
   }
-  const int tiles = (n + TILE_ROWS - 1) / TILE_ROWS;
-  const int total_steps = (k + kStepK - 1) / kStepK;
-  int splits = 1;                                             // 1, 2, 4 or 8 CTAs share K: up to 444 CTAs, one wave
-  while (splits < 8 && tiles * splits * 2 <= 3 * 148 && total_steps / (splits * 2) >= 4) splits *= 2;
-  if (g_forced_splits > 0) splits = g_forced_splits;
+  const int tiles = (n + tile_rows - 1) / tile_rows;
   uint32_t tmem_columns = 32;
   while ((int)tmem_columns < tokens) tmem_columns *= 2;
   return mir_launch_with(mir_pdl_for_streaming(), "tc_stream", tc_stream_kernel<MODE>, dim3(tiles, splits), dim3(kThreads), smem, stream, splits, w_map,
-                    x_map, bias, out, ldo, m, n, k, up_offset, tokens, stages, stage_stride, tmem_columns, norm);
+                    x_map, bias, out, ldo, m, n, k, up_offset, tokens, tile_rows, stages, stage_stride, tmem_columns, norm);
 }
 
 }  // namespace
@@ -318,13 +338,15 @@ MIR_EXPORT int mir_gemm_tc_stream_error() {
 
 MIR_EXPORT int mir_gemm_tc_stream_max_rows() { return 128; }
 
-// For measurements: 1, 2, 4 or 8 CTAs per cluster (0: the launcher chooses), and the ring's size in KB.
-MIR_EXPORT int mir_gemm_tc_stream_set_splits(int splits, int ring_kb) {
-  if ((splits != 0 && splits != 1 && splits != 2 && splits != 4 && splits != 8) || ring_kb < 32 || ring_kb > 200) {
-    mir_set_error("tc_stream: splits must be 0, 1, 2, 4 or 8 and the ring 32..200 KB");
+// For measurements: 1, 2, 4 or 8 CTAs per cluster, the ring's size in KB, the tile's height (0: the launcher chooses).
+MIR_EXPORT int mir_gemm_tc_stream_set_splits(int splits, int ring_kb, int tile_rows) {
+  if ((splits != 0 && splits != 1 && splits != 2 && splits != 4 && splits != 8) || ring_kb < 32 || ring_kb > 200 ||
+      (tile_rows != 0 && tile_rows != 32 && tile_rows != 64 && tile_rows != 128)) {
+    mir_set_error("tc_stream: splits must be 0, 1, 2, 4 or 8, the ring 32..200 KB, the tile 0, 32, 64 or 128 rows");
     return MIR_BAD_ARGUMENT;
   }
   g_forced_splits = splits;
+  g_forced_rows = tile_rows;
   g_ring_bytes = ring_kb * 1024;
   return MIR_OK;
 }
