@@ -120,6 +120,105 @@ __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict_
   }
 }
 
+// bf16, the whole head rotated (rotary_dim == head_dim), half a head a multiple of 8 elements: L = half / 8 lanes
+// take one head, each with two 16-byte pieces (elements 8 l .. 8 l + 7 and their partners half a head further),
+// so a warp works on 32 / L heads at once and every access is 16 bytes wide.
+template <int L>
+__global__ void qk_rope_store_wide_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                                          const int* __restrict__ slot_mapping, const float* __restrict__ inv_freq,
+                                          const float* __restrict__ q_norm, const float* __restrict__ k_norm,
+                                          __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
+                                          int heads, int kv_heads, float eps, int write_kv, int units_per_cta) {
+  constexpr int HALF = 8 * L, DIM = 2 * HALF, GROUPS = 32 / L;
+  __shared__ float angles[DIM];                      // [HALF] cosines then [HALF] sines of this token
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int token = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int group = lane / L, l = lane % L;
+  const int units = heads + 2 * kv_heads;
+  __nv_bfloat16* row = qkv + (size_t)token * units * DIM;
+  const float position = (float)positions[token];
+  const int slot = slot_mapping ? slot_mapping[token] : -1;
+  for (int pair = threadIdx.x; pair < HALF; pair += blockDim.x)
+    sincosf(position * inv_freq[pair], &angles[HALF + pair], &angles[pair]);
+  __syncthreads();
+  const int unit_begin = blockIdx.y * units_per_cta, unit_end = min(units, unit_begin + units_per_cta);
+  for (int base = unit_begin + warp * GROUPS; base < unit_end; base += warps * GROUPS) {
+    const int unit = base + group;
+    const bool active = unit < unit_end;
+    const bool is_query = unit < heads, is_value = unit >= heads + kv_heads;
+    const __nv_bfloat16* src = row + (size_t)unit * DIM;
+    uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
+    if (active) {
+      a = *reinterpret_cast<const uint4*>(src + 8 * l);
+      b = *reinterpret_cast<const uint4*>(src + HALF + 8 * l);
+    }
+    const bool writes = active && (is_query || (write_kv && slot >= 0));
+    __nv_bfloat16* dst = nullptr;
+    if (writes)
+      dst = is_query ? row + (size_t)unit * DIM
+                     : (is_value ? v_pages + ((size_t)slot * kv_heads + (unit - heads - kv_heads)) * DIM
+                                 : k_pages + ((size_t)slot * kv_heads + (unit - heads)) * DIM);
+    float fa[8], fb[8];
+    {
+      const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 x = __bfloat1622float2(ha[i]), y = __bfloat1622float2(hb[i]);
+        fa[2 * i] = x.x; fa[2 * i + 1] = x.y; fb[2 * i] = y.x; fb[2 * i + 1] = y.y;
+      }
+    }
+    const float* norm = (!active || is_value) ? nullptr : (is_query ? q_norm : k_norm);
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum = fmaf(fa[i], fa[i], fmaf(fb[i], fb[i], sum));
+#pragma unroll
+    for (int o = L / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);   // every lane takes part
+    if (norm) {
+      const float inverse = rsqrtf(sum / (float)DIM + eps);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        fa[i] *= inverse * norm[8 * l + i];
+        fb[i] *= inverse * norm[HALF + 8 * l + i];
+      }
+    }
+    if (!writes) continue;
+    if (!is_value) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float cosine = angles[8 * l + i], sine = angles[HALF + 8 * l + i];
+        const float first = fa[i], second = fb[i];
+        fa[i] = first * cosine - second * sine;
+        fb[i] = first * sine + second * cosine;
+      }
+      __nv_bfloat162* ha = reinterpret_cast<__nv_bfloat162*>(&a);
+      __nv_bfloat162* hb = reinterpret_cast<__nv_bfloat162*>(&b);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        ha[i] = __floats2bfloat162_rn(fa[2 * i], fa[2 * i + 1]);
+        hb[i] = __floats2bfloat162_rn(fb[2 * i], fb[2 * i + 1]);
+      }
+    }
+    *reinterpret_cast<uint4*>(dst + 8 * l) = a;                // a value head is copied as it is
+    *reinterpret_cast<uint4*>(dst + HALF + 8 * l) = b;
+  }
+}
+
+template <int L>
+int launch_rope_wide(__nv_bfloat16* qkv, const int* positions, const int* slot_mapping, const float* inv_freq,
+                     const float* q_norm, const float* k_norm, __nv_bfloat16* k_pages, __nv_bfloat16* v_pages, int tokens,
+                     int heads, int kv_heads, float eps, int write_kv, cudaStream_t stream) {
+  const int units = heads + 2 * kv_heads;
+  const bool many = tokens >= 256;                     // one CTA of 8 warps per token, else CTAs of 4 warps
+  const int threads = many ? 256 : 128;
+  const int units_per_cta = many ? units : 4 * (32 / L);
+  const dim3 grid(tokens, (units + units_per_cta - 1) / units_per_cta);
+  return mir_launch("qk_rope_store", qk_rope_store_wide_kernel<L>, grid, dim3(threads), 0, stream, 0, qkv, positions,
+                    slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages, heads, kv_heads, eps, write_kv, units_per_cta);
+}
+
 template <typename T>
 int launch_rope(T* qkv, const int* positions, const int* slot_mapping, const float* inv_freq, const float* q_norm,
                 const float* k_norm, T* k_pages, T* v_pages, int tokens, int heads, int kv_heads, int head_dim,
@@ -127,7 +226,7 @@ int launch_rope(T* qkv, const int* positions, const int* slot_mapping, const flo
   // few tokens: 4 warps per CTA and enough CTAs per token to give every head a warp; many tokens: one CTA of 8
   // warps per token, so that the token's angles are computed once
   const int units = heads + 2 * kv_heads;
-  const bool many = tokens >= 64;
+  const bool many = tokens >= 256;
   const int threads = many ? 256 : 128;
   const int units_per_cta = many ? units : 4;
   const dim3 grid(tokens, (units + units_per_cta - 1) / units_per_cta);
@@ -155,6 +254,20 @@ MIR_EXPORT int mir_qk_rope_store(int bf16, void* qkv, const int* positions, cons
     return MIR_BAD_ARGUMENT;
   }
   if (rotary_dim > 8192) { mir_set_error("qk_rope_store: rotary_dim %d is too large", rotary_dim); return MIR_BAD_ARGUMENT; }
+  if (bf16 && rotary_dim == head_dim && head_dim % 16 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pages & 15) == 0 &&
+      ((uintptr_t)v_pages & 15) == 0) {
+    __nv_bfloat16* q = (__nv_bfloat16*)qkv;
+    __nv_bfloat16* kp = (__nv_bfloat16*)k_pages;
+    __nv_bfloat16* vp = (__nv_bfloat16*)v_pages;
+    switch (head_dim / 16) {                             // lanes per head
+      case 1: return launch_rope_wide<1>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream);
+      case 2: return launch_rope_wide<2>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream);
+      case 4: return launch_rope_wide<4>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream);
+      case 8: return launch_rope_wide<8>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream);
+      case 16: return launch_rope_wide<16>(q, positions, slot_mapping, inv_freq, q_norm, k_norm, kp, vp, tokens, heads, kv_heads, eps, write_kv, stream);
+      default: break;                                    // other head sizes: the kernel below
+    }
+  }
   if (bf16)
     return launch_rope((__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, (__nv_bfloat16*)k_pages,
                        (__nv_bfloat16*)v_pages, tokens, heads, kv_heads, head_dim, rotary_dim, eps, write_kv, stream);
