@@ -56,6 +56,9 @@ _SIGNATURES = {
         "mir_gemm_tc_stream_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                     c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mir_gemm_tc_stream_error": [],
+        "mir_qkv_rope_store_tc_stream_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                              c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "mir_gemm_tc_stream_set_splits": [c_int, c_int, c_int],
         "mir_gemm_tc_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_void_p],
@@ -249,6 +252,51 @@ def qk_rope_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Opti
     _check(lib, lib.mir_qk_rope_store(_is_bf16(qkv), qkv.data_ptr(), positions.data_ptr(), _ptr(slot_mapping),
                                       _ptr(inv_freq), _ptr(q_norm), _ptr(k_norm), _ptr(k_pages), _ptr(v_pages),
                                       tokens, heads, kv_heads, head_dim, rotary_dim, eps, int(write_kv), _stream()))
+
+
+# Whether the QKV projection of a few rows does the per-head norm, the rotation and the cache write in its
+# epilogue (head_dim 128, the tcgen05 weight-streaming kernel): one kernel and one round trip of q, k, v less.
+# Measured on B200, Qwen3-4B sizes: 36 launches fewer per step but 3.14 ms against 3.11 ms at batch 8 and 2.45
+# against 2.41 ms at batch 1 (the longer tail of the projection costs more than the small kernel it saves): off.
+FUSE_ROPE_INTO_QKV = False
+
+
+def qkv_project_rope_store(x, w_qkv: torch.Tensor, b_qkv: Optional[torch.Tensor], qkv: torch.Tensor,
+                           positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+                           inv_freq: Optional[torch.Tensor], q_norm: Optional[torch.Tensor],
+                           k_norm: Optional[torch.Tensor], k_pages: Optional[torch.Tensor],
+                           v_pages: Optional[torch.Tensor], heads: int, kv_heads: int, head_dim: int, rotary_dim: int,
+                           eps: float, write_kv: bool = True) -> bool:
+    """qkv[:, :heads * head_dim] = rotate(norm(x . w_q^T + b)), keys and values likewise into their cache pages, in
+    ONE kernel, if the sizes allow it (up to 16 bfloat16 rows, head_dim 128, x plain or a NormedResidual); returns
+    False, having done nothing, if they do not: the caller then runs `linear` and `qk_rope_store`."""
+    lazy = x if isinstance(x, NormedResidual) else None
+    rows = lazy.weighted if lazy is not None else x
+    m, k = rows.shape
+    fits = (FUSE_ROPE_INTO_QKV and FEW_ROWS_KERNEL.get("store") == "stream" and head_dim == 128
+            and rows.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16 and qkv.dtype == torch.bfloat16
+            and 0 < m <= SKINNY_MAX_ROWS and _skinny_ok(rows, m, k) and w_qkv.is_contiguous()
+            and w_qkv.shape == ((heads + 2 * kv_heads) * head_dim, k) and qkv.stride(1) == 1
+            and qkv.shape == (m, w_qkv.shape[0]) and (b_qkv is None or b_qkv.dtype == torch.bfloat16)
+            and rotary_dim % 2 == 0 and 0 <= rotary_dim <= head_dim
+            and (not rotary_dim or (inv_freq is not None and inv_freq.dtype == torch.float32
+                                    and inv_freq.numel() == rotary_dim // 2))
+            and all(n is None or (n.dtype == torch.float32 and n.numel() == head_dim) for n in (q_norm, k_norm))
+            and positions.dtype == torch.int32 and positions.numel() >= m
+            and (not write_kv or (slot_mapping is not None and slot_mapping.dtype == torch.int32
+                                  and k_pages is not None and v_pages is not None and k_pages.dtype == torch.bfloat16
+                                  and v_pages.dtype == torch.bfloat16 and k_pages.is_contiguous()
+                                  and v_pages.is_contiguous())))
+    if not fits:
+        return False
+    _cuda(rows, w_qkv, b_qkv, qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages)
+    lib = library("bf16")
+    _check(lib, lib.mir_qkv_rope_store_tc_stream_bf16(
+        rows.data_ptr(), rows.stride(0), w_qkv.data_ptr(), _ptr(b_qkv), qkv.data_ptr(), qkv.stride(0), m, k,
+        lazy.sumsq.data_ptr() if lazy is not None else None, lazy.tiles if lazy is not None else 0,
+        lazy.eps if lazy is not None else 0.0, positions.data_ptr(), _ptr(slot_mapping), _ptr(inv_freq), _ptr(q_norm),
+        _ptr(k_norm), _ptr(k_pages), _ptr(v_pages), heads, kv_heads, head_dim, rotary_dim, eps, int(write_kv), _stream()))
+    return True
 
 
 def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,

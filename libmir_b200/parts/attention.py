@@ -73,13 +73,17 @@ class SoftmaxAttention(Mixer):
         s = self.spec
         tokens = x.shape[0]
         qkv = ctx.alloc((tokens, self.q_width + 2 * self.kv_width), self.env.dtype)
-        kernels.linear(x, self.w_qkv, qkv, self.b_qkv, alloc=ctx.alloc)
         group = ctx.groups[cache.group]
-        kernels.qk_rope_store(
-            qkv, ctx.positions, group.slot_mapping,
-            self.position.table if self.position is not None else None, self.q_norm, self.k_norm,
-            cache.k_pages, cache.v_pages, s.heads, s.kv_heads, s.head_dim,
-            self.position.rotary_dim if self.position is not None else 0, s.qk_norm_eps, write_kv=cache.writes)
+        table = self.position.table if self.position is not None else None
+        rotary_dim = self.position.rotary_dim if self.position is not None else 0
+        # a few rows: projection, per-head norm, rotation and cache write in one kernel where the sizes allow it
+        if not kernels.qkv_project_rope_store(x, self.w_qkv, self.b_qkv, qkv, ctx.positions, group.slot_mapping, table,
+                                              self.q_norm, self.k_norm, cache.k_pages, cache.v_pages, s.heads,
+                                              s.kv_heads, s.head_dim, rotary_dim, s.qk_norm_eps, write_kv=cache.writes):
+            kernels.linear(x, self.w_qkv, qkv, self.b_qkv, alloc=ctx.alloc)
+            kernels.qk_rope_store(qkv, ctx.positions, group.slot_mapping, table, self.q_norm, self.k_norm,
+                                  cache.k_pages, cache.v_pages, s.heads, s.kv_heads, s.head_dim, rotary_dim,
+                                  s.qk_norm_eps, write_kv=cache.writes)
         mixed = ctx.alloc((tokens, self.q_width), self.env.dtype)
         self.attend(ctx, group, cache, qkv, mixed)
         accumulate = getattr(ctx, "accumulate_with_stats", None)

@@ -502,3 +502,51 @@ def test_weight_streaming_product_and_its_epilogues(m, n, k):
     kernels.stream_linear(cuda(x), cuda(w[:2 * inter]), gated, swiglu=True)
     close(gated, plain_impl.silu(exact[:, :inter]) * exact[:, inter:2 * inter], torch.bfloat16, factor=2)
     assert kernels.stream_linear_error() == 0
+
+
+@pytest.mark.parametrize("m,rotary,norms,bias", [(1, 128, True, False), (8, 128, True, True), (13, 64, False, True),
+                                                 (16, 128, False, False), (5, 0, True, False)])
+def test_qkv_projection_with_norm_rotation_and_cache_write_in_its_epilogue(m, rotary, norms, bias):
+    """One kernel (head_dim 128, up to 16 rows) against the product followed by the q/k-norm + rope + cache
+    write kernel, and against the plain formulas; a row with a negative slot writes no key or value."""
+    from libmir_b200 import kernels
+    torch.manual_seed(m + rotary)
+    heads, kv_heads, dim, hidden, page = 6, 2, 128, 264, 8
+    units = heads + 2 * kv_heads
+    x = torch.randn(m, hidden).bfloat16()
+    w = (torch.randn(units * dim, hidden) * 0.1).bfloat16()
+    b = (torch.randn(units * dim) * 0.5).bfloat16() if bias else None
+    q_norm = (torch.rand(dim) + 0.5) if norms else None
+    k_norm = (torch.rand(dim) + 0.5) if norms else None
+    inv_freq = plain_impl.rope_inverse_frequencies(rotary, 10000.0, None).float() if rotary else None
+    positions = torch.randint(0, 3000, (m,), dtype=torch.int32)
+    slots = torch.randperm(4 * page)[:m].to(torch.int32)
+    if m > 1:
+        slots[m // 2] = -1
+    pools = [torch.full((4 * page, kv_heads, dim), 7.0).bfloat16() for _ in range(4)]
+    fused_k, fused_v, plain_k, plain_v = [cuda(p) for p in pools]
+    dev = lambda t: None if t is None else cuda(t)
+    fused = torch.zeros(m, units * dim, device="cuda", dtype=torch.bfloat16)
+    assert kernels.qkv_project_rope_store(cuda(x), cuda(w), dev(b), fused, cuda(positions), cuda(slots), dev(inv_freq),
+                                          dev(q_norm), dev(k_norm), fused_k, fused_v, heads, kv_heads, dim, rotary, 1e-6)
+    two = torch.zeros(m, units * dim, device="cuda", dtype=torch.bfloat16)
+    kernels.linear(cuda(x), cuda(w), two, dev(b))
+    kernels.qk_rope_store(two, cuda(positions), cuda(slots), dev(inv_freq), dev(q_norm), dev(k_norm), plain_k, plain_v,
+                          heads, kv_heads, dim, rotary, 1e-6)
+    assert kernels.stream_linear_error() == 0
+    # against the two-kernel path: the same up to one rounding of the projection to bf16
+    close(fused[:, :heads * dim], two[:, :heads * dim].double(), torch.bfloat16, factor=2)
+    close(fused_k, plain_k.double(), torch.bfloat16, factor=2)
+    close(fused_v, plain_v.double(), torch.bfloat16, factor=2)
+    assert torch.equal(fused_k[slots[slots >= 0].long()].cpu() == 7.0, plain_k[slots[slots >= 0].long()].cpu() == 7.0)
+    untouched = torch.ones(4 * page, dtype=torch.bool)
+    untouched[slots[slots >= 0].long()] = False
+    assert bool((fused_k[untouched.cuda()] == 7.0).all()) and bool((fused_v[untouched.cuda()] == 7.0).all())
+    # against the formulas
+    projected = plain_impl.linear(x.double(), w) + (b.double() if bias else 0.0)
+    q = projected[:, :heads * dim].reshape(m, heads, dim)
+    if norms:
+        q = plain_impl.rms_norm(q, q_norm, 1e-6)
+    if rotary:
+        q = plain_impl.rope(q, positions.long(), inv_freq)
+    close(fused[:, :heads * dim].reshape(m, heads, dim), q, torch.bfloat16, factor=2)
