@@ -233,7 +233,9 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
   const int head0 = kv_head * group + (blockIdx.y % group_tiles) * kDecodeHeads;
   const int valid_rows = min(kDecodeHeads, kv_head * group + group - head0);
   grid_launch_dependents();
-  grid_dependency_wait();                                     // the newest key was written by the kernel before
+  // Launched with programmatic stream serialization, this kernel may start while the kernel before it (which
+  // writes the newest key and value and rotates q) still runs.  Positions and block tables are older than that
+  // kernel, and so is every key but the newest: the first copies of old keys start before the wait.
   const int position = positions[row];
   if (position < 0) return;                                   // padding row of a captured batch
   const int context = position + 1;
@@ -250,7 +252,10 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
   const int my_begin = begin + warp * kDecodeTile;
   const int my_tiles = my_begin < part_end ? (part_end - my_begin + stride_keys - 1) / stride_keys : 0;
 
-  // the first copies are on their way before anything else is done
+  // the first copies are on their way before anything else is done; if one of them covers the newest key, the
+  // kernel that writes it has to be over first
+  const bool early = my_begin + (kDecodeStages - 2) * stride_keys + kDecodeTile <= position;
+  if (!early) grid_dependency_wait();
 #pragma unroll
   for (int j = 0; j < kDecodeStages - 1; ++j) {
     if (j < my_tiles) {
@@ -261,6 +266,7 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
     cp_async_commit();
   }
 
+  if (early) grid_dependency_wait();                          // q (and the newest key) come from the kernel before
   // Q fragments: rows 0..7 are the heads of the group, rows 8..15 are zero
   uint32_t qa[D / 16][4];
   {
@@ -574,7 +580,7 @@ int launch_decode(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages
   if (status != MIR_OK) return status;
   const int group = heads / kv_heads;
   const dim3 grid(num_partitions, kv_heads * ((group + kDecodeHeads - 1) / kDecodeHeads), rows);
-  status = mir_launch("decode_attention", decode_attention_kernel<D>, grid, dim3(kDecodeWarps * 32), smem, stream, 0,
+  status = mir_launch_with(mir_pdl_for_streaming(), "decode_attention", decode_attention_kernel<D>, grid, dim3(kDecodeWarps * 32), smem, stream, 0,
                       q, q_stride, k_pages, v_pages, block_table, table_width, positions, page_size, heads, kv_heads,
                       scale * 1.4426950408889634f, window, partition, num_partitions, partial_o, partial_ml, out);
   if (status != MIR_OK || num_partitions == 1) return status;

@@ -132,7 +132,6 @@ __global__ void qk_rope_store_wide_kernel(__nv_bfloat16* __restrict__ qkv, const
   constexpr int HALF = 8 * L, DIM = 2 * HALF, GROUPS = 32 / L;
   __shared__ float angles[DIM];                      // [HALF] cosines then [HALF] sines of this token
   grid_launch_dependents();
-  grid_dependency_wait();
   const int token = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int group = lane / L, l = lane % L;
@@ -140,8 +139,11 @@ __global__ void qk_rope_store_wide_kernel(__nv_bfloat16* __restrict__ qkv, const
   __nv_bfloat16* row = qkv + (size_t)token * units * DIM;
   const float position = (float)positions[token];
   const int slot = slot_mapping ? slot_mapping[token] : -1;
+  // positions and slots are older than the kernel before this one (the projection): the angles are computed
+  // while it may still be running, then this kernel waits for its rows
   for (int pair = threadIdx.x; pair < HALF; pair += blockDim.x)
     sincosf(position * inv_freq[pair], &angles[HALF + pair], &angles[pair]);
+  grid_dependency_wait();
   __syncthreads();
   const int unit_begin = blockIdx.y * units_per_cta, unit_end = min(units, unit_begin + units_per_cta);
   for (int base = unit_begin + warp * GROUPS; base < unit_end; base += warps * GROUPS) {
@@ -215,7 +217,7 @@ int launch_rope_wide(__nv_bfloat16* qkv, const int* positions, const int* slot_m
   const int threads = many ? 256 : 128;
   const int units_per_cta = many ? units : 4 * (32 / L);
   const dim3 grid(tokens, (units + units_per_cta - 1) / units_per_cta);
-  return mir_launch("qk_rope_store", qk_rope_store_wide_kernel<L>, grid, dim3(threads), 0, stream, 0, qkv, positions,
+  return mir_launch_with(mir_pdl_for_streaming(), "qk_rope_store", qk_rope_store_wide_kernel<L>, grid, dim3(threads), 0, stream, 0, qkv, positions,
                     slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages, heads, kv_heads, eps, write_kv, units_per_cta);
 }
 

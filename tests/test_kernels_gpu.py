@@ -506,10 +506,11 @@ def test_weight_streaming_product_and_its_epilogues(m, n, k):
 
 @pytest.mark.parametrize("m,rotary,norms,bias", [(1, 128, True, False), (8, 128, True, True), (13, 64, False, True),
                                                  (16, 128, False, False), (5, 0, True, False)])
-def test_qkv_projection_with_norm_rotation_and_cache_write_in_its_epilogue(m, rotary, norms, bias):
+def test_qkv_projection_with_norm_rotation_and_cache_write_in_its_epilogue(m, rotary, norms, bias, monkeypatch):
     """One kernel (head_dim 128, up to 16 rows) against the product followed by the q/k-norm + rope + cache
     write kernel, and against the plain formulas; a row with a negative slot writes no key or value."""
     from libmir_b200 import kernels
+    monkeypatch.setattr(kernels, "FUSE_ROPE_INTO_QKV", True)      # off by default (measured slower in a step)
     torch.manual_seed(m + rotary)
     heads, kv_heads, dim, hidden, page = 6, 2, 128, 264, 8
     units = heads + 2 * kv_heads
