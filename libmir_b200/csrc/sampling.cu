@@ -15,11 +15,14 @@
 // The ranked mode sorts 64-bit keys (orderable(score) << 32 | ~id) with a bitonic network in a
 // scratch buffer of rows * pow2ceil(vocab) keys that the caller provides.
 #include <cfloat>
+#include <cooperative_groups.h>
 #include "common.cuh"
 
+namespace cg = cooperative_groups;
 using namespace mir;
 
 constexpr int kThreads = 1024;
+constexpr int kSlices = 8;     // CTAs of a cluster that share the scan for a row's highest logit
 
 struct SampleOptions {   // one per row; mirrored by a numpy structured dtype on the host
   double draw;
@@ -127,17 +130,36 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
   __shared__ int found;
   grid_launch_dependents();
   grid_dependency_wait();
-  const int row = blockIdx.x;
+  // A cluster of kSlices CTAs per row: each finds the highest logit of its slice of the vocabulary, the first CTA
+  // takes the best of them out of distributed shared memory (ties to the lowest id, as one scan would) and goes
+  // on alone if the row is not greedy.
+  __shared__ float slice_value;
+  __shared__ int slice_index;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int row = blockIdx.x, slice = blockIdx.y;
   const SampleOptions opt = options[row];
   const float* l = logits + (size_t)row * ld;
 
+  const int per_slice = (vocab + kSlices - 1) / kSlices;
+  const int slice_begin = slice * per_slice, slice_end = min(vocab, slice_begin + per_slice);
   float best = -FLT_MAX;
   int best_index = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += kThreads) {
+  for (int i = slice_begin + threadIdx.x; i < slice_end; i += kThreads) {
     const float v = l[i];
     if (isfinite(v) && (v > best || (v == best && i < best_index))) { best = v; best_index = i; }
   }
   block_argmax(best, best_index, s_value, s_index);
+  if (threadIdx.x == 0) { slice_value = best; slice_index = best_index; }
+  cluster.sync();
+  if (slice == 0) {
+    for (int other = 1; other < kSlices; ++other) {
+      const float v = *cluster.map_shared_rank(&slice_value, other);
+      const int i = *cluster.map_shared_rank(&slice_index, other);
+      if (v > best || (v == best && i < best_index)) { best = v; best_index = i; }
+    }
+  }
+  cluster.sync();                                   // the other CTAs keep their shared memory until it was read
+  if (slice != 0) return;
   if (best_index == 0x7fffffff) best_index = 0;   // no finite logit: the host reports it
   if (is_greedy(opt)) {
     if (threadIdx.x == 0) tokens[row] = best_index;
@@ -227,7 +249,7 @@ MIR_EXPORT int mir_sample(const float* logits, long long ld, int rows, int vocab
                   sort_keys_capacity);
     return MIR_BAD_ARGUMENT;
   }
-  return mir_launch("sample", sample_kernel, dim3(rows), dim3(kThreads), 0, stream, 0, logits, (size_t)ld, vocab,
+  return mir_launch("sample", sample_kernel, dim3(rows, kSlices), dim3(kThreads), 0, stream, kSlices, logits, (size_t)ld, vocab,
                     (const SampleOptions*)options, needs_ranked ? (unsigned long long*)sort_keys : nullptr, padded,
                     tokens);
 }
