@@ -606,6 +606,9 @@ def tensor_core_linear_error() -> int:
 
 
 SKINNY_MAX_ROWS = 16
+# Up to how many rows a product runs a few-rows kernel rather than the library (the streaming kernel takes up to
+# 128; measured alone at 64 rows it loses to cuBLASLt: 12.2 / 8.5, 17.0 / 15.2, 14.9 / 8.2 us).
+FEW_ROWS_MAX = 16
 SKINNY_MODES = {"store", "accum", "f32", "swiglu"}     # the few-rows epilogues in use; the rest go to the library
 SKINNY_STORE, SKINNY_ACCUM, SKINNY_F32, SKINNY_SWIGLU = 0, 1, 2, 3
 
@@ -622,6 +625,8 @@ STREAM_ACCUM_MIN_ROWS = 1
 
 
 def _few_rows_kernel(m: int, mode_name: str) -> str:
+    if m > SKINNY_MAX_ROWS:
+        return "stream"                     # 17 .. FEW_ROWS_MAX rows: only the streaming kernel takes them
     choice = FEW_ROWS_KERNEL.get(mode_name, "skinny")
     if choice == "auto":
         return "stream" if m >= STREAM_ACCUM_MIN_ROWS else "skinny"
@@ -630,7 +635,8 @@ def _few_rows_kernel(m: int, mode_name: str) -> str:
 
 def _skinny_ok(x: torch.Tensor, m: int, k: int) -> bool:
     """Whether the few-rows kernel takes this product: up to 16 rows, 16-byte aligned rows of 8-element multiples."""
-    return (0 < m <= SKINNY_MAX_ROWS and k % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
+    return (0 < m <= min(FEW_ROWS_MAX, STREAM_MAX_ROWS) and k % 8 == 0 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0)
 
 
 def gate_up_silu(x, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -> None:
@@ -645,7 +651,8 @@ def gate_up_silu(x, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -
     inter = out.shape[1]
     _require(w_gate_up.shape == (2 * inter, k) and out.shape[0] == m and out.is_contiguous()
              and w_gate_up.is_contiguous(), "gate_up_silu: shapes do not fit")
-    few = (w_gate_up.dtype == torch.bfloat16 and 0 < m <= SKINNY_MAX_ROWS and k % 8 == 0 and "swiglu" in SKINNY_MODES)
+    few = (w_gate_up.dtype == torch.bfloat16 and 0 < m <= min(FEW_ROWS_MAX, STREAM_MAX_ROWS) and k % 8 == 0
+           and "swiglu" in SKINNY_MODES)
     if lazy is not None:
         xw = lazy.weighted
         if few and _skinny_ok(xw, m, k):
