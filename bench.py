@@ -37,6 +37,25 @@ QWEN3_4B = {
     "max_position_embeddings": 40960, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
     "tie_word_embeddings": True, "hidden_act": "silu",
 }
+LLAMA31_8B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256,
+    "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": False, "hidden_act": "silu",
+}
+QWEN3_32B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "hidden_size": 5120, "intermediate_size": 25600, "num_hidden_layers": 64,
+    "num_attention_heads": 64, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 151936,
+    "max_position_embeddings": 40960, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "tie_word_embeddings": False, "hidden_act": "silu",
+}
+SIZES = {"qwen3-4b": ("Qwen3-4B sizes (BASELINE.json configs[2])", QWEN3_4B),
+         "llama-3.1-8b": ("Llama-3.1-8B sizes (BASELINE.json configs[3])", LLAMA31_8B),
+         "qwen3-32b": ("Qwen3-32B sizes (BASELINE.json configs[4])", QWEN3_32B)}
 PROMPT_TOKENS = 2048
 GENERATED_TOKENS = 256
 PAGE_SIZE = 16
@@ -123,6 +142,8 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=128)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--sizes", default="qwen3-4b", choices=sorted(SIZES),
+                        help="layer sizes of the model (default: the headline configuration)")
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--skip-points", action="store_true", help="only the batch-8 decode and the prefill")
@@ -173,7 +194,8 @@ def main() -> int:
     if args.decode_ctas_per_sm is not None:
         kernels.DECODE_CTAS_PER_SM = args.decode_ctas_per_sm
     peaks, peaks_kind = read_peaks()
-    config = dict(QWEN3_4B)
+    sizes_name, sizes_config = SIZES[args.sizes]
+    config = dict(sizes_config)
     layers_full = config["num_hidden_layers"]
     if args.layers:
         config["num_hidden_layers"] = args.layers
@@ -318,15 +340,15 @@ def main() -> int:
             points[f"decode_b{batch}"] = round(decode_device(batch, args.steps, args.warmup)[0], 1)
 
     line = {
-        "metric": "decode tok/s at batch 8 (Qwen3-4B sizes, 2,048-token context, 1 B200)",
+        "metric": f"decode tok/s at batch {args.batch} ({sizes_name.split(' (')[0]}, 2,048-token context, 1 B200)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random token ids, random N(0,0.02) weights, random cache",
         "config": {
-            "model": "Qwen3-4B sizes (BASELINE.json configs[2])", "layers": layers, "layers_of_config": layers_full,
+            "model": sizes_name, "layers": layers, "layers_of_config": layers_full,
             "hidden": hidden, "heads": heads, "kv_heads": kv_heads, "head_dim": dim, "intermediate": inter,
             "vocab": vocab, "global_batch": args.batch, "seq_len": PROMPT_TOKENS + GENERATED_TOKENS,
-            "context_at_decode": round(context, 1), "page_size": PAGE_SIZE, "tied_embeddings": True,
+            "context_at_decode": round(context, 1), "page_size": PAGE_SIZE, "tied_embeddings": bool(config.get("tie_word_embeddings", False)),
             "parallelism": "1 GPU", "l2": "inputs larger than L2 (a step reads every weight and the cache)",
             "peaks": peaks_kind,
         },
