@@ -57,6 +57,7 @@ class Sequence_:
     reserved: int = 0                                 # length pages have been allocated for
     tables: List[List[int]] = field(default_factory=list)      # per group: page id or -1 per block
     first_live: List[int] = field(default_factory=list)        # per group: first block not yet released
+    serial: int = 0                                   # unique over the manager's life (ids and slots are reused)
 
 
 class CacheManager:
@@ -99,7 +100,9 @@ class CacheManager:
         if not self._free_slots:
             raise NoFreeSlot(f"all {self.max_requests} request slots are taken")
         slot = self._free_slots.pop()
-        sequence = Sequence_(request_id, slot, tables=[[] for _ in self.groups], first_live=[0] * len(self.groups))
+        self._serial = getattr(self, "_serial", 0) + 1
+        sequence = Sequence_(request_id, slot, tables=[[] for _ in self.groups], first_live=[0] * len(self.groups),
+                             serial=self._serial)
         self.live[request_id] = sequence
         self.fresh_slots.append(slot)
         return sequence

@@ -40,6 +40,7 @@ class DecodeGraph:
         self.runner = runner
         self.rows = rows
         self.widths = list(widths)
+        self._written = [[None] * rows for _ in self.widths]      # per group and row: what its table holds
         self.ranked = ranked
         device = runner.device
         groups = len(widths)
@@ -156,13 +157,28 @@ class DecodeGraph:
             records["draw"], records["temperature"], records["top_p"], records["top_k"] = 0.0, 0.0, 1.0, 0
         else:
             records[:n] = options
+        # Block tables only grow at the end (and lose their head to a window): a row whose request, length and
+        # first live block are what was written last time is left as it is.
         for g, width in enumerate(self.widths):
             table = self._host_part(4 + g).reshape(self.rows, width)
-            table[n:] = 0
+            written = self._written[g]
             for r, seq in enumerate(sequences):
                 blocks = seq.tables[g]
-                table[r, :len(blocks)] = blocks
-                table[r, len(blocks):] = -1
+                state = (seq.serial, len(blocks), seq.first_live[g])
+                if written[r] == state:
+                    continue
+                previous = written[r]
+                if previous is not None and previous[0] == seq.serial and previous[2] == seq.first_live[g] \
+                        and previous[1] <= len(blocks):
+                    table[r, previous[1]:len(blocks)] = blocks[previous[1]:]     # only the new blocks
+                else:
+                    table[r, :len(blocks)] = blocks
+                    table[r, len(blocks):] = -1
+                written[r] = state
+            for r in range(n, self.rows):
+                if written[r] is not None:
+                    table[r] = 0
+                    written[r] = None
         self.meta[:self._upload].copy_(self.staging, non_blocking=True)
         self._copied = torch.cuda.Event()
         self._copied.record()
