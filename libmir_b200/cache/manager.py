@@ -137,8 +137,10 @@ class CacheManager:
         if new_length < sequence.length:
             raise ValueError("a request cannot shrink")
         need = self.pages_needed(sequence, new_length)
-        for n, group, table in zip(need, self.groups, sequence.tables):
-            live_now = sum(1 for page in table if page >= 0)
+        for n, group, table, first in zip(need, self.groups, sequence.tables, sequence.first_live):
+            if n == 0:
+                continue
+            live_now = len(table) - first                    # the blocks before `first` were given back
             if live_now + n > group.pool.count:
                 raise KvCapacity(live_now + n, group.pool.count, f"group {group.index}")
             if n > group.pool.free:
