@@ -27,8 +27,8 @@ bool mir_pdl_enabled();
 bool mir_pdl_for_streaming();   // also true in the mode that launches only the weight-streaming kernels this way
 
 template <typename... KernelArgs, typename... Args>
-int mir_launch_with(bool programmatic, const char* what, void (*kernel)(KernelArgs...), dim3 grid, dim3 block,
-                    size_t smem, cudaStream_t stream, int cluster_y, Args... args) {
+int mir_launch_cluster(bool programmatic, const char* what, void (*kernel)(KernelArgs...), dim3 grid, dim3 block,
+                       size_t smem, cudaStream_t stream, dim3 cluster, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
@@ -36,11 +36,11 @@ int mir_launch_with(bool programmatic, const char* what, void (*kernel)(KernelAr
   config.stream = stream;
   cudaLaunchAttribute attributes[2];
   int count = 0;
-  if (cluster_y > 0) {
+  if (cluster.x * cluster.y * cluster.z > 1) {
     attributes[count].id = cudaLaunchAttributeClusterDimension;
-    attributes[count].val.clusterDim.x = 1;
-    attributes[count].val.clusterDim.y = (unsigned)cluster_y;
-    attributes[count].val.clusterDim.z = 1;
+    attributes[count].val.clusterDim.x = cluster.x;
+    attributes[count].val.clusterDim.y = cluster.y;
+    attributes[count].val.clusterDim.z = cluster.z;
     ++count;
   }
   if (programmatic) {
@@ -56,6 +56,13 @@ int mir_launch_with(bool programmatic, const char* what, void (*kernel)(KernelAr
     return MIR_CUDA_ERROR;
   }
   return mir_check_launch(what);
+}
+
+template <typename... KernelArgs, typename... Args>
+int mir_launch_with(bool programmatic, const char* what, void (*kernel)(KernelArgs...), dim3 grid, dim3 block,
+                    size_t smem, cudaStream_t stream, int cluster_y, Args... args) {
+  return mir_launch_cluster(programmatic, what, kernel, grid, block, smem, stream,
+                            dim3(1, cluster_y > 0 ? (unsigned)cluster_y : 1u, 1), args...);
 }
 
 template <typename... KernelArgs, typename... Args>
