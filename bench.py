@@ -151,6 +151,8 @@ def main() -> int:
                         help="CTAs per SM that split decode attention aims for when it picks the partition size")
     parser.add_argument("--set", action="append", default=[], metavar="NAME=VALUE",
                         help="set a tuning constant of libmir_b200.kernels (an integer), e.g. STREAM_ACCUM_MIN_ROWS=1")
+    parser.add_argument("--stream-shape", default=None, metavar="SPLITS,RING_KB,TILE_ROWS",
+                        help="fix the shape of the weight-streaming product (0 = chosen by the launcher), e.g. 0,56,0")
     parser.add_argument("--no-fold-norm", action="store_true",
                         help="run every RMSNorm as a kernel of its own instead of folding it into the few-rows "
                              "products around it")
@@ -191,6 +193,11 @@ def main() -> int:
         if not hasattr(kernels, name):
             parser.error(f"libmir_b200.kernels has no constant {name}")
         setattr(kernels, name, int(value))
+    if args.stream_shape:
+        splits, ring_kb, tile_rows = (int(v) for v in args.stream_shape.split(","))
+        lib = kernels.library("bf16")
+        if lib.mir_gemm_tc_stream_set_splits(splits, ring_kb, tile_rows) != 0:
+            parser.error(lib.mir_last_error().decode())
     if args.decode_ctas_per_sm is not None:
         kernels.DECODE_CTAS_PER_SM = args.decode_ctas_per_sm
     peaks, peaks_kind = read_peaks()
