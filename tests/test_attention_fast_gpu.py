@@ -230,3 +230,32 @@ def test_engine_uses_the_fast_kernels_and_matches_the_plain_model(tmp_path, fuse
               f"decode step {offset}")
         assert result.tokens.cpu().tolist() == [int(np.argmax(l)) for l in result.logits.cpu().numpy()]
     assert model.runner._graphs is not None and len(model.runner._graphs.graphs) >= 1
+
+
+def test_decode_attention_over_a_long_context():
+    """20,000 cached keys for one request beside a 3-key request: 40 partitions of 512 keys and their merge; one
+    far key dominates the long request's scores for some heads."""
+    from libmir_b200 import kernels
+    heads, kv_heads, dim, page = 8, 2, 128, 16
+    lengths = [20000, 3]
+    rng = np.random.default_rng(5)
+    torch.manual_seed(5)
+    scale = 1.0 / math.sqrt(dim)
+    qs = [torch.randn(n, heads, dim).to(BF16) for n in lengths]
+    ks = [torch.randn(n, kv_heads, dim).to(BF16) for n in lengths]
+    vs = [torch.randn(n, kv_heads, dim).to(BF16) for n in lengths]
+    ks[0][777, 0] = (qs[0][-1, 0].float() * 3.0).to(BF16)       # head 0's query meets its own direction far back
+    k_pool, v_pool, table = build_pool(ks, vs, page, rng)
+    rows = len(lengths)
+    q_rows = torch.cat([q[-1:] for q in qs]).reshape(rows, heads * dim)
+    packed = torch.cat([q_rows, torch.zeros(rows, 2 * kv_heads * dim, dtype=BF16)], dim=1).contiguous()
+    positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32)
+    partition, count = kernels.decode_partitioning(rows, kv_heads, max(lengths))
+    assert count >= 40
+    scratch = torch.empty(kernels.decode_attention_scratch_floats(rows, heads, dim, count), device="cuda")
+    out = torch.empty(rows, heads * dim, device="cuda", dtype=BF16)
+    kernels.decode_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table), cuda(positions), page, heads,
+                             kv_heads, dim, scale, None, partition, count, scratch)
+    expected = torch.cat([expect(q, k, v, scale, None, slice(n - 1, n)) for q, k, v, n in zip(qs, ks, vs, lengths)])
+    close(out.reshape(rows, heads, dim), expected)
+    assert torch.allclose(out.reshape(rows, heads, dim)[0, 0].float().cpu(), vs[0][777, 0].float(), atol=5e-2)
