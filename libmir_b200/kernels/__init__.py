@@ -63,6 +63,9 @@ _SIGNATURES = {
         "mir_gemm_tc_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_void_p],
         "mir_gemm_tc_set_width": [c_int],
+        "mir_gemm_tc_pair_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                  c_void_p],
+        "mir_gemm_tc_pair_error": [],
         "mir_gemm_tc_error": [],
         "mir_gemm_bf16_lt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_void_p, c_size_t, c_void_p],
@@ -524,7 +527,8 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
 
 
 def tensor_core_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
-                       bias: Optional[torch.Tensor] = None, accumulate: bool = False, swiglu: bool = False) -> None:
+                       bias: Optional[torch.Tensor] = None, accumulate: bool = False, swiglu: bool = False,
+                       pairs: bool = False) -> None:
     """The tcgen05 product for many bfloat16 rows: out = x . weight^T (+ bias) as bfloat16, or as float32
     (added to out if `accumulate`); with `swiglu`, weight is [gate rows; up rows] and
     out[M, I] = silu(x w_gate^T) * (x w_up^T) in one kernel."""
@@ -545,8 +549,14 @@ def tensor_core_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
                  and (out.dtype == torch.float32 or not accumulate),
                  "tensor_core_linear: out must be [M, N]; bias shares its dtype; only float32 accumulates")
         mode = SKINNY_STORE if out.dtype == torch.bfloat16 else (SKINNY_ACCUM if accumulate else SKINNY_F32)
-    _check(lib, lib.mir_gemm_tc_bf16(mode, x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias), out.data_ptr(),
-                                     out.stride(0), m, n, k, up_offset, _stream()))
+    entry = lib.mir_gemm_tc_pair_bf16 if pairs else lib.mir_gemm_tc_bf16
+    _check(lib, entry(mode, x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias), out.data_ptr(), out.stride(0), m, n,
+                      k, up_offset, _stream()))
+
+
+def tensor_core_pair_error() -> int:
+    """0, or which role of the two-SM tcgen05 product gave up a bounded wait (synchronises the device)."""
+    return int(library("bf16").mir_gemm_tc_pair_error())
 
 
 # From how many rows the tcgen05 kernel computes the gated feed-forward product.  Measured on B200 at K 2,560,

@@ -386,37 +386,41 @@ def test_gate_up_silu(dtype, m, inter, k, which, monkeypatch):
     close(out, plain_impl.silu(gate) * up, dtype, factor=2)
 
 
+@pytest.mark.parametrize("pairs", [False, True])
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 328, 520), (77, 100, 72), (300, 272, 1032), (129, 48, 8),
                                    (640, 1000, 264)])
-def test_tensor_core_product_and_its_epilogues(m, n, k):
-    """The tcgen05 product (TMA ring, accumulator in tensor memory): store with bias, accumulate into the 32-bit
-    residual, 32-bit output, a strided view as input, and the SwiGLU epilogue, at sizes that are no multiples of
-    its tiles; none of its bounded waits may have run out."""
+def test_tensor_core_product_and_its_epilogues(m, n, k, pairs):
+    """The tcgen05 products for many rows (TMA ring, accumulator in tensor memory; `pairs`: two SMs on one 256 x 256
+    tile with tcgen05.mma.cta_group::2): store with bias, accumulate into the 32-bit residual, 32-bit output, a
+    strided view as input, and the SwiGLU epilogue, at sizes that are no multiples of the tiles; none of the
+    bounded waits may have run out."""
     from libmir_b200 import kernels
+    import functools
+    kernels_tensor_core_linear = functools.partial(kernels.tensor_core_linear, pairs=pairs)
     torch.manual_seed(m + n + k)
     x, w = torch.randn(m, k).bfloat16(), (torch.randn(n, k) * 0.3).bfloat16()
     exact = plain_impl.linear(x.double(), w)
     out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
     bias = torch.randn(n).bfloat16()
-    kernels.tensor_core_linear(cuda(x), cuda(w), out, cuda(bias))
+    kernels_tensor_core_linear(cuda(x), cuda(w), out, cuda(bias))
     close(out, exact + bias.double(), torch.bfloat16, factor=2)
     base = torch.randn(m, n)
     residual = cuda(base.clone())
-    kernels.tensor_core_linear(cuda(x), cuda(w), residual, accumulate=True)
+    kernels_tensor_core_linear(cuda(x), cuda(w), residual, accumulate=True)
     close(residual, base.double() + exact, torch.float32, factor=40)       # bf16 products, 32-bit sums
     logits = torch.empty(m, n, device="cuda")
     float_bias = torch.randn(n)
-    kernels.tensor_core_linear(cuda(x), cuda(w), logits, cuda(float_bias))
+    kernels_tensor_core_linear(cuda(x), cuda(w), logits, cuda(float_bias))
     close(logits, exact + float_bias.double(), torch.float32, factor=40)
     wide = cuda(torch.randn(m, k + 40).bfloat16())
-    kernels.tensor_core_linear(wide[:, 16:16 + k], cuda(w), logits)
+    kernels_tensor_core_linear(wide[:, 16:16 + k], cuda(w), logits)
     close(logits, plain_impl.linear(wide[:, 16:16 + k].double().cpu(), w), torch.float32, factor=40)
     if n % 2 == 0:
         inter = n // 2
         gated = torch.empty(m, inter, device="cuda", dtype=torch.bfloat16)
-        kernels.tensor_core_linear(cuda(x), cuda(w), gated, swiglu=True)
+        kernels_tensor_core_linear(cuda(x), cuda(w), gated, swiglu=True)
         close(gated, plain_impl.silu(exact[:, :inter]) * exact[:, inter:], torch.bfloat16, factor=2)
-    assert kernels.tensor_core_linear_error() == 0
+    assert kernels.tensor_core_linear_error() == 0 and kernels.tensor_core_pair_error() == 0
 
 
 def test_tensor_core_product_refuses_what_it_cannot_take():
