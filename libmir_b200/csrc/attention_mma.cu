@@ -205,7 +205,9 @@ __device__ __forceinline__ void softmax(float (&s)[NT][4], float (&m)[2], float 
 // ------------------------------------------------------------------------------------------------ decode
 constexpr int kDecodeWarps = 4;
 constexpr int kDecodeTile = 16;
-constexpr int kDecodeStages = 2;
+// tiles of 16 keys in flight per warp: 2 where the CTAs are many (three CTAs fit on an SM), 3 where they are few and
+// a CTA's chain of dependent copies sets the kernel's time (batch 8, 2,120 keys: 20.0 against 21.7 us; batch 64:
+// 118 against 105 us)
 constexpr int kDecodeHeads = 8;                 // query heads one CTA serves (rows 8..15 of the tile are padding)
 constexpr int kDecodeMaxPartition = 512;
 constexpr int kDecodeMaxTiles = kDecodeMaxPartition / (kDecodeWarps * kDecodeTile);   // tiles per warp
@@ -214,7 +216,7 @@ constexpr int kDecodeMaxTiles = kDecodeMaxPartition / (kDecodeWarps * kDecodeTil
 // Per 16-key tile a warp computes S = Q K^T (heads on the M side, 8 real rows), the softmax update of its
 // 8 heads, and O^T += V^T P^T (head_dim on the M side, heads on the N side: the padding rows cost nothing
 // here, and P^T in the layout the product wants is exactly the layout S came out in).
-template <int D>
+template <int D, int kDecodeStages>
 __global__ void __launch_bounds__(kDecodeWarps * 32)
 decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* __restrict__ k_pages,
                         const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
@@ -567,26 +569,43 @@ int set_smem(Kernel kernel, size_t bytes, const char* what, bool& done) {
   return MIR_OK;
 }
 
+template <int D, int STAGES>
+int launch_decode_staged(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages, const bf16* v_pages,
+                         const int* block_table, int table_width, const int* positions, int rows, int page_size,
+                         int heads, int kv_heads, float scale, int window, int partition, int num_partitions,
+                         float* partial_o, float* partial_ml, cudaStream_t stream) {
+  const size_t pipeline = (size_t)kDecodeWarps * STAGES * 2 * kDecodeTile * (D + 8) * sizeof(bf16);
+  const size_t combine = (size_t)kDecodeWarps * kDecodeHeads * (D + 2) * sizeof(float);
+  const size_t smem = pipeline > combine ? pipeline : combine;
+  static bool smem_set = false;                               // per head size and depth: this function is a template
+  int status = set_smem(decode_attention_kernel<D, STAGES>, smem, "decode_attention", smem_set);
+  if (status != MIR_OK) return status;
+  const int group = heads / kv_heads;
+  const dim3 grid(num_partitions, kv_heads * ((group + kDecodeHeads - 1) / kDecodeHeads), rows);
+  status = mir_launch_with(mir_pdl_for_streaming(), "decode_attention", decode_attention_kernel<D, STAGES>, grid,
+                           dim3(kDecodeWarps * 32), smem, stream, 0, q, q_stride, k_pages, v_pages, block_table,
+                           table_width, positions, page_size, heads, kv_heads, scale * 1.4426950408889634f, window,
+                           partition, num_partitions, partial_o, partial_ml, out);
+  if (status != MIR_OK || num_partitions == 1) return status;
+  return mir_launch("decode_merge", decode_merge_kernel<D>, dim3(heads, rows), dim3(D <= 64 ? 64 : 128), 0, stream, 0,
+                    (const float*)partial_o, (const float*)partial_ml, positions, heads, window, partition,
+                    num_partitions, out);
+}
+
 template <int D>
 int launch_decode(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages, const bf16* v_pages,
                   const int* block_table, int table_width, const int* positions, int rows, int page_size, int heads,
                   int kv_heads, float scale, int window, int partition, int num_partitions, float* partial_o,
                   float* partial_ml, cudaStream_t stream) {
-  const size_t pipeline = (size_t)kDecodeWarps * kDecodeStages * 2 * kDecodeTile * (D + 8) * sizeof(bf16);
-  const size_t combine = (size_t)kDecodeWarps * kDecodeHeads * (D + 2) * sizeof(float);
-  const size_t smem = pipeline > combine ? pipeline : combine;
-  static bool smem_set = false;                               // per head size: this function is a template
-  int status = set_smem(decode_attention_kernel<D>, smem, "decode_attention", smem_set);
-  if (status != MIR_OK) return status;
   const int group = heads / kv_heads;
-  const dim3 grid(num_partitions, kv_heads * ((group + kDecodeHeads - 1) / kDecodeHeads), rows);
-  status = mir_launch_with(mir_pdl_for_streaming(), "decode_attention", decode_attention_kernel<D>, grid, dim3(kDecodeWarps * 32), smem, stream, 0,
-                      q, q_stride, k_pages, v_pages, block_table, table_width, positions, page_size, heads, kv_heads,
-                      scale * 1.4426950408889634f, window, partition, num_partitions, partial_o, partial_ml, out);
-  if (status != MIR_OK || num_partitions == 1) return status;
-  return mir_launch("decode_merge", decode_merge_kernel<D>, dim3(heads, rows), dim3(D <= 64 ? 64 : 128), 0, stream, 0,
-                    (const float*)partial_o, (const float*)partial_ml, positions, heads, window, partition,
-                    num_partitions, out);
+  const long long ctas = (long long)num_partitions * kv_heads * ((group + kDecodeHeads - 1) / kDecodeHeads) * rows;
+  if (ctas <= 1536)
+    return launch_decode_staged<D, 3>(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows,
+                                      page_size, heads, kv_heads, scale, window, partition, num_partitions, partial_o,
+                                      partial_ml, stream);
+  return launch_decode_staged<D, 2>(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows,
+                                    page_size, heads, kv_heads, scale, window, partition, num_partitions, partial_o,
+                                    partial_ml, stream);
 }
 
 template <int D>

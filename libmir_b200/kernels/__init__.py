@@ -322,19 +322,18 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
 
 FAST_HEAD_DIMS = (64, 128)      # what the tensor-core attention kernels take; other sizes use the reference kernel
 SM_COUNT = 148
-DECODE_CTAS_PER_SM = 2      # how many CTAs per SM split decode attention aims for
+DECODE_CTAS_PER_SM = 4      # how many CTAs per SM split decode attention wants before it takes 512-key partitions
 
 
 def decode_partitioning(rows: int, kv_heads: int, max_context: int) -> tuple:
-    """(keys per partition, partitions) for split decode attention: the largest partition that still gives
-    about two CTAs per SM, so that long contexts at small batch spread over the whole GPU; not below 128 keys
-    (measured at one row and 2,120 keys: attention and merge take 10.0 us with 128-key partitions, 12.7 with 64)."""
+    """(keys per partition, partitions) for split decode attention: 512 keys where that already gives about four
+    CTAs per SM, else 256, so that long contexts at small batch spread over the whole GPU.  Measured at 2,120 keys
+    (attention and merge, us): batch 8 20.0 with 256 keys, 20.7 with 512, 25.9 with 128; batch 1 7.8 / 15.9 / 8.8;
+    batch 64 103 / 105 / 124."""
     partition = 512
-    while True:
-        count = max(1, -(-max_context // partition))
-        if rows * kv_heads * count >= DECODE_CTAS_PER_SM * SM_COUNT or partition == 128:
-            return partition, count
-        partition //= 2
+    if rows * kv_heads * max(1, -(-max_context // partition)) < DECODE_CTAS_PER_SM * SM_COUNT:
+        partition = 256
+    return partition, max(1, -(-max_context // partition))
 
 
 def decode_attention_scratch_floats(rows: int, heads: int, head_dim: int, num_partitions: int) -> int:
