@@ -147,6 +147,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--skip-points", action="store_true", help="only the batch-8 decode and the prefill")
+    parser.add_argument("--deep-ring-ctas", type=int, default=None,
+                        help="up to how many CTAs decode attention keeps three tiles in flight per warp")
     parser.add_argument("--decode-ctas-per-sm", type=int, default=None,
                         help="CTAs per SM that split decode attention aims for when it picks the partition size")
     parser.add_argument("--set", action="append", default=[], metavar="NAME=VALUE",
@@ -200,6 +202,12 @@ def main() -> int:
             parser.error(lib.mir_last_error().decode())
     if args.decode_ctas_per_sm is not None:
         kernels.DECODE_CTAS_PER_SM = args.decode_ctas_per_sm
+    if args.deep_ring_ctas is not None:
+        import ctypes
+        lib = kernels.library("bf16")
+        lib.mir_decode_attention_set_deep_ring_ctas.argtypes = [ctypes.c_longlong]
+        lib.mir_decode_attention_set_deep_ring_ctas.restype = None
+        lib.mir_decode_attention_set_deep_ring_ctas(args.deep_ring_ctas)
     peaks, peaks_kind = read_peaks()
     sizes_name, sizes_config = SIZES[args.sizes]
     config = dict(sizes_config)

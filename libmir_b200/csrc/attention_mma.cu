@@ -592,6 +592,8 @@ int launch_decode_staged(const bf16* q, size_t q_stride, bf16* out, const bf16* 
                     num_partitions, out);
 }
 
+long long g_deep_ring_ctas = 1536;                              // up to this many CTAs run three tiles in flight per warp
+
 template <int D>
 int launch_decode(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages, const bf16* v_pages,
                   const int* block_table, int table_width, const int* positions, int rows, int page_size, int heads,
@@ -599,7 +601,7 @@ int launch_decode(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages
                   float* partial_ml, cudaStream_t stream) {
   const int group = heads / kv_heads;
   const long long ctas = (long long)num_partitions * kv_heads * ((group + kDecodeHeads - 1) / kDecodeHeads) * rows;
-  if (ctas <= 1536)
+  if (ctas <= g_deep_ring_ctas)
     return launch_decode_staged<D, 3>(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows,
                                       page_size, heads, kv_heads, scale, window, partition, num_partitions, partial_o,
                                       partial_ml, stream);
@@ -637,6 +639,9 @@ bool bad_common(const char* what, int heads, int kv_heads, int head_dim, int pag
 }
 
 }  // namespace
+
+// For measurements: up to how many CTAs split decode attention keeps three (instead of two) tiles in flight per warp.
+MIR_EXPORT void mir_decode_attention_set_deep_ring_ctas(long long ctas) { g_deep_ring_ctas = ctas; }
 
 // How many floats of scratch decode attention needs: partial outputs and (maximum, denominator) pairs.
 MIR_EXPORT long long mir_decode_attention_scratch_floats(int rows, int heads, int head_dim, int num_partitions) {
