@@ -447,7 +447,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* buffers = reinterpret_cast<bf16*>(smem_raw);          // [stage][K | V][64][STRIDE]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y;
+  const int head = blockIdx.x;                                // the fast index: all heads of the longest tile start first
   const int kv_head = head / (heads / kv_heads);
 
   grid_launch_dependents();
@@ -455,7 +455,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, size_t q_stride, bf16* __re
   // which request row and which 64-token tile of its portion this CTA has
   int row = -1, local_tile = 0;
   {
-    int remaining = gridDim.x - 1 - blockIdx.x;              // late tiles see the most keys: start them first
+    int remaining = gridDim.y - 1 - blockIdx.y;              // late tiles see the most keys: start them first
     for (int r = 0; r < num_rows; ++r) {
       const int tiles = (query_starts[r + 1] - query_starts[r] + kQueryTile - 1) / kQueryTile;
       if (remaining < tiles) { row = r; local_tile = remaining; break; }
@@ -620,7 +620,11 @@ int launch_prefill(const bf16* q, size_t q_stride, bf16* out, const bf16* k_page
   int status = set_smem(prefill_attention_kernel<D>, smem, "prefill_attention", smem_set);
   if (status != MIR_OK) return status;
   const int tiles = (tokens + kQueryTile - 1) / kQueryTile + num_rows;   // an upper bound; spare CTAs return
-  return mir_launch("prefill_attention", prefill_attention_kernel<D>, dim3(tiles, heads), dim3(kPrefillWarps * 32),
+  if (tiles > 65535) {
+    mir_set_error("prefill_attention: %d tokens in %d rows are more than one launch takes", tokens, num_rows);
+    return MIR_BAD_ARGUMENT;
+  }
+  return mir_launch("prefill_attention", prefill_attention_kernel<D>, dim3(heads, tiles), dim3(kPrefillWarps * 32),
                     smem, stream, 0, q, q_stride, out, k_pages, v_pages, block_table, table_width, query_starts,
                     context_lens, num_rows, page_size, heads, kv_heads, scale * 1.4426950408889634f, window);
 }
@@ -687,7 +691,7 @@ MIR_EXPORT int mir_prefill_attention_bf16(const void* q, long long q_stride, voi
                                           int window, cudaStream_t stream) {
   if (tokens == 0 || num_rows == 0) return MIR_OK;
   if (bad_common("prefill_attention", heads, kv_heads, head_dim, page_size, table_width, window)) return MIR_BAD_ARGUMENT;
-  if (tokens < 0 || num_rows < 0 || heads > 65535) {
+  if (tokens < 0 || num_rows < 0) {
     mir_set_error("prefill_attention: bad tokens %d, rows %d or heads %d", tokens, num_rows, heads);
     return MIR_BAD_ARGUMENT;
   }

@@ -14,8 +14,10 @@
 //             128-byte swizzle), into two-stage rings.  Pages the block table does not have (-1) are skipped.
 //   issuer    one thread.  S(t+1) = Q K(t+1)^T is issued before O += P(t) V(t), so that the tensor cores work on
 //             the next scores while the softmax threads are busy with the current ones (two S accumulators).
-//   softmax   eight warps: query row r = accumulator lane r belongs to two threads, which take 64 columns each
-//             (of the scores, of P and of O) and share the row's maximum through shared memory.  The running
+//   softmax   sixteen warps: query row r = accumulator lane r belongs to four threads (one in each of the four
+//             warps that may touch that quarter of the lanes), which take 32 columns each (of the scores, of P
+//             and of O) and share the row's maximum through shared memory; four warps per scheduler hide the
+//             latencies of one another's dependent chains (tensor-memory load, maximum, exponentials).  The running
 //             maximum is only raised when a tile's maximum exceeds it by more than 2^8 (then O and the
 //             denominator are rescaled, O by tcgen05.ld / tcgen05.st), so most tiles need no pass over O.
 //
@@ -42,7 +44,9 @@ constexpr int kHalf = 128 * 128;            // bytes of a 128-row x 64-element h
 constexpr int kTile = 2 * kHalf;            // 32 KB
 constexpr int kOffQ = 0, kOffK = kTile, kOffV = 3 * kTile, kOffP = 5 * kTile;
 constexpr int kSmemBytes = 6 * kTile + 1024;
-constexpr int kThreads = 11 * 32;           // key loader, issuer, eight softmax warps, value loader
+// kParts softmax threads per query row (each takes 128 / kParts columns): key loader, issuer, 4 kParts softmax
+// warps, value loader
+__host__ __device__ constexpr int threads_for(int parts) { return (3 + 4 * parts) * 32; }
 constexpr uint32_t kTmemColumns = 512;      // S0 at 0, S1 at 128, O at 256
 constexpr float kRescaleThreshold = 8.0f;   // log2 of how far a tile's maximum may exceed the running one
 
@@ -51,6 +55,7 @@ enum { Q_FULL = 0, K_FULL = 1, K_FREE = 3, V_FULL = 5, V_FREE = 7, S_FULL = 9, S
        BARRIERS = 15 };
 
 __device__ int g_tc_attention_error = 0;
+int g_softmax_parts = 2;
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -76,17 +81,17 @@ __device__ __forceinline__ void tmem_load_32_nowait(uint32_t address, float* v) 
 }
 __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-constexpr int kCols = kKeys / 2;             // columns of a tile that one softmax thread handles
-
-// One tile of the softmax for this thread's half (64 columns starting at `first`) of its row: the scores are
-// read once (two loads in flight, one wait), then the visible maximum (columns low..high of the tile; all if
-// !MASKED), which the two threads of a row exchange through `mine` / `other` and the named barrier `pair`; then
-// the decision whether the running maximum rises, and p = exp2(scale s - reference) packed to bf16.  Returns
-// the sum of this thread's p.
-template <bool MASKED>
+// One tile of the softmax for this thread's part (kCols columns starting at `first`) of its row: the scores are
+// read once (all loads in flight, one wait), then the visible maximum (columns low..high of the tile; all if
+// !MASKED), which the kParts threads of a row exchange through `shared_max` (one float per part, kRows apart)
+// and the named barrier `team` of the four warps that hold the row's quarter of lanes; then the decision whether
+// the running maximum rises, and p = exp2(scale s - reference) packed to bf16.  Returns the sum of this thread's p.
+template <int kParts, bool MASKED>
 __device__ __forceinline__ float softmax_tile(uint32_t scores, int first, int low, int high, float scale_log2,
-                                              float& reference, float& factor, bool& grow, uint32_t (&packed)[kCols / 2],
-                                              float* mine, const float* other, int pair) {
+                                              float& reference, float& factor, bool& grow,
+                                              uint32_t (&packed)[kKeys / kParts / 2], float* shared_max, int part,
+                                              int team) {
+  constexpr int kCols = kKeys / kParts;        // columns of a tile that one softmax thread handles
   float v[kCols];
 #pragma unroll
   for (int c0 = 0; c0 < kCols; c0 += 32) tmem_load_32_nowait(scores + first + c0, v + c0);
@@ -98,9 +103,11 @@ __device__ __forceinline__ float softmax_tile(uint32_t scores, int first, int lo
   for (int c = 0; c < kCols; ++c)
     if (!MASKED || (first + c <= high && first + c >= low)) best[c & 3] = fmaxf(best[c & 3], v[c]);
   float maximum = fmaxf(fmaxf(best[0], best[1]), fmaxf(best[2], best[3]));
-  *mine = maximum;
-  asm volatile("bar.sync %0, 64;" ::"r"(pair) : "memory");
-  maximum = fmaxf(maximum, *other) * scale_log2;                       // scale > 0
+  shared_max[part * kRows] = maximum;
+  asm volatile("bar.sync %0, %1;" ::"r"(team), "n"(32 * kParts) : "memory");
+#pragma unroll
+  for (int other = 0; other < kParts; ++other) maximum = fmaxf(maximum, shared_max[other * kRows]);
+  maximum *= scale_log2;                                               // scale > 0
   grow = maximum > reference + kRescaleThreshold;
   factor = grow ? fast_exp2(reference - maximum) : 1.0f;               // 0 when nothing was seen before
   reference = grow ? maximum : reference;
@@ -120,19 +127,25 @@ __device__ __forceinline__ float softmax_tile(uint32_t scores, int first, int lo
   return (sums[0] + sums[1]) + (sums[2] + sums[3]);
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+template <int kParts>
+__global__ void __launch_bounds__(threads_for(kParts), 1)
 tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                             const __grid_constant__ CUtensorMap v_map, bf16* __restrict__ out,
                             const int* __restrict__ block_table, int table_width, const int* __restrict__ query_starts,
                             const int* __restrict__ context_lens, int num_rows, int page_size, int heads, int kv_heads,
                             float scale_log2, int window) {
+  constexpr int kThreads = threads_for(kParts), kSoftmaxThreads = kRows * kParts, kCols = kKeys / kParts;
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long barriers[BARRIERS];
   __shared__ uint32_t tmem_base_slot;
-  __shared__ float exchange[2][2][kRows];                    // [tile parity][half][row]: what a row's two threads share
+  __shared__ float exchange[2][kParts][kRows];               // [tile parity][part][row]: what a row's threads share
+  __shared__ float denominators[kParts][kRows];              // (apart: a slow thread may still read the last maxima)
   if (*reinterpret_cast<volatile int*>(&g_tc_attention_error) != 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y;
+  // The head is the fast index of the grid: CTAs are handed out in the order of blockIdx.x first, so all heads of
+  // the query tile that sees the most keys start first and the shortest tiles fill the end (and the heads of
+  // one group, which read the same keys, run at the same time).
+  const int head = blockIdx.x;
   const int kv_head = head / (heads / kv_heads);
 
   grid_launch_dependents();
@@ -140,7 +153,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   // which request row and which 128-token tile of its portion this CTA has
   int row = -1, local_tile = 0;
   {
-    int remaining = gridDim.x - 1 - blockIdx.x;              // late tiles see the most keys: start them first
+    int remaining = gridDim.y - 1 - blockIdx.y;              // late tiles see the most keys: start them first
     for (int r = 0; r < num_rows; ++r) {
       const int tiles = (query_starts[r + 1] - query_starts[r] + kRows - 1) / kRows;
       if (remaining < tiles) { row = r; local_tile = remaining; break; }
@@ -169,7 +182,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   if (threadIdx.x == 0) {
     for (int i = 0; i < BARRIERS; ++i) {
       const bool many = i == S_FREE || i == S_FREE + 1 || i == P_READY;   // every softmax thread arrives
-      barrier_init(bar(i), many ? 256u : 1u);
+      barrier_init(bar(i), many ? (uint32_t)kSoftmaxThreads : 1u);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -270,18 +283,18 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax: two threads per query row (warps 2..9)
+    // ------------------------------------------------------------------ softmax: kParts threads per query row
     const int quarter = warp & 3;                             // the accumulator lanes this warp may touch
-    const int half = (warp - 2) >> 2;                         // which 64 columns of the row (and of O) it takes
+    const int part = (warp - 2) >> 2;                         // which kCols columns of the row (and of O) it takes
     const int r = quarter * 32 + lane;
     const bool valid_row = r < tile_rows;
     const int position = first_position + min(r, tile_rows - 1);
     const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
-    const int first = half * kCols;
+    const int first = part * kCols;
     float reference = -INFINITY, denominator = 0.0f;          // running maximum (scaled, log2 domain), partial sum
     bool alive = true;
-    // (a thread whose wait ran out keeps walking the tiles without waiting, so that the pair's named barrier
-    // still sees both of its threads)
+    // (a thread whose wait ran out keeps walking the tiles without waiting, so that the row's named barrier
+    // still sees all of its threads)
     for (int t = 0; t < tiles; ++t) {
       const int stage = t & 1;
       const uint32_t parity = (uint32_t)(t >> 1) & 1u;
@@ -296,12 +309,11 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       uint32_t packed[kCols / 2];
       bool grow;
       float factor;
-      float* mine = &exchange[stage][half][r];
-      const float* other = &exchange[stage][half ^ 1][r];
-      const float sum = every ? softmax_tile<false>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
-                                                    mine, other, 1 + quarter)
-                              : softmax_tile<true>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
-                                                   mine, other, 1 + quarter);
+      float* shared_max = &exchange[stage][0][r];
+      const float sum = every ? softmax_tile<kParts, false>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
+                                                    shared_max, part, 1 + quarter)
+                              : softmax_tile<kParts, true>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
+                                                   shared_max, part, 1 + quarter);
       tensor_fence_before_sync();
       barrier_arrive(bar(S_FREE + stage));                    // the scores are in registers
       denominator = denominator * factor + sum;
@@ -311,7 +323,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         tensor_fence_after_sync();
         if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-          for (int c0 = 0; c0 < kDim / 2; c0 += 32) {
+          for (int c0 = 0; c0 < kDim / kParts; c0 += 32) {
             float o[32];
             tmem_load_32(tmem_o + lane_bits + first + c0, o);
 #pragma unroll
@@ -321,11 +333,12 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           tmem_store_wait();
         }
       }
-      // P as the A operand: rows of 128 bytes (64 keys, this thread's half), 16-byte chunks swizzled by the row
-      unsigned char* p_row = smem + kOffP + (size_t)half * kHalf + (size_t)r * 128;
+      // P as the A operand: rows of 128 bytes (64 keys), 16-byte chunks swizzled by the row; this thread's columns
+      // are chunks first / 8 ... of the half they lie in
+      unsigned char* p_row = smem + kOffP + (size_t)(first / 64) * kHalf + (size_t)r * 128;
 #pragma unroll
-      for (int chunk = 0; chunk < 8; ++chunk) {
-        const int where = chunk ^ (r & 7);
+      for (int chunk = 0; chunk < kCols / 8; ++chunk) {
+        const int where = ((first % 64) / 8 + chunk) ^ (r & 7);
         *reinterpret_cast<uint4*>(p_row + where * 16) =
             make_uint4(packed[4 * chunk], packed[4 * chunk + 1], packed[4 * chunk + 2], packed[4 * chunk + 3]);
       }
@@ -333,17 +346,19 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       tensor_fence_before_sync();
       barrier_arrive(bar(P_READY));
     }
-    // the row's denominator is the sum of its two threads' parts
-    exchange[0][half][r] = denominator;
-    asm volatile("bar.sync %0, 64;" ::"r"(5 + quarter) : "memory");
-    denominator += exchange[0][half ^ 1][r];
+    // the row's denominator is the sum of its threads' parts
+    denominators[part][r] = denominator;
+    asm volatile("bar.sync %0, %1;" ::"r"(5 + quarter), "n"(32 * kParts) : "memory");
+    denominator = 0.0f;
+#pragma unroll
+    for (int other = 0; other < kParts; ++other) denominator += denominators[other][r];
     if (alive && !wait_barrier(bar(PV_DONE), (uint32_t)(tiles - 1) & 1u)) { g_tc_attention_error = 3; alive = false; }
     tensor_fence_after_sync();
     if (alive) {
       const float inverse = denominator > 0.0f ? 1.0f / denominator : 0.0f;
       bf16* dst = out + ((size_t)(q_begin + local0 + r) * heads + head) * kDim + first;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kDim / 2; c0 += 32) {
+      for (int c0 = 0; c0 < kDim / kParts; c0 += 32) {
         float o[32];
         tmem_load_32(tmem_o + lane_bits + first + c0, o);
         if (valid_row) {
@@ -393,7 +408,7 @@ MIR_EXPORT int mir_prefill_attention_tc_bf16(const void* q, long long q_stride, 
                                              int head_dim, float scale, int window, cudaStream_t stream) {
   if (num_rows == 0 || tokens == 0) return MIR_OK;
   if (!mir_prefill_attention_tc_takes(head_dim, page_size) || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
-      table_width <= 0 || window < 0 || num_rows < 0 || tokens < 0 || heads > 65535 || scale <= 0.0f ||
+      table_width <= 0 || window < 0 || num_rows < 0 || tokens < 0 || scale <= 0.0f ||
       (q_stride % 8) || q_stride < (long long)heads * kDim || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) ||
       ((uintptr_t)v_pages & 15) || ((uintptr_t)out & 15) || cache_rows <= 0 || cache_rows > 0x7fffffffll ||
       q_stride > 0x7fffffffll) {
@@ -411,8 +426,10 @@ MIR_EXPORT int mir_prefill_attention_tc_bf16(const void* q, long long q_stride, 
   if (status != MIR_OK) return status;
   static bool configured = false;
   if (!configured) {
-    const cudaError_t err = cudaFuncSetAttribute(tc_prefill_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 kSmemBytes);
+    cudaError_t err = cudaFuncSetAttribute(tc_prefill_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kSmemBytes);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(tc_prefill_attention_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (err != cudaSuccess) {
       mir_set_error("prefill_attention_tc: cannot reserve %d bytes of shared memory: %s", kSmemBytes,
                     cudaGetErrorString(err));
@@ -421,8 +438,24 @@ MIR_EXPORT int mir_prefill_attention_tc_bf16(const void* q, long long q_stride, 
     configured = true;
   }
   const int tiles = (tokens + kRows - 1) / kRows + num_rows;   // an upper bound; spare CTAs return
-  return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel, dim3(tiles, heads), dim3(kThreads),
+  if (tiles > 65535) {
+    mir_set_error("prefill_attention_tc: %d tokens in %d rows are more than one launch takes", tokens, num_rows);
+    return MIR_BAD_ARGUMENT;
+  }
+  if (g_softmax_parts == 2)
+    return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<2>, dim3(heads, tiles), dim3(threads_for(2)),
+                      (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, (bf16*)out, block_table, table_width,
+                      query_starts, context_lens, num_rows, page_size, heads, kv_heads,
+                      scale * 1.4426950408889634f, window);
+  return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<4>, dim3(heads, tiles), dim3(threads_for(4)),
                     (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, (bf16*)out, block_table, table_width,
                     query_starts, context_lens, num_rows, page_size, heads, kv_heads,
                     scale * 1.4426950408889634f, window);
+}
+
+// How many softmax threads share a query row: 2 (eight softmax warps) or 4 (sixteen).
+MIR_EXPORT int mir_prefill_attention_tc_set_parts(int parts) {
+  if (parts != 2 && parts != 4) return MIR_BAD_ARGUMENT;
+  g_softmax_parts = parts;
+  return MIR_OK;
 }

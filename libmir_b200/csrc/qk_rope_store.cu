@@ -9,6 +9,9 @@
 // q is rotated in place; k (rotated) and v go straight to
 //   pages[(slot_mapping[t]) * Hkv + h][:]  with slot = page * page_size + position % page_size,
 // and a negative slot means "do not write" (a padded row of a captured decode batch).
+// write_kv: 0 only the queries are treated (a reader of another entry's cache), 1 keys and values go to their
+// pages, 2 keys are normed and rotated in place like the queries and nothing goes to the pages (a position
+// encoding of another kind works on them next; a second call with 1 and neither norm nor rotation then stores).
 #include "common.cuh"
 
 using namespace mir;
@@ -52,7 +55,7 @@ __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict_
   for (int unit = unit_begin + warp; unit < unit_end; unit += warps) {
     T* src = row + (size_t)unit * head_dim;
     if (unit >= heads + kv_heads) {                 // a value head: copy to its page
-      if (!write_kv || slot < 0) continue;
+      if (write_kv != 1 || slot < 0) continue;
       T* dst = v_pages + ((size_t)slot * kv_heads + (unit - heads - kv_heads)) * head_dim;
       if ((head_dim * sizeof(T)) % 16 == 0 && ((uintptr_t)src & 15) == 0 && ((uintptr_t)dst & 15) == 0) {
         const int chunks = head_dim * (int)sizeof(T) / 16;
@@ -63,7 +66,8 @@ __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict_
       continue;
     }
     const bool is_query = unit < heads;
-    if (!is_query && (!write_kv || slot < 0)) continue;
+    const bool key_in_place = write_kv == 2;        // normed and rotated keys stay in the packed row
+    if (!is_query && !key_in_place && (!write_kv || slot < 0)) continue;
     const float* norm = is_query ? q_norm : k_norm;
     float inverse = 1.0f;
     if (norm) {
@@ -82,7 +86,7 @@ __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict_
       sum = warp_sum(sum);
       inverse = rsqrtf(sum / (float)head_dim + eps);
     }
-    T* dst = is_query ? src : k_pages + ((size_t)slot * kv_heads + (unit - heads)) * head_dim;
+    T* dst = (is_query || key_in_place) ? src : k_pages + ((size_t)slot * kv_heads + (unit - heads)) * head_dim;
     if (PAIRED) {
       for (int pair = 2 * lane; pair < half; pair += 64) {
         float2 first = load2(src + pair), second = load2(src + pair + half);
@@ -156,10 +160,11 @@ __global__ void qk_rope_store_wide_kernel(__nv_bfloat16* __restrict__ qkv, const
       a = *reinterpret_cast<const uint4*>(src + 8 * l);
       b = *reinterpret_cast<const uint4*>(src + HALF + 8 * l);
     }
-    const bool writes = active && (is_query || (write_kv && slot >= 0));
+    const bool in_place = is_query || (write_kv == 2 && !is_value);
+    const bool writes = active && (in_place || (write_kv == 1 && slot >= 0));
     __nv_bfloat16* dst = nullptr;
     if (writes)
-      dst = is_query ? row + (size_t)unit * DIM
+      dst = in_place ? row + (size_t)unit * DIM
                      : (is_value ? v_pages + ((size_t)slot * kv_heads + (unit - heads - kv_heads)) * DIM
                                  : k_pages + ((size_t)slot * kv_heads + (unit - heads)) * DIM);
     float fa[8], fb[8];

@@ -196,10 +196,9 @@ class DecodeGraphs:
         self.graphs: Dict[Tuple, DecodeGraph] = {}
 
     def usable(self) -> bool:
-        """Every mixer must read the batch from device memory only (graph_safe), since a replay cannot
-        see what the host knew at capture time."""
-        from ..parts.base import Mixer
-        return all(part.graph_safe for part in self.runner.model.parts() if isinstance(part, Mixer))
+        """Every part must read the batch from device memory only and never wait for the device (graph_safe),
+        since a replay cannot see what the host knew at capture time."""
+        return all(getattr(part, "graph_safe", False) for part in self.runner.model.parts())
 
     def get(self, rows: int, sequences, extra_tokens: int, ranked: bool) -> DecodeGraph:
         page = self.runner.manager.page_size

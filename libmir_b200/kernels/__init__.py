@@ -51,6 +51,7 @@ _SIGNATURES = {
                                           c_void_p],
         "mir_prefill_attention_tc_takes": [c_int, c_int],
         "mir_prefill_attention_tc_error": [],
+        "mir_prefill_attention_tc_set_parts": [c_int],
         "mir_gemm_skinny_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                  c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mir_gemm_tc_stream_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -234,8 +235,11 @@ def decode_advance(sampled, tokens, positions, token_log, step_counter) -> None:
 def qk_rope_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
                   inv_freq: Optional[torch.Tensor], q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
                   k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], heads: int, kv_heads: int,
-                  head_dim: int, rotary_dim: int, eps: float, write_kv: bool = True) -> None:
-    """q/k-norm + rotary on the packed qkv rows in place for q, k and v into their pages."""
+                  head_dim: int, rotary_dim: int, eps: float, write_kv: bool = True,
+                  keys_in_place: bool = False) -> None:
+    """q/k-norm + rotary on the packed qkv rows in place for q, k and v into their pages.  `keys_in_place`:
+    the keys are normed and rotated in place like the queries and nothing is written to the pages."""
+    write_kv = write_kv and not keys_in_place
     _cuda(qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages)
     tokens = qkv.shape[0]
     _require(qkv.is_contiguous() and qkv.shape[1] == (heads + 2 * kv_heads) * head_dim, "qk_rope_store: bad qkv")
@@ -254,7 +258,8 @@ def qk_rope_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Opti
     lib = library("core")
     _check(lib, lib.mir_qk_rope_store(_is_bf16(qkv), qkv.data_ptr(), positions.data_ptr(), _ptr(slot_mapping),
                                       _ptr(inv_freq), _ptr(q_norm), _ptr(k_norm), _ptr(k_pages), _ptr(v_pages),
-                                      tokens, heads, kv_heads, head_dim, rotary_dim, eps, int(write_kv), _stream()))
+                                      tokens, heads, kv_heads, head_dim, rotary_dim, eps,
+                                      2 if keys_in_place else int(write_kv), _stream()))
 
 
 # Whether the QKV projection of a few rows does the per-head norm, the rotation and the cache write in its
@@ -401,6 +406,12 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], query_starts.data_ptr(), context_lens.data_ptr(), rows, tokens, page_size, heads,
         kv_heads, head_dim, scale, int(window or 0), _stream()))
+
+
+def set_prefill_softmax_threads_per_row(parts: int) -> None:
+    """How many softmax threads of the tcgen05 attention share a query row: 2 or 4 (the default)."""
+    lib = library("bf16")
+    _check(lib, lib.mir_prefill_attention_tc_set_parts(int(parts)))
 
 
 def prefill_attention_error() -> int:

@@ -20,7 +20,6 @@ from .base import Mixer
 
 
 class SoftmaxAttention(Mixer):
-    graph_safe = True
     takes_normed_residual = True
 
     def __init__(self, spec, env):
@@ -32,6 +31,10 @@ class SoftmaxAttention(Mixer):
         self.kv_width = s.kv_heads * s.head_dim
         self.position = build_part(s.position, env) if s.position is not None else None
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_norm = self.k_norm = None
+
+    @property
+    def graph_safe(self):
+        return self.position is None or self.position.graph_safe
 
     def cache_requirement(self):
         return PagedKv(self.spec.kv_heads, self.spec.head_dim, self.spec.window)
@@ -74,16 +77,11 @@ class SoftmaxAttention(Mixer):
         tokens = x.shape[0]
         qkv = ctx.alloc((tokens, self.q_width + 2 * self.kv_width), self.env.dtype)
         group = ctx.groups[cache.group]
-        table = self.position.table if self.position is not None else None
-        rotary_dim = self.position.rotary_dim if self.position is not None else 0
-        # a few rows: projection, per-head norm, rotation and cache write in one kernel where the sizes allow it
-        if not kernels.qkv_project_rope_store(x, self.w_qkv, self.b_qkv, qkv, ctx.positions, group.slot_mapping, table,
-                                              self.q_norm, self.k_norm, cache.k_pages, cache.v_pages, s.heads,
-                                              s.kv_heads, s.head_dim, rotary_dim, s.qk_norm_eps, write_kv=cache.writes):
-            kernels.linear(x, self.w_qkv, qkv, self.b_qkv, alloc=ctx.alloc)
-            kernels.qk_rope_store(qkv, ctx.positions, group.slot_mapping, table, self.q_norm, self.k_norm,
-                                  cache.k_pages, cache.v_pages, s.heads, s.kv_heads, s.head_dim, rotary_dim,
-                                  s.qk_norm_eps, write_kv=cache.writes)
+        rotation = self.position.rotation() if self.position is not None else (None, 0)
+        if rotation is None:
+            self.project_with_other_position(ctx, cache, group, x, qkv)
+        else:
+            self.project(ctx, cache, group, x, qkv, *rotation)
         mixed = ctx.alloc((tokens, self.q_width), self.env.dtype)
         self.attend(ctx, group, cache, qkv, mixed)
         accumulate = getattr(ctx, "accumulate_with_stats", None)
@@ -91,6 +89,34 @@ class SoftmaxAttention(Mixer):
             kernels.linear(mixed, self.w_o, residual, self.b_o, accumulate=True)
         else:
             accumulate(mixed, self.w_o, residual, self.b_o)      # may also prepare the norm that follows
+
+    def project(self, ctx, cache, group, x, qkv, table, rotary_dim):
+        """Projection, per-head norm, rotation and cache write: in one kernel for a few rows where the sizes
+        allow it, else the library product and one kernel for the rest."""
+        s = self.spec
+        if not kernels.qkv_project_rope_store(x, self.w_qkv, self.b_qkv, qkv, ctx.positions, group.slot_mapping, table,
+                                              self.q_norm, self.k_norm, cache.k_pages, cache.v_pages, s.heads,
+                                              s.kv_heads, s.head_dim, rotary_dim, s.qk_norm_eps, write_kv=cache.writes):
+            kernels.linear(x, self.w_qkv, qkv, self.b_qkv, alloc=ctx.alloc)
+            kernels.qk_rope_store(qkv, ctx.positions, group.slot_mapping, table, self.q_norm, self.k_norm,
+                                  cache.k_pages, cache.v_pages, s.heads, s.kv_heads, s.head_dim, rotary_dim,
+                                  s.qk_norm_eps, write_kv=cache.writes)
+
+    def project_with_other_position(self, ctx, cache, group, x, qkv):
+        """A position encoding that is no rotation of the kernel's: projection, then the per-head norms alone, then
+        the encoding's own `apply` on the q and k views, then keys and values into their pages."""
+        s = self.spec
+        kernels.linear(x, self.w_qkv, qkv, self.b_qkv, alloc=ctx.alloc)
+        if s.qk_norm:
+            kernels.qk_rope_store(qkv, ctx.positions, None, None, self.q_norm, self.k_norm, None, None, s.heads,
+                                  s.kv_heads, s.head_dim, 0, s.qk_norm_eps, keys_in_place=True)
+        tokens = qkv.shape[0]
+        queries = qkv[:, :self.q_width].view(tokens, s.heads, s.head_dim)
+        keys = qkv[:, self.q_width:self.q_width + self.kv_width].view(tokens, s.kv_heads, s.head_dim)
+        self.position.apply(ctx, queries, keys)
+        if cache.writes:
+            kernels.qk_rope_store(qkv, ctx.positions, group.slot_mapping, None, None, None, cache.k_pages,
+                                  cache.v_pages, s.heads, s.kv_heads, s.head_dim, 0, s.qk_norm_eps, write_kv=True)
 
     def attend(self, ctx, group, cache, qkv, out):
         """Attention of every packed row over its request's pages; the kernel is chosen by dtype and size:

@@ -12,7 +12,10 @@ the batch is in the StepContext (libmir_b200/engine/context.py).
                   x is [T, H] in the engine dtype (already normed); cache is the CacheView of the
                   schedule entry being run (None if the mixer asked for none).
     FeedForward   forward(ctx, x, residual) -> None             residual += feed_forward(x)
-    Position      a helper owned by a mixer (tables on the device); it has no weights.
+    Position      owned by the mixer that uses it.  rotation() -> (table, rotary_dim) if the encoding is the
+                  half-split rotation that the q/k kernel applies itself, else None, and then
+                  apply(ctx, queries, keys) changes [T, heads, head_dim] views in place (after the per-head
+                  norm, before keys go to their pages).
     Block         forward(ctx, cache, residual) -> None          one arrangement of the above
 
 `parameters()` maps a name local to the part ("q_proj.weight") to a ParamSpec; the model joins it
@@ -53,6 +56,10 @@ class Part:
         """Bytes of weights that one step reads (for the roofline account)."""
         return 0
 
+    # True if forward reads the batch only from device tensors of the context and never waits for the device:
+    # decode steps of a model whose parts all say so are captured in CUDA graphs.
+    graph_safe = False
+
 
 class Norm(Part):
     def forward(self, ctx, x: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -61,12 +68,23 @@ class Norm(Part):
 
 
 class Mixer(Part):
-    graph_safe = False     # True if forward reads the batch only from device tensors of the context
-
     def cache_requirement(self) -> CacheRequirement:
         return None
 
     def forward(self, ctx, cache, x: torch.Tensor, residual: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class Position(Part):
+    def rotation(self):
+        """(float32 table of rotary_dim / 2 inverse frequencies, rotary_dim) if this encoding is the half-split
+        rotation by position * frequency, which the kernel that norms q and k and writes the cache applies
+        itself; None for every other encoding, which `apply` then computes."""
+        return None
+
+    def apply(self, ctx, queries: torch.Tensor, keys: torch.Tensor) -> None:
+        """Encode ctx.positions into queries [T, heads, head_dim] and keys [T, kv_heads, head_dim] in place
+        (views of the packed projection in the engine dtype)."""
         raise NotImplementedError
 
 

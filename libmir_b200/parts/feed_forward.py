@@ -15,6 +15,7 @@ from .base import FeedForward
 
 
 class SwiGlu(FeedForward):
+    graph_safe = True
     takes_normed_residual = True
 
     def __init__(self, spec, env):

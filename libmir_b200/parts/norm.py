@@ -16,6 +16,7 @@ from .base import Norm
 
 
 class RmsNorm(Norm):
+    graph_safe = True
     foldable = True       # y = x * s * w with one s per row: the products around it can take it over
 
     def __init__(self, spec, env):

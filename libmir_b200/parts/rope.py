@@ -12,7 +12,7 @@ import math
 
 import torch
 
-from .base import Part
+from .base import Position
 
 
 def inverse_frequencies(rotary_dim: int, theta: float, scaling=None) -> torch.Tensor:
@@ -26,8 +26,10 @@ def inverse_frequencies(rotary_dim: int, theta: float, scaling=None) -> torch.Te
     return inverse.to(torch.float32)
 
 
-class Rotary(Part):
+class Rotary(Position):
     """Owned by a mixer; `table` is what its kernel multiplies positions with."""
+
+    graph_safe = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -35,3 +37,6 @@ class Rotary(Part):
             raise ValueError(f"rotary_dim {spec.rotary_dim} must be even and at most head_dim {spec.head_dim}")
         self.rotary_dim = spec.rotary_dim
         self.table = inverse_frequencies(spec.rotary_dim, spec.theta, spec.scaling).to(env.device)
+
+    def rotation(self):
+        return self.table, self.rotary_dim

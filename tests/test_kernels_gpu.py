@@ -169,6 +169,33 @@ def test_qk_norm_rope_and_cache_write(dtype, heads, kv_heads, dim, rotary, norm)
     assert torch.all(k_pages[untouched] == 7.0) and torch.all(v_pages[untouched] == 7.0)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,dim,rotary", [(3, 1, 48, 24), (10, 5, 128, 128), (4, 2, 16, 0)])
+def test_qk_norm_rope_with_keys_in_place(dtype, heads, kv_heads, dim, rotary):
+    """Keys are normed and rotated in the packed rows like the queries; values and the pages stay as they are."""
+    from libmir_b200 import kernels
+    torch.manual_seed(8)
+    tokens = 7
+    qkv = torch.randn(tokens, (heads + 2 * kv_heads) * dim).to(dtype)
+    positions = torch.tensor([0, 1, 2, 400, 401, 5, 6], dtype=torch.int32)
+    frequencies = plain_impl.rope_inverse_frequencies(rotary, 5000.0, None) if rotary else None
+    q_weight, k_weight = torch.randn(dim), torch.randn(dim)
+    pages = torch.full((8, kv_heads, dim), 7.0, device="cuda", dtype=dtype)
+    device_qkv = cuda(qkv.clone())
+    kernels.qk_rope_store(device_qkv, cuda(positions), None, None if frequencies is None else cuda(frequencies),
+                          cuda(q_weight), cuda(k_weight), pages, pages, heads, kv_heads, dim, rotary, 1e-4,
+                          keys_in_place=True)
+    wide = qkv.double()
+    q = plain_impl.rms_norm(wide[:, :heads * dim].reshape(tokens, heads, dim), q_weight, 1e-4)
+    k = plain_impl.rms_norm(wide[:, heads * dim:(heads + kv_heads) * dim].reshape(tokens, kv_heads, dim), k_weight, 1e-4)
+    if rotary:
+        q, k = plain_impl.rope(q, positions, frequencies), plain_impl.rope(k, positions, frequencies)
+    close(device_qkv[:, :heads * dim].reshape(tokens, heads, dim), q, dtype)
+    close(device_qkv[:, heads * dim:(heads + kv_heads) * dim].reshape(tokens, kv_heads, dim), k, dtype)
+    close(device_qkv[:, (heads + kv_heads) * dim:], wide[:, (heads + kv_heads) * dim:], dtype)
+    assert torch.all(pages == 7.0)
+
+
 def paged(k, v, page, pages_total, rng):
     """Scatter one request's keys/values [S, H, D] into shuffled pages; returns pages and its table."""
     seq = k.shape[0]

@@ -163,3 +163,179 @@ def test_toy_architecture_is_registered_built_loaded_and_stepped(tmp_path, dtype
     result = model.step([StepEntry("c", second, range(45))])
     error = np.abs(result.logits.cpu().numpy() - want_second).max()
     assert error <= tol * max(1.0, np.abs(want_second).max()), f"reused slot: max |diff| {error:.3e}"
+
+
+# ------------------------------------------------------------------------------ a routed feed-forward and another position encoding
+@dataclass(frozen=True)
+class WaveOffsetSpec:
+    """Toy position encoding: q += a sin(p f_d), k += a cos(p f_d) with f_d = 1 / (d + 2)."""
+
+    head_dim: int = 0
+    amplitude: float = 0.5
+    kind: str = field(init=False, default="toy_wave_offset")
+
+
+@dataclass(frozen=True)
+class RoutedSpec:
+    """Toy routed feed-forward: the `top` experts with the largest router logits, weighted by the softmax over
+    those logits; an expert is out(relu(in(x)))."""
+
+    hidden_size: int = 0
+    inner_size: int = 0
+    experts: int = 0
+    top: int = 1
+    kind: str = field(init=False, default="toy_routed")
+
+
+def make_routed_toy():
+    from libmir_b200 import register_architecture, register_part
+    from libmir_b200.config.spec import (EmbeddingSpec, HeadSpec, LayerSpec, ModelSpec, ParamSpec, RmsNormSpec,
+                                         RotarySpec, ScheduleEntry, SoftmaxAttentionSpec, SwiGluSpec)
+    from libmir_b200.parts import FeedForward, Position
+
+    class WaveOffset(Position):
+        graph_safe = True                                  # reads positions from the device only
+
+        def __init__(self, spec, env):
+            super().__init__(spec, env)
+            self.frequency = 1.0 / (torch.arange(spec.head_dim, dtype=torch.float32, device=env.device) + 2.0)
+
+        def apply(self, ctx, queries, keys):
+            angle = ctx.positions[:queries.shape[0]].float()[:, None, None] * self.frequency
+            queries.copy_(queries.float() + self.spec.amplitude * torch.sin(angle))
+            keys.copy_(keys.float() + self.spec.amplitude * torch.cos(angle))
+
+    class Routed(FeedForward):
+        def parameters(self):
+            s = self.spec
+            return {"router.weight": ParamSpec((s.experts, s.hidden_size), store="float32"),
+                    "experts.in": ParamSpec((s.experts, s.inner_size, s.hidden_size)),
+                    "experts.out": ParamSpec((s.experts, s.hidden_size, s.inner_size))}
+
+        def bind(self, tensors):
+            self.router, self.w_in, self.w_out = (tensors[n] for n in ("router.weight", "experts.in", "experts.out"))
+
+        def forward(self, ctx, x, residual):
+            x = x.float()
+            logits = x @ self.router.T                                    # 32-bit router
+            chosen = logits.topk(self.spec.top, dim=-1)
+            share = torch.softmax(chosen.values, dim=-1)
+            for expert in range(self.spec.experts):
+                tokens, place = (chosen.indices == expert).nonzero(as_tuple=True)
+                if tokens.numel():
+                    inner = torch.relu(x[tokens] @ self.w_in[expert].float().T)
+                    residual.index_add_(0, tokens, (inner @ self.w_out[expert].float().T) * share[tokens, place, None])
+
+    register_part("toy_wave_offset", WaveOffset)
+    register_part("toy_routed", Routed)
+
+    def build(config, catalog):
+        hidden = config["hidden_size"]
+        norm = lambda: RmsNormSpec(size=hidden, eps=config["eps"])
+        names = {"mixer_norm": "norm_a.", "mixer": "mixer.", "feed_forward_norm": "norm_b.", "feed_forward": "ff."}
+        def attention(position, qk_norm):
+            return SoftmaxAttentionSpec(hidden_size=hidden, heads=3, kv_heads=1, head_dim=16, scale=0.25,
+                                        qk_norm=qk_norm, qk_norm_eps=1e-5, position=position)
+        routed = RoutedSpec(hidden, config["expert_size"], config["experts"], config["top"])
+        dense = SwiGluSpec(hidden_size=hidden, intermediate_size=config["intermediate_size"])
+        layers = (
+            LayerSpec("toy.layers.0.", attention(WaveOffsetSpec(16, 0.5), True), routed, norm(), norm(), names),
+            LayerSpec("toy.layers.1.", attention(RotarySpec(head_dim=16, rotary_dim=8, theta=100.0), False), dense,
+                      norm(), norm(), names),
+            LayerSpec("toy.layers.2.", attention(WaveOffsetSpec(16, 0.25), False), routed, norm(), norm(), names),
+        )
+        return ModelSpec("ToyRoutedForCausalLM", hidden, config["vocab_size"], config["max_positions"],
+                         EmbeddingSpec("toy.embed.weight", config["vocab_size"], hidden), layers,
+                         tuple(ScheduleEntry(i) for i in range(3)), norm(), "toy.final_norm.",
+                         HeadSpec("toy.head.weight", config["vocab_size"], hidden, tied=False))
+
+    register_architecture("ToyRoutedForCausalLM", build)
+
+
+ROUTED_CONFIG = {"architectures": ["ToyRoutedForCausalLM"], "hidden_size": 48, "intermediate_size": 56,
+                 "vocab_size": 77, "max_positions": 160, "eps": 1e-5, "experts": 4, "top": 2, "expert_size": 24}
+
+
+def plain_routed_toy(weights, ids, wave_scale=1.0):
+    """Returns the logits and the smallest gap between the last chosen and the first rejected router logit."""
+    w = {name: tensor.double() for name, tensor in weights.items()}
+    seq = len(ids)
+    x = w["toy.embed.weight"][torch.tensor(ids)]
+    positions = torch.arange(seq)
+    smallest_gap = math.inf
+
+    def attention(x, prefix, qk_norm, encode):
+        normed = plain_impl.rms_norm(x, w[prefix + "norm_a.weight"], 1e-5)
+        q = plain_impl.linear(normed, w[prefix + "mixer.q_proj.weight"]).reshape(seq, 3, 16)
+        k = plain_impl.linear(normed, w[prefix + "mixer.k_proj.weight"]).reshape(seq, 1, 16)
+        v = plain_impl.linear(normed, w[prefix + "mixer.v_proj.weight"]).reshape(seq, 1, 16)
+        if qk_norm:
+            q = plain_impl.rms_norm(q, w[prefix + "mixer.q_norm.weight"], 1e-5)
+            k = plain_impl.rms_norm(k, w[prefix + "mixer.k_norm.weight"], 1e-5)
+        q, k = encode(q, k)
+        mixed = plain_impl.attention_scores_softmax_values(q, k, v, 0.25, None)
+        return x + plain_impl.linear(mixed.reshape(seq, -1), w[prefix + "mixer.o_proj.weight"])
+
+    def wave(amplitude):
+        angle = positions.double()[:, None, None] / (torch.arange(16, dtype=torch.float64) + 2.0)
+        amplitude = amplitude * wave_scale
+        return lambda q, k: (q + amplitude * torch.sin(angle), k + amplitude * torch.cos(angle))
+
+    def rotary(q, k):
+        frequencies = plain_impl.rope_inverse_frequencies(8, 100.0, None)
+        turn = lambda t: torch.cat([plain_impl.rope(t[..., :8], positions, frequencies), t[..., 8:]], dim=-1)
+        return turn(q), turn(k)
+
+    def routed(x, prefix):
+        nonlocal smallest_gap
+        normed = plain_impl.rms_norm(x, w[prefix + "norm_b.weight"], 1e-5)
+        logits = normed @ w[prefix + "ff.router.weight"].T
+        ordered = logits.sort(dim=-1, descending=True)
+        smallest_gap = min(smallest_gap, float((ordered.values[:, 1] - ordered.values[:, 2]).min()))
+        share = torch.softmax(ordered.values[:, :2], dim=-1)
+        out = torch.zeros_like(x)
+        for token in range(seq):
+            for place in range(2):
+                expert = int(ordered.indices[token, place])
+                inner = torch.relu(w[prefix + "ff.experts.in"][expert] @ normed[token])
+                out[token] += share[token, place] * (w[prefix + "ff.experts.out"][expert] @ inner)
+        return x + out
+
+    x = routed(attention(x, "toy.layers.0.", True, wave(0.5)), "toy.layers.0.")
+    x = attention(x, "toy.layers.1.", False, rotary)
+    x = x + plain_impl.swiglu(plain_impl.rms_norm(x, w["toy.layers.1.norm_b.weight"], 1e-5), w, "toy.layers.1.ff.")
+    x = routed(attention(x, "toy.layers.2.", False, wave(0.25)), "toy.layers.2.")
+    logits = plain_impl.linear(plain_impl.rms_norm(x, w["toy.final_norm.weight"], 1e-5), w["toy.head.weight"])
+    return logits.numpy(), smallest_gap
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 3e-5), ("bfloat16", 4e-2)])
+def test_toy_routed_feed_forward_and_other_position_encoding(tmp_path, dtype, tol):
+    make_routed_toy()
+    from libmir_b200 import CacheConfig, Library, RuntimeConfig, StepEntry
+    from libmir_b200.weights import write_file, write_model_folder
+    folder = write_model_folder(tmp_path, ROUTED_CONFIG, seed=12, dtype=dtype)
+    _, weights = plain_impl.read_model(folder)
+    for name in weights:                     # make the router decisive and the toy parts' numbers matter
+        if name.endswith("router.weight"):
+            weights[name] = weights[name] * 200
+        elif "experts." in name or name.endswith(("q_proj.weight", "k_proj.weight")):
+            weights[name] = weights[name] * 8
+    write_file(folder / "model.safetensors", weights)
+    _, weights = plain_impl.read_model(folder)
+    model = Library(RuntimeConfig(kv_cache=CacheConfig(block_size=8, block_count=24), dtype=dtype)).load(folder)
+    rng = np.random.default_rng(5)
+    ids = random_ids(rng, 77, 70)
+    want, gap = plain_routed_toy(weights, ids)
+    assert gap > 0.2, f"the router's choice is too close to call for a comparison across precisions (gap {gap:.3g})"
+    model.admit("a")
+    got, cursor = [], 0
+    for size in (33, 2, 1, 1, 17, 1, 15):    # portions, then decoded tokens, across page edges
+        result = model.step([StepEntry("a", ids[cursor:cursor + size], range(size))])
+        got.append(result.logits.cpu().numpy())
+        cursor += size
+    got = np.concatenate(got)
+    error = np.abs(got - want).max()
+    assert error <= tol * max(1.0, np.abs(want).max()), f"max |diff| {error:.3e}"
+    without_wave = plain_routed_toy(weights, ids, wave_scale=0.0)[0]
+    assert np.abs(want - without_wave).max() > 10 * tol * np.abs(want).max(), "the toy position encoding must matter"
