@@ -12,13 +12,17 @@
 //   loaders   one warp for keys (and Q, once), one for values.  Per tile the pages that hold it: one TMA box per
 //             page and 64-wide half of the head (cp.async.bulk.tensor.2d through a tensor map over the cache,
 //             128-byte swizzle), into two-stage rings.  Pages the block table does not have (-1) are skipped.
-//   issuer    one thread.  S(t+1) = Q K(t+1)^T is issued before O += P(t) V(t), so that the tensor cores work on
-//             the next scores while the softmax threads are busy with the current ones (two S accumulators).
-//   softmax   sixteen warps: query row r = accumulator lane r belongs to four threads (one in each of the four
-//             warps that may touch that quarter of the lanes), which take 32 columns each (of the scores, of P
-//             and of O) and share the row's maximum through shared memory; four warps per scheduler hide the
-//             latencies of one another's dependent chains (tensor-memory load, maximum, exponentials).  The running
-//             maximum is only raised when a tile's maximum exceeds it by more than 2^8 (then O and the
+//   issuer    one thread.  S(t+2) = Q K(t+2)^T is issued before O += P(t) V(t), as soon as the softmax threads
+//             have read S(t) out of the accumulator it reuses (two S accumulators), so that the tensor cores
+//             work on coming scores while the softmax threads are busy with the current ones.
+//   softmax   two streams of eight warps.  Stream s takes the key tiles t = s, s + 2, ... and keeps a softmax of
+//             its own over them: running maximum, denominator and an O accumulator of its own in tensor memory
+//             (as if the keys were split in two, as decode attention splits them); the two are merged when the
+//             row of tiles is over.  While one stream computes exponentials the other reads scores, finds its
+//             maximum and writes P, so the exponential unit and the tensor cores both stay busy.  Within a
+//             stream, query row r = accumulator lane r belongs to two threads, which take 64 columns each (of
+//             the scores and of P) and share the row's maximum through shared memory.  A stream's running
+//             maximum is only raised when a tile's maximum exceeds it by more than 2^8 (then its O and its
 //             denominator are rescaled, O by tcgen05.ld / tcgen05.st), so most tiles need no pass over O.
 //
 // V is read as an MN-major operand (rows of keys, 64 head elements per 128-byte row) exactly as the cache stores
@@ -44,18 +48,24 @@ constexpr int kHalf = 128 * 128;            // bytes of a 128-row x 64-element h
 constexpr int kTile = 2 * kHalf;            // 32 KB
 constexpr int kOffQ = 0, kOffK = kTile, kOffV = 3 * kTile, kOffP = 5 * kTile;
 constexpr int kSmemBytes = 6 * kTile + 1024;
-// kParts softmax threads per query row (each takes 128 / kParts columns): key loader, issuer, 4 kParts softmax
-// warps, value loader
-__host__ __device__ constexpr int threads_for(int parts) { return (3 + 4 * parts) * 32; }
-constexpr uint32_t kTmemColumns = 512;      // S0 at 0, S1 at 128, O at 256
+constexpr int kParts = 2;                   // softmax threads per query row and stream (each takes 64 columns)
+constexpr int kCols = kKeys / kParts;       // columns of a tile that one softmax thread handles
+constexpr int kStreamThreads = kRows * kParts;
+// key loader, issuer, eight softmax warps per stream, value loader
+__host__ __device__ constexpr int threads_for(int streams) { return (3 + 8 * streams) * 32; }
+constexpr uint32_t kTmemColumns = 512;      // S0 at 0, S1 at 128, O of stream 0 at 256, of stream 1 at 384
 constexpr float kRescaleThreshold = 8.0f;   // log2 of how far a tile's maximum may exceed the running one
 
 // barrier indices
 enum { Q_FULL = 0, K_FULL = 1, K_FREE = 3, V_FULL = 5, V_FREE = 7, S_FULL = 9, S_FREE = 11, P_READY = 13, PV_DONE = 14,
-       BARRIERS = 15 };
+       BARRIERS = 16 };
+// PV_DONE + (t & 1) for tile t: a wait on an mbarrier names a phase by its parity only, so a thread may only wait
+// for a phase when it knows that the phase before has completed.  A stream that takes every second tile waits
+// for the products of the tiles in between; with one barrier for all tiles it would see every second phase
+// only, with one for even and one for odd tiles it sees every phase of the one it waits on.
 
 __device__ int g_tc_attention_error = 0;
-int g_softmax_parts = 2;
+int g_streams = 2;
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -82,22 +92,23 @@ __device__ __forceinline__ void tmem_load_32_nowait(uint32_t address, float* v) 
 __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // One tile of the softmax for this thread's part (kCols columns starting at `first`) of its row: the scores are
-// read once (all loads in flight, one wait), then the visible maximum (columns low..high of the tile; all if
+// read once (all loads in flight, one wait; then `scores_read` is told), then the visible maximum (columns low..high of the tile; all if
 // !MASKED), which the kParts threads of a row exchange through `shared_max` (one float per part, kRows apart)
-// and the named barrier `team` of the four warps that hold the row's quarter of lanes; then the decision whether
+// and the named barrier `team` of the stream's warps that hold the row's quarter of lanes; then the decision whether
 // the running maximum rises, and p = exp2(scale s - reference) packed to bf16.  Returns the sum of this thread's p.
-template <int kParts, bool MASKED>
+template <bool MASKED>
 __device__ __forceinline__ float softmax_tile(uint32_t scores, int first, int low, int high, float scale_log2,
                                               float& reference, float& factor, bool& grow,
-                                              uint32_t (&packed)[kKeys / kParts / 2], float* shared_max, int part,
-                                              int team) {
-  constexpr int kCols = kKeys / kParts;        // columns of a tile that one softmax thread handles
+                                              uint32_t (&packed)[kCols / 2], float* shared_max, int part, int team,
+                                              uint32_t scores_read) {
   float v[kCols];
 #pragma unroll
   for (int c0 = 0; c0 < kCols; c0 += 32) tmem_load_32_nowait(scores + first + c0, v + c0);
   tmem_load_wait();
 #pragma unroll
   for (int c = 0; c < kCols; ++c) asm volatile("" : "+f"(v[c])::"memory");   // no use of v moves above the wait
+  tensor_fence_before_sync();
+  barrier_arrive(scores_read);                                         // the scores are in registers
   float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};        // four chains instead of one
 #pragma unroll
   for (int c = 0; c < kCols; ++c)
@@ -127,19 +138,20 @@ __device__ __forceinline__ float softmax_tile(uint32_t scores, int first, int lo
   return (sums[0] + sums[1]) + (sums[2] + sums[3]);
 }
 
-template <int kParts>
-__global__ void __launch_bounds__(threads_for(kParts), 1)
+template <int kStreams>
+__global__ void __launch_bounds__(threads_for(kStreams), 1)
 tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                             const __grid_constant__ CUtensorMap v_map, bf16* __restrict__ out,
                             const int* __restrict__ block_table, int table_width, const int* __restrict__ query_starts,
                             const int* __restrict__ context_lens, int num_rows, int page_size, int heads, int kv_heads,
                             float scale_log2, int window) {
-  constexpr int kThreads = threads_for(kParts), kSoftmaxThreads = kRows * kParts, kCols = kKeys / kParts;
+  constexpr int kThreads = threads_for(kStreams);
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long barriers[BARRIERS];
   __shared__ uint32_t tmem_base_slot;
-  __shared__ float exchange[2][kParts][kRows];               // [tile parity][part][row]: what a row's threads share
-  __shared__ float denominators[kParts][kRows];              // (apart: a slow thread may still read the last maxima)
+  __shared__ float exchange[kStreams][2][kParts][kRows];     // [stream][its tile parity][part][row]: a row's maxima
+  __shared__ float denominators[kStreams][kParts][kRows];    // (apart: a slow thread may still read the last maxima)
+  __shared__ float references[kStreams][kRows];
   if (*reinterpret_cast<volatile int*>(&g_tc_attention_error) != 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // The head is the fast index of the grid: CTAs are handed out in the order of blockIdx.x first, so all heads of
@@ -181,8 +193,8 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < BARRIERS; ++i) {
-      const bool many = i == S_FREE || i == S_FREE + 1 || i == P_READY;   // every softmax thread arrives
-      barrier_init(bar(i), many ? (uint32_t)kSoftmaxThreads : 1u);
+      const bool many = i == S_FREE || i == S_FREE + 1 || i == P_READY;   // every softmax thread of a stream arrives
+      barrier_init(bar(i), many ? (uint32_t)kStreamThreads : 1u);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -262,9 +274,13 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         mma_commit(bar(S_FULL + stage));
         mma_commit(bar(K_FREE + stage));
       };
+      // scores run two tiles ahead of the products with P: S(t + 2) goes into the accumulator of S(t) as soon as
+      // the softmax threads have read that (early in their work on tile t), so a stream finds its next scores
+      // ready when it is done with a tile
       issue_scores(0);
+      if (tiles > 1) issue_scores(1);
       for (int t = 0; t < tiles; ++t) {
-        if (t + 1 < tiles) issue_scores(t + 1);
+        if (t + 2 < tiles) issue_scores(t + 2);
         const int stage = t & 1;
         const uint32_t parity = (uint32_t)(t >> 1) & 1u;
         if (alive && !wait_barrier(bar(V_FULL + stage), parity)) { g_tc_attention_error = 2; alive = false; }
@@ -275,27 +291,30 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         for (int kk = 0; kk < kKeys / 16; ++kk) {
           // P: 16 keys further along its 128-byte rows; V: 16 rows of keys further down
           const uint32_t a_offset = (uint32_t)(kk >> 2) * kHalf + (uint32_t)(kk & 3) * 32u;
-          mma_bf16_ss(tmem_o, operand_descriptor(a + a_offset), operand_descriptor_mn_major(b + (uint32_t)kk * 2048u, kHalf),
-                      idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
+          mma_bf16_ss(tmem_o + (uint32_t)(t % kStreams) * 128u, operand_descriptor(a + a_offset),
+                      operand_descriptor_mn_major(b + (uint32_t)kk * 2048u, kHalf), idesc_pv,
+                      (t >= kStreams || kk > 0) ? 1u : 0u);
         }
-        mma_commit(bar(PV_DONE));
+        mma_commit(bar(PV_DONE + (t & 1)));
         mma_commit(bar(V_FREE + stage));
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax: kParts threads per query row
+    // ------------------------------------------------------------------ softmax: kStreams streams of eight warps
+    const int stream = (warp - 2) >> 3;                       // takes the tiles t = stream, stream + kStreams, ...
     const int quarter = warp & 3;                             // the accumulator lanes this warp may touch
-    const int part = (warp - 2) >> 2;                         // which kCols columns of the row (and of O) it takes
+    const int part = ((warp - 2) >> 2) & 1;                   // which kCols columns of the row it takes
     const int r = quarter * 32 + lane;
     const bool valid_row = r < tile_rows;
     const int position = first_position + min(r, tile_rows - 1);
     const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
     const int first = part * kCols;
+    const uint32_t my_o = tmem_o + (uint32_t)stream * 128u + lane_bits;
     float reference = -INFINITY, denominator = 0.0f;          // running maximum (scaled, log2 domain), partial sum
     bool alive = true;
     // (a thread whose wait ran out keeps walking the tiles without waiting, so that the row's named barrier
     // still sees all of its threads)
-    for (int t = 0; t < tiles; ++t) {
+    for (int t = stream; t < tiles; t += kStreams) {
       const int stage = t & 1;
       const uint32_t parity = (uint32_t)(t >> 1) & 1u;
       const int key0 = key_begin + t * kKeys;
@@ -309,36 +328,38 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       uint32_t packed[kCols / 2];
       bool grow;
       float factor;
-      float* shared_max = &exchange[stage][0][r];
-      const float sum = every ? softmax_tile<kParts, false>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
-                                                    shared_max, part, 1 + quarter)
-                              : softmax_tile<kParts, true>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
-                                                   shared_max, part, 1 + quarter);
-      tensor_fence_before_sync();
-      barrier_arrive(bar(S_FREE + stage));                    // the scores are in registers
+      float* shared_max = &exchange[stream][(t / kStreams) & 1][0][r];
+      const int team = 1 + stream * 4 + quarter;
+      const float sum = every ? softmax_tile<false>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
+                                                    shared_max, part, team, bar(S_FREE + stage))
+                              : softmax_tile<true>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
+                                                   shared_max, part, team, bar(S_FREE + stage));
       denominator = denominator * factor + sum;
-      // the product with the previous tile's P must be over before P or O change
+      // the product with the previous tile's P (the other stream's, if there are two) must be over before P
+      // changes, and this stream's previous product before its O does
       if (t > 0) {
-        if (alive && !wait_barrier(bar(PV_DONE), (uint32_t)(t - 1) & 1u)) { g_tc_attention_error = 3; alive = false; }
+        if (alive && !wait_barrier(bar(PV_DONE + ((t - 1) & 1)), (uint32_t)((t - 1) >> 1) & 1u)) {
+          g_tc_attention_error = 3;
+          alive = false;
+        }
         tensor_fence_after_sync();
-        if (__any_sync(0xffffffffu, grow)) {
+        if (t >= kStreams && __any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
           for (int c0 = 0; c0 < kDim / kParts; c0 += 32) {
             float o[32];
-            tmem_load_32(tmem_o + lane_bits + first + c0, o);
+            tmem_load_32(my_o + first + c0, o);
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] *= factor;
-            tmem_store_32(tmem_o + lane_bits + first + c0, o);
+            tmem_store_32(my_o + first + c0, o);
           }
           tmem_store_wait();
         }
       }
-      // P as the A operand: rows of 128 bytes (64 keys), 16-byte chunks swizzled by the row; this thread's columns
-      // are chunks first / 8 ... of the half they lie in
-      unsigned char* p_row = smem + kOffP + (size_t)(first / 64) * kHalf + (size_t)r * 128;
+      // P as the A operand: rows of 128 bytes (64 keys: this thread's half), 16-byte chunks swizzled by the row
+      unsigned char* p_row = smem + kOffP + (size_t)part * kHalf + (size_t)r * 128;
 #pragma unroll
-      for (int chunk = 0; chunk < kCols / 8; ++chunk) {
-        const int where = ((first % 64) / 8 + chunk) ^ (r & 7);
+      for (int chunk = 0; chunk < 8; ++chunk) {
+        const int where = chunk ^ (r & 7);
         *reinterpret_cast<uint4*>(p_row + where * 16) =
             make_uint4(packed[4 * chunk], packed[4 * chunk + 1], packed[4 * chunk + 2], packed[4 * chunk + 3]);
       }
@@ -346,28 +367,54 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       tensor_fence_before_sync();
       barrier_arrive(bar(P_READY));
     }
-    // the row's denominator is the sum of its threads' parts
-    denominators[part][r] = denominator;
-    asm volatile("bar.sync %0, %1;" ::"r"(5 + quarter), "n"(32 * kParts) : "memory");
-    denominator = 0.0f;
+    // every softmax thread learns every stream's maximum and denominator (the sum of its two threads' parts)
+    denominators[stream][part][r] = denominator;
+    if (part == 0) references[stream][r] = reference;
+    asm volatile("bar.sync %0, %1;" ::"r"(9), "n"(kStreamThreads * kStreams) : "memory");
+    float top = -INFINITY;
 #pragma unroll
-    for (int other = 0; other < kParts; ++other) denominator += denominators[other][r];
-    if (alive && !wait_barrier(bar(PV_DONE), (uint32_t)(tiles - 1) & 1u)) { g_tc_attention_error = 3; alive = false; }
+    for (int other = 0; other < kStreams; ++other) top = fmaxf(top, references[other][r]);
+    float weight[kStreams], total = 0.0f;
+#pragma unroll
+    for (int other = 0; other < kStreams; ++other) {
+      const float theirs = references[other][r];              // -inf: that stream saw no key of this row
+      weight[other] = theirs > -INFINITY ? fast_exp2(theirs - top) : 0.0f;
+      total += (denominators[other][0][r] + denominators[other][1][r]) * weight[other];
+    }
+    // (every thread has passed the named barrier above, so the products before the last one are over)
+    if (alive && !wait_barrier(bar(PV_DONE + ((tiles - 1) & 1)), (uint32_t)((tiles - 1) >> 1) & 1u)) {
+      g_tc_attention_error = 3;
+      alive = false;
+    }
     tensor_fence_after_sync();
     if (alive) {
-      const float inverse = denominator > 0.0f ? 1.0f / denominator : 0.0f;
-      bf16* dst = out + ((size_t)(q_begin + local0 + r) * heads + head) * kDim + first;
+      // this thread's columns of the output: the row's 128 are shared out over all its softmax threads
+      constexpr int kOut = kDim / (kParts * kStreams);
+      const int column = (stream * kParts + part) * kOut;
+      const float inverse = total > 0.0f ? 1.0f / total : 0.0f;
+      bf16* dst = out + ((size_t)(q_begin + local0 + r) * heads + head) * kDim + column;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kDim / kParts; c0 += 32) {
+      for (int c0 = 0; c0 < kOut; c0 += 32) {
         float o[32];
-        tmem_load_32(tmem_o + lane_bits + first + c0, o);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = 0.0f;
+#pragma unroll
+        for (int other = 0; other < kStreams; ++other) {
+          if (other < tiles) {                                // a stream without a tile never wrote its O
+            float theirs[32];
+            tmem_load_32(tmem_o + (uint32_t)other * 128u + lane_bits + column + c0, theirs);
+            const float w = weight[other] * inverse;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] += w > 0.0f ? theirs[i] * w : 0.0f;
+          }
+        }
         if (valid_row) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 packed_out;
             __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed_out);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(o[i + 2 * j] * inverse, o[i + 2 * j + 1] * inverse);
+            for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(o[i + 2 * j], o[i + 2 * j + 1]);
             *reinterpret_cast<uint4*>(dst + c0 + i) = packed_out;
           }
         }
@@ -429,7 +476,7 @@ MIR_EXPORT int mir_prefill_attention_tc_bf16(const void* q, long long q_stride, 
     cudaError_t err = cudaFuncSetAttribute(tc_prefill_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            kSmemBytes);
     if (err == cudaSuccess)
-      err = cudaFuncSetAttribute(tc_prefill_attention_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+      err = cudaFuncSetAttribute(tc_prefill_attention_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (err != cudaSuccess) {
       mir_set_error("prefill_attention_tc: cannot reserve %d bytes of shared memory: %s", kSmemBytes,
                     cudaGetErrorString(err));
@@ -442,20 +489,20 @@ MIR_EXPORT int mir_prefill_attention_tc_bf16(const void* q, long long q_stride, 
     mir_set_error("prefill_attention_tc: %d tokens in %d rows are more than one launch takes", tokens, num_rows);
     return MIR_BAD_ARGUMENT;
   }
-  if (g_softmax_parts == 2)
+  if (g_streams == 2)
     return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<2>, dim3(heads, tiles), dim3(threads_for(2)),
                       (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, (bf16*)out, block_table, table_width,
                       query_starts, context_lens, num_rows, page_size, heads, kv_heads,
                       scale * 1.4426950408889634f, window);
-  return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<4>, dim3(heads, tiles), dim3(threads_for(4)),
+  return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<1>, dim3(heads, tiles), dim3(threads_for(1)),
                     (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, (bf16*)out, block_table, table_width,
                     query_starts, context_lens, num_rows, page_size, heads, kv_heads,
                     scale * 1.4426950408889634f, window);
 }
 
-// How many softmax threads share a query row: 2 (eight softmax warps) or 4 (sixteen).
-MIR_EXPORT int mir_prefill_attention_tc_set_parts(int parts) {
-  if (parts != 2 && parts != 4) return MIR_BAD_ARGUMENT;
-  g_softmax_parts = parts;
+// For measurements: 2 (the default) splits a row's key tiles over two softmax streams, 1 runs one stream.
+MIR_EXPORT int mir_prefill_attention_tc_set_streams(int streams) {
+  if (streams != 1 && streams != 2) return MIR_BAD_ARGUMENT;
+  g_streams = streams;
   return MIR_OK;
 }

@@ -51,7 +51,7 @@ _SIGNATURES = {
                                           c_void_p],
         "mir_prefill_attention_tc_takes": [c_int, c_int],
         "mir_prefill_attention_tc_error": [],
-        "mir_prefill_attention_tc_set_parts": [c_int],
+        "mir_prefill_attention_tc_set_streams": [c_int],
         "mir_gemm_skinny_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                  c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mir_gemm_tc_stream_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -408,10 +408,10 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
         kv_heads, head_dim, scale, int(window or 0), _stream()))
 
 
-def set_prefill_softmax_threads_per_row(parts: int) -> None:
-    """How many softmax threads of the tcgen05 attention share a query row: 2 or 4 (the default)."""
+def set_prefill_softmax_streams(streams: int) -> None:
+    """For measurements: over how many softmax streams the tcgen05 attention splits a row's key tiles, 1 or 2."""
     lib = library("bf16")
-    _check(lib, lib.mir_prefill_attention_tc_set_parts(int(parts)))
+    _check(lib, lib.mir_prefill_attention_tc_set_streams(int(streams)))
 
 
 def prefill_attention_error() -> int:
