@@ -259,3 +259,45 @@ def test_decode_attention_over_a_long_context():
     expected = torch.cat([expect(q, k, v, scale, None, slice(n - 1, n)) for q, k, v, n in zip(qs, ks, vs, lengths)])
     close(out.reshape(rows, heads, dim), expected)
     assert torch.allclose(out.reshape(rows, heads, dim)[0, 0].float().cpu(), vs[0][777, 0].float(), atol=5e-2)
+
+
+@pytest.mark.parametrize("window", [None, 1000])
+def test_prefill_attention_on_tcgen05_over_a_long_prompt(window):
+    """9,000 tokens in one portion: 71 key tiles for the last queries, shared out over both softmax streams; keys
+    late in the prompt that dominate (one in an even tile, one in an odd one) raise each stream's running maximum
+    after thousands of keys, which rescales what it has accumulated.  Checked on a sample of query rows."""
+    from libmir_b200 import kernels
+    heads, kv_heads, dim, page, n = 4, 2, 128, 16, 9000
+    rng = np.random.default_rng(17)
+    torch.manual_seed(17)
+    scale = 1.0 / math.sqrt(dim)
+    q = torch.randn(n, heads, dim).to(BF16)
+    k = torch.randn(n, kv_heads, dim).to(BF16)
+    v = torch.randn(n, kv_heads, dim).to(BF16)
+    for key in (7000, 7000 + 128 + 5):                         # tile 54 (even) and tile 55 (odd)
+        k[key, 0] = (q[8500, 0].float() * 2.0).to(BF16)        # head 0 of query 8500 looks straight at them
+        k[key, 1] = (q[8990, 3].float() * 2.0).to(BF16)
+    k_pool, v_pool, table = build_pool([k], [v], page, rng)
+    packed = torch.cat([q.reshape(n, -1), torch.zeros(n, 2 * kv_heads * dim, dtype=BF16)], dim=1).contiguous()
+    out = torch.full((n, heads * dim), 9.0, device="cuda", dtype=BF16)
+    kernels.prefill_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table),
+                              cuda(torch.tensor([0, n], dtype=torch.int32)), cuda(torch.tensor([n], dtype=torch.int32)),
+                              page, heads, kv_heads, dim, scale, window, tensor_cores=True)
+    torch.cuda.synchronize()
+    assert kernels.prefill_attention_error() == 0
+    rows = sorted(set([0, 1, 127, 128, 129, 999, 1000, 1001, 4095, 4096, 7133, 7134, 8500, 8990, n - 1]
+                      + rng.integers(0, n, 150).tolist()))
+    qd, kd, vd = cuda(q).double(), cuda(k).double(), cuda(v).double()
+    group = heads // kv_heads
+    index = torch.tensor(rows, device="cuda")
+    scores = torch.einsum("rhd,shd->rhs", qd[index], kd.repeat_interleave(group, dim=1)) * scale
+    keys = torch.arange(n, device="cuda")
+    visible = keys[None, :] <= index[:, None]
+    if window is not None:
+        visible &= keys[None, :] > index[:, None] - window
+    scores = scores.masked_fill(~visible[:, None, :], float("-inf"))
+    expected = torch.einsum("rhs,shd->rhd", torch.softmax(scores, dim=-1), vd.repeat_interleave(group, dim=1))
+    close(out.reshape(n, heads, dim)[index], expected)
+    if window is None:                                         # the two planted keys carry nearly all the weight
+        planted = (v[7000, 0].float() + v[7133, 0].float()) / 2
+        assert torch.allclose(out.reshape(n, heads, dim)[8500, 0].float().cpu(), planted, atol=6e-2)
