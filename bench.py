@@ -146,6 +146,9 @@ def main() -> int:
                         help="layer sizes of the model (default: the headline configuration)")
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has")
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=PROMPT_TOKENS,
+                        help="tokens every request holds when decoding starts, and the length of the timed prompt "
+                             "(default: the headline configuration's 2,048; up to 8,192 in one prefill step)")
     parser.add_argument("--skip-points", action="store_true", help="only the batch-8 decode and the prefill")
     parser.add_argument("--deep-ring-ctas", type=int, default=None,
                         help="up to how many CTAs decode attention keeps three tiles in flight per warp")
@@ -215,8 +218,11 @@ def main() -> int:
     if args.layers:
         config["num_hidden_layers"] = args.layers
     layers = config["num_hidden_layers"]
-    max_batch = max(64, args.batch)
-    context_limit = PROMPT_TOKENS + GENERATED_TOKENS + args.steps + args.warmup + 64
+    prompt_tokens = args.context
+    if not 1 <= prompt_tokens <= 8192 and args.phase != "decode":
+        parser.error("--context above 8,192 only with --phase decode (one prefill step holds up to 8,192 tokens)")
+    max_batch = args.batch if (args.skip_points or args.phase != "all") else max(64, args.batch)
+    context_limit = prompt_tokens + GENERATED_TOKENS + args.steps + args.warmup + 64
     pages = max_batch * (-(-context_limit // PAGE_SIZE)) + 64
     runtime = RuntimeConfig(kv_cache=CacheConfig(block_size=PAGE_SIZE, block_count=pages),
                             scheduler=SchedulerConfig(max_batch_requests=max_batch, max_batch_tokens=8192,
@@ -237,8 +243,8 @@ def main() -> int:
         for index in range(batch):
             request_id = f"d{batch}-{index}"
             seq = model.cache.admit(request_id)
-            model.cache.grow(seq, PROMPT_TOKENS)
-            model.cache.commit(seq, PROMPT_TOKENS)
+            model.cache.grow(seq, prompt_tokens)
+            model.cache.commit(seq, prompt_tokens)
             ids.append(request_id)
         return ids
 
@@ -268,7 +274,7 @@ def main() -> int:
             torch.cuda.synchronize()
         ms = start.elapsed_time(stop)
         launches = kernels.LAUNCHES - launches
-        context = PROMPT_TOKENS + warmup + steps / 2.0
+        context = prompt_tokens + warmup + steps / 2.0
         release(ids)
         return batch * steps / (ms / 1e3), ms / steps, launches, clocks.summary(), context
 
@@ -300,7 +306,7 @@ def main() -> int:
         return batch * steps / seconds, h2d, d2h
 
     def prefill(repeats=5, profile=False):
-        tokens = rng.integers(0, vocab, size=PROMPT_TOKENS).tolist()
+        tokens = rng.integers(0, vocab, size=prompt_tokens).tolist()
         times = []
         for index in range(repeats + 2):
             request_id = f"p{index}"
@@ -310,7 +316,7 @@ def main() -> int:
             if profile and index == 2:
                 torch.cuda.profiler.start()
             start.record()
-            result = model.step([StepEntry(request_id, tokens, [PROMPT_TOKENS - 1])], [RequestSampler()])
+            result = model.step([StepEntry(request_id, tokens, [prompt_tokens - 1])], [RequestSampler()])
             stop.record()
             torch.cuda.synchronize()
             result.tokens.cpu()
@@ -325,23 +331,27 @@ def main() -> int:
                                                                "num_attention_heads", "num_key_value_heads",
                                                                "head_dim"))
     per_layer = hidden * (heads + 2 * kv_heads) * dim + heads * dim * hidden + 3 * hidden * inter
-    gemm_flops = 2.0 * PROMPT_TOKENS * per_layer * layers + 2.0 * hidden * vocab
-    attention_flops = 4.0 * heads * dim * (PROMPT_TOKENS * (PROMPT_TOKENS + 1) / 2.0) * layers
+    gemm_flops = 2.0 * prompt_tokens * per_layer * layers + 2.0 * hidden * vocab
+    attention_flops = 4.0 * heads * dim * (prompt_tokens * (prompt_tokens + 1) / 2.0) * layers
     prefill_flops = gemm_flops + attention_flops
 
     if args.phase == "decode":
-        device_value = device_ms = launches = 0.0
+        device_value = device_ms = launches = hbm_frac = 0.0
         if not args.no_graphs:
-            device_value, device_ms, launches, _, _ = decode_device(args.batch, args.steps, args.warmup)
+            device_value, device_ms, launches, _, context = decode_device(args.batch, args.steps, args.warmup)
+            step_bytes = weight_bytes + args.batch * context * kv_bytes_per_token
+            hbm_frac = step_bytes / (device_ms / 1e3) / 1e9 / peaks["hbm_gbs"]
         tokens_per_second, _, _ = decode_e2e(args.batch, args.steps, args.warmup, profile=True)
         print(json.dumps({"phase": "decode", "batch": args.batch, "steps": args.steps, "layers": layers,
                           "graphs": not args.no_graphs, "tokens_per_second": round(tokens_per_second, 1),
                           "device_tokens_per_second": round(device_value, 1), "device_ms_per_step": round(device_ms, 4),
+                          "context": prompt_tokens, "hbm_frac": round(hbm_frac, 4),
                           "launches_per_step": launches / max(1, args.steps)}))
         return 0
     if args.phase == "prefill":
         ms = prefill(repeats=max(1, min(args.steps, 5)), profile=True)
-        print(json.dumps({"phase": "prefill", "tokens": PROMPT_TOKENS, "layers": layers, "ms": round(ms, 3)}))
+        print(json.dumps({"phase": "prefill", "tokens": prompt_tokens, "layers": layers, "ms": round(ms, 3),
+                          "frac_of_peak": round(prefill_flops / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}))
         return 0
 
     value, ms_per_step, launches, clocks, context = decode_device(args.batch, args.steps, args.warmup)
@@ -362,7 +372,7 @@ def main() -> int:
         "config": {
             "model": sizes_name, "layers": layers, "layers_of_config": layers_full,
             "hidden": hidden, "heads": heads, "kv_heads": kv_heads, "head_dim": dim, "intermediate": inter,
-            "vocab": vocab, "global_batch": args.batch, "seq_len": PROMPT_TOKENS + GENERATED_TOKENS,
+            "vocab": vocab, "global_batch": args.batch, "seq_len": prompt_tokens + GENERATED_TOKENS,
             "context_at_decode": round(context, 1), "page_size": PAGE_SIZE, "tied_embeddings": bool(config.get("tie_word_embeddings", False)),
             "parallelism": "1 GPU", "l2": "inputs larger than L2 (a step reads every weight and the cache)",
             "peaks": peaks_kind,
@@ -371,7 +381,7 @@ def main() -> int:
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
         "clocks": clocks,
-        "prefill": {"value": round(PROMPT_TOKENS / (prefill_ms / 1e3), 1), "tokens": PROMPT_TOKENS,
+        "prefill": {"value": round(prompt_tokens / (prefill_ms / 1e3), 1), "tokens": prompt_tokens,
                     "ms": round(prefill_ms, 3),
                     "frac": round(prefill_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",

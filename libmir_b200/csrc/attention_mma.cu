@@ -400,11 +400,20 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
   }
 }
 
+// One CTA of four warps per (request, head).  The partitions are shared out over the warps (each lane four
+// consecutive elements of the head, 16-byte loads, four partitions in flight), so a long context's hundred
+// partitions cost a few rounds of loads, not a hundred; the warps' sums meet in shared memory.
+constexpr int kMergeWarps = 4;
 template <int D>
-__global__ void decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
-                                    const int* __restrict__ positions, int heads, int window, int partition,
-                                    int num_partitions, bf16* __restrict__ out) {
+__global__ void __launch_bounds__(kMergeWarps * 32)
+decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
+                    const int* __restrict__ positions, int heads, int window, int partition, int num_partitions,
+                    bf16* __restrict__ out) {
+  constexpr int LANES = D / 4;                                 // lanes of a warp that hold elements
+  __shared__ float warp_top[kMergeWarps];
+  __shared__ float sums[kMergeWarps][D + 1];                   // [warp][elements, then the denominator]
   const int head = blockIdx.x, row = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   grid_launch_dependents();
   grid_dependency_wait();
   const int position = positions[row];
@@ -417,16 +426,49 @@ __global__ void decode_merge_kernel(const float* __restrict__ partial_o, const f
   const int first_key = (window > 0 && context > window) ? context - window : 0;
   const int first_part = (first_key / kDecodeTile * kDecodeTile) / partition;
   const int last_part = position / partition;
+  const float* ml = partial_ml + index * num_partitions * 2;
+  const float* o = partial_o + index * num_partitions * D;
+  // the largest maximum over all partitions
   float top = -INFINITY;
-  for (int p = first_part; p <= last_part; ++p) top = fmaxf(top, partial_ml[(index * num_partitions + p) * 2]);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float acc = 0.0f, denom = 0.0f;
-    for (int p = first_part; p <= last_part; ++p) {
-      const float weight = exp2f(partial_ml[(index * num_partitions + p) * 2] - top);
-      acc += partial_o[(index * num_partitions + p) * D + d] * weight;
-      denom += partial_ml[(index * num_partitions + p) * 2 + 1] * weight;
+  for (int p = first_part + (int)threadIdx.x; p <= last_part; p += kMergeWarps * 32) top = fmaxf(top, ml[2 * p]);
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, offset));
+  if (lane == 0) warp_top[warp] = top;
+  __syncthreads();
+  top = fmaxf(fmaxf(warp_top[0], warp_top[1]), fmaxf(warp_top[2], warp_top[3]));
+  // this warp's partitions
+  float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  float denom = 0.0f;
+  constexpr int kAhead = 4;
+  for (int p0 = first_part + warp; p0 <= last_part; p0 += kMergeWarps * kAhead) {
+    float4 piece[kAhead];
+    float weight[kAhead], part_denom[kAhead];
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i) {
+      const int p = p0 + i * kMergeWarps;
+      const bool live = p <= last_part;
+      piece[i] = (live && lane < LANES) ? *reinterpret_cast<const float4*>(o + (size_t)p * D + 4 * lane)
+                                        : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      weight[i] = live ? ml[2 * p] : -INFINITY;
+      part_denom[i] = live ? ml[2 * p + 1] : 0.0f;
     }
-    out[index * D + d] = __float2bfloat16_rn(denom > 0.0f ? acc / denom : 0.0f);
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i) {
+      const float w = weight[i] > -INFINITY ? exp2f(weight[i] - top) : 0.0f;   // (a partition that saw no key)
+      acc.x += piece[i].x * w; acc.y += piece[i].y * w; acc.z += piece[i].z * w; acc.w += piece[i].w * w;
+      denom += part_denom[i] * w;
+    }
+  }
+  if (lane < LANES) {
+    sums[warp][4 * lane] = acc.x; sums[warp][4 * lane + 1] = acc.y;
+    sums[warp][4 * lane + 2] = acc.z; sums[warp][4 * lane + 3] = acc.w;
+  }
+  if (lane == 0) sums[warp][D] = denom;
+  __syncthreads();
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float total = (sums[0][d] + sums[1][d]) + (sums[2][d] + sums[3][d]);
+    const float all = (sums[0][D] + sums[1][D]) + (sums[2][D] + sums[3][D]);
+    out[index * D + d] = __float2bfloat16_rn(all > 0.0f ? total / all : 0.0f);
   }
 }
 
@@ -587,7 +629,7 @@ int launch_decode_staged(const bf16* q, size_t q_stride, bf16* out, const bf16* 
                            table_width, positions, page_size, heads, kv_heads, scale * 1.4426950408889634f, window,
                            partition, num_partitions, partial_o, partial_ml, out);
   if (status != MIR_OK || num_partitions == 1) return status;
-  return mir_launch("decode_merge", decode_merge_kernel<D>, dim3(heads, rows), dim3(D <= 64 ? 64 : 128), 0, stream, 0,
+  return mir_launch("decode_merge", decode_merge_kernel<D>, dim3(heads, rows), dim3(kMergeWarps * 32), 0, stream, 0,
                     (const float*)partial_o, (const float*)partial_ml, positions, heads, window, partition,
                     num_partitions, out);
 }
