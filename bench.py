@@ -152,10 +152,8 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="only the batch-8 decode and the prefill")
     parser.add_argument("--deep-ring-ctas", type=int, default=None,
                         help="up to how many CTAs decode attention keeps three tiles in flight per warp")
-    parser.add_argument("--decode-ctas-per-sm", type=int, default=None,
-                        help="CTAs per SM that split decode attention aims for when it picks the partition size")
     parser.add_argument("--set", action="append", default=[], metavar="NAME=VALUE",
-                        help="set a tuning constant of libmir_b200.kernels (an integer), e.g. STREAM_ACCUM_MIN_ROWS=1")
+                        help="set a tuning constant of libmir_b200.kernels (an integer), e.g. DECODE_PARTITION_KEYS=512")
     parser.add_argument("--stream-shape", default=None, metavar="SPLITS,RING_KB,TILE_ROWS",
                         help="fix the shape of the weight-streaming product (0 = chosen by the launcher), e.g. 0,56,0")
     parser.add_argument("--no-fold-norm", action="store_true",
@@ -203,8 +201,6 @@ def main() -> int:
         lib = kernels.library("bf16")
         if lib.mir_gemm_tc_stream_set_splits(splits, ring_kb, tile_rows) != 0:
             parser.error(lib.mir_last_error().decode())
-    if args.decode_ctas_per_sm is not None:
-        kernels.DECODE_CTAS_PER_SM = args.decode_ctas_per_sm
     if args.deep_ring_ctas is not None:
         import ctypes
         lib = kernels.library("bf16")

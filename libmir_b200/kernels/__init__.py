@@ -327,17 +327,16 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
 
 FAST_HEAD_DIMS = (64, 128)      # what the tensor-core attention kernels take; other sizes use the reference kernel
 SM_COUNT = 148
-DECODE_CTAS_PER_SM = 4      # how many CTAs per SM split decode attention wants before it takes 512-key partitions
+DECODE_PARTITION_KEYS = 256     # keys one CTA of split decode attention takes (a multiple of 64, at most 512)
 
 
 def decode_partitioning(rows: int, kv_heads: int, max_context: int) -> tuple:
-    """(keys per partition, partitions) for split decode attention: 512 keys where that already gives about four
-    CTAs per SM, else 256, so that long contexts at small batch spread over the whole GPU.  Measured at 2,120 keys
-    (attention and merge, us): batch 8 20.0 with 256 keys, 20.7 with 512, 25.9 with 128; batch 1 7.8 / 15.9 / 8.8;
-    batch 64 103 / 105 / 124."""
-    partition = 512
-    if rows * kv_heads * max(1, -(-max_context // partition)) < DECODE_CTAS_PER_SM * SM_COUNT:
-        partition = 256
+    """(keys per partition, partitions) for split decode attention.  256 keys: long contexts at small batch
+    spread over the whole GPU, and the merge shares the partitions out over its warps, so many partitions cost
+    little.  Measured (attention and merge, us, 256 against 512 keys): batch 1 at 2,120 keys 7.8 / 15.9, at
+    32,768 keys 37 / 45; batch 8 at 2,120 keys 20.0 / 20.7, at 8,192 keys 54 / 84, at 32,768 keys 184 / 190;
+    batch 32 at 2,120 keys 56 / 66; batch 64 102 / 106."""
+    partition = DECODE_PARTITION_KEYS
     return partition, max(1, -(-max_context // partition))
 
 
