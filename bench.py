@@ -7,7 +7,7 @@ Prints ONE JSON line.  `value` is decoded tokens per second at batch 8 with 2,04
 per request, timed on the device over exactly K decode steps that run back to back (each step's
 sampled token is the next step's input on the device).  `e2e` is the same through the Python entry
 point with host token ids in and out every step.  `prefill` is one 2,048-token prompt in one step.
-`points` has decode at batch 1 and 64.  Weights are random (N(0, 0.02), seeded), token ids are seeded
+`points` has decode at batch 1 and 64 and the time of a mixed step (32 decoded tokens beside a 512-token portion).  Weights are random (N(0, 0.02), seeded), token ids are seeded
 uniform random, and the cache of the decode runs is filled with random keys and values of the stated
 context length (a decode step's cost does not depend on the values).
 
@@ -323,6 +323,23 @@ def main() -> int:
             torch.cuda.profiler.stop()
         return statistics.median(times)
 
+    def mixed_step(decodes=32, portion=512, repeats=5):
+        """One step of `decodes` single decoded tokens beside one prompt portion of `portion` tokens (ms, host
+        clock around Model.step and the read of the logits)."""
+        ids = fill(decodes)
+        tokens = rng.integers(0, vocab, size=portion).tolist()
+        times = []
+        for index in range(repeats + 1):
+            model.admit("mixed")
+            entries = [StepEntry("mixed", tokens, [portion - 1])] + [StepEntry(i, [5], [0]) for i in ids]
+            torch.cuda.synchronize()
+            started = time.perf_counter()
+            model.step(entries).logits[:, :8].cpu()
+            times.append((time.perf_counter() - started) * 1e3)
+            model.release("mixed")
+        release(ids)
+        return statistics.median(times[1:])
+
     hidden, inter, heads, kv_heads, dim = (config[k] for k in ("hidden_size", "intermediate_size",
                                                                "num_attention_heads", "num_key_value_heads",
                                                                "head_dim"))
@@ -359,6 +376,7 @@ def main() -> int:
     if not args.skip_points:
         for batch in (1, 64):
             points[f"decode_b{batch}"] = round(decode_device(batch, args.steps, args.warmup)[0], 1)
+        points["mixed_32_decodes_512_prompt_tokens_ms"] = round(mixed_step(32, 512), 3)
 
     line = {
         "metric": f"decode tok/s at batch {args.batch} ({sizes_name.split(' (')[0]}, 2,048-token context, 1 B200)",

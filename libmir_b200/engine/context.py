@@ -91,6 +91,10 @@ class StepContext:
     max_context: int = 0
     max_portion: int = 0
     decode_only: bool = False
+    # Rows are ordered with the single-token rows first: rows [0, single_rows) have one token each, and token r is
+    # row r's; single_context is the longest context among them.
+    single_rows: int = 0
+    single_context: int = 0
     page_size: int = 0
     # (residual data_ptr, rows, sums-of-squares tensor, tiles, weighted rows, norm weight data_ptr) or None
     residual_stats: Optional[tuple] = None

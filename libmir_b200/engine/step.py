@@ -93,17 +93,23 @@ class StepRunner:
     def build_context(self, entries: Sequence[StepEntry], sequences) -> tuple:
         manager = self.manager
         page = manager.page_size
+        # Rows are packed with the single-token rows first (a stable order otherwise), so that a mixer can run
+        # them as a batch of decoded tokens beside the prompt portions; what is wanted keeps the entries' order.
+        given = list(entries)
+        order = sorted(range(len(given)), key=lambda index: len(given[index].tokens) != 1)
+        entries = [given[index] for index in order]
+        sequences = [sequences[index] for index in order]
         counts = [len(e.tokens) for e in entries]
         total = sum(counts)
         rows = len(entries)
+        single_rows = sum(1 for c in counts if c == 1)
         tokens = np.empty(total, dtype=np.int32)
         positions = np.empty(total, dtype=np.int32)
         row_of_token = np.empty(total, dtype=np.int32)
         query_starts = np.zeros(rows + 1, dtype=np.int32)
         context_lens = np.empty(rows, dtype=np.int32)
         state_slots = np.empty(rows, dtype=np.int32)
-        want_rows: List[int] = []
-        want_keys: List[tuple] = []
+        wanted: dict = {}
         vocab = self.model.spec.vocab_size
         cursor = 0
         for r, (entry, seq, count) in enumerate(zip(entries, sequences, counts)):
@@ -120,9 +126,14 @@ class StepRunner:
                 if not 0 <= local < count:
                     raise SchedulerError(f"request {entry.request_id!r}: wanted place {local} is outside its "
                                          f"{count} tokens")
-                want_rows.append(cursor + local)
-                want_keys.append((entry.request_id, local))
+            wanted[order[r]] = [(cursor + local, (entry.request_id, local)) for local in entry.want]
             cursor += count
+        want_rows: List[int] = []
+        want_keys: List[tuple] = []
+        for index in range(rows):                          # in the order the entries were given
+            for packed_row, key in wanted[index]:
+                want_rows.append(packed_row)
+                want_keys.append(key)
         arrays = [tokens, positions, row_of_token, query_starts, context_lens, state_slots,
                   np.asarray(want_rows, dtype=np.int32)]
         widths = []
@@ -151,6 +162,7 @@ class StepRunner:
             host_query_starts=query_starts.tolist(), host_start_positions=[seq.length for seq in sequences],
             host_state_slots=state_slots.tolist(), max_context=int(context_lens.max()) if rows else 0,
             max_portion=max(counts) if counts else 0, decode_only=all(c == 1 for c in counts),
+            single_rows=single_rows, single_context=int(context_lens[:single_rows].max()) if single_rows else 0,
             page_size=page)
         return ctx, staged[6], want_keys
 

@@ -376,9 +376,11 @@ PREFILL_TENSOR_CORE_MIN_PORTION = 32
 def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       block_table: torch.Tensor, query_starts: torch.Tensor, context_lens: torch.Tensor,
                       page_size: int, heads: int, kv_heads: int, head_dim: int, scale: float,
-                      window: Optional[int], tensor_cores: Optional[bool] = None) -> None:
-    """bf16 tensor-core attention for any mix of portions (row r owns tokens query_starts[r]..query_starts[r+1]).
-    `tensor_cores`: True runs the tcgen05 kernel, False the mma.sync kernel, None chooses."""
+                      window: Optional[int], tensor_cores: Optional[bool] = None,
+                      portion_tokens: Optional[int] = None) -> None:
+    """bf16 tensor-core attention for any mix of portions (row r owns tokens query_starts[r]..query_starts[r+1]
+    of the packed qkv and out; the rows may be a part of the batch, `portion_tokens` then says how many tokens
+    they have together).  `tensor_cores`: True runs the tcgen05 kernel, False the mma.sync kernel, None chooses."""
     _cuda(qkv, out, k_pages, v_pages, block_table, query_starts, context_lens)
     tokens = out.shape[0]
     rows = context_lens.numel()
@@ -390,7 +392,8 @@ def prefill_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
              and block_table.shape[0] >= rows, "prefill_attention: bad metadata")
     lib = library("bf16")
     if tensor_cores is None:
-        tensor_cores = (PREFILL_TENSOR_CORES and tokens >= PREFILL_TENSOR_CORE_MIN_PORTION * rows
+        portion_tokens = tokens if portion_tokens is None else portion_tokens
+        tensor_cores = (PREFILL_TENSOR_CORES and portion_tokens >= PREFILL_TENSOR_CORE_MIN_PORTION * rows
                         and bool(lib.mir_prefill_attention_tc_takes(head_dim, page_size))
                         and k_pages.is_contiguous() and v_pages.is_contiguous() and scale > 0)
     if tensor_cores:

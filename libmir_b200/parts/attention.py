@@ -124,17 +124,22 @@ class SoftmaxAttention(Mixer):
         single decoded token), everything else runs the reference kernel."""
         s = self.spec
         if self.env.dtype == torch.bfloat16 and s.head_dim in kernels.FAST_HEAD_DIMS:
-            if ctx.decode_only:
-                partition, count = kernels.decode_partitioning(ctx.num_rows, s.kv_heads, ctx.max_context)
-                floats = kernels.decode_attention_scratch_floats(ctx.num_rows, s.heads, s.head_dim, count)
+            # the single-token rows come first in the batch: they run as decoded tokens (keys split over CTAs, the
+            # heads of a KV group in one CTA), the prompt portions after them as tiles of queries
+            singles = ctx.num_rows if ctx.decode_only else getattr(ctx, "single_rows", 0)
+            if singles:
+                longest = ctx.max_context if ctx.decode_only else ctx.single_context
+                partition, count = kernels.decode_partitioning(singles, s.kv_heads, longest)
+                floats = kernels.decode_attention_scratch_floats(singles, s.heads, s.head_dim, count)
                 scratch = ctx.alloc((floats,), torch.float32) if floats else None
-                kernels.decode_attention(qkv, out, cache.k_pages, cache.v_pages, group.block_table, ctx.positions,
-                                         cache.page_size, s.heads, s.kv_heads, s.head_dim, s.scale, s.window,
-                                         partition, count, scratch)
-            else:
-                kernels.prefill_attention(qkv, out, cache.k_pages, cache.v_pages, group.block_table,
-                                          ctx.query_starts, ctx.context_lens, cache.page_size, s.heads, s.kv_heads,
-                                          s.head_dim, s.scale, s.window)
+                kernels.decode_attention(qkv[:singles], out[:singles], cache.k_pages, cache.v_pages,
+                                         group.block_table[:singles], ctx.positions, cache.page_size, s.heads,
+                                         s.kv_heads, s.head_dim, s.scale, s.window, partition, count, scratch)
+            if singles < ctx.num_rows:
+                kernels.prefill_attention(qkv, out, cache.k_pages, cache.v_pages, group.block_table[singles:],
+                                          ctx.query_starts[singles:], ctx.context_lens[singles:], cache.page_size,
+                                          s.heads, s.kv_heads, s.head_dim, s.scale, s.window,
+                                          portion_tokens=out.shape[0] - singles)
             return
         kernels.paged_attention_generic(qkv, out, cache.k_pages, cache.v_pages, group.block_table, ctx.row_of_token,
                                         ctx.positions, cache.page_size, s.heads, s.kv_heads, s.head_dim, s.scale,

@@ -230,6 +230,10 @@ def test_engine_uses_the_fast_kernels_and_matches_the_plain_model(tmp_path, fuse
               f"decode step {offset}")
         assert result.tokens.cpu().tolist() == [int(np.argmax(l)) for l in result.logits.cpu().numpy()]
     assert model.runner._graphs is not None and len(model.runner._graphs.graphs) >= 1
+    # a portion given before a single token: the step packs the single token first, the logits keep the given order
+    result = model.step([StepEntry("b", second[290:300], [9, 0]), StepEntry("a", [first[741]], [0])])
+    assert result.rows == [("b", 9), ("b", 0), ("a", 0)]
+    check(result.logits.cpu().numpy(), np.stack([ref_second[299], ref_second[290], ref_first[741]]), "portion, then single")
 
 
 def test_decode_attention_over_a_long_context():

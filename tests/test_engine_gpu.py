@@ -204,3 +204,30 @@ def test_generate_command_line(tmp_path):
     assert done.returncode == 0, done.stderr[-2000:]
     records = [json.loads(line) for line in done.stdout.strip().splitlines()]
     assert [r["request"] for r in records] == [0, 1] and all(len(r["token_ids"]) == 3 for r in records)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_single_tokens_between_portions_keep_the_order_of_what_is_wanted(tmp_path, dtype):
+    """The step packs single-token rows first (they run as decoded tokens, the portions as tiles of queries);
+    the logits still come in the order of the entries and of their wanted places."""
+    from libmir_b200 import StepEntry
+    folder = make_folder(tmp_path, TINY_B, seed=21, dtype=dtype)
+    rng = np.random.default_rng(21)
+    vocab = TINY_B["vocab_size"]
+    prompts = {name: random_ids(rng, vocab, n) for name, n in (("a", 70), ("b", 41), ("c", 55), ("d", 33))}
+    want = {name: plain_logits(folder, ids) for name, ids in prompts.items()}
+    model = load(folder, dtype, page_size=8, pages=64)
+    for name in prompts:
+        model.admit(name)
+    # b and d are 40 and 32 tokens in already, so that their next token is a single decoded one
+    model.step([StepEntry("b", prompts["b"][:40], []), StepEntry("d", prompts["d"][:32], [])])
+    result = model.step([StepEntry("a", prompts["a"][:37], [36, 0, 5]), StepEntry("b", prompts["b"][40:41], [0]),
+                         StepEntry("c", prompts["c"][:2], [1]), StepEntry("d", prompts["d"][32:33], [0])])
+    assert result.rows == [("a", 36), ("a", 0), ("a", 5), ("b", 0), ("c", 1), ("d", 0)]
+    got = result.logits.cpu().numpy()
+    expected = np.stack([want["a"][36], want["a"][0], want["a"][5], want["b"][40], want["c"][1], want["d"][32]])
+    check(got, expected, TOL[dtype], "mixed step")
+    # and the cache is right afterwards: everyone's next tokens
+    result = model.step([StepEntry("c", prompts["c"][2:55], [52]), StepEntry("a", prompts["a"][37:70], [32])])
+    assert result.rows == [("c", 52), ("a", 32)]
+    check(result.logits.cpu().numpy(), np.stack([want["c"][54], want["a"][69]]), TOL[dtype], "after the mixed step")
