@@ -237,7 +237,7 @@ def test_engine_uses_the_fast_kernels_and_matches_the_plain_model(tmp_path, fuse
 
 
 def test_decode_attention_over_a_long_context():
-    """20,000 cached keys for one request beside a 3-key request: 40 partitions of 512 keys and their merge; one
+    """20,000 cached keys for one request beside a 3-key request: 79 partitions of 256 keys and their merge; one
     far key dominates the long request's scores for some heads."""
     from libmir_b200 import kernels
     heads, kv_heads, dim, page = 8, 2, 128, 16
