@@ -72,6 +72,10 @@ int mir_launch(const char* what, void (*kernel)(KernelArgs...), dim3 grid, dim3 
 }
 
 namespace mir {
+// Row stride (in tokens) of the arrays of partial sums of squares that an accumulating few-rows product leaves for
+// the RMSNorm folded into the next product: [tiles of 16 columns][kNormStatStride tokens].
+constexpr int kNormStatStride = 32;
+
 
 // See mir_launch.  Both are no-ops in a kernel that was launched without the attribute.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

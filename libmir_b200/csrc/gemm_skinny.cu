@@ -69,10 +69,10 @@ __device__ __forceinline__ uint4 load_cached(const bf16* p, bool valid) {
 //     rsqrt(sum of squares / k + eps) (`sumsq`): W (r g s) = s W (r g), since s is one number per token.
 // Each value is rounded to bf16 once, as when the norm runs as a kernel of its own.
 struct NormFusion {
-  const float* sumsq;        // consumer: [sumsq_tiles][16] partial sums of squares of x's rows before weighting
+  const float* sumsq;        // consumer: [sumsq_tiles][kNormStatStride] partial sums of squares of x's rows before weighting
   int sumsq_tiles;
   float eps;
-  float* sumsq_out;          // producer (ACCUM): [tiles][16] partial sums of squares of the rows it updates
+  float* sumsq_out;          // producer (ACCUM): [tiles][kNormStatStride] partial sums of squares of the rows it updates
   const float* next_weight;  // producer: [n] weight of the norm that follows, or null
   bf16* weighted_out;        // producer: [m, ld_weighted] bf16(new residual * next_weight)
   int ld_weighted;
@@ -168,7 +168,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
     const int token = threadIdx.x >> 4, part = threadIdx.x & 15;
     float sum = 0.0f;
     if (token < m)
-      for (int tile = part; tile < norm.sumsq_tiles; tile += 16) sum += norm.sumsq[tile * 16 + token];
+      for (int tile = part; tile < norm.sumsq_tiles; tile += 16) sum += norm.sumsq[tile * kNormStatStride + token];
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     if (part == 0 && token < 16) inverse_rms[token] = rsqrtf(sum / (float)k + norm.eps);
@@ -236,7 +236,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__
         float square = active ? value * value : 0.0f;
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
-        if (local == 0 && token < m) norm.sumsq_out[(size_t)blockIdx.x * 16 + token] = square;
+        if (local == 0 && token < m) norm.sumsq_out[(size_t)blockIdx.x * kNormStatStride + token] = square;
       }
     }
   }
@@ -276,7 +276,7 @@ MIR_EXPORT int mir_skinny_gemm_max_rows() { return 16; }
 // mode: 0 out bf16 = x w^T (+bias bf16); 1 out float += x w^T (+bias float); 2 out float = x w^T (+bias float);
 // 3 out bf16 [m, n] = silu(x w[0:n]^T) * (x w[up_offset : up_offset + n]^T).
 // Needs m <= 16, k a multiple of 8, ldx a multiple of 8, and x and w on 16-byte boundaries.
-// Norm fusion (all optional, see NormFusion): with `sumsq` [sumsq_tiles][16] each token's results are
+// Norm fusion (all optional, see NormFusion): with `sumsq` [sumsq_tiles][kNormStatStride] each token's results are
 // multiplied by rsqrt(sum / k + eps) (modes 0 and 3); with `sumsq_out` (mode 1 only) the product also writes the
 // partial sums of squares of the rows it updates, [ceil(n / 16)][16] floats, and with `weighted_out` and
 // `next_weight` the new rows times that weight as bf16.

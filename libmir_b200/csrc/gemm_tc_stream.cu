@@ -42,10 +42,10 @@ enum Epilogue : int { STORE = 0, ACCUM = 1, F32 = 2, SWIGLU = 3, QKV = 4 };
 __device__ int g_tc_stream_error = 0;
 
 struct StreamNorm {
-  const float* sumsq;        // consumer: [sumsq_tiles][16] partial sums of squares of x's rows before weighting
+  const float* sumsq;        // consumer: [sumsq_tiles][kNormStatStride] partial sums of squares of x's rows before weighting
   int sumsq_tiles;
   float eps;
-  float* sumsq_out;          // producer (ACCUM): [ceil(n / 16)][16] partial sums of squares of the rows it updates
+  float* sumsq_out;          // producer (ACCUM): [ceil(n / 16)][kNormStatStride] partial sums of squares of the rows it updates
   const float* next_weight;  // producer: [n] weight of the norm that follows, or null
   bf16* weighted_out;        // producer: [m, ld_weighted] bf16(new residual * next_weight)
   int ld_weighted;
@@ -74,7 +74,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long barriers[2 * kMaxStages + 1];
   __shared__ uint32_t tmem_base_slot;
-  __shared__ float scale[16];
+  __shared__ float scale[kNormStatStride];
   __shared__ float head_parts[4][4];                          // QKV: [token of the batch][warp] sums of squares
   __shared__ float head_values[4][128];                       // QKV: [token of the batch][element] before rotation
   cg::cluster_group cluster = cg::this_cluster();
@@ -172,15 +172,15 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
     // While the products run: what the epilogue needs from earlier kernels.  Per token 1, or the folded norm's
     // rsqrt(mean of squares + eps) (8 threads per token add the tiles' sums); and the old residual values.
     grid_dependency_wait();
-    if (tid < 16) scale[tid] = 1.0f;
+    if (tid < kNormStatStride) scale[tid] = 1.0f;
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (norm.sumsq != nullptr) {
-      const int token = tid >> 3, part = tid & 7;
+      const int token = tid >> 2, part = tid & 3;              // 4 threads per token, 32 tokens
       float sum = 0.0f;
       if (token < m)
-        for (int t = part; t < norm.sumsq_tiles; t += 8) sum += norm.sumsq[t * 16 + token];
+        for (int t = part; t < norm.sumsq_tiles; t += 4) sum += norm.sumsq[t * kNormStatStride + token];
 #pragma unroll
-      for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      for (int o = 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
       if (part == 0) scale[token] = rsqrtf(sum / (float)k + norm.eps);
     }
     if (MODE == ACCUM && tid < tile_rows && n0 + tid < n) {
@@ -247,7 +247,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
         for (int j = 0; j < BATCH; ++j) {
           const int token = token0 + j * stride;
           if (token < m && column < n) {
-            const float s = token < 16 ? scale[token] : 1.0f;
+            const float s = token < kNormStatStride ? scale[token] : 1.0f;
             const float g = gate[j] * s;
             reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * (up[j] * s));
           }
@@ -268,7 +268,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
 #pragma unroll
         for (int j = 0; j < BATCH; ++j) {
           const int token = token0 + j * splits;
-          value[j] = token < m ? cluster_sum(token, tid) * (token < 16 ? scale[token] : 1.0f) + extra : 0.0f;
+          value[j] = token < m ? cluster_sum(token, tid) * (token < kNormStatStride ? scale[token] : 1.0f) + extra : 0.0f;
         }
         if (head_norm != nullptr) {
 #pragma unroll
@@ -333,7 +333,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
         for (int j = 0; j < BATCH; ++j) {
           const int token = token0 + j * splits;
           if (token >= m) break;                              // the same for every thread
-          const float result = value[j] * (token < 16 ? scale[token] : 1.0f) + extra + old[j];
+          const float result = value[j] * (token < kNormStatStride ? scale[token] : 1.0f) + extra + old[j];
           if (in_range) {
             if (MODE == STORE) {
               reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(result);
@@ -343,12 +343,12 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
                 norm.weighted_out[(size_t)token * norm.ld_weighted + column] = __float2bfloat16_rn(result * norm.next_weight[column]);
             }
           }
-          if (MODE == ACCUM && norm.sumsq_out != nullptr && token < 16) {
+          if (MODE == ACCUM && norm.sumsq_out != nullptr && token < kNormStatStride) {
             // sum of squares of 16 neighbouring new residual values of this token (16 consecutive lanes)
             float square = in_range ? result * result : 0.0f;
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
-            if ((tid & 15) == 0 && in_range) norm.sumsq_out[(size_t)(column >> 4) * 16 + token] = square;
+            if ((tid & 15) == 0 && in_range) norm.sumsq_out[(size_t)(column >> 4) * kNormStatStride + token] = square;
           }
         }
       }
@@ -441,7 +441,7 @@ MIR_EXPORT int mir_gemm_tc_stream_set_splits(int splits, int ring_kb, int tile_r
 }
 
 // Modes and the folded-norm arguments as in mir_gemm_skinny_bf16; 1 <= m <= 128, k and ldx multiples of 8, x and
-// w 16-byte aligned.  The sums of squares and the weighted rows are defined for up to 16 tokens.
+// w 16-byte aligned.  The sums of squares and the weighted rows are defined for up to kNormStatStride (32) tokens.
 MIR_EXPORT int mir_gemm_tc_stream_bf16(int mode, const void* x, int ldx, const void* w, const void* bias, void* out,
                                        int ldo, int m, int n, int k, int up_offset, const float* sumsq,
                                        int sumsq_tiles, float eps, float* sumsq_out, const float* next_weight,
@@ -453,12 +453,14 @@ MIR_EXPORT int mir_gemm_tc_stream_bf16(int mode, const void* x, int ldx, const v
                   "(m %d n %d k %d ldx %d ldo %d)", m, n, k, ldx, ldo);
     return MIR_BAD_ARGUMENT;
   }
-  if ((sumsq_out != nullptr || weighted_out != nullptr) && (mode != ACCUM || m > 16)) {
-    mir_set_error("tc_stream: sums of squares and weighted rows are written by the accumulate epilogue for up to 16 rows");
+  if ((sumsq_out != nullptr || weighted_out != nullptr) && (mode != ACCUM || m > kNormStatStride)) {
+    mir_set_error("tc_stream: sums of squares and weighted rows are written by the accumulate epilogue for up to %d rows",
+                  kNormStatStride);
     return MIR_BAD_ARGUMENT;
   }
-  if (sumsq != nullptr && (sumsq_tiles <= 0 || m > 16 || (mode != STORE && mode != SWIGLU))) {
-    mir_set_error("tc_stream: a folded norm needs its partial sums, up to 16 rows, and the store or SwiGLU epilogue");
+  if (sumsq != nullptr && (sumsq_tiles <= 0 || m > kNormStatStride || (mode != STORE && mode != SWIGLU))) {
+    mir_set_error("tc_stream: a folded norm needs its partial sums, up to %d rows, and the store or SwiGLU epilogue",
+                  kNormStatStride);
     return MIR_BAD_ARGUMENT;
   }
   if (weighted_out != nullptr && (next_weight == nullptr || sumsq_out == nullptr || ld_weighted < n)) {

@@ -132,12 +132,13 @@ class StepContext:
         norm = self.upcoming_norm
         norm_weight = getattr(norm, "weight", None) if getattr(norm, "foldable", False) else None
         if (not kernels.FUSE_NORM_INTO_PRODUCT or norm_weight is None or self.dtype != torch.bfloat16
-                or residual.shape[0] > kernels.SKINNY_MAX_ROWS or norm_weight.numel() != residual.shape[1]):
+                or residual.shape[0] > min(kernels.FOLDED_NORM_MAX_ROWS, kernels.FEW_ROWS_MAX)
+                or norm_weight.numel() != residual.shape[1]):
             kernels.linear(x, weight, residual, bias, accumulate=True)
             self.residual_stats = None
             return
         tiles = kernels.sumsq_tiles(residual.shape[1])
-        sumsq = self.alloc((tiles, 16), torch.float32)
+        sumsq = self.alloc((tiles, kernels.NORM_STAT_STRIDE), torch.float32)
         weighted = self.alloc(tuple(residual.shape), torch.bfloat16)
         wrote = kernels.linear(x, weight, residual, bias, accumulate=True, sumsq_out=sumsq,
                                weighted_out=(weighted, norm_weight))

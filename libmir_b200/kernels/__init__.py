@@ -464,10 +464,10 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
            weighted_out: Optional[tuple] = None) -> bool:
     """out = (out if accumulate) + x . weight^T (+ bias).
 
-    float32 tensors: the 32-bit FMA kernel.  bfloat16 x and weight: up to 16 rows run the weight-streaming
+    float32 tensors: the 32-bit FMA kernel.  bfloat16 x and weight: up to FEW_ROWS_MAX (32) rows run the weight-streaming
     kernel, more run cuBLASLt, both with 32-bit accumulation; out is bfloat16 or float32.  x and out may be
     row-strided views; weight is [out_features, in_features].  x may be a NormedResidual (then `alloc` must be
-    given in case it has to be materialised).  With `sumsq_out` (float32 [ceil(N / 16), 16]) an accumulating
+    given in case it has to be materialised).  With `sumsq_out` (float32 [ceil(N / 16), NORM_STAT_STRIDE]) an accumulating
     few-rows product also writes the sums of squares of the rows it updates, and with
     `weighted_out` = (bfloat16 [M, N], float32 norm weight [N]) those rows times the weight; the return value
     says whether it did."""
@@ -515,7 +515,8 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
     if _skinny_ok(x, m, k) and (out.dtype == torch.float32 or not accumulate) and mode_name in SKINNY_MODES:
         mode = SKINNY_STORE if out.dtype == torch.bfloat16 else (SKINNY_ACCUM if accumulate else SKINNY_F32)
         stats = sumsq_out if (mode == SKINNY_ACCUM and sumsq_out is not None
-                              and sumsq_out.numel() >= sumsq_tiles(n) * 16) else None
+                              and sumsq_out.numel() >= sumsq_tiles(n) * NORM_STAT_STRIDE
+                              and (m <= SKINNY_MAX_ROWS or _few_rows_kernel(m, mode_name) == "stream")) else None
         rows, next_weight = weighted_out if (stats is not None and weighted_out is not None) else (None, None)
         if rows is not None:
             _cuda(rows, next_weight)
@@ -586,7 +587,7 @@ def stream_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias
                   sumsq_out: Optional[torch.Tensor] = None, weighted_out: Optional[tuple] = None) -> None:
     """The tcgen05 weight-streaming product for 1 to 128 bfloat16 rows (see tensor_core_linear for the modes).
     `folded`: x is folded.weighted and each token's results are scaled by the folded norm; `sumsq_out`,
-    `weighted_out` as in linear (accumulate, up to 16 rows)."""
+    `weighted_out` as in linear (accumulate, up to 32 rows)."""
     if folded is not None:
         x = folded.weighted
     _cuda(x, weight, out, bias)
@@ -628,9 +629,14 @@ def tensor_core_linear_error() -> int:
 
 
 SKINNY_MAX_ROWS = 16
-# Up to how many rows a product runs a few-rows kernel rather than the library (the streaming kernel takes up to
-# 128; measured alone at 64 rows it loses to cuBLASLt: 12.2 / 8.5, 17.0 / 15.2, 14.9 / 8.2 us).
-FEW_ROWS_MAX = 16
+NORM_STAT_STRIDE = 32        # tokens per row of the sums-of-squares arrays (kNormStatStride of the kernels)
+FOLDED_NORM_MAX_ROWS = 32    # up to how many rows the streaming kernel writes and reads what a folded norm needs
+# Up to how many rows a product runs a few-rows kernel rather than the library.  The streaming kernel takes up to
+# 128; measured alone at 64 rows it loses to cuBLASLt (12.2 / 8.5, 17.0 / 15.2, 14.9 / 8.2 us), and at 17 to 32
+# rows it is about as fast, but there it also takes over the two RMSNorms of a layer and the SwiGLU, which the
+# library path runs as kernels of their own: decode steps at Qwen3-4B sizes, library / streaming: batch 17 3.76 /
+# 3.56 ms, batch 24 4.11 / 3.91 ms, batch 32 4.50 / 4.31 ms; batch 64 6.27 / 6.65 ms.
+FEW_ROWS_MAX = 32
 SKINNY_MODES = {"store", "accum", "f32", "swiglu"}     # the few-rows epilogues in use; the rest go to the library
 SKINNY_STORE, SKINNY_ACCUM, SKINNY_F32, SKINNY_SWIGLU = 0, 1, 2, 3
 
@@ -656,7 +662,8 @@ def _few_rows_kernel(m: int, mode_name: str) -> str:
 
 
 def _skinny_ok(x: torch.Tensor, m: int, k: int) -> bool:
-    """Whether the few-rows kernel takes this product: up to 16 rows, 16-byte aligned rows of 8-element multiples."""
+    """Whether a few-rows kernel takes this product: up to FEW_ROWS_MAX rows, 16-byte aligned rows of 8-element
+    multiples."""
     return (0 < m <= min(FEW_ROWS_MAX, STREAM_MAX_ROWS) and k % 8 == 0 and x.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0)
 
@@ -664,7 +671,7 @@ def _skinny_ok(x: torch.Tensor, m: int, k: int) -> bool:
 def gate_up_silu(x, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -> None:
     """out[M, I] = silu(x w_gate^T) * (x w_up^T) with w_gate_up = [w_gate; w_up] of shape [2 I, K].
 
-    Up to 16 bfloat16 rows (the weight-streaming kernel; x may be a NormedResidual, a norm folded into this
+    Up to FEW_ROWS_MAX (32) bfloat16 rows (the weight-streaming kernel; x may be a NormedResidual, a norm folded into this
     product) and from TENSOR_CORE_MIN_ROWS bfloat16 rows (the tcgen05 kernel): one kernel, the [M, 2 I] intermediate is never written.
     Otherwise the product (library or 32-bit kernel) followed by the SiLU-multiply kernel;
     `scratch_alloc(shape, dtype)` provides the intermediate."""

@@ -459,11 +459,16 @@ def test_tensor_core_product_refuses_what_it_cannot_take():
 
 
 @pytest.mark.parametrize("which", ["stream", "skinny"])
-@pytest.mark.parametrize("m", [1, 8, 13])
+@pytest.mark.parametrize("m", [1, 8, 13, 24, 32])
 def test_norm_folded_into_the_few_rows_products_around_it(m, which, monkeypatch):
     """The accumulating product leaves the sums of squares of the new residual and its rows times the next
-    norm's weight; the product after the norm scales its results: together they equal norm then product."""
+    norm's weight; the product after the norm scales its results: together they equal norm then product.
+    (17 to 32 rows: the streaming kernel only.)"""
     from libmir_b200 import kernels
+    if m > kernels.SKINNY_MAX_ROWS:
+        if which == "skinny":
+            pytest.skip("the mma.sync kernel takes up to 16 rows")
+        monkeypatch.setattr(kernels, "FEW_ROWS_MAX", 32)
     monkeypatch.setattr(kernels, "FEW_ROWS_KERNEL", {mode: which for mode in kernels.FEW_ROWS_KERNEL})
     torch.manual_seed(m)
     hidden, inner, wide, eps = 264, 136, 200, 1e-5
@@ -473,7 +478,7 @@ def test_norm_folded_into_the_few_rows_products_around_it(m, which, monkeypatch)
     base = torch.randn(m, hidden) * 3.0
     residual = cuda(base.clone())
     tiles = kernels.sumsq_tiles(hidden)
-    sumsq = torch.zeros(tiles, 16, device="cuda")
+    sumsq = torch.zeros(tiles, kernels.NORM_STAT_STRIDE, device="cuda")
     weighted = torch.zeros(m, hidden, device="cuda", dtype=torch.bfloat16)
     wrote = kernels.linear(cuda(x), cuda(w_in), residual, accumulate=True, sumsq_out=sumsq,
                            weighted_out=(weighted, cuda(gain)))
