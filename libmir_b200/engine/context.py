@@ -44,7 +44,7 @@ class Arena:
         count = 1
         for dim in shape:
             count *= int(dim)
-        nbytes = count * torch.empty((), dtype=dtype).element_size()
+        nbytes = count * dtype.itemsize
         padded = -(-max(nbytes, 1) // self.ALIGN) * self.ALIGN
         while True:
             if self.chunk >= len(self.chunks):
