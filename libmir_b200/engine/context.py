@@ -35,12 +35,27 @@ class Arena:
         self.chunks: List[torch.Tensor] = []
         self.chunk = 0
         self.offset = 0
+        self._views: dict = {}       # (chunk, offset, dtype, shape) -> (view, padded bytes): steps repeat their sizes
 
     def reset(self) -> None:
         self.chunk = 0
         self.offset = 0
 
     def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        shape = tuple(shape)
+        key = (self.chunk, self.offset, dtype, shape)
+        known = self._views.get(key)
+        if known is not None:                       # the same request at the same place as in an earlier step
+            self.offset += known[1]
+            return known[0]
+        view = self._alloc_new(shape, dtype)
+        if self.chunk == key[0]:                    # (it fitted into the chunk it was asked in)
+            if len(self._views) > 65536:
+                self._views.clear()
+            self._views[key] = (view, self.offset - key[1])
+        return view
+
+    def _alloc_new(self, shape, dtype: torch.dtype) -> torch.Tensor:
         count = 1
         for dim in shape:
             count *= int(dim)
