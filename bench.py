@@ -159,7 +159,7 @@ def main() -> int:
     parser.add_argument("--no-fold-norm", action="store_true",
                         help="run every RMSNorm as a kernel of its own instead of folding it into the few-rows "
                              "products around it")
-    parser.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
+    parser.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "serve"],
                         help="decode / prefill: run only that phase, bracketed by cudaProfilerStart/Stop (for ncu "
                              "--profile-from-start off); the JSON line then holds only that phase")
     parser.add_argument("--no-graphs", action="store_true", help="decode steps as plain launches, not as CUDA graphs")
@@ -219,6 +219,8 @@ def main() -> int:
         parser.error("--context above 8,192 only with --phase decode (one prefill step holds up to 8,192 tokens)")
     max_batch = args.batch if (args.skip_points or args.phase != "all") else max(64, args.batch)
     context_limit = prompt_tokens + GENERATED_TOKENS + args.steps + args.warmup + 64
+    if args.phase == "serve":                                 # 64 requests of up to 4,096 + 128 tokens
+        max_batch, context_limit = 64, 4096 + 128 + 64
     pages = max_batch * (-(-context_limit // PAGE_SIZE)) + 64
     runtime = RuntimeConfig(kv_cache=CacheConfig(block_size=PAGE_SIZE, block_count=pages),
                             scheduler=SchedulerConfig(max_batch_requests=max_batch, max_batch_tokens=8192,
@@ -360,6 +362,30 @@ def main() -> int:
                           "device_tokens_per_second": round(device_value, 1), "device_ms_per_step": round(device_ms, 4),
                           "context": prompt_tokens, "hbm_frac": round(hbm_frac, 4),
                           "launches_per_step": launches / max(1, args.steps)}))
+        return 0
+    if args.phase == "serve":
+        # BASELINE.json configs[3]'s workload: 64 requests through the scheduler (Model.generate_batch), prompt
+        # lengths uniform in 16..4,096, 128 generated tokens each; the second of two runs is timed.
+        from libmir_b200.config.generation import GenerationOverrides
+        from libmir_b200.engine.api import GenerationRequest
+        lengths = rng.integers(16, 4097, size=64).tolist()
+        options = GenerationOverrides(max_tokens=128, ignore_eos=True)
+
+        def run():
+            requests = [GenerationRequest(prompt_ids=rng.integers(0, vocab, size=n).tolist(), options=options)
+                        for n in lengths]
+            torch.cuda.synchronize()
+            started = time.perf_counter()
+            outputs = model.generate_batch(requests)
+            torch.cuda.synchronize()
+            return sum(len(o.token_ids) for o in outputs), time.perf_counter() - started, outputs[0].metrics["steps"]
+
+        run()
+        generated, seconds, steps = run()
+        print(json.dumps({"phase": "serve", "requests": 64, "prompt_tokens": int(sum(lengths)),
+                          "generated_tokens": generated, "seconds": round(seconds, 3), "steps": steps,
+                          "generated_tokens_per_second": round(generated / seconds, 1),
+                          "all_tokens_per_second": round((generated + sum(lengths)) / seconds, 1), "layers": layers}))
         return 0
     if args.phase == "prefill":
         ms = prefill(repeats=max(1, min(args.steps, 5)), profile=True)
