@@ -234,6 +234,12 @@ def test_engine_uses_the_fast_kernels_and_matches_the_plain_model(tmp_path, fuse
     result = model.step([StepEntry("b", second[290:300], [9, 0]), StepEntry("a", [first[741]], [0])])
     assert result.rows == [("b", 9), ("b", 0), ("a", 0)]
     check(result.logits.cpu().numpy(), np.stack([ref_second[299], ref_second[290], ref_first[741]]), "portion, then single")
+    # 24 and 31 tokens: more than 16 rows still run the few-rows products (with the norm folded into them if it is on)
+    result = model.step([StepEntry("a", first[742:766], [0, 23])])
+    check(result.logits.cpu().numpy(), ref_first[[742, 765]], "a portion of 24 tokens")
+    model.admit("c")
+    result = model.step([StepEntry("a", first[766:767], [0]), StepEntry("c", second[:30], [29])])
+    check(result.logits.cpu().numpy(), np.stack([ref_first[766], ref_second[29]]), "31 tokens in a mixed step")
 
 
 def test_decode_attention_over_a_long_context():
