@@ -311,3 +311,52 @@ def test_prefill_attention_on_tcgen05_over_a_long_prompt(window):
     if window is None:                                         # the two planted keys carry nearly all the weight
         planted = (v[7000, 0].float() + v[7133, 0].float()) / 2
         assert torch.allclose(out.reshape(n, heads, dim)[8500, 0].float().cpu(), planted, atol=6e-2)
+
+
+def test_engine_with_a_window_on_the_fast_kernels(tmp_path):
+    """head_dim 128 in bfloat16 with one sliding-window layer and one full layer: a whole portion longer than
+    the window (tcgen05 kernel, pages behind the window given back), mixed steps whose single tokens run the
+    split decode kernel beside a portion, and captured decode steps; logits against the plain implementation."""
+    from helpers import TOL, make_folder, plain_logits, random_ids
+    from libmir_b200 import CacheConfig, Library, RuntimeConfig, StepEntry
+    from libmir_b200.sampling import RequestSampler
+    config = {"architectures": ["Qwen3ForCausalLM"], "hidden_size": 128, "intermediate_size": 192,
+              "num_hidden_layers": 2, "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 128,
+              "vocab_size": 300, "max_position_embeddings": 2048, "rms_norm_eps": 1e-6, "rope_theta": 1e5,
+              "layer_types": ["sliding_attention", "full_attention"], "sliding_window": 200,
+              "tie_word_embeddings": False}
+    folder = make_folder(tmp_path, config, seed=9, dtype="bfloat16", sharpen=4.0)
+    rng = np.random.default_rng(9)
+    first, second, third = random_ids(rng, 300, 700), random_ids(rng, 300, 400), random_ids(rng, 300, 260)
+    refs = {"a": plain_logits(folder, first), "b": plain_logits(folder, second), "c": plain_logits(folder, third)}
+    model = Library(RuntimeConfig(kv_cache=CacheConfig(block_size=16, block_count=96), dtype="bfloat16")).load(folder)
+    for name in ("a", "b", "c"):
+        model.admit(name)
+
+    def check(got, want, label):
+        error = float(np.abs(got - want).max())
+        bound = TOL["bfloat16"] * max(1.0, float(np.abs(want).max()))
+        assert np.isfinite(got).all() and error <= bound, f"{label}: {error:.3e}"
+
+    result = model.step([StepEntry("a", first[:600], [0, 199, 200, 599])])
+    check(result.logits.cpu().numpy(), refs["a"][[0, 199, 200, 599]], "a portion longer than the window")
+    windowed = [g for g in model.cache.groups if g.window is not None][0]
+    assert windowed.pool.held < 600 // 16                       # pages behind the window were given back
+    result = model.step([StepEntry("b", second[:330], [329]), StepEntry("a", first[600:601], [0])])
+    check(result.logits.cpu().numpy(), np.stack([refs["b"][329], refs["a"][600]]), "portion beside a single token")
+    samplers = [RequestSampler(), RequestSampler()]
+    for offset in range(24):                                    # captured decode steps across a window's edge
+        result = model.step([StepEntry("a", [first[601 + offset]], [0]), StepEntry("b", [second[330 + offset]], [0])],
+                            samplers)
+        check(result.logits.cpu().numpy(), np.stack([refs["a"][601 + offset], refs["b"][330 + offset]]),
+              f"decode step {offset}")
+    result = model.step([StepEntry("a", [first[625]], [0]), StepEntry("c", third[:250], [0, 249]),
+                         StepEntry("b", [second[354]], [0])])
+    check(result.logits.cpu().numpy(), np.stack([refs["a"][625], refs["c"][0], refs["c"][249], refs["b"][354]]),
+          "two single tokens around a portion")
+    assert kernels_error_flags() == (0, 0)
+
+
+def kernels_error_flags():
+    from libmir_b200 import kernels
+    return kernels.prefill_attention_error(), kernels.stream_linear_error()
