@@ -90,6 +90,7 @@ class CacheManager:
                 self.entry_group[item.entry] = self.entry_group[item.source]
                 self.entry_local[item.entry] = self.entry_local[item.source]
         self._free_slots = list(range(max_requests - 1, -1, -1))
+        self._serial = 0                               # counts admissions: ids and slots are reused, serials are not
         self.live: Dict[object, Sequence_] = {}
         self.fresh_slots: List[int] = []               # slots handed out since the device last zeroed state
 
@@ -100,7 +101,7 @@ class CacheManager:
         if not self._free_slots:
             raise NoFreeSlot(f"all {self.max_requests} request slots are taken")
         slot = self._free_slots.pop()
-        self._serial = getattr(self, "_serial", 0) + 1
+        self._serial += 1
         sequence = Sequence_(request_id, slot, tables=[[] for _ in self.groups], first_live=[0] * len(self.groups),
                              serial=self._serial)
         self.live[request_id] = sequence
@@ -151,7 +152,7 @@ class CacheManager:
 
     def commit(self, sequence: Sequence_, new_length: int) -> None:
         """The tokens up to new_length are now cached; release what windows have passed."""
-        if new_length > len(sequence.tables[0]) * self.page_size if self.groups else False:
+        if self.groups and new_length > len(sequence.tables[0]) * self.page_size:
             raise ValueError("commit beyond the pages that were grown")
         sequence.length = new_length
         for index, group in enumerate(self.groups):
