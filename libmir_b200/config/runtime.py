@@ -27,7 +27,6 @@ class SchedulerConfig:
     max_batch_requests: int = 16      # live requests (and state slots)
     max_batch_tokens: int = 8192      # tokens in one step
     prefill_chunk_tokens: int = 2096  # the longest portion of one prompt in one step
-    decode_priority_burst: int = 8    # decode-only steps that may overtake a waiting prompt
     reserve_tokens: int = 0           # tokens of growth reserved at admission (0 = pages on demand)
     out_of_pages: str = "preempt"     # "preempt" (youngest is recomputed later) or "finish" (reason out_of_pages)
 
@@ -50,6 +49,7 @@ class RuntimeConfig:
     scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
     cuda: CudaConfig = field(default_factory=CudaConfig)
     dtype: str = "bfloat16"           # "bfloat16": the serving kernels; "float32": everything in true 32-bit
+    strict_weights: bool = False      # a stored tensor that the model does not ask for is an error, not auxiliary
 
     def validate(self) -> None:
         if self.dtype not in DTYPES:

@@ -21,6 +21,18 @@ from ..errors import ConfigError
 
 # --------------------------------------------------------------------------- parameters
 @dataclass(frozen=True)
+class TensorSource:
+    """Another way a checkpoint may store a wanted tensor: as rows [rows[0], rows[1]) of the stored tensor
+    `name` (a name local to the part, like the key of the ParamSpec that lists this source), which has
+    `total_rows` rows in all.  libmir splits a fused `self_attn.qkv_proj.weight` / `query_key_value.weight`
+    into query, key and value rows this way (models/src/weights/binding/shapes/transforms.rs:22-35)."""
+
+    name: str
+    rows: tuple
+    total_rows: int
+
+
+@dataclass(frozen=True)
 class ParamSpec:
     """One tensor that a part wants from the checkpoint.
 
@@ -34,6 +46,10 @@ class ParamSpec:
     init: str = "normal"          # "normal" N(0, 0.02), "ones", "zeros"
     store: str = "compute"        # "compute" | "float32" | "int32"
     optional: bool = False        # absent from the checkpoint is fine (bias, q/k-norm discovery)
+    sources: tuple = ()           # TensorSource: other stored tensors this one may be cut from
+    # A 2-d tensor stored with its two dimensions swapped ([in, out] for [out, in]) is recognised by its shape
+    # and transposed while loading (transforms.rs:52-58); a square tensor is always taken as stored.
+    accept_transposed: bool = True
 
 
 # --------------------------------------------------------------------------- cache needs

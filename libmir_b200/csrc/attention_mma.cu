@@ -67,7 +67,9 @@ __device__ __forceinline__ float quad_sum(float v) {
 
 // Copy ROWS consecutive keys and their values (one kv head, head_dim bf16 each) from the pages into padded
 // shared-memory rows with THREADS threads.  Row i holds key `first_key + i`; rows whose key is >= limit
-// are zero-filled.  One instruction of a warp copies whole rows: head_dim / 8 consecutive lanes take the
+// are zero-filled, and so are rows whose page the block table marks as released (a negative entry: a sliding
+// window has passed the page; such keys are masked by the caller, and no address is formed from the entry).
+// One instruction of a warp copies whole rows: head_dim / 8 consecutive lanes take the
 // consecutive 16-byte pieces of a row, so every 32-byte sector that is requested is used in full (a lane
 // that walked along its own row would ask for each sector twice, once per half).  The rows of one
 // instruction are GROUP consecutive keys; when the page size is a multiple of GROUP they lie in one page
@@ -85,14 +87,15 @@ __device__ __forceinline__ void load_tile(bf16* k_dst, bf16* v_dst, const bf16* 
   if (page_size % ROWS == 0 && first_key % ROWS == 0) {
     // the whole tile lies in one page: one table read, then constant strides
     const int block = first_key / page_size;
-    const int page = first_key < limit ? table[block] : 0;
+    const int entry = first_key < limit ? table[block] : -1;
+    const int page = entry < 0 ? 0 : entry;
     const size_t row_stride = (size_t)kv_heads * D;
     const size_t base = ((size_t)page * page_size + (first_key - block * page_size)) * row_stride + (size_t)kv_head * D +
                         piece * 8;
 #pragma unroll
     for (int i = 0; i < ROWS / GROUP; ++i) {
       const int r = i * GROUP + sub;
-      const bool valid = first_key + r < limit;
+      const bool valid = entry >= 0 && first_key + r < limit;
       const size_t offset = valid ? base + r * row_stride : 0;
       cp_async16(smem_u32(k_dst + r * STRIDE + piece * 8), k_pages + offset, valid);
       cp_async16(smem_u32(v_dst + r * STRIDE + piece * 8), v_pages + offset, valid);
@@ -104,13 +107,14 @@ __device__ __forceinline__ void load_tile(bf16* k_dst, bf16* v_dst, const bf16* 
   for (int i = 0; i < ROWS / GROUP; ++i) {
     const int r = i * GROUP + sub;
     const int key = first_key + r;
-    const bool valid = key < limit;
+    bool valid = key < limit;
     size_t offset = 0;
     if (valid) {
       const int lookup_key = one_page ? first_key + i * GROUP : key;
       const int block = lookup_key / page_size;
       const int page = table[block];
-      offset = (((size_t)page * page_size + (key - block * page_size)) * kv_heads + kv_head) * D + piece * 8;
+      valid = page >= 0;
+      if (valid) offset = (((size_t)page * page_size + (key - block * page_size)) * kv_heads + kv_head) * D + piece * 8;
     }
     cp_async16(smem_u32(k_dst + r * STRIDE + piece * 8), k_pages + offset, valid);
     cp_async16(smem_u32(v_dst + r * STRIDE + piece * 8), v_pages + offset, valid);
@@ -425,7 +429,7 @@ decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict
   const int context = position + 1;
   const int first_key = (window > 0 && context > window) ? context - window : 0;
   const int first_part = (first_key / kDecodeTile * kDecodeTile) / partition;
-  const int last_part = position / partition;
+  const int last_part = min(position / partition, num_partitions - 1);   // (a caller with too few partitions reads nothing beyond them)
   const float* ml = partial_ml + index * num_partitions * 2;
   const float* o = partial_o + index * num_partitions * D;
   // the largest maximum over all partitions
@@ -690,8 +694,12 @@ bool bad_common(const char* what, int heads, int kv_heads, int head_dim, int pag
 MIR_EXPORT void mir_decode_attention_set_deep_ring_ctas(long long ctas) { g_deep_ring_ctas = ctas; }
 
 // How many floats of scratch decode attention needs: partial outputs and (maximum, denominator) pairs.
+// Arguments that cannot be meant (negative, or so large that the product would leave 63 bits) give -1.
 MIR_EXPORT long long mir_decode_attention_scratch_floats(int rows, int heads, int head_dim, int num_partitions) {
-  return num_partitions <= 1 ? 0 : (long long)rows * heads * num_partitions * (head_dim + 2);
+  if (rows < 0 || heads < 0 || head_dim < 0 || num_partitions < 0) return -1;
+  if (num_partitions <= 1) return 0;
+  const unsigned __int128 floats = (unsigned __int128)rows * (unsigned)heads * (unsigned)num_partitions * (unsigned)(head_dim + 2);
+  return floats > (unsigned __int128)(1ll << 62) ? -1 : (long long)floats;
 }
 
 // One token per row.  `partition` (a multiple of 64) is how many keys one CTA takes; num_partitions must be
@@ -709,7 +717,7 @@ MIR_EXPORT int mir_decode_attention_bf16(const void* q, long long q_stride, void
     return MIR_BAD_ARGUMENT;
   }
   const long long need = mir_decode_attention_scratch_floats(rows, heads, head_dim, num_partitions);
-  if (need > 0 && (scratch == nullptr || scratch_floats < need)) {
+  if (need < 0 || (need > 0 && (scratch == nullptr || scratch_floats < need))) {
     mir_set_error("decode_attention: scratch of %lld floats is needed, got %lld", need, scratch_floats);
     return MIR_BAD_ARGUMENT;
   }
@@ -790,13 +798,16 @@ MIR_EXPORT int mir_decode_attention_bf16_static(const void* q, long long q_strid
                                                 int kv_heads, int head_dim, float scale, int window, int partition,
                                                 int num_partitions, cudaStream_t stream) {
   if (rows == 0) return MIR_OK;
-  if (rows < 0 || heads <= 0 || head_dim <= 0 || num_partitions <= 0) {
-    mir_set_error("decode_attention_static: bad rows %d, heads %d, head_dim %d or partition count %d", rows, heads,
-                  head_dim, num_partitions);
+  // the same checks as the ordinary entry point, before any size is computed from the arguments
+  if (bad_common("decode_attention_static", heads, kv_heads, head_dim, page_size, table_width, window)) return MIR_BAD_ARGUMENT;
+  if (rows < 0 || rows > 65535 || partition <= 0 || partition % 64 || partition > kDecodeMaxPartition ||
+      num_partitions <= 0) {
+    mir_set_error("decode_attention_static: bad rows %d, partition %d or partition count %d", rows, partition,
+                  num_partitions);
     return MIR_BAD_ARGUMENT;
   }
   const long long need = mir_decode_attention_scratch_floats(rows, heads, head_dim, num_partitions);
-  if (need > (long long)MIR_STATIC_SCRATCH_FLOATS) {
+  if (need < 0 || need > (long long)MIR_STATIC_SCRATCH_FLOATS) {
     mir_set_error("decode_attention_static: this call needs %lld floats of scratch (rows %d x heads %d x partitions "
                   "%d x (head_dim %d + 2)), the built-in array holds %u; use fewer rows or partitions per call, or "
                   "mir_decode_attention_bf16 with scratch of your own",

@@ -96,5 +96,6 @@ MIR_EXPORT int mir_gemm_bf16_lt(const void* x, int ldx, const void* w, int ldw, 
   const float alpha = 1.0f;
   LT_CHECK(cublasLtMatmul(g_handle, plan.op, &alpha, w, plan.w, x, plan.x, &beta, out, plan.c, out, plan.c, &plan.algo,
                           workspace, workspace_bytes, stream));
+  mir_count_launch("gemm_bf16_lt");
   return MIR_OK;
 }

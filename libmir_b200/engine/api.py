@@ -107,7 +107,7 @@ class Library:
             progress(f"building {spec.architecture}")
         decoder = DecoderModel(spec, env)
         with torch.cuda.device(device):
-            load_into(decoder, folder)
+            load_into(decoder, folder, strict=self.config.strict_weights)
         generation = GenerationConfig.from_folder(folder)
         model = Model(self, decoder, generation, overrides, config_json)
         self.models.append(model)
@@ -179,7 +179,8 @@ class Model:
         return result.tokens.cpu().tolist() if result.tokens is not None else []
 
     def _scheduler(self) -> Scheduler:
-        return Scheduler(self.cache, self.library.config.scheduler, self.spec.max_positions, self._run_and_sample)
+        return Scheduler(self.cache, self.library.config.scheduler, self.spec.max_positions, self._run_and_sample,
+                         portion_multiple=self.decoder.portion_multiple())
 
     def generate_batch(self, requests: Sequence[GenerationRequest],
                        on_token: Optional[Callable[[object, int], None]] = None) -> List[GenerationOutput]:
@@ -196,8 +197,11 @@ class Model:
                              RequestSampler.from_settings(settings, request.seed), callback)
             scheduler.submit(record)
             records.append(record)
-        with torch.cuda.device(self.device):
-            scheduler.run()
+        try:
+            with torch.cuda.device(self.device):
+                scheduler.run()
+        finally:
+            scheduler.abandon()          # after a step that raised: nothing of this call stays live in the shared cache
         elapsed = time.perf_counter() - started
         generated = sum(len(r.output) for r in records)
         outputs = []

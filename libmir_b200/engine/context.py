@@ -16,6 +16,7 @@ import numpy as np
 import torch
 
 from .. import kernels
+from ..parts.base import PartContext
 
 
 class Arena:
@@ -86,7 +87,7 @@ class GroupContext:
 
 
 @dataclass
-class StepContext:
+class StepContext(PartContext):
     num_tokens: int
     num_rows: int
     tokens: torch.Tensor                # int32 [T]
@@ -139,13 +140,12 @@ class StepContext:
             return stats[2], stats[3], stats[4]
         return None
 
-    def accumulate_with_stats(self, x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor,
-                              bias: Optional[torch.Tensor] = None) -> None:
-        """residual += x . weight^T (+ bias).  If a norm is known to follow (`upcoming_norm`, with a float32
-        `weight` and a `foldable` flag) and the product can do it, it also leaves what that norm needs to be
-        folded into the next product."""
+    def accumulate(self, x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor,
+                   bias: Optional[torch.Tensor] = None) -> None:
+        """residual += x . weight^T (+ bias).  If a foldable norm is known to follow (`upcoming_norm`) and the
+        product can do it, it also leaves what that norm needs to be folded into the next product."""
         norm = self.upcoming_norm
-        norm_weight = getattr(norm, "weight", None) if getattr(norm, "foldable", False) else None
+        norm_weight = norm.weight if (norm is not None and norm.foldable) else None
         if (not kernels.FUSE_NORM_INTO_PRODUCT or norm_weight is None or self.dtype != torch.bfloat16
                 or residual.shape[0] > min(kernels.FOLDED_NORM_MAX_ROWS, kernels.FEW_ROWS_MAX)
                 or norm_weight.numel() != residual.shape[1]):
@@ -161,11 +161,3 @@ class StepContext:
 
     def cache_view(self, entry: int):
         return self.views.get(entry)
-
-    def cast_residual(self, residual: torch.Tensor) -> torch.Tensor:
-        """The 32-bit residual in the engine's dtype (for an arrangement without a norm)."""
-        if self.dtype == torch.float32:
-            return residual
-        out = self.alloc(residual.shape, self.dtype)
-        kernels.cast(residual, out)
-        return out

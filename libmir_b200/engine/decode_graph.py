@@ -82,6 +82,7 @@ class DecodeGraph:
                                          dtype=torch.int64, device=device)
         self.host_tokens = torch.zeros(rows, dtype=torch.int32, pin_memory=True)
         self.launches_per_replay = 0
+        self.replays = 0
         self._copied = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._capture()
@@ -185,6 +186,7 @@ class DecodeGraph:
 
     def replay(self) -> None:
         self.graph.replay()
+        self.replays += 1
         kernels.LAUNCHES += self.launches_per_replay
 
 

@@ -71,10 +71,21 @@ class PlannedEntry:
 
 class Scheduler:
     def __init__(self, manager: CacheManager, config: SchedulerConfig, max_positions: int,
-                 run_step: Callable[[Sequence[StepEntry], Sequence[RequestSampler]], List[int]]):
+                 run_step: Callable[[Sequence[StepEntry], Sequence[RequestSampler]], List[int]],
+                 portion_multiple: int = 1):
         """`run_step(entries, samplers)` runs one batch and returns the sampled token of every entry
-        that wants one (those with a non-empty `want`), in order, as host integers."""
+        that wants one (those with a non-empty `want`), in order, as host integers.  `portion_multiple`: what
+        the model's parts ask of the cuts (a mixer that scans in chunks wants every portion but a request's last
+        to be a multiple of its chunk); a portion that does not end its request's pending tokens is cut down to
+        a multiple of it."""
         config.validate()
+        if portion_multiple < 1:
+            raise SchedulerError("portion_multiple must be at least 1")
+        if portion_multiple > 1 and portion_multiple > min(config.prefill_chunk_tokens,
+                                                          config.max_batch_tokens - config.max_batch_requests):
+            raise SchedulerError(f"the model wants portions in multiples of {portion_multiple} tokens: "
+                                 f"prefill_chunk_tokens and max_batch_tokens - max_batch_requests must be at least that")
+        self.portion_multiple = portion_multiple
         self.manager = manager
         self.config = config
         self.max_positions = max_positions
@@ -109,6 +120,19 @@ class Scheduler:
     @property
     def idle(self) -> bool:
         return not self.waiting and not self.running
+
+    def abandon(self, reason: str = "aborted") -> None:
+        """Finish every request that is still waiting or running and give back what it holds: what a caller does
+        when a step raised, so that the cache manager it shares with later calls keeps no holder of this one."""
+        for request in list(self.running) + list(self.waiting):
+            self._finish(request, reason)
+
+    def _portion(self, request: Request, budget: int) -> int:
+        """How many of the request's pending tokens the next step takes under `budget`."""
+        count = min(request.pending, budget, self.config.prefill_chunk_tokens)
+        if count < request.pending and self.portion_multiple > 1:
+            count -= count % self.portion_multiple
+        return count
 
     # -- finishing -------------------------------------------------------------------
     def _finish(self, request: Request, reason: str) -> None:
@@ -174,10 +198,12 @@ class Scheduler:
             for request in self.running:
                 if budget <= 0 or request in decoders or request.pending == 0:
                     continue
-                count = min(request.pending, budget, config.prefill_chunk_tokens)
+                count = self._portion(request, budget)
+                if count <= 0:
+                    continue
                 need = self._need(request, count)
                 if any(n > f for n, f in zip(need, free)):
-                    # shrink the portion to the pages that are free, whole pages only
+                    # shrink the portion to the pages that are free
                     count = self._fit(request, count, free)
                     if count <= 0:
                         continue
@@ -190,7 +216,7 @@ class Scheduler:
                    and len(self.running) < config.max_batch_requests):
                 request = self.waiting[0]
                 need_all = self._admission_need(request)
-                if any(n > f for n, f in zip(need_all, free)):
+                if any(n > f for n, f in zip(need_all, free)) or self._portion(request, budget) <= 0:
                     break
                 self.waiting.popleft()
                 self.manager.admit(request.request_id)
@@ -198,7 +224,7 @@ class Scheduler:
                 request.admitted_order = self._admissions
                 self._admissions += 1
                 self.running.append(request)
-                count = min(request.pending, budget, config.prefill_chunk_tokens)
+                count = self._portion(request, budget)
                 need = self._need(request, count)
                 free = [f - n for f, n in zip(free, need)]
                 budget -= count
@@ -220,6 +246,8 @@ class Scheduler:
         for g, table in enumerate(seq.tables):
             room = (len(table) + free[g]) * page - seq.length
             best = min(best, room)
+        if best < request.pending and self.portion_multiple > 1:
+            best -= best % self.portion_multiple
         return max(0, best)
 
     def _make_room(self) -> bool:

@@ -111,6 +111,26 @@ def set_programmatic_launch(mode) -> None:
         lib.mir_set_pdl(int(mode))
 
 
+def launch_counts(reset: bool = False) -> dict:
+    """How often each kernel of the loaded libraries was launched, by the name its launcher gives
+    ("decode_attention", "prefill_attention_tc", "paged_attention_generic", "tc_stream", "gemm_bf16_lt", ...).
+    A launch recorded into a CUDA graph counts once, however often the graph is replayed."""
+    counts: dict = {}
+    for lib in _LIBS.values():
+        lib.mir_launch_counts.argtypes = [ctypes.c_char_p, c_int]
+        lib.mir_launch_counts.restype = c_int
+        buffer = ctypes.create_string_buffer(lib.mir_launch_counts(None, 0))
+        lib.mir_launch_counts(buffer, len(buffer))
+        for line in buffer.value.decode().splitlines():
+            name, _, count = line.partition("=")
+            counts[name] = counts.get(name, 0) + int(count)
+        if reset:
+            lib.mir_reset_launch_counts.argtypes = []
+            lib.mir_reset_launch_counts.restype = None
+            lib.mir_reset_launch_counts()
+    return counts
+
+
 def loaded_libraries() -> dict:
     """Paths of the native libraries this process has loaded (for reports)."""
     return {name: lib._name for name, lib in _LIBS.items()}

@@ -95,6 +95,11 @@ class DecoderModel:
         out.append(self.final_norm)
         return out
 
+    def portion_multiple(self) -> int:
+        """The least common multiple of what the parts ask of the scheduler's cuts (Part.portion_multiple)."""
+        import math
+        return math.lcm(*[max(1, int(part.portion_multiple)) for part in self.parts()])
+
     def weight_bytes_per_step(self) -> int:
         """Bytes of weights one step reads: every layer of the schedule once, the final norm and the
         head; the embedding table is only gathered from."""
@@ -111,11 +116,9 @@ class DecoderModel:
         residual = ctx.alloc((ctx.num_tokens, spec.hidden_size), torch.float32)
         kernels.embed(self.embedding, ctx.tokens, residual, spec.embedding.multiplier)
         for index, entry in enumerate(spec.schedule):
-            if hasattr(ctx, "norm_after_block"):
-                # the norm that the next block in the schedule starts with: this block's last product may prepare it
-                following = (self.blocks[spec.schedule[index + 1].layer] if index + 1 < len(spec.schedule) else None)
-                first_norm = getattr(following, "first_norm", None)
-                ctx.norm_after_block = first_norm() if first_norm is not None else None
+            # the norm that the next block in the schedule starts with: this block's last product may prepare it
+            following = self.blocks[spec.schedule[index + 1].layer] if index + 1 < len(spec.schedule) else None
+            ctx.norm_after_block = following.first_norm() if following is not None else None
             self.blocks[entry.layer].forward(ctx, ctx.cache_view(index), residual)
         return residual
 

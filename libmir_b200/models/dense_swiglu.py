@@ -48,7 +48,8 @@ def _discover(config: DecoderConfig, catalog: Optional[Mapping[str, tuple]], arc
     qk_norm = has("q_norm.weight") and has("k_norm.weight")
     if config.qk_normalization is True and not qk_norm:
         raise ConfigError("qk_normalization is set but the checkpoint has no q_norm / k_norm weights")
-    return qk_norm, has("q_proj.bias"), has("o_proj.bias")
+    qkv_bias = has("q_proj.bias") or has("qkv_proj.bias") or has("query_key_value.bias")
+    return qk_norm, qkv_bias, has("o_proj.bias")
 
 
 def build(config_json: Mapping, catalog: Optional[Mapping[str, tuple]] = None) -> ModelSpec:

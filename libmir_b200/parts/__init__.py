@@ -2,7 +2,7 @@
 
 from ..registry import register_part
 from .attention import SoftmaxAttention
-from .base import Block, BuildEnv, FeedForward, Mixer, Norm, Part, Position
+from .base import Block, BuildEnv, FeedForward, Mixer, Norm, Part, PartContext, Position, ScratchContext
 from .block import ARRANGEMENTS, PreNormBlock, build_block
 from .feed_forward import SwiGlu
 from .norm import RmsNorm
@@ -13,5 +13,5 @@ register_part("rotary", Rotary)
 register_part("softmax_attention", SoftmaxAttention)
 register_part("swiglu", SwiGlu)
 
-__all__ = ["ARRANGEMENTS", "Block", "BuildEnv", "FeedForward", "Mixer", "Norm", "Part", "Position", "PreNormBlock", "RmsNorm",
-           "Rotary", "SoftmaxAttention", "SwiGlu", "build_block", "inverse_frequencies"]
+__all__ = ["ARRANGEMENTS", "Block", "BuildEnv", "FeedForward", "Mixer", "Norm", "Part", "PartContext", "Position", "PreNormBlock", "RmsNorm",
+           "Rotary", "ScratchContext", "SoftmaxAttention", "SwiGlu", "build_block", "inverse_frequencies"]

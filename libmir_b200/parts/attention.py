@@ -14,7 +14,7 @@ from typing import Optional
 import torch
 
 from .. import kernels
-from ..config.spec import PagedKv, ParamSpec
+from ..config.spec import PagedKv, ParamSpec, TensorSource
 from ..registry import build_part
 from .base import Mixer
 
@@ -39,18 +39,25 @@ class SoftmaxAttention(Mixer):
     def cache_requirement(self):
         return PagedKv(self.spec.kv_heads, self.spec.head_dim, self.spec.window)
 
+    # names under which checkpoints store query, key and value as one row-stacked tensor [Wq; Wk; Wv]
+    # (models/src/weights/binding/roles/parse.rs: "self_attn.qkv_proj.weight" | "self_attn.query_key_value.weight")
+    FUSED_NAMES = ("qkv_proj", "query_key_value")
+
     def parameters(self):
         s = self.spec
-        table = {
-            "q_proj.weight": ParamSpec((self.q_width, s.hidden_size)),
-            "k_proj.weight": ParamSpec((self.kv_width, s.hidden_size)),
-            "v_proj.weight": ParamSpec((self.kv_width, s.hidden_size)),
-            "o_proj.weight": ParamSpec((s.hidden_size, self.q_width)),
-        }
+        total = self.q_width + 2 * self.kv_width
+        ranges = {"q_proj": (0, self.q_width), "k_proj": (self.q_width, self.q_width + self.kv_width),
+                  "v_proj": (self.q_width + self.kv_width, total)}
+
+        def fused(projection, suffix):
+            return tuple(TensorSource(f"{name}.{suffix}", ranges[projection], total) for name in self.FUSED_NAMES)
+
+        table = {f"{projection}.weight": ParamSpec((end - begin, s.hidden_size), sources=fused(projection, "weight"))
+                 for projection, (begin, end) in ranges.items()}
+        table["o_proj.weight"] = ParamSpec((s.hidden_size, self.q_width))
         if s.qkv_bias:
-            table["q_proj.bias"] = ParamSpec((self.q_width,))
-            table["k_proj.bias"] = ParamSpec((self.kv_width,))
-            table["v_proj.bias"] = ParamSpec((self.kv_width,))
+            for projection, (begin, end) in ranges.items():
+                table[f"{projection}.bias"] = ParamSpec((end - begin,), sources=fused(projection, "bias"))
         if s.out_bias:
             table["o_proj.bias"] = ParamSpec((s.hidden_size,))
         if s.qk_norm:
@@ -84,11 +91,7 @@ class SoftmaxAttention(Mixer):
             self.project(ctx, cache, group, x, qkv, *rotation)
         mixed = ctx.alloc((tokens, self.q_width), self.env.dtype)
         self.attend(ctx, group, cache, qkv, mixed)
-        accumulate = getattr(ctx, "accumulate_with_stats", None)
-        if accumulate is None:
-            kernels.linear(mixed, self.w_o, residual, self.b_o, accumulate=True)
-        else:
-            accumulate(mixed, self.w_o, residual, self.b_o)      # may also prepare the norm that follows
+        ctx.accumulate(mixed, self.w_o, residual, self.b_o)      # may also prepare the norm that follows
 
     def project(self, ctx, cache, group, x, qkv, table, rotary_dim):
         """Projection, per-head norm, rotation and cache write: in one kernel for a few rows where the sizes
@@ -126,7 +129,7 @@ class SoftmaxAttention(Mixer):
         if self.env.dtype == torch.bfloat16 and s.head_dim in kernels.FAST_HEAD_DIMS:
             # the single-token rows come first in the batch: they run as decoded tokens (keys split over CTAs, the
             # heads of a KV group in one CTA), the prompt portions after them as tiles of queries
-            singles = ctx.num_rows if ctx.decode_only else getattr(ctx, "single_rows", 0)
+            singles = ctx.num_rows if ctx.decode_only else ctx.single_rows
             if singles:
                 longest = ctx.max_context if ctx.decode_only else ctx.single_context
                 partition, count = kernels.decode_partitioning(singles, s.kv_heads, longest)

@@ -18,6 +18,11 @@ the batch is in the StepContext (libmir_b200/engine/context.py).
                   norm, before keys go to their pages).
     Block         forward(ctx, cache, residual) -> None          one arrangement of the above
 
+What a part may use of the step is the PartContext below: scratch memory, the residual-adding product, and the
+protocol by which an RMSNorm between two few-rows products is folded into them.  That protocol is declared here,
+not discovered: a norm says `foldable`, a consumer says `takes_normed_residual`, and `Norm.forward` has the
+`lazy` argument in its signature.
+
 `parameters()` maps a name local to the part ("q_proj.weight") to a ParamSpec; the model joins it
 with the layer's prefix and the slot's sub-prefix from LayerSpec.names.
 """
@@ -38,8 +43,70 @@ class BuildEnv:
     device: torch.device
 
 
+class PartContext:
+    """What a step hands to every part.  The engine's StepContext (engine/context.py) derives from this and adds the
+    packed rows' metadata; a part that needs nothing of the batch (a norm, a feed-forward) runs on this alone, with
+    `ScratchContext` as the smallest concrete form.
+
+    alloc(shape, dtype)                   scratch memory that lives until the step ends.
+    accumulate(x, weight, residual, bias) residual += x . weight^T (+ bias) on the 32-bit residual stream; every
+                                          branch adds its result through this, so that the product can also
+                                          prepare the norm named by `upcoming_norm` (see below).
+    stats_for(residual, norm_weight)      what such a product left for the norm with that weight, or None.
+    cast_residual(residual)               the residual in the engine dtype, for an arrangement without a norm.
+
+    Folded norms: before a part runs, its block sets `upcoming_norm` to the norm that will be applied to the
+    residual right after the part has added into it (None if unknown); the model sets `norm_after_block` to the norm
+    the next block of the schedule starts with.  Whoever changes the residual in another way sets
+    `residual_stats = None`."""
+
+    dtype: Optional[torch.dtype] = None
+    upcoming_norm = None
+    norm_after_block = None
+    residual_stats = None
+
+    def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        raise NotImplementedError
+
+    def accumulate(self, x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor,
+                   bias: Optional[torch.Tensor] = None) -> None:
+        from .. import kernels
+        kernels.linear(x, weight, residual, bias, accumulate=True)
+        self.residual_stats = None
+
+    def stats_for(self, residual: torch.Tensor, norm_weight: torch.Tensor):
+        return None
+
+    def cast_residual(self, residual: torch.Tensor) -> torch.Tensor:
+        from .. import kernels
+        if self.dtype is None or self.dtype == torch.float32:
+            return residual
+        out = self.alloc(residual.shape, self.dtype)
+        kernels.cast(residual, out)
+        return out
+
+
+class ScratchContext(PartContext):
+    """A context that offers scratch memory and nothing of a batch: enough to run a norm or a feed-forward alone."""
+
+    def __init__(self, alloc, dtype: Optional[torch.dtype] = None):
+        self._alloc = alloc
+        self.dtype = dtype
+
+    def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        return self._alloc(shape, dtype)
+
+
 class Part:
     """Base of every part."""
+
+    # True if forward accepts a kernels.NormedResidual as x (an RMSNorm that was not run as a kernel but is
+    # folded into the part's first product); every other part gets the normed tensor.
+    takes_normed_residual = False
+
+    # What the part asks of how prompts are cut: every portion of a request but its last has a multiple of this
+    # many tokens (a mixer that scans in chunks names its chunk here; attention and per-token parts take any cut).
+    portion_multiple = 1
 
     def __init__(self, spec, env: BuildEnv):
         self.spec = spec
@@ -62,8 +129,15 @@ class Part:
 
 
 class Norm(Part):
+    # True if the norm is y = x * s * weight with one 32-bit scale s per row and a float32 `weight` attribute: the
+    # products around it can then take it over (the one before leaves sums of squares and weighted rows, the one
+    # after scales its results).  Only a foldable norm is ever called with lazy=True.
+    foldable = False
+
     def forward(self, ctx, x: torch.Tensor, out: Optional[torch.Tensor] = None,
-                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+                rows: Optional[torch.Tensor] = None, lazy: bool = False) -> torch.Tensor:
+        """The normed rows in the engine dtype.  `lazy` (foldable norms only): the caller's next product can take
+        a kernels.NormedResidual; return one if ctx.stats_for(x, weight) has what it needs."""
         raise NotImplementedError
 
 
@@ -95,6 +169,11 @@ class FeedForward(Part):
 
 class Block(Part):
     def cache_requirement(self) -> CacheRequirement:
+        return None
+
+    def first_norm(self) -> Optional["Norm"]:
+        """The norm this block applies to the incoming residual before anything else, or None: the block before
+        it in the schedule may prepare it in its last product."""
         return None
 
     def forward(self, ctx, cache, residual: torch.Tensor) -> None:

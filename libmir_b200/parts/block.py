@@ -34,40 +34,26 @@ class PreNormBlock(Block):
         return self.mixer_norm
 
     def forward(self, ctx, cache, residual):
-        # A part that sets `takes_normed_residual` accepts a kernels.NormedResidual as x (a norm folded into the
-        # products around it); every other part gets the normed tensor.  Before a part runs, the context is told
-        # which norm follows it, so that its last product can prepare that norm.
-        after = getattr(ctx, "norm_after_block", None)
+        # Before a part runs, the context is told which norm follows it, so that its last product can prepare
+        # that norm (parts.base.PartContext).
+        after = ctx.norm_after_block
         x = (self._norm(self.mixer_norm, self.mixer, ctx, residual) if self.mixer_norm is not None
              else ctx.cast_residual(residual))
-        self._forget_stats(ctx)              # the mixer changes the residual; it may note new sums of squares
-        self._announce(ctx, self.feed_forward_norm if self.feed_forward is not None else after)
+        ctx.residual_stats = None            # the mixer changes the residual; it may note new sums of squares
+        ctx.upcoming_norm = self.feed_forward_norm if self.feed_forward is not None else after
         self.mixer.forward(ctx, cache, x, residual)
         if self.feed_forward is not None:
             x = (self._norm(self.feed_forward_norm, self.feed_forward, ctx, residual)
                  if self.feed_forward_norm is not None else ctx.cast_residual(residual))
-            self._forget_stats(ctx)
-            self._announce(ctx, after)
-            self.feed_forward.forward(ctx, x, residual)
-        self._announce(ctx, None)
-
-    @staticmethod
-    def _announce(ctx, norm):
-        if hasattr(ctx, "upcoming_norm"):
-            ctx.upcoming_norm = norm
-
-    @staticmethod
-    def _forget_stats(ctx):
-        if hasattr(ctx, "residual_stats"):
             ctx.residual_stats = None
+            ctx.upcoming_norm = after
+            self.feed_forward.forward(ctx, x, residual)
+        ctx.upcoming_norm = None
 
     @staticmethod
     def _norm(norm, consumer, ctx, residual):
-        if getattr(consumer, "takes_normed_residual", False) and getattr(norm, "forward", None) is not None:
-            try:
-                return norm.forward(ctx, residual, lazy=True)
-            except TypeError:                 # a norm part without the `lazy` option
-                pass
+        if consumer.takes_normed_residual and norm.foldable:
+            return norm.forward(ctx, residual, lazy=True)
         return norm.forward(ctx, residual)
 
 

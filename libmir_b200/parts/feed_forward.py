@@ -42,8 +42,4 @@ class SwiGlu(FeedForward):
         tokens = x.shape[0]
         hidden = ctx.alloc((tokens, s.intermediate_size), self.env.dtype)
         kernels.gate_up_silu(x, self.w_gate_up, hidden, ctx.alloc)
-        accumulate = getattr(ctx, "accumulate_with_stats", None)
-        if accumulate is None:
-            kernels.linear(hidden, self.w_down, residual, accumulate=True)
-        else:
-            accumulate(hidden, self.w_down, residual)            # may also prepare the norm that follows
+        ctx.accumulate(hidden, self.w_down, residual)      # may also prepare the norm that follows

@@ -38,7 +38,7 @@ class RmsNorm(Norm):
         return a NormedResidual instead of running a kernel."""
         if (lazy and kernels.FUSE_NORM_INTO_PRODUCT and out is None and rows is None
                 and self.env.dtype == torch.bfloat16):
-            stats = ctx.stats_for(x, self.weight) if hasattr(ctx, "stats_for") else None
+            stats = ctx.stats_for(x, self.weight)
             if stats is not None:
                 return kernels.NormedResidual(x, self.weight, self.spec.eps, stats[0], stats[1], self.env.dtype,
                                               stats[2])

@@ -182,6 +182,60 @@ def test_one_far_key_among_hundreds_and_the_windows_edge(kind):
     assert not torch.allclose(out[0], v[n - window - 1, 0], atol=0.3), "a key outside the window was seen"
 
 
+def pool_after_poison(k_pool, v_pool, page):
+    """The pools as views that start one page into larger allocations whose first page holds NaN: a kernel that
+    formed an address from a block-table entry of -1 would read that page, and NaN times a zero weight is NaN."""
+    def shifted(pool):
+        whole = torch.full((pool.shape[0] + page,) + tuple(pool.shape[1:]), float("nan"), dtype=BF16, device="cuda")
+        whole[page:] = pool.to("cuda")
+        return whole[page:]
+    return shifted(k_pool), shifted(v_pool)
+
+
+@pytest.mark.parametrize("kind,dim,page,window,length,portion", [
+    ("decode", 128, 8, 1024, 2100, 1), ("decode", 64, 4, 200, 700, 1), ("decode", 128, 4, 70, 333, 1),
+    ("decode", 64, 16, 100, 1000, 1), ("prefill", 128, 16, 1024, 2106, 10), ("prefill", 64, 16, 1024, 2106, 10),
+    ("prefill", 64, 8, 100, 700, 70), ("prefill", 128, 4, 130, 450, 3), ("prefill_tcgen05", 128, 16, 1024, 2106, 40)])
+def test_pages_that_a_window_has_released_are_never_read(kind, dim, page, window, length, portion):
+    """The block table holds -1 for every page that lies wholly behind the window of the first query (what the cache
+    manager writes when it gives such pages back), and the memory one page before the pool is NaN."""
+    from libmir_b200 import kernels
+    heads, kv_heads = 4, 2
+    rng = np.random.default_rng(dim + page + length)
+    torch.manual_seed(dim + page + length)
+    scale = 0.8 / math.sqrt(dim)
+    q = (torch.randn(length, heads, dim) * 2).to(BF16)
+    k = (torch.randn(length, kv_heads, dim) * 2).to(BF16)
+    v = torch.randn(length, kv_heads, dim).to(BF16)
+    k_pool, v_pool, table = build_pool([k], [v], page, rng)
+    first_query = length - portion
+    first_visible = max(0, first_query + 1 - window)
+    released = first_visible // page
+    assert released > 2
+    for block in range(released):
+        physical = int(table[0, block])
+        k_pool[physical * page:(physical + 1) * page] = float("nan")          # given back: someone else's now
+        v_pool[physical * page:(physical + 1) * page] = float("nan")
+        table[0, block] = -1
+    k_dev, v_dev = pool_after_poison(k_pool, v_pool, page)
+    packed = torch.cat([q[first_query:].reshape(portion, -1), torch.zeros(portion, 2 * kv_heads * dim, dtype=BF16)],
+                       dim=1).contiguous()
+    out = torch.full((portion, heads * dim), 9.0, device="cuda", dtype=BF16)
+    if kind == "decode":
+        partition = 128
+        count = -(-length // partition)
+        scratch = torch.full((kernels.decode_attention_scratch_floats(1, heads, dim, count),), float("nan"), device="cuda")
+        kernels.decode_attention(cuda(packed), out, k_dev, v_dev, cuda(table), cuda(torch.tensor([length - 1], dtype=torch.int32)),
+                                 page, heads, kv_heads, dim, scale, window, partition, count, scratch)
+    else:
+        kernels.prefill_attention(cuda(packed), out, k_dev, v_dev, cuda(table), cuda(torch.tensor([0, portion], dtype=torch.int32)),
+                                  cuda(torch.tensor([length], dtype=torch.int32)), page, heads, kv_heads, dim, scale, window,
+                                  tensor_cores=(kind == "prefill_tcgen05"))
+        torch.cuda.synchronize()
+        assert kernels.prefill_attention_error() == 0
+    close(out.reshape(portion, heads, dim), expect(q, k, v, scale, window, slice(first_query, length)))
+
+
 def test_fast_kernels_refuse_other_head_sizes():
     from libmir_b200 import KernelError, kernels
     z = lambda *shape: torch.zeros(*shape, device="cuda", dtype=BF16)

@@ -105,7 +105,7 @@ def test_float32_logits_do_not_depend_on_the_cut_or_the_batch_at_all(tmp_path):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
-    """BASELINE workloads: prompts of 5/11/17 (A) and 1/9/33/64 (B) tokens, greedy, against the plain
+    """Prompts of 5/11/17 (A) and 1/9/33/64 (B) tokens, greedy, against the plain
     implementation decoding the same way (whole sequence recomputed for every token)."""
     from libmir_b200 import GenerationOverrides, GenerationRequest
     config = ALL[name]
@@ -156,6 +156,67 @@ def test_sampled_generation_follows_the_plain_sampler(tmp_path):
             tokens.append(token)
 
 
+def follow_plain_sampler(folder, prompts, options, seeds, outputs, dtype="float32"):
+    """Every generated token against the plain sampler on the plain logits, draw by draw."""
+    plain_config, weights = plain_impl.read_model(folder)
+    for index, (prompt, option, seed, output) in enumerate(zip(prompts, options, seeds, outputs)):
+        generator = plain_impl.SplitMix64(seed)
+        tokens = list(prompt)
+        assert len(output.token_ids) == option.max_tokens
+        for step, token in enumerate(output.token_ids):
+            logits = plain_impl.forward(plain_config, weights, tokens)[-1].numpy()
+            greedy = (option.temperature or 0.0) <= 1e-7 or option.top_k == 1
+            draw = 0.0 if greedy else generator.next_unit()
+            expected = plain_impl.sample(logits, draw, option.temperature or 0.0, option.top_k or 0,
+                                         option.top_p or 1.0, option.repetition_penalty or 1.0, tokens)
+            if token != expected and dtype == "bfloat16" and greedy:      # allowed only on a near-tie in bfloat16
+                margin = logits[expected] - logits[token]
+                assert margin <= 2 * TOL[dtype] * max(1.0, np.abs(logits).max()), (
+                    f"request {index} token {step}: {token}, plain says {expected} (margin {margin:.3e})")
+            else:
+                assert token == expected, f"request {index} token {step}: engine {token}, plain sampler {expected}"
+            tokens.append(token)
+
+
+def test_sampled_generation_on_captured_decode_steps_follows_the_plain_sampler(tmp_path):
+    """No request has a repetition penalty, so every decode-only step replays a captured graph, whose sampling
+    options (draw, temperature, top-p, top-k per row) the host writes into the graph's own block.  The requests
+    produce different numbers of tokens, so rows of the captured batch pass from one request to another while
+    others go on.  Every token must be the one the plain sampler picks with the same seed, draw by draw."""
+    from libmir_b200 import GenerationOverrides, GenerationRequest
+    folder = make_folder(tmp_path, TINY_B, seed=1, dtype="float32", sharpen=6.0)
+    rng = np.random.default_rng(19)
+    prompts = [random_ids(rng, TINY_B["vocab_size"], n) for n in (3, 9, 33, 20, 6)]
+    options = [GenerationOverrides(max_tokens=20, temperature=0.7),
+               GenerationOverrides(max_tokens=7, temperature=0.8, top_k=5),
+               GenerationOverrides(max_tokens=13, temperature=1.3, top_p=0.8),
+               GenerationOverrides(max_tokens=16, temperature=0.0),
+               GenerationOverrides(max_tokens=18, temperature=0.9, top_k=30, top_p=0.9)]
+    seeds = [200 + i for i in range(len(prompts))]
+    model = load(folder, "float32", page_size=8, prefill_chunk_tokens=16, max_batch_requests=4)
+    outputs = model.generate_batch([GenerationRequest(p, o, seed=s) for p, o, s in zip(prompts, options, seeds)])
+    graphs = model.runner._graphs
+    assert graphs is not None and sum(g.replays for g in graphs.graphs.values()) >= 15
+    assert any(g.ranked for g in graphs.graphs.values()) and len({g.rows for g in graphs.graphs.values()}) >= 2
+    follow_plain_sampler(folder, prompts, options, seeds, outputs)
+
+
+def test_greedy_generation_in_bfloat16_on_the_tensor_core_kernels(tmp_path):
+    """Configuration E (head_dim 128) through the entry point: prompts in portions of 128 tokens, then captured
+    decode steps; greedy tokens against the plain implementation, a differing token only at a near-tie."""
+    from libmir_b200 import GenerationOverrides, GenerationRequest
+    from tiny_configs import TINY_E
+    folder = make_folder(tmp_path, TINY_E, seed=3, dtype="bfloat16", sharpen=6.0)
+    rng = np.random.default_rng(23)
+    prompts = [random_ids(rng, TINY_E["vocab_size"], n) for n in (300, 5, 150)]
+    options = [GenerationOverrides(max_tokens=n, temperature=0.0) for n in (10, 6, 8)]
+    model = load(folder, "bfloat16", prefill_chunk_tokens=128)
+    outputs = model.generate_batch([GenerationRequest(p, o) for p, o in zip(prompts, options)])
+    graphs = model.runner._graphs
+    assert graphs is not None and sum(g.replays for g in graphs.graphs.values()) >= 5
+    follow_plain_sampler(folder, prompts, options, [0, 0, 0], outputs, dtype="bfloat16")
+
+
 def test_session_prefill_and_decode(tmp_path):
     from libmir_b200 import SamplingLogits
     folder = make_folder(tmp_path, TINY_A, seed=2, dtype="float32")
@@ -204,6 +265,13 @@ def test_generate_command_line(tmp_path):
     assert done.returncode == 0, done.stderr[-2000:]
     records = [json.loads(line) for line in done.stdout.strip().splitlines()]
     assert [r["request"] for r in records] == [0, 1] and all(len(r["token_ids"]) == 3 for r in records)
+    for record, prompt in zip(records, ([5, 17, 3], [9, 9])):               # every request draws from seed 7
+        generator = plain_impl.SplitMix64(7)
+        sequence = list(prompt)
+        for token in record["token_ids"]:
+            logits = plain_impl.forward(plain_config, weights, sequence)[-1].numpy()
+            assert token == plain_impl.sample(logits, generator.next_unit(), 0.8)
+            sequence.append(token)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -231,3 +299,30 @@ def test_single_tokens_between_portions_keep_the_order_of_what_is_wanted(tmp_pat
     result = model.step([StepEntry("c", prompts["c"][2:55], [52]), StepEntry("a", prompts["a"][37:70], [32])])
     assert result.rows == [("c", 52), ("a", 32)]
     check(result.logits.cpu().numpy(), np.stack([want["c"][54], want["a"][69]]), TOL[dtype], "after the mixed step")
+
+
+def test_a_folder_with_fused_and_transposed_tensors_gives_the_same_logits(tmp_path):
+    """The same weights stored as libmir also accepts them: query, key and value as one `qkv_proj` tensor, the
+    down projection as [in, out], an auxiliary buffer nobody asks for.  32-bit logits must be the same bits."""
+    from libmir_b200 import StepEntry
+    from libmir_b200.weights import load_tensor, read_catalog, write_file
+    plain_folder = make_folder(tmp_path / "plain", TINY_C, seed=12, dtype="float32", sharpen=6.0)
+    other = make_folder(tmp_path / "fused", TINY_C, seed=12, dtype="float32", sharpen=6.0)
+    tensors = {name: load_tensor(entry) for name, entry in read_catalog(other).items()}
+    for layer in range(TINY_C["num_hidden_layers"]):
+        stem = f"model.layers.{layer}."
+        for kind in ("weight", "bias"):
+            tensors[f"{stem}self_attn.qkv_proj.{kind}"] = torch.cat(
+                [tensors.pop(f"{stem}self_attn.{p}_proj.{kind}") for p in "qkv"], dim=0)
+        tensors[f"{stem}mlp.down_proj.weight"] = tensors[f"{stem}mlp.down_proj.weight"].t().contiguous()
+        tensors[f"{stem}self_attn.rotary_emb.inv_freq"] = torch.zeros(12)
+    write_file(other / "model.safetensors", tensors)
+    ids = random_ids(np.random.default_rng(12), TINY_C["vocab_size"], 75)
+    logits = []
+    for folder in (plain_folder, other):
+        model = load(folder, "float32", page_size=8)
+        model.admit("r")
+        logits.append(model.step([StepEntry("r", ids, range(len(ids)))]).logits.cpu().numpy())
+        model.unload()
+    assert np.array_equal(logits[0], logits[1])
+    check(logits[0], plain_logits(plain_folder, ids), TOL["float32"], "against the plain implementation")

@@ -56,11 +56,12 @@ def close(got, want, dtype, factor=1.0):
 def test_rms_norm_part(dtype):
     from libmir_b200.config.spec import RmsNormSpec
     from libmir_b200.engine.context import Arena
+    from libmir_b200.parts import ScratchContext
     from libmir_b200.registry import build_part
     part = build_part(RmsNormSpec(size=136, eps=2e-4), env(dtype))
     weights = bind_random(part, dtype)
     x = torch.randn(5, 136) * 2
-    ctx = SimpleNamespace(alloc=Arena(torch.device("cuda")).alloc)
+    ctx = ScratchContext(Arena(torch.device("cuda")).alloc, dtype)
     out = part.forward(ctx, x.cuda())
     assert out.dtype == dtype
     close(out, plain_impl.rms_norm(x.double(), weights["weight"], 2e-4), dtype)
@@ -84,13 +85,14 @@ def test_rotary_table_with_llama3_scaling():
 def test_swiglu_part(dtype):
     from libmir_b200.config.spec import SwiGluSpec
     from libmir_b200.engine.context import Arena
+    from libmir_b200.parts import ScratchContext
     from libmir_b200.registry import build_part
     part = build_part(SwiGluSpec(hidden_size=72, intermediate_size=200), env(dtype))
     weights = bind_random(part, dtype, std=0.15)
     x = torch.randn(9, 72).to(dtype)
     residual = torch.randn(9, 72)
     device_residual = residual.clone().cuda()
-    ctx = SimpleNamespace(alloc=Arena(torch.device("cuda")).alloc)
+    ctx = ScratchContext(Arena(torch.device("cuda")).alloc, dtype)
     part.forward(ctx, x.cuda(), device_residual)
     expected = residual.double() + plain_impl.swiglu(x.double(), weights, "")
     close(device_residual, expected, dtype)

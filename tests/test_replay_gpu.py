@@ -7,16 +7,21 @@ import numpy as np
 import pytest
 
 from helpers import TOL, Trace, compare_trace, make_folder, plain_logits, random_ids, run_trace
-from tiny_configs import ALL
+from tiny_configs import ALL, PAGE_SIZES
 
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [100, 70, 45, 120, 33, 64], "B": [200, 64, 33, 129, 97, 48], "C": [300, 130, 41, 520, 64, 90],
-           "D": [150, 90, 260, 48, 35, 201]}
+           "D": [150, 90, 260, 48, 35, 201],
+           # E and F run the tensor-core attention kernels in bfloat16: prompts of several 128-query tiles, contexts
+           # of more than one 256-key partition, longer than the window
+           "E": [700, 420, 300, 530, 160, 280], "F": [600, 330, 290, 450, 130, 200]}
 PORTIONS = [7, 2, 16, 3, 2, 33, 5, 2, 64, 9, 2, 17]
+LONG_PORTIONS = [130, 2, 257, 16, 3, 128, 40, 2, 64, 9, 2, 300]      # whole query tiles beside ragged ones
+FAST = ("E", "F")                                                  # configurations the tensor-core attention takes
 
 
-def build_trace(requests, rng):
+def build_trace(requests, rng, portions=PORTIONS, mixed_portion=24):
     trace = Trace()
     names = {}
     # 1. each request alone and whole
@@ -38,7 +43,7 @@ def build_trace(requests, rng):
         names[name] = index
         cursor, turn = 0, index
         while cursor < len(ids):
-            size = min(PORTIONS[turn % len(PORTIONS)], len(ids) - cursor)
+            size = min(portions[turn % len(portions)], len(ids) - cursor)
             turn += 1
             last = cursor + size == len(ids)
             trace.step([(name, ids[cursor:cursor + size], range(size))], end=[name] if last else [])
@@ -63,7 +68,7 @@ def build_trace(requests, rng):
             if cursor >= decode_from:
                 size = 1
             else:
-                size = min(int(rng.integers(2, 24)), decode_from - cursor)
+                size = min(int(rng.integers(2, mixed_portion)), decode_from - cursor)
                 if decode_from - cursor - size == 1:
                     size += 1
             want = [size - 1] if size > 1 else [0]
@@ -80,19 +85,54 @@ def build_trace(requests, rng):
     return trace, names
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", sorted(ALL))
-def test_replay_matches_the_plain_implementation(tmp_path, name, dtype):
+def replay_case(tmp_path, name, dtype, graphs):
+    import json
     config = ALL[name]
     rng = np.random.default_rng(sum(map(ord, name)))
     folder = make_folder(tmp_path / "model", config, seed=11, dtype=dtype, sharpen=6.0)
     requests = [random_ids(rng, config["vocab_size"], n) for n in LENGTHS[name]]
-    trace, names = build_trace(requests, rng)
+    fast = name in FAST
+    trace, names = build_trace(requests, rng, LONG_PORTIONS if fast else PORTIONS, 150 if fast else 24)
     logits = [plain_logits(folder, ids) for ids in requests]
     reference = {label: logits[index] for label, index in names.items()}
-    results = run_trace(folder, dtype, trace, tmp_path / "out")
-    worst = compare_trace(results, trace, reference, TOL[dtype], f"{name}/{dtype}")
-    print(f"{name}/{dtype}: {len(trace.lines)} steps, pool for {trace.peak} tokens, worst relative error {worst:.2e}")
+    report_path = tmp_path / "report.json"
+    extra = ["--page-size", str(PAGE_SIZES[name]), "--report", str(report_path)] + (["--decode-graphs"] if graphs else [])
+    results = run_trace(folder, dtype, trace, tmp_path / "out", extra_args=extra)
+    label = f"{name}/{dtype}" + ("/graphs" if graphs else "")
+    worst = compare_trace(results, trace, reference, TOL[dtype], label)
+    print(f"{label}: {len(trace.lines)} steps, pool for {trace.peak} tokens, worst relative error {worst:.2e}")
+    report = json.loads(report_path.read_text())
+    for group in report["cache"]["groups"]:
+        assert group["free"] == group["pages"], "every page came back"
+    assert any(group["reused"] > group["pages"] for group in report["cache"]["groups"]), "pages were used again"
+    assert all(flag == 0 for flag in report["errors"].values()), report["errors"]
+    if graphs:
+        assert report["graphs_captured"] > 0
+    return report
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(ALL))
+def test_replay_matches_the_plain_implementation(tmp_path, name, dtype):
+    report = replay_case(tmp_path, name, dtype, graphs=False)
+    launches = report["launches"]
+    if dtype == "bfloat16" and name in FAST:
+        # these configurations are here so that the four scripts run the tensor-core attention kernels
+        assert launches.get("paged_attention_generic", 0) == 0, launches
+        assert launches.get("decode_attention", 0) > 0 and launches.get("prefill_attention", 0) > 0, launches
+        if name == "E":
+            assert launches.get("prefill_attention_tc", 0) > 0, launches
+        assert launches.get("tc_stream", 0) > 0 and launches.get("gemm_bf16_lt", 0) > 0, launches
+
+
+@pytest.mark.parametrize("name, dtype", [("E", "bfloat16"), ("F", "bfloat16"), ("E", "float32"), ("B", "bfloat16"),
+                                         ("C", "float32")])
+def test_replay_with_captured_decode_steps(tmp_path, name, dtype):
+    """The same four scripts with every step of single tokens run as generation runs it: as a replay of a CUDA
+    graph captured for its bucket of rows and table widths."""
+    report = replay_case(tmp_path, name, dtype, graphs=True)
+    if dtype == "bfloat16" and name in FAST:
+        assert report["launches"].get("paged_attention_generic", 0) == 0, report["launches"]
 
 
 def test_pool_is_small_enough_that_pages_are_used_again(tmp_path):

@@ -203,3 +203,52 @@ def test_deterministic_schedule():
         scheduler.run()
         return runner.ran
     assert schedule() == schedule()
+
+
+def test_a_step_that_raises_leaves_nothing_live_once_the_caller_abandons():
+    """What Model.generate_batch does around Scheduler.run: a failing step must not leave this call's requests as
+    holders of pages and slots in the cache manager that later calls share."""
+    scheduler, _, manager = build(max_batch_tokens=16)
+    calls = {"n": 0}
+    inner = scheduler.run_step
+
+    def failing(entries, samplers):
+        calls["n"] += 1
+        if calls["n"] == 3:
+            raise RuntimeError("device failure")
+        return inner(entries, samplers)
+
+    scheduler.run_step = failing
+    for name in "abc":
+        scheduler.submit(request(name, 9, 6))
+    with pytest.raises(RuntimeError, match="device failure"):
+        try:
+            scheduler.run()
+        finally:
+            scheduler.abandon()
+    assert scheduler.idle and not manager.live
+    assert manager.groups[0].pool.free == 64 and manager.free_slots == 16
+    assert {r.finish_reason for r in scheduler.finished} == {"aborted"}
+    manager.check()
+
+
+def test_portions_keep_to_the_multiple_the_model_asks_for():
+    """A model whose parts scan in chunks of 8 tokens: every portion but the one that ends a request's pending
+    tokens is a multiple of 8, whatever the budget leaves."""
+    scheduler, runner, manager = build(max_batch_tokens=21, prefill_chunk_tokens=100)
+    scheduler.portion_multiple = 8
+    scheduler.submit(request("a", 45, 3))
+    scheduler.submit(request("b", 13, 2))
+    scheduler.run()
+    for step in runner.ran:
+        for rid, start, count, want in step:
+            total = 45 if rid == "a" else 13
+            if start < total and start + count < total:
+                assert count % 8 == 0 and start % 8 == 0, (rid, start, count)
+    assert [e for e in runner.ran[0]] == [("a", 0, 16, [])]              # 21 cut down to 16
+    assert runner.ran[1] == [("a", 16, 16, [])]
+    assert runner.ran[2] == [("a", 32, 13, [12]), ("b", 0, 8, [])]       # the rest of a; b gets a multiple of what is left
+    assert {r.request_id: len(r.output) for r in scheduler.finished} == {"a": 3, "b": 2}
+    manager.check()
+    with pytest.raises(SchedulerError, match="multiples of 64"):
+        Scheduler(manager, SchedulerConfig(max_batch_tokens=40), 128, lambda e, s: [], portion_multiple=64)

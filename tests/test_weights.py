@@ -110,3 +110,90 @@ def test_broken_files(tmp_path):
     (tmp_path / "model.safetensors").write_bytes((1 << 40).to_bytes(8, "little") + b"{}")
     with pytest.raises(WeightsError, match="exceeds the limit"):
         read_catalog(tmp_path)
+
+
+def rewrite(folder, change):
+    tensors = {name: load_tensor(entry) for name, entry in read_catalog(folder).items()}
+    change(tensors)
+    write_file(folder / "model.safetensors", tensors)
+    return tensors
+
+
+def test_extra_tensors_are_auxiliary_unless_strict(tmp_path):
+    """libmir classes a stored tensor that no role asks for as auxiliary; older Llama folders carry
+    rotary_emb.inv_freq buffers.  They are ignored (and remembered); with strict=True they are the error."""
+    folder = write_model_folder(tmp_path, TINY_A, seed=0, dtype="float32")
+    rewrite(folder, lambda t: t.update({"model.layers.0.self_attn.rotary_emb.inv_freq": torch.zeros(8)}))
+    model = cpu_model(TINY_A, folder)
+    load_into(model, folder)
+    assert model.ignored_tensors == ["model.layers.0.self_attn.rotary_emb.inv_freq"]
+    with pytest.raises(WeightsError) as info:
+        load_into(cpu_model(TINY_A, folder), folder, strict=True)
+    assert info.value.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq"] and not info.value.missing
+
+
+@pytest.mark.parametrize("fused_name", ["qkv_proj", "query_key_value"])
+def test_fused_qkv_is_split_by_rows(tmp_path, fused_name):
+    """A checkpoint that stores [Wq; Wk; Wv] (and the biases) as one tensor binds to the same weights as the
+    folder with separate tensors."""
+    folder = write_model_folder(tmp_path / "split", TINY_C, seed=0, dtype="float32")
+    split = cpu_model(TINY_C, folder)
+    load_into(split, folder)
+    fused_folder = write_model_folder(tmp_path / "fused", TINY_C, seed=0, dtype="float32")
+
+    def fuse(tensors):
+        for layer in range(TINY_C["num_hidden_layers"]):
+            stem = f"model.layers.{layer}.self_attn."
+            for kind in ("weight", "bias"):
+                parts = [tensors.pop(f"{stem}{p}_proj.{kind}") for p in "qkv"]
+                tensors[f"{stem}{fused_name}.{kind}"] = torch.cat(parts, dim=0)
+    rewrite(fused_folder, fuse)
+    fused = cpu_model(TINY_C, fused_folder)
+    assert fused.spec == split.spec                       # the bias was discovered from the fused tensor
+    load_into(fused, fused_folder)
+    for a, b in zip(split.blocks, fused.blocks):
+        assert torch.equal(a.mixer.w_qkv, b.mixer.w_qkv) and torch.equal(a.mixer.b_qkv, b.mixer.b_qkv)
+        assert torch.equal(a.mixer.w_o, b.mixer.w_o)
+
+
+def test_fused_and_separate_together_and_a_wrong_fused_shape_are_errors(tmp_path):
+    folder = write_model_folder(tmp_path, TINY_A, seed=0, dtype="float32")
+
+    def add_fused(tensors):
+        stem = "model.layers.1.self_attn."
+        tensors[stem + "qkv_proj.weight"] = torch.cat([tensors[stem + f"{p}_proj.weight"] for p in "qkv"], dim=0)
+    rewrite(folder, add_fused)
+    with pytest.raises(WeightsError, match="fused and separate") as info:
+        load_into(cpu_model(TINY_A, folder), folder)
+    assert "model.layers.1.self_attn.k_proj.weight" in str(info.value)
+
+    def only_fused_but_short(tensors):
+        stem = "model.layers.1.self_attn."
+        for p in "qkv":
+            del tensors[stem + f"{p}_proj.weight"]
+        tensors[stem + "qkv_proj.weight"] = tensors[stem + "qkv_proj.weight"][:-1]
+    rewrite(folder, only_fused_but_short)
+    with pytest.raises(WeightsError, match=r"qkv_proj.weight: expected \[128, 64\]") as info:
+        load_into(cpu_model(TINY_A, folder), folder)
+    assert len(info.value.wrong_shape) == 3 and not info.value.missing
+
+
+def test_tensors_stored_in_out_are_transposed(tmp_path):
+    """[in, out] tensors are recognised by their shape (libmir: transposes_last_two); a square tensor is taken as
+    stored."""
+    folder = write_model_folder(tmp_path / "plain", TINY_A, seed=0, dtype="float32")
+    plain = cpu_model(TINY_A, folder)
+    load_into(plain, folder)
+    other = write_model_folder(tmp_path / "swapped", TINY_A, seed=0, dtype="float32")
+
+    def swap(tensors):
+        for name in list(tensors):
+            if name.endswith(("mlp.down_proj.weight", "mlp.gate_proj.weight", "self_attn.k_proj.weight", "lm_head.weight")):
+                tensors[name] = tensors[name].t().contiguous()
+    rewrite(other, swap)
+    swapped = cpu_model(TINY_A, other)
+    load_into(swapped, other)
+    for a, b in zip(plain.blocks, swapped.blocks):
+        assert torch.equal(a.feed_forward.w_gate_up, b.feed_forward.w_gate_up)
+        assert torch.equal(a.feed_forward.w_down, b.feed_forward.w_down) and torch.equal(a.mixer.w_qkv, b.mixer.w_qkv)
+    assert torch.equal(plain.head, swapped.head)

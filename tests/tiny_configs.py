@@ -39,4 +39,24 @@ TINY_D = {   # Qwen2 style: q/k/v bias without output bias, MHA (groups of one),
     "tie_word_embeddings": True, "hidden_act": "silu",
 }
 
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+TINY_E = {   # head_dim 128: in bfloat16 the tcgen05 prompt kernel and the split decode kernel; one sliding layer
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "hidden_size": 256, "intermediate_size": 352, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 640,
+    "max_position_embeddings": 2048, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "layer_types": ["sliding_attention", "full_attention"], "sliding_window": 200,
+    "tie_word_embeddings": True, "hidden_act": "silu",
+}
+
+TINY_F = {   # head_dim 64: in bfloat16 the mma.sync prompt and decode kernels; groups of three, pages of 8, a window
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 192, "intermediate_size": 272, "num_hidden_layers": 3,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 410,
+    "max_position_embeddings": 1024, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+    "layer_types": ["full_attention", "sliding_attention", "full_attention"], "sliding_window": 100,
+    "tie_word_embeddings": False, "hidden_act": "silu",
+}
+
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
+# page sizes the replay tests give each configuration
+PAGE_SIZES = {"A": 16, "B": 8, "C": 16, "D": 16, "E": 16, "F": 8}
