@@ -186,7 +186,7 @@ def main() -> int:
     from libmir_b200.sampling import RequestSampler
 
     if args.library_modes:
-        kernels.SKINNY_MODES -= set(args.library_modes.split(","))
+        kernels.FEW_ROWS_MODES -= set(args.library_modes.split(","))
     if args.pdl is not None:
         kernels.set_programmatic_launch(args.pdl)
     if args.no_fold_norm:

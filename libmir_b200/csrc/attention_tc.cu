@@ -30,8 +30,10 @@
 // holds there, and the V ring starts zeroed, so a skipped page cannot inject a NaN (0 x NaN) into O.
 // Every wait is bounded in time; a role whose wait runs out raises g_tc_attention_error and stops waiting, the
 // CTA still frees its tensor memory and returns.
-// libmir computes prompt attention with a library (flash-attention style kernels in cuda/kernels/attention_bf16.cu
-// for decode; cuda/src/backend/attention/mod.rs chooses); the formula is metal/src/engine/attention/mod.rs:60-140.
+// libmir computes prompt attention with a library plan (FmhaBf16Plan of its external mircuda crate,
+// cuda/src/backend/attention/prefill/varlen.rs:1-23) or, over pages, with one thread block per token
+// (cuda/kernels/paged_prefill_attention_batch_bf16.cu:30-35,52-123); the formula as the Metal engine states it is
+// metal/src/engine/dense/swiglu/attention.rs:93-107.
 #include <algorithm>
 #include "tcgen05.cuh"
 

@@ -36,7 +36,7 @@ LIBRARIES = {
         "link": [],
     },
     "bf16": {
-        "sources": ["runtime.cu", "gemm_lt.cu", "attention_mma.cu", "gemm_skinny.cu", "gemm_tc.cu", "attention_tc.cu", "gemm_tc_stream.cu", "gemm_tc_pair.cu"],
+        "sources": ["runtime.cu", "gemm_lt.cu", "attention_mma.cu", "gemm_tc.cu", "attention_tc.cu", "gemm_tc_stream.cu"],
         "headers": ["no_alloc.h", "tcgen05.cuh"],
         "link": ["-lcublasLt"],
     },

@@ -328,7 +328,7 @@ MIR_EXPORT int mir_gemm_tc_set_width(int width) {
   return MIR_OK;
 }
 
-// mode as in mir_gemm_skinny_bf16: 0 store bf16, 1 accumulate into float, 2 float, 3 SwiGLU (w = [gate; up],
+// mode: 0 store bf16, 1 accumulate into float, 2 float, 3 SwiGLU (w = [gate; up],
 // up rows start at up_offset, n = number of output columns).  k and ldx must be multiples of 8, x and w 16-byte
 // aligned; m, n, k need not be multiples of the tile sizes.
 MIR_EXPORT int mir_gemm_tc_bf16(int mode, const void* x, int ldx, const void* w, const void* bias, void* out, int ldo,

@@ -37,7 +37,7 @@ constexpr int kMaxStages = 8;
 constexpr int kThreads = 6 * 32;            // producer warp, issuer warp, four epilogue warps
 constexpr int kRingBytes = 72 * 1024;       // per CTA, so that three CTAs fit on an SM
 int g_ring_bytes = kRingBytes;               // for measurements
-enum Epilogue : int { STORE = 0, ACCUM = 1, F32 = 2, SWIGLU = 3, QKV = 4 };
+enum Epilogue : int { STORE = 0, ACCUM = 1, F32 = 2, SWIGLU = 3 };
 
 __device__ int g_tc_stream_error = 0;
 
@@ -51,32 +51,15 @@ struct StreamNorm {
   int ld_weighted;
 };
 
-// The QKV epilogue (head_dim 128 = one tile per head): per-head q/k RMSNorm, rotary position encoding and the
-// write of K and V into their cache pages happen on the accumulator; q goes to the packed rows as bf16.
-struct QkvEpilogue {
-  const int* positions;      // [m]
-  const int* slot_mapping;   // [m] cache row of the token, negative: do not write K/V
-  const float* inv_freq;     // [rotary_dim / 2]
-  const float* q_norm;       // [128] or null
-  const float* k_norm;
-  bf16* k_pages;             // [cache rows, kv_heads, 128]
-  bf16* v_pages;
-  int heads, kv_heads, rotary_dim, write_kv;
-  float eps;
-};
-
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 3)
 tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                  const void* __restrict__ bias, void* __restrict__ out, int ldo, int m, int n, int k, int up_offset,
-                 int tokens, int tile_rows, int stages, int stage_stride, uint32_t tmem_columns, StreamNorm norm,
-                 QkvEpilogue qkv) {
+                 int tokens, int tile_rows, int stages, int stage_stride, uint32_t tmem_columns, StreamNorm norm) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long barriers[2 * kMaxStages + 1];
   __shared__ uint32_t tmem_base_slot;
   __shared__ float scale[kNormStatStride];
-  __shared__ float head_parts[4][4];                          // QKV: [token of the batch][warp] sums of squares
-  __shared__ float head_values[4][128];                       // QKV: [token of the batch][element] before rotation
   cg::cluster_group cluster = cg::this_cluster();
   const int splits = gridDim.y, split = blockIdx.y;           // the cluster spans gridDim.y
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -164,7 +147,6 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
   float* tile = reinterpret_cast<float*>(smem);               // [tokens][128]
   constexpr int BATCH = 4;                                    // tokens whose loads are in flight together
   float old_first[BATCH] = {0.0f, 0.0f, 0.0f, 0.0f};          // ACCUM: the residual under this thread's first tokens
-  float sine_first[BATCH] = {0.0f, 0.0f, 0.0f, 0.0f}, cosine_first[BATCH] = {1.0f, 1.0f, 1.0f, 1.0f};   // QKV
   if (warp >= 2) {
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;                      // feature row of the tile = accumulator lane
@@ -188,16 +170,6 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
       for (int j = 0; j < BATCH; ++j) {
         const int token = split + j * splits;
         if (token < m) old_first[j] = reinterpret_cast<const float*>(out)[(size_t)token * ldo + n0 + tid];
-      }
-    }
-    if (MODE == QKV && (int)blockIdx.x < qkv.heads + qkv.kv_heads && tid < qkv.rotary_dim) {
-      // the angles of this thread's element for this CTA's first tokens, while the products run
-      const int half = qkv.rotary_dim / 2;
-      const float frequency = qkv.inv_freq[tid < half ? tid : tid - half];
-#pragma unroll
-      for (int j = 0; j < BATCH; ++j) {
-        const int token = split + j * splits;
-        if (token < m) sincosf((float)qkv.positions[token] * frequency, &sine_first[j], &cosine_first[j]);
       }
     }
     const bool alive = wait_barrier(done, 0);
@@ -252,67 +224,6 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
             reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * (up[j] * s));
           }
         }
-      }
-    } else if (MODE == QKV) {
-      // this tile is one head: unit < heads a query head, then the key heads, then the value heads
-      const int unit = blockIdx.x;
-      const bool is_query = unit < qkv.heads, is_value = unit >= qkv.heads + qkv.kv_heads;
-      const float* head_norm = is_value ? nullptr : (is_query ? qkv.q_norm : qkv.k_norm);
-      const int half = qkv.rotary_dim / 2;
-      const float extra = bias != nullptr ? __bfloat162float(reinterpret_cast<const bf16*>(bias)[n0 + tid]) : 0.0f;
-      const float weight = head_norm != nullptr ? head_norm[tid] : 1.0f;
-      const float frequency = (!is_value && tid < qkv.rotary_dim) ? qkv.inv_freq[tid < half ? tid : tid - half] : 0.0f;
-      const int partner = tid < half ? tid + half : tid - half;          // used below rotary_dim only
-      for (int token0 = split; token0 < m; token0 += BATCH * splits) {
-        float value[BATCH];
-#pragma unroll
-        for (int j = 0; j < BATCH; ++j) {
-          const int token = token0 + j * splits;
-          value[j] = token < m ? cluster_sum(token, tid) * (token < kNormStatStride ? scale[token] : 1.0f) + extra : 0.0f;
-        }
-        if (head_norm != nullptr) {
-#pragma unroll
-          for (int j = 0; j < BATCH; ++j) {
-            float square = value[j] * value[j];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
-            if (lane == 0) head_parts[j][warp - 2] = square;
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-#pragma unroll
-          for (int j = 0; j < BATCH; ++j) {
-            const float total = (head_parts[j][0] + head_parts[j][1]) + (head_parts[j][2] + head_parts[j][3]);
-            value[j] *= rsqrtf(total / 128.0f + qkv.eps) * weight;
-          }
-        }
-        if (!is_value) {
-#pragma unroll
-          for (int j = 0; j < BATCH; ++j) head_values[j][tid] = value[j];
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-        }
-#pragma unroll
-        for (int j = 0; j < BATCH; ++j) {
-          const int token = token0 + j * splits;
-          if (token >= m) break;                              // the same for every thread
-          float result = value[j];
-          if (!is_value && tid < qkv.rotary_dim) {
-            float sine = sine_first[j], cosine = cosine_first[j];
-            if (token0 != split) sincosf((float)qkv.positions[token] * frequency, &sine, &cosine);
-            const float other = head_values[j][partner];
-            result = tid < half ? value[j] * cosine - other * sine : other * sine + value[j] * cosine;
-          }
-          if (is_query) {
-            reinterpret_cast<bf16*>(out)[(size_t)token * ldo + n0 + tid] = __float2bfloat16_rn(result);
-          } else {
-            const int slot = qkv.slot_mapping[token];
-            if (qkv.write_kv && slot >= 0) {
-              bf16* pages = is_value ? qkv.v_pages : qkv.k_pages;
-              const int kv_head = unit - qkv.heads - (is_value ? qkv.kv_heads : 0);
-              pages[((size_t)slot * qkv.kv_heads + kv_head) * 128 + tid] = __float2bfloat16_rn(result);
-            }
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");           // the shared arrays are reused by the next batch
       }
     } else {
       const int column = n0 + tid;
@@ -381,13 +292,13 @@ void choose_shape(int n, int total_steps, bool swiglu, int* tile_rows, int* spli
 
 template <int MODE>
 int launch(const void* x, int ldx, const void* w, const void* bias, void* out, int ldo, int m, int n, int k,
-           int up_offset, const StreamNorm& norm, cudaStream_t stream, const QkvEpilogue& qkv = QkvEpilogue()) {
+           int up_offset, const StreamNorm& norm, cudaStream_t stream) {
   const int tokens = (m + 15) / 16 * 16;
   const int total_steps = (k + kStepK - 1) / kStepK;
   int tile_rows, splits;
   choose_shape(n, total_steps, MODE == SWIGLU, &tile_rows, &splits);
   if (g_forced_splits > 0) splits = g_forced_splits;
-  if (g_forced_rows > 0 && MODE != SWIGLU && MODE != QKV) tile_rows = g_forced_rows;
+  if (g_forced_rows > 0 && MODE != SWIGLU) tile_rows = g_forced_rows;
   CUtensorMap w_map, x_map;
   int status = tensor_map_for(w, MODE == SWIGLU ? up_offset + n : n, k, k, tile_rows, &w_map);
   if (status != MIR_OK) return status;
@@ -414,7 +325,7 @@ int launch(const void* x, int ldx, const void* w, const void* bias, void* out, i
   uint32_t tmem_columns = 32;
   while ((int)tmem_columns < tokens) tmem_columns *= 2;
   return mir_launch_with(mir_pdl_for_streaming(), "tc_stream", tc_stream_kernel<MODE>, dim3(tiles, splits), dim3(kThreads), smem, stream, splits, w_map,
-                    x_map, bias, out, ldo, m, n, k, up_offset, tokens, tile_rows, stages, stage_stride, tmem_columns, norm, qkv);
+                    x_map, bias, out, ldo, m, n, k, up_offset, tokens, tile_rows, stages, stage_stride, tmem_columns, norm);
 }
 
 }  // namespace
@@ -440,7 +351,11 @@ MIR_EXPORT int mir_gemm_tc_stream_set_splits(int splits, int ring_kb, int tile_r
   return MIR_OK;
 }
 
-// Modes and the folded-norm arguments as in mir_gemm_skinny_bf16; 1 <= m <= 128, k and ldx multiples of 8, x and
+// mode: 0 store bf16 (+ bf16 bias), 1 accumulate into float (+ float bias), 2 float (+ float bias), 3 SwiGLU (w =
+// [gate rows; up rows], up rows start at up_offset, n = output columns).  sumsq / sumsq_tiles / eps: x is a folded
+// norm's weighted rows and every token's results are scaled by rsqrt(sum of its partial sums / k + eps) (store and
+// SwiGLU).  sumsq_out / next_weight / weighted_out: the accumulate epilogue also leaves the partial sums of squares
+// of the rows it updates and those rows times next_weight as bf16.  1 <= m <= 128, k and ldx multiples of 8, x and
 // w 16-byte aligned.  The sums of squares and the weighted rows are defined for up to kNormStatStride (32) tokens.
 MIR_EXPORT int mir_gemm_tc_stream_bf16(int mode, const void* x, int ldx, const void* w, const void* bias, void* out,
                                        int ldo, int m, int n, int k, int up_offset, const float* sumsq,
@@ -485,49 +400,4 @@ MIR_EXPORT int mir_gemm_tc_stream_bf16(int mode, const void* x, int ldx, const v
   }
   mir_set_error("tc_stream: unknown mode %d", mode);
   return MIR_BAD_ARGUMENT;
-}
-
-// The QKV projection of up to 128 rows with its post-processing in the epilogue (head_dim 128 only): out[m, ldo]
-// receives the rotated (and normalised) queries in its first heads * 128 columns; keys (rotated, normalised) and
-// values go to the cache rows slot_mapping[token] (negative: skipped; write_kv 0: nothing is written).
-// w is [(heads + 2 kv_heads) * 128, k]; bias (bf16) may be null; sumsq / sumsq_tiles / eps fold the norm before
-// the projection as in mir_gemm_tc_stream_bf16.
-MIR_EXPORT int mir_qkv_rope_store_tc_stream_bf16(const void* x, int ldx, const void* w, const void* bias, void* out,
-                                                 int ldo, int m, int k, const float* sumsq, int sumsq_tiles, float eps,
-                                                 const int* positions, const int* slot_mapping, const float* inv_freq,
-                                                 const float* q_norm, const float* k_norm, void* k_pages, void* v_pages,
-                                                 int heads, int kv_heads, int head_dim, int rotary_dim, float norm_eps,
-                                                 int write_kv, cudaStream_t stream) {
-  if (m == 0) return MIR_OK;
-  const int n = (heads + 2 * kv_heads) * 128;
-  if (head_dim != 128 || heads <= 0 || kv_heads <= 0 || rotary_dim < 0 || rotary_dim > 128 || (rotary_dim & 1) ||
-      m < 0 || m > 128 || k <= 0 || (k % 8) || (ldx % 8) || ldx < k || ldo < heads * 128 || ((uintptr_t)w & 15) ||
-      ((uintptr_t)x & 15) || x == nullptr || positions == nullptr || (rotary_dim > 0 && inv_freq == nullptr) ||
-      (write_kv && (slot_mapping == nullptr || k_pages == nullptr || v_pages == nullptr))) {
-    mir_set_error("qkv_rope_store_tc_stream: takes head_dim 128, 1..128 rows, an even rotary_dim up to 128, k and the "
-                  "row stride multiples of 8 (head_dim %d, m %d, k %d, rotary_dim %d)", head_dim, m, k, rotary_dim);
-    return MIR_BAD_ARGUMENT;
-  }
-  if (sumsq != nullptr && (sumsq_tiles <= 0 || m > 16)) {
-    mir_set_error("qkv_rope_store_tc_stream: a folded norm needs its partial sums and up to 16 rows");
-    return MIR_BAD_ARGUMENT;
-  }
-  StreamNorm norm = {};
-  norm.sumsq = sumsq;
-  norm.sumsq_tiles = sumsq_tiles;
-  norm.eps = eps;
-  QkvEpilogue qkv;
-  qkv.positions = positions;
-  qkv.slot_mapping = slot_mapping;
-  qkv.inv_freq = inv_freq;
-  qkv.q_norm = q_norm;
-  qkv.k_norm = k_norm;
-  qkv.k_pages = (bf16*)k_pages;
-  qkv.v_pages = (bf16*)v_pages;
-  qkv.heads = heads;
-  qkv.kv_heads = kv_heads;
-  qkv.rotary_dim = rotary_dim;
-  qkv.write_kv = write_kv;
-  qkv.eps = norm_eps;
-  return launch<QKV>(x, ldx, w, bias, out, ldo, m, n, k, 0, norm, stream, qkv);
 }

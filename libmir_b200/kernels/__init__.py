@@ -52,21 +52,13 @@ _SIGNATURES = {
         "mir_prefill_attention_tc_takes": [c_int, c_int],
         "mir_prefill_attention_tc_error": [],
         "mir_prefill_attention_tc_set_streams": [c_int],
-        "mir_gemm_skinny_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                 c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mir_gemm_tc_stream_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                     c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mir_gemm_tc_stream_error": [],
-        "mir_qkv_rope_store_tc_stream_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
-                                              c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                              c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "mir_gemm_tc_stream_set_splits": [c_int, c_int, c_int],
         "mir_gemm_tc_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_void_p],
         "mir_gemm_tc_set_width": [c_int],
-        "mir_gemm_tc_pair_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                  c_void_p],
-        "mir_gemm_tc_pair_error": [],
         "mir_gemm_tc_error": [],
         "mir_gemm_bf16_lt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_void_p, c_size_t, c_void_p],
@@ -289,51 +281,6 @@ def qk_rope_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Opti
                                       2 if keys_in_place else int(write_kv), _stream()))
 
 
-# Whether the QKV projection of a few rows does the per-head norm, the rotation and the cache write in its
-# epilogue (head_dim 128, the tcgen05 weight-streaming kernel): one kernel and one round trip of q, k, v less.
-# Measured on B200, Qwen3-4B sizes: 36 launches fewer per step but 3.14 ms against 3.11 ms at batch 8 and 2.45
-# against 2.41 ms at batch 1 (the longer tail of the projection costs more than the small kernel it saves): off.
-FUSE_ROPE_INTO_QKV = False
-
-
-def qkv_project_rope_store(x, w_qkv: torch.Tensor, b_qkv: Optional[torch.Tensor], qkv: torch.Tensor,
-                           positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
-                           inv_freq: Optional[torch.Tensor], q_norm: Optional[torch.Tensor],
-                           k_norm: Optional[torch.Tensor], k_pages: Optional[torch.Tensor],
-                           v_pages: Optional[torch.Tensor], heads: int, kv_heads: int, head_dim: int, rotary_dim: int,
-                           eps: float, write_kv: bool = True) -> bool:
-    """qkv[:, :heads * head_dim] = rotate(norm(x . w_q^T + b)), keys and values likewise into their cache pages, in
-    ONE kernel, if the sizes allow it (up to 16 bfloat16 rows, head_dim 128, x plain or a NormedResidual); returns
-    False, having done nothing, if they do not: the caller then runs `linear` and `qk_rope_store`."""
-    lazy = x if isinstance(x, NormedResidual) else None
-    rows = lazy.weighted if lazy is not None else x
-    m, k = rows.shape
-    fits = (FUSE_ROPE_INTO_QKV and FEW_ROWS_KERNEL.get("store") == "stream" and head_dim == 128
-            and rows.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16 and qkv.dtype == torch.bfloat16
-            and 0 < m <= SKINNY_MAX_ROWS and _skinny_ok(rows, m, k) and w_qkv.is_contiguous()
-            and w_qkv.shape == ((heads + 2 * kv_heads) * head_dim, k) and qkv.stride(1) == 1
-            and qkv.shape == (m, w_qkv.shape[0]) and (b_qkv is None or b_qkv.dtype == torch.bfloat16)
-            and rotary_dim % 2 == 0 and 0 <= rotary_dim <= head_dim
-            and (not rotary_dim or (inv_freq is not None and inv_freq.dtype == torch.float32
-                                    and inv_freq.numel() == rotary_dim // 2))
-            and all(n is None or (n.dtype == torch.float32 and n.numel() == head_dim) for n in (q_norm, k_norm))
-            and positions.dtype == torch.int32 and positions.numel() >= m
-            and (not write_kv or (slot_mapping is not None and slot_mapping.dtype == torch.int32
-                                  and k_pages is not None and v_pages is not None and k_pages.dtype == torch.bfloat16
-                                  and v_pages.dtype == torch.bfloat16 and k_pages.is_contiguous()
-                                  and v_pages.is_contiguous())))
-    if not fits:
-        return False
-    _cuda(rows, w_qkv, b_qkv, qkv, positions, slot_mapping, inv_freq, q_norm, k_norm, k_pages, v_pages)
-    lib = library("bf16")
-    _check(lib, lib.mir_qkv_rope_store_tc_stream_bf16(
-        rows.data_ptr(), rows.stride(0), w_qkv.data_ptr(), _ptr(b_qkv), qkv.data_ptr(), qkv.stride(0), m, k,
-        lazy.sumsq.data_ptr() if lazy is not None else None, lazy.tiles if lazy is not None else 0,
-        lazy.eps if lazy is not None else 0.0, positions.data_ptr(), _ptr(slot_mapping), _ptr(inv_freq), _ptr(q_norm),
-        _ptr(k_norm), _ptr(k_pages), _ptr(v_pages), heads, kv_heads, head_dim, rotary_dim, eps, int(write_kv), _stream()))
-    return True
-
-
 def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                             block_table: torch.Tensor, row_of_token: torch.Tensor, positions: torch.Tensor,
                             page_size: int, heads: int, kv_heads: int, head_dim: int, scale: float,
@@ -353,7 +300,6 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
 
 
 FAST_HEAD_DIMS = (64, 128)      # what the tensor-core attention kernels take; other sizes use the reference kernel
-SM_COUNT = 148
 DECODE_PARTITION_KEYS = 256     # keys one CTA of split decode attention takes (a multiple of 64, at most 512)
 
 
@@ -502,21 +448,9 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
     if lazy is not None:
         m, k = lazy.shape
         xw = lazy.weighted
-        fits = (weight.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and not accumulate
-                and "store" in SKINNY_MODES and _skinny_ok(xw, m, k))
-        if fits:
-            _cuda(xw, weight, out, bias, lazy.sumsq)
-            n = weight.shape[0]
-            _require(weight.shape[1] == k and out.shape == (m, n) and out.stride(1) == 1 and weight.is_contiguous()
-                     and xw.shape == (m, k) and xw.stride(1) == 1, "linear: shapes or strides do not fit")
-            if _few_rows_kernel(m, "store") == "stream":
-                stream_linear(xw, weight, out, bias, folded=lazy)
-                return False
-            lib = library("bf16")
-            _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_STORE, xw.data_ptr(), xw.stride(0), weight.data_ptr(),
-                                                 _ptr(bias), out.data_ptr(), out.stride(0), m, n, k, 0,
-                                                 lazy.sumsq.data_ptr(), lazy.tiles, lazy.eps, None, None, None, 0,
-                                                 _stream()))
+        if (weight.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and not accumulate
+                and "store" in FEW_ROWS_MODES and _few_rows_ok(xw, m, k)):
+            stream_linear(xw, weight, out, bias, folded=lazy)
             return False
         x = lazy.materialize(alloc)
     _cuda(x, weight, out, bias)
@@ -539,25 +473,12 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
         bias = None
     lib = library("bf16")
     mode_name = "store" if out.dtype == torch.bfloat16 else ("accum" if accumulate else "f32")
-    if _skinny_ok(x, m, k) and (out.dtype == torch.float32 or not accumulate) and mode_name in SKINNY_MODES:
-        mode = SKINNY_STORE if out.dtype == torch.bfloat16 else (SKINNY_ACCUM if accumulate else SKINNY_F32)
-        stats = sumsq_out if (mode == SKINNY_ACCUM and sumsq_out is not None
-                              and sumsq_out.numel() >= sumsq_tiles(n) * NORM_STAT_STRIDE
-                              and (m <= SKINNY_MAX_ROWS or _few_rows_kernel(m, mode_name) == "stream")) else None
+    if _few_rows_ok(x, m, k) and (out.dtype == torch.float32 or not accumulate) and mode_name in FEW_ROWS_MODES:
+        stats = sumsq_out if (mode_name == "accum" and sumsq_out is not None and m <= FOLDED_NORM_MAX_ROWS
+                              and sumsq_out.numel() >= sumsq_tiles(n) * NORM_STAT_STRIDE) else None
         rows, next_weight = weighted_out if (stats is not None and weighted_out is not None) else (None, None)
-        if rows is not None:
-            _cuda(rows, next_weight)
-            _require(rows.dtype == torch.bfloat16 and rows.shape == (m, n) and rows.stride(1) == 1
-                     and next_weight.dtype == torch.float32 and next_weight.numel() == n
-                     and next_weight.is_contiguous(), "linear: weighted rows are bfloat16 [M, N], the weight float32 [N]")
-        if _few_rows_kernel(m, mode_name) == "stream":
-            stream_linear(x, weight, out, bias, accumulate=accumulate, sumsq_out=stats,
-                          weighted_out=(rows, next_weight) if rows is not None else None)
-            return stats is not None
-        _check(lib, lib.mir_gemm_skinny_bf16(mode, x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias),
-                                             out.data_ptr(), out.stride(0), m, n, k, 0, None, 0, 0.0, _ptr(stats),
-                                             _ptr(next_weight), _ptr(rows), rows.stride(0) if rows is not None else 0,
-                                             _stream()))
+        stream_linear(x, weight, out, bias, accumulate=accumulate, sumsq_out=stats,
+                      weighted_out=(rows, next_weight) if rows is not None else None)
         return stats is not None
     workspace = _lt_workspace(x.device)
     _check(lib, lib.mir_gemm_bf16_lt(x.data_ptr(), x.stride(0), weight.data_ptr(), k, _ptr(bias), out.data_ptr(),
@@ -567,8 +488,7 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
 
 
 def tensor_core_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
-                       bias: Optional[torch.Tensor] = None, accumulate: bool = False, swiglu: bool = False,
-                       pairs: bool = False) -> None:
+                       bias: Optional[torch.Tensor] = None, accumulate: bool = False, swiglu: bool = False) -> None:
     """The tcgen05 product for many bfloat16 rows: out = x . weight^T (+ bias) as bfloat16, or as float32
     (added to out if `accumulate`); with `swiglu`, weight is [gate rows; up rows] and
     out[M, I] = silu(x w_gate^T) * (x w_up^T) in one kernel."""
@@ -582,21 +502,15 @@ def tensor_core_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
         inter = out.shape[1]
         _require(weight.shape[0] == 2 * inter and out.dtype == torch.bfloat16 and bias is None and not accumulate,
                  "tensor_core_linear: the SwiGLU epilogue takes [2 I, K] weights, no bias, and writes bfloat16")
-        mode, n, up_offset = SKINNY_SWIGLU, inter, inter
+        mode, n, up_offset = MODE_SWIGLU, inter, inter
     else:
         n, up_offset = weight.shape[0], 0
         _require(out.shape[1] == n and (bias is None or bias.dtype == out.dtype)
                  and (out.dtype == torch.float32 or not accumulate),
                  "tensor_core_linear: out must be [M, N]; bias shares its dtype; only float32 accumulates")
-        mode = SKINNY_STORE if out.dtype == torch.bfloat16 else (SKINNY_ACCUM if accumulate else SKINNY_F32)
-    entry = lib.mir_gemm_tc_pair_bf16 if pairs else lib.mir_gemm_tc_bf16
-    _check(lib, entry(mode, x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias), out.data_ptr(), out.stride(0), m, n,
-                      k, up_offset, _stream()))
-
-
-def tensor_core_pair_error() -> int:
-    """0, or which role of the two-SM tcgen05 product gave up a bounded wait (synchronises the device)."""
-    return int(library("bf16").mir_gemm_tc_pair_error())
+        mode = MODE_STORE if out.dtype == torch.bfloat16 else (MODE_ACCUM if accumulate else MODE_F32)
+    _check(lib, lib.mir_gemm_tc_bf16(mode, x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias), out.data_ptr(),
+                                     out.stride(0), m, n, k, up_offset, _stream()))
 
 
 # From how many rows the tcgen05 kernel computes the gated feed-forward product.  Measured on B200 at K 2,560,
@@ -627,14 +541,19 @@ def stream_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias
         inter = out.shape[1]
         _require(weight.shape[0] == 2 * inter and out.dtype == torch.bfloat16 and bias is None and not accumulate,
                  "stream_linear: the SwiGLU epilogue takes [2 I, K] weights, no bias, and writes bfloat16")
-        mode, n, up_offset = SKINNY_SWIGLU, inter, inter
+        mode, n, up_offset = MODE_SWIGLU, inter, inter
     else:
         n, up_offset = weight.shape[0], 0
         _require(out.shape[1] == n and (bias is None or bias.dtype == out.dtype)
                  and (out.dtype == torch.float32 or not accumulate),
                  "stream_linear: out must be [M, N]; bias shares its dtype; only float32 accumulates")
-        mode = SKINNY_STORE if out.dtype == torch.bfloat16 else (SKINNY_ACCUM if accumulate else SKINNY_F32)
+        mode = MODE_STORE if out.dtype == torch.bfloat16 else (MODE_ACCUM if accumulate else MODE_F32)
     rows, next_weight = weighted_out if weighted_out is not None else (None, None)
+    if rows is not None:
+        _cuda(rows, next_weight)
+        _require(rows.dtype == torch.bfloat16 and rows.shape == (m, n) and rows.stride(1) == 1
+                 and next_weight.dtype == torch.float32 and next_weight.numel() == n and next_weight.is_contiguous(),
+                 "stream_linear: weighted rows are bfloat16 [M, N], the norm weight float32 [N]")
     _check(lib, lib.mir_gemm_tc_stream_bf16(
         mode, x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias), out.data_ptr(), out.stride(0), m, n, k,
         up_offset, folded.sumsq.data_ptr() if folded is not None else None, folded.tiles if folded is not None else 0,
@@ -655,42 +574,21 @@ def tensor_core_linear_error() -> int:
     return int(library("bf16").mir_gemm_tc_error())
 
 
-SKINNY_MAX_ROWS = 16
 NORM_STAT_STRIDE = 32        # tokens per row of the sums-of-squares arrays (kNormStatStride of the kernels)
 FOLDED_NORM_MAX_ROWS = 32    # up to how many rows the streaming kernel writes and reads what a folded norm needs
-# Up to how many rows a product runs a few-rows kernel rather than the library.  The streaming kernel takes up to
+# Up to how many rows a product runs the weight-streaming kernel rather than the library.  The kernel takes up to
 # 128; measured alone at 64 rows it loses to cuBLASLt (12.2 / 8.5, 17.0 / 15.2, 14.9 / 8.2 us), and at 17 to 32
 # rows it is about as fast, but there it also takes over the two RMSNorms of a layer and the SwiGLU, which the
 # library path runs as kernels of their own: decode steps at Qwen3-4B sizes, library / streaming: batch 17 3.76 /
 # 3.56 ms, batch 24 4.11 / 3.91 ms, batch 32 4.50 / 4.31 ms; batch 64 6.27 / 6.65 ms.
 FEW_ROWS_MAX = 32
-SKINNY_MODES = {"store", "accum", "f32", "swiglu"}     # the few-rows epilogues in use; the rest go to the library
-SKINNY_STORE, SKINNY_ACCUM, SKINNY_F32, SKINNY_SWIGLU = 0, 1, 2, 3
+FEW_ROWS_MODES = {"store", "accum", "f32", "swiglu"}     # the streaming epilogues in use; the rest go to the library
+MODE_STORE, MODE_ACCUM, MODE_F32, MODE_SWIGLU = 0, 1, 2, 3
 
 
-# Which of the two few-rows kernels runs a product of up to 16 rows: "stream" (tcgen05, TMA ring, launched so
-# that its weights load while the kernel before it drains) or "skinny" (mma.sync from registers).  Measured on
-# B200 inside a CUDA graph at Qwen3-4B sizes, 8 rows, each kernel alone (us, stream / skinny): QKV 10.6 / 13.5,
-# gate-up with SwiGLU 21.5 / 27.0, output head 122 / 179, output projection 9.0 / 8.7, down projection
-# 14.1 / 13.9; 16 rows: 10.3 / 15.3, 15.0 / 25.1, 11.7 / 19.7, 25.5 / 37.5.  In the whole decode step, where the
-# streaming kernel's early start counts, batch 8 takes 3.12 ms with it everywhere against 3.25 ms with the
-# accumulating products on the other kernel, and 3.73 ms without it.
-FEW_ROWS_KERNEL = {"store": "stream", "f32": "stream", "swiglu": "stream", "accum": "auto"}
-STREAM_ACCUM_MIN_ROWS = 1
-
-
-def _few_rows_kernel(m: int, mode_name: str) -> str:
-    if m > SKINNY_MAX_ROWS:
-        return "stream"                     # 17 .. FEW_ROWS_MAX rows: only the streaming kernel takes them
-    choice = FEW_ROWS_KERNEL.get(mode_name, "skinny")
-    if choice == "auto":
-        return "stream" if m >= STREAM_ACCUM_MIN_ROWS else "skinny"
-    return choice
-
-
-def _skinny_ok(x: torch.Tensor, m: int, k: int) -> bool:
-    """Whether a few-rows kernel takes this product: up to FEW_ROWS_MAX rows, 16-byte aligned rows of 8-element
-    multiples."""
+def _few_rows_ok(x: torch.Tensor, m: int, k: int) -> bool:
+    """Whether the weight-streaming kernel takes this product: up to FEW_ROWS_MAX rows, 16-byte aligned rows of
+    8-element multiples."""
     return (0 < m <= min(FEW_ROWS_MAX, STREAM_MAX_ROWS) and k % 8 == 0 and x.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0)
 
@@ -708,31 +606,16 @@ def gate_up_silu(x, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -
     _require(w_gate_up.shape == (2 * inter, k) and out.shape[0] == m and out.is_contiguous()
              and w_gate_up.is_contiguous(), "gate_up_silu: shapes do not fit")
     few = (w_gate_up.dtype == torch.bfloat16 and 0 < m <= min(FEW_ROWS_MAX, STREAM_MAX_ROWS) and k % 8 == 0
-           and "swiglu" in SKINNY_MODES)
+           and "swiglu" in FEW_ROWS_MODES)
     if lazy is not None:
-        xw = lazy.weighted
-        if few and _skinny_ok(xw, m, k):
-            _cuda(xw, w_gate_up, out, lazy.sumsq)
-            if _few_rows_kernel(m, "swiglu") == "stream":
-                stream_linear(xw, w_gate_up, out, swiglu=True, folded=lazy)
-                return
-            lib = library("bf16")
-            _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_SWIGLU, xw.data_ptr(), xw.stride(0), w_gate_up.data_ptr(), None,
-                                                 out.data_ptr(), out.stride(0), m, inter, k, inter,
-                                                 lazy.sumsq.data_ptr(), lazy.tiles, lazy.eps, None, None, None, 0,
-                                                 _stream()))
+        if few and _few_rows_ok(lazy.weighted, m, k):
+            stream_linear(lazy.weighted, w_gate_up, out, swiglu=True, folded=lazy)
             return
         x = lazy.materialize(scratch_alloc)
     _cuda(x, w_gate_up, out)
     _require(x.stride(1) == 1, "gate_up_silu: x rows must be contiguous")
-    if few and x.dtype == torch.bfloat16 and _skinny_ok(x, m, k):
-        if _few_rows_kernel(m, "swiglu") == "stream":
-            stream_linear(x, w_gate_up, out, swiglu=True)
-            return
-        lib = library("bf16")
-        _check(lib, lib.mir_gemm_skinny_bf16(SKINNY_SWIGLU, x.data_ptr(), x.stride(0), w_gate_up.data_ptr(), None,
-                                             out.data_ptr(), out.stride(0), m, inter, k, inter, None, 0, 0.0, None,
-                                             None, None, 0, _stream()))
+    if few and x.dtype == torch.bfloat16 and _few_rows_ok(x, m, k):
+        stream_linear(x, w_gate_up, out, swiglu=True)
         return
     if (x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and m >= TENSOR_CORE_MIN_ROWS
             and _tensor_core_ok(x, k)):

@@ -94,16 +94,12 @@ class SoftmaxAttention(Mixer):
         ctx.accumulate(mixed, self.w_o, residual, self.b_o)      # may also prepare the norm that follows
 
     def project(self, ctx, cache, group, x, qkv, table, rotary_dim):
-        """Projection, per-head norm, rotation and cache write: in one kernel for a few rows where the sizes
-        allow it, else the library product and one kernel for the rest."""
+        """Projection, then per-head norm, rotation and cache write in one kernel."""
         s = self.spec
-        if not kernels.qkv_project_rope_store(x, self.w_qkv, self.b_qkv, qkv, ctx.positions, group.slot_mapping, table,
-                                              self.q_norm, self.k_norm, cache.k_pages, cache.v_pages, s.heads,
-                                              s.kv_heads, s.head_dim, rotary_dim, s.qk_norm_eps, write_kv=cache.writes):
-            kernels.linear(x, self.w_qkv, qkv, self.b_qkv, alloc=ctx.alloc)
-            kernels.qk_rope_store(qkv, ctx.positions, group.slot_mapping, table, self.q_norm, self.k_norm,
-                                  cache.k_pages, cache.v_pages, s.heads, s.kv_heads, s.head_dim, rotary_dim,
-                                  s.qk_norm_eps, write_kv=cache.writes)
+        kernels.linear(x, self.w_qkv, qkv, self.b_qkv, alloc=ctx.alloc)
+        kernels.qk_rope_store(qkv, ctx.positions, group.slot_mapping, table, self.q_norm, self.k_norm,
+                              cache.k_pages, cache.v_pages, s.heads, s.kv_heads, s.head_dim, rotary_dim,
+                              s.qk_norm_eps, write_kv=cache.writes)
 
     def project_with_other_position(self, ctx, cache, group, x, qkv):
         """A position encoding that is no rotation of the kernel's: projection, then the per-head norms alone, then

@@ -366,15 +366,12 @@ def test_repetition_penalty_rewrites_the_rows_logits():
     assert device.cpu().tolist() == [[2.0, -2.0, 0.5, 1.5], [1.0, 1.0, -3.0, 0.0]]
 
 
-@pytest.mark.parametrize("which", ["stream", "skinny"])
 @pytest.mark.parametrize("m", [1, 5, 8, 9, 16, 17, 32, 33, 64, 65])
 @pytest.mark.parametrize("n,k", [(136, 264), (50, 72), (2560, 1024)])
-def test_few_rows_products_and_their_epilogues(m, n, k, which, monkeypatch):
-    """Up to 16 bf16 rows run one of the two few-rows kernels (tcgen05 weight streaming, or mma.sync from
-    registers), more run the library: store, accumulate into the 32-bit residual, 32-bit output, bias, and a
-    strided view as input."""
+def test_few_rows_products_and_their_epilogues(m, n, k):
+    """Up to 32 bf16 rows run the tcgen05 weight-streaming kernel, more run the library: store, accumulate into
+    the 32-bit residual, 32-bit output, bias, and a strided view as input."""
     from libmir_b200 import kernels
-    monkeypatch.setattr(kernels, "FEW_ROWS_KERNEL", {mode: which for mode in kernels.FEW_ROWS_KERNEL})
     torch.manual_seed(m * n + k)
     x, w = torch.randn(m, k).bfloat16(), (torch.randn(n, k) * 0.3).bfloat16()
     exact = plain_impl.linear(x.double(), w)
@@ -394,15 +391,11 @@ def test_few_rows_products_and_their_epilogues(m, n, k, which, monkeypatch):
     close(logits, plain_impl.linear(wide[:, 16:16 + k].double().cpu(), w), torch.float32, factor=40)
 
 
-@pytest.mark.parametrize("which", ["stream", "skinny"])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("m,inter,k", [(1, 333, 72), (8, 9728 // 8, 320), (40, 200, 136), (64, 176, 264), (70, 96, 64),
                                        (130, 200, 136), (256, 333, 72), (300, 1216, 320)])
-def test_gate_up_silu(dtype, m, inter, k, which, monkeypatch):
+def test_gate_up_silu(dtype, m, inter, k):
     from libmir_b200 import kernels
-    if which == "skinny" and (m > 16 or dtype != torch.bfloat16):
-        pytest.skip("the choice of the few-rows kernel only matters for up to 16 bfloat16 rows")
-    monkeypatch.setattr(kernels, "FEW_ROWS_KERNEL", {mode: which for mode in kernels.FEW_ROWS_KERNEL})
     torch.manual_seed(m + inter)
     x = torch.randn(m, k).to(dtype)
     w = (torch.randn(2 * inter, k) * 0.2).to(dtype)
@@ -413,17 +406,14 @@ def test_gate_up_silu(dtype, m, inter, k, which, monkeypatch):
     close(out, plain_impl.silu(gate) * up, dtype, factor=2)
 
 
-@pytest.mark.parametrize("pairs", [False, True])
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 328, 520), (77, 100, 72), (300, 272, 1032), (129, 48, 8),
                                    (640, 1000, 264)])
-def test_tensor_core_product_and_its_epilogues(m, n, k, pairs):
-    """The tcgen05 products for many rows (TMA ring, accumulator in tensor memory; `pairs`: two SMs on one 256 x 256
-    tile with tcgen05.mma.cta_group::2): store with bias, accumulate into the 32-bit residual, 32-bit output, a
+def test_tensor_core_product_and_its_epilogues(m, n, k):
+    """The tcgen05 products for many rows (TMA ring, accumulator in tensor memory): store with bias, accumulate into the 32-bit residual, 32-bit output, a
     strided view as input, and the SwiGLU epilogue, at sizes that are no multiples of the tiles; none of the
     bounded waits may have run out."""
     from libmir_b200 import kernels
-    import functools
-    kernels_tensor_core_linear = functools.partial(kernels.tensor_core_linear, pairs=pairs)
+    kernels_tensor_core_linear = kernels.tensor_core_linear
     torch.manual_seed(m + n + k)
     x, w = torch.randn(m, k).bfloat16(), (torch.randn(n, k) * 0.3).bfloat16()
     exact = plain_impl.linear(x.double(), w)
@@ -447,7 +437,7 @@ def test_tensor_core_product_and_its_epilogues(m, n, k, pairs):
         gated = torch.empty(m, inter, device="cuda", dtype=torch.bfloat16)
         kernels_tensor_core_linear(cuda(x), cuda(w), gated, swiglu=True)
         close(gated, plain_impl.silu(exact[:, :inter]) * exact[:, inter:], torch.bfloat16, factor=2)
-    assert kernels.tensor_core_linear_error() == 0 and kernels.tensor_core_pair_error() == 0
+    assert kernels.tensor_core_linear_error() == 0
 
 
 def test_tensor_core_product_refuses_what_it_cannot_take():
@@ -458,18 +448,11 @@ def test_tensor_core_product_refuses_what_it_cannot_take():
         kernels.tensor_core_linear(x, w, torch.empty(128, 64, device="cuda", dtype=torch.bfloat16))
 
 
-@pytest.mark.parametrize("which", ["stream", "skinny"])
 @pytest.mark.parametrize("m", [1, 8, 13, 24, 32])
-def test_norm_folded_into_the_few_rows_products_around_it(m, which, monkeypatch):
+def test_norm_folded_into_the_few_rows_products_around_it(m):
     """The accumulating product leaves the sums of squares of the new residual and its rows times the next
-    norm's weight; the product after the norm scales its results: together they equal norm then product.
-    (17 to 32 rows: the streaming kernel only.)"""
+    norm's weight; the product after the norm scales its results: together they equal norm then product."""
     from libmir_b200 import kernels
-    if m > kernels.SKINNY_MAX_ROWS:
-        if which == "skinny":
-            pytest.skip("the mma.sync kernel takes up to 16 rows")
-        monkeypatch.setattr(kernels, "FEW_ROWS_MAX", 32)
-    monkeypatch.setattr(kernels, "FEW_ROWS_KERNEL", {mode: which for mode in kernels.FEW_ROWS_KERNEL})
     torch.manual_seed(m)
     hidden, inner, wide, eps = 264, 136, 200, 1e-5
     x = torch.randn(m, inner).bfloat16()
@@ -538,52 +521,3 @@ def test_weight_streaming_product_and_its_epilogues(m, n, k):
     kernels.stream_linear(cuda(x), cuda(w[:2 * inter]), gated, swiglu=True)
     close(gated, plain_impl.silu(exact[:, :inter]) * exact[:, inter:2 * inter], torch.bfloat16, factor=2)
     assert kernels.stream_linear_error() == 0
-
-
-@pytest.mark.parametrize("m,rotary,norms,bias", [(1, 128, True, False), (8, 128, True, True), (13, 64, False, True),
-                                                 (16, 128, False, False), (5, 0, True, False)])
-def test_qkv_projection_with_norm_rotation_and_cache_write_in_its_epilogue(m, rotary, norms, bias, monkeypatch):
-    """One kernel (head_dim 128, up to 16 rows) against the product followed by the q/k-norm + rope + cache
-    write kernel, and against the plain formulas; a row with a negative slot writes no key or value."""
-    from libmir_b200 import kernels
-    monkeypatch.setattr(kernels, "FUSE_ROPE_INTO_QKV", True)      # off by default (measured slower in a step)
-    torch.manual_seed(m + rotary)
-    heads, kv_heads, dim, hidden, page = 6, 2, 128, 264, 8
-    units = heads + 2 * kv_heads
-    x = torch.randn(m, hidden).bfloat16()
-    w = (torch.randn(units * dim, hidden) * 0.1).bfloat16()
-    b = (torch.randn(units * dim) * 0.5).bfloat16() if bias else None
-    q_norm = (torch.rand(dim) + 0.5) if norms else None
-    k_norm = (torch.rand(dim) + 0.5) if norms else None
-    inv_freq = plain_impl.rope_inverse_frequencies(rotary, 10000.0, None).float() if rotary else None
-    positions = torch.randint(0, 3000, (m,), dtype=torch.int32)
-    slots = torch.randperm(4 * page)[:m].to(torch.int32)
-    if m > 1:
-        slots[m // 2] = -1
-    pools = [torch.full((4 * page, kv_heads, dim), 7.0).bfloat16() for _ in range(4)]
-    fused_k, fused_v, plain_k, plain_v = [cuda(p) for p in pools]
-    dev = lambda t: None if t is None else cuda(t)
-    fused = torch.zeros(m, units * dim, device="cuda", dtype=torch.bfloat16)
-    assert kernels.qkv_project_rope_store(cuda(x), cuda(w), dev(b), fused, cuda(positions), cuda(slots), dev(inv_freq),
-                                          dev(q_norm), dev(k_norm), fused_k, fused_v, heads, kv_heads, dim, rotary, 1e-6)
-    two = torch.zeros(m, units * dim, device="cuda", dtype=torch.bfloat16)
-    kernels.linear(cuda(x), cuda(w), two, dev(b))
-    kernels.qk_rope_store(two, cuda(positions), cuda(slots), dev(inv_freq), dev(q_norm), dev(k_norm), plain_k, plain_v,
-                          heads, kv_heads, dim, rotary, 1e-6)
-    assert kernels.stream_linear_error() == 0
-    # against the two-kernel path: the same up to one rounding of the projection to bf16
-    close(fused[:, :heads * dim], two[:, :heads * dim].double(), torch.bfloat16, factor=2)
-    close(fused_k, plain_k.double(), torch.bfloat16, factor=2)
-    close(fused_v, plain_v.double(), torch.bfloat16, factor=2)
-    assert torch.equal(fused_k[slots[slots >= 0].long()].cpu() == 7.0, plain_k[slots[slots >= 0].long()].cpu() == 7.0)
-    untouched = torch.ones(4 * page, dtype=torch.bool)
-    untouched[slots[slots >= 0].long()] = False
-    assert bool((fused_k[untouched.cuda()] == 7.0).all()) and bool((fused_v[untouched.cuda()] == 7.0).all())
-    # against the formulas
-    projected = plain_impl.linear(x.double(), w) + (b.double() if bias else 0.0)
-    q = projected[:, :heads * dim].reshape(m, heads, dim)
-    if norms:
-        q = plain_impl.rms_norm(q, q_norm, 1e-6)
-    if rotary:
-        q = plain_impl.rope(q, positions.long(), inv_freq)
-    close(fused[:, :heads * dim].reshape(m, heads, dim), q, torch.bfloat16, factor=2)
