@@ -146,6 +146,8 @@ def main() -> int:
                         help="layer sizes of the model (default: the headline configuration)")
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has")
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--repeats", type=int, default=5,
+                        help="how often the timed region of K steps is run; the median region is reported")
     parser.add_argument("--context", type=int, default=PROMPT_TOKENS,
                         help="tokens every request holds when decoding starts, and the length of the timed prompt "
                              "(default: the headline configuration's 2,048; up to 8,192 in one prefill step)")
@@ -159,7 +161,7 @@ def main() -> int:
     parser.add_argument("--no-fold-norm", action="store_true",
                         help="run every RMSNorm as a kernel of its own instead of folding it into the few-rows "
                              "products around it")
-    parser.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "serve"],
+    parser.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "serve", "kernels"],
                         help="decode / prefill: run only that phase, bracketed by cudaProfilerStart/Stop (for ncu "
                              "--profile-from-start off); the JSON line then holds only that phase")
     parser.add_argument("--no-graphs", action="store_true", help="decode steps as plain launches, not as CUDA graphs")
@@ -253,28 +255,32 @@ def main() -> int:
     def event_pair():
         return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
-    def decode_device(batch, steps, warmup):
-        """K back-to-back decode steps on the device; returns (tokens/s, ms per step, launches, clocks)."""
-        ids = fill(batch)
-        samplers = [RequestSampler() for _ in ids]
-        tokens = rng.integers(0, vocab, size=batch).tolist()
-        entries = [StepEntry(i, [t], [0]) for i, t in zip(ids, tokens)]
-        out = model.decode_many(entries, samplers, warmup)
-        entries = [StepEntry(i, [int(t)], [0]) for i, t in zip(ids, out[-1].tolist())]
-        torch.cuda.synchronize()
-        launches = kernels.LAUNCHES
-        start, stop = event_pair()
+    def decode_device(batch, steps, warmup, repeats=1):
+        """`repeats` regions of K back-to-back decode steps on the device, each after W warm-up steps from the same
+        context; returns (tokens/s, ms per step, launches, clocks, context, ms per step of every region) with the
+        median region's time."""
+        regions, launches = [], 0
         with ClockSampler() as clocks:
-            torch.cuda.synchronize()
-            start.record()
-            model.decode_many(entries, samplers, steps)
-            stop.record()
-            torch.cuda.synchronize()
-        ms = start.elapsed_time(stop)
-        launches = kernels.LAUNCHES - launches
+            for _ in range(repeats):
+                ids = fill(batch)
+                samplers = [RequestSampler() for _ in ids]
+                tokens = rng.integers(0, vocab, size=batch).tolist()
+                entries = [StepEntry(i, [t], [0]) for i, t in zip(ids, tokens)]
+                out = model.decode_many(entries, samplers, warmup)
+                entries = [StepEntry(i, [int(t)], [0]) for i, t in zip(ids, out[-1].tolist())]
+                torch.cuda.synchronize()
+                launches = kernels.LAUNCHES
+                start, stop = event_pair()
+                start.record()
+                model.decode_many(entries, samplers, steps)
+                stop.record()
+                torch.cuda.synchronize()
+                regions.append(start.elapsed_time(stop) / steps)
+                launches = kernels.LAUNCHES - launches
+                release(ids)
+        ms_per_step = statistics.median(regions)
         context = prompt_tokens + warmup + steps / 2.0
-        release(ids)
-        return batch * steps / (ms / 1e3), ms / steps, launches, clocks.summary(), context
+        return batch * 1e3 / ms_per_step, ms_per_step, launches, clocks.summary(), context, regions
 
     def decode_e2e(batch, steps, warmup, profile=False):
         """The same through Model.step: host ids in, sampled ids out, every step."""
@@ -342,6 +348,107 @@ def main() -> int:
         release(ids)
         return statistics.median(times[1:])
 
+    def kernel_points(batch, repeats=5):
+        """Each dominant kernel of the step alone at this model's layer sizes: (microseconds, fraction of its
+        roofline).  A kernel runs 24 times inside one CUDA graph, each time on another copy of its weights (or
+        another layer of the cache), together more than the L2 holds, so every launch reads from HBM; the graph is
+        replayed `repeats` times and the median per-launch time is taken (CUDA events).  Decode kernels (few rows)
+        are measured against the copy bandwidth over the bytes they must read, the prompt kernels (2,048 rows)
+        against the matrix-product peak over their flops."""
+        import math
+        bf16, f32 = torch.bfloat16, torch.float32
+        results = {}
+        launches_per_graph = 24
+
+        def timed(build, work, peak):
+            calls = build()
+            for call in calls[:2]:
+                call()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for index in range(launches_per_graph):
+                    calls[index % len(calls)]()
+            graph.replay()
+            torch.cuda.synchronize()
+            times = []
+            for _ in range(repeats):
+                start, stop = event_pair()
+                start.record()
+                graph.replay()
+                stop.record()
+                torch.cuda.synchronize()
+                times.append(start.elapsed_time(stop) * 1e3 / launches_per_graph)
+            us = statistics.median(times)
+            return [round(us, 2), round(work / (us * 1e-6) / peak, 4)]
+
+        def copies_of(rows, cols, scale=0.02):
+            count = max(2, min(launches_per_graph, -(-(400 << 20) // (rows * cols * 2))))
+            return [torch.randn(rows, cols, device="cuda", dtype=bf16) * scale for _ in range(count)]
+
+        hbm, flops_peak = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+        qkv_width = (heads + 2 * kv_heads) * dim
+        shapes = {"qkv": (qkv_width, hidden), "output": (hidden, heads * dim), "gate_up": (2 * inter, hidden),
+                  "down": (hidden, inter)}
+        for rows, label in ((batch, f"decode_b{batch}"), (prompt_tokens, f"prefill_{prompt_tokens}")):
+            for name, (n, k) in shapes.items():
+                def build(n=n, k=k, name=name, rows=rows):
+                    weights = copies_of(n, k)
+                    x = torch.randn(rows, k, device="cuda", dtype=bf16)
+                    if name == "gate_up":
+                        out = torch.empty(rows, n // 2, device="cuda", dtype=bf16)
+                        scratch = lambda shape, dtype: torch.empty(shape, device="cuda", dtype=dtype)
+                        return [lambda w=w: kernels.gate_up_silu(x, w, out, scratch) for w in weights]
+                    if name == "qkv":
+                        out = torch.empty(rows, n, device="cuda", dtype=bf16)
+                        return [lambda w=w: kernels.linear(x, w, out) for w in weights]
+                    out = torch.zeros(rows, n, device="cuda", dtype=f32)
+                    return [lambda w=w: kernels.linear(x, w, out, accumulate=True) for w in weights]
+                if rows == batch:
+                    results[f"{label}_{name}"] = timed(build, n * k * 2, hbm)
+                else:
+                    results[f"{label}_{name}"] = timed(build, 2.0 * rows * n * k, flops_peak)
+        # the output head of a decode step
+        def build_head():
+            x = torch.randn(batch, hidden, device="cuda", dtype=bf16)
+            out = torch.empty(batch, vocab, device="cuda", dtype=f32)
+            return [lambda: kernels.linear(x, model.decoder.head, out)]
+        results[f"decode_b{batch}_head"] = timed(build_head, vocab * hidden * 2, hbm)
+        # attention over distinct layers of the cache: decoded tokens, and one prompt
+        group = model.cache.groups[0]
+        views = [model.storage.views[entry] for entry in group.entries]
+        ids = fill(batch)
+        sequences = [model.cache.live[i] for i in ids]
+        width = max(len(seq.tables[0]) for seq in sequences)
+        table = torch.tensor([seq.tables[0] + [-1] * (width - len(seq.tables[0])) for seq in sequences],
+                             dtype=torch.int32, device="cuda")
+        positions = torch.full((batch,), prompt_tokens - 1, dtype=torch.int32, device="cuda")
+        qkv = torch.randn(batch, qkv_width, device="cuda", dtype=bf16)
+        mixed = torch.empty(batch, heads * dim, device="cuda", dtype=bf16)
+        partition, count = kernels.decode_partitioning(batch, kv_heads, prompt_tokens)
+        scratch = torch.empty(max(1, kernels.decode_attention_scratch_floats(batch, heads, dim, count)), device="cuda")
+        scale = 1.0 / math.sqrt(dim)
+        def build_decode_attention():
+            return [lambda v=v: kernels.decode_attention(qkv, mixed, v.k_pages, v.v_pages, table, positions, PAGE_SIZE,
+                                                         heads, kv_heads, dim, scale, None, partition, count, scratch)
+                    for v in views]
+        results[f"decode_b{batch}_attention"] = timed(build_decode_attention,
+                                                      batch * prompt_tokens * kv_heads * dim * 2 * 2, hbm)
+        release(ids)
+        ids = fill(1)
+        table = torch.tensor([model.cache.live[ids[0]].tables[0]], dtype=torch.int32, device="cuda")
+        qkv = torch.randn(prompt_tokens, qkv_width, device="cuda", dtype=bf16)
+        mixed = torch.empty(prompt_tokens, heads * dim, device="cuda", dtype=bf16)
+        starts = torch.tensor([0, prompt_tokens], dtype=torch.int32, device="cuda")
+        lens = torch.tensor([prompt_tokens], dtype=torch.int32, device="cuda")
+        def build_prompt_attention():
+            return [lambda v=v: kernels.prefill_attention(qkv, mixed, v.k_pages, v.v_pages, table, starts, lens,
+                                                          PAGE_SIZE, heads, kv_heads, dim, scale, None) for v in views]
+        results[f"prefill_{prompt_tokens}_attention"] = timed(
+            build_prompt_attention, 4.0 * heads * dim * prompt_tokens * (prompt_tokens + 1) / 2.0, flops_peak)
+        release(ids)
+        return results
+
     hidden, inter, heads, kv_heads, dim = (config[k] for k in ("hidden_size", "intermediate_size",
                                                                "num_attention_heads", "num_key_value_heads",
                                                                "head_dim"))
@@ -353,7 +460,8 @@ def main() -> int:
     if args.phase == "decode":
         device_value = device_ms = launches = hbm_frac = 0.0
         if not args.no_graphs:
-            device_value, device_ms, launches, _, context = decode_device(args.batch, args.steps, args.warmup)
+            device_value, device_ms, launches, _, context, _ = decode_device(args.batch, args.steps, args.warmup,
+                                                                            args.repeats)
             step_bytes = weight_bytes + args.batch * context * kv_bytes_per_token
             hbm_frac = step_bytes / (device_ms / 1e3) / 1e9 / peaks["hbm_gbs"]
         tokens_per_second, _, _ = decode_e2e(args.batch, args.steps, args.warmup, profile=True)
@@ -387,13 +495,18 @@ def main() -> int:
                           "generated_tokens_per_second": round(generated / seconds, 1),
                           "all_tokens_per_second": round((generated + sum(lengths)) / seconds, 1), "layers": layers}))
         return 0
+    if args.phase == "kernels":
+        print(json.dumps({"phase": "kernels", "batch": args.batch, "context": prompt_tokens,
+                          "kernels": kernel_points(args.batch)}))
+        return 0
     if args.phase == "prefill":
         ms = prefill(repeats=max(1, min(args.steps, 5)), profile=True)
         print(json.dumps({"phase": "prefill", "tokens": prompt_tokens, "layers": layers, "ms": round(ms, 3),
                           "frac_of_peak": round(prefill_flops / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}))
         return 0
 
-    value, ms_per_step, launches, clocks, context = decode_device(args.batch, args.steps, args.warmup)
+    value, ms_per_step, launches, clocks, context, regions = decode_device(args.batch, args.steps, args.warmup,
+                                                                           args.repeats)
     step_bytes = weight_bytes + args.batch * context * kv_bytes_per_token
     achieved_gbs = step_bytes / (ms_per_step / 1e3) / 1e9
     e2e_value, h2d, d2h = decode_e2e(args.batch, args.steps, args.warmup)
@@ -401,7 +514,7 @@ def main() -> int:
     points = {}
     if not args.skip_points:
         for batch in (1, 64):
-            points[f"decode_b{batch}"] = round(decode_device(batch, args.steps, args.warmup)[0], 1)
+            points[f"decode_b{batch}"] = round(decode_device(batch, args.steps, args.warmup, args.repeats)[0], 1)
         points["mixed_32_decodes_512_prompt_tokens_ms"] = round(mixed_step(32, 512), 3)
 
     line = {
@@ -415,8 +528,9 @@ def main() -> int:
             "vocab": vocab, "global_batch": args.batch, "seq_len": prompt_tokens + GENERATED_TOKENS,
             "context_at_decode": round(context, 1), "page_size": PAGE_SIZE, "tied_embeddings": bool(config.get("tie_word_embeddings", False)),
             "parallelism": "1 GPU", "l2": "inputs larger than L2 (a step reads every weight and the cache)",
-            "peaks": peaks_kind,
+            "peaks": peaks_kind, "timed_regions": args.repeats,
         },
+        "ms_per_step_regions": [round(r, 4) for r in regions],
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
@@ -427,6 +541,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved_gbs / peaks["hbm_gbs"], 4)},
         "points": points,
+        "kernels": kernel_points(args.batch) if not args.skip_points else {},
         "native_libraries": sorted(os.path.basename(p) for p in kernels.loaded_libraries().values()),
     }
     print(json.dumps(line))

@@ -16,6 +16,7 @@
 // (row stride head_dim + 8 elements: an odd number of 16-byte chunks, so ldmatrix is conflict-free).
 // Scores, maxima, exponentials and sums are 32-bit.  Keys outside [first visible, position] are masked
 // before the maximum is taken; a tile's tail beyond the context is zero-filled, never read.
+#include <algorithm>
 #include <cfloat>
 #include "common.cuh"
 
@@ -225,14 +226,17 @@ __global__ void __launch_bounds__(kDecodeWarps * 32)
 decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* __restrict__ k_pages,
                         const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                         const int* __restrict__ positions, int page_size, int heads, int kv_heads, float scale_log2,
-                        int window, int partition, int num_partitions, float* __restrict__ partial_o,
+                        int window, int partition, int num_partitions, int part_slow, float* __restrict__ partial_o,
                         float* __restrict__ partial_ml, bf16* __restrict__ out) {
   constexpr int STRIDE = D + 8;
   constexpr int TILE_ELEMS = kDecodeTile * STRIDE;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int quad = lane & 3, group_row = lane >> 2;
-  const int part = blockIdx.x, row = blockIdx.z;
+  // The partition is the fast index of the grid (a request's CTAs start together), except for a handful of rows,
+  // where it is the slow one, so that partitions beyond the contexts (dead CTAs of a captured batch, whose table is
+  // wider than any context) are dispatched last: batch 1 at 2,112 keys 8.4 against 9.4 us, batch 8 19.8 against 19.4.
+  const int part = part_slow ? blockIdx.z : blockIdx.x, row = part_slow ? blockIdx.x : blockIdx.z;
   const int group = heads / kv_heads;
   const int group_tiles = (group + kDecodeHeads - 1) / kDecodeHeads;
   const int kv_head = blockIdx.y / group_tiles;
@@ -627,11 +631,12 @@ int launch_decode_staged(const bf16* q, size_t q_stride, bf16* out, const bf16* 
   int status = set_smem(decode_attention_kernel<D, STAGES>, smem, "decode_attention", smem_set);
   if (status != MIR_OK) return status;
   const int group = heads / kv_heads;
-  const dim3 grid(num_partitions, kv_heads * ((group + kDecodeHeads - 1) / kDecodeHeads), rows);
+  const int units = kv_heads * ((group + kDecodeHeads - 1) / kDecodeHeads);
+  const dim3 grid = rows <= 4 ? dim3(rows, units, num_partitions) : dim3(num_partitions, units, rows);
   status = mir_launch_with(mir_pdl_for_streaming(), "decode_attention", decode_attention_kernel<D, STAGES>, grid,
                            dim3(kDecodeWarps * 32), smem, stream, 0, q, q_stride, k_pages, v_pages, block_table,
                            table_width, positions, page_size, heads, kv_heads, scale * 1.4426950408889634f, window,
-                           partition, num_partitions, partial_o, partial_ml, out);
+                           partition, num_partitions, rows <= 4 ? 1 : 0, partial_o, partial_ml, out);
   if (status != MIR_OK || num_partitions == 1) return status;
   return mir_launch("decode_merge", decode_merge_kernel<D>, dim3(heads, rows), dim3(kMergeWarps * 32), 0, stream, 0,
                     (const float*)partial_o, (const float*)partial_ml, positions, heads, window, partition,
@@ -639,7 +644,6 @@ int launch_decode_staged(const bf16* q, size_t q_stride, bf16* out, const bf16* 
 }
 
 long long g_deep_ring_ctas = 1536;                              // up to this many CTAs run three tiles in flight per warp
-
 template <int D>
 int launch_decode(const bf16* q, size_t q_stride, bf16* out, const bf16* k_pages, const bf16* v_pages,
                   const int* block_table, int table_width, const int* positions, int rows, int page_size, int heads,
@@ -693,6 +697,7 @@ bool bad_common(const char* what, int heads, int kv_heads, int head_dim, int pag
 // For measurements: up to how many CTAs split decode attention keeps three (instead of two) tiles in flight per warp.
 MIR_EXPORT void mir_decode_attention_set_deep_ring_ctas(long long ctas) { g_deep_ring_ctas = ctas; }
 
+
 // How many floats of scratch decode attention needs: partial outputs and (maximum, denominator) pairs.
 // Arguments that cannot be meant (negative, or so large that the product would leave 63 bits) give -1.
 MIR_EXPORT long long mir_decode_attention_scratch_floats(int rows, int heads, int head_dim, int num_partitions) {
@@ -712,7 +717,7 @@ MIR_EXPORT int mir_decode_attention_bf16(const void* q, long long q_stride, void
   if (rows == 0) return MIR_OK;
   if (bad_common("decode_attention", heads, kv_heads, head_dim, page_size, table_width, window)) return MIR_BAD_ARGUMENT;
   if (rows < 0 || rows > 65535 || partition <= 0 || partition % 64 || partition > kDecodeMaxPartition ||
-      num_partitions <= 0) {
+      num_partitions <= 0 || num_partitions > 65535) {
     mir_set_error("decode_attention: bad rows %d, partition %d or partition count %d", rows, partition, num_partitions);
     return MIR_BAD_ARGUMENT;
   }

@@ -101,24 +101,31 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
       const uint32_t stage_bytes = weight_bytes + (uint32_t)tokens * 128u;
-      bool waited = false;
-      for (int i = 0; i < my_steps; ++i) {
+      auto load_weights = [&](int i, uint32_t barrier, uint32_t dst) {
+        const int k0 = (step_begin + i) * kStepK;
+        barrier_expect_bytes(barrier, stage_bytes);
+        tma_load_2d(dst, &w_map, barrier, k0, n0);
+        if (MODE == SWIGLU) tma_load_2d(dst + kWeightBytes / 2, &w_map, barrier, k0, up_offset + n0);
+      };
+      // The weights belong to no kernel: the whole ring is filled with them before this kernel waits for the one
+      // before it, whose results are only the activations.  Launched with programmatic stream serialization, the
+      // CTA becomes resident while that kernel still runs (if its CTAs leave the shared memory), and its first
+      // products can start the moment the activations exist.
+      const int ahead = min(stages, my_steps);
+      for (int i = 0; i < ahead; ++i)
+        load_weights(i, full0 + 8 * i, smem_base + (uint32_t)i * (uint32_t)stage_stride);
+      grid_dependency_wait();
+      for (int i = 0; i < ahead; ++i)
+        tma_load_2d(smem_base + (uint32_t)i * (uint32_t)stage_stride + weight_bytes, &x_map, full0 + 8 * i,
+                    (step_begin + i) * kStepK, 0);
+      for (int i = ahead; i < my_steps; ++i) {
         const int stage = i % stages;
         const uint32_t parity = (uint32_t)(i / stages) & 1u;
         if (!wait_barrier(empty0 + 8 * stage, parity ^ 1u)) { g_tc_stream_error = 1; break; }
         const uint32_t barrier = full0 + 8 * stage;
         const uint32_t dst = smem_base + (uint32_t)stage * (uint32_t)stage_stride;
-        const int k0 = (step_begin + i) * kStepK;
-        barrier_expect_bytes(barrier, stage_bytes);
-        if (MODE == SWIGLU) {
-          tma_load_2d(dst, &w_map, barrier, k0, n0);
-          tma_load_2d(dst + kWeightBytes / 2, &w_map, barrier, k0, up_offset + n0);
-        } else {
-          tma_load_2d(dst, &w_map, barrier, k0, n0);
-        }
-        // the weights belong to no kernel; the activations come from the kernel before this one
-        if (!waited) { grid_dependency_wait(); waited = true; }
-        tma_load_2d(dst + weight_bytes, &x_map, barrier, k0, 0);
+        load_weights(i, barrier, dst);
+        tma_load_2d(dst + weight_bytes, &x_map, barrier, (step_begin + i) * kStepK, 0);
       }
     }
   } else if (warp == 1) {

@@ -10,9 +10,12 @@ sampled tokens back; `run_many` replays several steps without any host work in b
 libmir captures decode per bucket of rows {1, 2, 4, 5, 8, 10, 16, ...} and re-captures when split
 attention's partition counts change (cuda/src/engine/batch/mod.rs:18-32,108-131,
 cuda/src/backend/model/batch/capture.rs:26-54), and chains batch-1 decode on the device-resident token
-(cuda/src/backend/model/graph/mod.rs:54-100, session/mod.rs:152-160).  Here nothing is re-captured when
-contexts grow: kernels read lengths and tables from device memory, and a bucket is keyed by
-(rows, table width, ranked sampling).
+(cuda/src/backend/model/graph/mod.rs:54-100, session/mod.rs:152-160).  Here kernels read lengths and tables
+from device memory, and a bucket is keyed by (rows, table widths, ranked sampling): rows are rounded up to a
+power of two or one and a half times one (17 live requests run 24 rows, 33 run 40), table widths to the pages
+of the next 512 tokens, so that split attention launches about as many partitions as the longest context has
+and a graph is captured anew once per 512 generated tokens.  The least recently used graphs are dropped
+beyond MAX_GRAPHS.
 """
 
 from __future__ import annotations
@@ -28,11 +31,36 @@ from .context import GroupContext, StepContext
 LOG_STEPS = 512            # sampled tokens kept on the device between host reads
 
 
+MAX_GRAPHS = 32            # captured buckets kept per model
+WIDTH_STEP_TOKENS = 512    # table widths above this many tokens are rounded up to the pages of a multiple of it
+
+
 def _bucket(n: int, floor: int = 1) -> int:
     size = floor
     while size < n:
         size *= 2
     return size
+
+
+def row_bucket(rows: int) -> int:
+    """Rows of the captured batch for `rows` live requests: 1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 40, 48, 64, 96, ..."""
+    if 32 < rows <= 40:
+        return 40
+    size = 1
+    while size < rows:
+        if size + size // 2 >= rows and size >= 2:
+            return size + size // 2
+        size *= 2
+    return size
+
+
+def width_bucket(pages: int, page_size: int) -> int:
+    """Columns of the captured block table for requests of up to `pages` pages."""
+    tokens = pages * page_size
+    if tokens <= WIDTH_STEP_TOKENS:
+        return _bucket(pages, 8)
+    rounded = -(-tokens // WIDTH_STEP_TOKENS) * WIDTH_STEP_TOKENS
+    return -(-rounded // page_size)
 
 
 class DecodeGraph:
@@ -208,10 +236,12 @@ class DecodeGraphs:
         for g in range(len(self.runner.manager.groups)):
             need = max(-(-(seq.length + extra_tokens) // page) for seq in sequences)
             need = max(need, max(len(seq.tables[g]) for seq in sequences))
-            widths.append(_bucket(need, 8))
-        key = (_bucket(rows), tuple(widths), ranked)
-        graph = self.graphs.get(key)
+            widths.append(width_bucket(need, page))
+        key = (row_bucket(rows), tuple(widths), ranked)
+        graph = self.graphs.pop(key, None)
         if graph is None:
             graph = DecodeGraph(self.runner, key[0], widths, ranked)
-            self.graphs[key] = graph
+            while len(self.graphs) >= MAX_GRAPHS:
+                self.graphs.pop(next(iter(self.graphs)))        # the least recently used (dicts keep insertion order)
+        self.graphs[key] = graph                                # (re-inserted: the most recently used is last)
         return graph

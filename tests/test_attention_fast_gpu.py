@@ -54,7 +54,8 @@ def close(got, want, tol=2e-2):
 
 @pytest.mark.parametrize("heads,kv_heads,dim,page,window,partition", [
     (32, 8, 128, 16, None, 512), (32, 8, 128, 16, None, 64), (8, 8, 64, 8, None, 128), (16, 1, 128, 16, 300, 256),
-    (40, 2, 64, 4, None, 64), (6, 3, 128, 32, 70, 64), (4, 4, 128, 1, None, 192), (64, 8, 128, 16, None, 128)])
+    (40, 2, 64, 4, None, 64), (6, 3, 128, 32, 70, 64), (4, 4, 128, 1, None, 192), (64, 8, 128, 16, None, 128),
+    (8, 2, 128, 12, None, 256), (6, 2, 64, 2, 45, 128)])
 def test_decode_attention(heads, kv_heads, dim, page, window, partition):
     from libmir_b200 import kernels
     rng = np.random.default_rng(heads + dim)
@@ -194,7 +195,7 @@ def pool_after_poison(k_pool, v_pool, page):
 
 @pytest.mark.parametrize("kind,dim,page,window,length,portion", [
     ("decode", 128, 8, 1024, 2100, 1), ("decode", 64, 4, 200, 700, 1), ("decode", 128, 4, 70, 333, 1),
-    ("decode", 64, 16, 100, 1000, 1), ("prefill", 128, 16, 1024, 2106, 10), ("prefill", 64, 16, 1024, 2106, 10),
+    ("decode", 64, 16, 100, 1000, 1), ("decode", 128, 1, 40, 300, 1), ("prefill", 128, 16, 1024, 2106, 10), ("prefill", 64, 16, 1024, 2106, 10),
     ("prefill", 64, 8, 100, 700, 70), ("prefill", 128, 4, 130, 450, 3), ("prefill_tcgen05", 128, 16, 1024, 2106, 40)])
 def test_pages_that_a_window_has_released_are_never_read(kind, dim, page, window, length, portion):
     """The block table holds -1 for every page that lies wholly behind the window of the first query (what the cache
