@@ -155,7 +155,8 @@ def main() -> int:
     parser.add_argument("--deep-ring-ctas", type=int, default=None,
                         help="up to how many CTAs decode attention keeps three tiles in flight per warp")
     parser.add_argument("--set", action="append", default=[], metavar="NAME=VALUE",
-                        help="set a tuning constant of libmir_b200.kernels (an integer), e.g. DECODE_PARTITION_KEYS=512")
+                        help="set a tuning constant of libmir_b200.kernels or an option of the native product dispatch (an "
+                             "integer), e.g. DECODE_PARTITION_KEYS=512 or few_rows_max=16")
     parser.add_argument("--stream-shape", default=None, metavar="SPLITS,RING_KB,TILE_ROWS",
                         help="fix the shape of the weight-streaming product (0 = chosen by the launcher), e.g. 0,56,0")
     parser.add_argument("--no-fold-norm", action="store_true",
@@ -188,16 +189,22 @@ def main() -> int:
     from libmir_b200.sampling import RequestSampler
 
     if args.library_modes:
-        kernels.FEW_ROWS_MODES -= set(args.library_modes.split(","))
+        modes = kernels.get_option("few_rows_modes")
+        for name in args.library_modes.split(","):
+            modes &= ~(1 << ["store", "accum", "f32", "swiglu"].index(name))
+        kernels.set_option("few_rows_modes", modes)
     if args.pdl is not None:
         kernels.set_programmatic_launch(args.pdl)
     if args.no_fold_norm:
         kernels.FUSE_NORM_INTO_PRODUCT = False
     for item in args.set:
         name, _, value = item.partition("=")
-        if not hasattr(kernels, name):
-            parser.error(f"libmir_b200.kernels has no constant {name}")
-        setattr(kernels, name, int(value))
+        if hasattr(kernels, name):
+            setattr(kernels, name, int(value))
+        elif kernels.get_option(name) >= 0:
+            kernels.set_option(name, int(value))
+        else:
+            parser.error(f"libmir_b200.kernels has no constant or option {name}")
     if args.stream_shape:
         splits, ring_kb, tile_rows = (int(v) for v in args.stream_shape.split(","))
         lib = kernels.library("bf16")
@@ -234,8 +241,7 @@ def main() -> int:
     vocab = config["vocab_size"]
     for buffer in model.storage.buffers:                      # synthetic cache content
         buffer.normal_(0.0, 0.5)
-    kv_bytes_per_token = sum(len(g.entries) * 2 * g.requirement.kv_heads * g.requirement.head_dim * 2
-                             for g in model.cache.groups)
+    kv_bytes_per_token = sum(len(g.entries) * g.requirement.elements_per_token * 2 for g in model.cache.groups)
     weight_bytes = model.decoder.weight_bytes_per_step()
 
     def fill(batch):
@@ -269,14 +275,14 @@ def main() -> int:
                 out = model.decode_many(entries, samplers, warmup)
                 entries = [StepEntry(i, [int(t)], [0]) for i, t in zip(ids, out[-1].tolist())]
                 torch.cuda.synchronize()
-                launches = kernels.LAUNCHES
+                launches = kernels.launches()
                 start, stop = event_pair()
                 start.record()
                 model.decode_many(entries, samplers, steps)
                 stop.record()
                 torch.cuda.synchronize()
                 regions.append(start.elapsed_time(stop) / steps)
-                launches = kernels.LAUNCHES - launches
+                launches = kernels.launches() - launches
                 release(ids)
         ms_per_step = statistics.median(regions)
         context = prompt_tokens + warmup + steps / 2.0

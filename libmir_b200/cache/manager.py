@@ -191,6 +191,7 @@ class CacheManager:
             "live_requests": len(self.live),
             "free_slots": len(self._free_slots),
             "groups": [{"window": g.window, "kv_heads": g.requirement.kv_heads, "head_dim": g.requirement.head_dim,
+                        "value_head_dim": g.requirement.value_dim,
                         "entries": len(g.entries), "pages": g.pool.count, "free": g.pool.free,
                         "high_water": g.pool.high_water, "reused": g.pool.reused} for g in self.groups],
         }

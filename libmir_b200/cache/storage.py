@@ -1,8 +1,9 @@
 """Device memory behind the cache manager's ids.
 
-Per group ONE allocation [entries, 2 (key, value), pages * page_size, kv_heads, head_dim] in the
-engine's dtype, so a page id is the same offset in every layer run of the group (libmir keeps one K
-and one V buffer per layer, cuda/src/backend/kv/storage/mod.rs:47-89; token-major NHD layout as there).
+Per group one allocation for the keys, [entries, pages * page_size, kv_heads, head_dim], and one for the
+values, [entries, pages * page_size, kv_heads, value_dim], in the engine's dtype, so a page id is the same
+offset in every layer run of the group (libmir keeps one K and one V buffer per layer with widths of their
+own, cuda/src/backend/kv/storage/mod.rs:17-25,47-89; token-major NHD layout as there).
 Per schedule entry with fixed-size state: [max_requests, *shape], one record per request slot.
 """
 
@@ -33,11 +34,15 @@ class CacheView:
 class CacheStorage:
     def __init__(self, manager: CacheManager, plan, dtype: torch.dtype, device: torch.device):
         self.manager = manager
-        self.buffers = []
+        self.key_buffers, self.value_buffers = [], []
         for group in manager.groups:
             r = group.requirement
-            shape = (len(group.entries), 2, group.pool.count * manager.page_size, r.kv_heads, r.head_dim)
-            self.buffers.append(torch.zeros(shape, dtype=dtype, device=device))
+            rows = group.pool.count * manager.page_size
+            self.key_buffers.append(torch.zeros((len(group.entries), rows, r.kv_heads, r.head_dim), dtype=dtype,
+                                                device=device))
+            self.value_buffers.append(torch.zeros((len(group.entries), rows, r.kv_heads, r.value_dim), dtype=dtype,
+                                                  device=device))
+        self.buffers = self.key_buffers + self.value_buffers
         self.states: Dict[int, torch.Tensor] = {}
         for entry, requirement in manager.state_entries.items():
             self.states[entry] = torch.zeros((manager.max_requests, *requirement.shape),
@@ -49,8 +54,8 @@ class CacheStorage:
                 group = manager.entry_group[item.entry]
                 local = manager.entry_local[item.entry]
                 view.group = group
-                view.k_pages = self.buffers[group][local, 0]
-                view.v_pages = self.buffers[group][local, 1]
+                view.k_pages = self.key_buffers[group][local]
+                view.v_pages = self.value_buffers[group][local]
                 view.page_size = manager.page_size
             if item.source in self.states:
                 view.state = self.states[item.source]

@@ -55,11 +55,23 @@ class ParamSpec:
 # --------------------------------------------------------------------------- cache needs
 @dataclass(frozen=True)
 class PagedKv:
-    """Keys and values of every token in pages; with a window only the last `window` are kept."""
+    """Keys and values of every token in pages; with a window only the last `window` are kept.  Keys are
+    `head_dim` wide; values too unless `value_head_dim` says otherwise (libmir's KvStorageSpec has both widths,
+    cuda/src/backend/kv/storage/mod.rs:17-25)."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.value_head_dim is None else self.value_head_dim
+
+    @property
+    def elements_per_token(self) -> int:
+        """Cached elements per token and schedule entry: keys and values of every kv head."""
+        return self.kv_heads * (self.head_dim + self.value_dim)
 
 
 @dataclass(frozen=True)

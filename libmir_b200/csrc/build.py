@@ -2,8 +2,9 @@
 
 There are two libraries so that a run compiles only what its model needs:
   core   kernels of both engine dtypes (norms, rotary + cache write, reference attention, 32-bit
-         matrix product, sampling)
-  bf16   what only the bfloat16 engine uses (tensor-core attention, cuBLASLt and tcgen05 products)
+         matrix product, sampling) and the layer executor for the float32 engine
+  bf16   the same, and what only the bfloat16 engine uses (tensor-core attention, cuBLASLt and tcgen05
+         products, the choice between them), with the layer executor for both engine dtypes
 A library is rebuilt when the hash of its sources and flags changes.  Objects are compiled in
 parallel, and a line is printed for each so that a first call shows progress.  The libraries are
 written beside the package (libmir_b200/_lib) when that folder can be written, else under the
@@ -32,16 +33,21 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xc
 LIBRARIES = {
     "core": {
         "sources": ["runtime.cu", "elementwise.cu", "qk_rope_store.cu", "attention_generic.cu", "gemm_f32.cu",
-                    "sampling.cu"],
+                    "sampling.cu", "executor.cu"],
         "link": [],
+        "defines": [],
     },
+    # everything of `core` as well: the layer executor of this library runs both engine dtypes
     "bf16": {
-        "sources": ["runtime.cu", "gemm_lt.cu", "attention_mma.cu", "gemm_tc.cu", "attention_tc.cu", "gemm_tc_stream.cu"],
+        "sources": ["runtime.cu", "elementwise.cu", "qk_rope_store.cu", "attention_generic.cu", "gemm_f32.cu",
+                    "gemm_lt.cu", "attention_mma.cu", "gemm_tc.cu", "attention_tc.cu", "gemm_tc_stream.cu",
+                    "ops_bf16.cu", "executor.cu"],
         "headers": ["no_alloc.h", "tcgen05.cuh"],
         "link": ["-lcublasLt"],
+        "defines": ["-DMIR_WITH_BF16"],
     },
 }
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "launchers.h"]
 
 
 def _nvcc() -> str:
@@ -58,7 +64,7 @@ def _digest(name: str) -> str:
     for rel in spec["sources"] + HEADERS + spec.get("headers", []):
         h.update(rel.encode())
         h.update((HERE / rel).read_bytes())
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + spec["link"]).encode())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + spec["link"] + spec.get("defines", [])).encode())
     return h.hexdigest()[:16]
 
 
@@ -113,7 +119,8 @@ def build(name: str, verbose: bool = True, force: bool = False) -> Path:
     def compile_one(rel: str) -> Path:
         obj = work / (Path(rel).stem + ".o")
         t0 = time.time()
-        command = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", str(HERE), "-c", str(HERE / rel), "-o", str(obj)]
+        command = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *spec.get("defines", []), "-I", str(HERE), "-c", str(HERE / rel),
+                   "-o", str(obj)]
         done = subprocess.run(command, capture_output=True, text=True)
         if done.returncode != 0:
             raise KernelError(f"nvcc failed on {rel}:\n{done.stdout}\n{done.stderr}")

@@ -147,7 +147,7 @@ class StepContext(PartContext):
         norm = self.upcoming_norm
         norm_weight = norm.weight if (norm is not None and norm.foldable) else None
         if (not kernels.FUSE_NORM_INTO_PRODUCT or norm_weight is None or self.dtype != torch.bfloat16
-                or residual.shape[0] > min(kernels.FOLDED_NORM_MAX_ROWS, kernels.FEW_ROWS_MAX)
+                or residual.shape[0] > kernels.few_rows_max()
                 or norm_weight.numel() != residual.shape[1]):
             kernels.linear(x, weight, residual, bias, accumulate=True)
             self.residual_stats = None

@@ -160,11 +160,11 @@ class DecodeGraph:
                 self._body()                       # builds library plans and grows the arena before capture
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize()
-        before = kernels.LAUNCHES
+        before = kernels.launches()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             self._body()
-        self.launches_per_replay = kernels.LAUNCHES - before
+        self.launches_per_replay = kernels.launches() - before
         self.graph = graph
         self.step_counter.zero_()
 
@@ -215,7 +215,7 @@ class DecodeGraph:
     def replay(self) -> None:
         self.graph.replay()
         self.replays += 1
-        kernels.LAUNCHES += self.launches_per_replay
+        kernels.REPLAYED_LAUNCHES += self.launches_per_replay
 
 
 class DecodeGraphs:

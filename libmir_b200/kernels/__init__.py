@@ -60,6 +60,13 @@ _SIGNATURES = {
                              c_void_p],
         "mir_gemm_tc_set_width": [c_int],
         "mir_gemm_tc_error": [],
+        "mir_linear_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_size_t, c_void_p,
+                            c_void_p],
+        "mir_gate_up_silu_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_float,
+                                  c_void_p, c_void_p, c_size_t, c_void_p],
+        "mir_set_option": [ctypes.c_char_p, c_int],
+        "mir_get_option": [ctypes.c_char_p],
         "mir_gemm_bf16_lt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_void_p, c_size_t, c_void_p],
     },
@@ -132,12 +139,33 @@ def loaded_libraries() -> dict:
 # leaves the sums of squares and the weighted rows, the product after it scales its results.  Two kernels fewer
 # per layer in a decode step.
 FUSE_NORM_INTO_PRODUCT = True
-LAUNCHES = 0        # kernels (and library matrix products) launched through this module, for reports
+# Whether layers of the built-in kind are run by the native executor (csrc/executor.cu), one call per run of such
+# layers; False runs every layer part by part from Python (the same kernels, launched from the interpreter).
+NATIVE_LAYERS = True
+REPLAYED_LAUNCHES = 0   # launches that ran as part of replayed CUDA graphs (a replay counts what its capture counted)
+
+
+def launches() -> int:
+    """Kernels and library products launched so far by this process's native libraries, replays of captured graphs
+    included (for reports)."""
+    return sum(launch_counts().values()) + REPLAYED_LAUNCHES
+
+
+MIR_CANNOT_FOLD = 4     # a product was given a folded norm's rows that it cannot take over (launchers.h)
+
+
+def set_option(name: str, value: int) -> None:
+    """A threshold of the bfloat16 product dispatch (csrc/ops_bf16.cu): few_rows_max, folded_norm_max_rows,
+    tensor_core_min_rows, few_rows_modes (bits: store, accumulate, float32, SwiGLU)."""
+    lib = library("bf16")
+    _check(lib, lib.mir_set_option(name.encode(), int(value)))
+
+
+def get_option(name: str) -> int:
+    return int(library("bf16").mir_get_option(name.encode()))
 
 
 def _check(lib: ctypes.CDLL, status: int) -> None:
-    global LAUNCHES
-    LAUNCHES += 1
     if status != 0:
         raise KernelError(lib.mir_last_error().decode(errors="replace") or f"kernel launch failed with status {status}")
 
@@ -336,8 +364,6 @@ def decode_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor
         block_table.shape[1], positions.data_ptr(), rows, page_size, heads, kv_heads, head_dim, scale,
         int(window or 0), partition, num_partitions, _ptr(scratch), 0 if scratch is None else scratch.numel(),
         _stream()))
-    global LAUNCHES
-    LAUNCHES += 1 if num_partitions > 1 else 0
 
 
 # Whether prompt portions run the tcgen05 attention kernel where it takes the sizes (head_dim 128, pages of 8 to
@@ -437,54 +463,58 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tens
            weighted_out: Optional[tuple] = None) -> bool:
     """out = (out if accumulate) + x . weight^T (+ bias).
 
-    float32 tensors: the 32-bit FMA kernel.  bfloat16 x and weight: up to FEW_ROWS_MAX (32) rows run the weight-streaming
-    kernel, more run cuBLASLt, both with 32-bit accumulation; out is bfloat16 or float32.  x and out may be
-    row-strided views; weight is [out_features, in_features].  x may be a NormedResidual (then `alloc` must be
-    given in case it has to be materialised).  With `sumsq_out` (float32 [ceil(N / 16), NORM_STAT_STRIDE]) an accumulating
-    few-rows product also writes the sums of squares of the rows it updates, and with
-    `weighted_out` = (bfloat16 [M, N], float32 norm weight [N]) those rows times the weight; the return value
-    says whether it did."""
+    float32 tensors: the 32-bit FMA kernel.  bfloat16 x and weight: the native dispatch (csrc/ops_bf16.cu) runs up
+    to few_rows_max (32) rows on the weight-streaming kernel and more on cuBLASLt, both with 32-bit accumulation;
+    out is bfloat16 or float32.  x and out may be row-strided views; weight is [out_features, in_features].  x may
+    be a NormedResidual (then `alloc` must be given in case it has to be materialised).  With `sumsq_out` (float32
+    [ceil(N / 16), NORM_STAT_STRIDE]) and `weighted_out` = (bfloat16 [M, N], float32 norm weight [N]) an
+    accumulating few-rows product also writes the sums of squares of the rows it updates and those rows times the
+    weight; the return value says whether it did."""
     lazy = x if isinstance(x, NormedResidual) else None
-    if lazy is not None:
-        m, k = lazy.shape
-        xw = lazy.weighted
-        if (weight.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and not accumulate
-                and "store" in FEW_ROWS_MODES and _few_rows_ok(xw, m, k)):
-            stream_linear(xw, weight, out, bias, folded=lazy)
-            return False
-        x = lazy.materialize(alloc)
-    _cuda(x, weight, out, bias)
-    m, k = x.shape
+    rows = lazy.weighted if lazy is not None else x
+    _cuda(rows, weight, out, bias)
+    m, k = rows.shape
     n = weight.shape[0]
-    _require(weight.shape[1] == k and out.shape == (m, n) and x.stride(1) == 1 and out.stride(1) == 1
+    _require(weight.shape[1] == k and out.shape == (m, n) and rows.stride(1) == 1 and out.stride(1) == 1
              and weight.is_contiguous(), "linear: shapes or strides do not fit")
-    beta = 1.0 if accumulate else 0.0
-    if x.dtype == torch.float32:
+    if rows.dtype == torch.float32:
         _require(weight.dtype == torch.float32 and out.dtype == torch.float32
                  and (bias is None or bias.dtype == torch.float32), "linear: float32 takes float32 everywhere")
         lib = library("core")
         _check(lib, lib.mir_gemm_f32(x.data_ptr(), x.stride(0), weight.data_ptr(), k, _ptr(bias), out.data_ptr(),
-                                     out.stride(0), m, n, k, beta, _stream()))
+                                     out.stride(0), m, n, k, 1.0 if accumulate else 0.0, _stream()))
         return False
-    _require(x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16, "linear: x and weight must share a dtype")
+    _require(rows.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16, "linear: x and weight must share a dtype")
+    _require(out.dtype == torch.float32 or not accumulate, "linear: only a float32 output accumulates")
     if bias is not None and bias.dtype != out.dtype:
         _require(out.dtype == torch.float32 and accumulate, "linear: bias dtype must match out")
         add_bias(out, bias)
         bias = None
+    stats, weighted, next_weight = None, None, None
+    if sumsq_out is not None and weighted_out is not None and sumsq_out.numel() >= sumsq_tiles(n) * NORM_STAT_STRIDE:
+        stats, (weighted, next_weight) = sumsq_out, weighted_out
+        _cuda(stats, weighted, next_weight)
+        _require(stats.dtype == torch.float32 and weighted.dtype == torch.bfloat16 and weighted.shape == (m, n)
+                 and weighted.stride(1) == 1 and next_weight.dtype == torch.float32 and next_weight.numel() == n
+                 and next_weight.is_contiguous(), "linear: weighted rows are bfloat16 [M, N], the weight float32 [N]")
     lib = library("bf16")
-    mode_name = "store" if out.dtype == torch.bfloat16 else ("accum" if accumulate else "f32")
-    if _few_rows_ok(x, m, k) and (out.dtype == torch.float32 or not accumulate) and mode_name in FEW_ROWS_MODES:
-        stats = sumsq_out if (mode_name == "accum" and sumsq_out is not None and m <= FOLDED_NORM_MAX_ROWS
-                              and sumsq_out.numel() >= sumsq_tiles(n) * NORM_STAT_STRIDE) else None
-        rows, next_weight = weighted_out if (stats is not None and weighted_out is not None) else (None, None)
-        stream_linear(x, weight, out, bias, accumulate=accumulate, sumsq_out=stats,
-                      weighted_out=(rows, next_weight) if rows is not None else None)
-        return stats is not None
-    workspace = _lt_workspace(x.device)
-    _check(lib, lib.mir_gemm_bf16_lt(x.data_ptr(), x.stride(0), weight.data_ptr(), k, _ptr(bias), out.data_ptr(),
-                                     out.stride(0), int(out.dtype == torch.float32), m, n, k, beta,
-                                     workspace.data_ptr(), workspace.numel(), _stream()))
-    return False
+    workspace = _lt_workspace(rows.device)
+    wrote = c_int(0)
+
+    def call(source, folded):
+        return lib.mir_linear_bf16(
+            source.data_ptr(), source.stride(0), weight.data_ptr(), _ptr(bias), out.data_ptr(), out.stride(0),
+            int(out.dtype == torch.float32), int(accumulate), m, n, k,
+            folded.sumsq.data_ptr() if folded is not None else None, folded.tiles if folded is not None else 0,
+            folded.eps if folded is not None else 0.0, _ptr(stats), _ptr(next_weight), _ptr(weighted),
+            weighted.stride(0) if weighted is not None else 0, workspace.data_ptr(), workspace.numel(), _stream(),
+            ctypes.addressof(wrote))
+
+    status = call(rows, lazy)
+    if status == MIR_CANNOT_FOLD and lazy is not None:
+        status = call(lazy.materialize(alloc), None)
+    _check(lib, status)
+    return bool(wrote.value)
 
 
 def tensor_core_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
@@ -511,16 +541,6 @@ def tensor_core_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
         mode = MODE_STORE if out.dtype == torch.bfloat16 else (MODE_ACCUM if accumulate else MODE_F32)
     _check(lib, lib.mir_gemm_tc_bf16(mode, x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias), out.data_ptr(),
                                      out.stride(0), m, n, k, up_offset, _stream()))
-
-
-# From how many rows the tcgen05 kernel computes the gated feed-forward product.  Measured on B200 at K 2,560,
-# I 9,728: 2,048 rows 153 us against 175 us for the library product and the SiLU-multiply kernel, 512 rows 55
-# against 59, 128 rows 26 against 37, 32 rows 25 against 26.
-TENSOR_CORE_MIN_ROWS = 128
-
-
-def _tensor_core_ok(x: torch.Tensor, k: int) -> bool:
-    return k % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and x.stride(1) == 1
 
 
 def stream_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -575,55 +595,51 @@ def tensor_core_linear_error() -> int:
 
 
 NORM_STAT_STRIDE = 32        # tokens per row of the sums-of-squares arrays (kNormStatStride of the kernels)
-FOLDED_NORM_MAX_ROWS = 32    # up to how many rows the streaming kernel writes and reads what a folded norm needs
-# Up to how many rows a product runs the weight-streaming kernel rather than the library.  The kernel takes up to
-# 128; measured alone at 64 rows it loses to cuBLASLt (12.2 / 8.5, 17.0 / 15.2, 14.9 / 8.2 us), and at 17 to 32
-# rows it is about as fast, but there it also takes over the two RMSNorms of a layer and the SwiGLU, which the
-# library path runs as kernels of their own: decode steps at Qwen3-4B sizes, library / streaming: batch 17 3.76 /
-# 3.56 ms, batch 24 4.11 / 3.91 ms, batch 32 4.50 / 4.31 ms; batch 64 6.27 / 6.65 ms.
-FEW_ROWS_MAX = 32
-FEW_ROWS_MODES = {"store", "accum", "f32", "swiglu"}     # the streaming epilogues in use; the rest go to the library
 MODE_STORE, MODE_ACCUM, MODE_F32, MODE_SWIGLU = 0, 1, 2, 3
 
 
-def _few_rows_ok(x: torch.Tensor, m: int, k: int) -> bool:
-    """Whether the weight-streaming kernel takes this product: up to FEW_ROWS_MAX rows, 16-byte aligned rows of
-    8-element multiples."""
-    return (0 < m <= min(FEW_ROWS_MAX, STREAM_MAX_ROWS) and k % 8 == 0 and x.stride(0) % 8 == 0
-            and x.data_ptr() % 16 == 0)
+def few_rows_max() -> int:
+    """Up to how many rows products run the weight-streaming kernel, which can also take over RMSNorms."""
+    return min(get_option("few_rows_max"), get_option("folded_norm_max_rows"), STREAM_MAX_ROWS)
 
 
 def gate_up_silu(x, w_gate_up: torch.Tensor, out: torch.Tensor, scratch_alloc) -> None:
     """out[M, I] = silu(x w_gate^T) * (x w_up^T) with w_gate_up = [w_gate; w_up] of shape [2 I, K].
 
-    Up to FEW_ROWS_MAX (32) bfloat16 rows (the weight-streaming kernel; x may be a NormedResidual, a norm folded into this
-    product) and from TENSOR_CORE_MIN_ROWS bfloat16 rows (the tcgen05 kernel): one kernel, the [M, 2 I] intermediate is never written.
-    Otherwise the product (library or 32-bit kernel) followed by the SiLU-multiply kernel;
-    `scratch_alloc(shape, dtype)` provides the intermediate."""
+    bfloat16: the native dispatch (csrc/ops_bf16.cu) runs up to few_rows_max (32) rows on the weight-streaming
+    kernel (x may be a NormedResidual, a norm folded into this product) and from tensor_core_min_rows (128) rows on
+    the tcgen05 many-rows kernel, one kernel each, the [M, 2 I] intermediate never written; between them the library
+    product followed by the SiLU-multiply kernel.  float32: the 32-bit product and that kernel.
+    `scratch_alloc(shape, dtype)` provides the intermediate where one is needed."""
     lazy = x if isinstance(x, NormedResidual) else None
-    m, k = x.shape
+    rows = lazy.weighted if lazy is not None else x
+    m, k = rows.shape
     inter = out.shape[1]
+    _cuda(rows, w_gate_up, out)
     _require(w_gate_up.shape == (2 * inter, k) and out.shape[0] == m and out.is_contiguous()
-             and w_gate_up.is_contiguous(), "gate_up_silu: shapes do not fit")
-    few = (w_gate_up.dtype == torch.bfloat16 and 0 < m <= min(FEW_ROWS_MAX, STREAM_MAX_ROWS) and k % 8 == 0
-           and "swiglu" in FEW_ROWS_MODES)
-    if lazy is not None:
-        if few and _few_rows_ok(lazy.weighted, m, k):
-            stream_linear(lazy.weighted, w_gate_up, out, swiglu=True, folded=lazy)
-            return
-        x = lazy.materialize(scratch_alloc)
-    _cuda(x, w_gate_up, out)
-    _require(x.stride(1) == 1, "gate_up_silu: x rows must be contiguous")
-    if few and x.dtype == torch.bfloat16 and _few_rows_ok(x, m, k):
-        stream_linear(x, w_gate_up, out, swiglu=True)
+             and w_gate_up.is_contiguous() and rows.stride(1) == 1, "gate_up_silu: shapes do not fit")
+    if rows.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16:
+        gate_up = scratch_alloc((m, 2 * inter), rows.dtype)
+        linear(x, w_gate_up, gate_up)
+        silu_mul(gate_up, out)
         return
-    if (x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and m >= TENSOR_CORE_MIN_ROWS
-            and _tensor_core_ok(x, k)):
-        tensor_core_linear(x, w_gate_up, out, swiglu=True)
-        return
-    gate_up = scratch_alloc((m, 2 * inter), x.dtype)
-    linear(x, w_gate_up, gate_up)
-    silu_mul(gate_up, out)
+    _require(out.dtype == torch.bfloat16, "gate_up_silu: bfloat16 rows give a bfloat16 result")
+    lib = library("bf16")
+    workspace = _lt_workspace(rows.device)
+    needs_scratch = get_option("few_rows_max") < m < get_option("tensor_core_min_rows") or k % 8 != 0 \
+        or rows.stride(0) % 8 != 0 or rows.data_ptr() % 16 != 0
+
+    def call(source, folded):
+        scratch = scratch_alloc((m, 2 * inter), torch.bfloat16) if needs_scratch else None
+        return lib.mir_gate_up_silu_bf16(
+            source.data_ptr(), source.stride(0), w_gate_up.data_ptr(), out.data_ptr(), m, inter, k,
+            folded.sumsq.data_ptr() if folded is not None else None, folded.tiles if folded is not None else 0,
+            folded.eps if folded is not None else 0.0, _ptr(scratch), workspace.data_ptr(), workspace.numel(), _stream())
+
+    status = call(rows, lazy)
+    if status == MIR_CANNOT_FOLD and lazy is not None:
+        status = call(lazy.materialize(scratch_alloc), None)
+    _check(lib, status)
 
 
 # --------------------------------------------------------------------------- sampling

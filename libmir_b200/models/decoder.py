@@ -40,6 +40,7 @@ class DecoderModel:
         self.final_norm = build_part(spec.final_norm, env)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
+        self._runs_key, self._runs_list, self._native = None, [], {}
 
     # -- what the cache manager must provide ------------------------------------
     def cache_plan(self) -> List[CacheEntryPlan]:
@@ -87,6 +88,7 @@ class DecoderModel:
         if self.spec.head.tied:
             self.head = self.embedding
         self.head = self.head.contiguous()
+        self._runs_key = None                       # descriptors of the layers hold pointers to the old tensors
 
     def parts(self) -> List[Part]:
         out: List[Part] = []
@@ -115,12 +117,45 @@ class DecoderModel:
         spec = self.spec
         residual = ctx.alloc((ctx.num_tokens, spec.hidden_size), torch.float32)
         kernels.embed(self.embedding, ctx.tokens, residual, spec.embedding.multiplier)
-        for index, entry in enumerate(spec.schedule):
+        for run in self._runs(ctx):
+            if run.layers is not None:
+                run.execute(ctx, residual)
+                continue
+            index = run.first
+            entry = spec.schedule[index]
             # the norm that the next block in the schedule starts with: this block's last product may prepare it
             following = self.blocks[spec.schedule[index + 1].layer] if index + 1 < len(spec.schedule) else None
             ctx.norm_after_block = following.first_norm() if following is not None else None
+            if index + 1 < len(spec.schedule) and self._native.get(index + 1) is not None:
+                ctx.norm_after_block = None          # the executor that runs the next block starts from the residual
             self.blocks[entry.layer].forward(ctx, ctx.cache_view(index), residual)
         return residual
+
+    def _runs(self, ctx) -> list:
+        """The schedule cut into runs: consecutive entries whose blocks the native executor takes form one run (one
+        native call), every other entry runs part by part from Python.  Built once per cache storage, since the
+        descriptors hold pointers to its pages."""
+        key = id(ctx.views)
+        if self._runs_key == key:
+            return self._runs_list
+        from ..kernels.executor import LayerRun
+        self._native = {}
+        if kernels.NATIVE_LAYERS:
+            for index, entry in enumerate(self.spec.schedule):
+                self._native[index] = self.blocks[entry.layer].native_descriptor(ctx.cache_view(index))
+        runs, index = [], 0
+        while index < len(self.spec.schedule):
+            if self._native.get(index) is None:
+                runs.append(LayerRun(index, None, self.env.dtype))
+                index += 1
+                continue
+            last = index
+            while last + 1 < len(self.spec.schedule) and self._native.get(last + 1) is not None:
+                last += 1
+            runs.append(LayerRun(index, [self._native[i] for i in range(index, last + 1)], self.env.dtype))
+            index = last + 1
+        self._runs_key, self._runs_list = key, runs
+        return runs
 
     def logits(self, ctx, residual: torch.Tensor, rows: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """32-bit logits [len(rows), V] at the packed rows `rows` (an int32 device tensor)."""

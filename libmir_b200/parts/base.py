@@ -171,6 +171,11 @@ class Block(Part):
     def cache_requirement(self) -> CacheRequirement:
         return None
 
+    def native_descriptor(self, cache):
+        """What the native layer executor needs to run this block by itself (kernels.executor.LayerDesc), or None if
+        the block's parts run one by one from Python."""
+        return None
+
     def first_norm(self) -> Optional["Norm"]:
         """The norm this block applies to the incoming residual before anything else, or None: the block before
         it in the schedule may prepare it in its last product."""

@@ -326,3 +326,35 @@ def test_a_folder_with_fused_and_transposed_tensors_gives_the_same_logits(tmp_pa
         model.unload()
     assert np.array_equal(logits[0], logits[1])
     check(logits[0], plain_logits(plain_folder, ids), TOL["float32"], "against the plain implementation")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["C", "E", "F"])
+def test_native_executor_and_python_parts_launch_the_same_work(tmp_path, name, dtype, monkeypatch):
+    """The layer executor issues the launches that the parts issue when they run one by one from Python: the same
+    kernels on the same data in the same order, so the logits must be the same bits, for whole prompts, portions,
+    mixed steps and decoded tokens (folded norms included)."""
+    from libmir_b200 import StepEntry, kernels
+    config = ALL[name]
+    folder = make_folder(tmp_path, config, seed=31, dtype=dtype, sharpen=4.0)
+    rng = np.random.default_rng(31)
+    first, second = random_ids(rng, config["vocab_size"], 330), random_ids(rng, config["vocab_size"], 200)
+    results = []
+    for native in (True, False):
+        monkeypatch.setattr(kernels, "NATIVE_LAYERS", native)
+        counts_before = kernels.launch_counts()
+        model = load(folder, dtype, page_size=8, pages=128)
+        model.admit("a"); model.admit("b")
+        logits = [model.step([StepEntry("a", first[:150], [0, 149])]).logits.clone()]
+        logits.append(model.step([StepEntry("a", first[150:151], [0]), StepEntry("b", second[:140], [139])]).logits.clone())
+        logits.append(model.step([StepEntry("b", second[140:160], [19]), StepEntry("a", first[151:152], [0])]).logits.clone())
+        for offset in range(3):
+            logits.append(model.step([StepEntry("a", [first[152 + offset]], [0]),
+                                      StepEntry("b", [second[160 + offset]], [0])]).logits.clone())
+        logits.append(model.step([StepEntry("a", first[155:330], [174])]).logits.clone())
+        results.append(torch.cat(logits).cpu())
+        assert any(isinstance(run.layers, list) for run in model.decoder._runs_list) == native
+        model.unload()
+    assert torch.equal(results[0], results[1])
+    reference = plain_logits(folder, first)
+    check(results[0][-1].numpy(), reference[329], TOL[dtype], "against the plain implementation")
