@@ -12,8 +12,11 @@
 // The uniform draw in [0, 1) comes from the host's SplitMix64, one per row and step, as in libmir
 // (src/generation/sampling.rs:36-41).  Non-finite logits are not candidates.
 //
-// The ranked mode sorts 64-bit keys (orderable(score) << 32 | ~id) with a bitonic network in a
-// scratch buffer of rows * pow2ceil(vocab) keys that the caller provides.
+// Keys are 64 bits, orderable(score) << 32 | ~id, so that one comparison orders by score and then by lower id
+// (libmir's tie rule).  The ranked mode first looks at the 1,024 best tokens, found by counting (libmir looks at
+// chunks of candidates and merges them, cuda/kernels/sampling_bf16.cu:30-133, with top_k capped at 64); only a
+// draw that they cannot decide sorts the whole vocabulary, in a scratch buffer of rows * pow2ceil(vocab) keys
+// that the caller provides.
 #include <cfloat>
 #include <cooperative_groups.h>
 #include "common.cuh"
@@ -119,6 +122,50 @@ __device__ __forceinline__ float from_orderable(unsigned key) {
   return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
 }
 
+// Inclusive sum over the block of one double per thread (thread order); every thread gets its own inclusive value,
+// *total (shared) the sum of all.  scratch: 32 doubles.
+__device__ double block_scan_f64(double v, double* scratch, double* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const double other = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += other;
+  }
+  __syncthreads();
+  if (lane == 31) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    double w = scratch[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const double other = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += other;
+    }
+    scratch[lane] = w;
+    if (lane == 31) *total = w;
+  }
+  __syncthreads();
+  return v + (warp > 0 ? scratch[warp - 1] : 0.0);
+}
+
+constexpr int kCandidates = 1024;       // ranked sampling looks at this many best tokens first ...
+constexpr int kCandidateRoom = 2048;    // ... and takes up to this many when scores tie at the threshold
+constexpr int kBins = 4096;
+
+// One cluster of kSlices CTAs per row; slice s owns the ids [s, s + 1) * ceil(vocab / kSlices).
+//
+//   every mode  each slice finds its highest logit; slice 0 takes the best of them (ties to the lowest id, as one
+//               scan would).
+//   full        each thread sums the 64-bit weights of a contiguous chunk of its slice; prefix sums over threads and
+//               slices locate the chunk in which the cumulative weight (vocabulary order) reaches draw * total, and
+//               that thread walks its chunk.
+//   ranked      the kCandidates best tokens are found without sorting the vocabulary: three counting passes over
+//               the orderable scores (12 + 12 + 8 bits, histograms added up over the cluster) give the score that
+//               the kCandidates-th best token has; everything at or above it goes to slice 0, which sorts it
+//               (bitonic, shared memory) and takes prefix sums in rank order.  That decides the draw whenever the
+//               nucleus (top_p of the total weight of ALL tokens) or top_k ends inside the candidates.  When it
+//               does not (a flat distribution with top_p alone, or thousands of tied scores), slice 0 sorts the
+//               whole vocabulary in the caller's scratch as before: slow and exact.
 __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restrict__ logits, size_t ld, int vocab,
                                                            const SampleOptions* __restrict__ options,
                                                            unsigned long long* __restrict__ sort_keys, int padded,
@@ -128,20 +175,21 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
   __shared__ double s_sum[32];
   __shared__ double chunk_sums[kThreads];
   __shared__ int found;
+  __shared__ __align__(16) unsigned char overlay[kCandidateRoom * (sizeof(unsigned long long) + sizeof(double))];
+  __shared__ float slice_value;                    // this slice's best, then (slice 0) the row's best
+  __shared__ int slice_index;
+  __shared__ double slice_total;                   // sum of this slice's weights
+  __shared__ unsigned select_prefix, select_above; // slice 0: the threshold found so far; tokens strictly above it
+  __shared__ int candidate_count;                  // slice 0: candidates gathered
   grid_launch_dependents();
   grid_dependency_wait();
-  // A cluster of kSlices CTAs per row: each finds the highest logit of its slice of the vocabulary, the first CTA
-  // takes the best of them out of distributed shared memory (ties to the lowest id, as one scan would) and goes
-  // on alone if the row is not greedy.
-  __shared__ float slice_value;
-  __shared__ int slice_index;
   cg::cluster_group cluster = cg::this_cluster();
   const int row = blockIdx.x, slice = blockIdx.y;
   const SampleOptions opt = options[row];
   const float* l = logits + (size_t)row * ld;
 
   const int per_slice = (vocab + kSlices - 1) / kSlices;
-  const int slice_begin = slice * per_slice, slice_end = min(vocab, slice_begin + per_slice);
+  const int slice_begin = min(vocab, slice * per_slice), slice_end = min(vocab, slice_begin + per_slice);
   float best = -FLT_MAX;
   int best_index = 0x7fffffff;
   for (int i = slice_begin + threadIdx.x; i < slice_end; i += kThreads) {
@@ -151,36 +199,242 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
   block_argmax(best, best_index, s_value, s_index);
   if (threadIdx.x == 0) { slice_value = best; slice_index = best_index; }
   cluster.sync();
-  if (slice == 0) {
+  if (slice == 0 && threadIdx.x == 0) {
     for (int other = 1; other < kSlices; ++other) {
       const float v = *cluster.map_shared_rank(&slice_value, other);
       const int i = *cluster.map_shared_rank(&slice_index, other);
       if (v > best || (v == best && i < best_index)) { best = v; best_index = i; }
     }
+    if (best_index == 0x7fffffff) best_index = 0;   // no finite logit: the host reports it
   }
-  cluster.sync();                                   // the other CTAs keep their shared memory until it was read
-  if (slice != 0) return;
-  if (best_index == 0x7fffffff) best_index = 0;   // no finite logit: the host reports it
+  cluster.sync();                                   // slice 0 has read the slices' results ...
+  if (slice == 0 && threadIdx.x == 0) { slice_value = best; slice_index = best_index; }
+  cluster.sync();                                   // ... and published the row's
+  best = *cluster.map_shared_rank(&slice_value, 0);
+  best_index = *cluster.map_shared_rank(&slice_index, 0);
   if (is_greedy(opt)) {
-    if (threadIdx.x == 0) tokens[row] = best_index;
+    if (slice == 0 && threadIdx.x == 0) tokens[row] = best_index;
+    cluster.sync();                                 // nobody leaves while its shared memory may still be read
     return;
   }
   const double temperature = (double)opt.temperature;
+  auto weight = [&](int i) -> double {
+    const float v = l[i];
+    return isfinite(v) ? exp((double)(v - best) / temperature) : 0.0;
+  };
+
+  // every mode below needs the total weight: per thread a contiguous chunk of the slice, in vocabulary order
+  const int slice_len = slice_end - slice_begin;
+  const int chunk = (slice_len + kThreads - 1) / kThreads;
+  const int begin = min(slice_end, slice_begin + (int)threadIdx.x * chunk), end = min(slice_end, begin + chunk);
+  double mine = 0.0;
+  for (int i = begin; i < end; ++i) mine += weight(i);
+  const double inclusive = block_scan_f64(mine, s_sum, &slice_total);
+  cluster.sync();
+  double total = 0.0, before_slice = 0.0;
+  for (int other = 0; other < kSlices; ++other) {
+    const double t = *cluster.map_shared_rank(&slice_total, other);
+    if (other < slice) before_slice += t;
+    total += t;
+  }
 
   if (is_full(opt)) {
-    auto weight = [&](int i) -> double {
-      const float v = l[i];
-      return isfinite(v) ? exp((double)(v - best) / temperature) : 0.0;
-    };
-    double mine = 0.0;
-    for (int i = threadIdx.x; i < vocab; i += kThreads) mine += weight(i);
-    const double total = block_sum_f64(mine, s_sum);
-    const int token = first_reaching(weight, vocab, opt.draw * total, chunk_sums, &found, best_index);
-    if (threadIdx.x == 0) tokens[row] = token;
+    const double target = opt.draw * total;
+    if (slice == 0 && threadIdx.x == 0) tokens[row] = target <= 0.0 ? 0 : best_index;   // unless a chunk is found
+    cluster.sync();
+    const double before = before_slice + inclusive - mine;
+    if (target > 0.0 && end > begin && before < target && before + mine >= target) {
+      double remaining = target - before;
+      int hit = end - 1;
+      for (int i = begin; i < end; ++i) {
+        remaining -= weight(i);
+        if (remaining <= 0.0) { hit = i; break; }
+      }
+      tokens[row] = hit;
+    }
+    cluster.sync();
     return;
   }
 
-  // ranked: sort keys descending (score, then lower id first)
+  // ---- ranked: the score of the kCandidates-th best token, by counting
+  int* histogram = reinterpret_cast<int*>(overlay);                 // kBins counters (16 KB of the overlay)
+  unsigned prefix = 0u;                                             // the threshold's leading bits found so far
+  unsigned above = 0u;                                              // tokens whose score is above every threshold bucket
+  for (int pass = 0; pass < 3; ++pass) {
+    const int shift = pass == 0 ? 20 : (pass == 1 ? 8 : 0);
+    const int bins = pass == 2 ? 256 : kBins;
+    const unsigned fixed_mask = pass == 0 ? 0u : (pass == 1 ? 0xfff00000u : 0xffffff00u);
+    for (int i = threadIdx.x; i < kBins; i += kThreads) histogram[i] = 0;
+    __syncthreads();
+    for (int i = slice_begin + threadIdx.x; i < slice_end; i += kThreads) {
+      const float v = l[i];
+      if (!isfinite(v)) continue;
+      const unsigned key = orderable(v);
+      if ((key & fixed_mask) != prefix) continue;
+      // scores crowd into a few bins: the lanes of a warp that hit the same bin count once, through their first lane
+      const unsigned bin = (key >> shift) & (unsigned)(bins - 1);
+      const unsigned same = __match_any_sync(__activemask(), bin);
+      if ((int)(__ffs(same) - 1) == (int)(threadIdx.x & 31)) atomicAdd(&histogram[bin], __popc(same));
+    }
+    cluster.sync();
+    if (slice == 0) {
+      // add the slices' histograms up, then find from the top the bin in which the count reaches kCandidates
+      for (int i = threadIdx.x; i < bins; i += kThreads) {
+        int sum = 0;
+        for (int other = 0; other < kSlices; ++other) sum += cluster.map_shared_rank(histogram, other)[i];
+        reinterpret_cast<int*>(overlay + kBins * sizeof(int))[i] = sum;          // the cluster's histogram
+      }
+      __syncthreads();
+      {
+        // from the top bin down: thread t takes the bins [hi - 4 t - 3, hi - 4 t], a block-wide running sum finds the
+        // bin in which the count of tokens at or above it first reaches kCandidates
+        const int* all = reinterpret_cast<const int*>(overlay + kBins * sizeof(int));
+        const int per_thread = kBins / kThreads;                     // 4
+        int mine[kBins / kThreads];
+        int sum = 0;
+#pragma unroll
+        for (int j = 0; j < per_thread; ++j) {
+          const int bin = bins - 1 - ((int)threadIdx.x * per_thread + j);
+          mine[j] = bin >= 0 ? all[bin] : 0;
+          sum += mine[j];
+        }
+        __shared__ double all_bins;
+        const double upto = block_scan_f64((double)sum, s_sum, &all_bins);      // counts: exact in a double
+        unsigned running = above + (unsigned)(upto - (double)sum);              // tokens above this thread's bins
+        if (threadIdx.x == 0) { select_above = above + (unsigned)all_bins - (unsigned)all[0]; select_prefix = prefix; }
+        __syncthreads();
+        if (running < (unsigned)kCandidates && running + (unsigned)sum >= (unsigned)kCandidates) {
+#pragma unroll
+          for (int j = 0; j < per_thread; ++j) {
+            const int bin = bins - 1 - ((int)threadIdx.x * per_thread + j);
+            if (bin < 0) break;
+            if (running + (unsigned)mine[j] >= (unsigned)kCandidates) {
+              select_above = running;                                 // strictly above bin `bin`
+              select_prefix = prefix | ((unsigned)bin << shift);
+              break;
+            }
+            running += (unsigned)mine[j];
+          }
+        }
+        __syncthreads();
+      }
+    }
+    cluster.sync();                                                  // (slice 0 has read everyone's histogram)
+    prefix = *cluster.map_shared_rank(&select_prefix, 0);
+    above = *cluster.map_shared_rank(&select_above, 0);
+  }
+  // `prefix` is now the orderable score of the threshold: fewer than kCandidates tokens score above it.  Everything
+  // at or above it goes to slice 0 (if it has room: ties at the threshold may be many).
+  unsigned long long* candidates = reinterpret_cast<unsigned long long*>(overlay);
+  double* cumulative = reinterpret_cast<double*>(overlay + kCandidateRoom * sizeof(unsigned long long));
+  // each slice collects its own candidates first (behind the places slice 0 sorts in: the upper half of the overlay),
+  // then reserves a range in slice 0's list with one remote addition and copies them there
+  unsigned long long* local = reinterpret_cast<unsigned long long*>(cumulative);
+  __shared__ int local_count, remote_base;
+  if (threadIdx.x == 0) { candidate_count = 0; local_count = 0; }
+  for (int i = threadIdx.x; i < kCandidateRoom; i += kThreads) candidates[i] = 0ull;
+  __syncthreads();
+  for (int i0 = slice_begin; i0 < slice_end; i0 += kThreads) {
+    const int i = i0 + (int)threadIdx.x;
+    unsigned key = 0u;
+    bool take = false;
+    if (i < slice_end) {
+      const float v = l[i];
+      if (isfinite(v)) { key = orderable(v); take = key >= prefix; }
+    }
+    const unsigned takers = __ballot_sync(0xffffffffu, take);
+    if (takers == 0u) continue;
+    const int lane = threadIdx.x & 31;
+    int base = 0;
+    if (lane == 0) base = atomicAdd(&local_count, __popc(takers));
+    base = __shfl_sync(0xffffffffu, base, 0);
+    const int at = base + __popc(takers & ((1u << lane) - 1u));
+    if (take && at < kCandidateRoom) local[at] = ((unsigned long long)key << 32) | (unsigned)(~(unsigned)i);
+  }
+  cluster.sync();                                                    // slice 0's list is cleared, every local list is complete
+  if (threadIdx.x == 0) remote_base = atomicAdd(cluster.map_shared_rank(&candidate_count, 0), local_count);
+  __syncthreads();
+  {
+    unsigned long long* remote = cluster.map_shared_rank(candidates, 0);
+    const int count = min(local_count, kCandidateRoom);
+    for (int i = threadIdx.x; i < count; i += kThreads)
+      if (remote_base + i < kCandidateRoom) remote[remote_base + i] = local[i];
+  }
+  cluster.sync();
+  if (slice != 0) {
+    cluster.sync();                                                  // (slice 0 is done with everyone's memory)
+    return;
+  }
+  const int gathered = candidate_count;
+  int token = -1;
+  if (gathered <= kCandidateRoom) {
+    // sort the candidates descending (score, then lower id first); empty places hold 0 and sink to the end
+    for (int size = 2; size <= kCandidateRoom; size <<= 1) {
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        const int t = threadIdx.x;                                   // kCandidateRoom / 2 pairs, one per thread
+        const int low = 2 * t - (t & (stride - 1)), high = low + stride;
+        const bool descending = (low & size) == 0;
+        const unsigned long long a = candidates[low], b = candidates[high];
+        if ((a < b) == descending) { candidates[low] = b; candidates[high] = a; }
+        __syncthreads();
+      }
+    }
+    // prefix sums of the weights in rank order: two ranks per thread
+    double pair[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const unsigned long long key = candidates[2 * threadIdx.x + j];
+      pair[j] = key == 0ull ? 0.0 : exp((double)(from_orderable((unsigned)(key >> 32)) - best) / temperature);
+    }
+    __shared__ double candidates_total;
+    const double upto = block_scan_f64(pair[0] + pair[1], s_sum, &candidates_total);
+    cumulative[2 * threadIdx.x] = upto - pair[1];
+    cumulative[2 * threadIdx.x + 1] = upto;
+    __syncthreads();
+    // the first rank whose cumulative weight reaches `target`, among the first `count` ranks; -1 if none does
+    auto first_rank_reaching = [&](double target, int count) -> int {
+      if (threadIdx.x == 0) found = -1;
+      __syncthreads();
+      for (int j = 0; j < 2; ++j) {
+        const int rank = 2 * threadIdx.x + j;
+        if (rank < count && cumulative[rank] >= target && (rank == 0 || cumulative[rank - 1] < target)) found = rank;
+      }
+      __syncthreads();
+      const int result = found;
+      __syncthreads();
+      return result;
+    };
+    // Do the candidates decide the draw?  `everything`: no bin ever reached kCandidates, the threshold is the lowest
+    // score there is and the candidates are all the row's finite tokens.
+    const bool everything = prefix == 0u;
+    int keep_p = gathered;                                           // ranks the nucleus keeps, if it ends in here
+    bool beyond = !everything;                                       // ... or it ends beyond the candidates
+    if (opt.top_p < 1.0f) {
+      const double target = (double)opt.top_p * total;
+      const int rank = target <= 0.0 ? 0 : first_rank_reaching(target, gathered);
+      if (rank >= 0) { keep_p = rank + 1; beyond = false; }
+    }
+    int keep = -1;
+    if (!beyond) keep = opt.top_k > 0 ? min(keep_p, opt.top_k) : keep_p;
+    else if (opt.top_k > 0 && opt.top_k <= gathered) keep = opt.top_k;
+    if (gathered == 0) {
+      token = best_index;                                            // no finite logit
+    } else if (keep > 0) {
+      const double kept_total = cumulative[keep - 1];
+      const double target = opt.draw * kept_total;
+      int rank = target <= 0.0 ? 0 : first_rank_reaching(target, keep);
+      if (rank < 0) rank = keep - 1;
+      token = (int)(~(unsigned)(candidates[rank] & 0xffffffffull));
+    }
+  }
+  if (token >= 0) {
+    if (threadIdx.x == 0) tokens[row] = token;
+    cluster.sync();
+    return;
+  }
+  cluster.sync();                                                    // the other slices may leave
+
+  // ---- the whole vocabulary, sorted in the caller's scratch
   if (sort_keys == nullptr) {
     if (threadIdx.x == 0) tokens[row] = -1;   // the launcher refuses this before the launch
     return;
@@ -209,16 +463,13 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
     if (key == 0ull) return 0.0;
     return exp((double)(from_orderable((unsigned)(key >> 32)) - best) / temperature);
   };
-  double mine = 0.0;
-  for (int i = threadIdx.x; i < vocab; i += kThreads) mine += ranked_weight(i);
-  const double total = block_sum_f64(mine, s_sum);
   int keep = vocab;
   if (opt.top_p < 1.0f)
     keep = first_reaching(ranked_weight, vocab, (double)opt.top_p * total, chunk_sums, &found, vocab - 1) + 1;
   if (opt.top_k > 0) keep = min(keep, opt.top_k);
-  mine = 0.0;
-  for (int i = threadIdx.x; i < keep; i += kThreads) mine += ranked_weight(i);
-  const double kept_total = block_sum_f64(mine, s_sum);
+  double kept = 0.0;
+  for (int i = threadIdx.x; i < keep; i += kThreads) kept += ranked_weight(i);
+  const double kept_total = block_sum_f64(kept, s_sum);
   const int rank = first_reaching(ranked_weight, keep, opt.draw * kept_total, chunk_sums, &found, keep - 1);
   if (threadIdx.x == 0) tokens[row] = (int)(~(unsigned)(keys[rank] & 0xffffffffull));
 }

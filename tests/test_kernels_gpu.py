@@ -357,6 +357,30 @@ def test_sampling_picks_what_the_plain_sampler_picks(vocab):
         assert got == want
 
 
+def test_ranked_sampling_beyond_the_candidates_and_with_many_ties():
+    """Ranked sampling decides most draws from the 1,024 best tokens.  Rows made so that it cannot: a flat
+    distribution whose nucleus holds tens of thousands of tokens, thousands of tokens tied at the best score (the
+    tie goes by lower id), a top_k wider than the candidates, and rows with few or no finite logits; every draw
+    must still be the plain sampler's."""
+    vocab = 40000
+    rng = np.random.default_rng(3)
+    flat = rng.normal(0, 0.05, size=vocab).astype(np.float32)
+    tied = np.full(vocab, -2.0, dtype=np.float32)
+    tied[rng.choice(vocab, size=5000, replace=False)] = 1.5            # 5,000 tokens share the best score
+    peaked = rng.normal(0, 3.0, size=vocab).astype(np.float32)
+    sparse = np.full(vocab, -np.inf, dtype=np.float32)
+    sparse[[7, 39999, 1234]] = [0.5, 0.5, -1.0]                         # three finite logits, two of them tied
+    rows = [flat, flat, tied, tied, tied, peaked, peaked, sparse, sparse]
+    modes = [(1.0, 0, 0.9), (0.8, 30000, 0.999), (1.0, 0, 0.5), (0.7, 4000, 1.0), (1.0, 3, 0.9), (1.0, 3000, 1.0),
+             (5.0, 0, 0.97), (1.0, 0, 0.9), (0.7, 2, 1.0)]
+    logits = torch.from_numpy(np.stack(rows))
+    for draws in ([0.0] * len(rows), rng.random(len(rows)).tolist(), rng.random(len(rows)).tolist(), [0.999999] * len(rows)):
+        options = [(draw, t, k, p) for draw, (t, k, p) in zip(draws, modes)]
+        got = device_sample(logits, options)
+        want = [plain_impl.sample(logits[r].numpy(), draw, t, k, p) for r, (draw, t, k, p) in enumerate(options)]
+        assert got == want, (draws[0], got, want)
+
+
 def test_repetition_penalty_rewrites_the_rows_logits():
     from libmir_b200 import kernels
     logits = torch.tensor([[2.0, -1.0, 0.5, 3.0], [1.0, 1.0, -2.0, 0.0]])
