@@ -148,6 +148,181 @@ __device__ double block_scan_f64(double v, double* scratch, double* total) {
   return v + (warp > 0 ? scratch[warp - 1] : 0.0);
 }
 
+// Where, in rank order (score descending, then id ascending), the cumulative weight first reaches a target: the
+// orderable score at which it happens, the weight and the number of tokens that score higher, and how many tokens
+// share that score.  Found without sorting: three passes over the orderable scores (11 + 11 + 10 bits), each adding
+// the weights and the counts of the tokens that match the bits found so far into the bins of the next bits (the
+// lanes of a warp that hit the same bin add once, 64-bit sums), summed over the cluster by slice 0, which scans the
+// bins from the top.  If rounding lets no bin reach the target, the lowest score is the answer.
+struct Crossing {
+  unsigned key;          // orderable score of the rank at which the target is reached
+  unsigned above_count;  // tokens that score higher
+  unsigned ties;         // tokens with exactly this score
+  unsigned pad;
+  double above_weight;   // weight of the tokens that score higher
+};
+
+constexpr int kSearchBins = 2048;
+
+template <typename Weight>
+__device__ Crossing find_crossing(cg::cluster_group& cluster, const float* __restrict__ l, int slice, int slice_begin,
+                                  int slice_end, Weight weight, double target, unsigned char* overlay, double* s_sum,
+                                  Crossing* shared_result) {
+  int* counts = reinterpret_cast<int*>(overlay);                                  // kSearchBins
+  double* weights = reinterpret_cast<double*>(overlay + kSearchBins * sizeof(int));  // kSearchBins
+  unsigned prefix = 0u, above_count = 0u, ties = 0u;
+  double above_weight = 0.0;
+  const int lane = threadIdx.x & 31;
+  for (int pass = 0; pass < 3; ++pass) {
+    const int shift = pass == 0 ? 21 : (pass == 1 ? 10 : 0);
+    const int bins = pass == 2 ? 1024 : kSearchBins;
+    const unsigned fixed_mask = pass == 0 ? 0u : (pass == 1 ? 0xffe00000u : 0xfffffc00u);
+    for (int i = threadIdx.x; i < kSearchBins; i += kThreads) { counts[i] = 0; weights[i] = 0.0; }
+    __syncthreads();
+    for (int i0 = slice_begin; i0 < slice_end; i0 += kThreads) {
+      const int i = i0 + (int)threadIdx.x;
+      bool match = false;
+      unsigned bin = 0u;
+      double w = 0.0;
+      if (i < slice_end) {
+        const float v = l[i];
+        if (isfinite(v)) {
+          const unsigned key = orderable(v);
+          if ((key & fixed_mask) == prefix) { match = true; bin = (key >> shift) & (unsigned)(bins - 1); w = weight(i); }
+        }
+      }
+      unsigned todo = __ballot_sync(0xffffffffu, match);
+      while (todo != 0u) {                                     // one round per distinct bin among the warp's lanes
+        const int leader = __ffs(todo) - 1;
+        const unsigned leader_bin = __shfl_sync(0xffffffffu, bin, leader);
+        const unsigned group = __ballot_sync(0xffffffffu, match && bin == leader_bin) & todo;
+        double sum = (group >> lane) & 1u ? w : 0.0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == leader) {
+          atomicAdd(&counts[leader_bin], __popc(group));
+          atomicAdd(&weights[leader_bin], sum);
+        }
+        todo &= ~group;
+      }
+    }
+    cluster.sync();
+    if (slice == 0) {
+      for (int i = threadIdx.x; i < bins; i += kThreads) {
+        int count = counts[i];
+        double sum = weights[i];
+        for (int other = 1; other < kSlices; ++other) {
+          count += cluster.map_shared_rank(counts, other)[i];
+          sum += cluster.map_shared_rank(weights, other)[i];
+        }
+        counts[i] = count;
+        weights[i] = sum;
+      }
+      __syncthreads();
+      // from the top bin down, two bins per thread
+      constexpr int per_thread = kSearchBins / kThreads;
+      int my_counts[per_thread];
+      double my_weights[per_thread];
+      int count_sum = 0;
+      double weight_sum = 0.0;
+#pragma unroll
+      for (int j = 0; j < per_thread; ++j) {
+        const int b = bins - 1 - ((int)threadIdx.x * per_thread + j);
+        my_counts[j] = b >= 0 ? counts[b] : 0;
+        my_weights[j] = b >= 0 ? weights[b] : 0.0;
+        count_sum += my_counts[j];
+        weight_sum += my_weights[j];
+      }
+      __shared__ double scan_total;
+      __shared__ int lowest_bin;
+      const double weight_upto = block_scan_f64(weight_sum, s_sum, &scan_total);
+      const double count_upto = block_scan_f64((double)count_sum, s_sum, &scan_total);   // counts: exact in a double
+      if (threadIdx.x == 0) { lowest_bin = bins; shared_result->pad = 0u; }
+      __syncthreads();
+      for (int j = 0; j < per_thread; ++j) {                     // the lowest bin that holds a token: the answer if none reaches
+        const int b = bins - 1 - ((int)threadIdx.x * per_thread + j);
+        if (b >= 0 && my_counts[j] > 0) atomicMin(&lowest_bin, b);
+      }
+      __syncthreads();
+      double running_weight = above_weight + (weight_upto - weight_sum);
+      unsigned running_count = above_count + (unsigned)(count_upto - (double)count_sum);
+      const bool reaches = running_weight < target && running_weight + weight_sum >= target;
+      if (reaches) {
+        // the first of this thread's bins with which the running weight reaches the target (rounding may let the sum
+        // of the bins reach it and no single step: then the last bin that holds a token)
+        int chosen = -1, last_held = -1;
+        double weight_before = running_weight;
+        unsigned count_before = running_count;
+        for (int j = 0; j < per_thread && chosen < 0; ++j) {
+          if (my_counts[j] > 0) last_held = j;
+          if (my_counts[j] > 0 && running_weight + my_weights[j] >= target) {
+            chosen = j;
+            break;
+          }
+          running_weight += my_weights[j];
+          running_count += (unsigned)my_counts[j];
+        }
+        if (chosen < 0 && last_held >= 0) {
+          chosen = last_held;
+          running_weight = weight_before;
+          running_count = count_before;
+          for (int j = 0; j < chosen; ++j) { running_weight += my_weights[j]; running_count += (unsigned)my_counts[j]; }
+        }
+        if (chosen >= 0) {
+          const int b = bins - 1 - ((int)threadIdx.x * per_thread + chosen);
+          shared_result->key = prefix | ((unsigned)b << shift);
+          shared_result->above_count = running_count;
+          shared_result->above_weight = running_weight;
+          shared_result->ties = (unsigned)my_counts[chosen];
+          shared_result->pad = 1u;
+        }
+      }
+      __syncthreads();
+      if (shared_result->pad == 0u && threadIdx.x == 0) {        // nothing reached the target (or it is not positive)
+        const int b = target <= 0.0 ? -1 : lowest_bin;
+        int top = bins - 1;
+        while (top > 0 && counts[top] == 0) --top;                // target <= 0: the highest bin that holds a token
+        const int chosen = (b < 0 || b >= bins) ? top : b;
+        unsigned count_above = above_count;
+        double weight_above = above_weight;
+        for (int other = bins - 1; other > chosen; --other) { count_above += (unsigned)counts[other]; weight_above += weights[other]; }
+        shared_result->key = prefix | ((unsigned)chosen << shift);
+        shared_result->above_count = count_above;
+        shared_result->above_weight = weight_above;
+        shared_result->ties = (unsigned)counts[chosen];
+      }
+      __syncthreads();
+    }
+    cluster.sync();
+    const Crossing* result = cluster.map_shared_rank(shared_result, 0);
+    prefix = result->key;
+    above_count = result->above_count;
+    above_weight = result->above_weight;
+    ties = result->ties;
+    cluster.sync();                                               // read by everyone before the next pass rewrites it
+  }
+  Crossing out;
+  out.key = prefix;
+  out.above_count = above_count;
+  out.above_weight = above_weight;
+  out.ties = ties;
+  out.pad = 0u;
+  return out;
+}
+
+// How many of `ties` tokens of weight `each`, added one after the other to `above`, it takes to reach `target`
+// (at least 1, at most `ties`).
+__device__ unsigned ties_needed(double above, double each, unsigned ties, double target) {
+  if (ties <= 1u || !(each > 0.0)) return max(1u, min(ties, 1u));
+  double guess = ceil((target - above) / each);
+  if (!(guess >= 1.0)) guess = 1.0;
+  if (guess > (double)ties) guess = (double)ties;
+  unsigned count = (unsigned)guess;
+  while (count > 1u && above + (double)(count - 1u) * each >= target) --count;
+  while (count < ties && above + (double)count * each < target) ++count;
+  return count;
+}
+
 constexpr int kCandidates = 1024;       // ranked sampling looks at this many best tokens first ...
 constexpr int kCandidateRoom = 2048;    // ... and takes up to this many when scores tie at the threshold
 constexpr int kBins = 4096;
@@ -181,6 +356,8 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
   __shared__ double slice_total;                   // sum of this slice's weights
   __shared__ unsigned select_prefix, select_above; // slice 0: the threshold found so far; tokens strictly above it
   __shared__ int candidate_count;                  // slice 0: candidates gathered
+  __shared__ int search_mode;                      // slice 0: 0 the candidates decided, 1 the nucleus must be searched
+  __shared__ Crossing crossing;                    // slice 0: result of a pass of find_crossing
   grid_launch_dependents();
   grid_dependency_wait();
   cg::cluster_group cluster = cg::this_cluster();
@@ -361,13 +538,9 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
       if (remote_base + i < kCandidateRoom) remote[remote_base + i] = local[i];
   }
   cluster.sync();
-  if (slice != 0) {
-    cluster.sync();                                                  // (slice 0 is done with everyone's memory)
-    return;
-  }
-  const int gathered = candidate_count;
+  const int gathered = slice == 0 ? candidate_count : 0;
   int token = -1;
-  if (gathered <= kCandidateRoom) {
+  if (slice == 0 && gathered <= kCandidateRoom) {
     // sort the candidates descending (score, then lower id first); empty places hold 0 and sink to the end
     for (int size = 2; size <= kCandidateRoom; size <<= 1) {
       for (int stride = size >> 1; stride > 0; stride >>= 1) {
@@ -427,12 +600,55 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
       token = (int)(~(unsigned)(candidates[rank] & 0xffffffffull));
     }
   }
-  if (token >= 0) {
-    if (threadIdx.x == 0) tokens[row] = token;
-    cluster.sync();
-    return;
+  // The candidates decided (slice 0 knows), or the nucleus ends beyond them and is searched for by the whole cluster;
+  // what then still cannot be decided (a top_k wider than the candidates that cuts the nucleus) is left to the sort.
+  if (slice == 0 && threadIdx.x == 0) {
+    search_mode = token >= 0 ? 0 : (opt.top_p < 1.0f ? 1 : 2);
+    if (token >= 0) tokens[row] = token;
   }
-  cluster.sync();                                                    // the other slices may leave
+  cluster.sync();
+  const int mode = *cluster.map_shared_rank(&search_mode, 0);
+  cluster.sync();                                                    // (read by everyone before slice 0 goes on)
+  if (mode == 0) return;
+  if (mode == 1) {
+    const Crossing edge = find_crossing(cluster, l, slice, slice_begin, slice_end, weight, (double)opt.top_p * total,
+                                        overlay, s_sum, &crossing);
+    const double edge_weight = exp((double)(from_orderable(edge.key) - best) / temperature);
+    const unsigned edge_ties = ties_needed(edge.above_weight, edge_weight, edge.ties, (double)opt.top_p * total);
+    const unsigned keep_p = edge.above_count + edge_ties;            // ranks the nucleus keeps
+    if (opt.top_k <= 0 || (unsigned)opt.top_k >= keep_p) {
+      const double kept_total = edge.above_weight + (double)edge_ties * edge_weight;
+      const double target = opt.draw * kept_total;
+      if (target <= 0.0) {
+        if (slice == 0 && threadIdx.x == 0) tokens[row] = best_index;   // rank 0: the best score, the lowest id
+        return;
+      }
+      const Crossing hit = find_crossing(cluster, l, slice, slice_begin, slice_end, weight, target, overlay, s_sum,
+                                         &crossing);
+      const double hit_weight = exp((double)(from_orderable(hit.key) - best) / temperature);
+      const unsigned nth = ties_needed(hit.above_weight, hit_weight, hit.ties, target);   // 1-based, in id order
+      // the nth token (ascending id) whose score is exactly hit.key: per thread a contiguous chunk of the slice
+      int held = 0;
+      for (int i = begin; i < end; ++i) {
+        const float v = l[i];
+        held += (isfinite(v) && orderable(v) == hit.key) ? 1 : 0;
+      }
+      const double held_upto = block_scan_f64((double)held, s_sum, &slice_total);    // counts: exact in a double
+      cluster.sync();
+      double held_before = held_upto - (double)held;
+      for (int other = 0; other < slice; ++other) held_before += *cluster.map_shared_rank(&slice_total, other);
+      if ((double)nth > held_before && (double)nth <= held_before + (double)held) {
+        unsigned remaining = nth - (unsigned)held_before;
+        for (int i = begin; i < end; ++i) {
+          const float v = l[i];
+          if (isfinite(v) && orderable(v) == hit.key && --remaining == 0u) { tokens[row] = i; break; }
+        }
+      }
+      cluster.sync();                                                // nobody leaves while its totals may still be read
+      return;
+    }
+  }
+  if (slice != 0) return;
 
   // ---- the whole vocabulary, sorted in the caller's scratch
   if (sort_keys == nullptr) {
