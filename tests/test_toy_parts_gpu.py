@@ -339,3 +339,113 @@ def test_toy_routed_feed_forward_and_other_position_encoding(tmp_path, dtype, to
     assert error <= tol * max(1.0, np.abs(want).max()), f"max |diff| {error:.3e}"
     without_wave = plain_routed_toy(weights, ids, wave_scale=0.0)[0]
     assert np.abs(want - without_wave).max() > 10 * tol * np.abs(want).max(), "the toy position encoding must matter"
+
+
+# ------------------------------------------------------------------------------ keys and values of different widths
+@dataclass(frozen=True)
+class NarrowKeySpec:
+    """Toy mixer: one-head softmax attention whose keys are `key_dim` wide and whose values are `value_dim` wide
+    (a compressed key beside a full value), both in pages of the cache."""
+
+    hidden_size: int = 0
+    key_dim: int = 8
+    value_dim: int = 24
+    kind: str = field(init=False, default="toy_narrow_key")
+
+
+def make_narrow_key_toy():
+    from libmir_b200 import register_architecture, register_part
+    from libmir_b200.config.spec import (EmbeddingSpec, HeadSpec, LayerSpec, ModelSpec, PagedKv, ParamSpec, RmsNormSpec,
+                                         ScheduleEntry, SwiGluSpec)
+    from libmir_b200.parts import Mixer
+
+    class NarrowKeyAttention(Mixer):
+        def parameters(self):
+            s = self.spec
+            return {"q.weight": ParamSpec((s.key_dim, s.hidden_size)), "k.weight": ParamSpec((s.key_dim, s.hidden_size)),
+                    "v.weight": ParamSpec((s.value_dim, s.hidden_size)), "o.weight": ParamSpec((s.hidden_size, s.value_dim))}
+
+        def bind(self, tensors):
+            self.w = {name.split(".")[0]: tensor.float() for name, tensor in tensors.items()}
+
+        def cache_requirement(self):
+            return PagedKv(kv_heads=1, head_dim=self.spec.key_dim, value_head_dim=self.spec.value_dim)
+
+        def forward(self, ctx, cache, x, residual):
+            x = x.float()
+            group = ctx.groups[cache.group]
+            slots = group.slot_mapping[:x.shape[0]].long()
+            cache.k_pages[slots, 0] = (x @ self.w["k"].T).to(cache.k_pages.dtype)
+            cache.v_pages[slots, 0] = (x @ self.w["v"].T).to(cache.v_pages.dtype)
+            queries = x @ self.w["q"].T
+            table = group.block_table.cpu()
+            page = cache.page_size
+            for row in range(ctx.num_rows):
+                begin, end = ctx.host_query_starts[row], ctx.host_query_starts[row + 1]
+                length = ctx.host_start_positions[row] + (end - begin)
+                rows = torch.cat([torch.arange(page) + int(table[row, block]) * page for block in range(-(-length // page))])
+                rows = rows[:length].to(x.device)
+                keys, values = cache.k_pages[rows, 0].float(), cache.v_pages[rows, 0].float()
+                scores = queries[begin:end] @ keys.T
+                positions = torch.arange(ctx.host_start_positions[row], length, device=x.device)
+                scores = scores.masked_fill(torch.arange(length, device=x.device)[None, :] > positions[:, None], float("-inf"))
+                residual[begin:end] += (torch.softmax(scores, dim=-1) @ values) @ self.w["o"].T
+
+    register_part("toy_narrow_key", NarrowKeyAttention)
+
+    def build(config, catalog):
+        hidden = config["hidden_size"]
+        norm = lambda: RmsNormSpec(size=hidden, eps=1e-5)
+        names = {"mixer_norm": "norm_a.", "mixer": "mixer.", "feed_forward_norm": "norm_b.", "feed_forward": "ff."}
+        layers = (LayerSpec("toy.layers.0.", NarrowKeySpec(hidden, config["key_dim"], config["value_dim"]),
+                            SwiGluSpec(hidden_size=hidden, intermediate_size=config["intermediate_size"]), norm(), norm(),
+                            names),)
+        return ModelSpec("ToyNarrowKeyForCausalLM", hidden, config["vocab_size"], 128,
+                         EmbeddingSpec("toy.embed.weight", config["vocab_size"], hidden), layers, (ScheduleEntry(0),),
+                         norm(), "toy.final_norm.", HeadSpec("toy.head.weight", config["vocab_size"], hidden, tied=True))
+
+    register_architecture("ToyNarrowKeyForCausalLM", build)
+
+
+NARROW_CONFIG = {"architectures": ["ToyNarrowKeyForCausalLM"], "hidden_size": 32, "intermediate_size": 40,
+                 "vocab_size": 50, "key_dim": 8, "value_dim": 24}
+
+
+def plain_narrow_key_toy(weights, ids):
+    w = {name: tensor.double() for name, tensor in weights.items()}
+    x = w["toy.embed.weight"][torch.tensor(ids)]
+    prefix = "toy.layers.0."
+    normed = plain_impl.rms_norm(x, w[prefix + "norm_a.weight"], 1e-5)
+    q, k, v = (normed @ w[prefix + f"mixer.{name}.weight"].T for name in "qkv")
+    scores = (q @ k.T).masked_fill(torch.triu(torch.ones(len(ids), len(ids), dtype=torch.bool), 1), float("-inf"))
+    x = x + (torch.softmax(scores, dim=-1) @ v) @ w[prefix + "mixer.o.weight"].T
+    x = x + plain_impl.swiglu(plain_impl.rms_norm(x, w[prefix + "norm_b.weight"], 1e-5), w, prefix + "ff.")
+    return plain_impl.linear(plain_impl.rms_norm(x, w["toy.final_norm.weight"], 1e-5), w["toy.embed.weight"]).numpy()
+
+
+def test_toy_mixer_with_keys_and_values_of_different_widths(tmp_path):
+    """The cache requirement names a key width and a value width; the storage gives the mixer pages of each width,
+    and the cache manager, the step function and the scheduler's cuts need to know nothing about it."""
+    make_narrow_key_toy()
+    from libmir_b200 import CacheConfig, Library, RuntimeConfig, StepEntry
+    from libmir_b200.weights import write_file, write_model_folder
+    folder = write_model_folder(tmp_path, NARROW_CONFIG, seed=7, dtype="float32")
+    _, weights = plain_impl.read_model(folder)
+    for name in weights:
+        if ".mixer." in name:
+            weights[name] = weights[name] * 20
+    write_file(folder / "model.safetensors", weights)
+    _, weights = plain_impl.read_model(folder)
+    model = Library(RuntimeConfig(kv_cache=CacheConfig(block_size=4, block_count=24), dtype="float32")).load(folder)
+    assert model.storage.key_buffers[0].shape[-2:] == (1, 8) and model.storage.value_buffers[0].shape[-2:] == (1, 24)
+    stats = model.cache_stats()["groups"][0]
+    assert (stats["head_dim"], stats["value_head_dim"]) == (8, 24)
+    ids = random_ids(np.random.default_rng(3), 50, 37)
+    want = plain_narrow_key_toy(weights, ids)
+    model.admit("a")
+    got, cursor = [], 0
+    for size in (9, 1, 2, 13, 1, 11):
+        got.append(model.step([StepEntry("a", ids[cursor:cursor + size], range(size))]).logits.cpu().numpy())
+        cursor += size
+    error = np.abs(np.concatenate(got) - want).max()
+    assert error <= 3e-5 * max(1.0, np.abs(want).max()), f"max |diff| {error:.3e}"
