@@ -3,8 +3,11 @@
 //
 //   out[i] = softmax_j(scale q_i . k_j) v_j     over the keys j <= position(i) (and inside the window, if any)
 //
-// One CTA takes 128 consecutive query tokens of one request and one head, and walks over the request's keys in
-// tiles of 128.  Per tile:  S = Q K^T  (tcgen05.mma, 128 x 128 x 128, accumulator in tensor memory),
+// A work item is 128 consecutive query tokens of one request and one head; a CTA (one per SM) walks over the
+// request's keys in tiles of 128 for one item after the other (the heaviest items first, dealt out to the CTAs back
+// and forth so that every CTA gets about the same number of key tiles), and every ring and barrier runs on across
+// the items: the loaders fetch the next item's queries and first keys while the softmax threads still merge and
+// write the last item's result, which took half of a CTA's life when every item had a CTA of its own.  Per tile:  S = Q K^T  (tcgen05.mma, 128 x 128 x 128, accumulator in tensor memory),
 // P = exp2(scale S - m) by the softmax threads (one query row per thread, read with tcgen05.ld, written to
 // shared memory as the bf16 A operand of the next product),  O += P V  (tcgen05.mma, accumulator stays in tensor
 // memory for the whole row of tiles).  Roles:
@@ -60,7 +63,9 @@ constexpr float kRescaleThreshold = 8.0f;   // log2 of how far a tile's maximum 
 
 // barrier indices
 enum { Q_FULL = 0, K_FULL = 1, K_FREE = 3, V_FULL = 5, V_FREE = 7, S_FULL = 9, S_FREE = 11, P_READY = 13, PV_DONE = 14,
-       BARRIERS = 16 };
+       Q_FREE = 16, O_FREE = 17, BARRIERS = 18 };
+// Tiles are counted over all items of a CTA (g): stage g & 1 of the rings and of the score accumulators, phase
+// parity (g >> 1) & 1; items are counted too (n): Q_FULL, Q_FREE and O_FREE complete once per item.
 // PV_DONE + (t & 1) for tile t: a wait on an mbarrier names a phase by its parity only, so a thread may only wait
 // for a phase when it knows that the phase before has completed.  A stream that takes every second tile waits
 // for the products of the tiles in between; with one barrier for all tiles it would see every second phase
@@ -68,6 +73,7 @@ enum { Q_FULL = 0, K_FULL = 1, K_FREE = 3, V_FULL = 5, V_FREE = 7, S_FULL = 9, S
 
 __device__ int g_tc_attention_error = 0;
 int g_streams = 2;
+int g_ctas = 0;                             // for measurements: 0 = one CTA per SM
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -140,53 +146,92 @@ __device__ __forceinline__ float softmax_tile(uint32_t scores, int first, int lo
   return (sums[0] + sums[1]) + (sums[2] + sums[3]);
 }
 
+// What one work item is: which queries, which keys.
+struct Work {
+  bool valid;
+  int head, kv_head, q_row0, tile_rows, first_position, last_position, first_key, key_begin, key_end, tiles;
+  const int* table;
+};
+
+// Item `index` of the launch: head = index % heads (the fast index, so that the heads of a group, which read the
+// same keys, run at the same time), and the batch's `query_tiles` query tiles from the last one of the last row
+// backwards (late tiles see the most keys: they come first).
+__device__ __forceinline__ Work work_item(int index, int items, int query_tiles, int heads, int kv_heads, int num_rows,
+                                          const int* __restrict__ query_starts, const int* __restrict__ context_lens,
+                                          const int* __restrict__ block_table, int table_width, int window) {
+  Work w;
+  w.valid = false;
+  if (index < 0 || index >= items) return w;
+  w.head = index % heads;
+  w.kv_head = w.head / (heads / kv_heads);
+  int remaining = query_tiles - 1 - index / heads;
+  int row = -1, local_tile = 0;
+  for (int r = 0; r < num_rows; ++r) {
+    const int tiles = (query_starts[r + 1] - query_starts[r] + kRows - 1) / kRows;
+    if (remaining < tiles) { row = r; local_tile = remaining; break; }
+    remaining -= tiles;
+  }
+  if (row < 0) return w;
+  const int q_begin = query_starts[row];
+  const int count = query_starts[row + 1] - q_begin;
+  const int start_position = context_lens[row] - count;
+  const int local0 = local_tile * kRows;
+  w.q_row0 = q_begin + local0;
+  w.tile_rows = min(kRows, count - local0);
+  w.first_position = start_position + local0;
+  w.last_position = w.first_position + w.tile_rows - 1;
+  w.table = block_table + (size_t)row * table_width;
+  w.first_key = (window > 0 && w.first_position + 1 > window) ? w.first_position + 1 - window : 0;
+  w.key_begin = w.first_key / kKeys * kKeys;
+  w.key_end = w.last_position + 1;                            // exclusive
+  w.tiles = (w.key_end - w.key_begin + kKeys - 1) / kKeys;
+  w.valid = true;
+  return w;
+}
+
+// The k-th item of CTA `cta` of `ctas`: round k deals the items k * ctas .. (k + 1) * ctas - 1 out forwards if k is
+// even and backwards if it is odd, so that the CTA that got the heaviest item of one round gets the lightest of the
+// next.  -1 when the rounds are over.
+__device__ __forceinline__ int item_of(int k, int cta, int ctas, int items) {
+  if ((long long)k * ctas >= items) return -1;
+  return k * ctas + ((k & 1) ? ctas - 1 - cta : cta);
+}
+
 template <int kStreams>
 __global__ void __launch_bounds__(threads_for(kStreams), 1)
 tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                             const __grid_constant__ CUtensorMap v_map, bf16* __restrict__ out,
                             const int* __restrict__ block_table, int table_width, const int* __restrict__ query_starts,
                             const int* __restrict__ context_lens, int num_rows, int page_size, int heads, int kv_heads,
-                            float scale_log2, int window) {
+                            float scale_log2, int window, int tile_slots) {
   constexpr int kThreads = threads_for(kStreams);
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long barriers[BARRIERS];
   __shared__ uint32_t tmem_base_slot;
   __shared__ float exchange[kStreams][2][kParts][kRows];     // [stream][its tile parity][part][row]: a row's maxima
-  __shared__ float denominators[kStreams][kParts][kRows];    // (apart: a slow thread may still read the last maxima)
-  __shared__ float references[kStreams][kRows];
+  __shared__ float denominators[2][kStreams][kParts][kRows]; // [item parity]...: a slow thread may still read the last item's
+  __shared__ float references[2][kStreams][kRows];
+  __shared__ int query_tiles_slot;
   if (*reinterpret_cast<volatile int*>(&g_tc_attention_error) != 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // The head is the fast index of the grid: CTAs are handed out in the order of blockIdx.x first, so all heads of
-  // the query tile that sees the most keys start first and the shortest tiles fill the end (and the heads of
-  // one group, which read the same keys, run at the same time).
-  const int head = blockIdx.x;
-  const int kv_head = head / (heads / kv_heads);
+  const int cta = blockIdx.x, ctas = gridDim.x;
 
   grid_launch_dependents();
   grid_dependency_wait();
-  // which request row and which 128-token tile of its portion this CTA has
-  int row = -1, local_tile = 0;
-  {
-    int remaining = gridDim.y - 1 - blockIdx.y;              // late tiles see the most keys: start them first
-    for (int r = 0; r < num_rows; ++r) {
-      const int tiles = (query_starts[r + 1] - query_starts[r] + kRows - 1) / kRows;
-      if (remaining < tiles) { row = r; local_tile = remaining; break; }
-      remaining -= tiles;
-    }
+  if (threadIdx.x == 0) {
+    // how many query tiles the batch really has (the launch was sized for at most tile_slots)
+    int total = 0;
+    for (int r = 0; r < num_rows; ++r) total += (query_starts[r + 1] - query_starts[r] + kRows - 1) / kRows;
+    query_tiles_slot = min(total, tile_slots);
   }
-  if (row < 0) return;                                        // a spare CTA (uniform for the whole CTA)
-  const int q_begin = query_starts[row];
-  const int count = query_starts[row + 1] - q_begin;
-  const int start_position = context_lens[row] - count;
-  const int local0 = local_tile * kRows;
-  const int tile_rows = min(kRows, count - local0);
-  const int first_position = start_position + local0;
-  const int last_position = first_position + tile_rows - 1;
-  const int* table = block_table + (size_t)row * table_width;
-  const int first_key = (window > 0 && first_position + 1 > window) ? first_position + 1 - window : 0;
-  const int key_begin = first_key / kKeys * kKeys;
-  const int key_end = last_position + 1;                      // exclusive
-  const int tiles = (key_end - key_begin + kKeys - 1) / kKeys;
+  __syncthreads();
+  const int query_tiles = query_tiles_slot;
+  const int items = heads * query_tiles;
+  auto work = [&](int k) {
+    return work_item(item_of(k, cta, ctas, items), items, query_tiles, heads, kv_heads, num_rows, query_starts,
+                     context_lens, block_table, table_width, window);
+  };
+  auto more = [&](int k) { return (long long)k * ctas < items; };
 
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t smem_base = smem_u32(smem);
@@ -196,7 +241,8 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   if (threadIdx.x == 0) {
     for (int i = 0; i < BARRIERS; ++i) {
       const bool many = i == S_FREE || i == S_FREE + 1 || i == P_READY;   // every softmax thread of a stream arrives
-      barrier_init(bar(i), many ? (uint32_t)kStreamThreads : 1u);
+      const bool all = i == O_FREE;                                        // every softmax thread of every stream
+      barrier_init(bar(i), all ? (uint32_t)(kStreamThreads * kStreams) : (many ? (uint32_t)kStreamThreads : 1u));
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -220,85 +266,116 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     // ------------------------------------------------------------------ loaders: warp 0 keys, the last warp values
     // (apart, so that the keys of a later tile do not queue behind values whose stage is still being read)
     const int which = warp == 0 ? 0 : 1;
-    if (which == 0 && lane == 0) {
-      barrier_expect_bytes(bar(Q_FULL), kTile);
-      tma_load_2d(smem_base + kOffQ, &q_map, bar(Q_FULL), head * kDim, q_begin + local0);
-      tma_load_2d(smem_base + kOffQ + kHalf, &q_map, bar(Q_FULL), head * kDim + 64, q_begin + local0);
-    }
     const int pages_per_tile = kKeys / page_size;
     const uint32_t box_bytes = (uint32_t)page_size * 128u;
     // lane l loads half (l & 1) of page slot (l >> 1): at most 16 pages of 8 keys, so one round of 32 lanes
     const int slot = lane >> 1, half = lane & 1;
-    auto page_of = [&](int t) {
-      const int key = key_begin + t * kKeys + slot * page_size;
-      return (t < tiles && lane < 2 * pages_per_tile && key < key_end && key + page_size > first_key)
-                 ? table[key / page_size] : -1;
-    };
-    int page = page_of(0);
-    for (int t = 0; t < tiles; ++t) {
-      const int stage = t & 1;
-      const uint32_t parity = (uint32_t)(t >> 1) & 1u;
-      const int next_page = page_of(t + 1);                   // on its way while this tile's stage is awaited
-      const uint32_t full = bar((which ? V_FULL : K_FULL) + stage), free_bar = bar((which ? V_FREE : K_FREE) + stage);
-      int ok = 1;
-      if (lane == 0) ok = wait_barrier(free_bar, parity ^ 1u) ? 1 : 0;
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) { if (lane == 0) g_tc_attention_error = 1; break; }
-      const uint32_t dst = smem_base + (which ? kOffV : kOffK) + (uint32_t)stage * kTile;
-      const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
-      if (lane == 0) barrier_expect_bytes(full, (uint32_t)__popc(valid) * box_bytes);
-      __syncwarp();
-      if (page >= 0)
-        tma_load_2d(dst + (uint32_t)half * kHalf + (uint32_t)(slot * page_size) * 128u, which ? &v_map : &k_map, full,
-                    kv_head * kDim + half * 64, page * page_size);
-      page = next_page;
+    int g0 = 0, n = 0;
+    bool alive = true;
+    for (int k = 0; more(k) && alive; ++k) {
+      const Work w = work(k);
+      if (!w.valid) continue;
+      if (which == 0) {
+        // the queries, once the products with the last item's are over
+        int ok = 1;
+        if (lane == 0 && n > 0) ok = wait_barrier(bar(Q_FREE), (uint32_t)(n - 1) & 1u) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { if (lane == 0) g_tc_attention_error = 1; break; }
+        if (lane == 0) {
+          barrier_expect_bytes(bar(Q_FULL), kTile);
+          tma_load_2d(smem_base + kOffQ, &q_map, bar(Q_FULL), w.head * kDim, w.q_row0);
+          tma_load_2d(smem_base + kOffQ + kHalf, &q_map, bar(Q_FULL), w.head * kDim + 64, w.q_row0);
+        }
+      }
+      auto page_of = [&](int t) {
+        const int key = w.key_begin + t * kKeys + slot * page_size;
+        return (t < w.tiles && lane < 2 * pages_per_tile && key < w.key_end && key + page_size > w.first_key)
+                   ? w.table[key / page_size] : -1;
+      };
+      int page = page_of(0);
+      for (int t = 0; t < w.tiles; ++t) {
+        const int g = g0 + t;
+        const int stage = g & 1;
+        const uint32_t parity = (uint32_t)(g >> 1) & 1u;
+        const int next_page = page_of(t + 1);                 // on its way while this tile's stage is awaited
+        const uint32_t full = bar((which ? V_FULL : K_FULL) + stage), free_bar = bar((which ? V_FREE : K_FREE) + stage);
+        int ok = 1;
+        if (lane == 0) ok = wait_barrier(free_bar, parity ^ 1u) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { if (lane == 0) g_tc_attention_error = 1; alive = false; break; }
+        const uint32_t dst = smem_base + (which ? kOffV : kOffK) + (uint32_t)stage * kTile;
+        const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
+        if (lane == 0) barrier_expect_bytes(full, (uint32_t)__popc(valid) * box_bytes);
+        __syncwarp();
+        if (page >= 0)
+          tma_load_2d(dst + (uint32_t)half * kHalf + (uint32_t)(slot * page_size) * 128u, which ? &v_map : &k_map, full,
+                      w.kv_head * kDim + half * 64, page * page_size);
+        page = next_page;
+      }
+      g0 += w.tiles;
+      ++n;
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = instruction_descriptor(kRows, kKeys, false);
       constexpr uint32_t idesc_pv = instruction_descriptor(kRows, kDim, true);
-      bool alive = wait_barrier(bar(Q_FULL), 0);
-      if (!alive) g_tc_attention_error = 2;
-      auto issue_scores = [&](int t) {
-        const int stage = t & 1;
-        const uint32_t parity = (uint32_t)(t >> 1) & 1u;
-        if (alive && !wait_barrier(bar(K_FULL + stage), parity)) { g_tc_attention_error = 2; alive = false; }
-        if (alive && !wait_barrier(bar(S_FREE + stage), parity ^ 1u)) { g_tc_attention_error = 2; alive = false; }
-        tensor_fence_after_sync();
-        const uint32_t a = smem_base + kOffQ, b = smem_base + kOffK + (uint32_t)stage * kTile;
+      bool alive = true;
+      int g0 = 0, n = 0;
+      for (int k = 0; more(k); ++k) {
+        const Work w = work(k);
+        if (!w.valid) continue;
+        if (alive && !wait_barrier(bar(Q_FULL), (uint32_t)n & 1u)) { g_tc_attention_error = 2; alive = false; }
+        auto issue_scores = [&](int t) {
+          const int g = g0 + t;
+          const int stage = g & 1;
+          const uint32_t parity = (uint32_t)(g >> 1) & 1u;
+          if (alive && !wait_barrier(bar(K_FULL + stage), parity)) { g_tc_attention_error = 2; alive = false; }
+          if (alive && !wait_barrier(bar(S_FREE + stage), parity ^ 1u)) { g_tc_attention_error = 2; alive = false; }
+          tensor_fence_after_sync();
+          const uint32_t a = smem_base + kOffQ, b = smem_base + kOffK + (uint32_t)stage * kTile;
 #pragma unroll
-        for (int kk = 0; kk < kDim / 16; ++kk) {
-          const uint32_t offset = (uint32_t)(kk >> 2) * kHalf + (uint32_t)(kk & 3) * 32u;
-          mma_bf16_ss(tmem_base + (uint32_t)stage * 128u, operand_descriptor(a + offset), operand_descriptor(b + offset),
-                      idesc_qk, kk > 0 ? 1u : 0u);
-        }
-        mma_commit(bar(S_FULL + stage));
-        mma_commit(bar(K_FREE + stage));
-      };
-      // scores run two tiles ahead of the products with P: S(t + 2) goes into the accumulator of S(t) as soon as
-      // the softmax threads have read that (early in their work on tile t), so a stream finds its next scores
-      // ready when it is done with a tile
-      issue_scores(0);
-      if (tiles > 1) issue_scores(1);
-      for (int t = 0; t < tiles; ++t) {
-        if (t + 2 < tiles) issue_scores(t + 2);
-        const int stage = t & 1;
-        const uint32_t parity = (uint32_t)(t >> 1) & 1u;
-        if (alive && !wait_barrier(bar(V_FULL + stage), parity)) { g_tc_attention_error = 2; alive = false; }
-        if (alive && !wait_barrier(bar(P_READY), (uint32_t)t & 1u)) { g_tc_attention_error = 2; alive = false; }
-        tensor_fence_after_sync();
-        const uint32_t a = smem_base + kOffP, b = smem_base + kOffV + (uint32_t)stage * kTile;
+          for (int kk = 0; kk < kDim / 16; ++kk) {
+            const uint32_t offset = (uint32_t)(kk >> 2) * kHalf + (uint32_t)(kk & 3) * 32u;
+            mma_bf16_ss(tmem_base + (uint32_t)stage * 128u, operand_descriptor(a + offset), operand_descriptor(b + offset),
+                        idesc_qk, kk > 0 ? 1u : 0u);
+          }
+          mma_commit(bar(S_FULL + stage));
+          mma_commit(bar(K_FREE + stage));
+          if (t == w.tiles - 1) mma_commit(bar(Q_FREE));       // the item's last product with its queries
+        };
+        // scores run two tiles ahead of the products with P: S(t + 2) goes into the accumulator of S(t) as soon as
+        // the softmax threads have read that (early in their work on tile t), so a stream finds its next scores
+        // ready when it is done with a tile
+        issue_scores(0);
+        if (w.tiles > 1) issue_scores(1);
+        for (int t = 0; t < w.tiles; ++t) {
+          if (t + 2 < w.tiles) issue_scores(t + 2);
+          const int g = g0 + t;
+          const int stage = g & 1;
+          const uint32_t parity = (uint32_t)(g >> 1) & 1u;
+          if (alive && !wait_barrier(bar(V_FULL + stage), parity)) { g_tc_attention_error = 2; alive = false; }
+          if (alive && !wait_barrier(bar(P_READY), (uint32_t)g & 1u)) { g_tc_attention_error = 2; alive = false; }
+          // the output accumulators are the last item's until every softmax thread has read them out
+          if (t == 0 && n > 0 && alive && !wait_barrier(bar(O_FREE), (uint32_t)(n - 1) & 1u)) {
+            g_tc_attention_error = 2;
+            alive = false;
+          }
+          tensor_fence_after_sync();
+          const uint32_t a = smem_base + kOffP, b = smem_base + kOffV + (uint32_t)stage * kTile;
 #pragma unroll
-        for (int kk = 0; kk < kKeys / 16; ++kk) {
-          // P: 16 keys further along its 128-byte rows; V: 16 rows of keys further down
-          const uint32_t a_offset = (uint32_t)(kk >> 2) * kHalf + (uint32_t)(kk & 3) * 32u;
-          mma_bf16_ss(tmem_o + (uint32_t)(t % kStreams) * 128u, operand_descriptor(a + a_offset),
-                      operand_descriptor_mn_major(b + (uint32_t)kk * 2048u, kHalf), idesc_pv,
-                      (t >= kStreams || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kKeys / 16; ++kk) {
+            // P: 16 keys further along its 128-byte rows; V: 16 rows of keys further down
+            const uint32_t a_offset = (uint32_t)(kk >> 2) * kHalf + (uint32_t)(kk & 3) * 32u;
+            mma_bf16_ss(tmem_o + (uint32_t)(t % kStreams) * 128u, operand_descriptor(a + a_offset),
+                        operand_descriptor_mn_major(b + (uint32_t)kk * 2048u, kHalf), idesc_pv,
+                        (t >= kStreams || kk > 0) ? 1u : 0u);
+          }
+          mma_commit(bar(PV_DONE + (g & 1)));
+          mma_commit(bar(V_FREE + stage));
         }
-        mma_commit(bar(PV_DONE + (t & 1)));
-        mma_commit(bar(V_FREE + stage));
+        g0 += w.tiles;
+        ++n;
       }
     }
   } else {
@@ -307,120 +384,136 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     const int quarter = warp & 3;                             // the accumulator lanes this warp may touch
     const int part = ((warp - 2) >> 2) & 1;                   // which kCols columns of the row it takes
     const int r = quarter * 32 + lane;
-    const bool valid_row = r < tile_rows;
-    const int position = first_position + min(r, tile_rows - 1);
     const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
     const int first = part * kCols;
     const uint32_t my_o = tmem_o + (uint32_t)stream * 128u + lane_bits;
-    float reference = -INFINITY, denominator = 0.0f;          // running maximum (scaled, log2 domain), partial sum
     bool alive = true;
     // (a thread whose wait ran out keeps walking the tiles without waiting, so that the row's named barrier
     // still sees all of its threads)
-    for (int t = stream; t < tiles; t += kStreams) {
-      const int stage = t & 1;
-      const uint32_t parity = (uint32_t)(t >> 1) & 1u;
-      const int key0 = key_begin + t * kKeys;
-      if (alive && !wait_barrier(bar(S_FULL + stage), parity)) { g_tc_attention_error = 3; alive = false; }
-      tensor_fence_after_sync();
-      const uint32_t scores = tmem_base + (uint32_t)stage * 128u + lane_bits;
-      // keys of this tile that row r may see: columns [low, high]; most tiles are visible to every row
-      const int high = position - key0;                       // last visible column, may be >= 128 or < 0
-      const int low = window > 0 ? position - window + 1 - key0 : -1;
-      const bool every = key0 + kKeys - 1 <= first_position && (window == 0 || last_position - window + 1 <= key0);
-      uint32_t packed[kCols / 2];
-      bool grow;
-      float factor;
-      float* shared_max = &exchange[stream][(t / kStreams) & 1][0][r];
-      const int team = 1 + stream * 4 + quarter;
-      const float sum = every ? softmax_tile<false>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
-                                                    shared_max, part, team, bar(S_FREE + stage))
-                              : softmax_tile<true>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
-                                                   shared_max, part, team, bar(S_FREE + stage));
-      denominator = denominator * factor + sum;
-      // the product with the previous tile's P (the other stream's, if there are two) must be over before P
-      // changes, and this stream's previous product before its O does
-      if (t > 0) {
-        if (alive && !wait_barrier(bar(PV_DONE + ((t - 1) & 1)), (uint32_t)((t - 1) >> 1) & 1u)) {
-          g_tc_attention_error = 3;
-          alive = false;
-        }
+    int g0 = 0, n = 0;
+    for (int k = 0; more(k); ++k) {
+      const Work w = work(k);
+      if (!w.valid) continue;
+      const bool valid_row = r < w.tile_rows;
+      const int position = w.first_position + min(r, w.tile_rows - 1);
+      float reference = -INFINITY, denominator = 0.0f;        // running maximum (scaled, log2 domain), partial sum
+      for (int t = stream; t < w.tiles; t += kStreams) {
+        const int g = g0 + t;
+        const int stage = g & 1;
+        const uint32_t parity = (uint32_t)(g >> 1) & 1u;
+        const int key0 = w.key_begin + t * kKeys;
+        if (alive && !wait_barrier(bar(S_FULL + stage), parity)) { g_tc_attention_error = 3; alive = false; }
         tensor_fence_after_sync();
-        if (t >= kStreams && __any_sync(0xffffffffu, grow)) {
+        const uint32_t scores = tmem_base + (uint32_t)stage * 128u + lane_bits;
+        // keys of this tile that row r may see: columns [low, high]; most tiles are visible to every row
+        const int high = position - key0;                     // last visible column, may be >= 128 or < 0
+        const int low = window > 0 ? position - window + 1 - key0 : -1;
+        const bool every = key0 + kKeys - 1 <= w.first_position && (window == 0 || w.last_position - window + 1 <= key0);
+        uint32_t packed[kCols / 2];
+        bool grow;
+        float factor;
+        float* shared_max = &exchange[stream][(t / kStreams) & 1][0][r];
+        const int team = 1 + stream * 4 + quarter;
+        const float sum = every ? softmax_tile<false>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
+                                                      shared_max, part, team, bar(S_FREE + stage))
+                                : softmax_tile<true>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
+                                                     shared_max, part, team, bar(S_FREE + stage));
+        denominator = denominator * factor + sum;
+        // the product with the previous tile's P (the other stream's, if there are two) must be over before P
+        // changes, and this stream's previous product before its O does (the last item's products are over: every
+        // thread waited for the last of them before it read the result out)
+        if (t > 0) {
+          if (alive && !wait_barrier(bar(PV_DONE + ((g - 1) & 1)), (uint32_t)((g - 1) >> 1) & 1u)) {
+            g_tc_attention_error = 3;
+            alive = false;
+          }
+          tensor_fence_after_sync();
+          if (t >= kStreams && __any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-          for (int c0 = 0; c0 < kDim / kParts; c0 += 32) {
-            float o[32];
-            tmem_load_32(my_o + first + c0, o);
+            for (int c0 = 0; c0 < kDim / kParts; c0 += 32) {
+              float o[32];
+              tmem_load_32(my_o + first + c0, o);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] *= factor;
-            tmem_store_32(my_o + first + c0, o);
+              for (int i = 0; i < 32; ++i) o[i] *= factor;
+              tmem_store_32(my_o + first + c0, o);
+            }
+            tmem_store_wait();
           }
-          tmem_store_wait();
         }
+        // P as the A operand: rows of 128 bytes (64 keys: this thread's half), 16-byte chunks swizzled by the row
+        unsigned char* p_row = smem + kOffP + (size_t)part * kHalf + (size_t)r * 128;
+#pragma unroll
+        for (int chunk = 0; chunk < 8; ++chunk) {
+          const int where = chunk ^ (r & 7);
+          *reinterpret_cast<uint4*>(p_row + where * 16) =
+              make_uint4(packed[4 * chunk], packed[4 * chunk + 1], packed[4 * chunk + 2], packed[4 * chunk + 3]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        tensor_fence_before_sync();
+        barrier_arrive(bar(P_READY));
       }
-      // P as the A operand: rows of 128 bytes (64 keys: this thread's half), 16-byte chunks swizzled by the row
-      unsigned char* p_row = smem + kOffP + (size_t)part * kHalf + (size_t)r * 128;
+      // every softmax thread learns every stream's maximum and denominator (the sum of its two threads' parts)
+      const int slot = n & 1;
+      denominators[slot][stream][part][r] = denominator;
+      if (part == 0) references[slot][stream][r] = reference;
+      asm volatile("bar.sync %0, %1;" ::"r"(9), "n"(kStreamThreads * kStreams) : "memory");
+      float top = -INFINITY;
 #pragma unroll
-      for (int chunk = 0; chunk < 8; ++chunk) {
-        const int where = chunk ^ (r & 7);
-        *reinterpret_cast<uint4*>(p_row + where * 16) =
-            make_uint4(packed[4 * chunk], packed[4 * chunk + 1], packed[4 * chunk + 2], packed[4 * chunk + 3]);
+      for (int other = 0; other < kStreams; ++other) top = fmaxf(top, references[slot][other][r]);
+      float weight[kStreams], total = 0.0f;
+#pragma unroll
+      for (int other = 0; other < kStreams; ++other) {
+        const float theirs = references[slot][other][r];      // -inf: that stream saw no key of this row
+        weight[other] = theirs > -INFINITY ? fast_exp2(theirs - top) : 0.0f;
+        total += (denominators[slot][other][0][r] + denominators[slot][other][1][r]) * weight[other];
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      tensor_fence_before_sync();
-      barrier_arrive(bar(P_READY));
-    }
-    // every softmax thread learns every stream's maximum and denominator (the sum of its two threads' parts)
-    denominators[stream][part][r] = denominator;
-    if (part == 0) references[stream][r] = reference;
-    asm volatile("bar.sync %0, %1;" ::"r"(9), "n"(kStreamThreads * kStreams) : "memory");
-    float top = -INFINITY;
-#pragma unroll
-    for (int other = 0; other < kStreams; ++other) top = fmaxf(top, references[other][r]);
-    float weight[kStreams], total = 0.0f;
-#pragma unroll
-    for (int other = 0; other < kStreams; ++other) {
-      const float theirs = references[other][r];              // -inf: that stream saw no key of this row
-      weight[other] = theirs > -INFINITY ? fast_exp2(theirs - top) : 0.0f;
-      total += (denominators[other][0][r] + denominators[other][1][r]) * weight[other];
-    }
-    // (every thread has passed the named barrier above, so the products before the last one are over)
-    if (alive && !wait_barrier(bar(PV_DONE + ((tiles - 1) & 1)), (uint32_t)((tiles - 1) >> 1) & 1u)) {
-      g_tc_attention_error = 3;
-      alive = false;
-    }
-    tensor_fence_after_sync();
-    if (alive) {
-      // this thread's columns of the output: the row's 128 are shared out over all its softmax threads
-      constexpr int kOut = kDim / (kParts * kStreams);
-      const int column = (stream * kParts + part) * kOut;
-      const float inverse = total > 0.0f ? 1.0f / total : 0.0f;
-      bf16* dst = out + ((size_t)(q_begin + local0 + r) * heads + head) * kDim + column;
+      // (every thread has passed the named barrier above, so the products before the last one are over)
+      const int last = g0 + w.tiles - 1;
+      if (alive && !wait_barrier(bar(PV_DONE + (last & 1)), (uint32_t)(last >> 1) & 1u)) {
+        g_tc_attention_error = 3;
+        alive = false;
+      }
+      tensor_fence_after_sync();
+      {
+        // this thread's columns of the output: the row's 128 are shared out over all its softmax threads
+        constexpr int kOut = kDim / (kParts * kStreams);
+        const int column = (stream * kParts + part) * kOut;
+        const float inverse = total > 0.0f ? 1.0f / total : 0.0f;
+        bf16* dst = out + ((size_t)(w.q_row0 + r) * heads + w.head) * kDim + column;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kOut; c0 += 32) {
-        float o[32];
+        for (int c0 = 0; c0 < kOut; c0 += 32) {
+          float o[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = 0.0f;
+          for (int i = 0; i < 32; ++i) o[i] = 0.0f;
 #pragma unroll
-        for (int other = 0; other < kStreams; ++other) {
-          if (other < tiles) {                                // a stream without a tile never wrote its O
-            float theirs[32];
-            tmem_load_32(tmem_o + (uint32_t)other * 128u + lane_bits + column + c0, theirs);
-            const float w = weight[other] * inverse;
+          for (int other = 0; other < kStreams; ++other) {
+            if (other < w.tiles) {                            // a stream without a tile never wrote its O
+              float theirs[32];
+              tmem_load_32(tmem_o + (uint32_t)other * 128u + lane_bits + column + c0, theirs);
+              const float share = weight[other] * inverse;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] += w > 0.0f ? theirs[i] * w : 0.0f;
+              for (int i = 0; i < 32; ++i) o[i] += share > 0.0f ? theirs[i] * share : 0.0f;
+            }
           }
-        }
-        if (valid_row) {
+          if (c0 + 32 >= kOut) {
+            // the accumulators are read out: the next item's products may overwrite them
+            tensor_fence_before_sync();
+            barrier_arrive(bar(O_FREE));
+          }
+          if (valid_row && alive) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 packed_out;
-            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed_out);
+            for (int i = 0; i < 32; i += 8) {
+              uint4 packed_out;
+              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed_out);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(o[i + 2 * j], o[i + 2 * j + 1]);
-            *reinterpret_cast<uint4*>(dst + c0 + i) = packed_out;
+              for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(o[i + 2 * j], o[i + 2 * j + 1]);
+              *reinterpret_cast<uint4*>(dst + c0 + i) = packed_out;
+            }
           }
         }
       }
+      g0 += w.tiles;
+      ++n;
     }
     tensor_fence_before_sync();
   }
@@ -486,25 +579,41 @@ MIR_EXPORT int mir_prefill_attention_tc_bf16(const void* q, long long q_stride, 
     }
     configured = true;
   }
-  const int tiles = (tokens + kRows - 1) / kRows + num_rows;   // an upper bound; spare CTAs return
-  if (tiles > 65535) {
+  const int tile_slots = (tokens + kRows - 1) / kRows + num_rows;   // an upper bound; spare items are skipped
+  const long long items = (long long)tile_slots * heads;
+  if (items > 0x7fffffffll) {
     mir_set_error("prefill_attention_tc: %d tokens in %d rows are more than one launch takes", tokens, num_rows);
     return MIR_BAD_ARGUMENT;
   }
+  static int sms = 0;
+  if (sms == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  const int ctas = (int)std::min<long long>(items, g_ctas > 0 ? g_ctas : sms);
   if (g_streams == 2)
-    return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<2>, dim3(heads, tiles), dim3(threads_for(2)),
+    return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<2>, dim3(ctas), dim3(threads_for(2)),
                       (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, (bf16*)out, block_table, table_width,
                       query_starts, context_lens, num_rows, page_size, heads, kv_heads,
-                      scale * 1.4426950408889634f, window);
-  return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<1>, dim3(heads, tiles), dim3(threads_for(1)),
+                      scale * 1.4426950408889634f, window, tile_slots);
+  return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<1>, dim3(ctas), dim3(threads_for(1)),
                     (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, (bf16*)out, block_table, table_width,
                     query_starts, context_lens, num_rows, page_size, heads, kv_heads,
-                    scale * 1.4426950408889634f, window);
+                    scale * 1.4426950408889634f, window, tile_slots);
 }
 
 // For measurements: 2 (the default) splits a row's key tiles over two softmax streams, 1 runs one stream.
 MIR_EXPORT int mir_prefill_attention_tc_set_streams(int streams) {
   if (streams != 1 && streams != 2) return MIR_BAD_ARGUMENT;
   g_streams = streams;
+  return MIR_OK;
+}
+
+// For measurements: at most this many CTAs (0: one per SM).  As many CTAs as there are items gives every item a CTA
+// of its own.
+MIR_EXPORT int mir_prefill_attention_tc_set_ctas(int ctas) {
+  if (ctas < 0) return MIR_BAD_ARGUMENT;
+  g_ctas = ctas;
   return MIR_OK;
 }
