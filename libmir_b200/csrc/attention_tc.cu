@@ -7,24 +7,26 @@
 // request's keys in tiles of 128 for one item after the other (the heaviest items first, dealt out to the CTAs back
 // and forth so that every CTA gets about the same number of key tiles), and every ring and barrier runs on across
 // the items: the loaders fetch the next item's queries and first keys while the softmax threads still merge and
-// write the last item's result, which took half of a CTA's life when every item had a CTA of its own.  Per tile:  S = Q K^T  (tcgen05.mma, 128 x 128 x 128, accumulator in tensor memory),
-// P = exp2(scale S - m) by the softmax threads (one query row per thread, read with tcgen05.ld, written to
-// shared memory as the bf16 A operand of the next product),  O += P V  (tcgen05.mma, accumulator stays in tensor
-// memory for the whole row of tiles).  Roles:
+// write the last item's result, which took half of a CTA's life when every item had a CTA of its own.
+// Per tile:  S = Q K^T  (tcgen05.mma, 128 x 128 x 128, accumulator in tensor memory),  P = exp2(scale S - m) by the
+// softmax threads (one query row per thread, read with tcgen05.ld and written back with tcgen05.st as packed bf16
+// pairs over the scores they came from: the A operand of the next product stays in tensor memory and never
+// touches shared memory),  O += P V  (tcgen05.mma with A in tensor memory, accumulator stays in tensor memory for
+// the whole row of tiles).  Roles:
 //
 //   loaders   one warp for keys (and Q, once), one for values.  Per tile the pages that hold it: one TMA box per
 //             page and 64-wide half of the head (cp.async.bulk.tensor.2d through a tensor map over the cache,
 //             128-byte swizzle), into two-stage rings.  Pages the block table does not have (-1) are skipped.
-//   issuer    one thread.  S(t+2) = Q K(t+2)^T is issued before O += P(t) V(t), as soon as the softmax threads
-//             have read S(t) out of the accumulator it reuses (two S accumulators), so that the tensor cores
-//             work on coming scores while the softmax threads are busy with the current ones.
+//   issuer    one thread.  Two S accumulators: S(t+2) = Q K(t+2)^T takes the one that holds P(t), so it is issued
+//             right behind O += P(t) V(t) (the tensor cores run products in the order of issue); while they work
+//             on one stream's tile, the other stream's softmax threads work on theirs.
 //   softmax   two streams of eight warps.  Stream s takes the key tiles t = s, s + 2, ... and keeps a softmax of
 //             its own over them: running maximum, denominator and an O accumulator of its own in tensor memory
 //             (as if the keys were split in two, as decode attention splits them); the two are merged when the
 //             row of tiles is over.  While one stream computes exponentials the other reads scores, finds its
 //             maximum and writes P, so the exponential unit and the tensor cores both stay busy.  Within a
 //             stream, query row r = accumulator lane r belongs to two threads, which take 64 columns each (of
-//             the scores and of P) and share the row's maximum through shared memory.  A stream's running
+//             the scores; 32 of P) and share the row's maximum through shared memory.  A stream's running
 //             maximum is only raised when a tile's maximum exceeds it by more than 2^8 (then its O and its
 //             denominator are rescaled, O by tcgen05.ld / tcgen05.st), so most tiles need no pass over O.
 //
@@ -46,13 +48,13 @@ typedef __nv_bfloat16 bf16;
 
 namespace {
 
-constexpr int kRows = 128;                  // query tokens per CTA
+constexpr int kRows = 128;                  // query tokens per work item
 constexpr int kKeys = 128;                  // keys per tile
 constexpr int kDim = 128;                   // head_dim
 constexpr int kHalf = 128 * 128;            // bytes of a 128-row x 64-element half tile
 constexpr int kTile = 2 * kHalf;            // 32 KB
-constexpr int kOffQ = 0, kOffK = kTile, kOffV = 3 * kTile, kOffP = 5 * kTile;
-constexpr int kSmemBytes = 6 * kTile + 1024;
+constexpr int kOffQ = 0, kOffK = kTile, kOffV = 3 * kTile;
+constexpr int kSmemBytes = 5 * kTile + 1024;
 constexpr int kParts = 2;                   // softmax threads per query row and stream (each takes 64 columns)
 constexpr int kCols = kKeys / kParts;       // columns of a tile that one softmax thread handles
 constexpr int kStreamThreads = kRows * kParts;
@@ -62,15 +64,12 @@ constexpr uint32_t kTmemColumns = 512;      // S0 at 0, S1 at 128, O of stream 0
 constexpr float kRescaleThreshold = 8.0f;   // log2 of how far a tile's maximum may exceed the running one
 
 // barrier indices
-enum { Q_FULL = 0, K_FULL = 1, K_FREE = 3, V_FULL = 5, V_FREE = 7, S_FULL = 9, S_FREE = 11, P_READY = 13, PV_DONE = 14,
-       Q_FREE = 16, O_FREE = 17, BARRIERS = 18 };
+enum { Q_FULL = 0, K_FULL = 1, K_FREE = 3, V_FULL = 5, V_FREE = 7, S_FULL = 9, P_READY = 11, ITEM_DONE = 13, Q_FREE = 14,
+       O_FREE = 15, BARRIERS = 16 };
 // Tiles are counted over all items of a CTA (g): stage g & 1 of the rings and of the score accumulators, phase
-// parity (g >> 1) & 1; items are counted too (n): Q_FULL, Q_FREE and O_FREE complete once per item.
-// PV_DONE + (t & 1) for tile t: a wait on an mbarrier names a phase by its parity only, so a thread may only wait
-// for a phase when it knows that the phase before has completed.  A stream that takes every second tile waits
-// for the products of the tiles in between; with one barrier for all tiles it would see every second phase
-// only, with one for even and one for odd tiles it sees every phase of the one it waits on.
-
+// parity (g >> 1) & 1 (P_READY too has one barrier per stage: the two streams work on neighbouring tiles at the same
+// time, and the arrivals of one must not count for the other's tile); items are counted too (n): Q_FULL, Q_FREE,
+// ITEM_DONE and O_FREE complete once per item.
 __device__ int g_tc_attention_error = 0;
 int g_streams = 2;
 int g_ctas = 0;                             // for measurements: 0 = one CTA per SM
@@ -100,23 +99,20 @@ __device__ __forceinline__ void tmem_load_32_nowait(uint32_t address, float* v) 
 __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // One tile of the softmax for this thread's part (kCols columns starting at `first`) of its row: the scores are
-// read once (all loads in flight, one wait; then `scores_read` is told), then the visible maximum (columns low..high of the tile; all if
+// read once (all loads in flight, one wait), then the visible maximum (columns low..high of the tile; all if
 // !MASKED), which the kParts threads of a row exchange through `shared_max` (one float per part, kRows apart)
 // and the named barrier `team` of the stream's warps that hold the row's quarter of lanes; then the decision whether
 // the running maximum rises, and p = exp2(scale s - reference) packed to bf16.  Returns the sum of this thread's p.
 template <bool MASKED>
 __device__ __forceinline__ float softmax_tile(uint32_t scores, int first, int low, int high, float scale_log2,
                                               float& reference, float& factor, bool& grow,
-                                              uint32_t (&packed)[kCols / 2], float* shared_max, int part, int team,
-                                              uint32_t scores_read) {
+                                              uint32_t (&packed)[kCols / 2], float* shared_max, int part, int team) {
   float v[kCols];
 #pragma unroll
   for (int c0 = 0; c0 < kCols; c0 += 32) tmem_load_32_nowait(scores + first + c0, v + c0);
   tmem_load_wait();
 #pragma unroll
   for (int c = 0; c < kCols; ++c) asm volatile("" : "+f"(v[c])::"memory");   // no use of v moves above the wait
-  tensor_fence_before_sync();
-  barrier_arrive(scores_read);                                         // the scores are in registers
   float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};        // four chains instead of one
 #pragma unroll
   for (int c = 0; c < kCols; ++c)
@@ -240,7 +236,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < BARRIERS; ++i) {
-      const bool many = i == S_FREE || i == S_FREE + 1 || i == P_READY;   // every softmax thread of a stream arrives
+      const bool many = i == P_READY || i == P_READY + 1;                  // every softmax thread of a stream arrives
       const bool all = i == O_FREE;                                        // every softmax thread of every stream
       barrier_init(bar(i), all ? (uint32_t)(kStreamThreads * kStreams) : (many ? (uint32_t)kStreamThreads : 1u));
     }
@@ -331,7 +327,6 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           const int stage = g & 1;
           const uint32_t parity = (uint32_t)(g >> 1) & 1u;
           if (alive && !wait_barrier(bar(K_FULL + stage), parity)) { g_tc_attention_error = 2; alive = false; }
-          if (alive && !wait_barrier(bar(S_FREE + stage), parity ^ 1u)) { g_tc_attention_error = 2; alive = false; }
           tensor_fence_after_sync();
           const uint32_t a = smem_base + kOffQ, b = smem_base + kOffK + (uint32_t)stage * kTile;
 #pragma unroll
@@ -344,35 +339,34 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           mma_commit(bar(K_FREE + stage));
           if (t == w.tiles - 1) mma_commit(bar(Q_FREE));       // the item's last product with its queries
         };
-        // scores run two tiles ahead of the products with P: S(t + 2) goes into the accumulator of S(t) as soon as
-        // the softmax threads have read that (early in their work on tile t), so a stream finds its next scores
-        // ready when it is done with a tile
+        // P(t) is written over S(t) in tensor memory, so S(t + 2), which takes the same accumulator, is issued
+        // behind the product with P(t): the tensor cores run products in the order of issue, and while they work
+        // on one stream's tile the other stream's softmax threads work on theirs
         issue_scores(0);
         if (w.tiles > 1) issue_scores(1);
         for (int t = 0; t < w.tiles; ++t) {
-          if (t + 2 < w.tiles) issue_scores(t + 2);
           const int g = g0 + t;
           const int stage = g & 1;
           const uint32_t parity = (uint32_t)(g >> 1) & 1u;
           if (alive && !wait_barrier(bar(V_FULL + stage), parity)) { g_tc_attention_error = 2; alive = false; }
-          if (alive && !wait_barrier(bar(P_READY), (uint32_t)g & 1u)) { g_tc_attention_error = 2; alive = false; }
+          if (alive && !wait_barrier(bar(P_READY + stage), parity)) { g_tc_attention_error = 2; alive = false; }
           // the output accumulators are the last item's until every softmax thread has read them out
           if (t == 0 && n > 0 && alive && !wait_barrier(bar(O_FREE), (uint32_t)(n - 1) & 1u)) {
             g_tc_attention_error = 2;
             alive = false;
           }
           tensor_fence_after_sync();
-          const uint32_t a = smem_base + kOffP, b = smem_base + kOffV + (uint32_t)stage * kTile;
+          const uint32_t p = tmem_base + (uint32_t)stage * 128u, b = smem_base + kOffV + (uint32_t)stage * kTile;
 #pragma unroll
           for (int kk = 0; kk < kKeys / 16; ++kk) {
-            // P: 16 keys further along its 128-byte rows; V: 16 rows of keys further down
-            const uint32_t a_offset = (uint32_t)(kk >> 2) * kHalf + (uint32_t)(kk & 3) * 32u;
-            mma_bf16_ss(tmem_o + (uint32_t)(t % kStreams) * 128u, operand_descriptor(a + a_offset),
+            // P: 16 keys are 8 columns of packed pairs further on; V: 16 rows of keys further down
+            mma_bf16_ts(tmem_o + (uint32_t)(t % kStreams) * 128u, p + (uint32_t)kk * 8u,
                         operand_descriptor_mn_major(b + (uint32_t)kk * 2048u, kHalf), idesc_pv,
                         (t >= kStreams || kk > 0) ? 1u : 0u);
           }
-          mma_commit(bar(PV_DONE + (g & 1)));
           mma_commit(bar(V_FREE + stage));
+          if (t == w.tiles - 1) mma_commit(bar(ITEM_DONE));
+          if (t + 2 < w.tiles) issue_scores(t + 2);
         }
         g0 += w.tiles;
         ++n;
@@ -415,42 +409,29 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         float* shared_max = &exchange[stream][(t / kStreams) & 1][0][r];
         const int team = 1 + stream * 4 + quarter;
         const float sum = every ? softmax_tile<false>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
-                                                      shared_max, part, team, bar(S_FREE + stage))
+                                                      shared_max, part, team)
                                 : softmax_tile<true>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
-                                                     shared_max, part, team, bar(S_FREE + stage));
+                                                     shared_max, part, team);
         denominator = denominator * factor + sum;
-        // the product with the previous tile's P (the other stream's, if there are two) must be over before P
-        // changes, and this stream's previous product before its O does (the last item's products are over: every
-        // thread waited for the last of them before it read the result out)
-        if (t > 0) {
-          if (alive && !wait_barrier(bar(PV_DONE + ((g - 1) & 1)), (uint32_t)((g - 1) >> 1) & 1u)) {
-            g_tc_attention_error = 3;
-            alive = false;
-          }
-          tensor_fence_after_sync();
-          if (t >= kStreams && __any_sync(0xffffffffu, grow)) {
+        // This stream's previous product (tile t - kStreams) is over: S(t) was issued behind it, and the scores'
+        // barrier completes only when everything issued before it has.  So its O may be rescaled now.
+        if (t >= kStreams && __any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-            for (int c0 = 0; c0 < kDim / kParts; c0 += 32) {
-              float o[32];
-              tmem_load_32(my_o + first + c0, o);
+          for (int c0 = 0; c0 < kDim / kParts; c0 += 32) {
+            float o[32];
+            tmem_load_32(my_o + first + c0, o);
 #pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] *= factor;
-              tmem_store_32(my_o + first + c0, o);
-            }
-            tmem_store_wait();
+            for (int i = 0; i < 32; ++i) o[i] *= factor;
+            tmem_store_32(my_o + first + c0, o);
           }
         }
-        // P as the A operand: rows of 128 bytes (64 keys: this thread's half), 16-byte chunks swizzled by the row
-        unsigned char* p_row = smem + kOffP + (size_t)part * kHalf + (size_t)r * 128;
-#pragma unroll
-        for (int chunk = 0; chunk < 8; ++chunk) {
-          const int where = chunk ^ (r & 7);
-          *reinterpret_cast<uint4*>(p_row + where * 16) =
-              make_uint4(packed[4 * chunk], packed[4 * chunk + 1], packed[4 * chunk + 2], packed[4 * chunk + 3]);
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // P as the A operand of the product with V, in tensor memory over the scores it came from: this row's lane,
+        // two keys per 32-bit column, this thread's kCols keys from column first / 2 on (its partner has read its
+        // half of the scores: the two met at the row's barrier inside softmax_tile)
+        tmem_store_32_bits(scores + (uint32_t)(first / 2), packed);
+        tmem_store_wait();
         tensor_fence_before_sync();
-        barrier_arrive(bar(P_READY));
+        barrier_arrive(bar(P_READY + stage));
       }
       // every softmax thread learns every stream's maximum and denominator (the sum of its two threads' parts)
       const int slot = n & 1;
@@ -467,9 +448,8 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         weight[other] = theirs > -INFINITY ? fast_exp2(theirs - top) : 0.0f;
         total += (denominators[slot][other][0][r] + denominators[slot][other][1][r]) * weight[other];
       }
-      // (every thread has passed the named barrier above, so the products before the last one are over)
-      const int last = g0 + w.tiles - 1;
-      if (alive && !wait_barrier(bar(PV_DONE + (last & 1)), (uint32_t)(last >> 1) & 1u)) {
+      // the item's last product is over
+      if (alive && !wait_barrier(bar(ITEM_DONE), (uint32_t)n & 1u)) {
         g_tc_attention_error = 3;
         alive = false;
       }
