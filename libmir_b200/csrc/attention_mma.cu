@@ -57,6 +57,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
+// 2^x for x <= 0 (or -inf): the hardware approximation (2 ulp), far below what rounding the weights to bf16 loses.
+__device__ __forceinline__ float exp2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float quad_max(float v) {
   v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
   return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
@@ -325,12 +331,12 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
     const float tile_max = quad_max(fmaxf(fmaxf(v00, v01), fmaxf(v10, v11)));
     const float next = fmaxf(m, tile_max);
     const float ref = next == -INFINITY ? 0.0f : next;
-    const float corr = exp2f(m - ref);
+    const float corr = exp2_fast(m - ref);
     m = next;
-    v00 = exp2f(v00 - ref);
-    v01 = exp2f(v01 - ref);
-    v10 = exp2f(v10 - ref);
-    v11 = exp2f(v11 - ref);
+    v00 = exp2_fast(v00 - ref);
+    v01 = exp2_fast(v01 - ref);
+    v10 = exp2_fast(v10 - ref);
+    v11 = exp2_fast(v11 - ref);
     l = l * corr + (v00 + v01 + v10 + v11);
     if (__any_sync(0xffffffffu, corr != 1.0f)) {                // the maximum moved for some head: rescale O^T
       const float corr_a = __shfl_sync(0xffffffffu, corr, quad * 8);        // head quad*2   lives in lanes 8*quad..
