@@ -156,7 +156,7 @@ def main() -> int:
                         help="up to how many CTAs decode attention keeps three tiles in flight per warp")
     parser.add_argument("--set", action="append", default=[], metavar="NAME=VALUE",
                         help="set a tuning constant of libmir_b200.kernels or an option of the native product dispatch (an "
-                             "integer), e.g. DECODE_PARTITION_KEYS=512 or few_rows_max=16")
+                             "integer), e.g. PREFILL_TENSOR_CORES=0, few_rows_max=16 or decode_tensor_cores=0")
     parser.add_argument("--stream-shape", default=None, metavar="SPLITS,RING_KB,TILE_ROWS",
                         help="fix the shape of the weight-streaming product (0 = chosen by the launcher), e.g. 0,56,0")
     parser.add_argument("--no-fold-norm", action="store_true",
@@ -431,7 +431,7 @@ def main() -> int:
         positions = torch.full((batch,), prompt_tokens - 1, dtype=torch.int32, device="cuda")
         qkv = torch.randn(batch, qkv_width, device="cuda", dtype=bf16)
         mixed = torch.empty(batch, heads * dim, device="cuda", dtype=bf16)
-        partition, count = kernels.decode_partitioning(batch, kv_heads, prompt_tokens)
+        partition, count = kernels.decode_partitioning(batch, heads, kv_heads, dim, PAGE_SIZE, prompt_tokens)
         scratch = torch.empty(max(1, kernels.decode_attention_scratch_floats(batch, heads, dim, count)), device="cuda")
         scale = 1.0 / math.sqrt(dim)
         def build_decode_attention():

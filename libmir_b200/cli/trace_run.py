@@ -97,7 +97,8 @@ def main(argv=None) -> int:
                   "graphs_captured": len(graphs.graphs) if graphs is not None else 0,
                   "errors": {"stream_linear": kernels.stream_linear_error(),
                              "tensor_core_linear": kernels.tensor_core_linear_error(),
-                             "prefill_attention": kernels.prefill_attention_error()}
+                             "prefill_attention": kernels.prefill_attention_error(),
+                             "decode_attention": kernels.decode_attention_error()}
                   if args.dtype == "bfloat16" else {}}
         Path(args.report).write_text(json.dumps(report, indent=1, default=str))
     return 0

@@ -713,6 +713,24 @@ MIR_EXPORT long long mir_decode_attention_scratch_floats(int rows, int heads, in
   return floats > (unsigned __int128)(1ll << 62) ? -1 : (long long)floats;
 }
 
+// The merge of the partitions' results alone (the tcgen05 decode kernel leaves them in the same layout): scratch as
+// mir_decode_attention_bf16 lays it out, partial outputs then (maximum, denominator) pairs.
+MIR_EXPORT int mir_decode_merge_bf16(const float* partial_o, const float* partial_ml, const int* positions, int rows,
+                                     int heads, int head_dim, int window, int partition, int num_partitions, void* out,
+                                     cudaStream_t stream) {
+  if (rows <= 0 || rows > 65535 || heads <= 0 || partition <= 0 || num_partitions <= 0 || window < 0 ||
+      (head_dim != 64 && head_dim != 128) || partial_o == nullptr || partial_ml == nullptr) {
+    mir_set_error("decode_merge: bad sizes (rows %d, heads %d, head_dim %d, partition %d, partitions %d)", rows, heads,
+                  head_dim, partition, num_partitions);
+    return MIR_BAD_ARGUMENT;
+  }
+  if (head_dim == 64)
+    return mir_launch("decode_merge", decode_merge_kernel<64>, dim3(heads, rows), dim3(kMergeWarps * 32), 0, stream, 0,
+                      partial_o, partial_ml, positions, heads, window, partition, num_partitions, (bf16*)out);
+  return mir_launch("decode_merge", decode_merge_kernel<128>, dim3(heads, rows), dim3(kMergeWarps * 32), 0, stream, 0,
+                    partial_o, partial_ml, positions, heads, window, partition, num_partitions, (bf16*)out);
+}
+
 // One token per row.  `partition` (a multiple of 64) is how many keys one CTA takes; num_partitions must be
 // >= ceil(longest context / partition).  scratch holds mir_decode_attention_scratch_floats floats.
 MIR_EXPORT int mir_decode_attention_bf16(const void* q, long long q_stride, void* out, const void* k_pages,

@@ -40,8 +40,8 @@ LIBRARIES = {
     # everything of `core` as well: the layer executor of this library runs both engine dtypes
     "bf16": {
         "sources": ["runtime.cu", "elementwise.cu", "qk_rope_store.cu", "attention_generic.cu", "gemm_f32.cu",
-                    "gemm_lt.cu", "attention_mma.cu", "gemm_tc.cu", "attention_tc.cu", "gemm_tc_stream.cu",
-                    "ops_bf16.cu", "executor.cu"],
+                    "gemm_lt.cu", "attention_mma.cu", "gemm_tc.cu", "attention_tc.cu", "attention_tc_decode.cu",
+                    "gemm_tc_stream.cu", "ops_bf16.cu", "executor.cu"],
         "headers": ["no_alloc.h", "tcgen05.cuh"],
         "link": ["-lcublasLt"],
         "defines": ["-DMIR_WITH_BF16"],

@@ -17,6 +17,7 @@ enum MirStatus : int {
 
 void mir_set_error(const char* fmt, ...);
 int mir_check_launch(const char* what);
+int mir_sm_count();
 void mir_count_launch(const char* what);   // launches that do not end in mir_check_launch (library products)
 
 // Programmatic dependent launch: a kernel launched this way may be scheduled while the kernel before it in

@@ -79,10 +79,8 @@ struct MirStepDesc {
   long long attention_scratch_floats;
   void* workspace;               // for the library products
   size_t workspace_bytes;
-  int decode_partition_keys;
   int prefill_tensor_cores;      // 0 never the tcgen05 prompt kernel
   int prefill_tensor_core_min_portion;
-  int pad;
   const float* norm_after;       // weight of the norm that the block after this run starts with, or null
   cudaStream_t stream;
 };
@@ -170,12 +168,14 @@ struct Run {
       const int singles = step.decode_only ? step.rows : step.singles;
       if (singles > 0) {
         const int longest = step.decode_only ? step.max_context : step.single_context;
-        const int partition = step.decode_partition_keys;
+        const int partition = mir_decode_partition_keys(singles, layer.heads, layer.kv_heads, layer.head_dim,
+                                                        layer.page_size, longest);
         const int count = std::max(1, (longest + partition - 1) / partition);
-        MIR_TRY(mir_decode_attention_bf16(step.qkv, width, step.mixed, layer.k_pages, layer.v_pages, group.block_table,
-                                          group.table_width, step.positions, singles, layer.page_size, layer.heads,
-                                          layer.kv_heads, layer.head_dim, layer.scale, layer.window, partition, count,
-                                          step.attention_scratch, step.attention_scratch_floats, step.stream));
+        MIR_TRY(mir_decode_attention_paged_bf16(step.qkv, width, step.mixed, layer.k_pages, layer.v_pages,
+                                                layer.cache_rows, group.block_table, group.table_width, step.positions,
+                                                singles, layer.page_size, layer.heads, layer.kv_heads, layer.head_dim,
+                                                layer.scale, layer.window, partition, count, step.attention_scratch,
+                                                step.attention_scratch_floats, step.stream));
       }
       if (singles < step.rows) {
         const int rows = step.rows - singles, portion_tokens = step.tokens - singles;

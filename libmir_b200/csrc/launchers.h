@@ -32,12 +32,20 @@ int mir_gemm_tc_stream_bf16(int mode, const void* x, int ldx, const void* w, con
                             cudaStream_t stream);
 int mir_gemm_tc_bf16(int mode, const void* x, int ldx, const void* w, const void* bias, void* out, int ldo, int m, int n,
                      int k, int up_offset, cudaStream_t stream);
-// attention_mma.cu, attention_tc.cu
+// attention_mma.cu, attention_tc.cu, attention_tc_decode.cu
 long long mir_decode_attention_scratch_floats(int rows, int heads, int head_dim, int num_partitions);
 int mir_decode_attention_bf16(const void* q, long long q_stride, void* out, const void* k_pages, const void* v_pages,
                               const int* block_table, int table_width, const int* positions, int rows, int page_size,
                               int heads, int kv_heads, int head_dim, float scale, int window, int partition,
                               int num_partitions, float* scratch, long long scratch_floats, cudaStream_t stream);
+int mir_decode_merge_bf16(const float* partial_o, const float* partial_ml, const int* positions, int rows, int heads,
+                          int head_dim, int window, int partition, int num_partitions, void* out, cudaStream_t stream);
+int mir_decode_attention_tc_takes(int head_dim, int page_size, int partition);
+int mir_decode_attention_tc_bf16(const void* q, long long q_stride, void* out, const void* k_pages, const void* v_pages,
+                                 long long cache_rows, const int* block_table, int table_width, const int* positions,
+                                 int rows, int page_size, int heads, int kv_heads, int head_dim, float scale, int window,
+                                 int partition, int num_partitions, float* scratch, long long scratch_floats,
+                                 cudaStream_t stream);
 int mir_prefill_attention_bf16(const void* q, long long q_stride, void* out, const void* k_pages, const void* v_pages,
                                const int* block_table, int table_width, const int* query_starts,
                                const int* context_lens, int num_rows, int tokens, int page_size, int heads,
@@ -56,6 +64,12 @@ int mir_linear_bf16(const void* x, int ldx, const void* w, const void* bias, voi
 int mir_gate_up_silu_bf16(const void* x, int ldx, const void* w_gate_up, void* out, int m, int inter, int k,
                           const float* sumsq, int sumsq_tiles, float eps, void* gate_up_scratch, void* workspace,
                           size_t workspace_bytes, cudaStream_t stream);
+int mir_decode_attention_paged_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                    const void* v_pages, long long cache_rows, const int* block_table, int table_width,
+                                    const int* positions, int rows, int page_size, int heads, int kv_heads,
+                                    int head_dim, float scale, int window, int partition, int num_partitions,
+                                    float* scratch, long long scratch_floats, cudaStream_t stream);
+int mir_decode_partition_keys(int rows, int heads, int kv_heads, int head_dim, int page_size, int longest);
 int mir_get_option(const char* name);
 #endif
 }

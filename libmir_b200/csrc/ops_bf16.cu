@@ -8,6 +8,7 @@
 //                                                            (cuda/src/backend/linear/mod.rs:141-194)
 //
 // The thresholds are options with the measurements that chose them; mir_set_option changes them for A/B runs.
+#include <algorithm>
 #include <cstring>
 #include "common.cuh"
 #define MIR_WITH_BF16
@@ -29,12 +30,22 @@ int g_folded_norm_max_rows = 32;
 int g_tensor_core_min_rows = 128;
 // The streaming epilogues in use (bit 0 store, 1 accumulate, 2 float32, 3 SwiGLU); the rest go to the library.
 int g_few_rows_modes = 0xF;
+// Whether single decoded tokens run the tcgen05 attention kernel where it takes the sizes (else the mma.sync kernel).
+int g_decode_tensor_cores = 1;
+// Keys one CTA of the mma.sync decode kernel takes (a multiple of 64, at most 512).  Measured (attention and merge,
+// us, 256 against 512 keys): batch 1 at 2,120 keys 7.8 / 15.9, at 32,768 keys 37 / 45; batch 8 at 2,120 keys 20.0 /
+// 20.7, at 8,192 keys 54 / 84; batch 32 at 2,120 keys 56 / 66; batch 64 102 / 106.
+int g_decode_partition_keys = 256;
+// Keys one CTA of the tcgen05 decode kernel takes: 0 lets mir_decode_partition_keys choose, else this many.
+int g_decode_tc_partition_keys = 0;
 
 enum Mode : int { STORE = 0, ACCUM = 1, F32 = 2, SWIGLU = 3 };
 
 struct Option { const char* name; int* value; };
 Option g_options[] = {{"few_rows_max", &g_few_rows_max}, {"folded_norm_max_rows", &g_folded_norm_max_rows},
-                      {"tensor_core_min_rows", &g_tensor_core_min_rows}, {"few_rows_modes", &g_few_rows_modes}};
+                      {"tensor_core_min_rows", &g_tensor_core_min_rows}, {"few_rows_modes", &g_few_rows_modes},
+                      {"decode_tensor_cores", &g_decode_tensor_cores}, {"decode_partition_keys", &g_decode_partition_keys},
+                      {"decode_tc_partition_keys", &g_decode_tc_partition_keys}};
 
 bool few_rows_ok(const void* x, int ldx, int m, int k) {
   return m > 0 && m <= g_few_rows_max && m <= 128 && k % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0;
@@ -106,4 +117,47 @@ MIR_EXPORT int mir_gate_up_silu_bf16(const void* x, int ldx, const void* w_gate_
                                 workspace, workspace_bytes, stream);
   if (status != MIR_OK) return status;
   return mir_silu_mul(1, gate_up_scratch, out, m, inter, stream);
+}
+
+// How many keys one CTA of split decode attention takes for `rows` single tokens whose longest context (or the
+// width of the block tables of a captured step) is `longest` keys; the number of partitions is ceil(longest / that).
+// The tcgen05 kernel keeps three CTAs on an SM, and a CTA costs about 5 us to start and end and 2.5 us per tile of
+// 128 keys, so the choice is the partition with the fewest waves x (5 + 2.5 tiles): measured (attention and merge,
+// us, partitions of 128 / 256 / 512 / 1,024 keys) batch 1 at 2,112 keys 7.8 / 9.2 / 12.6 / 19.2; batch 8: 23.1 / 20.0 /
+// 19.1 / 23.3; batch 32: 73.5 / 56.3 / 52.5 / 55.6; batch 64: 142 / 106 / 96.1 / 95.9; batch 8 at 8,192 keys 76.3 / 54.0 /
+// 51.2 / 54.7; batch 1 at 32,768 keys 49.2 / 33.8 / 31.2 / 28.1; batch 8 at 32,768 keys 262 / 197 / 174 / 169.
+MIR_EXPORT int mir_decode_partition_keys(int rows, int heads, int kv_heads, int head_dim, int page_size, int longest) {
+  if (!g_decode_tensor_cores || !mir_decode_attention_tc_takes(head_dim, page_size, 128)) return g_decode_partition_keys;
+  if (g_decode_tc_partition_keys > 0) return g_decode_tc_partition_keys;
+  const long long group = kv_heads > 0 ? (heads + kv_heads - 1) / kv_heads : 1;
+  const long long units = (long long)std::max(rows, 1) * std::max(kv_heads, 1) * ((group + 15) / 16);
+  const long long resident = 3ll * mir_sm_count();
+  int best = 128;
+  double best_cost = 0.0;
+  for (int partition = 128; partition <= 1024; partition *= 2) {
+    const long long full = std::max(longest, 1) / partition, rest = std::max(longest, 1) % partition;
+    // CTAs that take a whole partition; the one with the rest of the keys is short and fills a gap
+    const long long ctas = units * (full + (rest * 2 > partition ? 1 : 0));
+    const long long waves = std::max(1ll, (ctas + resident - 1) / resident);
+    const double cost = (double)waves * (5.0 + 2.5 * std::min(partition, std::max(longest, 1) + 127) / 128.0);
+    if (partition == 128 || cost < best_cost) { best = partition; best_cost = cost; }
+  }
+  return best;
+}
+
+// Attention of single decoded tokens over the pages: the tcgen05 kernel where it takes the sizes, else the mma.sync
+// kernel.  Arguments as mir_decode_attention_bf16, and how many token rows the cache tensors have.
+MIR_EXPORT int mir_decode_attention_paged_bf16(const void* q, long long q_stride, void* out, const void* k_pages,
+                                               const void* v_pages, long long cache_rows, const int* block_table,
+                                               int table_width, const int* positions, int rows, int page_size,
+                                               int heads, int kv_heads, int head_dim, float scale, int window,
+                                               int partition, int num_partitions, float* scratch,
+                                               long long scratch_floats, cudaStream_t stream) {
+  if (g_decode_tensor_cores && cache_rows > 0 && mir_decode_attention_tc_takes(head_dim, page_size, partition))
+    return mir_decode_attention_tc_bf16(q, q_stride, out, k_pages, v_pages, cache_rows, block_table, table_width,
+                                        positions, rows, page_size, heads, kv_heads, head_dim, scale, window, partition,
+                                        num_partitions, scratch, scratch_floats, stream);
+  return mir_decode_attention_bf16(q, q_stride, out, k_pages, v_pages, block_table, table_width, positions, rows,
+                                   page_size, heads, kv_heads, head_dim, scale, window, partition, num_partitions,
+                                   scratch, scratch_floats, stream);
 }

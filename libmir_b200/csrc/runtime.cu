@@ -62,6 +62,20 @@ int mir_check_launch(const char* what) {
 
 MIR_EXPORT const char* mir_last_error() { return g_error; }
 
+// Multiprocessors of the current device (148 on a B200; also the answer when the device cannot be asked).
+int mir_sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int device = 0, found = 0;
+    if (cudaGetDevice(&device) == cudaSuccess &&
+        cudaDeviceGetAttribute(&found, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && found > 0)
+      count = found;
+    else
+      return 148;
+  }
+  return count;
+}
+
 MIR_EXPORT int mir_abi_version() { return 1; }
 
 // 0 off, 1 every kernel, 2 only the kernels that stream weights before they wait.  Measured inside captured

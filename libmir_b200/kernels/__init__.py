@@ -8,6 +8,7 @@ refuses its sizes, a KernelError is raised.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from ctypes import c_double, c_float, c_int, c_longlong, c_size_t, c_void_p
 from typing import Optional
@@ -44,6 +45,12 @@ _SIGNATURES = {
         "mir_decode_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                       c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p,
                                       c_longlong, c_void_p],
+        "mir_decode_attention_paged_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                                            c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                            c_int, c_void_p, c_longlong, c_void_p],
+        "mir_decode_attention_tc_takes": [c_int, c_int, c_int],
+        "mir_decode_partition_keys": [c_int, c_int, c_int, c_int, c_int, c_int],
+        "mir_decode_attention_tc_error": [],
         "mir_prefill_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "mir_prefill_attention_tc_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int,
@@ -156,13 +163,25 @@ MIR_CANNOT_FOLD = 4     # a product was given a folded norm's rows that it canno
 
 def set_option(name: str, value: int) -> None:
     """A threshold of the bfloat16 product dispatch (csrc/ops_bf16.cu): few_rows_max, folded_norm_max_rows,
-    tensor_core_min_rows, few_rows_modes (bits: store, accumulate, float32, SwiGLU)."""
+    tensor_core_min_rows, few_rows_modes (bits: store, accumulate, float32, SwiGLU), decode_tensor_cores,
+    decode_partition_keys, decode_tc_partition_keys."""
     lib = library("bf16")
     _check(lib, lib.mir_set_option(name.encode(), int(value)))
 
 
 def get_option(name: str) -> int:
     return int(library("bf16").mir_get_option(name.encode()))
+
+
+@contextlib.contextmanager
+def option(name: str, value: int):
+    """An option of the native dispatch set for the duration of a `with` block (measurements, tests)."""
+    before = get_option(name)
+    set_option(name, value)
+    try:
+        yield
+    finally:
+        set_option(name, before)
 
 
 def _check(lib: ctypes.CDLL, status: int) -> None:
@@ -328,16 +347,14 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
 
 
 FAST_HEAD_DIMS = (64, 128)      # what the tensor-core attention kernels take; other sizes use the reference kernel
-DECODE_PARTITION_KEYS = 256     # keys one CTA of split decode attention takes (a multiple of 64, at most 512)
 
 
-def decode_partitioning(rows: int, kv_heads: int, max_context: int) -> tuple:
-    """(keys per partition, partitions) for split decode attention.  256 keys: long contexts at small batch
-    spread over the whole GPU, and the merge shares the partitions out over its warps, so many partitions cost
-    little.  Measured (attention and merge, us, 256 against 512 keys): batch 1 at 2,120 keys 7.8 / 15.9, at
-    32,768 keys 37 / 45; batch 8 at 2,120 keys 20.0 / 20.7, at 8,192 keys 54 / 84, at 32,768 keys 184 / 190;
-    batch 32 at 2,120 keys 56 / 66; batch 64 102 / 106."""
-    partition = DECODE_PARTITION_KEYS
+def decode_partitioning(rows: int, heads: int, kv_heads: int, head_dim: int, page_size: int, max_context: int) -> tuple:
+    """(keys per partition, partitions) for split decode attention of `rows` single tokens whose longest context
+    (or block-table width) is max_context keys.  The choice is native (csrc/ops_bf16.cu: mir_decode_partition_keys),
+    the same for the Python launcher and the layer executor; options decode_partition_keys (the mma.sync kernel) and
+    decode_tc_partition_keys (the tcgen05 kernel, 0 = chosen by the cost of its waves) change it."""
+    partition = int(library("bf16").mir_decode_partition_keys(rows, heads, kv_heads, head_dim, page_size, max_context))
     return partition, max(1, -(-max_context // partition))
 
 
@@ -359,9 +376,12 @@ def decode_attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor
              and positions.numel() >= rows and block_table.shape[0] >= rows, "decode_attention: bad metadata")
     _require(scratch is None or scratch.dtype == torch.float32, "decode_attention: scratch must be float32")
     lib = library("bf16")
-    _check(lib, lib.mir_decode_attention_bf16(
-        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
-        block_table.shape[1], positions.data_ptr(), rows, page_size, heads, kv_heads, head_dim, scale,
+    _require(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape[0] == v_pages.shape[0],
+             "decode_attention: the cache tensors must be contiguous [token rows, kv_heads, head_dim]")
+    _check(lib, lib.mir_decode_attention_paged_bf16(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
+        block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), rows, page_size, heads, kv_heads, head_dim,
+        scale,
         int(window or 0), partition, num_partitions, _ptr(scratch), 0 if scratch is None else scratch.numel(),
         _stream()))
 
@@ -413,6 +433,18 @@ def set_prefill_softmax_streams(streams: int) -> None:
     """For measurements: over how many softmax streams the tcgen05 attention splits a row's key tiles, 1 or 2."""
     lib = library("bf16")
     _check(lib, lib.mir_prefill_attention_tc_set_streams(int(streams)))
+
+
+def decode_attention_error() -> int:
+    """0 unless a bounded wait of the tcgen05 decode attention kernel ran out (synchronises the device)."""
+    return int(library("bf16").mir_decode_attention_tc_error())
+
+
+def decode_attention_takes_tensor_cores(head_dim: int, page_size: int, partition: int) -> bool:
+    """Whether single decoded tokens of these sizes run the tcgen05 kernel (and the option decode_tensor_cores is on)."""
+    lib = library("bf16")
+    return bool(lib.mir_get_option(b"decode_tensor_cores")) and \
+        bool(lib.mir_decode_attention_tc_takes(head_dim, page_size, partition))
 
 
 def prefill_attention_error() -> int:

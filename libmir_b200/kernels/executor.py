@@ -53,8 +53,7 @@ class StepDesc(Structure):
         ("sumsq", c_void_p * 2), ("weighted", c_void_p * 2),
         ("attention_scratch", c_void_p), ("attention_scratch_floats", c_longlong),
         ("workspace", c_void_p), ("workspace_bytes", c_size_t),
-        ("decode_partition_keys", c_int), ("prefill_tensor_cores", c_int),
-        ("prefill_tensor_core_min_portion", c_int), ("pad", c_int),
+        ("prefill_tensor_cores", c_int), ("prefill_tensor_core_min_portion", c_int),
         ("norm_after", c_void_p), ("stream", c_void_p),
     ]
 
@@ -111,13 +110,15 @@ class LayerRun:
         self.heads = max(d.heads for d in layers)
         self.head_dim = max(d.head_dim for d in layers)
         self.fast_attention = self.bf16 and any(d.head_dim in (64, 128) for d in layers)
+        self.attention_shapes = sorted({(d.heads, d.kv_heads, d.head_dim, d.page_size) for d in layers
+                                        if d.head_dim in (64, 128)})
 
     def execute(self, ctx, residual: torch.Tensor) -> None:
         """Scratch from the step's arena (one set for the whole run: the layers use it one after the other), the
         step's metadata, one native call."""
-        from . import (DECODE_PARTITION_KEYS, FUSE_NORM_INTO_PRODUCT, PREFILL_TENSOR_CORE_MIN_PORTION,
+        from . import (FUSE_NORM_INTO_PRODUCT, PREFILL_TENSOR_CORE_MIN_PORTION,
                        PREFILL_TENSOR_CORES, NORM_STAT_STRIDE, _lt_workspace, _stream, decode_attention_scratch_floats,
-                       few_rows_max, get_option, sumsq_tiles)
+                       decode_partitioning, few_rows_max, get_option, sumsq_tiles)
         tokens, hidden = residual.shape
         dtype = self.dtype
         step = StepDesc()
@@ -151,15 +152,16 @@ class LayerRun:
         if self.fast_attention:
             singles = ctx.num_rows if ctx.decode_only else ctx.single_rows
             longest = ctx.max_context if ctx.decode_only else ctx.single_context
-            count = max(1, -(-longest // DECODE_PARTITION_KEYS))
-            floats = decode_attention_scratch_floats(singles, self.heads, self.head_dim, count)
+            floats = max(decode_attention_scratch_floats(singles, heads, head_dim,
+                                                         decode_partitioning(singles, heads, kv_heads, head_dim,
+                                                                             page_size, longest)[1])
+                         for heads, kv_heads, head_dim, page_size in self.attention_shapes) if singles else 0
             if floats:
                 step.attention_scratch = ctx.alloc((floats,), torch.float32).data_ptr()
                 step.attention_scratch_floats = floats
         if self.bf16:
             workspace = _lt_workspace(residual.device)
             step.workspace, step.workspace_bytes = workspace.data_ptr(), workspace.numel()
-        step.decode_partition_keys = DECODE_PARTITION_KEYS
         step.prefill_tensor_cores = int(PREFILL_TENSOR_CORES)
         step.prefill_tensor_core_min_portion = PREFILL_TENSOR_CORE_MIN_PORTION
         step.stream = _stream()

@@ -52,11 +52,21 @@ def close(got, want, tol=2e-2):
     assert torch.isfinite(got).all() and error <= bound, f"max |diff| {error:.3e} > {bound:.3e}"
 
 
+def decode_kernel_counts(kernels):
+    counts = kernels.launch_counts()
+    return counts.get("decode_attention_tc", 0), counts.get("decode_attention", 0)
+
+
+@pytest.mark.parametrize("tensor_cores", [True, False])
 @pytest.mark.parametrize("heads,kv_heads,dim,page,window,partition", [
     (32, 8, 128, 16, None, 512), (32, 8, 128, 16, None, 64), (8, 8, 64, 8, None, 128), (16, 1, 128, 16, 300, 256),
     (40, 2, 64, 4, None, 64), (6, 3, 128, 32, 70, 64), (4, 4, 128, 1, None, 192), (64, 8, 128, 16, None, 128),
-    (8, 2, 128, 12, None, 256), (6, 2, 64, 2, 45, 128)])
-def test_decode_attention(heads, kv_heads, dim, page, window, partition):
+    (8, 2, 128, 12, None, 256), (6, 2, 64, 2, 45, 128), (40, 2, 128, 32, None, 128), (12, 4, 128, 128, 100, 256),
+    (8, 2, 128, 8, None, 384), (6, 3, 128, 64, 70, 128)])
+def test_decode_attention(heads, kv_heads, dim, page, window, partition, tensor_cores):
+    """Both decode kernels: the tcgen05 kernel takes head_dim 128 with pages of 8..128 keys that divide 128 and
+    partitions that are multiples of 128 keys (groups of 1, 3, 4, 8, 16 and 20 query heads here), the mma.sync kernel
+    everything else, and everything when the option decode_tensor_cores is off."""
     from libmir_b200 import kernels
     rng = np.random.default_rng(heads + dim)
     torch.manual_seed(heads * dim)
@@ -75,12 +85,19 @@ def test_decode_attention(heads, kv_heads, dim, page, window, partition):
     floats = kernels.decode_attention_scratch_floats(rows, heads, dim, count)
     scratch = torch.full((max(floats, 1),), float("nan"), device="cuda")
     out = torch.full((rows, heads * dim), 9.0, device="cuda", dtype=BF16)
-    kernels.decode_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table), cuda(positions), page, heads,
-                             kv_heads, dim, scale, window, partition, count, scratch if floats else None)
+    takes = dim == 128 and page in (8, 16, 32, 64, 128) and partition % 128 == 0
+    with kernels.option("decode_tensor_cores", int(tensor_cores)):
+        assert kernels.decode_attention_takes_tensor_cores(dim, page, partition) == (takes and tensor_cores)
+        before = decode_kernel_counts(kernels)
+        kernels.decode_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table), cuda(positions), page, heads,
+                                 kv_heads, dim, scale, window, partition, count, scratch if floats else None)
+        after = decode_kernel_counts(kernels)
+    assert (after[0] - before[0], after[1] - before[1]) == ((1, 0) if takes and tensor_cores else (0, 1))
     expected = torch.cat([expect(q, k, v, scale, window, slice(n - 1, n)) for q, k, v, n in zip(qs, ks, vs, lengths)])
     close(out[:len(lengths)].reshape(len(lengths), heads, dim), expected)
     if count > 1:
         assert float(out[len(lengths):].abs().max()) == 0.0     # padding rows give zeros
+    assert kernels.decode_attention_error() == 0
 
 
 @pytest.mark.parametrize("heads,kv_heads,dim,page,window", [
@@ -142,7 +159,7 @@ def test_prefill_attention_on_tcgen05(heads, kv_heads, page, window):
     close(out.reshape(tokens, heads, dim), expected)
 
 
-@pytest.mark.parametrize("kind", ["decode", "prefill", "prefill_tcgen05"])
+@pytest.mark.parametrize("kind", ["decode", "decode_tcgen05", "prefill", "prefill_tcgen05"])
 def test_one_far_key_among_hundreds_and_the_windows_edge(kind):
     from libmir_b200 import kernels
     heads, kv_heads, dim, page, n = 8, 2, 128, 16, 1100
@@ -159,12 +176,13 @@ def test_one_far_key_among_hundreds_and_the_windows_edge(kind):
         k_pool, v_pool, table = build_pool([k], [v], page, np.random.default_rng(strong_key), garbage=0.0)
         packed = torch.cat([q.reshape(1, -1), torch.zeros(1, 2 * kv_heads * dim, dtype=BF16)], dim=1)
         out = torch.empty(1, heads * dim, device="cuda", dtype=BF16)
-        if kind == "decode":
+        if kind.startswith("decode"):
             count = -(-n // 128)
             scratch = torch.empty(kernels.decode_attention_scratch_floats(1, heads, dim, count), device="cuda")
-            kernels.decode_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table),
-                                     cuda(torch.tensor([n - 1], dtype=torch.int32)), page, heads, kv_heads, dim, 1.0,
-                                     window, 128, count, scratch)
+            with kernels.option("decode_tensor_cores", int(kind == "decode_tcgen05")):
+                kernels.decode_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table),
+                                         cuda(torch.tensor([n - 1], dtype=torch.int32)), page, heads, kv_heads, dim,
+                                         1.0, window, 128, count, scratch)
         else:
             kernels.prefill_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table),
                                       cuda(torch.tensor([0, 1], dtype=torch.int32)),
@@ -195,7 +213,9 @@ def pool_after_poison(k_pool, v_pool, page):
 
 @pytest.mark.parametrize("kind,dim,page,window,length,portion", [
     ("decode", 128, 8, 1024, 2100, 1), ("decode", 64, 4, 200, 700, 1), ("decode", 128, 4, 70, 333, 1),
-    ("decode", 64, 16, 100, 1000, 1), ("decode", 128, 1, 40, 300, 1), ("prefill", 128, 16, 1024, 2106, 10), ("prefill", 64, 16, 1024, 2106, 10),
+    ("decode", 64, 16, 100, 1000, 1), ("decode", 128, 1, 40, 300, 1), ("decode_tcgen05", 128, 8, 1024, 2100, 1),
+    ("decode_tcgen05", 128, 16, 300, 900, 1), ("decode_tcgen05", 128, 128, 200, 1000, 1),
+    ("prefill", 128, 16, 1024, 2106, 10), ("prefill", 64, 16, 1024, 2106, 10),
     ("prefill", 64, 8, 100, 700, 70), ("prefill", 128, 4, 130, 450, 3), ("prefill_tcgen05", 128, 16, 1024, 2106, 40)])
 def test_pages_that_a_window_has_released_are_never_read(kind, dim, page, window, length, portion):
     """The block table holds -1 for every page that lies wholly behind the window of the first query (what the cache
@@ -222,12 +242,15 @@ def test_pages_that_a_window_has_released_are_never_read(kind, dim, page, window
     packed = torch.cat([q[first_query:].reshape(portion, -1), torch.zeros(portion, 2 * kv_heads * dim, dtype=BF16)],
                        dim=1).contiguous()
     out = torch.full((portion, heads * dim), 9.0, device="cuda", dtype=BF16)
-    if kind == "decode":
+    if kind.startswith("decode"):
         partition = 128
         count = -(-length // partition)
         scratch = torch.full((kernels.decode_attention_scratch_floats(1, heads, dim, count),), float("nan"), device="cuda")
-        kernels.decode_attention(cuda(packed), out, k_dev, v_dev, cuda(table), cuda(torch.tensor([length - 1], dtype=torch.int32)),
-                                 page, heads, kv_heads, dim, scale, window, partition, count, scratch)
+        with kernels.option("decode_tensor_cores", int(kind == "decode_tcgen05")):
+            kernels.decode_attention(cuda(packed), out, k_dev, v_dev, cuda(table),
+                                     cuda(torch.tensor([length - 1], dtype=torch.int32)), page, heads, kv_heads, dim,
+                                     scale, window, partition, count, scratch)
+        assert kernels.decode_attention_error() == 0
     else:
         kernels.prefill_attention(cuda(packed), out, k_dev, v_dev, cuda(table), cuda(torch.tensor([0, portion], dtype=torch.int32)),
                                   cuda(torch.tensor([length], dtype=torch.int32)), page, heads, kv_heads, dim, scale, window,
@@ -297,7 +320,8 @@ def test_engine_uses_the_fast_kernels_and_matches_the_plain_model(tmp_path, fuse
     check(result.logits.cpu().numpy(), np.stack([ref_first[766], ref_second[29]]), "31 tokens in a mixed step")
 
 
-def test_decode_attention_over_a_long_context():
+@pytest.mark.parametrize("tensor_cores", [True, False])
+def test_decode_attention_over_a_long_context(tensor_cores):
     """20,000 cached keys for one request beside a 3-key request: 79 partitions of 256 keys and their merge; one
     far key dominates the long request's scores for some heads."""
     from libmir_b200 import kernels
@@ -315,12 +339,16 @@ def test_decode_attention_over_a_long_context():
     q_rows = torch.cat([q[-1:] for q in qs]).reshape(rows, heads * dim)
     packed = torch.cat([q_rows, torch.zeros(rows, 2 * kv_heads * dim, dtype=BF16)], dim=1).contiguous()
     positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32)
-    partition, count = kernels.decode_partitioning(rows, kv_heads, max(lengths))
-    assert count >= 40
-    scratch = torch.empty(kernels.decode_attention_scratch_floats(rows, heads, dim, count), device="cuda")
-    out = torch.empty(rows, heads * dim, device="cuda", dtype=BF16)
-    kernels.decode_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table), cuda(positions), page, heads,
-                             kv_heads, dim, scale, None, partition, count, scratch)
+    with kernels.option("decode_tensor_cores", int(tensor_cores)):
+        # (the tcgen05 kernel walks over several tiles per partition here: the far key raises its running maximum
+        # after it has accumulated hundreds of keys, so what it holds in tensor memory is rescaled)
+        partition, count = kernels.decode_partitioning(rows, heads, kv_heads, dim, page, max(lengths))
+        assert count >= (16 if tensor_cores else 40) and (partition > 128 or not tensor_cores)
+        scratch = torch.empty(kernels.decode_attention_scratch_floats(rows, heads, dim, count), device="cuda")
+        out = torch.empty(rows, heads * dim, device="cuda", dtype=BF16)
+        kernels.decode_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table), cuda(positions), page,
+                                 heads, kv_heads, dim, scale, None, partition, count, scratch)
+    assert kernels.decode_attention_error() == 0
     expected = torch.cat([expect(q, k, v, scale, None, slice(n - 1, n)) for q, k, v, n in zip(qs, ks, vs, lengths)])
     close(out.reshape(rows, heads, dim), expected)
     assert torch.allclose(out.reshape(rows, heads, dim)[0, 0].float().cpu(), vs[0][777, 0].float(), atol=5e-2)

@@ -169,7 +169,8 @@ def plain_attention(q, k, v, scale, first_position):
     return torch.einsum("hqk,khd->qhd", torch.softmax(scores, dim=-1), v.float().repeat_interleave(group, dim=1))
 
 
-def test_decode_attention_at_batch_64():
+@pytest.mark.parametrize("tensor_cores", [True, False])
+def test_decode_attention_at_batch_64(tensor_cores):
     """64 requests of 2,060 to 2,304 cached keys: 4,608 CTAs of 256 keys and the merge of nine partitions."""
     from libmir_b200 import kernels
     rng = np.random.default_rng(3)
@@ -181,12 +182,15 @@ def test_decode_attention_at_batch_64():
     q = randn(rows, HEADS, DIM, seed=21)
     packed = torch.cat([q.reshape(rows, -1), torch.zeros(rows, 2 * KV_HEADS * DIM, device="cuda", dtype=BF16)], dim=1)
     positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device="cuda")
-    partition, count = kernels.decode_partitioning(rows, KV_HEADS, max(lengths))
-    scratch = torch.full((kernels.decode_attention_scratch_floats(rows, HEADS, DIM, count),), float("nan"), device="cuda")
     out = torch.full((rows, HEADS * DIM), 7.0, device="cuda", dtype=BF16)
     scale = 1.0 / math.sqrt(DIM)
-    kernels.decode_attention(packed, out, k_pool, v_pool, table, positions, page, HEADS, KV_HEADS, DIM, scale, None,
-                             partition, count, scratch)
+    with kernels.option("decode_tensor_cores", int(tensor_cores)):
+        partition, count = kernels.decode_partitioning(rows, HEADS, KV_HEADS, DIM, page, max(lengths))
+        scratch = torch.full((kernels.decode_attention_scratch_floats(rows, HEADS, DIM, count),), float("nan"),
+                             device="cuda")
+        kernels.decode_attention(packed, out, k_pool, v_pool, table, positions, page, HEADS, KV_HEADS, DIM, scale, None,
+                                 partition, count, scratch)
+    assert kernels.decode_attention_error() == 0
     expected = torch.cat([plain_attention(q[r:r + 1], keys[r], values[r], scale, lengths[r] - 1) for r in range(rows)])
     close(out.reshape(rows, HEADS, DIM), expected, label="decode attention, 64 rows")
 

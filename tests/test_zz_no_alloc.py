@@ -65,8 +65,9 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice_in_a_row(dim,
         floats = kernels.decode_attention_scratch_floats(rows, heads, dim, count)
         assert 0 < floats <= STATIC_FLOATS
         expected = torch.empty(rows, heads * dim, device="cuda", dtype=torch.bfloat16)
-        kernels.decode_attention(qkv, expected, k_pool, v_pool, table, positions, page, heads, kv_heads, dim, scale,
-                                 window, partition, count, torch.empty(floats, device="cuda"))
+        with kernels.option("decode_tensor_cores", 0):     # the ordinary entry point of the same (mma.sync) kernel
+            kernels.decode_attention(qkv, expected, k_pool, v_pool, table, positions, page, heads, kv_heads, dim, scale,
+                                     window, partition, count, torch.empty(floats, device="cuda"))
         got = torch.full_like(expected, 7.0)
         status = static_entry(qkv.data_ptr(), qkv.stride(0), got.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
                               table.data_ptr(), table.shape[1], positions.data_ptr(), rows, page, heads, kv_heads,

@@ -39,7 +39,7 @@ TINY_D = {   # Qwen2 style: q/k/v bias without output bias, MHA (groups of one),
     "tie_word_embeddings": True, "hidden_act": "silu",
 }
 
-TINY_E = {   # head_dim 128: in bfloat16 the tcgen05 prompt kernel and the split decode kernel; one sliding layer
+TINY_E = {   # head_dim 128: in bfloat16 the tcgen05 prompt and decode kernels; one sliding layer
     "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
     "hidden_size": 256, "intermediate_size": 352, "num_hidden_layers": 2,
     "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 640,
