@@ -431,8 +431,8 @@ def main() -> int:
         positions = torch.full((batch,), prompt_tokens - 1, dtype=torch.int32, device="cuda")
         qkv = torch.randn(batch, qkv_width, device="cuda", dtype=bf16)
         mixed = torch.empty(batch, heads * dim, device="cuda", dtype=bf16)
-        partition, count = kernels.decode_partitioning(batch, heads, kv_heads, dim, PAGE_SIZE, prompt_tokens)
-        scratch = torch.empty(max(1, kernels.decode_attention_scratch_floats(batch, heads, dim, count)), device="cuda")
+        partition, count, floats = kernels.decode_attention_plan(batch, heads, kv_heads, dim, PAGE_SIZE, prompt_tokens)
+        scratch = torch.empty(max(1, floats), device="cuda")
         scale = 1.0 / math.sqrt(dim)
         def build_decode_attention():
             return [lambda v=v: kernels.decode_attention(qkv, mixed, v.k_pages, v.v_pages, table, positions, PAGE_SIZE,

@@ -409,9 +409,9 @@ MIR_EXPORT int mir_decode_attention_tc_bf16(const void* q, long long q_stride, v
   if (rows == 0) return MIR_OK;
   if (!mir_decode_attention_tc_takes(head_dim, page_size, partition) || heads <= 0 || kv_heads <= 0 ||
       heads % kv_heads || table_width <= 0 || window < 0 || rows < 0 || rows > 65535 || num_partitions <= 0 ||
-      num_partitions > 65535 || (q_stride % 8) || q_stride < (long long)heads * kDim ||
-      ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || cache_rows <= 0 ||
-      cache_rows > 0x7fffffffll || (long long)partition * num_partitions > 0x7fffffffll) {
+      num_partitions > 65535 || (q_stride % 8) || q_stride < (long long)heads * kDim || ((uintptr_t)q & 15) ||
+      ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || cache_rows <= 0 || cache_rows > 0x7fffffffll ||
+      (long long)partition * num_partitions > 0x7fffffffll) {
     mir_set_error("decode_attention_tc: takes head_dim 128, pages of 8..128 keys that divide 128, partitions that are "
                   "multiples of 128 and 16-byte aligned tensors (head_dim %d, page %d, partition %d, "
                   "heads %d, kv heads %d, rows %d, partitions %d)",
@@ -428,22 +428,15 @@ MIR_EXPORT int mir_decode_attention_tc_bf16(const void* q, long long q_stride, v
   if (status != MIR_OK) return status;
   status = tensor_map_for(v_pages, (int)cache_rows, kv_heads * kDim, kv_heads * kDim, page_size, &v_map);
   if (status != MIR_OK) return status;
-  float* partial_o = scratch;
-  float* partial_ml = scratch ? scratch + (size_t)rows * heads * num_partitions * head_dim : nullptr;
   const int group = heads / kv_heads;
   const int columns = std::min(group, kHeads);
-  if (columns <= 4)
-    status = launch<4>(k_map, v_map, (const bf16*)q, (size_t)q_stride, block_table, table_width, positions, rows,
-                       page_size, heads, kv_heads, scale, window, partition, num_partitions, partial_o, partial_ml,
-                       (bf16*)out, stream);
-  else if (columns <= 8)
-    status = launch<8>(k_map, v_map, (const bf16*)q, (size_t)q_stride, block_table, table_width, positions, rows,
-                       page_size, heads, kv_heads, scale, window, partition, num_partitions, partial_o, partial_ml,
-                       (bf16*)out, stream);
-  else
-    status = launch<16>(k_map, v_map, (const bf16*)q, (size_t)q_stride, block_table, table_width, positions, rows,
-                        page_size, heads, kv_heads, scale, window, partition, num_partitions, partial_o, partial_ml,
-                        (bf16*)out, stream);
+  float* partial_o = scratch;
+  float* partial_ml = scratch ? scratch + (size_t)rows * heads * num_partitions * head_dim : nullptr;
+#define MIR_SPLIT(G)                                                                                                 \
+  launch<G>(k_map, v_map, (const bf16*)q, (size_t)q_stride, block_table, table_width, positions, rows, page_size, heads, \
+            kv_heads, scale, window, partition, num_partitions, partial_o, partial_ml, (bf16*)out, stream)
+  status = columns <= 4 ? MIR_SPLIT(4) : (columns <= 8 ? MIR_SPLIT(8) : MIR_SPLIT(16));
+#undef MIR_SPLIT
   if (status != MIR_OK || num_partitions == 1) return status;
   return mir_decode_merge_bf16(partial_o, partial_ml, positions, rows, heads, head_dim, window, partition,
                                num_partitions, out, stream);

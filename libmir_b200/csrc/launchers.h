@@ -70,6 +70,8 @@ int mir_decode_attention_paged_bf16(const void* q, long long q_stride, void* out
                                     int head_dim, float scale, int window, int partition, int num_partitions,
                                     float* scratch, long long scratch_floats, cudaStream_t stream);
 int mir_decode_partition_keys(int rows, int heads, int kv_heads, int head_dim, int page_size, int longest);
+int mir_decode_attention_plan(int rows, int heads, int kv_heads, int head_dim, int page_size, int longest,
+                              int* partition, int* partitions, long long* scratch_floats);
 int mir_get_option(const char* name);
 #endif
 }

@@ -161,3 +161,15 @@ MIR_EXPORT int mir_decode_attention_paged_bf16(const void* q, long long q_stride
                                    page_size, heads, kv_heads, head_dim, scale, window, partition, num_partitions,
                                    scratch, scratch_floats, stream);
 }
+
+// What a caller has to provide for the attention of `rows` single tokens whose longest context (or block-table width)
+// is `longest` keys: keys per partition, partitions, floats of scratch, as mir_decode_attention_paged_bf16 will use them.
+MIR_EXPORT int mir_decode_attention_plan(int rows, int heads, int kv_heads, int head_dim, int page_size, int longest,
+                                         int* partition, int* partitions, long long* scratch_floats) {
+  const int keys = mir_decode_partition_keys(rows, heads, kv_heads, head_dim, page_size, longest);
+  const int count = std::max(1, (std::max(longest, 1) + keys - 1) / keys);
+  *partition = keys;
+  *partitions = count;
+  *scratch_floats = mir_decode_attention_scratch_floats(rows, heads, head_dim, count);
+  return MIR_OK;
+}

@@ -50,6 +50,7 @@ _SIGNATURES = {
                                             c_int, c_void_p, c_longlong, c_void_p],
         "mir_decode_attention_tc_takes": [c_int, c_int, c_int],
         "mir_decode_partition_keys": [c_int, c_int, c_int, c_int, c_int, c_int],
+        "mir_decode_attention_plan": [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "mir_decode_attention_tc_error": [],
         "mir_prefill_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
@@ -349,16 +350,21 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
 FAST_HEAD_DIMS = (64, 128)      # what the tensor-core attention kernels take; other sizes use the reference kernel
 
 
-def decode_partitioning(rows: int, heads: int, kv_heads: int, head_dim: int, page_size: int, max_context: int) -> tuple:
-    """(keys per partition, partitions) for split decode attention of `rows` single tokens whose longest context
-    (or block-table width) is max_context keys.  The choice is native (csrc/ops_bf16.cu: mir_decode_partition_keys),
-    the same for the Python launcher and the layer executor; options decode_partition_keys (the mma.sync kernel) and
-    decode_tc_partition_keys (the tcgen05 kernel, 0 = chosen by the cost of its waves) change it."""
-    partition = int(library("bf16").mir_decode_partition_keys(rows, heads, kv_heads, head_dim, page_size, max_context))
-    return partition, max(1, -(-max_context // partition))
+def decode_attention_plan(rows: int, heads: int, kv_heads: int, head_dim: int, page_size: int, max_context: int) -> tuple:
+    """(keys per partition, partitions, floats of scratch) for the attention of `rows` single tokens whose longest
+    context (or block-table width) is max_context keys.  The plan is native (csrc/ops_bf16.cu:
+    mir_decode_attention_plan), the same for the Python launcher and the layer executor: the tcgen05 kernel where
+    it takes the sizes (partitions chosen by the cost of its waves, or decode_tc_partition_keys), else the mma.sync
+    kernel with partitions of decode_partition_keys."""
+    partition, count, floats = ctypes.c_int(), ctypes.c_int(), ctypes.c_longlong()
+    lib = library("bf16")
+    _check(lib, lib.mir_decode_attention_plan(rows, heads, kv_heads, head_dim, page_size, max_context,
+                                              ctypes.byref(partition), ctypes.byref(count), ctypes.byref(floats)))
+    return partition.value, count.value, floats.value
 
 
 def decode_attention_scratch_floats(rows: int, heads: int, head_dim: int, num_partitions: int) -> int:
+    """What the kernels that take one partition per CTA want (decode_attention_plan says what a call will use)."""
     return 0 if num_partitions <= 1 else rows * heads * num_partitions * (head_dim + 2)
 
 

@@ -117,8 +117,8 @@ class LayerRun:
         """Scratch from the step's arena (one set for the whole run: the layers use it one after the other), the
         step's metadata, one native call."""
         from . import (FUSE_NORM_INTO_PRODUCT, PREFILL_TENSOR_CORE_MIN_PORTION,
-                       PREFILL_TENSOR_CORES, NORM_STAT_STRIDE, _lt_workspace, _stream, decode_attention_scratch_floats,
-                       decode_partitioning, few_rows_max, get_option, sumsq_tiles)
+                       PREFILL_TENSOR_CORES, NORM_STAT_STRIDE, _lt_workspace, _stream, decode_attention_plan,
+                       few_rows_max, get_option, sumsq_tiles)
         tokens, hidden = residual.shape
         dtype = self.dtype
         step = StepDesc()
@@ -152,9 +152,7 @@ class LayerRun:
         if self.fast_attention:
             singles = ctx.num_rows if ctx.decode_only else ctx.single_rows
             longest = ctx.max_context if ctx.decode_only else ctx.single_context
-            floats = max(decode_attention_scratch_floats(singles, heads, head_dim,
-                                                         decode_partitioning(singles, heads, kv_heads, head_dim,
-                                                                             page_size, longest)[1])
+            floats = max(decode_attention_plan(singles, heads, kv_heads, head_dim, page_size, longest)[2]
                          for heads, kv_heads, head_dim, page_size in self.attention_shapes) if singles else 0
             if floats:
                 step.attention_scratch = ctx.alloc((floats,), torch.float32).data_ptr()

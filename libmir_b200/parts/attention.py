@@ -128,9 +128,8 @@ class SoftmaxAttention(Mixer):
             singles = ctx.num_rows if ctx.decode_only else ctx.single_rows
             if singles:
                 longest = ctx.max_context if ctx.decode_only else ctx.single_context
-                partition, count = kernels.decode_partitioning(singles, s.heads, s.kv_heads, s.head_dim,
-                                                               cache.page_size, longest)
-                floats = kernels.decode_attention_scratch_floats(singles, s.heads, s.head_dim, count)
+                partition, count, floats = kernels.decode_attention_plan(singles, s.heads, s.kv_heads, s.head_dim,
+                                                                         cache.page_size, longest)
                 scratch = ctx.alloc((floats,), torch.float32) if floats else None
                 kernels.decode_attention(qkv[:singles], out[:singles], cache.k_pages, cache.v_pages,
                                          group.block_table[:singles], ctx.positions, cache.page_size, s.heads,

@@ -342,9 +342,9 @@ def test_decode_attention_over_a_long_context(tensor_cores):
     with kernels.option("decode_tensor_cores", int(tensor_cores)):
         # (the tcgen05 kernel walks over several tiles per partition here: the far key raises its running maximum
         # after it has accumulated hundreds of keys, so what it holds in tensor memory is rescaled)
-        partition, count = kernels.decode_partitioning(rows, heads, kv_heads, dim, page, max(lengths))
+        partition, count, floats = kernels.decode_attention_plan(rows, heads, kv_heads, dim, page, max(lengths))
         assert count >= (16 if tensor_cores else 40) and (partition > 128 or not tensor_cores)
-        scratch = torch.empty(kernels.decode_attention_scratch_floats(rows, heads, dim, count), device="cuda")
+        scratch = torch.empty(floats, device="cuda")
         out = torch.empty(rows, heads * dim, device="cuda", dtype=BF16)
         kernels.decode_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table), cuda(positions), page,
                                  heads, kv_heads, dim, scale, None, partition, count, scratch)

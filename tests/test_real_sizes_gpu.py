@@ -185,9 +185,8 @@ def test_decode_attention_at_batch_64(tensor_cores):
     out = torch.full((rows, HEADS * DIM), 7.0, device="cuda", dtype=BF16)
     scale = 1.0 / math.sqrt(DIM)
     with kernels.option("decode_tensor_cores", int(tensor_cores)):
-        partition, count = kernels.decode_partitioning(rows, HEADS, KV_HEADS, DIM, page, max(lengths))
-        scratch = torch.full((kernels.decode_attention_scratch_floats(rows, HEADS, DIM, count),), float("nan"),
-                             device="cuda")
+        partition, count, floats = kernels.decode_attention_plan(rows, HEADS, KV_HEADS, DIM, page, max(lengths))
+        scratch = torch.full((floats,), float("nan"), device="cuda")
         kernels.decode_attention(packed, out, k_pool, v_pool, table, positions, page, HEADS, KV_HEADS, DIM, scale, None,
                                  partition, count, scratch)
     assert kernels.decode_attention_error() == 0
