@@ -51,8 +51,11 @@ struct StreamNorm {
   int ld_weighted;
 };
 
+// (Shared memory lets three CTAs share an SM; the registers are capped as if six did: 56 instead of up to 95 per
+// thread, no spills, and the captured decode step at Qwen3-4B sizes takes 2.621 instead of 2.638 ms at batch 8,
+// 2.226 instead of 2.241 ms at batch 1.)
 template <int MODE>
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, 6)
 tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                  const void* __restrict__ bias, void* __restrict__ out, int ldo, int m, int n, int k, int up_offset,
                  int tokens, int tile_rows, int stages, int stage_stride, uint32_t tmem_columns, StreamNorm norm) {
