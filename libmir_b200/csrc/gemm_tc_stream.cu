@@ -157,6 +157,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
   float* tile = reinterpret_cast<float*>(smem);               // [tokens][128]
   constexpr int BATCH = 4;                                    // tokens whose loads are in flight together
   float old_first[BATCH] = {0.0f, 0.0f, 0.0f, 0.0f};          // ACCUM: the residual under this thread's first tokens
+  float extra = 0.0f, next_weight = 0.0f;                     // this thread's column of the bias and of the next norm's weight
   if (warp >= 2) {
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;                      // feature row of the tile = accumulator lane
@@ -174,6 +175,12 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
 #pragma unroll
       for (int o = 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
       if (part == 0) scale[token] = rsqrtf(sum / (float)k + norm.eps);
+    }
+    if (MODE != SWIGLU && tid < tile_rows && n0 + tid < n) {
+      if (bias != nullptr)
+        extra = MODE == STORE ? __bfloat162float(reinterpret_cast<const bf16*>(bias)[n0 + tid])
+                              : reinterpret_cast<const float*>(bias)[n0 + tid];
+      if (MODE == ACCUM && norm.weighted_out != nullptr) next_weight = norm.next_weight[n0 + tid];
     }
     if (MODE == ACCUM && tid < tile_rows && n0 + tid < n) {
 #pragma unroll
@@ -196,6 +203,9 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
     tensor_fence_before_sync();
   }
   cluster.sync();                                             // every CTA's partial tile is in its shared memory
+  // The peers keep their shared memory until it was read: every thread arrives at a second cluster barrier as soon
+  // as its last remote values are in registers, before it writes its results, and waits for it at the very end.
+  bool arrived = false;
   // Every CTA of the cluster finishes a share of the tokens (token = split, split + splits, ...): it adds the
   // cluster's partial tiles over distributed shared memory in rank order and applies the epilogue.
   if (warp >= 2) {
@@ -225,6 +235,11 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
           gate[j] = token < m ? cluster_sum(token, feature) : 0.0f;
           up[j] = token < m ? cluster_sum(token, 64 + feature) : 0.0f;
         }
+        if (token0 + BATCH * stride >= m) {                   // this thread's last reads of its peers' tiles are over
+          asm volatile("" ::"f"(gate[0]), "f"(gate[1]), "f"(gate[2]), "f"(gate[3]), "f"(up[0]), "f"(up[1]), "f"(up[2]), "f"(up[3]) : "memory");
+          asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+          arrived = true;
+        }
 #pragma unroll
         for (int j = 0; j < BATCH; ++j) {
           const int token = token0 + j * stride;
@@ -238,9 +253,6 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
     } else {
       const int column = n0 + tid;
       const bool in_range = tid < tile_rows && column < n;
-      float extra = 0.0f;
-      if (bias != nullptr && in_range)
-        extra = MODE == STORE ? __bfloat162float(reinterpret_cast<const bf16*>(bias)[column]) : reinterpret_cast<const float*>(bias)[column];
       for (int token0 = split; token0 < m; token0 += BATCH * splits) {
         float value[BATCH], old[BATCH];
 #pragma unroll
@@ -249,6 +261,11 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
           value[j] = (token < m && in_range) ? cluster_sum(token, tid) : 0.0f;
           old[j] = token0 == split ? old_first[j]
                    : ((MODE == ACCUM && token < m && in_range) ? reinterpret_cast<const float*>(out)[(size_t)token * ldo + column] : 0.0f);
+        }
+        if (token0 + BATCH * splits >= m) {                   // this thread's last reads of its peers' tiles are over
+          asm volatile("" ::"f"(value[0]), "f"(value[1]), "f"(value[2]), "f"(value[3]) : "memory");
+          asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+          arrived = true;
         }
 #pragma unroll
         for (int j = 0; j < BATCH; ++j) {
@@ -261,7 +278,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
             } else {
               reinterpret_cast<float*>(out)[(size_t)token * ldo + column] = result;
               if (MODE == ACCUM && norm.weighted_out != nullptr)
-                norm.weighted_out[(size_t)token * norm.ld_weighted + column] = __float2bfloat16_rn(result * norm.next_weight[column]);
+                norm.weighted_out[(size_t)token * norm.ld_weighted + column] = __float2bfloat16_rn(result * next_weight);
             }
           }
           if (MODE == ACCUM && norm.sumsq_out != nullptr && token < kNormStatStride) {
@@ -275,7 +292,8 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
       }
     }
   }
-  cluster.sync();                                             // peers keep their shared memory until it was read
+  if (!arrived) asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
     tensor_fence_after_sync();
