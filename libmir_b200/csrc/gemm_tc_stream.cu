@@ -205,6 +205,8 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
   cluster.sync();                                             // every CTA's partial tile is in its shared memory
   // The peers keep their shared memory until it was read: every thread arrives at a second cluster barrier as soon
   // as its last remote values are in registers, before it writes its results, and waits for it at the very end.
+  // The arrival orders nothing in memory (what it guards are loads that have returned), so it is a relaxed one: a
+  // releasing arrival cost 0.06 ms of a 2.56 ms decode step.
   bool arrived = false;
   // Every CTA of the cluster finishes a share of the tokens (token = split, split + splits, ...): it adds the
   // cluster's partial tiles over distributed shared memory in rank order and applies the epilogue.
@@ -237,7 +239,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
         }
         if (token0 + BATCH * stride >= m) {                   // this thread's last reads of its peers' tiles are over
           asm volatile("" ::"f"(gate[0]), "f"(gate[1]), "f"(gate[2]), "f"(gate[3]), "f"(up[0]), "f"(up[1]), "f"(up[2]), "f"(up[3]) : "memory");
-          asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+          asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
           arrived = true;
         }
 #pragma unroll
@@ -264,7 +266,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
         }
         if (token0 + BATCH * splits >= m) {                   // this thread's last reads of its peers' tiles are over
           asm volatile("" ::"f"(value[0]), "f"(value[1]), "f"(value[2]), "f"(value[3]) : "memory");
-          asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+          asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
           arrived = true;
         }
 #pragma unroll
@@ -292,7 +294,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
       }
     }
   }
-  if (!arrived) asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  if (!arrived) asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
