@@ -59,6 +59,7 @@ __global__ void __launch_bounds__(kThreads, 6)
 tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                  const void* __restrict__ bias, void* __restrict__ out, int ldo, int m, int n, int k, int up_offset,
                  int tokens, int tile_rows, int stages, int stage_stride, uint32_t tmem_columns, StreamNorm norm) {
+  grid_launch_dependents();
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long barriers[2 * kMaxStages + 1];
   __shared__ uint32_t tmem_base_slot;
@@ -98,7 +99,6 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
   __syncthreads();
   tensor_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
-  grid_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -203,6 +203,10 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
     tensor_fence_before_sync();
   }
   cluster.sync();                                             // every CTA's partial tile is in its shared memory
+  if (warp == 1) {                                            // (the accumulator has been read out)
+    tensor_fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_columns) : "memory");
+  }
   // The peers keep their shared memory until it was read: every thread arrives at a second cluster barrier as soon
   // as its last remote values are in registers, before it writes its results, and waits for it at the very end.
   // The arrival orders nothing in memory (what it guards are loads that have returned), so it is a relaxed one: a
@@ -296,11 +300,6 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
   }
   if (!arrived) asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-  __syncthreads();
-  if (warp == 1) {
-    tensor_fence_after_sync();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_columns) : "memory");
-  }
 }
 
 int g_forced_splits = 0;                                      // for measurements: 0 = choose
