@@ -199,7 +199,7 @@ def main() -> int:
         kernels.FUSE_NORM_INTO_PRODUCT = False
     for item in args.set:
         name, _, value = item.partition("=")
-        if hasattr(kernels, name):
+        if isinstance(getattr(kernels, name, None), (int, bool)):
             setattr(kernels, name, int(value))
         elif kernels.get_option(name) >= 0:
             kernels.set_option(name, int(value))
