@@ -162,7 +162,7 @@ def main() -> int:
     parser.add_argument("--no-fold-norm", action="store_true",
                         help="run every RMSNorm as a kernel of its own instead of folding it into the few-rows "
                              "products around it")
-    parser.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "serve", "kernels"],
+    parser.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "serve", "kernels", "trace"],
                         help="decode / prefill: run only that phase, bracketed by cudaProfilerStart/Stop (for ncu "
                              "--profile-from-start off); the JSON line then holds only that phase")
     parser.add_argument("--no-graphs", action="store_true", help="decode steps as plain launches, not as CUDA graphs")
@@ -188,6 +188,8 @@ def main() -> int:
     from libmir_b200 import CacheConfig, CudaConfig, Library, RuntimeConfig, SchedulerConfig, StepEntry, kernels
     from libmir_b200.sampling import RequestSampler
 
+    if args.phase == "trace":
+        kernels.use_traced_kernels()                          # before anything loads the plain bfloat16 library
     if args.library_modes:
         modes = kernels.get_option("few_rows_modes")
         for name in args.library_modes.split(","):
@@ -500,6 +502,37 @@ def main() -> int:
                           "generated_tokens": generated, "seconds": round(seconds, 3), "steps": steps,
                           "generated_tokens_per_second": round(generated / seconds, 1),
                           "all_tokens_per_second": round((generated + sum(lengths)) / seconds, 1), "layers": layers}))
+        return 0
+    if args.phase == "trace":
+        # A few captured decode steps with the traced kernels (csrc/trace.cuh), then the last step's records on one
+        # time line: microseconds since the step's first record, per launch the first CTA and the last one.
+        decode_device(args.batch, 3, 2, 1)
+        records = kernels.read_trace()
+        names = {
+            "stream": ["start", "weights_asked", "dependency", "activations_asked", "first_stage", "last_stage",
+                       "products_done", "cluster_barrier", "written", "second_barrier"],
+            "decode": ["start", "set_up", "loads_may_go", "dependency", "queries_in", "scores_issued", "first_scores",
+                       "first_p", "last_scores", "last_p", "last_product", "written", "end"],
+            "merge": ["start", "dependency", "end"], "rope": ["start", "dependency", "end"]}
+        stream_kinds = {0: "store (QKV)", 1: "accumulate (output / down)", 2: "float32 (head)", 3: "SwiGLU (gate-up)"}
+        rows = []
+        for group, table in records.items():
+            for record in table:
+                tag = int(record[15])
+                what = f"stream {stream_kinds[tag // 2]}" if group == "stream" else group
+                if group == "decode":
+                    what += f" ({int(record[14])} tiles)"
+                rows.append((int(record[0]), what, "first CTA" if tag % 2 == 0 else "last CTA", group, record))
+        rows.sort(key=lambda row: row[0])
+        per_step = (layers * 7 + 1) * 2                       # launches with records in a step, two CTAs each
+        rows = rows[-per_step:]
+        origin = rows[0][0] if rows else 0
+        for _, what, which, group, record in rows:
+            stamps = " ".join(f"{name}={(int(record[i]) - origin) / 1e3:.2f}" for i, name in enumerate(names[group])
+                              if record[i] > 0)
+            print(f"{what:36s} {which:9s} {stamps}")
+        print(json.dumps({"phase": "trace", "batch": args.batch, "layers": layers, "records": len(rows),
+                          "unit": "us since the step's first record"}))
         return 0
     if args.phase == "kernels":
         print(json.dumps({"phase": "kernels", "batch": args.batch, "context": prompt_tokens,

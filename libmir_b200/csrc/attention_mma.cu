@@ -19,6 +19,7 @@
 #include <algorithm>
 #include <cfloat>
 #include "common.cuh"
+#include "trace.cuh"
 
 using namespace mir;
 typedef __nv_bfloat16 bf16;
@@ -417,6 +418,8 @@ decode_attention_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16*
 // One CTA of four warps per (request, head).  The partitions are shared out over the warps (each lane four
 // consecutive elements of the head, 16-byte loads, four partitions in flight), so a long context's hundred
 // partitions cost a few rounds of loads, not a hundred; the warps' sums meet in shared memory.
+// time stamps (trace.cuh) of the merge's first and last CTA: 0 start, 1 the attention kernel is over, 2 end; tag 300 / 301
+MIR_TRACE_DEFINE(merge)
 constexpr int kMergeWarps = 4;
 template <int D>
 __global__ void __launch_bounds__(kMergeWarps * 32)
@@ -429,7 +432,11 @@ decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict
   const int head = blockIdx.x, row = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   grid_launch_dependents();
+  MIR_TRACE_BEGIN(merge, (blockIdx.x == 0 && blockIdx.y == 0) || (blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1),
+                  300 + (blockIdx.x == 0 && blockIdx.y == 0 ? 0 : 1))
+  if (threadIdx.x == 0) MIR_TRACE_POINT(merge, 0);
   grid_dependency_wait();
+  if (threadIdx.x == 0) MIR_TRACE_POINT(merge, 1);
   const int position = positions[row];
   const size_t index = (size_t)row * heads + head;
   if (position < 0) {
@@ -484,6 +491,7 @@ decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict
     const float all = (sums[0][D] + sums[1][D]) + (sums[2][D] + sums[3][D]);
     out[index * D + d] = __float2bfloat16_rn(all > 0.0f ? total / all : 0.0f);
   }
+  if (threadIdx.x == 0) MIR_TRACE_POINT(merge, 2);
 }
 
 // The same for up to kMergeFew partitions: one warp per (request, head), every lane D / 32 consecutive elements of
@@ -499,7 +507,11 @@ decode_merge_few_kernel(const float* __restrict__ partial_o, const float* __rest
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.x * kMergeWarps + warp, row = blockIdx.y;
   grid_launch_dependents();
+  MIR_TRACE_BEGIN(merge, (blockIdx.x == 0 && blockIdx.y == 0) || (blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1),
+                  300 + (blockIdx.x == 0 && blockIdx.y == 0 ? 0 : 1))
+  if (threadIdx.x == 0) MIR_TRACE_POINT(merge, 0);
   grid_dependency_wait();
+  if (threadIdx.x == 0) MIR_TRACE_POINT(merge, 1);
   if (head >= heads) return;
   const int position = positions[row];
   const size_t index = (size_t)row * heads + head;
@@ -551,6 +563,7 @@ decode_merge_few_kernel(const float* __restrict__ partial_o, const float* __rest
   for (int j = 0; j < PER; j += 2)
     *reinterpret_cast<__nv_bfloat162*>(dst + j) =
         __floats2bfloat162_rn(denom > 0.0f ? acc[j] / denom : 0.0f, denom > 0.0f ? acc[j + 1] / denom : 0.0f);
+  if (threadIdx.x == 0) MIR_TRACE_POINT(merge, 2);
 }
 
 // ------------------------------------------------------------------------------------------------ prefill

@@ -31,6 +31,7 @@
 #include <algorithm>
 #include "tcgen05.cuh"
 #include "launchers.h"
+#include "trace.cuh"
 
 using namespace mir;
 using namespace mir::tc;
@@ -54,6 +55,11 @@ constexpr float kRescaleThreshold = 8.0f;   // log2 of how far a tile's maximum 
 enum { K_FULL = 0, K_FREE, V_FULL, V_FREE, S_FULL, P_READY, Q_READY, O_DONE, BARRIERS };
 
 __device__ int g_tc_decode_error = 0;
+// time stamps (trace.cuh) of the grid's first CTA and of the last row's last live partition: 0 start, 1 set up,
+// 2 loader: first loads may go, 3 softmax: the kernel before is over, 4 issuer: the queries are in shared memory,
+// 5 first scores issued, 6 first scores there, 7 first P written, 8 last scores there, 9 last P written, 10 last
+// product over, 11 results written, 12 end; value = tiles of the CTA; tag 200 first CTA, 201 the other
+MIR_TRACE_DEFINE(decode)
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -172,6 +178,15 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
   __syncthreads();
   tensor_fence_after_sync();
   const uint32_t tmem_s = tmem_base_slot, tmem_o = tmem_base_slot + 16u;
+  MIR_TRACE_BEGIN(decode, (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ||
+                              (part_end == context && blockIdx.y == gridDim.y - 1 &&
+                               row == (int)(part_slow ? gridDim.x : gridDim.z) - 1),
+                  200 + (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 ? 0 : 1))
+  if (threadIdx.x == 0) {
+    MIR_TRACE_VALUE(decode, tiles);
+    MIR_TRACE_POINT(decode, 0);
+    MIR_TRACE_POINT(decode, 1);
+  }
 
   if (warp == 4) {
     // ------------------------------------------------------------------ loader
@@ -182,6 +197,7 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
     const bool loads = lane < 2 * pages_per_tile;
     // the newest key is the kernel's before this one; every other key is older
     if (part_end > position) grid_dependency_wait();
+    if (lane == 0) MIR_TRACE_POINT(decode, 2);
     auto row_of = [&](int t) {
       const int key = begin + t * kKeys + slot * page_size;
       int page = -1;
@@ -230,7 +246,9 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
         mma_commit(bar(K_FREE));
       };
       check(Q_READY, 0u);
+      MIR_TRACE_POINT(decode, 4);
       issue_scores(0);
+      MIR_TRACE_POINT(decode, 5);
       for (int t = 0; t < tiles; ++t) {
         const uint32_t parity = (uint32_t)t & 1u;
         check(V_FULL, parity);
@@ -254,6 +272,7 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
     const uint32_t lane_bits = (uint32_t)(warp * 32) << 16;
     bool alive = true;
     grid_dependency_wait();                                   // q comes from the kernel before
+    if (r == 0) MIR_TRACE_POINT(decode, 3);
     {
       // the group's queries as a B operand: 16 rows (heads beyond the group are zero) x 128 elements
       unsigned char* q_smem = smem + kOffQ;
@@ -276,6 +295,8 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
       const int key = begin + t * kKeys + r;
       const bool visible = key >= first_key && key <= position;
       if (alive && !wait_barrier(bar(S_FULL), parity)) { g_tc_decode_error = 3; alive = false; }
+      if (r == 0 && t == 0) MIR_TRACE_POINT(decode, 6);
+      if (r == 0 && t == tiles - 1) MIR_TRACE_POINT(decode, 8);
       tensor_fence_after_sync();
       float s[G];
       tmem_load<G>(tmem_s + lane_bits, s);
@@ -317,6 +338,8 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tensor_fence_before_sync();
       barrier_arrive(bar(P_READY));
+      if (r == 0 && t == 0) MIR_TRACE_POINT(decode, 7);
+      if (r == 0 && t == tiles - 1) MIR_TRACE_POINT(decode, 9);
     }
     // the denominators: every thread holds its keys' share
 #pragma unroll
@@ -326,6 +349,7 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
     if (alive && !wait_barrier(bar(O_DONE), 0u)) { g_tc_decode_error = 3; alive = false; }
+    if (r == 0) MIR_TRACE_POINT(decode, 10);
     tensor_fence_after_sync();
     float o[G];
     tmem_load<G>(tmem_o + lane_bits, o);
@@ -346,6 +370,7 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
         }
       }
     }
+    if (r == 0) MIR_TRACE_POINT(decode, 11);
     tensor_fence_before_sync();
   }
   __syncthreads();
@@ -353,6 +378,7 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
     tensor_fence_after_sync();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"(kTmemColumns) : "memory");
   }
+  if (threadIdx.x == 0) MIR_TRACE_POINT(decode, 12);
 }
 
 template <int G>

@@ -47,7 +47,9 @@ LIBRARIES = {
         "defines": ["-DMIR_WITH_BF16"],
     },
 }
-HEADERS = ["common.cuh", "launchers.h"]
+# the bfloat16 library with time stamps inside its kernels (trace.cuh), for bench.py --phase trace
+LIBRARIES["bf16_trace"] = dict(LIBRARIES["bf16"], defines=LIBRARIES["bf16"]["defines"] + ["-DMIR_TRACE"])
+HEADERS = ["common.cuh", "launchers.h", "trace.cuh"]
 
 
 def _nvcc() -> str:

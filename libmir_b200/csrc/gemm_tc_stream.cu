@@ -23,6 +23,7 @@
 #include <algorithm>
 #include <cooperative_groups.h>
 #include "tcgen05.cuh"
+#include "trace.cuh"
 
 namespace cg = cooperative_groups;
 using namespace mir;
@@ -40,6 +41,11 @@ int g_ring_bytes = kRingBytes;               // for measurements
 enum Epilogue : int { STORE = 0, ACCUM = 1, F32 = 2, SWIGLU = 3 };
 
 __device__ int g_tc_stream_error = 0;
+// time stamps (trace.cuh) of the first and the last CTA of a launch: 0 start, 1 the ring's first weights are asked
+// for, 2 the kernel before is over, 3 the activations are asked for, 4 the first stage has landed, 5 the last one,
+// 6 the products are over, 7 after the first cluster barrier, 8 results written, 9 after the second barrier;
+// tag = 2 x epilogue + (0 first CTA, 1 last)
+MIR_TRACE_DEFINE(stream)
 
 struct StreamNorm {
   const float* sumsq;        // consumer: [sumsq_tiles][kNormStatStride] partial sums of squares of x's rows before weighting
@@ -99,6 +105,9 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
   __syncthreads();
   tensor_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
+  MIR_TRACE_BEGIN(stream, (blockIdx.x == 0 && blockIdx.y == 0) || (blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1),
+                  2 * MODE + (blockIdx.x == 0 && blockIdx.y == 0 ? 0 : 1))
+  if (threadIdx.x == 0) MIR_TRACE_POINT(stream, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -117,10 +126,13 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
       const int ahead = min(stages, my_steps);
       for (int i = 0; i < ahead; ++i)
         load_weights(i, full0 + 8 * i, smem_base + (uint32_t)i * (uint32_t)stage_stride);
+      MIR_TRACE_POINT(stream, 1);
       grid_dependency_wait();
+      MIR_TRACE_POINT(stream, 2);
       for (int i = 0; i < ahead; ++i)
         tma_load_2d(smem_base + (uint32_t)i * (uint32_t)stage_stride + weight_bytes, &x_map, full0 + 8 * i,
                     (step_begin + i) * kStepK, 0);
+      MIR_TRACE_POINT(stream, 3);
       for (int i = ahead; i < my_steps; ++i) {
         const int stage = i % stages;
         const uint32_t parity = (uint32_t)(i / stages) & 1u;
@@ -140,6 +152,8 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
         const int stage = i % stages;
         const uint32_t parity = (uint32_t)(i / stages) & 1u;
         if (alive && !wait_barrier(full0 + 8 * stage, parity)) { g_tc_stream_error = 2; alive = false; }
+        if (i == 0) MIR_TRACE_POINT(stream, 4);
+        if (i == my_steps - 1) MIR_TRACE_POINT(stream, 5);
         tensor_fence_after_sync();
         const uint32_t a_base = smem_base + (uint32_t)stage * (uint32_t)stage_stride;
         const uint32_t b_base = a_base + weight_bytes;
@@ -190,6 +204,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
       }
     }
     const bool alive = wait_barrier(done, 0);
+    if (tid == 0) MIR_TRACE_POINT(stream, 6);
     if (!alive) g_tc_stream_error = 3;
     tensor_fence_after_sync();
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -203,6 +218,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
     tensor_fence_before_sync();
   }
   cluster.sync();                                             // every CTA's partial tile is in its shared memory
+  if (threadIdx.x == 64) MIR_TRACE_POINT(stream, 7);
   if (warp == 1) {                                            // (the accumulator has been read out)
     tensor_fence_after_sync();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_columns) : "memory");
@@ -298,8 +314,10 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
       }
     }
   }
+  if (threadIdx.x == 64) MIR_TRACE_POINT(stream, 8);
   if (!arrived) asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+  if (threadIdx.x == 64) MIR_TRACE_POINT(stream, 9);
 }
 
 int g_forced_splits = 0;                                      // for measurements: 0 = choose

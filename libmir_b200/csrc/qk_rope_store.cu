@@ -13,6 +13,7 @@
 // pages, 2 keys are normed and rotated in place like the queries and nothing goes to the pages (a position
 // encoding of another kind works on them next; a second call with 1 and neither norm nor rotation then stores).
 #include "common.cuh"
+#include "trace.cuh"
 
 using namespace mir;
 
@@ -124,6 +125,10 @@ __global__ void qk_rope_store_kernel(T* __restrict__ qkv, const int* __restrict_
   }
 }
 
+// time stamps (trace.cuh) of the first and the last CTA of the kernel below: 0 start, 1 the projection is over,
+// 2 end; tag 100 / 101
+MIR_TRACE_DEFINE(rope)
+
 // bf16, the whole head rotated (rotary_dim == head_dim), half a head a multiple of 8 elements: L = half / 8 lanes
 // take one head, each with two 16-byte pieces (elements 8 l .. 8 l + 7 and their partners half a head further),
 // so a warp works on 32 / L heads at once and every access is 16 bytes wide.
@@ -136,6 +141,9 @@ __global__ void qk_rope_store_wide_kernel(__nv_bfloat16* __restrict__ qkv, const
   constexpr int HALF = 8 * L, DIM = 2 * HALF, GROUPS = 32 / L;
   __shared__ float angles[DIM];                      // [HALF] cosines then [HALF] sines of this token
   grid_launch_dependents();
+  MIR_TRACE_BEGIN(rope, (blockIdx.x == 0 && blockIdx.y == 0) || (blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1),
+                  100 + (blockIdx.x == 0 && blockIdx.y == 0 ? 0 : 1))
+  if (threadIdx.x == 0) MIR_TRACE_POINT(rope, 0);
   const int token = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int group = lane / L, l = lane % L;
@@ -149,6 +157,7 @@ __global__ void qk_rope_store_wide_kernel(__nv_bfloat16* __restrict__ qkv, const
     sincosf(position * inv_freq[pair], &angles[HALF + pair], &angles[pair]);
   grid_dependency_wait();
   __syncthreads();
+  if (threadIdx.x == 0) MIR_TRACE_POINT(rope, 1);
   const int unit_begin = blockIdx.y * units_per_cta, unit_end = min(units, unit_begin + units_per_cta);
   for (int base = unit_begin + warp * GROUPS; base < unit_end; base += warps * GROUPS) {
     const int unit = base + group;
@@ -211,6 +220,7 @@ __global__ void qk_rope_store_wide_kernel(__nv_bfloat16* __restrict__ qkv, const
     *reinterpret_cast<uint4*>(dst + 8 * l) = a;                // a value head is copied as it is
     *reinterpret_cast<uint4*>(dst + HALF + 8 * l) = b;
   }
+  if (threadIdx.x == 0) MIR_TRACE_POINT(rope, 2);
 }
 
 template <int L>

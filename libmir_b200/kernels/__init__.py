@@ -86,12 +86,44 @@ def set_build_verbosity(verbose: bool) -> None:
     _VERBOSE_BUILD = verbose
 
 
+_TRACED = False
+
+
+def use_traced_kernels() -> None:
+    """Load the bfloat16 library with time stamps inside its kernels (csrc/trace.cuh) instead of the plain one.
+    To be called before the first bfloat16 kernel runs; read_trace() returns what they recorded."""
+    global _TRACED
+    if "bf16" in _LIBS and not _TRACED:
+        raise KernelError("use_traced_kernels: the plain bfloat16 library is loaded already")
+    _TRACED = True
+
+
+def read_trace() -> dict:
+    """The records of the traced kernels since the last call, per group ("stream", "decode", "merge", "rope"):
+    int64 arrays [records, 16] of %globaltimer nanoseconds (0 = not reached), [:, 14] a value, [:, 15] a tag; the
+    sources say which time stamp is what.  Synchronises the device."""
+    import numpy as np
+    _require(_TRACED, "read_trace: call use_traced_kernels() first")
+    lib = library("bf16")
+    capacity = 4096
+    host = (ctypes.c_ulonglong * (16 * capacity))()
+    records = {}
+    for group in ("stream", "decode", "merge", "rope"):
+        reader = getattr(lib, f"mir_trace_read_{group}")
+        reader.argtypes = [c_void_p, c_int]
+        reader.restype = c_int
+        count = reader(host, capacity)
+        _require(count >= 0, f"read_trace: reading the {group} records failed")
+        records[group] = np.array(host[: count * 16], dtype=np.uint64).reshape(count, 16).astype(np.int64)
+    return records
+
+
 def library(name: str) -> ctypes.CDLL:
     """The loaded native library `name`, compiled first if its sources changed or it was never built."""
     lib = _LIBS.get(name)
     if lib is not None:
         return lib
-    path = _build.build(name, verbose=_VERBOSE_BUILD)
+    path = _build.build("bf16_trace" if name == "bf16" and _TRACED else name, verbose=_VERBOSE_BUILD)
     try:
         lib = ctypes.CDLL(str(path), mode=ctypes.RTLD_LOCAL)
     except OSError as error:
