@@ -201,7 +201,9 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
     auto row_of = [&](int t) {
       const int key = begin + t * kKeys + slot * page_size;
       int page = -1;
-      if (loads && t < tiles && key < part_end && key + page_size > first_key) page = table[key / page_size];
+      // (a position beyond what the table holds reads no entry: its keys count as released)
+      if (loads && t < tiles && key < part_end && key + page_size > first_key && key / page_size < table_width)
+        page = table[key / page_size];
       return page >= 0 ? page * page_size : -page_size;       // a negative row lies outside the tensor: zeros
     };
     int cache_row = row_of(0);
