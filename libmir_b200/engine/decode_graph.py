@@ -112,6 +112,8 @@ class DecodeGraph:
         self.launches_per_replay = 0
         self.replays = 0
         self._copied = None
+        self._live_rows = -1                       # rows the upload block was last filled for
+        self._greedy_options = False               # whether its sampling records are the greedy defaults
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._capture()
 
@@ -176,16 +178,21 @@ class DecodeGraph:
             self._copied.synchronize()             # the previous copy has read the pinned block
         host_tokens, host_positions, host_slots = self._host_part(1), self._host_part(2), self._host_part(3)
         host_tokens[:n] = tokens
-        host_tokens[n:] = 0
         host_positions[:n] = [seq.length for seq in sequences]
-        host_positions[n:] = -1
         host_slots[:n] = [seq.slot for seq in sequences]
-        host_slots[n:] = 0
-        records = self._host_part(0).view(kernels.SAMPLE_OPTIONS)
+        if n != self._live_rows:                   # (the padding rows are as the last call left them otherwise)
+            host_tokens[n:] = 0
+            host_positions[n:] = -1
+            host_slots[n:] = 0
+            self._live_rows = n
         if options is None:
-            records["draw"], records["temperature"], records["top_p"], records["top_k"] = 0.0, 0.0, 1.0, 0
+            if not self._greedy_options:
+                records = self._host_part(0).view(kernels.SAMPLE_OPTIONS)
+                records["draw"], records["temperature"], records["top_p"], records["top_k"] = 0.0, 0.0, 1.0, 0
+                self._greedy_options = True
         else:
-            records[:n] = options
+            self._host_part(0).view(kernels.SAMPLE_OPTIONS)[:n] = options
+            self._greedy_options = False
         # Block tables only grow at the end (and lose their head to a window): a row whose request, length and
         # first live block are what was written last time is left as it is.
         for g, width in enumerate(self.widths):
@@ -209,7 +216,8 @@ class DecodeGraph:
                     table[r] = 0
                     written[r] = None
         self.meta[:self._upload].copy_(self.staging, non_blocking=True)
-        self._copied = torch.cuda.Event()
+        if self._copied is None:
+            self._copied = torch.cuda.Event()
         self._copied.record()
 
     def replay(self) -> None:
