@@ -21,6 +21,7 @@
 // of squares and the weighted bf16 copy of the rows it updates).  Waits on mbarriers are bounded in time.
 // libmir takes these products from a library (cuda/src/backend/linear/mod.rs:141-194).
 #include <algorithm>
+#include <cfloat>
 #include <cooperative_groups.h>
 #include "tcgen05.cuh"
 #include "trace.cuh"
@@ -55,6 +56,9 @@ struct StreamNorm {
   const float* next_weight;  // producer: [n] weight of the norm that follows, or null
   bf16* weighted_out;        // producer: [m, ld_weighted] bf16(new residual * next_weight)
   int ld_weighted;
+  float* best_value;         // float32 epilogue (the output head): [m][best_stride] the largest finite result of every
+  int* best_index;           //   32 columns (entry 4 x tile + warp) and its column, ties to the lower column; or null
+  int best_stride;
 };
 
 // (Shared memory lets three CTAs share an SM; the registers are capped as if six did: 56 instead of up to 95 per
@@ -303,6 +307,24 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
                 norm.weighted_out[(size_t)token * norm.ld_weighted + column] = __float2bfloat16_rn(result * next_weight);
             }
           }
+          if (MODE == F32 && norm.best_value != nullptr) {
+            // The head's logits: what a sampler asks first is each row's largest one.  Every warp leaves the best of
+            // its 32 columns, so that the sampling kernel looks at V / 32 candidates instead of V logits.
+            const bool counts = in_range && isfinite(result);
+            float best = counts ? result : -FLT_MAX;
+            int best_column = counts ? column : 0x7fffffff;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+              const float other = __shfl_xor_sync(0xffffffffu, best, o);
+              const int other_column = __shfl_xor_sync(0xffffffffu, best_column, o);
+              if (other > best || (other == best && other_column < best_column)) { best = other; best_column = other_column; }
+            }
+            if ((tid & 31) == 0) {
+              const size_t at = (size_t)token * norm.best_stride + blockIdx.x * 4 + (tid >> 5);
+              norm.best_value[at] = best;
+              norm.best_index[at] = best_column;
+            }
+          }
           if (MODE == ACCUM && norm.sumsq_out != nullptr && token < kNormStatStride) {
             // sum of squares of 16 neighbouring new residual values of this token (16 consecutive lanes)
             float square = in_range ? result * result : 0.0f;
@@ -437,6 +459,9 @@ MIR_EXPORT int mir_gemm_tc_stream_bf16(int mode, const void* x, int ldx, const v
   norm.next_weight = next_weight;
   norm.weighted_out = (bf16*)weighted_out;
   norm.ld_weighted = ld_weighted;
+  norm.best_value = nullptr;
+  norm.best_index = nullptr;
+  norm.best_stride = 0;
   switch (mode) {
     case STORE: return launch<STORE>(x, ldx, w, bias, out, ldo, m, n, k, 0, norm, stream);
     case ACCUM: return launch<ACCUM>(x, ldx, w, bias, out, ldo, m, n, k, 0, norm, stream);
@@ -447,4 +472,35 @@ MIR_EXPORT int mir_gemm_tc_stream_bf16(int mode, const void* x, int ldx, const v
   }
   mir_set_error("tc_stream: unknown mode %d", mode);
   return MIR_BAD_ARGUMENT;
+}
+
+// Entries per row that mir_gemm_tc_stream_head_bf16 leaves for n output columns: four per tile of 128 columns.
+MIR_EXPORT int mir_gemm_tc_stream_head_candidates(int n) { return n <= 0 ? 0 : (n + 127) / 128 * 4; }
+
+// The output head: the float32 epilogue (out[m, n] = x . w^T), which also leaves, per row, the largest finite logit of every 32 columns and its column (ties to the lower column) in
+// best_value / best_index [m][best_stride], best_stride >= mir_gemm_tc_stream_head_candidates(n): the sampling kernel
+// finds a row's largest logit among these instead of among all n.
+MIR_EXPORT int mir_gemm_tc_stream_head_bf16(const void* x, int ldx, const void* w, void* out, int ldo, int m, int n, int k,
+                                            float* best_value, int* best_index, int best_stride, cudaStream_t stream) {
+  if (m == 0 || n == 0) return MIR_OK;
+  if (m < 0 || m > 128 || n < 0 || k <= 0 || (k % 8) || ldo < n || ((uintptr_t)w & 15) || (ldx % 8) || ldx < k ||
+      ((uintptr_t)x & 15) || x == nullptr || best_value == nullptr || best_index == nullptr ||
+      best_stride < mir_gemm_tc_stream_head_candidates(n) || g_forced_rows != 0) {
+    mir_set_error("tc_stream: the head needs 1..128 rows, k and the row stride multiples of 8, 16-byte aligned operands "
+                  "and room for %d candidates per row (m %d n %d k %d ldx %d ldo %d stride %d)",
+                  mir_gemm_tc_stream_head_candidates(n), m, n, k, ldx, ldo, best_stride);
+    return MIR_BAD_ARGUMENT;
+  }
+  StreamNorm norm;
+  norm.sumsq = nullptr;
+  norm.sumsq_tiles = 0;
+  norm.eps = 0.0f;
+  norm.sumsq_out = nullptr;
+  norm.next_weight = nullptr;
+  norm.weighted_out = nullptr;
+  norm.ld_weighted = 0;
+  norm.best_value = best_value;
+  norm.best_index = best_index;
+  norm.best_stride = best_stride;
+  return launch<F32>(x, ldx, w, nullptr, out, ldo, m, n, k, 0, norm, stream);
 }

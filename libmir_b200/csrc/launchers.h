@@ -30,6 +30,9 @@ int mir_gemm_tc_stream_bf16(int mode, const void* x, int ldx, const void* w, con
                             int n, int k, int up_offset, const float* sumsq, int sumsq_tiles, float eps,
                             float* sumsq_out, const float* next_weight, void* weighted_out, int ld_weighted,
                             cudaStream_t stream);
+int mir_gemm_tc_stream_head_candidates(int n);
+int mir_gemm_tc_stream_head_bf16(const void* x, int ldx, const void* w, void* out, int ldo, int m, int n, int k,
+                                 float* best_value, int* best_index, int best_stride, cudaStream_t stream);
 int mir_gemm_tc_bf16(int mode, const void* x, int ldx, const void* w, const void* bias, void* out, int ldo, int m, int n,
                      int k, int up_offset, cudaStream_t stream);
 // attention_mma.cu, attention_tc.cu, attention_tc_decode.cu

@@ -173,3 +173,21 @@ MIR_EXPORT int mir_decode_attention_plan(int rows, int heads, int kv_heads, int 
   *scratch_floats = mir_decode_attention_scratch_floats(rows, heads, head_dim, count);
   return MIR_OK;
 }
+
+// The output head: float32 logits out[m, n] = x . w^T.  Up to few_rows_max rows run the weight-streaming kernel, which
+// then also leaves each row's candidates for its largest logit (see mir_gemm_tc_stream_head_bf16) if best_value is
+// given: *wrote_best says whether it did (a library product leaves none).
+MIR_EXPORT int mir_head_logits_bf16(const void* x, int ldx, const void* w, void* out, int ldo, int m, int n, int k,
+                                    float* best_value, int* best_index, int best_stride, void* workspace,
+                                    size_t workspace_bytes, cudaStream_t stream, int* wrote_best) {
+  if (wrote_best) *wrote_best = 0;
+  if (best_value != nullptr && best_index != nullptr && few_rows_ok(x, ldx, m, k) && (g_few_rows_modes & (1 << F32)) &&
+      best_stride >= mir_gemm_tc_stream_head_candidates(n) && ldo >= n) {
+    const int status = mir_gemm_tc_stream_head_bf16(x, ldx, w, out, ldo, m, n, k, best_value, best_index, best_stride,
+                                                    stream);
+    if (status == MIR_OK && wrote_best) *wrote_best = 1;
+    return status;
+  }
+  return mir_linear_bf16(x, ldx, w, nullptr, out, ldo, 1, 0, m, n, k, nullptr, 0, 0.0f, nullptr, nullptr, nullptr, 0,
+                         workspace, workspace_bytes, stream, nullptr);
+}

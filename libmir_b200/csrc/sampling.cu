@@ -344,7 +344,9 @@ constexpr int kBins = 4096;
 __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restrict__ logits, size_t ld, int vocab,
                                                            const SampleOptions* __restrict__ options,
                                                            unsigned long long* __restrict__ sort_keys, int padded,
-                                                           int* __restrict__ tokens) {
+                                                           int* __restrict__ tokens,
+                                                           const float* __restrict__ candidate_value,
+                                                           const int* __restrict__ candidate_index, int given) {
   __shared__ float s_value[32];
   __shared__ int s_index[32];
   __shared__ double s_sum[32];
@@ -369,9 +371,21 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
   const int slice_begin = min(vocab, slice * per_slice), slice_end = min(vocab, slice_begin + per_slice);
   float best = -FLT_MAX;
   int best_index = 0x7fffffff;
-  for (int i = slice_begin + threadIdx.x; i < slice_end; i += kThreads) {
-    const float v = l[i];
-    if (isfinite(v) && (v > best || (v == best && i < best_index))) { best = v; best_index = i; }
+  if (candidate_value != nullptr) {
+    // the kernel that wrote the logits left the largest finite one of every 32 columns (and its column, ties to the
+    // lower one; -FLT_MAX and 0x7fffffff where there is none): the row's largest is among these
+    const int per = (given + kSlices - 1) / kSlices;
+    const int begin = min(given, slice * per), end = min(given, begin + per);
+    for (int c = begin + threadIdx.x; c < end; c += kThreads) {
+      const float v = candidate_value[(size_t)row * given + c];
+      const int i = candidate_index[(size_t)row * given + c];
+      if (i < vocab && (v > best || (v == best && i < best_index))) { best = v; best_index = i; }
+    }
+  } else {
+    for (int i = slice_begin + threadIdx.x; i < slice_end; i += kThreads) {
+      const float v = l[i];
+      if (isfinite(v) && (v > best || (v == best && i < best_index))) { best = v; best_index = i; }
+    }
   }
   block_argmax(best, best_index, s_value, s_index);
   if (threadIdx.x == 0) { slice_value = best; slice_index = best_index; }
@@ -704,9 +718,11 @@ __global__ void penalty_kernel(float* __restrict__ logits, size_t ld, int vocab,
   *slot = signbit(v) ? v * penalty : v / penalty;
 }
 
+// best_value / best_index [rows][best_count] (or null): per row, candidates among which its largest finite logit is,
+// as the output head's kernel leaves them (every finite logit is <= the candidate of its group of columns).
 MIR_EXPORT int mir_sample(const float* logits, long long ld, int rows, int vocab, const void* options,
                           void* sort_keys, long long sort_keys_capacity, int needs_ranked, int* tokens,
-                          cudaStream_t stream) {
+                          const float* best_value, const int* best_index, int best_count, cudaStream_t stream) {
   if (rows == 0) return MIR_OK;
   if (rows < 0 || vocab <= 0 || ld < vocab) { mir_set_error("sample: bad sizes"); return MIR_BAD_ARGUMENT; }
   int padded = 1;
@@ -718,7 +734,8 @@ MIR_EXPORT int mir_sample(const float* logits, long long ld, int rows, int vocab
   }
   return mir_launch("sample", sample_kernel, dim3(rows, kSlices), dim3(kThreads), 0, stream, kSlices, logits, (size_t)ld, vocab,
                     (const SampleOptions*)options, needs_ranked ? (unsigned long long*)sort_keys : nullptr, padded,
-                    tokens);
+                    tokens, best_count > 0 && best_index != nullptr ? best_value : (const float*)nullptr, best_index,
+                    best_count);
 }
 
 MIR_EXPORT int mir_repetition_penalty(float* logits, long long ld, int vocab, const int* ids, const int* id_rows,

@@ -108,6 +108,9 @@ class DecodeGraph:
         if ranked:
             self.sort_keys = torch.empty(kernels.ranked_scratch_keys(rows, runner.model.spec.vocab_size),
                                          dtype=torch.int64, device=device)
+        # what the head's kernel leaves for the sampling kernel (each row's largest logit is among them)
+        self.candidates = kernels.HeadCandidates.allocate(
+            lambda shape, dtype: torch.zeros(shape, dtype=dtype, device=device), rows, runner.model.spec.vocab_size)
         self.host_tokens = torch.zeros(rows, dtype=torch.int32, pin_memory=True)
         self.launches_per_replay = 0
         self.replays = 0
@@ -143,8 +146,8 @@ class DecodeGraph:
             kernels.decode_prepare(self.positions, self.tables[g], runner.manager.page_size, self.slot_mappings[g],
                                    self.context_lens)
         residual = runner.model.forward(ctx)
-        self.logits = runner.model.logits(ctx, residual, self.want_rows)
-        kernels.sample(self.logits, self.options, self.sampled, self.sort_keys, self.ranked)
+        self.logits = runner.model.logits(ctx, residual, self.want_rows, candidates=self.candidates)
+        kernels.sample(self.logits, self.options, self.sampled, self.sort_keys, self.ranked, self.candidates)
         kernels.decode_advance(self.sampled, self.tokens, self.positions, self.token_log, self.step_counter)
 
     def _capture(self) -> None:

@@ -239,10 +239,14 @@ class StepRunner:
         self.arena.reset()
         ctx, want_rows, want_keys = self.build_context(entries, sequences)
         residual = self.model.forward(ctx)
-        logits = self.model.logits(ctx, residual, want_rows) if want_keys else None
+        candidates = None
+        if samplers is not None and want_keys:
+            from .. import kernels
+            candidates = kernels.HeadCandidates.allocate(ctx.alloc, len(want_keys), self.model.spec.vocab_size)
+        logits = self.model.logits(ctx, residual, want_rows, candidates=candidates) if want_keys else None
         tokens = None
         if samplers is not None and logits is not None:
-            tokens = self.sampler.sample(logits, samplers)
+            tokens = self.sampler.sample(logits, samplers, candidates)
         return StepResult(logits, want_keys, ctx.num_tokens, tokens)
 
     def commit(self, entries: Sequence[StepEntry], sequences) -> None:

@@ -36,7 +36,8 @@ _SIGNATURES = {
                                         c_void_p],
         "mir_gemm_f32": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
                          c_void_p],
-        "mir_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
+        "mir_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
+                       c_void_p, c_int, c_void_p],
         "mir_repetition_penalty": [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mir_decode_prepare": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
         "mir_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p],
@@ -49,6 +50,9 @@ _SIGNATURES = {
                                             c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                             c_int, c_void_p, c_longlong, c_void_p],
         "mir_decode_attention_tc_takes": [c_int, c_int, c_int],
+        "mir_head_logits_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                 c_int, c_void_p, c_size_t, c_void_p, c_void_p],
+        "mir_gemm_tc_stream_head_candidates": [c_int],
         "mir_decode_partition_keys": [c_int, c_int, c_int, c_int, c_int, c_int],
         "mir_decode_attention_plan": [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "mir_decode_attention_tc_error": [],
@@ -725,18 +729,71 @@ def ranked_scratch_keys(rows: int, vocab: int) -> int:
     return rows * padded
 
 
+class HeadCandidates:
+    """What the output head's kernel can leave beside the logits (head_logits): per row the largest finite logit of
+    every 32 columns and its column.  `valid` says whether the last product that was given these buffers filled
+    them; sample() then finds each row's largest logit among them instead of among the whole vocabulary."""
+
+    def __init__(self, values: torch.Tensor, indices: torch.Tensor):
+        self.values, self.indices, self.valid = values, indices, False
+
+    @staticmethod
+    def count(vocab: int) -> int:
+        return -(-vocab // 128) * 4
+
+    @classmethod
+    def allocate(cls, alloc, rows: int, vocab: int) -> "HeadCandidates":
+        return cls(alloc((rows, cls.count(vocab)), torch.float32), alloc((rows, cls.count(vocab)), torch.int32))
+
+
+def head_logits(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
+                candidates: Optional[HeadCandidates] = None) -> None:
+    """out[M, V] (float32) = x . weight^T, the output head.  bfloat16 rows up to few_rows_max go through the
+    weight-streaming kernel, whose epilogue also fills `candidates` (and sets candidates.valid); every other case is
+    linear() and leaves candidates.valid False."""
+    if candidates is not None:
+        candidates.valid = False
+    if candidates is None or x.dtype != torch.bfloat16:
+        linear(x, weight, out)
+        return
+    _cuda(x, weight, out, candidates.values, candidates.indices)
+    m, k = x.shape
+    n = weight.shape[0]
+    _require(weight.dtype == torch.bfloat16 and weight.shape[1] == k and weight.is_contiguous()
+             and out.dtype == torch.float32 and out.shape == (m, n) and x.stride(1) == 1 and out.stride(1) == 1,
+             "head_logits: bfloat16 x [M, K] and weight [V, K], float32 out [M, V]")
+    _require(candidates.values.shape == candidates.indices.shape and candidates.values.shape[0] >= m
+             and candidates.values.is_contiguous() and candidates.indices.is_contiguous()
+             and candidates.values.dtype == torch.float32 and candidates.indices.dtype == torch.int32,
+             "head_logits: candidates are float32 values and int32 indices of one shape [rows, count]")
+    lib = library("bf16")
+    workspace = _lt_workspace(x.device)
+    wrote = c_int(0)
+    _check(lib, lib.mir_head_logits_bf16(x.data_ptr(), x.stride(0), weight.data_ptr(), out.data_ptr(), out.stride(0), m, n,
+                                         k, candidates.values.data_ptr(), candidates.indices.data_ptr(),
+                                         candidates.values.shape[1], workspace.data_ptr(), workspace.numel(), _stream(),
+                                         ctypes.addressof(wrote)))
+    candidates.valid = bool(wrote.value)
+
+
 def sample(logits: torch.Tensor, options: torch.Tensor, tokens: torch.Tensor,
-           sort_keys: Optional[torch.Tensor] = None, needs_ranked: bool = False) -> None:
-    """tokens[r] = one token from row r of the 32-bit logits; options is a uint8 view of SAMPLE_OPTIONS records."""
+           sort_keys: Optional[torch.Tensor] = None, needs_ranked: bool = False,
+           candidates: Optional[HeadCandidates] = None) -> None:
+    """tokens[r] = one token from row r of the 32-bit logits; options is a uint8 view of SAMPLE_OPTIONS records.
+    `candidates` (valid, from the product that wrote these very logits): where each row's largest logit is found."""
     _cuda(logits, options, tokens, sort_keys)
     rows, vocab = logits.shape
     _require(logits.dtype == torch.float32 and logits.stride(1) == 1 and tokens.dtype == torch.int32
              and tokens.numel() >= rows and options.numel() * options.element_size() >= rows * SAMPLE_OPTIONS.itemsize,
              "sample: bad arguments")
     capacity = 0 if sort_keys is None else sort_keys.numel() * sort_keys.element_size() // 8
+    use = candidates is not None and candidates.valid and candidates.values.shape[0] >= rows
     lib = library("core")
     _check(lib, lib.mir_sample(logits.data_ptr(), logits.stride(0), rows, vocab, options.data_ptr(), _ptr(sort_keys),
-                               capacity, int(needs_ranked), tokens.data_ptr(), _stream()))
+                               capacity, int(needs_ranked), tokens.data_ptr(),
+                               candidates.values.data_ptr() if use else None,
+                               candidates.indices.data_ptr() if use else None,
+                               candidates.values.shape[1] if use else 0, _stream()))
 
 
 def repetition_penalty(logits: torch.Tensor, ids: torch.Tensor, id_rows: torch.Tensor,

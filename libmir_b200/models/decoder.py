@@ -157,10 +157,12 @@ class DecoderModel:
         self._runs_key, self._runs_list = key, runs
         return runs
 
-    def logits(self, ctx, residual: torch.Tensor, rows: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """32-bit logits [len(rows), V] at the packed rows `rows` (an int32 device tensor)."""
+    def logits(self, ctx, residual: torch.Tensor, rows: torch.Tensor, out: Optional[torch.Tensor] = None,
+               candidates=None) -> torch.Tensor:
+        """32-bit logits [len(rows), V] at the packed rows `rows` (an int32 device tensor).  `candidates`
+        (kernels.HeadCandidates): filled by the head's kernel where it can, for the sampling that follows."""
         normed = self.final_norm.forward(ctx, residual, rows=rows)
         if out is None:
             out = ctx.alloc((rows.numel(), self.spec.vocab_size), torch.float32)
-        kernels.linear(normed, self.head, out)
+        kernels.head_logits(normed, self.head, out, candidates)
         return out

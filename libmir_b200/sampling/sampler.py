@@ -78,13 +78,15 @@ class DeviceSampler:
             self._greedy_options = torch.from_numpy(host.view(np.uint8)).to(self.device)
         return self._greedy_options
 
-    def sample(self, logits: torch.Tensor, samplers: Sequence[RequestSampler]) -> torch.Tensor:
-        """One token per row; returns an int32 device tensor [rows] (valid until the next call)."""
+    def sample(self, logits: torch.Tensor, samplers: Sequence[RequestSampler], candidates=None) -> torch.Tensor:
+        """One token per row; returns an int32 device tensor [rows] (valid until the next call).  `candidates`:
+        what the head's kernel left beside these logits (kernels.HeadCandidates); not used once a penalty has
+        changed the logits."""
         rows = logits.shape[0]
         assert rows == len(samplers)
         tokens = self._token_buffer(rows)
         if all(s.greedy and s.repetition_penalty <= 1.0 for s in samplers):
-            kernels.sample(logits, self.greedy_options(rows), tokens)
+            kernels.sample(logits, self.greedy_options(rows), tokens, candidates=candidates)
             return tokens
         penalised = [(r, s) for r, s in enumerate(samplers) if s.repetition_penalty > 1.0 and s.seen]
         if penalised:
@@ -105,5 +107,6 @@ class DeviceSampler:
             need = kernels.ranked_scratch_keys(rows, self.vocab_size)
             if self._sort_keys is None or self._sort_keys.numel() < need:
                 self._sort_keys = torch.empty(need, dtype=torch.int64, device=self.device)
-        kernels.sample(logits, options, tokens, self._sort_keys if needs_ranked else None, needs_ranked)
+        kernels.sample(logits, options, tokens, self._sort_keys if needs_ranked else None, needs_ranked,
+                       None if penalised else candidates)
         return tokens

@@ -333,6 +333,54 @@ def device_sample(logits, options):
     return tokens.cpu().tolist()
 
 
+@pytest.mark.parametrize("rows,vocab,hidden", [(8, 5003, 256), (1, 640, 64), (19, 33000, 128), (40, 2000, 64)])
+def test_the_heads_kernel_leaves_the_candidates_for_each_rows_largest_logit(rows, vocab, hidden):
+    """The output head through the weight-streaming kernel also writes, per row, the largest finite logit of every
+    32 columns and its column.  The candidates must hold each row's arg max (ties to the lowest id: some vocabulary
+    rows are copies of others), and sampling with them must give what sampling from the logits alone gives, greedy
+    and drawn.  More than 32 rows go through the library: no candidates, the same tokens."""
+    from libmir_b200 import kernels
+    torch.manual_seed(vocab)
+    x = (torch.randn(rows, hidden) * 0.7).bfloat16().cuda()
+    weight = (torch.randn(vocab, hidden) * 0.3).bfloat16()
+    copies = torch.randint(0, vocab, (vocab // 7,))
+    weight[copies] = weight[(copies * 31 + 5) % vocab]                # equal logits at different ids
+    weight = weight.cuda()
+    logits = torch.empty(rows, vocab, device="cuda")
+    candidates = kernels.HeadCandidates.allocate(lambda shape, dtype: torch.full(shape, -7, dtype=dtype, device="cuda"),
+                                                 rows, vocab)
+    kernels.head_logits(x, weight, logits, candidates)
+    plain = torch.empty_like(logits)
+    kernels.linear(x, weight, plain)
+    assert torch.equal(logits, plain)
+    assert candidates.valid == (rows <= kernels.few_rows_max())
+    want = [int(torch.nonzero(row == row.max())[0]) for row in logits.cpu()]
+    if candidates.valid:
+        values, indices = candidates.values.cpu(), candidates.indices.cpu()
+        groups = -(-vocab // 32)
+        for r in range(rows):
+            for g in range(groups):
+                chunk = logits[r, 32 * g: 32 * g + 32].cpu()
+                assert float(values[r, g]) == float(chunk.max())
+                assert int(indices[r, g]) == 32 * g + int(torch.nonzero(chunk == chunk.max())[0])
+            assert (indices[r, groups:] == 0x7fffffff).all()          # columns beyond the vocabulary: no candidate
+    host = np.zeros(rows, dtype=kernels.SAMPLE_OPTIONS)
+    for name, options in (("greedy", (0.0, 0.0, 1.0, 0, 0)), ("drawn", (0.37, 0.8, 1.0, 0, 0)),
+                          ("top-k", (0.61, 0.9, 1.0, 20, 0))):
+        host[:] = options
+        device_options = torch.from_numpy(host.view(np.uint8)).cuda()
+        ranked = name == "top-k"
+        keys = torch.empty(kernels.ranked_scratch_keys(rows, vocab), dtype=torch.int64, device="cuda") if ranked else None
+        with_candidates = torch.empty(rows, dtype=torch.int32, device="cuda")
+        without = torch.empty(rows, dtype=torch.int32, device="cuda")
+        kernels.sample(logits, device_options, with_candidates, keys, ranked, candidates)
+        kernels.sample(logits, device_options, without, keys, ranked)
+        assert with_candidates.tolist() == without.tolist(), name
+        if name == "greedy":
+            assert without.tolist() == want
+    assert kernels.stream_linear_error() == 0
+
+
 def test_greedy_ties_go_to_the_lowest_id():
     logits = torch.full((3, 5003), -1.0)
     logits[0, [4000, 17, 2500]] = 3.0
