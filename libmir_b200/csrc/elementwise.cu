@@ -3,6 +3,7 @@
 //
 // What each replaces in libmir: embedding_bf16.cu:3-19, rms_norm_bf16.cu:3-36,
 // elementwise_bf16.cu:42-70 (packed gate|up), select_row_bf16.cu (row gather, folded into the norm).
+#include <cuda_fp16.h>
 #include "common.cuh"
 
 using namespace mir;
@@ -182,12 +183,39 @@ MIR_EXPORT int mir_add_bias(int bf16, float* x, const void* bias, int rows, int 
   return mir_check_launch("add_bias");
 }
 
-// kind: 0 f32->bf16, 1 bf16->f32.
+// kind: 0 f32->bf16, 1 bf16->f32, 2 f16->bf16, 3 f16->f32 (what a checkpoint may store, to what the engine keeps).
 MIR_EXPORT int mir_cast(int kind, const void* src, void* dst, size_t total, cudaStream_t stream) {
   if (kind == 0) LAUNCH_1D(cast_kernel, total, (const float*)src, (__nv_bfloat16*)dst, total);
   else if (kind == 1) LAUNCH_1D(cast_kernel, total, (const __nv_bfloat16*)src, (float*)dst, total);
+  else if (kind == 2) LAUNCH_1D(cast_kernel, total, (const __half*)src, (__nv_bfloat16*)dst, total);
+  else if (kind == 3) LAUNCH_1D(cast_kernel, total, (const __half*)src, (float*)dst, total);
   else { mir_set_error("cast: unknown kind %d", kind); return MIR_BAD_ARGUMENT; }
   return mir_check_launch("cast");
+}
+
+// Random weights on the device: element i of a tensor is a normal deviate (Box-Muller on two uniforms from the
+// SplitMix64 of seed + 2 i and seed + 2 i + 1) times `deviation`: the same for a seed whatever the launch shape.
+__device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+template <typename T>
+__global__ void random_normal_kernel(T* __restrict__ out, size_t total, unsigned long long seed, float deviation) {
+  const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (index >= total) return;
+  const unsigned long long a = splitmix64(seed + 2ull * index), b = splitmix64(seed + 2ull * index + 1ull);
+  const float u = ((float)(a >> 40) + 0.5f) * (1.0f / 16777216.0f);      // (0, 1)
+  const float v = (float)(b >> 40) * (1.0f / 16777216.0f);               // [0, 1)
+  out[index] = from_float<T>(deviation * sqrtf(-2.0f * logf(u)) * cospif(2.0f * v));
+}
+
+MIR_EXPORT int mir_random_normal(int bf16, void* out, size_t total, unsigned long long seed, float deviation,
+                                 cudaStream_t stream) {
+  if (bf16) LAUNCH_1D(random_normal_kernel, total, (__nv_bfloat16*)out, total, seed, deviation);
+  else LAUNCH_1D(random_normal_kernel, total, (float*)out, total, seed, deviation);
+  return mir_check_launch("random_normal");
 }
 
 // ---- decode batches that run as a captured graph -------------------------------------------------

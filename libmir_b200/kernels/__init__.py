@@ -306,15 +306,31 @@ def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
     _check(lib, lib.mir_add_bias(_is_bf16(bias), x.data_ptr(), bias.data_ptr(), rows, cols, _stream()))
 
 
+CAST_KINDS = {(torch.float32, torch.bfloat16): 0, (torch.bfloat16, torch.float32): 1, (torch.float16, torch.bfloat16): 2,
+              (torch.float16, torch.float32): 3}
+
+
 def cast(src: torch.Tensor, dst: torch.Tensor) -> None:
-    """float32 <-> bfloat16 copy of equal shapes (load-time cast, libmir dense_cast.cu)."""
+    """Copy of equal shapes between what a checkpoint stores and what the engine keeps: float32 <-> bfloat16,
+    float16 -> bfloat16 or float32 (load-time casts, libmir dense_cast.cu)."""
     _cuda(src, dst)
     _require(src.is_contiguous() and dst.is_contiguous() and src.numel() == dst.numel(), "cast: bad arguments")
-    kinds = {(torch.float32, torch.bfloat16): 0, (torch.bfloat16, torch.float32): 1}
-    kind = kinds.get((src.dtype, dst.dtype))
+    kind = CAST_KINDS.get((src.dtype, dst.dtype))
     _require(kind is not None, f"cast: {src.dtype} -> {dst.dtype} is not supported")
     lib = library("core")
     _check(lib, lib.mir_cast(kind, src.data_ptr(), dst.data_ptr(), src.numel(), _stream()))
+
+
+def random_normal(out: torch.Tensor, seed: int, deviation: float) -> None:
+    """out (contiguous float32 or bfloat16, on the device) = deviation x normal deviates that depend on `seed` and
+    the element's index only."""
+    _cuda(out)
+    _require(out.is_contiguous() and out.dtype in (torch.float32, torch.bfloat16), "random_normal: bad arguments")
+    lib = library("core")
+    lib.mir_random_normal.argtypes = [c_int, c_void_p, c_size_t, ctypes.c_ulonglong, c_float, c_void_p]
+    lib.mir_random_normal.restype = c_int
+    _check(lib, lib.mir_random_normal(int(out.dtype == torch.bfloat16), out.data_ptr(), out.numel(),
+                                      seed & ((1 << 64) - 1), float(deviation), _stream()))
 
 
 def decode_prepare(positions, block_table, page_size, slot_mapping, context_lens) -> None:

@@ -118,7 +118,19 @@ def _to_device(tensor: torch.Tensor, store: str, env) -> torch.Tensor:
     target = torch.float32 if store == "float32" else env.dtype
     if tensor.dtype not in (torch.float32, torch.float16, torch.bfloat16, torch.float64):
         raise WeightsError(f"a floating-point tensor is stored as {tensor.dtype}")
-    return tensor.to(device=env.device).to(target)
+    moved = tensor.to(device=env.device)
+    if moved.dtype == target:
+        return moved
+    if moved.is_cuda and moved.is_contiguous() and (moved.dtype, target) in _kernels().CAST_KINDS:
+        cast = torch.empty(moved.shape, dtype=target, device=moved.device)
+        _kernels().cast(moved, cast)                 # the engine's own cast kernel (libmir: dense_cast.cu)
+        return cast
+    return moved.to(target)
+
+
+def _kernels():
+    from .. import kernels
+    return kernels
 
 
 def load_into(model, folder, strict: bool = False) -> None:

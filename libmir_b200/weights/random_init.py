@@ -38,6 +38,11 @@ def random_tensor(name: str, spec, seed: int, dtype: torch.dtype, device="cpu") 
         return torch.ones(spec.shape, dtype=target, device=device)
     if spec.init == "zeros":
         return torch.zeros(spec.shape, dtype=target, device=device)
+    if torch.device(device).type == "cuda" and target in (torch.float32, torch.bfloat16):
+        from .. import kernels
+        values = torch.empty(spec.shape, dtype=target, device=device)
+        kernels.random_normal(values, _seed_for(seed, name), STD)     # the engine's own generator, on the device
+        return values
     generator = torch.Generator(device=device)
     generator.manual_seed(_seed_for(seed, name))
     values = torch.randn(spec.shape, generator=generator, dtype=torch.float32, device=device) * STD

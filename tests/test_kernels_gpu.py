@@ -593,3 +593,38 @@ def test_weight_streaming_product_and_its_epilogues(m, n, k):
     kernels.stream_linear(cuda(x), cuda(w[:2 * inter]), gated, swiglu=True)
     close(gated, plain_impl.silu(exact[:, :inter]) * exact[:, inter:2 * inter], torch.bfloat16, factor=2)
     assert kernels.stream_linear_error() == 0
+
+
+# ------------------------------------------------------------------------------ load-time kernels
+@pytest.mark.parametrize("source,target", [(torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32),
+                                           (torch.float16, torch.bfloat16), (torch.float16, torch.float32)])
+def test_load_time_casts_round_as_a_conversion_does(source, target):
+    from libmir_b200 import kernels
+    torch.manual_seed(3)
+    values = (torch.randn(3, 1001) * 5).to(source).cuda()
+    values[0, :4] = torch.tensor([0.0, -0.0, 65504.0 if source == torch.float16 else 3.0e38, -1e-7]).to(source)
+    out = torch.empty(values.shape, dtype=target, device="cuda")
+    kernels.cast(values, out)
+    assert torch.equal(out, values.to(target))
+
+
+def test_random_weights_from_the_device_generator():
+    """Normal deviates that depend on the seed and the element's index only: the same again for the same seed, others
+    for another seed, the asked deviation, no correlation between neighbours."""
+    from libmir_b200 import kernels
+    a = torch.empty(1 << 20, device="cuda")
+    b = torch.empty(1 << 20, device="cuda")
+    kernels.random_normal(a, 12345, 0.02)
+    kernels.random_normal(b, 12345, 0.02)
+    assert torch.equal(a, b) and torch.isfinite(a).all()
+    head = torch.empty(1000, device="cuda")
+    kernels.random_normal(head, 12345, 0.02)
+    assert torch.equal(head, a[:1000])                           # (no dependence on the launch's size)
+    kernels.random_normal(b, 12346, 0.02)
+    assert not torch.equal(a, b)
+    assert abs(float(a.mean())) < 2e-4 and abs(float(a.std()) - 0.02) < 2e-4
+    assert abs(float((a[1:] * a[:-1]).mean())) < 2e-6 and abs(float((a * b).mean())) < 2e-6
+    assert 0.66 < float((a.abs() < 0.02).float().mean()) < 0.70   # one deviation holds 68 % of a normal
+    half = torch.empty(4096, device="cuda", dtype=torch.bfloat16)
+    kernels.random_normal(half, 12345, 0.02)
+    assert torch.equal(half, a[:4096].bfloat16())
