@@ -2,8 +2,8 @@ from .api import (DecodeOutput, GenerationOutput, GenerationRequest, Library, Mo
                   Session)
 from .context import Arena, GroupContext, StepContext
 from .scheduler import PlannedEntry, Request, Scheduler
-from .step import StepEntry, StepResult, StepRunner
+from .step import DecodeTimings, StepEntry, StepResult, StepRunner
 
 __all__ = ["Arena", "DecodeOutput", "GenerationOutput", "GenerationRequest", "GroupContext", "Library", "Model",
            "PlannedEntry", "PrefillOutput", "Request", "SamplingLogits", "Scheduler", "Session", "StepContext",
-           "StepEntry", "StepResult", "StepRunner"]
+           "DecodeTimings", "StepEntry", "StepResult", "StepRunner"]

@@ -161,6 +161,28 @@ class Model:
         with torch.cuda.device(self.device):
             return self.runner.step(entries, samplers)
 
+    # -- profiling, in libmir's manner (src/engine/profile.rs:46-90, cuda/src/engine/mod.rs:75-103) -------------
+    def set_profile_decode(self, enabled: bool) -> None:
+        """While on, every decode step (one token per request) carries DecodeTimings (StepResult.timings, kept in
+        runner.decode_timings; generate's metrics add them up), and an accelerator-profiler capture range is open."""
+        if enabled:
+            self.start_profiler_capture()
+            self.runner.profile_decode = True
+            return
+        self.runner.profile_decode = False
+        self.stop_profiler_capture()
+
+    def start_profiler_capture(self) -> None:
+        """Opens a capture range for an attached profiler (cudaProfilerStart) without changing what runs."""
+        if not getattr(self, "_capturing", False):
+            torch.cuda.profiler.start()
+            self._capturing = True
+
+    def stop_profiler_capture(self) -> None:
+        if getattr(self, "_capturing", False):
+            torch.cuda.profiler.stop()
+            self._capturing = False
+
     def decode_many(self, entries: Sequence[StepEntry], samplers: Sequence[RequestSampler], steps: int):
         """Several greedy decode steps back to back on the device; see StepRunner.decode_many."""
         with torch.cuda.device(self.device):
@@ -188,6 +210,7 @@ class Model:
         self._check_loaded()
         scheduler = self._scheduler()
         started = time.perf_counter()
+        first_timing = len(self.runner.decode_timings)
         records = []
         for request in requests:
             settings = self._settings(request.options)
@@ -204,12 +227,18 @@ class Model:
             scheduler.abandon()          # after a step that raised: nothing of this call stays live in the shared cache
         elapsed = time.perf_counter() - started
         generated = sum(len(r.output) for r in records)
+        profile = {}
+        if self.runner.profile_decode:
+            timings = self.runner.decode_timings[first_timing:]
+            profile = {"decode_steps_profiled": len(timings),
+                       "decode_backend_seconds": sum(t.backend_execution for t in timings),
+                       "decode_device_seconds": sum(t.device_execution for t in timings)}
         outputs = []
         for record in records:
             outputs.append(GenerationOutput(list(record.output), record.finish_reason or "unknown", {
                 "seconds": elapsed, "steps": scheduler.steps, "prompt_tokens": len(record.prompt),
                 "generated_tokens": len(record.output), "preemptions": record.preemptions,
-                "batch_tokens_per_second": generated / elapsed if elapsed > 0 else 0.0,
+                "batch_tokens_per_second": generated / elapsed if elapsed > 0 else 0.0, **profile,
             }, record.request_id))
         return outputs
 

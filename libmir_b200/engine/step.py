@@ -10,6 +10,7 @@ output.rs:112-178), which returns only last-position results; here any position 
 
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -30,12 +31,37 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
+class DecodeTimings:
+    """What libmir attaches to the outputs of a decode step while decode profiling is on (runtime DecodeTimings,
+    cuda/src/engine/profile.rs:7-46): how long the step took on the host (taking pages, the upload, the launches) and
+    on the device (between two events on the step's stream), and how many rows it had."""
+
+    def __init__(self, backend_execution: float, batch_rows: int, started: torch.cuda.Event, stopped: torch.cuda.Event):
+        self.backend_execution = backend_execution      # seconds on the host
+        self.batch_rows = batch_rows
+        self._events = (started, stopped)
+        self._device: Optional[float] = None
+
+    @property
+    def device_execution(self) -> float:
+        """Seconds on the device (waits for the step to be over the first time it is asked for)."""
+        if self._device is None:
+            self._events[1].synchronize()
+            self._device = self._events[0].elapsed_time(self._events[1]) / 1e3
+        return self._device
+
+    def as_dict(self) -> dict:
+        return {"backend_execution": self.backend_execution, "device_execution": self.device_execution,
+                "batch_rows": self.batch_rows}
+
+
 @dataclass
 class StepResult:
     logits: Optional[torch.Tensor]          # float32 [wanted, vocab] on the device; valid until the next step
     rows: List[tuple]                       # (request_id, local index) for each logits row, in order
     num_tokens: int = 0
     tokens: Optional[torch.Tensor] = None   # int32 [wanted] sampled tokens on the device, if samplers were given
+    timings: Optional[DecodeTimings] = None  # of a decode step, while decode profiling is on
 
 
 class StepRunner:
@@ -48,6 +74,8 @@ class StepRunner:
         self.storage = storage
         self.device = device
         self.decode_graphs = decode_graphs
+        self.profile_decode = False          # Model.set_profile_decode
+        self.decode_timings: List[DecodeTimings] = []   # of the profiled decode steps, oldest first (at most 4,096)
         self._graphs = None
         self._graphs_usable = False
         self.sampler = None
@@ -256,6 +284,11 @@ class StepRunner:
     def step(self, entries: Sequence[StepEntry], samplers=None) -> StepResult:
         """Run one batch: reserve pages, run the tokens, commit the new lengths.  With `samplers` (one
         per wanted row, in order) the result also holds the sampled tokens."""
+        profiled = self.profile_decode and bool(entries) and all(len(e.tokens) == 1 for e in entries)
+        if profiled:
+            started_at = time.perf_counter()
+            started, stopped = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            started.record()
         entries, sequences = self.reserve(entries)
         if not entries:
             return StepResult(None, [], 0)
@@ -263,6 +296,11 @@ class StepRunner:
         self.commit(entries, sequences)
         self.steps += 1
         self.tokens_run += result.num_tokens
+        if profiled:
+            stopped.record()
+            result.timings = DecodeTimings(time.perf_counter() - started_at, len(entries), started, stopped)
+            self.decode_timings.append(result.timings)
+            del self.decode_timings[:-4096]
         return result
 
     def decode_many(self, entries: Sequence[StepEntry], samplers, steps: int) -> torch.Tensor:

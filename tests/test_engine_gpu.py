@@ -233,6 +233,46 @@ def test_session_prefill_and_decode(tmp_path):
     model.unload()
 
 
+def test_decode_profiling_attaches_timings_to_decode_steps_only(tmp_path):
+    """Model.set_profile_decode, as libmir's: while it is on, steps of one token per request carry how long they took
+    on the host and on the device and how many rows they had; portions of prompts and steps after it was switched off
+    carry nothing, and the tokens are what they are without it."""
+    from libmir_b200 import GenerationOverrides, GenerationRequest, StepEntry
+    from libmir_b200.sampling import RequestSampler
+    folder = make_folder(tmp_path, TINY_B, seed=5, dtype="bfloat16")
+    rng = np.random.default_rng(9)
+    prompts = [random_ids(rng, TINY_B["vocab_size"], n) for n in (12, 7)]
+    model = load(folder, "bfloat16")
+    request = [GenerationRequest(prompt_ids=p, options=GenerationOverrides(max_tokens=6, ignore_eos=True)) for p in prompts]
+    plain = [o.token_ids for o in model.generate_batch(request)]
+    model.set_profile_decode(True)
+    outputs = model.generate_batch(request)
+    assert [o.token_ids for o in outputs] == plain
+    metrics = outputs[0].metrics
+    assert metrics["decode_steps_profiled"] == 5                  # six tokens: one from the prompts' step, five decoded
+    assert 0.0 < metrics["decode_device_seconds"] < 1.0 and 0.0 < metrics["decode_backend_seconds"] < 5.0
+    for name in ("a", "b"):
+        model.admit(name)
+    first = model.step([StepEntry("a", prompts[0], [len(prompts[0]) - 1]), StepEntry("b", prompts[1], [6])],
+                       [RequestSampler(), RequestSampler()])
+    assert first.timings is None                                  # a step of prompt portions
+    tokens = first.tokens.cpu().tolist()
+    second = model.step([StepEntry("a", [tokens[0]], [0]), StepEntry("b", [tokens[1]], [0])],
+                        [RequestSampler(), RequestSampler()])
+    assert second.timings is not None and second.timings.batch_rows == 2
+    assert second.timings.device_execution > 0.0 and second.timings.backend_execution > 0.0
+    assert set(second.timings.as_dict()) == {"backend_execution", "device_execution", "batch_rows"}
+    model.set_profile_decode(False)
+    tokens = second.tokens.cpu().tolist()
+    third = model.step([StepEntry("a", [tokens[0]], [0]), StepEntry("b", [tokens[1]], [0])],
+                       [RequestSampler(), RequestSampler()])
+    assert third.timings is None
+    for name in ("a", "b"):
+        model.release(name)
+    assert "decode_steps_profiled" not in model.generate_batch(request)[0].metrics
+    model.unload()
+
+
 def test_generate_command_line(tmp_path):
     """bin/generate as a user runs it: a folder written by --write-random-model, then greedy tokens that match
     the plain implementation, the `finish_reason=` line, and the batch form."""
