@@ -31,6 +31,7 @@ from typing import Dict, List, Optional, Sequence
 from ..config.spec import FixedState, PagedKv
 from ..errors import KvCachePressure, KvCapacity, NoFreeSlot
 from .pages import PagePool
+from .prefix import PrefixIndex, page_key
 
 
 @dataclass
@@ -58,11 +59,18 @@ class Sequence_:
     tables: List[List[int]] = field(default_factory=list)      # per group: page id or -1 per block
     first_live: List[int] = field(default_factory=list)        # per group: first block not yet released
     serial: int = 0                                   # unique over the manager's life (ids and slots are reused)
+    tokens: Optional[List[int]] = None                # with a prefix cache: the ids of the cached tokens (None: unknown)
+    keys: List[bytes] = field(default_factory=list)   # with a prefix cache: the key of every full page so far
+    prefix_tokens: int = 0                            # tokens this request found cached when it was admitted
 
 
 class CacheManager:
-    def __init__(self, plan: Sequence, page_size: int, num_pages: int, max_requests: int):
-        """`plan` is DecoderModel.cache_plan(): one CacheEntryPlan per schedule entry."""
+    def __init__(self, plan: Sequence, page_size: int, num_pages: int, max_requests: int,
+                 prefix_cache: bool = False, model_key: str = ""):
+        """`plan` is DecoderModel.cache_plan(): one CacheEntryPlan per schedule entry.  `prefix_cache`: full pages
+        are remembered by the tokens they hold (cache/prefix.py) and shared by requests that start alike; it takes
+        effect where every cached token stays in its page for the request's life and nothing else is kept per
+        request: one group of pages without a window, no fixed-size state."""
         if page_size <= 0 or max_requests <= 0:
             raise ValueError("page_size and max_requests must be greater than zero")
         self.page_size = page_size
@@ -89,13 +97,21 @@ class CacheManager:
             if item.source != item.entry and isinstance(item.requirement, PagedKv):
                 self.entry_group[item.entry] = self.entry_group[item.source]
                 self.entry_local[item.entry] = self.entry_local[item.source]
+        capable = len(self.groups) == 1 and self.groups[0].window is None and not self.state_entries
+        self.prefix: Optional[PrefixIndex] = PrefixIndex() if prefix_cache and capable else None
+        self._model_key = model_key.encode()
+        self.prefix_hit_tokens = 0                     # tokens that admitted requests found cached
+        self.prefix_evictions = 0
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self._serial = 0                               # counts admissions: ids and slots are reused, serials are not
         self.live: Dict[object, Sequence_] = {}
         self.fresh_slots: List[int] = []               # slots handed out since the device last zeroed state
 
     # -- admission ---------------------------------------------------------------
-    def admit(self, request_id) -> Sequence_:
+    def admit(self, request_id, tokens: Optional[Sequence[int]] = None) -> Sequence_:
+        """A new live request.  With a prefix cache and the tokens it will be fed: the longest run of full pages that
+        hold exactly its first tokens is taken over (shared, not copied), `length` starts behind them, and at least
+        one token is left to compute."""
         if request_id in self.live:
             raise ValueError(f"request {request_id!r} is already live")
         if not self._free_slots:
@@ -106,6 +122,24 @@ class CacheManager:
                              serial=self._serial)
         self.live[request_id] = sequence
         self.fresh_slots.append(slot)
+        if self.prefix is not None:
+            sequence.tokens = []
+            if tokens is not None:
+                pool, table, page = self.groups[0].pool, sequence.tables[0], self.page_size
+                parent = None
+                for block in range((len(tokens) - 1) // page):
+                    key = page_key(self._model_key, parent, tokens[block * page:(block + 1) * page])
+                    cached = self.prefix.get(key)
+                    if cached is None:
+                        break
+                    pool.retain(cached)
+                    table.append(cached)
+                    sequence.keys.append(key)
+                    parent = key
+                cached_tokens = len(table) * page
+                sequence.tokens = [int(t) for t in tokens[:cached_tokens]]
+                sequence.length = sequence.reserved = sequence.prefix_tokens = cached_tokens
+                self.prefix_hit_tokens += cached_tokens
         return sequence
 
     @property
@@ -131,7 +165,7 @@ class CacheManager:
     def can_grow(self, sequence: Sequence_, new_length: int, spare: Optional[List[int]] = None) -> bool:
         need = self.pages_needed(sequence, new_length)
         spare = spare or [0] * len(self.groups)
-        return all(n <= g.pool.free - s for n, g, s in zip(need, self.groups, spare))
+        return all(n <= g.pool.available - s for n, g, s in zip(need, self.groups, spare))
 
     def grow(self, sequence: Sequence_, new_length: int) -> None:
         """Allocate pages so that tokens up to new_length fit, in every group or in none."""
@@ -144,16 +178,56 @@ class CacheManager:
             live_now = len(table) - first                    # the blocks before `first` were given back
             if live_now + n > group.pool.count:
                 raise KvCapacity(live_now + n, group.pool.count, f"group {group.index}")
-            if n > group.pool.free:
-                raise KvCachePressure(n, group.pool.free, f"group {group.index}")
+            if n > group.pool.available:
+                raise KvCachePressure(n, group.pool.available, f"group {group.index}")
         for n, group, table in zip(need, self.groups, sequence.tables):
+            self._reclaim(group, n)
             table.extend(group.pool.take(n))
         sequence.reserved = max(sequence.reserved, new_length)
 
-    def commit(self, sequence: Sequence_, new_length: int) -> None:
-        """The tokens up to new_length are now cached; release what windows have passed."""
+    def _reclaim(self, group: GroupInfo, n: int) -> None:
+        """Make n pages free by dropping cached prefixes that no request holds, the least recently used first."""
+        if n <= group.pool.free or self.prefix is None:
+            return
+        for key, page in self.prefix.oldest_first():
+            if group.pool.holders(page) == 1:
+                self.prefix.remove(key)
+                group.pool.evict(page)
+                self.prefix_evictions += 1
+                if n <= group.pool.free:
+                    return
+
+    def clear_prefix(self) -> int:
+        """Forget every cached prefix (libmir: Engine::clear_prefix_cache, src/engine/mod.rs:187-200).  Pages that live
+        requests hold stay theirs; the rest are free again.  Returns how many pages were forgotten."""
+        if self.prefix is None:
+            return 0
+        pool, dropped = self.groups[0].pool, 0
+        for key, page in self.prefix.oldest_first():
+            self.prefix.remove(key)
+            pool.forget(page)
+            dropped += 1
+        return dropped
+
+    def commit(self, sequence: Sequence_, new_length: int, tokens: Optional[Sequence[int]] = None) -> None:
+        """The tokens up to new_length are now cached; release what windows have passed.  `tokens`: the ids that were
+        just cached (with a prefix cache, the pages they complete are remembered; without them the request's later
+        pages are not)."""
         if self.groups and new_length > len(sequence.tables[0]) * self.page_size:
             raise ValueError("commit beyond the pages that were grown")
+        if self.prefix is not None and sequence.tokens is not None:
+            if tokens is None or len(sequence.tokens) + len(tokens) != new_length:
+                sequence.tokens = None                         # what the pages hold from here on is not known
+            else:
+                sequence.tokens.extend(int(t) for t in tokens)
+                pool, table, page = self.groups[0].pool, sequence.tables[0], self.page_size
+                for block in range(len(sequence.keys), new_length // page):
+                    parent = sequence.keys[-1] if sequence.keys else None
+                    key = page_key(self._model_key, parent, sequence.tokens[block * page:(block + 1) * page])
+                    sequence.keys.append(key)
+                    if self.prefix.get(key, touch=False) is None and not pool.is_cached(table[block]):
+                        self.prefix.insert(key, table[block])
+                        pool.mark_cached(table[block])
         sequence.length = new_length
         for index, group in enumerate(self.groups):
             if group.window is None:
@@ -192,26 +266,36 @@ class CacheManager:
             "free_slots": len(self._free_slots),
             "groups": [{"window": g.window, "kv_heads": g.requirement.kv_heads, "head_dim": g.requirement.head_dim,
                         "value_head_dim": g.requirement.value_dim,
-                        "entries": len(g.entries), "pages": g.pool.count, "free": g.pool.free,
+                        "entries": len(g.entries), "pages": g.pool.count, "free": g.pool.available,
                         "high_water": g.pool.high_water, "reused": g.pool.reused} for g in self.groups],
+            "cached_prefix_pages": len(self.prefix) if self.prefix is not None else 0,
+            "prefix_hit_tokens": self.prefix_hit_tokens, "prefix_evictions": self.prefix_evictions,
         }
 
     def check(self) -> None:
         """No page lost, held twice or freed twice; no slot lost or held twice."""
         for index, group in enumerate(self.groups):
             group.pool.check()
-            holders: Dict[int, object] = {}
+            holders: Dict[int, list] = {}
             for sequence in self.live.values():
                 for page in sequence.tables[index]:
                     if page < 0:
                         continue
-                    if page in holders:
-                        raise RuntimeError(f"page {page} of group {index} is held by {holders[page]!r} and "
-                                           f"{sequence.request_id!r}")
-                    holders[page] = sequence.request_id
-            if len(holders) != group.pool.held:
-                raise RuntimeError(f"group {index}: the pool says {group.pool.held} pages are held, tables hold "
-                                   f"{len(holders)}")
+                    holders.setdefault(page, []).append(sequence.request_id)
+            cached = set(self.prefix.pages()) if self.prefix is not None and index == 0 else set()
+            if self.prefix is not None and len(cached) != len(self.prefix):
+                raise RuntimeError("a page is in the prefix index under two keys")
+            for page, who in holders.items():
+                if len(who) > 1 and page not in cached:
+                    raise RuntimeError(f"page {page} of group {index} is held by {who!r} and is no cached prefix")
+            for page in set(holders) | cached:
+                expected = len(holders.get(page, [])) + (1 if page in cached else 0)
+                if group.pool.holders(page) != expected or group.pool.is_cached(page) != (page in cached):
+                    raise RuntimeError(f"page {page} of group {index}: the pool counts {group.pool.holders(page)} "
+                                       f"holders, tables and index hold it {expected} times")
+            if len(set(holders) | cached) != group.pool.held:
+                raise RuntimeError(f"group {index}: the pool says {group.pool.held} pages are held, tables and index "
+                                   f"hold {len(set(holders) | cached)}")
         slots = [s.slot for s in self.live.values()] + self._free_slots
         if sorted(slots) != list(range(self.max_requests)):
             raise RuntimeError(f"state slots are lost or held twice: {sorted(slots)}")

@@ -35,6 +35,8 @@ def main(argv=None) -> int:
     parser.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     parser.add_argument("--block-size", type=int, default=16, help="tokens in one cache page")
     parser.add_argument("--block-count", type=int, default=4096, help="cache pages")
+    parser.add_argument("--prefix-cache", action="store_true",
+                        help="remember full cache pages by their tokens and share them between requests that start alike")
     parser.add_argument("--max-batch-tokens", type=int, default=8192)
     parser.add_argument("--random-weights", metavar="CONFIG_JSON", default=None,
                         help="build the model this config.json describes with seeded random weights instead of "
@@ -59,7 +61,8 @@ def main(argv=None) -> int:
     if not args.model and not args.random_weights:
         parser.error("MODEL or the first argument is required")
 
-    runtime = RuntimeConfig(kv_cache=CacheConfig(block_size=args.block_size, block_count=args.block_count),
+    runtime = RuntimeConfig(kv_cache=CacheConfig(block_size=args.block_size, block_count=args.block_count,
+                                                 prefix_cache=args.prefix_cache),
                             scheduler=SchedulerConfig(max_batch_tokens=args.max_batch_tokens), dtype=args.dtype)
     library = Library(runtime)
     if args.random_weights:

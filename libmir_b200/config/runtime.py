@@ -16,6 +16,7 @@ DTYPES = ("bfloat16", "float32")
 class CacheConfig:
     block_size: int = 16          # tokens in one page
     block_count: int = 4096       # pages in every group's pool
+    prefix_cache: bool = False    # full pages are remembered by their tokens and shared by requests that start alike
 
     def validate(self) -> None:
         if self.block_size <= 0 or self.block_count <= 0:

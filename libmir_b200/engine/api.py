@@ -139,7 +139,8 @@ class Model:
         self.device = decoder.env.device
         plan = decoder.cache_plan()
         self.cache = CacheManager(plan, runtime.kv_cache.block_size, runtime.kv_cache.block_count,
-                                  runtime.scheduler.max_batch_requests)
+                                  runtime.scheduler.max_batch_requests, prefix_cache=runtime.kv_cache.prefix_cache,
+                                  model_key=f"{decoder.env.dtype}:{id(self)}")
         with torch.cuda.device(self.device):
             self.storage = CacheStorage(self.cache, plan, decoder.env.dtype, self.device)
             self.runner = StepRunner(decoder, self.cache, self.storage, self.device,
@@ -149,8 +150,10 @@ class Model:
         self._unloaded = False
 
     # -- the raw step (trace replay, tests) ------------------------------------------
-    def admit(self, request_id) -> None:
-        self.cache.admit(request_id)
+    def admit(self, request_id, tokens: Optional[Sequence[int]] = None) -> int:
+        """Make a request live.  With `tokens` (what it will be fed) and a prefix cache, the pages that hold its first
+        tokens already are taken over; returns how many tokens that is: feed the request from there."""
+        return self.cache.admit(request_id, tokens).length
 
     def release(self, request_id) -> None:
         self.cache.release(request_id)
@@ -238,6 +241,7 @@ class Model:
             outputs.append(GenerationOutput(list(record.output), record.finish_reason or "unknown", {
                 "seconds": elapsed, "steps": scheduler.steps, "prompt_tokens": len(record.prompt),
                 "generated_tokens": len(record.output), "preemptions": record.preemptions,
+                "cached_prompt_tokens": record.cached_tokens,
                 "batch_tokens_per_second": generated / elapsed if elapsed > 0 else 0.0, **profile,
             }, record.request_id))
         return outputs
@@ -250,6 +254,10 @@ class Model:
     def session(self) -> "Session":
         self._check_loaded()
         return Session(self)
+
+    def clear_prefix_cache(self) -> int:
+        """Forget the cached prefixes of this model (libmir: Engine::clear_prefix_cache, src/engine/mod.rs:187-200)."""
+        return self.cache.clear_prefix()
 
     def cache_stats(self) -> dict:
         return self.cache.stats()

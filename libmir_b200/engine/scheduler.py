@@ -51,6 +51,7 @@ class Request:
     preemptions: int = 0
     admitted_order: int = -1
     cancelled: bool = False
+    cached_tokens: int = 0               # tokens it found in the prefix cache (over all its admissions)
 
     @property
     def tokens(self) -> List[int]:
@@ -156,7 +157,7 @@ class Scheduler:
 
     # -- planning --------------------------------------------------------------------
     def _pages_free(self) -> List[int]:
-        return [group.pool.free for group in self.manager.groups]
+        return [group.pool.available for group in self.manager.groups]
 
     def _need(self, request: Request, count: int) -> List[int]:
         seq = self.manager.live[request.request_id]
@@ -219,7 +220,12 @@ class Scheduler:
                 if any(n > f for n, f in zip(need_all, free)) or self._portion(request, budget) <= 0:
                     break
                 self.waiting.popleft()
-                self.manager.admit(request.request_id)
+                # (with a prefix cache the request may find the pages of its first tokens: they count as fed, and
+                # as taken from what was free, though some of them were held by others anyway)
+                sequence = self.manager.admit(request.request_id, request.tokens)
+                request.fed = sequence.length
+                request.cached_tokens += sequence.prefix_tokens
+                free = [f - len(table) for f, table in zip(free, sequence.tables)]
                 request.state = "running"
                 request.admitted_order = self._admissions
                 self._admissions += 1

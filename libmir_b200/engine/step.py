@@ -220,13 +220,13 @@ class StepRunner:
         needs = [manager.pages_needed(seq, seq.length + len(e.tokens)) for e, seq in zip(entries, sequences)]
         for g, group in enumerate(manager.groups):
             total_need = sum(n[g] for n in needs)
-            if total_need <= group.pool.free:
+            if total_need <= group.pool.available:
                 continue
             for need, seq in zip(needs, sequences):     # a request too large for the whole pool is a hard error
                 alone = sum(1 for p in seq.tables[g] if p >= 0) + need[g]
                 if alone > group.pool.count:
                     raise KvCapacity(alone, group.pool.count, f"group {g}")
-            raise KvCachePressure(total_need, group.pool.free, f"group {g}")
+            raise KvCachePressure(total_need, group.pool.available, f"group {g}")
         for entry, seq in zip(entries, sequences):
             manager.grow(seq, seq.length + len(entry.tokens))
         return entries, sequences
@@ -279,7 +279,7 @@ class StepRunner:
 
     def commit(self, entries: Sequence[StepEntry], sequences) -> None:
         for entry, seq in zip(entries, sequences):
-            self.manager.commit(seq, seq.length + len(entry.tokens))
+            self.manager.commit(seq, seq.length + len(entry.tokens), entry.tokens)
 
     def step(self, entries: Sequence[StepEntry], samplers=None) -> StepResult:
         """Run one batch: reserve pages, run the tokens, commit the new lengths.  With `samplers` (one
@@ -327,7 +327,8 @@ class StepRunner:
             graph.replay()
         tokens = graph.token_log[:steps, :len(entries)].cpu()
         graph.step_counter.zero_()
-        self.commit(ahead, sequences)
+        for entry, seq in zip(ahead, sequences):      # (the sampled ids stayed on the device: no tokens to remember)
+            self.manager.commit(seq, seq.length + len(entry.tokens))
         self.steps += steps
         self.tokens_run += steps * len(entries)
         return tokens

@@ -27,10 +27,11 @@ class HostOnlyRunner(StepRunner):
         return StepResult(None, keys, sum(len(e.tokens) for e in entries))
 
 
-def build(config=TINY_A, pages=64, page_size=4, **scheduler_options):
+def build(config=TINY_A, pages=64, page_size=4, prefix_cache=False, **scheduler_options):
     model = DecoderModel(build_spec(config), BuildEnv(torch.float32, torch.device("meta")))
     options = SchedulerConfig(**scheduler_options)
-    manager = CacheManager(model.cache_plan(), page_size, pages, options.max_batch_requests)
+    manager = CacheManager(model.cache_plan(), page_size, pages, options.max_batch_requests,
+                           prefix_cache=prefix_cache, model_key="tiny")
     runner = HostOnlyRunner(model, manager)
     counter = {"n": 0}
 
@@ -252,3 +253,35 @@ def test_portions_keep_to_the_multiple_the_model_asks_for():
     manager.check()
     with pytest.raises(SchedulerError, match="multiples of 64"):
         Scheduler(manager, SchedulerConfig(max_batch_tokens=40), 128, lambda e, s: [], portion_multiple=64)
+
+
+def test_a_prompt_that_was_seen_before_is_fed_from_where_the_cached_pages_end():
+    scheduler, runner, manager = build(prefix_cache=True, max_batch_tokens=16, prefill_chunk_tokens=10)
+    scheduler.submit(request("a", 23, 3))
+    scheduler.run()
+    assert scheduler.finished[0].cached_tokens == 0
+    runner.ran.clear()
+    scheduler.submit(request("b", 23, 2))                  # the same 23 tokens: five full pages are there
+    scheduler.submit(request("c", 9, 2))                   # its first two pages too
+    scheduler.run()
+    by_name = {r.request_id: r for r in scheduler.finished}
+    assert by_name["b"].cached_tokens == 20 and by_name["c"].cached_tokens == 8
+    first = {rid: (start, count) for rid, start, count, _ in runner.ran[0]}
+    assert first == {"b": (20, 3), "c": (8, 1)}
+    assert all(start >= 20 for step in runner.ran for rid, start, _, _ in step if rid == "b")
+    assert len(by_name["b"].output) == 2 and len(by_name["c"].output) == 2
+    pool = manager.groups[0].pool
+    assert pool.available == 64 and pool.free == 64 - len(manager.prefix)
+    manager.check()
+
+
+def test_a_preempted_request_finds_its_own_pages_again_unless_they_were_needed():
+    scheduler, runner, manager = build(pages=6, page_size=4, prefix_cache=True, out_of_pages="preempt")
+    scheduler.submit(request("old", 8, 12))
+    scheduler.submit(request("young", 7, 12))
+    scheduler.run()
+    by_name = {r.request_id: r for r in scheduler.finished}
+    assert by_name["young"].preemptions >= 1
+    assert len(by_name["old"].output) == 12 and len(by_name["young"].output) == 12
+    assert manager.groups[0].pool.available == 6 and manager.prefix_evictions > 0
+    manager.check()
