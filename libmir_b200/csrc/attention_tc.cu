@@ -14,12 +14,17 @@
 // touches shared memory),  O += P V  (tcgen05.mma with A in tensor memory, accumulator stays in tensor memory for
 // the whole row of tiles).  Roles:
 //
-//   loaders   one warp for keys (and Q, once), one for values.  Per tile the pages that hold it: one TMA box per
-//             page and 64-wide half of the head (cp.async.bulk.tensor.2d through a tensor map over the cache,
-//             128-byte swizzle), into two-stage rings.  Pages the block table does not have (-1) are skipped.
-//   issuer    one thread.  Two S accumulators: S(t+2) = Q K(t+2)^T takes the one that holds P(t), so it is issued
-//             right behind O += P(t) V(t) (the tensor cores run products in the order of issue); while they work
-//             on one stream's tile, the other stream's softmax threads work on theirs.
+//   loaders   one warp for keys (and Q, once per item), one for values.  Per tile the pages that hold it: one TMA box
+//             per page and 64-wide half of the head (cp.async.bulk.tensor.2d through a tensor map over the cache,
+//             128-byte swizzle), into a ring of three key tiles and one of two value tiles.  Pages the block table
+//             does not have (-1) are skipped.  A tile costs a loader a handful of instructions (what does not change
+//             with the tile is worked out per item, stages are counted, the block table is read two tiles ahead).
+//   issuer    one warp that stays converged; the products are predicated on its elected lane and take their
+//             descriptors as 32-bit halves (tcgen05.cuh says why: a lone thread in a divergent branch fed the tensor
+//             cores a 64-cycle product only every 80 to 95 cycles beside the softmax warps).  Two S accumulators:
+//             S(t+2) = Q K(t+2)^T takes the one that holds P(t), so it is issued right behind O += P(t) V(t) (the
+//             tensor cores run products in the order of issue); while they work on one stream's tile, the other
+//             stream's softmax threads work on theirs.
 //   softmax   two streams of eight warps.  Stream s takes the key tiles t = s, s + 2, ... and keeps a softmax of
 //             its own over them: running maximum, denominator and an O accumulator of its own in tensor memory
 //             (as if the keys were split in two, as decode attention splits them); the two are merged when the
@@ -31,8 +36,9 @@
 //             denominator are rescaled, O by tcgen05.ld / tcgen05.st), so most tiles need no pass over O.
 //
 // V is read as an MN-major operand (rows of keys, 64 head elements per 128-byte row) exactly as the cache stores
-// it; nothing is transposed.  Masked keys get probability 0 by selection, never by arithmetic on what the cache
-// holds there, and the V ring starts zeroed, so a skipped page cannot inject a NaN (0 x NaN) into O.
+// it; nothing is transposed.  A hidden key's score is set to -inf by selection (in tiles that hide any), never by
+// arithmetic on what the cache holds there, so its probability is exactly 0; the V ring starts zeroed, so a skipped
+// page cannot inject a NaN (0 x NaN) into O.
 // Every wait is bounded in time; a role whose wait runs out raises g_tc_attention_error and stops waiting, the
 // CTA still frees its tensor memory and returns.
 // libmir computes prompt attention with a library plan (FmhaBf16Plan of its external mircuda crate,
@@ -41,6 +47,7 @@
 // metal/src/engine/dense/swiglu/attention.rs:93-107.
 #include <algorithm>
 #include "tcgen05.cuh"
+#include "trace.cuh"
 
 using namespace mir;
 using namespace mir::tc;
@@ -53,26 +60,47 @@ constexpr int kKeys = 128;                  // keys per tile
 constexpr int kDim = 128;                   // head_dim
 constexpr int kHalf = 128 * 128;            // bytes of a 128-row x 64-element half tile
 constexpr int kTile = 2 * kHalf;            // 32 KB
-constexpr int kOffQ = 0, kOffK = kTile, kOffV = 3 * kTile;
-constexpr int kSmemBytes = 5 * kTile + 1024;
+constexpr int kKeyStages = 3;              // the key ring: a tile is asked for when the product with the one three back is over
+constexpr int kOffQ = 0, kOffK = kTile, kOffV = (1 + kKeyStages) * kTile;
+constexpr int kSmemBytes = (3 + kKeyStages) * kTile + 1024;
 constexpr int kParts = 2;                   // softmax threads per query row and stream (each takes 64 columns)
 constexpr int kCols = kKeys / kParts;       // columns of a tile that one softmax thread handles
 constexpr int kStreamThreads = kRows * kParts;
 // key loader, issuer, eight softmax warps per stream, value loader
 __host__ __device__ constexpr int threads_for(int streams) { return (3 + 8 * streams) * 32; }
+constexpr int kFirstSoftmaxWarp = 2;
 constexpr uint32_t kTmemColumns = 512;      // S0 at 0, S1 at 128, O of stream 0 at 256, of stream 1 at 384
 constexpr float kRescaleThreshold = 8.0f;   // log2 of how far a tile's maximum may exceed the running one
 
 // barrier indices
-enum { Q_FULL = 0, K_FULL = 1, K_FREE = 3, V_FULL = 5, V_FREE = 7, S_FULL = 9, P_READY = 11, ITEM_DONE = 13, Q_FREE = 14,
-       O_FREE = 15, BARRIERS = 16 };
-// Tiles are counted over all items of a CTA (g): stage g & 1 of the rings and of the score accumulators, phase
-// parity (g >> 1) & 1 (P_READY too has one barrier per stage: the two streams work on neighbouring tiles at the same
+enum { Q_FULL = 0, K_FULL = 1, K_FREE = K_FULL + kKeyStages, V_FULL = K_FREE + kKeyStages, V_FREE = V_FULL + 2,
+       S_FULL = V_FREE + 2, P_READY = S_FULL + 2, ITEM_DONE = P_READY + 2, Q_FREE, O_FREE, BARRIERS };
+// Tiles are counted over all items of a CTA (g): stage g & 1 of the value ring and of the score accumulators, phase
+// parity (g >> 1) & 1 (the key ring: g % 3 and (g / 3) & 1, kept as running counters; P_READY too has one barrier per stage: the two streams work on neighbouring tiles at the same
 // time, and the arrivals of one must not count for the other's tile); items are counted too (n): Q_FULL, Q_FREE,
 // ITEM_DONE and O_FREE complete once per item.
 __device__ int g_tc_attention_error = 0;
 int g_streams = 2;
 int g_ctas = 0;                             // for measurements: 0 = one CTA per SM
+
+#ifdef MIR_TRACE
+// Cycle stamps (clock64 of the SM) of the first CTA's key tiles, one row of 16 per tile counted over its items:
+// 0 keys requested, 1 values requested, 2 scores issued, 3 issuer starts waiting for P, 4 issuer has P (product with
+// V issued next), 5 softmax starts waiting for the scores, 6 has them, 7 has read them, 8 knows the row's maximum,
+// 9 has the exponentials, 10 has written P and arrived (the softmax stamps: first warp of each stream); issuer again:
+// 11 starts waiting for the keys, 12 has them, 13 starts waiting for the values (3: has them), 14 product with V issued;
+// key loader: 15 keys' copies issued.  Rows 200 + n hold the end of the CTA's n-th item as its first softmax warp
+// sees it: 0 its tiles are done, 1 the streams have exchanged maxima and denominators, 2 the item's last product is
+// over, 3 the accumulators are read, 4 the rows are stored; 5 (row of the next item) the next item is known.
+constexpr int kTraceTiles = 256;
+__device__ long long g_prompt_tiles[kTraceTiles * 16];
+#define ATT_STAMP(tile, index)                                                                  \
+  do {                                                                                          \
+    if (blockIdx.x == 0 && (tile) >= 0 && (tile) < kTraceTiles) g_prompt_tiles[(tile) * 16 + (index)] = clock64(); \
+  } while (0)
+#else
+#define ATT_STAMP(tile, index) do { } while (0)
+#endif
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -100,41 +128,48 @@ __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::l
 
 // One tile of the softmax for this thread's part (kCols columns starting at `first`) of its row: the scores are
 // read once (all loads in flight, one wait), then the visible maximum (columns low..high of the tile; all if
-// !MASKED), which the kParts threads of a row exchange through `shared_max` (one float per part, kRows apart)
+// !MASKED: the hidden ones are set to -inf first), which the kParts threads of a row exchange through `shared_max` (one float per part, kRows apart)
 // and the named barrier `team` of the stream's warps that hold the row's quarter of lanes; then the decision whether
 // the running maximum rises, and p = exp2(scale s - reference) packed to bf16.  Returns the sum of this thread's p.
 template <bool MASKED>
 __device__ __forceinline__ float softmax_tile(uint32_t scores, int first, int low, int high, float scale_log2,
                                               float& reference, float& factor, bool& grow,
-                                              uint32_t (&packed)[kCols / 2], float* shared_max, int part, int team) {
+                                              uint32_t (&packed)[kCols / 2], float* shared_max, int part, int team,
+                                              int stamp_tile) {
   float v[kCols];
 #pragma unroll
   for (int c0 = 0; c0 < kCols; c0 += 32) tmem_load_32_nowait(scores + first + c0, v + c0);
   tmem_load_wait();
 #pragma unroll
   for (int c = 0; c < kCols; ++c) asm volatile("" : "+f"(v[c])::"memory");   // no use of v moves above the wait
+  ATT_STAMP(stamp_tile, 7);
+  if (MASKED) {
+    // a hidden key's score becomes -inf by selection (whatever the cache held there, a NaN too), once; from here on
+    // the tile is handled like any other: -inf never wins the maximum and its exponential is exactly 0
+    const int lo = low - first, hi = high - first;
+#pragma unroll
+    for (int c = 0; c < kCols; ++c) v[c] = (c >= lo && c <= hi) ? v[c] : -INFINITY;
+  }
   float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};        // four chains instead of one
 #pragma unroll
-  for (int c = 0; c < kCols; ++c)
-    if (!MASKED || (first + c <= high && first + c >= low)) best[c & 3] = fmaxf(best[c & 3], v[c]);
+  for (int c = 0; c < kCols; ++c) best[c & 3] = fmaxf(best[c & 3], v[c]);
   float maximum = fmaxf(fmaxf(best[0], best[1]), fmaxf(best[2], best[3]));
   shared_max[part * kRows] = maximum;
   asm volatile("bar.sync %0, %1;" ::"r"(team), "n"(32 * kParts) : "memory");
 #pragma unroll
   for (int other = 0; other < kParts; ++other) maximum = fmaxf(maximum, shared_max[other * kRows]);
+  ATT_STAMP(stamp_tile, 8);
   maximum *= scale_log2;                                               // scale > 0
   grow = maximum > reference + kRescaleThreshold;
   factor = grow ? fast_exp2(reference - maximum) : 1.0f;               // 0 when nothing was seen before
   reference = grow ? maximum : reference;
+  // (a row that has seen no key yet, in this tile either, has reference -inf: -inf - -inf would not be a number)
+  const float shift = (MASKED && reference == -INFINITY) ? 0.0f : -reference;
   float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
   for (int c = 0; c < kCols; c += 2) {
-    float p0 = fast_exp2(fmaf(v[c], scale_log2, -reference));
-    float p1 = fast_exp2(fmaf(v[c + 1], scale_log2, -reference));
-    if (MASKED) {
-      p0 = (first + c <= high && first + c >= low) ? p0 : 0.0f;
-      p1 = (first + c + 1 <= high && first + c + 1 >= low) ? p1 : 0.0f;
-    }
+    const float p0 = fast_exp2(fmaf(v[c], scale_log2, shift));
+    const float p1 = fast_exp2(fmaf(v[c + 1], scale_log2, shift));
     sums[(c >> 1) & 3] += p0 + p1;
     const __nv_bfloat162 pair2 = __floats2bfloat162_rn(p0, p1);
     packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&pair2);
@@ -233,7 +268,6 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar0 = smem_u32(&barriers[0]);
   auto bar = [&](int index) { return bar0 + 8u * (uint32_t)index; };
-
   if (threadIdx.x == 0) {
     for (int i = 0; i < BARRIERS; ++i) {
       const bool many = i == P_READY || i == P_READY + 1;                  // every softmax thread of a stream arrives
@@ -258,125 +292,145 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   const uint32_t tmem_base = tmem_base_slot;
   const uint32_t tmem_o = tmem_base + 256u;
 
-  if (warp == 0 || warp == kThreads / 32 - 1) {
-    // ------------------------------------------------------------------ loaders: warp 0 keys, the last warp values
-    // (apart, so that the keys of a later tile do not queue behind values whose stage is still being read)
-    const int which = warp == 0 ? 0 : 1;
-    const int pages_per_tile = kKeys / page_size;
+  constexpr int kValueLoader = kFirstSoftmaxWarp + 8 * kStreams;   // the warp behind the softmax warps
+  if (warp == 0 || warp == kValueLoader) {
+    // ------------------------------------------------------------------ loaders: warp 0 keys (and Q), the last warp
+    // values (apart, so that the keys of a later tile do not queue behind values whose stage is still being read).
+    // These warps share their schedulers with four softmax warps each and every instruction of theirs takes long, so
+    // a tile costs them as few as can be: everything that does not change with the tile is worked out before the
+    // loop, the stage and its parity are counted, not divided, and the block table is read two tiles ahead.
+    const int which = warp == 0 ? 0 : 1;                      // keys or values
+    const int page_shift = 31 - __clz(page_size);             // pages are powers of two (they divide 128)
+    const int pages_per_tile = kKeys >> page_shift;
     const uint32_t box_bytes = (uint32_t)page_size * 128u;
     // lane l loads half (l & 1) of page slot (l >> 1): at most 16 pages of 8 keys, so one round of 32 lanes
     const int slot = lane >> 1, half = lane & 1;
+    const bool loads = lane < 2 * pages_per_tile;
+    const uint32_t lane_dst = smem_base + (which ? kOffV : kOffK) + (uint32_t)half * kHalf +
+                              (uint32_t)(slot * page_size) * 128u;
+    const CUtensorMap* map = which ? &v_map : &k_map;
+    const int stages = which ? 2 : kKeyStages;
+    const uint32_t full0 = bar(which ? V_FULL : K_FULL), free0 = bar(which ? V_FREE : K_FREE);
+    int stage = 0;                                            // of the CTA's tile g = g0 + t: g % stages,
+    uint32_t parity = 0;                                      // (g / stages) & 1
     int g0 = 0, n = 0;
     bool alive = true;
     for (int k = 0; more(k) && alive; ++k) {
       const Work w = work(k);
       if (!w.valid) continue;
-      if (which == 0) {
+      if (warp == 0) {
         // the queries, once the products with the last item's are over
-        int ok = 1;
-        if (lane == 0 && n > 0) ok = wait_barrier(bar(Q_FREE), (uint32_t)(n - 1) & 1u) ? 1 : 0;
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) { if (lane == 0) g_tc_attention_error = 1; break; }
+        if (n > 0 && !wait_barrier(bar(Q_FREE), (uint32_t)(n - 1) & 1u)) { g_tc_attention_error = 1; break; }
         if (lane == 0) {
           barrier_expect_bytes(bar(Q_FULL), kTile);
           tma_load_2d(smem_base + kOffQ, &q_map, bar(Q_FULL), w.head * kDim, w.q_row0);
           tma_load_2d(smem_base + kOffQ + kHalf, &q_map, bar(Q_FULL), w.head * kDim + 64, w.q_row0);
         }
       }
+      const int x = w.kv_head * kDim + half * 64;
+      const int lane_key = w.key_begin + slot * page_size;    // the first key of this lane's page in tile 0
+      const int* entry = w.table + (lane_key >> page_shift);  // its block table entry; pages_per_tile further per tile
+      const int tiles = w.tiles, key_end = w.key_end, first_visible = w.first_key - page_size;
       auto page_of = [&](int t) {
-        const int key = w.key_begin + t * kKeys + slot * page_size;
-        return (t < w.tiles && lane < 2 * pages_per_tile && key < w.key_end && key + page_size > w.first_key)
-                   ? w.table[key / page_size] : -1;
+        const int key = lane_key + t * kKeys;
+        return (loads && t < tiles && key < key_end && key > first_visible) ? entry[t * pages_per_tile] : -1;
       };
-      int page = page_of(0);
-      for (int t = 0; t < w.tiles; ++t) {
-        const int g = g0 + t;
-        const int stage = g & 1;
-        const uint32_t parity = (uint32_t)(g >> 1) & 1u;
-        const int next_page = page_of(t + 1);                 // on its way while this tile's stage is awaited
-        const uint32_t full = bar((which ? V_FULL : K_FULL) + stage), free_bar = bar((which ? V_FREE : K_FREE) + stage);
-        int ok = 1;
-        if (lane == 0) ok = wait_barrier(free_bar, parity ^ 1u) ? 1 : 0;
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) { if (lane == 0) g_tc_attention_error = 1; alive = false; break; }
-        const uint32_t dst = smem_base + (which ? kOffV : kOffK) + (uint32_t)stage * kTile;
+      int page_next = page_of(0), page_after = page_of(1);
+      for (int t = 0; t < tiles; ++t) {
+        const int page = page_next;
+        page_next = page_after;
+        page_after = page_of(t + 2);                          // on its way while these tiles' stages are awaited
+        const uint32_t full = full0 + 8u * (uint32_t)stage;
+        if (!wait_barrier(free0 + 8u * (uint32_t)stage, parity ^ 1u)) { g_tc_attention_error = 1; alive = false; break; }
+        if (lane == 0) ATT_STAMP(g0 + t, which);
         const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
         if (lane == 0) barrier_expect_bytes(full, (uint32_t)__popc(valid) * box_bytes);
         __syncwarp();
-        if (page >= 0)
-          tma_load_2d(dst + (uint32_t)half * kHalf + (uint32_t)(slot * page_size) * 128u, which ? &v_map : &k_map, full,
-                      w.kv_head * kDim + half * 64, page * page_size);
-        page = next_page;
+        if (page >= 0) tma_load_2d(lane_dst + (uint32_t)stage * kTile, map, full, x, page << page_shift);
+        if (lane == 0 && which == 0) ATT_STAMP(g0 + t, 15);
+        if (++stage == stages) { stage = 0; parity ^= 1u; }
       }
-      g0 += w.tiles;
+      g0 += tiles;
       ++n;
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = instruction_descriptor(kRows, kKeys, false);
-      constexpr uint32_t idesc_pv = instruction_descriptor(kRows, kDim, true);
-      bool alive = true;
-      int g0 = 0, n = 0;
-      for (int k = 0; more(k); ++k) {
-        const Work w = work(k);
-        if (!w.valid) continue;
-        if (alive && !wait_barrier(bar(Q_FULL), (uint32_t)n & 1u)) { g_tc_attention_error = 2; alive = false; }
-        auto issue_scores = [&](int t) {
-          const int g = g0 + t;
-          const int stage = g & 1;
-          const uint32_t parity = (uint32_t)(g >> 1) & 1u;
-          if (alive && !wait_barrier(bar(K_FULL + stage), parity)) { g_tc_attention_error = 2; alive = false; }
-          tensor_fence_after_sync();
-          const uint32_t a = smem_base + kOffQ, b = smem_base + kOffK + (uint32_t)stage * kTile;
+    // ------------------------------------------------------------------ issuer: the whole warp stays converged, the
+    // products are predicated on the elected lane (see tcgen05.cuh on issuing from a whole warp)
+    constexpr uint32_t idesc_qk = instruction_descriptor(kRows, kKeys, false);
+    constexpr uint32_t idesc_pv = instruction_descriptor(kRows, kDim, true);
+    const uint32_t elected = elect_one();
+    const uint32_t q_low = operand_low(smem_base + kOffQ), k_low = operand_low(smem_base + kOffK);
+    const uint32_t v_low = operand_low_mn_major(smem_base + kOffV, kHalf);
+    bool alive = true;
+    int g0 = 0, n = 0;
+    uint32_t key_stage = 0, key_parity = 0;                   // of the next tile of scores: g % kKeyStages, (g / kKeyStages) & 1
+    for (int k = 0; more(k); ++k) {
+      const Work w = work(k);
+      if (!w.valid) continue;
+      const int tiles = __shfl_sync(0xffffffffu, w.tiles, 0);             // (tells the compiler it is warp-uniform)
+      if (alive && !wait_barrier(bar(Q_FULL), (uint32_t)n & 1u)) { g_tc_attention_error = 2; alive = false; }
+      auto issue_scores = [&](int t) {
+        const int g = g0 + t;
+        const uint32_t stage = (uint32_t)g & 1u;
+        if (elected) ATT_STAMP(g, 11);
+        if (alive && !wait_barrier(bar(K_FULL + key_stage), key_parity)) { g_tc_attention_error = 2; alive = false; }
+        if (elected) ATT_STAMP(g, 12);
+        tensor_fence_after_sync();
+        const uint32_t b_low = k_low + key_stage * (uint32_t)(kTile >> 4), d = tmem_base + stage * 128u;
+        mma_bf16_ss_halves<false>(d, q_low, b_low, idesc_qk, elected);
 #pragma unroll
-          for (int kk = 0; kk < kDim / 16; ++kk) {
-            const uint32_t offset = (uint32_t)(kk >> 2) * kHalf + (uint32_t)(kk & 3) * 32u;
-            mma_bf16_ss(tmem_base + (uint32_t)stage * 128u, operand_descriptor(a + offset), operand_descriptor(b + offset),
-                        idesc_qk, kk > 0 ? 1u : 0u);
-          }
-          mma_commit(bar(S_FULL + stage));
-          mma_commit(bar(K_FREE + stage));
-          if (t == w.tiles - 1) mma_commit(bar(Q_FREE));       // the item's last product with its queries
-        };
-        // P(t) is written over S(t) in tensor memory, so S(t + 2), which takes the same accumulator, is issued
-        // behind the product with P(t): the tensor cores run products in the order of issue, and while they work
-        // on one stream's tile the other stream's softmax threads work on theirs
-        issue_scores(0);
-        if (w.tiles > 1) issue_scores(1);
-        for (int t = 0; t < w.tiles; ++t) {
-          const int g = g0 + t;
-          const int stage = g & 1;
-          const uint32_t parity = (uint32_t)(g >> 1) & 1u;
-          if (alive && !wait_barrier(bar(V_FULL + stage), parity)) { g_tc_attention_error = 2; alive = false; }
-          if (alive && !wait_barrier(bar(P_READY + stage), parity)) { g_tc_attention_error = 2; alive = false; }
-          // the output accumulators are the last item's until every softmax thread has read them out
-          if (t == 0 && n > 0 && alive && !wait_barrier(bar(O_FREE), (uint32_t)(n - 1) & 1u)) {
-            g_tc_attention_error = 2;
-            alive = false;
-          }
-          tensor_fence_after_sync();
-          const uint32_t p = tmem_base + (uint32_t)stage * 128u, b = smem_base + kOffV + (uint32_t)stage * kTile;
-#pragma unroll
-          for (int kk = 0; kk < kKeys / 16; ++kk) {
-            // P: 16 keys are 8 columns of packed pairs further on; V: 16 rows of keys further down
-            mma_bf16_ts(tmem_o + (uint32_t)(t % kStreams) * 128u, p + (uint32_t)kk * 8u,
-                        operand_descriptor_mn_major(b + (uint32_t)kk * 2048u, kHalf), idesc_pv,
-                        (t >= kStreams || kk > 0) ? 1u : 0u);
-          }
-          mma_commit(bar(V_FREE + stage));
-          if (t == w.tiles - 1) mma_commit(bar(ITEM_DONE));
-          if (t + 2 < w.tiles) issue_scores(t + 2);
+        for (int kk = 1; kk < kDim / 16; ++kk) {
+          constexpr uint32_t kHalfStep = (uint32_t)(kHalf >> 4);
+          const uint32_t offset = (uint32_t)(kk >> 2) * kHalfStep + (uint32_t)(kk & 3) * 2u;
+          mma_bf16_ss_halves<true>(d, q_low + offset, b_low + offset, idesc_qk, elected);
         }
-        g0 += w.tiles;
-        ++n;
+        mma_commit_elected(bar(S_FULL + stage), elected);
+        mma_commit_elected(bar(K_FREE + key_stage), elected);
+        if (elected) ATT_STAMP(g, 2);
+        if (t == tiles - 1) mma_commit_elected(bar(Q_FREE), elected);   // the item's last product with its queries
+        if (++key_stage == (uint32_t)kKeyStages) { key_stage = 0; key_parity ^= 1u; }   // (scores are issued in order)
+      };
+      // P(t) is written over S(t) in tensor memory, so S(t + 2), which takes the same accumulator, is issued
+      // behind the product with P(t): the tensor cores run products in the order of issue, and while they work
+      // on one stream's tile the other stream's softmax threads work on theirs
+      issue_scores(0);
+      if (tiles > 1) issue_scores(1);
+      for (int t = 0; t < tiles; ++t) {
+        const int g = g0 + t;
+        const uint32_t stage = (uint32_t)g & 1u;
+        const uint32_t parity = (uint32_t)(g >> 1) & 1u;
+        if (elected) ATT_STAMP(g, 13);
+        if (alive && !wait_barrier(bar(V_FULL + stage), parity)) { g_tc_attention_error = 2; alive = false; }
+        if (elected) ATT_STAMP(g, 3);
+        if (alive && !wait_barrier(bar(P_READY + stage), parity)) { g_tc_attention_error = 2; alive = false; }
+        if (elected) ATT_STAMP(g, 4);
+        // the output accumulators are the last item's until every softmax thread has read them out
+        if (t == 0 && n > 0 && alive && !wait_barrier(bar(O_FREE), (uint32_t)(n - 1) & 1u)) {
+          g_tc_attention_error = 2;
+          alive = false;
+        }
+        tensor_fence_after_sync();
+        const uint32_t p = tmem_base + stage * 128u;
+        const uint32_t b_low = v_low + stage * (uint32_t)(kTile >> 4);
+        const uint32_t o = tmem_o + (uint32_t)(t % kStreams) * 128u;
+        // P: 16 keys are 8 columns of packed pairs further on; V: 16 rows of keys (2 KB) further down
+        mma_bf16_ts_halves(o, p, b_low, idesc_pv, t >= kStreams ? 1u : 0u, elected);
+#pragma unroll
+        for (int kk = 1; kk < kKeys / 16; ++kk)
+          mma_bf16_ts_halves(o, p + (uint32_t)kk * 8u, b_low + (uint32_t)kk * (2048u >> 4), idesc_pv, 1u, elected);
+        mma_commit_elected(bar(V_FREE + stage), elected);
+        if (elected) ATT_STAMP(g, 14);
+        if (t == tiles - 1) mma_commit_elected(bar(ITEM_DONE), elected);
+        if (t + 2 < tiles) issue_scores(t + 2);
       }
+      g0 += tiles;
+      ++n;
     }
   } else {
     // ------------------------------------------------------------------ softmax: kStreams streams of eight warps
-    const int stream = (warp - 2) >> 3;                       // takes the tiles t = stream, stream + kStreams, ...
+    const int stream = (warp - kFirstSoftmaxWarp) >> 3;       // takes the tiles t = stream, stream + kStreams, ...
     const int quarter = warp & 3;                             // the accumulator lanes this warp may touch
-    const int part = ((warp - 2) >> 2) & 1;                   // which kCols columns of the row it takes
+    const int part = ((warp - kFirstSoftmaxWarp) >> 2) & 1;   // which kCols columns of the row it takes
     const int r = quarter * 32 + lane;
     const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
     const int first = part * kCols;
@@ -388,6 +442,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     for (int k = 0; more(k); ++k) {
       const Work w = work(k);
       if (!w.valid) continue;
+      ATT_STAMP(((lane == 0 && quarter == 0 && part == 0 && stream == 0) ? 200 + n : -1), 5);
       const bool valid_row = r < w.tile_rows;
       const int position = w.first_position + min(r, w.tile_rows - 1);
       float reference = -INFINITY, denominator = 0.0f;        // running maximum (scaled, log2 domain), partial sum
@@ -396,7 +451,10 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         const int stage = g & 1;
         const uint32_t parity = (uint32_t)(g >> 1) & 1u;
         const int key0 = w.key_begin + t * kKeys;
+        const int stamp_tile = (lane == 0 && quarter == 0 && part == 0) ? g : -1;
+        ATT_STAMP(stamp_tile, 5);
         if (alive && !wait_barrier(bar(S_FULL + stage), parity)) { g_tc_attention_error = 3; alive = false; }
+        ATT_STAMP(stamp_tile, 6);
         tensor_fence_after_sync();
         const uint32_t scores = tmem_base + (uint32_t)stage * 128u + lane_bits;
         // keys of this tile that row r may see: columns [low, high]; most tiles are visible to every row
@@ -409,9 +467,10 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         float* shared_max = &exchange[stream][(t / kStreams) & 1][0][r];
         const int team = 1 + stream * 4 + quarter;
         const float sum = every ? softmax_tile<false>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
-                                                      shared_max, part, team)
+                                                      shared_max, part, team, stamp_tile)
                                 : softmax_tile<true>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
-                                                     shared_max, part, team);
+                                                     shared_max, part, team, stamp_tile);
+        ATT_STAMP(stamp_tile, 9);
         denominator = denominator * factor + sum;
         // This stream's previous product (tile t - kStreams) is over: S(t) was issued behind it, and the scores'
         // barrier completes only when everything issued before it has.  So its O may be rescaled now.
@@ -432,12 +491,16 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         tmem_store_wait();
         tensor_fence_before_sync();
         barrier_arrive(bar(P_READY + stage));
+        ATT_STAMP(stamp_tile, 10);
       }
       // every softmax thread learns every stream's maximum and denominator (the sum of its two threads' parts)
+      [[maybe_unused]] const int stamp_item = (lane == 0 && quarter == 0 && part == 0 && stream == 0) ? 200 + n : -1;
+      ATT_STAMP(stamp_item, 0);
       const int slot = n & 1;
       denominators[slot][stream][part][r] = denominator;
       if (part == 0) references[slot][stream][r] = reference;
       asm volatile("bar.sync %0, %1;" ::"r"(9), "n"(kStreamThreads * kStreams) : "memory");
+      ATT_STAMP(stamp_item, 1);
       float top = -INFINITY;
 #pragma unroll
       for (int other = 0; other < kStreams; ++other) top = fmaxf(top, references[slot][other][r]);
@@ -454,6 +517,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         alive = false;
       }
       tensor_fence_after_sync();
+      ATT_STAMP(stamp_item, 2);
       {
         // this thread's columns of the output: the row's 128 are shared out over all its softmax threads
         constexpr int kOut = kDim / (kParts * kStreams);
@@ -479,6 +543,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             // the accumulators are read out: the next item's products may overwrite them
             tensor_fence_before_sync();
             barrier_arrive(bar(O_FREE));
+            ATT_STAMP(stamp_item, 3);
           }
           if (valid_row && alive) {
 #pragma unroll
@@ -492,6 +557,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           }
         }
       }
+      ATT_STAMP(stamp_item, 4);
       g0 += w.tiles;
       ++n;
     }
@@ -504,7 +570,19 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   }
 }
 
+
 }  // namespace
+
+#ifdef MIR_TRACE
+// The first CTA's tile stamps of the last launch (cycles), [kTraceTiles][16]; returns the number of rows.
+MIR_EXPORT int mir_trace_read_prompt_tiles(long long* host, int capacity) {
+  const int rows = capacity < kTraceTiles ? capacity : kTraceTiles;
+  if (cudaDeviceSynchronize() != cudaSuccess ||
+      cudaMemcpyFromSymbol(host, g_prompt_tiles, sizeof(long long) * 16 * rows) != cudaSuccess)
+    return -1;
+  return rows;
+}
+#endif
 
 // 0 if no bounded wait of the tcgen05 attention ever ran out; else which role gave up last (1 loader, 2 issuer,
 // 3 softmax).  Synchronises the device.

@@ -132,10 +132,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ issuer: the whole warp stays converged, the
+    // products are predicated on the elected lane (see tcgen05.cuh on issuing from a whole warp)
+    {
       const uint32_t idesc = instruction_descriptor(kTileM, width);
-      uint32_t count = 0, local = 0;                         // stages consumed; tiles of this CTA
+      const uint32_t elected = elect_one();
+      const uint32_t a_low0 = operand_low(smem_u32(smem)), b_low0 = operand_low(smem_u32(smem) + kTileM * 128);
+      uint32_t stage = 0, parity = 0, local = 0;             // of the stages consumed so far; tiles of this CTA
       bool alive = true;
       for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
         const uint32_t buffer = local & 1u, use = (local >> 1) & 1u;
@@ -143,21 +146,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
         if (alive && !wait_barrier(acc_free0 + 8 * buffer, use ^ 1u)) { g_tc_gemm_error = 2; alive = false; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t accumulator = tmem_base + buffer * 256u;
-        for (int step = 0; step < steps; ++step, ++count) {
-          const uint32_t stage = count % kStages, parity = (count / kStages) & 1u;
+        for (int step = 0; step < steps; ++step) {
           if (alive && !wait_barrier(full0 + 8 * stage, parity)) { g_tc_gemm_error = 2; alive = false; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_base = smem_u32(smem + (size_t)stage * kStageStride);
-          const uint32_t b_base = a_base + kTileM * 128;
+          const uint32_t a_low = a_low0 + stage * (uint32_t)(kStageStride >> 4);
+          const uint32_t b_low = b_low0 + stage * (uint32_t)(kStageStride >> 4);
+          // 16 k = 32 bytes further along the swizzled rows: the start address moves by 32 bytes
+          mma_bf16_ss_halves(accumulator, a_low, b_low, idesc, step > 0 ? 1u : 0u, elected);
 #pragma unroll
-          for (int kk = 0; kk < kStepK / 16; ++kk) {
-            // 16 k = 32 bytes further along the swizzled rows: the start address moves by 32 bytes
-            mma_bf16_ss(accumulator, operand_descriptor(a_base + kk * 32), operand_descriptor(b_base + kk * 32), idesc,
-                        (step > 0 || kk > 0) ? 1u : 0u);
-          }
-          mma_commit(empty0 + 8 * stage);                    // the stage is free once these have read it
+          for (int kk = 1; kk < kStepK / 16; ++kk)
+            mma_bf16_ss_halves<true>(accumulator, a_low + 2u * kk, b_low + 2u * kk, idesc, elected);
+          mma_commit_elected(empty0 + 8 * stage, elected);   // the stage is free once these have read it
+          if (++stage == (uint32_t)kStages) { stage = 0; parity ^= 1u; }
         }
-        mma_commit(acc_full0 + 8 * buffer);                  // this tile's accumulator is complete
+        mma_commit_elected(acc_full0 + 8 * buffer, elected); // this tile's accumulator is complete
       }
     }
   } else {

@@ -98,6 +98,78 @@ __device__ __forceinline__ void mma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
       : "memory");
 }
 
+// Issuing from a whole warp.  A thread that issues products shares its scheduler with the CTA's other warps, and
+// every instruction it needs between two products is one it has to win an issue slot for; when the others are busy
+// (a softmax, an epilogue) a lone thread in a divergent branch, whose descriptors the compiler has to build in
+// ordinary registers and move to uniform ones, fed the tensor cores a product of 64 cycles only every 80 to 170.
+// So the issuing warp stays converged: all its lanes run the loop, the products are predicated on `elected`
+// (elect_one(), taken once), and the descriptors are passed in two 32-bit halves: the upper half is the same for
+// every operand with the 128-byte swizzle (stride byte offset 1024, version 1), the lower half holds the address in
+// 16-byte units (and the leading byte offset of an MN-major operand), so the operand 16 bytes * n further on is
+// `low + n`.  Measured beside 16 warps that saturate the schedulers: 71 cycles a product against 177.
+constexpr uint32_t kOperandHigh = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t operand_low(uint32_t smem_address) {
+  return ((smem_address >> 4) & 0x3FFFu) | (1u << 16);
+}
+__device__ __forceinline__ uint32_t operand_low_mn_major(uint32_t smem_address, uint32_t block_bytes) {
+  return ((smem_address >> 4) & 0x3FFFu) | (((block_bytes >> 4) & 0x3FFFu) << 16);
+}
+// 1 in one lane of the (converged) warp, 0 in the others.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t elected;
+  asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\tselp.b32 %0, 1, 0, q;\n\t}" : "=r"(elected));
+  return elected;
+}
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_bf16_ss_halves(uint32_t tmem_d, uint32_t a_low, uint32_t b_low, uint32_t idesc,
+                                                   uint32_t elected) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 q, %7, 0;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, {%6, %6, %6, %6}, p;\n\t}"
+      :
+      : "r"(tmem_d), "r"(a_low), "r"(b_low), "r"(idesc), "n"(kAccumulate ? 1 : 0), "r"(kOperandHigh), "r"(0u),
+        "r"(elected)
+      : "memory");
+}
+// The same with the accumulate flag in a register.
+__device__ __forceinline__ void mma_bf16_ss_halves(uint32_t tmem_d, uint32_t a_low, uint32_t b_low, uint32_t idesc,
+                                                   uint32_t accumulate, uint32_t elected) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 q, %7, 0;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, {%6, %6, %6, %6}, p;\n\t}"
+      :
+      : "r"(tmem_d), "r"(a_low), "r"(b_low), "r"(idesc), "r"(accumulate), "r"(kOperandHigh), "r"(0u), "r"(elected)
+      : "memory");
+}
+__device__ __forceinline__ void mma_bf16_ts_halves(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_low, uint32_t idesc,
+                                                   uint32_t accumulate, uint32_t elected) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 q, %7, 0;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, {%6, %6, %6, %6}, p;\n\t}"
+      :
+      : "r"(tmem_d), "r"(tmem_a), "r"(b_low), "r"(idesc), "r"(accumulate), "r"(kOperandHigh), "r"(0u), "r"(elected)
+      : "memory");
+}
+// mma_commit by the elected lane of a converged warp.
+__device__ __forceinline__ void mma_commit_elected(uint32_t barrier, uint32_t elected) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(barrier), "r"(elected)
+      : "memory");
+}
+
 // Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint32_t barrier) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(barrier) : "memory");

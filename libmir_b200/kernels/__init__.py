@@ -122,6 +122,22 @@ def read_trace() -> dict:
     return records
 
 
+def read_prompt_attention_trace():
+    """Cycle stamps of the first CTA of the last tcgen05 prompt-attention launch (traced kernels only): an int64 array
+    [256, 16]; row g is the CTA's g-th key tile, rows 200 + n the end of its n-th item; csrc/attention_tc.cu says
+    which column is what.  0 = not reached.  Synchronises the device."""
+    import numpy as np
+    _require(_TRACED, "read_prompt_attention_trace: call use_traced_kernels() first")
+    lib = library("bf16")
+    rows = 256
+    host = (ctypes.c_longlong * (16 * rows))()
+    lib.mir_trace_read_prompt_tiles.argtypes = [c_void_p, c_int]
+    lib.mir_trace_read_prompt_tiles.restype = c_int
+    count = lib.mir_trace_read_prompt_tiles(host, rows)
+    _require(count == rows, "read_prompt_attention_trace: reading the records failed")
+    return np.array(host, dtype=np.int64).reshape(rows, 16)
+
+
 def library(name: str) -> ctypes.CDLL:
     """The loaded native library `name`, compiled first if its sources changed or it was never built."""
     lib = _LIBS.get(name)

@@ -57,8 +57,29 @@ SCRIPT = textwrap.dedent("""
             expected = weights @ values[:, h // (heads // kv_heads)]
             got = attended[r].float().view(heads, dim)[h]
             attention_error = max(attention_error, float((got - expected).abs().max()))
+    # prompt attention over 700 tokens of one request (tcgen05 kernel): the first CTA's tiles
+    n = 700
+    k_pool = torch.randn(704, kv_heads, dim, device="cuda").bfloat16()
+    v_pool = torch.randn(704, kv_heads, dim, device="cuda").bfloat16()
+    prompt_table = torch.arange(44, dtype=torch.int32, device="cuda").view(1, 44)
+    packed = torch.randn(n, (heads + 2 * kv_heads) * dim, device="cuda").bfloat16()
+    prompt_out = torch.empty(n, heads * dim, device="cuda", dtype=torch.bfloat16)
+    kernels.prefill_attention(packed, prompt_out, k_pool, v_pool, prompt_table,
+                              torch.tensor([0, n], dtype=torch.int32, device="cuda"),
+                              torch.tensor([n], dtype=torch.int32, device="cuda"), page, heads, kv_heads, dim, scale, None,
+                              tensor_cores=True)
+    keys, values = k_pool[:n].float(), v_pool[:n].float()
+    prompt_error = 0.0
+    for row in (0, 127, 128, 699):
+        for h in range(heads):
+            weights = torch.softmax(keys[:row + 1, h // (heads // kv_heads)] @ packed[row, h * dim:(h + 1) * dim].float() * scale, dim=0)
+            expected = weights @ values[:row + 1, h // (heads // kv_heads)]
+            prompt_error = max(prompt_error, float((prompt_out[row].float().view(heads, dim)[h] - expected).abs().max()))
+    tiles = kernels.read_prompt_attention_trace()
     records = {name: table_.tolist() for name, table_ in kernels.read_trace().items()}
     print(json.dumps({"product_error": product_error, "attention_error": attention_error, "records": records,
+                      "prompt_error": prompt_error, "prompt_tiles": tiles[:8].tolist(), "prompt_items": tiles[200:202].tolist(),
+                      "prompt_flag": kernels.prefill_attention_error(),
                       "library": kernels.library("bf16")._name, "flags": [kernels.stream_linear_error(),
                                                                            kernels.decode_attention_error()]}))
 """)
@@ -71,6 +92,15 @@ def test_traced_kernels_compute_the_same_and_leave_time_lines():
     assert "bf16_trace" in report["library"]
     assert report["flags"] == [0, 0]
     assert report["product_error"] < 0.05 and report["attention_error"] < 0.03
+    assert report["prompt_error"] < 0.03 and report["prompt_flag"] == 0
+    first = report["prompt_tiles"][0]                           # the first CTA's first tile: its item has six
+    # keys asked for <= the issuer has them <= scores issued; the softmax has the scores <= has read them <= knows the
+    # maximum <= has the exponentials <= has arrived; then the issuer has P and issues the product with V
+    for line in ([first[i] for i in (0, 12, 2)], [first[i] for i in (6, 7, 8, 9, 10)], [first[i] for i in (4, 14)]):
+        assert all(stamp > 0 for stamp in line) and all(a <= b for a, b in zip(line, line[1:])), first
+    assert first[10] <= first[4] + 2000 and first[2] <= first[6]
+    item = report["prompt_items"][0]                            # the end of its first item, in order
+    assert all(a <= b for a, b in zip(item[:5], item[1:5])) and item[0] > 0, item
     records = report["records"]
     assert len(records["stream"]) == 2 and len(records["merge"]) >= 1 and len(records["decode"]) >= 1
     assert records["rope"] == []                                # (no such kernel ran)
