@@ -67,7 +67,8 @@ class GenerationOutput:
 class PrefillOutput:
     next_token: Optional[int] = None
     logits: Optional[np.ndarray] = None      # float32 [vocab]
-    cached_tokens: int = 0
+    cached_tokens: int = 0                   # tokens of the session in the cache after the call
+    reused_tokens: int = 0                   # of these, found in the prefix cache instead of computed
 
 
 DecodeOutput = PrefillOutput
@@ -293,15 +294,21 @@ class Session:
         if not self._open:
             raise SchedulerError("the session is closed")
         tokens = [int(t) for t in tokens]
-        entry = StepEntry(self.request_id, tokens, [len(tokens) - 1])
+        reused = 0
+        cache = self.model.cache
+        if cache.prefix is not None and cache.live[self.request_id].length == 0 and len(tokens) > 1:
+            # a prompt into an empty session: take over the pages that hold its first tokens already
+            self.model.release(self.request_id)
+            reused = self.model.admit(self.request_id, tokens)
+        entry = StepEntry(self.request_id, tokens[reused:], [len(tokens) - reused - 1])
         if want == SamplingLogits.FULL:
             result = self.model.step([entry])
-            cached = self.model.cache.live[self.request_id].length
-            return PrefillOutput(logits=result.logits[0].float().cpu().numpy(), cached_tokens=cached)
+            cached = cache.live[self.request_id].length
+            return PrefillOutput(logits=result.logits[0].float().cpu().numpy(), cached_tokens=cached, reused_tokens=reused)
         self.sampler.observe(tokens)
         result = self.model.step([entry], [self.sampler])
-        cached = self.model.cache.live[self.request_id].length
-        return PrefillOutput(next_token=int(result.tokens.cpu()[0]), cached_tokens=cached)
+        cached = cache.live[self.request_id].length
+        return PrefillOutput(next_token=int(result.tokens.cpu()[0]), cached_tokens=cached, reused_tokens=reused)
 
     def prefill(self, prompt_ids: Sequence[int], sampling: str = SamplingLogits.TOKEN,
                 settings: Optional[GenerationSettings] = None, seed: Optional[int] = None) -> PrefillOutput:

@@ -129,3 +129,27 @@ def test_generation_gives_the_same_tokens_with_and_without_the_prefix_cache(tmp_
     assert stats["groups"][0]["free"] == 64 and stats["cached_prefix_pages"] > 0 and stats["live_requests"] == 0
     model.cache.check()
     model.unload()
+
+
+def test_a_session_takes_over_cached_pages_at_its_first_prefill(tmp_path):
+    from libmir_b200 import SamplingLogits
+    folder = make_folder(tmp_path, TINY_A, seed=4, dtype="float32", sharpen=6.0)
+    ids = random_ids(np.random.default_rng(8), TINY_A["vocab_size"], 45)
+    reference = plain_logits(folder, ids)
+    model = load(folder, "float32", pages=16, page_size=8)
+    with model.session() as session:
+        out = session.prefill(ids[:40], SamplingLogits.FULL)
+        assert out.reused_tokens == 0 and out.cached_tokens == 40
+        check(out.logits, reference[39], TOL["float32"], "first session")
+    with model.session() as session:                         # five full pages of the same tokens are there
+        out = session.prefill(ids[:44], SamplingLogits.FULL)
+        assert out.reused_tokens == 40 and out.cached_tokens == 44
+        check(out.logits, reference[43], TOL["float32"], "second session, 40 tokens taken over")
+        out = session.decode(ids[44], SamplingLogits.FULL)
+        assert out.reused_tokens == 0 and out.cached_tokens == 45
+        check(out.logits, reference[44], TOL["float32"], "second session decoding")
+    assert model.clear_prefix_cache() == 5 and model.cache_stats()["cached_prefix_pages"] == 0
+    with model.session() as session:
+        assert session.prefill(ids[:44], SamplingLogits.FULL).reused_tokens == 0
+    model.cache.check()
+    model.unload()
