@@ -115,6 +115,7 @@ class DecodeGraph:
         self.launches_per_replay = 0
         self.replays = 0
         self._copied = None
+        self._fast_tokens, self._fast_positions = self._host_part(1), self._host_part(2)
         self._live_rows = -1                       # rows the upload block was last filled for
         self._greedy_options = False               # whether its sampling records are the greedy defaults
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -221,6 +222,16 @@ class DecodeGraph:
         self.meta[:self._upload].copy_(self.staging, non_blocking=True)
         if self._copied is None:
             self._copied = torch.cuda.Event()
+        self._copied.record()
+
+    def load_again(self, tokens: Sequence[int], sequences) -> None:
+        """The upload for the same greedy rows as the last `load`, none of which got a page since: only the tokens
+        and the positions differ."""
+        n = len(tokens)
+        self._copied.synchronize()                 # the previous copy has read the pinned block
+        self._fast_tokens[:n] = tokens
+        self._fast_positions[:n] = [seq.length for seq in sequences]
+        self.meta[:self._upload].copy_(self.staging, non_blocking=True)
         self._copied.record()
 
     def replay(self) -> None:

@@ -89,6 +89,11 @@ class StepRunner:
         self._flip = 0
         self.steps = 0
         self.tokens_run = 0
+        # After a captured greedy decode step: (request ids, their sequences, the graph, the result's row keys), so that
+        # the next step of the same requests, if none of them needs a page, skips everything that cannot have changed
+        # (`_step_again`).  None after any other step.
+        self._again = None
+        self.steps_again = 0
 
     # -- metadata ------------------------------------------------------------------
     def _stage(self, arrays: List[np.ndarray]) -> List[torch.Tensor]:
@@ -259,10 +264,18 @@ class StepRunner:
         self.storage.zero_slots(self.manager.take_fresh_slots())
         if self._graph_eligible(entries, samplers):
             graph = self._graphs.get(len(entries), sequences, 1, any(s.ranked for s in samplers))
-            graph.load([e.tokens[0] for e in entries], sequences, self._options(samplers))
+            options = self._options(samplers)
+            vocab = self.model.spec.vocab_size
+            for entry in entries:
+                if not 0 <= entry.tokens[0] < vocab:
+                    raise SchedulerError(f"request {entry.request_id!r}: token id outside [0, {vocab})")
+            graph.load([e.tokens[0] for e in entries], sequences, options)
             graph.replay()
             rows = len(entries)
             keys = [(e.request_id, 0) for e in entries]
+            manager = self.manager
+            if options is None and manager.prefix is None and len(manager.groups) == 1 and manager.groups[0].window is None:
+                self._again = ([e.request_id for e in entries], list(sequences), graph, keys)
             return StepResult(graph.logits[:rows], keys, rows, graph.sampled[:rows])
         self.arena.reset()
         ctx, want_rows, want_keys = self.build_context(entries, sequences)
@@ -281,9 +294,44 @@ class StepRunner:
         for entry, seq in zip(entries, sequences):
             self.manager.commit(seq, seq.length + len(entry.tokens), entry.tokens)
 
+    def _step_again(self, entries: Sequence[StepEntry], samplers) -> Optional[StepResult]:
+        """The step after a captured greedy decode step of the same requests in the same order, each of which has room
+        in its last page: the block tables, slots and sampling records on the device are as they must be, so only
+        tokens and positions are uploaded, the same graph is replayed and the lengths move on by one.  None if any of
+        this does not hold; the ordinary path then runs (and says what is wrong, if something is)."""
+        ids, sequences, graph, keys = self._again
+        if samplers is None or len(entries) != len(ids) or len(samplers) != len(ids):
+            return None
+        live, limit, vocab = self.manager.live, self.model.spec.max_positions, self.model.spec.vocab_size
+        capacity = self.manager.page_size
+        tokens = []
+        for entry, rid, seq, sampler in zip(entries, ids, sequences, samplers):
+            if entry.request_id != rid or len(entry.tokens) != 1 or len(entry.want) != 1 or entry.want[0] != 0 \
+                    or live.get(rid) is not seq or seq.length >= len(seq.tables[0]) * capacity or seq.length >= limit \
+                    or not sampler.greedy or sampler.repetition_penalty > 1.0 or not 0 <= entry.tokens[0] < vocab:
+                return None
+            tokens.append(entry.tokens[0])
+        if self.manager.fresh_slots:
+            return None
+        graph.load_again(tokens, sequences)
+        graph.replay()
+        for seq in sequences:                                  # (no window to release pages, no prefix to remember)
+            seq.length += 1
+            seq.reserved = max(seq.reserved, seq.length)
+        rows = len(ids)
+        self.steps += 1
+        self.steps_again += 1
+        self.tokens_run += rows
+        return StepResult(graph.logits[:rows], keys, rows, graph.sampled[:rows])
+
     def step(self, entries: Sequence[StepEntry], samplers=None) -> StepResult:
         """Run one batch: reserve pages, run the tokens, commit the new lengths.  With `samplers` (one
         per wanted row, in order) the result also holds the sampled tokens."""
+        if self._again is not None and not self.profile_decode:
+            result = self._step_again(entries, samplers)
+            if result is not None:
+                return result
+        self._again = None
         profiled = self.profile_decode and bool(entries) and all(len(e.tokens) == 1 for e in entries)
         if profiled:
             started_at = time.perf_counter()
@@ -317,6 +365,7 @@ class StepRunner:
                                  "without a repetition penalty")
         if any(not s.greedy for s in samplers):
             raise SchedulerError("decode_many draws nothing on the host: greedy samplers only")
+        self._again = None
         ahead = [StepEntry(e.request_id, list(e.tokens) + [0] * (steps - 1), []) for e in entries]
         ahead, sequences = self.reserve(ahead)
         self.storage.zero_slots(self.manager.take_fresh_slots())

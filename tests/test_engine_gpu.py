@@ -398,3 +398,71 @@ def test_native_executor_and_python_parts_launch_the_same_work(tmp_path, name, d
     assert torch.equal(results[0], results[1])
     reference = plain_logits(folder, first)
     check(results[0][-1].numpy(), reference[329], TOL[dtype], "against the plain implementation")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repeated_greedy_decode_steps_take_the_short_path_and_stay_right(tmp_path, dtype):
+    """Captured greedy decode steps of the same requests skip what cannot have changed (StepRunner._step_again) until
+    one of them needs a page, another request joins, one leaves, or a sampler draws: the logits of every step, short
+    path or not, are the plain implementation's."""
+    from libmir_b200 import StepEntry
+    from libmir_b200.sampling import RequestSampler
+    config = TINY_A
+    folder = make_folder(tmp_path, config, seed=6, dtype=dtype, sharpen=6.0)
+    rng = np.random.default_rng(21)
+    model = load(folder, dtype, pages=32, page_size=4)
+    runner = model.runner
+    sequences = {name: random_ids(rng, config["vocab_size"], n) for name, n in (("a", 5), ("b", 11))}
+    samplers = {name: RequestSampler() for name in ("a", "b", "c")}
+    for name, ids in sequences.items():
+        model.admit(name)
+        model.step([StepEntry(name, ids, [])])
+
+    last = {"names": None}
+
+    def decode(names):
+        """One greedy decode step; the short path must be taken exactly when the step before was a captured greedy
+        decode step of the same requests in the same order and every one of them has room in its last page."""
+        cached = {name: len(sequences[name]) for name in names}
+        expect_short = last["names"] == names and all(cached[name] % 4 != 0 for name in names)
+        before = runner.steps_again
+        for name in names:
+            sequences[name].append(int(rng.integers(config["vocab_size"])))
+        result = model.step([StepEntry(name, [sequences[name][-1]], [0]) for name in names], [samplers[n] for n in names])
+        assert (runner.steps_again - before == 1) == expect_short, (names, cached, last)
+        last["names"] = list(names)
+        got = result.logits.float().cpu().numpy()
+        for row, name in enumerate(names):
+            check(got[row], plain_logits(folder, sequences[name])[-1], TOL[dtype], f"{name} at {len(sequences[name]) - 1}")
+        assert result.tokens.cpu().tolist() == [int(np.argmax(got[row])) for row in range(len(names))]
+        return expect_short
+
+    taken = [decode(["a", "b"]) for _ in range(7)]             # pages of 4: a and b reach page edges at different steps
+    assert taken.count(True) >= 3 and taken.count(False) >= 3, taken
+    taken = [decode(["b", "a"]) for _ in range(4)]             # another order is another batch
+    assert taken[0] is False and True in taken
+    sequences["c"] = random_ids(rng, config["vocab_size"], 6)
+    model.admit("c")
+    model.step([StepEntry("c", sequences["c"], [])])          # a prompt in between
+    last["names"] = None
+    assert decode(["b", "a"]) is False
+    assert decode(["b", "a", "c"]) is False
+    taken = [decode(["b", "a", "c"]) for _ in range(5)]
+    assert True in taken
+    model.release("a")
+    model.admit("a")                                           # the same name, another request
+    sequences["a"] = random_ids(rng, config["vocab_size"], 3)
+    model.step([StepEntry("a", sequences["a"], [])])
+    last["names"] = None
+    assert decode(["b", "a", "c"]) is False
+    decode(["b", "a", "c"])
+    samplers["c"] = RequestSampler(temperature=0.7, seed=3)    # a sampler that draws ends it, too
+    before = runner.steps_again
+    for name in ("b", "a", "c"):
+        sequences[name].append(int(rng.integers(config["vocab_size"])))
+    model.step([StepEntry(n, [sequences[n][-1]], [0]) for n in ("b", "a", "c")], [samplers[n] for n in ("b", "a", "c")])
+    assert runner.steps_again == before
+    with pytest.raises(Exception, match="token id outside"):
+        model.step([StepEntry("b", [config["vocab_size"]], [0])], [samplers["b"]])
+    model.cache.check()
+    model.unload()
