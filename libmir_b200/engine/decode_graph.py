@@ -224,13 +224,15 @@ class DecodeGraph:
             self._copied = torch.cuda.Event()
         self._copied.record()
 
-    def load_again(self, tokens: Sequence[int], sequences) -> None:
-        """The upload for the same greedy rows as the last `load`, none of which got a page since: only the tokens
-        and the positions differ."""
+    def load_again(self, tokens: Sequence[int], sequences, draws: Optional[Sequence[float]] = None) -> None:
+        """The upload for the same rows with the same sampling settings as the last `load`, none of which got a page
+        since: only the tokens, the positions and (for samplers that draw) the draws differ."""
         n = len(tokens)
         self._copied.synchronize()                 # the previous copy has read the pinned block
         self._fast_tokens[:n] = tokens
         self._fast_positions[:n] = [seq.length for seq in sequences]
+        if draws is not None:
+            self._host_part(0).view(kernels.SAMPLE_OPTIONS)["draw"][:n] = draws
         self.meta[:self._upload].copy_(self.staging, non_blocking=True)
         self._copied.record()
 

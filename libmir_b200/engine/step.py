@@ -89,9 +89,9 @@ class StepRunner:
         self._flip = 0
         self.steps = 0
         self.tokens_run = 0
-        # After a captured greedy decode step: (request ids, their sequences, the graph, the result's row keys), so that
-        # the next step of the same requests, if none of them needs a page, skips everything that cannot have changed
-        # (`_step_again`).  None after any other step.
+        # After a captured decode step: (request ids, their sequences, the graph, the result's row keys, the samplers'
+        # settings or None if all were greedy), so that the next step of the same requests, if none of them needs a
+        # page, skips everything that cannot have changed (`_step_again`).  None after any other step.
         self._again = None
         self.steps_again = 0
 
@@ -274,8 +274,10 @@ class StepRunner:
             rows = len(entries)
             keys = [(e.request_id, 0) for e in entries]
             manager = self.manager
-            if options is None and manager.prefix is None and len(manager.groups) == 1 and manager.groups[0].window is None:
-                self._again = ([e.request_id for e in entries], list(sequences), graph, keys)
+            if manager.prefix is None and len(manager.groups) == 1 and manager.groups[0].window is None:
+                settings = None if options is None else [(s.temperature, s.top_p, s.top_k, s.repetition_penalty)
+                                                         for s in samplers]
+                self._again = ([e.request_id for e in entries], list(sequences), graph, keys, settings)
             return StepResult(graph.logits[:rows], keys, rows, graph.sampled[:rows])
         self.arena.reset()
         ctx, want_rows, want_keys = self.build_context(entries, sequences)
@@ -295,25 +297,35 @@ class StepRunner:
             self.manager.commit(seq, seq.length + len(entry.tokens), entry.tokens)
 
     def _step_again(self, entries: Sequence[StepEntry], samplers) -> Optional[StepResult]:
-        """The step after a captured greedy decode step of the same requests in the same order, each of which has room
-        in its last page: the block tables, slots and sampling records on the device are as they must be, so only
-        tokens and positions are uploaded, the same graph is replayed and the lengths move on by one.  None if any of
+        """The step after a captured decode step of the same requests in the same order with the same sampling settings,
+        each of which has room in its last page: the block tables, slots and sampling records on the device are as
+        they must be, so only tokens, positions and draws are uploaded, the same graph is replayed and the lengths
+        move on by one.  None if any of
         this does not hold; the ordinary path then runs (and says what is wrong, if something is)."""
-        ids, sequences, graph, keys = self._again
+        ids, sequences, graph, keys, settings = self._again
         if samplers is None or len(entries) != len(ids) or len(samplers) != len(ids):
             return None
         live, limit, vocab = self.manager.live, self.model.spec.max_positions, self.model.spec.vocab_size
         capacity = self.manager.page_size
         tokens = []
-        for entry, rid, seq, sampler in zip(entries, ids, sequences, samplers):
+        for entry, rid, seq in zip(entries, ids, sequences):
             if entry.request_id != rid or len(entry.tokens) != 1 or len(entry.want) != 1 or entry.want[0] != 0 \
                     or live.get(rid) is not seq or seq.length >= len(seq.tables[0]) * capacity or seq.length >= limit \
-                    or not sampler.greedy or sampler.repetition_penalty > 1.0 or not 0 <= entry.tokens[0] < vocab:
+                    or not 0 <= entry.tokens[0] < vocab:
                 return None
             tokens.append(entry.tokens[0])
         if self.manager.fresh_slots:
             return None
-        graph.load_again(tokens, sequences)
+        draws = None
+        if settings is None:                                   # the rows were greedy: they must still be
+            if any(not s.greedy or s.repetition_penalty > 1.0 for s in samplers):
+                return None
+        else:                                                  # the sampling records on the device but for the draws
+            if any((s.temperature, s.top_p, s.top_k, s.repetition_penalty) != known
+                   for s, known in zip(samplers, settings)):
+                return None
+            draws = [s.next_draw() for s in samplers]          # (one per row, as the ordinary path takes them)
+        graph.load_again(tokens, sequences, draws)
         graph.replay()
         for seq in sequences:                                  # (no window to release pages, no prefix to remember)
             seq.length += 1

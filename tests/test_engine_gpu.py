@@ -198,6 +198,7 @@ def test_sampled_generation_on_captured_decode_steps_follows_the_plain_sampler(t
     graphs = model.runner._graphs
     assert graphs is not None and sum(g.replays for g in graphs.graphs.values()) >= 15
     assert any(g.ranked for g in graphs.graphs.values()) and len({g.rows for g in graphs.graphs.values()}) >= 2
+    assert model.runner.steps_again >= 5         # steps that only wrote tokens, positions and draws (_step_again)
     follow_plain_sampler(folder, prompts, options, seeds, outputs)
 
 
