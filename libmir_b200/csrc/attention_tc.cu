@@ -14,26 +14,37 @@
 // touches shared memory),  O += P V  (tcgen05.mma with A in tensor memory, accumulator stays in tensor memory for
 // the whole row of tiles).  Roles:
 //
-//   loaders   one warp for keys (and Q, once per item), one for values.  Per tile the pages that hold it: one TMA box
-//             per page and 64-wide half of the head (cp.async.bulk.tensor.2d through a tensor map over the cache,
-//             128-byte swizzle), into a ring of three key tiles and one of two value tiles.  Pages the block table
-//             does not have (-1) are skipped.  A tile costs a loader a handful of instructions (what does not change
-//             with the tile is worked out per item, stages are counted, the block table is read two tiles ahead).
+//   loaders   two warps for keys (the CTA's even and odd tiles; the first also fetches Q, once per item), one for
+//             values, into a ring of three key tiles and one of two value tiles (cp.async.bulk.tensor.2d through
+//             tensor maps over the cache, 128-byte swizzle).  A copy instruction costs a warp about 75 cycles for every
+//             lane that takes part, so where a tile's pages lie one behind the other in the pool (while the pool is
+//             not fragmented they do) two lanes fetch the tile as two boxes of 128 keys; else one lane per page and
+//             64-wide half of the head (16 lanes for pages of 16 keys: 1,200 cycles, which then set the kernel's
+//             pace).  Pages the block table does not have (-1) are skipped.  The rest of a tile's work is a handful of
+//             instructions (what does not change with the tile is worked out per item, stages are counted, the block
+//             table is read two tiles ahead).  Registers are handed out to four warps at a time: the twentieth warp
+//             costs the others nothing.
 //   issuer    one warp that stays converged; the products are predicated on its elected lane and take their
 //             descriptors as 32-bit halves (tcgen05.cuh says why: a lone thread in a divergent branch fed the tensor
-//             cores a 64-cycle product only every 80 to 95 cycles beside the softmax warps).  Two S accumulators:
-//             S(t+2) = Q K(t+2)^T takes the one that holds P(t), so it is issued right behind O += P(t) V(t) (the
-//             tensor cores run products in the order of issue); while they work on one stream's tile, the other
-//             stream's softmax threads work on theirs.
-//   softmax   two streams of eight warps.  Stream s takes the key tiles t = s, s + 2, ... and keeps a softmax of
-//             its own over them: running maximum, denominator and an O accumulator of its own in tensor memory
-//             (as if the keys were split in two, as decode attention splits them); the two are merged when the
-//             row of tiles is over.  While one stream computes exponentials the other reads scores, finds its
-//             maximum and writes P, so the exponential unit and the tensor cores both stay busy.  Within a
-//             stream, query row r = accumulator lane r belongs to two threads, which take 64 columns each (of
-//             the scores; 32 of P) and share the row's maximum through shared memory.  A stream's running
-//             maximum is only raised when a tile's maximum exceeds it by more than 2^8 (then its O and its
-//             denominator are rescaled, O by tcgen05.ld / tcgen05.st), so most tiles need no pass over O.
+//             cores a 64-cycle product only every 80 to 95 cycles beside the softmax warps).  Three score
+//             accumulators and one for the output: S(t+3) = Q K(t+3)^T takes the accumulator that holds P(t), so it
+//             is issued right behind O += P(t) V(t) (the tensor cores run products in the order of issue), and the
+//             scores of a stream's next tile are there before its softmax of this one is over.
+//   softmax   two streams of eight warps take the key tiles in turn (stream s the tiles t = s, s + 2, ...), so that
+//             while one computes exponentials the other reads scores, finds its maximum and writes P.  A row has one
+//             running reference (its maximum, raised only when a tile's maximum exceeds it by more than 2^8), which
+//             the streams hand to each other through shared memory tile by tile (REF_READY; the value is known right
+//             after a tile's maximum, long before its exponentials are done), one output accumulator, and a partial
+//             denominator per stream, which are added when the row of tiles is over.  The stream that raises the
+//             reference rescales O (tcgen05.ld / tcgen05.st) once the product of the tile before has ended (PV_DONE);
+//             the product with its own P is not issued before it arrives, so nothing else touches O meanwhile.
+//             Within a stream, query row r = accumulator lane r belongs to two threads, which take 64 columns each
+//             (of the scores; 32 of P) and share the row's maximum through shared memory.
+//             (kShared = false is the form this one replaced, kept for measurements: every stream with a reference,
+//             a denominator and an output accumulator of its own over its tiles, two score accumulators, the two
+//             results merged at the end.  There a stream's next scores can only be issued behind its product with V,
+//             because P lies over the scores and tensor memory has no room for a third accumulator beside two
+//             outputs: softmax, product and next scores of a stream form a chain of 1,800 + 1,040 cycles.)
 //
 // V is read as an MN-major operand (rows of keys, 64 head elements per 128-byte row) exactly as the cache stores
 // it; nothing is transposed.  A hidden key's score is set to -inf by selection (in tiles that hide any), never by
@@ -66,21 +77,26 @@ constexpr int kSmemBytes = (3 + kKeyStages) * kTile + 1024;
 constexpr int kParts = 2;                   // softmax threads per query row and stream (each takes 64 columns)
 constexpr int kCols = kKeys / kParts;       // columns of a tile that one softmax thread handles
 constexpr int kStreamThreads = kRows * kParts;
-// key loader, issuer, eight softmax warps per stream, value loader
-__host__ __device__ constexpr int threads_for(int streams) { return (3 + 8 * streams) * 32; }
+// key loader (even tiles), issuer, eight softmax warps per stream, value loader, key loader (odd tiles): registers are
+// handed out to four warps at a time, so the twentieth warp costs the others nothing
+__host__ __device__ constexpr int threads_for(int streams) { return (4 + 8 * streams) * 32; }
 constexpr int kFirstSoftmaxWarp = 2;
 constexpr uint32_t kTmemColumns = 512;      // S0 at 0, S1 at 128, O of stream 0 at 256, of stream 1 at 384
 constexpr float kRescaleThreshold = 8.0f;   // log2 of how far a tile's maximum may exceed the running one
 
 // barrier indices
 enum { Q_FULL = 0, K_FULL = 1, K_FREE = K_FULL + kKeyStages, V_FULL = K_FREE + kKeyStages, V_FREE = V_FULL + 2,
-       S_FULL = V_FREE + 2, P_READY = S_FULL + 2, ITEM_DONE = P_READY + 2, Q_FREE, O_FREE, BARRIERS };
-// Tiles are counted over all items of a CTA (g): stage g & 1 of the value ring and of the score accumulators, phase
-// parity (g >> 1) & 1 (the key ring: g % 3 and (g / 3) & 1, kept as running counters; P_READY too has one barrier per stage: the two streams work on neighbouring tiles at the same
-// time, and the arrivals of one must not count for the other's tile); items are counted too (n): Q_FULL, Q_FREE,
+       S_FULL = V_FREE + 2, P_READY = S_FULL + 3, ITEM_DONE = P_READY + 3, Q_FREE, O_FREE, REF_READY, PV_DONE = REF_READY + 2,
+       BARRIERS = PV_DONE + 2 };
+// Tiles are counted over all items of a CTA (g): stage g & 1 of the value ring (and of REF_READY, PV_DONE), phase
+// parity (g >> 1) & 1; the key ring and the score accumulators: g % 3 and (g / 3) & 1, kept as running counters where
+// a role sees every tile (with kShared = false the score accumulators go by g & 1).  P_READY has one barrier per
+// score accumulator: the two streams work on neighbouring tiles at the same time, and the arrivals of one must not
+// count for the other's tile.  Items are counted too (n): Q_FULL, Q_FREE,
 // ITEM_DONE and O_FREE complete once per item.
 __device__ int g_tc_attention_error = 0;
 int g_streams = 2;
+int g_shared = 1;                           // the streams share a row's reference and one output accumulator
 int g_ctas = 0;                             // for measurements: 0 = one CTA per SM
 
 #ifdef MIR_TRACE
@@ -131,11 +147,22 @@ __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::l
 // !MASKED: the hidden ones are set to -inf first), which the kParts threads of a row exchange through `shared_max` (one float per part, kRows apart)
 // and the named barrier `team` of the stream's warps that hold the row's quarter of lanes; then the decision whether
 // the running maximum rises, and p = exp2(scale s - reference) packed to bf16.  Returns the sum of this thread's p.
-template <bool MASKED>
+// With a reference that the streams share (SHARED): the row's reference after the tile before comes from the other
+// stream (`from`: its barrier and where it left the value; none for an item's first tile), this tile's is left for the
+// next (`to`); `reference` is then the one this thread's partial denominator is scaled to, `factor` what the output
+// accumulator has to be multiplied by (if `grow`), `own_factor` what the denominator has to be.
+struct Handoff {
+  bool has_from;
+  uint32_t from_barrier, from_parity;
+  const float* from;
+  uint32_t to_barrier;
+  float* to;
+};
+template <bool MASKED, bool SHARED>
 __device__ __forceinline__ float softmax_tile(uint32_t scores, int first, int low, int high, float scale_log2,
                                               float& reference, float& factor, bool& grow,
                                               uint32_t (&packed)[kCols / 2], float* shared_max, int part, int team,
-                                              int stamp_tile) {
+                                              int stamp_tile, const Handoff& handoff, float& own_factor, bool& alive) {
   float v[kCols];
 #pragma unroll
   for (int c0 = 0; c0 < kCols; c0 += 32) tmem_load_32_nowait(scores + first + c0, v + c0);
@@ -160,9 +187,25 @@ __device__ __forceinline__ float softmax_tile(uint32_t scores, int first, int lo
   for (int other = 0; other < kParts; ++other) maximum = fmaxf(maximum, shared_max[other * kRows]);
   ATT_STAMP(stamp_tile, 8);
   maximum *= scale_log2;                                               // scale > 0
-  grow = maximum > reference + kRescaleThreshold;
-  factor = grow ? fast_exp2(reference - maximum) : 1.0f;               // 0 when nothing was seen before
-  reference = grow ? maximum : reference;
+  if (SHARED) {
+    float before = -INFINITY;
+    if (handoff.has_from) {
+      if (alive && !wait_barrier(handoff.from_barrier, handoff.from_parity)) { g_tc_attention_error = 3; alive = false; }
+      before = *handoff.from;
+    }
+    const float now = maximum > before + kRescaleThreshold ? maximum : before;
+    if (part == 0) *handoff.to = now;
+    barrier_arrive(handoff.to_barrier);
+    grow = now != before;
+    factor = grow ? fast_exp2(before - now) : 1.0f;                    // 0 when nothing was seen before
+    own_factor = reference == now ? 1.0f : fast_exp2(reference - now); // (-inf - -inf is no number: the first branch)
+    reference = now;
+  } else {
+    grow = maximum > reference + kRescaleThreshold;
+    factor = grow ? fast_exp2(reference - maximum) : 1.0f;             // 0 when nothing was seen before
+    reference = grow ? maximum : reference;
+    own_factor = factor;
+  }
   // (a row that has seen no key yet, in this tile either, has reference -inf: -inf - -inf would not be a number)
   const float shift = (MASKED && reference == -INFINITY) ? 0.0f : -reference;
   float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -228,10 +271,11 @@ __device__ __forceinline__ int item_of(int k, int cta, int ctas, int items) {
   return k * ctas + ((k & 1) ? ctas - 1 - cta : cta);
 }
 
-template <int kStreams>
+template <int kStreams, bool kShared>
 __global__ void __launch_bounds__(threads_for(kStreams), 1)
 tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-                            const __grid_constant__ CUtensorMap v_map, bf16* __restrict__ out,
+                            const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap k_tile_map,
+                            const __grid_constant__ CUtensorMap v_tile_map, bf16* __restrict__ out,
                             const int* __restrict__ block_table, int table_width, const int* __restrict__ query_starts,
                             const int* __restrict__ context_lens, int num_rows, int page_size, int heads, int kv_heads,
                             float scale_log2, int window, int tile_slots) {
@@ -242,6 +286,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   __shared__ float exchange[kStreams][2][kParts][kRows];     // [stream][its tile parity][part][row]: a row's maxima
   __shared__ float denominators[2][kStreams][kParts][kRows]; // [item parity]...: a slow thread may still read the last item's
   __shared__ float references[2][kStreams][kRows];
+  __shared__ float handed[2][kRows];                          // kShared: a row's reference after the CTA's tile g, by g & 1
   __shared__ int query_tiles_slot;
   if (*reinterpret_cast<volatile int*>(&g_tc_attention_error) != 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -270,7 +315,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   auto bar = [&](int index) { return bar0 + 8u * (uint32_t)index; };
   if (threadIdx.x == 0) {
     for (int i = 0; i < BARRIERS; ++i) {
-      const bool many = i == P_READY || i == P_READY + 1;                  // every softmax thread of a stream arrives
+      const bool many = (i >= P_READY && i < P_READY + 3) || i == REF_READY || i == REF_READY + 1;   // a stream's threads arrive
       const bool all = i == O_FREE;                                        // every softmax thread of every stream
       barrier_init(bar(i), all ? (uint32_t)(kStreamThreads * kStreams) : (many ? (uint32_t)kStreamThreads : 1u));
     }
@@ -290,16 +335,19 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   __syncthreads();
   tensor_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
-  const uint32_t tmem_o = tmem_base + 256u;
+  // split keys: S0 at 0, S1 at 128, O of stream 0 at 256, of stream 1 at 384; shared reference: S0, S1, S2, O at 384
+  const uint32_t tmem_o = tmem_base + (kShared ? 384u : 256u);
 
   constexpr int kValueLoader = kFirstSoftmaxWarp + 8 * kStreams;   // the warp behind the softmax warps
-  if (warp == 0 || warp == kValueLoader) {
+  if (warp == 0 || warp >= kValueLoader) {
     // ------------------------------------------------------------------ loaders: warp 0 keys (and Q), the last warp
     // values (apart, so that the keys of a later tile do not queue behind values whose stage is still being read).
     // These warps share their schedulers with four softmax warps each and every instruction of theirs takes long, so
     // a tile costs them as few as can be: everything that does not change with the tile is worked out before the
     // loop, the stage and its parity are counted, not divided, and the block table is read two tiles ahead.
-    const int which = warp == 0 ? 0 : 1;                      // keys or values
+    const int which = warp == kValueLoader ? 1 : 0;           // keys or values
+    // the keys have two loaders, which take the CTA's even and odd tiles (one loader's loop set the kernel's pace)
+    const int turns = which ? 1 : 2, turn = warp == 0 ? 0 : 1;
     const int page_shift = 31 - __clz(page_size);             // pages are powers of two (they divide 128)
     const int pages_per_tile = kKeys >> page_shift;
     const uint32_t box_bytes = (uint32_t)page_size * 128u;
@@ -309,6 +357,8 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     const uint32_t lane_dst = smem_base + (which ? kOffV : kOffK) + (uint32_t)half * kHalf +
                               (uint32_t)(slot * page_size) * 128u;
     const CUtensorMap* map = which ? &v_map : &k_map;
+    const CUtensorMap* tile_map = which ? &v_tile_map : &k_tile_map;     // boxes of 128 keys
+    const uint32_t tile_dst = smem_base + (which ? kOffV : kOffK);
     const int stages = which ? 2 : kKeyStages;
     const uint32_t full0 = bar(which ? V_FULL : K_FULL), free0 = bar(which ? V_FREE : K_FREE);
     int stage = 0;                                            // of the CTA's tile g = g0 + t: g % stages,
@@ -335,20 +385,41 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         const int key = lane_key + t * kKeys;
         return (loads && t < tiles && key < key_end && key > first_visible) ? entry[t * pages_per_tile] : -1;
       };
-      int page_next = page_of(0), page_after = page_of(1);
-      for (int t = 0; t < tiles; ++t) {
+      // this loader's tiles of the item: every one, or those whose number in the CTA is even (odd)
+      const int first_tile = turns == 1 ? 0 : ((g0 & 1) == turn ? 0 : 1);
+      if (turns == 2 && first_tile == 1) {                     // (the ring's other loader has tile 0)
+        if (++stage == stages) { stage = 0; parity ^= 1u; }
+      }
+      int page_next = page_of(first_tile), page_after = page_of(first_tile + turns);
+      for (int t = first_tile; t < tiles; t += turns) {
         const int page = page_next;
         page_next = page_after;
-        page_after = page_of(t + 2);                          // on its way while these tiles' stages are awaited
+        page_after = page_of(t + 2 * turns);                  // on its way while these tiles' stages are awaited
         const uint32_t full = full0 + 8u * (uint32_t)stage;
         if (!wait_barrier(free0 + 8u * (uint32_t)stage, parity ^ 1u)) { g_tc_attention_error = 1; alive = false; break; }
         if (lane == 0) ATT_STAMP(g0 + t, which);
-        const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
-        if (lane == 0) barrier_expect_bytes(full, (uint32_t)__popc(valid) * box_bytes);
-        __syncwarp();
-        if (page >= 0) tma_load_2d(lane_dst + (uint32_t)stage * kTile, map, full, x, page << page_shift);
+        // A copy instruction costs the warp about 75 cycles for every lane that takes part (16 lanes: 1,200 cycles a
+        // tile, which set the kernel's pace).  Where the tile's pages lie one behind the other in the pool, as they do
+        // while the pool is not fragmented, two lanes fetch the whole tile, one box of 128 keys for each half.
+        const int first_page = __shfl_sync(0xffffffffu, page, 0);
+        const bool in_a_row = first_page >= 0 && __all_sync(0xffffffffu, !loads || page == first_page + slot);
+        if (in_a_row) {
+          if (lane == 0) barrier_expect_bytes(full, kTile);
+          __syncwarp();
+          if (lane < 2)
+            tma_load_2d(tile_dst + (uint32_t)lane * kHalf + (uint32_t)stage * kTile, tile_map, full,
+                        w.kv_head * kDim + lane * 64, first_page << page_shift);
+        } else {
+          const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
+          if (lane == 0) barrier_expect_bytes(full, (uint32_t)__popc(valid) * box_bytes);
+          __syncwarp();
+          if (page >= 0) tma_load_2d(lane_dst + (uint32_t)stage * kTile, map, full, x, page << page_shift);
+        }
         if (lane == 0 && which == 0) ATT_STAMP(g0 + t, 15);
         if (++stage == stages) { stage = 0; parity ^= 1u; }
+        if (turns == 2 && t + 1 < tiles) {                     // the other loader's tile
+          if (++stage == stages) { stage = 0; parity ^= 1u; }
+        }
       }
       g0 += tiles;
       ++n;
@@ -364,6 +435,8 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     bool alive = true;
     int g0 = 0, n = 0;
     uint32_t key_stage = 0, key_parity = 0;                   // of the next tile of scores: g % kKeyStages, (g / kKeyStages) & 1
+    uint32_t p_stage = 0, p_parity = 0;                       // kShared: of the next product with V: g % 3, (g / 3) & 1
+    static_assert(!kShared || kKeyStages == 3, "the score accumulators go round with the key ring");
     for (int k = 0; more(k); ++k) {
       const Work w = work(k);
       if (!w.valid) continue;
@@ -376,7 +449,9 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         if (alive && !wait_barrier(bar(K_FULL + key_stage), key_parity)) { g_tc_attention_error = 2; alive = false; }
         if (elected) ATT_STAMP(g, 12);
         tensor_fence_after_sync();
-        const uint32_t b_low = k_low + key_stage * (uint32_t)(kTile >> 4), d = tmem_base + stage * 128u;
+        // (with the shared reference the scores have three buffers and go round with the key ring)
+        const uint32_t score_stage = kShared ? key_stage : stage;
+        const uint32_t b_low = k_low + key_stage * (uint32_t)(kTile >> 4), d = tmem_base + score_stage * 128u;
         mma_bf16_ss_halves<false>(d, q_low, b_low, idesc_qk, elected);
 #pragma unroll
         for (int kk = 1; kk < kDim / 16; ++kk) {
@@ -384,7 +459,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           const uint32_t offset = (uint32_t)(kk >> 2) * kHalfStep + (uint32_t)(kk & 3) * 2u;
           mma_bf16_ss_halves<true>(d, q_low + offset, b_low + offset, idesc_qk, elected);
         }
-        mma_commit_elected(bar(S_FULL + stage), elected);
+        mma_commit_elected(bar(S_FULL + score_stage), elected);
         mma_commit_elected(bar(K_FREE + key_stage), elected);
         if (elected) ATT_STAMP(g, 2);
         if (t == tiles - 1) mma_commit_elected(bar(Q_FREE), elected);   // the item's last product with its queries
@@ -393,8 +468,12 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       // P(t) is written over S(t) in tensor memory, so S(t + 2), which takes the same accumulator, is issued
       // behind the product with P(t): the tensor cores run products in the order of issue, and while they work
       // on one stream's tile the other stream's softmax threads work on theirs
+      // With the shared reference there are three score accumulators and one for the output: S(t + 3) takes the one
+      // that holds P(t), and a stream's next scores are there before its softmax of this tile is over.
+      constexpr int kAhead = kShared ? 3 : 2;
       issue_scores(0);
       if (tiles > 1) issue_scores(1);
+      if (kShared && tiles > 2) issue_scores(2);
       for (int t = 0; t < tiles; ++t) {
         const int g = g0 + t;
         const uint32_t stage = (uint32_t)g & 1u;
@@ -402,7 +481,8 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         if (elected) ATT_STAMP(g, 13);
         if (alive && !wait_barrier(bar(V_FULL + stage), parity)) { g_tc_attention_error = 2; alive = false; }
         if (elected) ATT_STAMP(g, 3);
-        if (alive && !wait_barrier(bar(P_READY + stage), parity)) { g_tc_attention_error = 2; alive = false; }
+        const uint32_t p_slot = kShared ? p_stage : stage, p_turn = kShared ? p_parity : parity;
+        if (alive && !wait_barrier(bar(P_READY + p_slot), p_turn)) { g_tc_attention_error = 2; alive = false; }
         if (elected) ATT_STAMP(g, 4);
         // the output accumulators are the last item's until every softmax thread has read them out
         if (t == 0 && n > 0 && alive && !wait_barrier(bar(O_FREE), (uint32_t)(n - 1) & 1u)) {
@@ -410,18 +490,22 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           alive = false;
         }
         tensor_fence_after_sync();
-        const uint32_t p = tmem_base + stage * 128u;
+        const uint32_t p = tmem_base + p_slot * 128u;
         const uint32_t b_low = v_low + stage * (uint32_t)(kTile >> 4);
-        const uint32_t o = tmem_o + (uint32_t)(t % kStreams) * 128u;
+        const uint32_t o = kShared ? tmem_o : tmem_o + (uint32_t)(t % kStreams) * 128u;
         // P: 16 keys are 8 columns of packed pairs further on; V: 16 rows of keys (2 KB) further down
-        mma_bf16_ts_halves(o, p, b_low, idesc_pv, t >= kStreams ? 1u : 0u, elected);
+        mma_bf16_ts_halves(o, p, b_low, idesc_pv, t >= (kShared ? 1 : kStreams) ? 1u : 0u, elected);
 #pragma unroll
         for (int kk = 1; kk < kKeys / 16; ++kk)
           mma_bf16_ts_halves(o, p + (uint32_t)kk * 8u, b_low + (uint32_t)kk * (2048u >> 4), idesc_pv, 1u, elected);
         mma_commit_elected(bar(V_FREE + stage), elected);
+        if (kShared) {
+          mma_commit_elected(bar(PV_DONE + stage), elected);  // (a stream that raises the reference waits for it)
+          if (++p_stage == 3u) { p_stage = 0; p_parity ^= 1u; }
+        }
         if (elected) ATT_STAMP(g, 14);
         if (t == tiles - 1) mma_commit_elected(bar(ITEM_DONE), elected);
-        if (t + 2 < tiles) issue_scores(t + 2);
+        if (t + kAhead < tiles) issue_scores(t + kAhead);
       }
       g0 += tiles;
       ++n;
@@ -434,7 +518,7 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     const int r = quarter * 32 + lane;
     const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
     const int first = part * kCols;
-    const uint32_t my_o = tmem_o + (uint32_t)stream * 128u + lane_bits;
+    const uint32_t my_o = tmem_o + (kShared ? 0u : (uint32_t)stream * 128u) + lane_bits;
     bool alive = true;
     // (a thread whose wait ran out keeps walking the tiles without waiting, so that the row's named barrier
     // still sees all of its threads)
@@ -448,8 +532,8 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       float reference = -INFINITY, denominator = 0.0f;        // running maximum (scaled, log2 domain), partial sum
       for (int t = stream; t < w.tiles; t += kStreams) {
         const int g = g0 + t;
-        const int stage = g & 1;
-        const uint32_t parity = (uint32_t)(g >> 1) & 1u;
+        const int stage = kShared ? g % 3 : g & 1;            // the score accumulator of the tile
+        const uint32_t parity = (uint32_t)(kShared ? g / 3 : g >> 1) & 1u;
         const int key0 = w.key_begin + t * kKeys;
         const int stamp_tile = (lane == 0 && quarter == 0 && part == 0) ? g : -1;
         ATT_STAMP(stamp_tile, 5);
@@ -466,15 +550,35 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         float factor;
         float* shared_max = &exchange[stream][(t / kStreams) & 1][0][r];
         const int team = 1 + stream * 4 + quarter;
-        const float sum = every ? softmax_tile<false>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
-                                                      shared_max, part, team, stamp_tile)
-                                : softmax_tile<true>(scores, first, low, high, scale_log2, reference, factor, grow, packed,
-                                                     shared_max, part, team, stamp_tile);
+        Handoff handoff;
+        handoff.has_from = kShared && t > 0;                  // the row's reference after the CTA's tile g - 1
+        handoff.from_barrier = bar(REF_READY + ((g - 1) & 1));
+        handoff.from_parity = (uint32_t)((g - 1) >> 1) & 1u;
+        handoff.from = &handed[(g - 1) & 1][r];
+        handoff.to_barrier = bar(REF_READY + (g & 1));
+        handoff.to = &handed[g & 1][r];
+        float own_factor;
+        const float sum = every ? softmax_tile<false, kShared>(scores, first, low, high, scale_log2, reference, factor, grow,
+                                                               packed, shared_max, part, team, stamp_tile, handoff,
+                                                               own_factor, alive)
+                                : softmax_tile<true, kShared>(scores, first, low, high, scale_log2, reference, factor, grow,
+                                                              packed, shared_max, part, team, stamp_tile, handoff,
+                                                              own_factor, alive);
         ATT_STAMP(stamp_tile, 9);
-        denominator = denominator * factor + sum;
-        // This stream's previous product (tile t - kStreams) is over: S(t) was issued behind it, and the scores'
-        // barrier completes only when everything issued before it has.  So its O may be rescaled now.
-        if (t >= kStreams && __any_sync(0xffffffffu, grow)) {
+        denominator = denominator * own_factor + sum;
+        // Split keys: this stream's previous product (tile t - kStreams) is over: S(t) was issued behind it, and the
+        // scores' barrier completes only when everything issued before it has.  So its O may be rescaled now.
+        // Shared reference: the one accumulator holds the products up to tile t - 1, whose end is waited for (the
+        // product with this tile's P is not issued before this stream arrives, so nothing else touches O meanwhile).
+        const bool rescale = (kShared ? t > 0 : t >= kStreams) && __any_sync(0xffffffffu, grow);
+        if (kShared && rescale) {
+          if (alive && !wait_barrier(bar(PV_DONE + ((g - 1) & 1)), (uint32_t)((g - 1) >> 1) & 1u)) {
+            g_tc_attention_error = 3;
+            alive = false;
+          }
+          tensor_fence_after_sync();
+        }
+        if (rescale) {
 #pragma unroll 1
           for (int c0 = 0; c0 < kDim / kParts; c0 += 32) {
             float o[32];
@@ -530,8 +634,14 @@ tc_prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __g
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = 0.0f;
 #pragma unroll
-          for (int other = 0; other < kStreams; ++other) {
-            if (other < w.tiles) {                            // a stream without a tile never wrote its O
+          for (int other = 0; other < (kShared ? 1 : kStreams); ++other) {
+            if (kShared) {
+              // one accumulator, scaled to the last tile's reference, which is the largest
+              float theirs[32];
+              tmem_load_32(tmem_o + lane_bits + column + c0, theirs);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = inverse > 0.0f ? theirs[i] * inverse : 0.0f;
+            } else if (other < w.tiles) {                     // a stream without a tile never wrote its O
               float theirs[32];
               tmem_load_32(tmem_o + (uint32_t)other * 128u + lane_bits + column + c0, theirs);
               const float share = weight[other] * inverse;
@@ -617,19 +727,27 @@ MIR_EXPORT int mir_prefill_attention_tc_bf16(const void* q, long long q_stride, 
                   heads, kv_heads);
     return MIR_BAD_ARGUMENT;
   }
-  CUtensorMap q_map, k_map, v_map;
+  CUtensorMap q_map, k_map, v_map, k_tile_map, v_tile_map;
   int status = tensor_map_for(q, tokens, (int)q_stride, (int)q_stride, kRows, &q_map);
   if (status != MIR_OK) return status;
   status = tensor_map_for(k_pages, (int)cache_rows, kv_heads * kDim, kv_heads * kDim, page_size, &k_map);
   if (status != MIR_OK) return status;
   status = tensor_map_for(v_pages, (int)cache_rows, kv_heads * kDim, kv_heads * kDim, page_size, &v_map);
   if (status != MIR_OK) return status;
+  status = tensor_map_for(k_pages, (int)cache_rows, kv_heads * kDim, kv_heads * kDim, kKeys, &k_tile_map);
+  if (status != MIR_OK) return status;
+  status = tensor_map_for(v_pages, (int)cache_rows, kv_heads * kDim, kv_heads * kDim, kKeys, &v_tile_map);
+  if (status != MIR_OK) return status;
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(tc_prefill_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           kSmemBytes);
+    cudaError_t err = cudaFuncSetAttribute(tc_prefill_attention_kernel<2, false>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (err == cudaSuccess)
-      err = cudaFuncSetAttribute(tc_prefill_attention_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+      err = cudaFuncSetAttribute(tc_prefill_attention_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kSmemBytes);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(tc_prefill_attention_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kSmemBytes);
     if (err != cudaSuccess) {
       mir_set_error("prefill_attention_tc: cannot reserve %d bytes of shared memory: %s", kSmemBytes,
                     cudaGetErrorString(err));
@@ -650,13 +768,18 @@ MIR_EXPORT int mir_prefill_attention_tc_bf16(const void* q, long long q_stride, 
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
   }
   const int ctas = (int)std::min<long long>(items, g_ctas > 0 ? g_ctas : sms);
-  if (g_streams == 2)
-    return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<2>, dim3(ctas), dim3(threads_for(2)),
-                      (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, (bf16*)out, block_table, table_width,
+  if (g_streams == 2 && g_shared)
+    return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<2, true>, dim3(ctas), dim3(threads_for(2)),
+                      (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, k_tile_map, v_tile_map, (bf16*)out, block_table, table_width,
                       query_starts, context_lens, num_rows, page_size, heads, kv_heads,
                       scale * 1.4426950408889634f, window, tile_slots);
-  return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<1>, dim3(ctas), dim3(threads_for(1)),
-                    (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, (bf16*)out, block_table, table_width,
+  if (g_streams == 2)
+    return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<2, false>, dim3(ctas), dim3(threads_for(2)),
+                      (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, k_tile_map, v_tile_map, (bf16*)out, block_table, table_width,
+                      query_starts, context_lens, num_rows, page_size, heads, kv_heads,
+                      scale * 1.4426950408889634f, window, tile_slots);
+  return mir_launch("prefill_attention_tc", tc_prefill_attention_kernel<1, false>, dim3(ctas), dim3(threads_for(1)),
+                    (size_t)kSmemBytes, stream, 0, q_map, k_map, v_map, k_tile_map, v_tile_map, (bf16*)out, block_table, table_width,
                     query_starts, context_lens, num_rows, page_size, heads, kv_heads,
                     scale * 1.4426950408889634f, window, tile_slots);
 }
@@ -665,6 +788,14 @@ MIR_EXPORT int mir_prefill_attention_tc_bf16(const void* q, long long q_stride, 
 MIR_EXPORT int mir_prefill_attention_tc_set_streams(int streams) {
   if (streams != 1 && streams != 2) return MIR_BAD_ARGUMENT;
   g_streams = streams;
+  return MIR_OK;
+}
+
+// For measurements: 1 (the default) the two streams share a row's running reference, three score accumulators and
+// one output accumulator; 0 each stream keeps a softmax of its own over its tiles and the two are merged.
+MIR_EXPORT int mir_prefill_attention_tc_set_shared(int shared) {
+  if (shared != 0 && shared != 1) return MIR_BAD_ARGUMENT;
+  g_shared = shared;
   return MIR_OK;
 }
 

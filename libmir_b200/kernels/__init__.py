@@ -64,6 +64,7 @@ _SIGNATURES = {
         "mir_prefill_attention_tc_takes": [c_int, c_int],
         "mir_prefill_attention_tc_error": [],
         "mir_prefill_attention_tc_set_streams": [c_int],
+        "mir_prefill_attention_tc_set_shared": [c_int],
         "mir_gemm_tc_stream_bf16": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                     c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "mir_gemm_tc_stream_error": [],
@@ -507,6 +508,13 @@ def set_prefill_softmax_streams(streams: int) -> None:
     """For measurements: over how many softmax streams the tcgen05 attention splits a row's key tiles, 1 or 2."""
     lib = library("bf16")
     _check(lib, lib.mir_prefill_attention_tc_set_streams(int(streams)))
+
+
+def set_prefill_shared_reference(shared: bool) -> None:
+    """For measurements: whether the two softmax streams of the tcgen05 prompt attention share a row's reference and
+    one output accumulator (the default) or keep a softmax each over their tiles."""
+    lib = library("bf16")
+    _check(lib, lib.mir_prefill_attention_tc_set_shared(1 if shared else 0))
 
 
 def decode_attention_error() -> int:

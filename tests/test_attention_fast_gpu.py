@@ -19,12 +19,21 @@ def cuda(t):
     return t.to("cuda")
 
 
-def build_pool(ks, vs, page, rng, garbage=50.0):
-    """Scatter each request's keys/values into shuffled pages of one pool; returns pools and the tables."""
+def build_pool(ks, vs, page, rng, garbage=50.0, runs=False):
+    """Scatter each request's keys/values into shuffled pages of one pool; returns pools and the tables.  With `runs`
+    the pages lie one behind the other in stretches of 1 to 40 pages (a pool that is partly fragmented): the tcgen05
+    prompt kernel then fetches whole tiles where it can and single pages where it cannot."""
     kv_heads, dim = ks[0].shape[1:]
     blocks = [-(-k.shape[0] // page) for k in ks]
     total = sum(blocks) + 5
     order = rng.permutation(total)
+    if runs:
+        starts, cursor = [], 0
+        while cursor < total:
+            length = int(rng.integers(1, 41))
+            starts.append((cursor, min(total, cursor + length)))
+            cursor += length
+        order = np.concatenate([np.arange(a, b) for a, b in (starts[i] for i in rng.permutation(len(starts)))])
     k_pool = (torch.randn(total * page, kv_heads, dim) * garbage).to(BF16)
     v_pool = (torch.randn(total * page, kv_heads, dim) * garbage).to(BF16)
     table = torch.full((len(ks), max(blocks)), -1, dtype=torch.int32)
@@ -130,10 +139,14 @@ def test_prefill_attention_mixed_portions(heads, kv_heads, dim, page, window):
 
 @pytest.mark.parametrize("heads,kv_heads,page,window", [
     (8, 2, 16, None), (4, 4, 8, None), (6, 1, 32, 100), (3, 3, 128, 300), (32, 8, 16, None), (2, 1, 64, 129)])
-def test_prefill_attention_on_tcgen05(heads, kv_heads, page, window):
-    """The tcgen05 kernel (head_dim 128): a whole 700-token prompt, a 300-token portion that starts at 333, a
-    single decoded token at 129, a 2-token portion at 64, and a 130-token portion that ends on a tile's edge."""
+@pytest.mark.parametrize("runs", [False, True])
+@pytest.mark.parametrize("shared", [True, False])
+def test_prefill_attention_on_tcgen05(heads, kv_heads, page, window, shared, runs):
+    """The tcgen05 kernel (head_dim 128; its two softmax streams sharing a row's reference and one output accumulator,
+    or each with a softmax of its own): a whole 700-token prompt, a 300-token portion that starts at 333, a single
+    decoded token at 129, a 2-token portion at 64, and a 130-token portion that ends on a tile's edge."""
     from libmir_b200 import kernels
+    kernels.set_prefill_shared_reference(shared)
     dim = 128
     rng = np.random.default_rng(page + heads)
     torch.manual_seed(page + heads)
@@ -142,7 +155,7 @@ def test_prefill_attention_on_tcgen05(heads, kv_heads, page, window):
     qs = [(torch.randn(end, heads, dim) * 2).to(BF16) for _, end in spans]
     ks = [(torch.randn(end, kv_heads, dim) * 2).to(BF16) for _, end in spans]
     vs = [torch.randn(end, kv_heads, dim).to(BF16) for _, end in spans]
-    k_pool, v_pool, table = build_pool(ks, vs, page, rng)
+    k_pool, v_pool, table = build_pool(ks, vs, page, rng, runs=runs)
     q_rows = torch.cat([q[start:end] for q, (start, end) in zip(qs, spans)])
     tokens = q_rows.shape[0]
     packed = torch.cat([q_rows.reshape(tokens, -1), torch.randn(tokens, 2 * kv_heads * dim).to(BF16)], dim=1).contiguous()
@@ -153,6 +166,7 @@ def test_prefill_attention_on_tcgen05(heads, kv_heads, page, window):
                               cuda(torch.tensor([end for _, end in spans], dtype=torch.int32)), page, heads, kv_heads,
                               dim, scale, window, tensor_cores=True)
     torch.cuda.synchronize()
+    kernels.set_prefill_shared_reference(True)
     assert kernels.prefill_attention_error() == 0
     expected = torch.cat([expect(q, k, v, scale, window, slice(start, end))
                           for q, k, v, (start, end) in zip(qs, ks, vs, spans)])
@@ -354,8 +368,9 @@ def test_decode_attention_over_a_long_context(tensor_cores):
     assert torch.allclose(out.reshape(rows, heads, dim)[0, 0].float().cpu(), vs[0][777, 0].float(), atol=5e-2)
 
 
+@pytest.mark.parametrize("shared", [True, False])
 @pytest.mark.parametrize("window", [None, 1000])
-def test_prefill_attention_on_tcgen05_over_a_long_prompt(window):
+def test_prefill_attention_on_tcgen05_over_a_long_prompt(window, shared):
     """9,000 tokens in one portion: 71 key tiles for the last queries, shared out over both softmax streams; keys
     late in the prompt that dominate (one in an even tile, one in an odd one) raise each stream's running maximum
     after thousands of keys, which rescales what it has accumulated.  Checked on a sample of query rows."""
@@ -370,13 +385,15 @@ def test_prefill_attention_on_tcgen05_over_a_long_prompt(window):
     for key in (7000, 7000 + 128 + 5):                         # tile 54 (even) and tile 55 (odd)
         k[key, 0] = (q[8500, 0].float() * 2.0).to(BF16)        # head 0 of query 8500 looks straight at them
         k[key, 1] = (q[8990, 3].float() * 2.0).to(BF16)
-    k_pool, v_pool, table = build_pool([k], [v], page, rng)
+    k_pool, v_pool, table = build_pool([k], [v], page, rng, runs=shared)
     packed = torch.cat([q.reshape(n, -1), torch.zeros(n, 2 * kv_heads * dim, dtype=BF16)], dim=1).contiguous()
     out = torch.full((n, heads * dim), 9.0, device="cuda", dtype=BF16)
+    kernels.set_prefill_shared_reference(shared)
     kernels.prefill_attention(cuda(packed), out, cuda(k_pool), cuda(v_pool), cuda(table),
                               cuda(torch.tensor([0, n], dtype=torch.int32)), cuda(torch.tensor([n], dtype=torch.int32)),
                               page, heads, kv_heads, dim, scale, window, tensor_cores=True)
     torch.cuda.synchronize()
+    kernels.set_prefill_shared_reference(True)
     assert kernels.prefill_attention_error() == 0
     rows = sorted(set([0, 1, 127, 128, 129, 999, 1000, 1001, 4095, 4096, 7133, 7134, 8500, 8990, n - 1]
                       + rng.integers(0, n, 150).tolist()))
