@@ -128,6 +128,8 @@ __device__ __forceinline__ uint32_t small_operand_offset(int row, int column) {
 template <int G>
 __global__ void __launch_bounds__(kThreads)
 tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                           const __grid_constant__ CUtensorMap k_tile_map,
+                           const __grid_constant__ CUtensorMap v_tile_map,
                            const bf16* __restrict__ q, size_t q_stride, const int* __restrict__ block_table,
                            int table_width, const int* __restrict__ positions, int page_size, int heads, int kv_heads,
                            float scale_log2, int window, int partition, int num_partitions, int part_slow,
@@ -211,6 +213,11 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
     for (int t = 0; t < tiles && alive; ++t) {
       const uint32_t parity = (uint32_t)t & 1u;
       const int next_row = row_of(t + 1);                     // on its way while this tile's slots are awaited
+      // A copy instruction costs the warp about 75 cycles for every lane that takes part: 2,400 cycles for the keys
+      // and values of a tile of 16-key pages.  Where the tile's pages lie one behind the other in the pool (a prompt's
+      // pages do while the pool is not fragmented), two lanes fetch each of them as two boxes of 128 keys.
+      const int first_row = __shfl_sync(0xffffffffu, cache_row, 0);
+      const bool in_a_row = first_row >= 0 && __all_sync(0xffffffffu, !loads || cache_row == first_row + slot * page_size);
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const uint32_t full = bar(which ? V_FULL : K_FULL), free_bar = bar(which ? V_FREE : K_FREE);
@@ -220,9 +227,14 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
         if (!ok) { if (lane == 0) g_tc_decode_error = 1; alive = false; break; }
         if (lane == 0) barrier_expect_bytes(full, (uint32_t)kTile);
         __syncwarp();
-        if (loads)
+        if (in_a_row) {
+          if (lane < 2)
+            tma_load_2d(smem_base + (which ? kOffV : kOffK) + (uint32_t)lane * kHalf, which ? &v_tile_map : &k_tile_map,
+                        full, kv_head * kDim + lane * 64, first_row);
+        } else if (loads) {
           tma_load_2d(smem_base + (which ? kOffV : kOffK) + (uint32_t)half * kHalf + (uint32_t)(slot * page_size) * 128u,
                       which ? &v_map : &k_map, full, kv_head * kDim + half * 64, cache_row);
+        }
       }
       cache_row = next_row;
     }
@@ -384,7 +396,8 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
 }
 
 template <int G>
-int launch(const CUtensorMap& k_map, const CUtensorMap& v_map, const bf16* q, size_t q_stride, const int* block_table,
+int launch(const CUtensorMap& k_map, const CUtensorMap& v_map, const CUtensorMap& k_tile_map,
+           const CUtensorMap& v_tile_map, const bf16* q, size_t q_stride, const int* block_table,
            int table_width, const int* positions, int rows, int page_size, int heads, int kv_heads, float scale,
            int window, int partition, int num_partitions, float* partial_o, float* partial_ml, bf16* out,
            cudaStream_t stream) {
@@ -405,7 +418,8 @@ int launch(const CUtensorMap& k_map, const CUtensorMap& v_map, const bf16* q, si
   // partitions beyond the contexts (dead CTAs of a captured batch) are dispatched last
   const dim3 grid = rows <= 4 ? dim3(rows, units, num_partitions) : dim3(num_partitions, units, rows);
   return mir_launch_with(mir_pdl_for_streaming(), "decode_attention_tc", tc_decode_attention_kernel<G>, grid,
-                         dim3(kThreads), (size_t)kSmemBytes, stream, 0, k_map, v_map, q, q_stride, block_table,
+                         dim3(kThreads), (size_t)kSmemBytes, stream, 0, k_map, v_map, k_tile_map, v_tile_map, q, q_stride,
+                         block_table,
                          table_width, positions, page_size, heads, kv_heads, scale * 1.4426950408889634f, window,
                          partition, num_partitions, rows <= 4 ? 1 : 0, partial_o, partial_ml, out);
 }
@@ -451,17 +465,21 @@ MIR_EXPORT int mir_decode_attention_tc_bf16(const void* q, long long q_stride, v
     mir_set_error("decode_attention_tc: scratch of %lld floats is needed, got %lld", need, scratch_floats);
     return MIR_BAD_ARGUMENT;
   }
-  CUtensorMap k_map, v_map;
+  CUtensorMap k_map, v_map, k_tile_map, v_tile_map;
   int status = tensor_map_for(k_pages, (int)cache_rows, kv_heads * kDim, kv_heads * kDim, page_size, &k_map);
   if (status != MIR_OK) return status;
   status = tensor_map_for(v_pages, (int)cache_rows, kv_heads * kDim, kv_heads * kDim, page_size, &v_map);
+  if (status != MIR_OK) return status;
+  status = tensor_map_for(k_pages, (int)cache_rows, kv_heads * kDim, kv_heads * kDim, kKeys, &k_tile_map);
+  if (status != MIR_OK) return status;
+  status = tensor_map_for(v_pages, (int)cache_rows, kv_heads * kDim, kv_heads * kDim, kKeys, &v_tile_map);
   if (status != MIR_OK) return status;
   const int group = heads / kv_heads;
   const int columns = std::min(group, kHeads);
   float* partial_o = scratch;
   float* partial_ml = scratch ? scratch + (size_t)rows * heads * num_partitions * head_dim : nullptr;
 #define MIR_SPLIT(G)                                                                                                 \
-  launch<G>(k_map, v_map, (const bf16*)q, (size_t)q_stride, block_table, table_width, positions, rows, page_size, heads, \
+  launch<G>(k_map, v_map, k_tile_map, v_tile_map, (const bf16*)q, (size_t)q_stride, block_table, table_width, positions, rows, page_size, heads, \
             kv_heads, scale, window, partition, num_partitions, partial_o, partial_ml, (bf16*)out, stream)
   status = columns <= 4 ? MIR_SPLIT(4) : (columns <= 8 ? MIR_SPLIT(8) : MIR_SPLIT(16));
 #undef MIR_SPLIT

@@ -84,7 +84,8 @@ def test_decode_attention(heads, kv_heads, dim, page, window, partition, tensor_
     qs = [(torch.randn(n, heads, dim) * 2).to(BF16) for n in lengths]
     ks = [(torch.randn(n, kv_heads, dim) * 2).to(BF16) for n in lengths]
     vs = [torch.randn(n, kv_heads, dim).to(BF16) for n in lengths]
-    k_pool, v_pool, table = build_pool(ks, vs, page, rng)
+    # (pages in runs where the partition is 256 keys or more: the tcgen05 kernel then fetches whole tiles where it can)
+    k_pool, v_pool, table = build_pool(ks, vs, page, rng, runs=partition >= 256)
     rows = len(lengths) + 2                                      # two padding rows, as in a captured batch
     q_rows = torch.cat([q[-1:] for q in qs] + [torch.zeros(2, heads, dim, dtype=BF16)]).reshape(rows, heads * dim)
     packed = torch.cat([q_rows, torch.randn(rows, 2 * kv_heads * dim).to(BF16)], dim=1).contiguous()
