@@ -239,10 +239,16 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
       cache_row = next_row;
     }
   } else if (warp == 5) {
-    // ------------------------------------------------------------------ issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ issuer: the whole warp stays converged, the
+    // products are predicated on the elected lane and take their descriptors as 32-bit halves (tcgen05.cuh: a product
+    // of 16 columns is over in a few cycles, and a lone thread in a divergent branch needs longer than that to issue
+    // the next one)
+    {
       constexpr uint32_t idesc_scores = instruction_descriptor(kKeys, kHeads, false);
       constexpr uint32_t idesc_values = instruction_descriptor(kDim, kHeads, false) | (1u << 15);   // A MN-major
+      const uint32_t elected = elect_one();
+      const uint32_t k_low = operand_low(smem_base + kOffK), q_low = operand_low(smem_base + kOffQ);
+      const uint32_t v_low = operand_low_mn_major(smem_base + kOffV, kHalf), p_low = operand_low(smem_base + kOffP);
       bool alive = true;
       auto check = [&](int index, uint32_t parity) {
         if (alive && !wait_barrier(bar(index), parity)) { g_tc_decode_error = 2; alive = false; }
@@ -250,34 +256,34 @@ tc_decode_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __gr
       auto issue_scores = [&](int t) {
         check(K_FULL, (uint32_t)t & 1u);
         tensor_fence_after_sync();
-        const uint32_t a = smem_base + kOffK, b = smem_base + kOffQ;
+        mma_bf16_ss_halves<false>(tmem_s, k_low, q_low, idesc_scores, elected);
 #pragma unroll
-        for (int kk = 0; kk < kDim / 16; ++kk)
-          mma_bf16_ss(tmem_s, operand_descriptor(a + (uint32_t)(kk >> 2) * kHalf + (uint32_t)(kk & 3) * 32u),
-                      operand_descriptor(b + (uint32_t)(kk >> 2) * kSmallHalf + (uint32_t)(kk & 3) * 32u), idesc_scores,
-                      kk > 0 ? 1u : 0u);
-        mma_commit(bar(S_FULL));
-        mma_commit(bar(K_FREE));
+        for (int kk = 1; kk < kDim / 16; ++kk)
+          mma_bf16_ss_halves<true>(tmem_s, k_low + (uint32_t)(kk >> 2) * (uint32_t)(kHalf >> 4) + (uint32_t)(kk & 3) * 2u,
+                                   q_low + (uint32_t)(kk >> 2) * (uint32_t)(kSmallHalf >> 4) + (uint32_t)(kk & 3) * 2u,
+                                   idesc_scores, elected);
+        mma_commit_elected(bar(S_FULL), elected);
+        mma_commit_elected(bar(K_FREE), elected);
       };
       check(Q_READY, 0u);
-      MIR_TRACE_POINT(decode, 4);
+      if (elected) MIR_TRACE_POINT(decode, 4);
       issue_scores(0);
-      MIR_TRACE_POINT(decode, 5);
+      if (elected) MIR_TRACE_POINT(decode, 5);
       for (int t = 0; t < tiles; ++t) {
         const uint32_t parity = (uint32_t)t & 1u;
         check(V_FULL, parity);
         check(P_READY, parity);
         tensor_fence_after_sync();
-        const uint32_t a = smem_base + kOffV, b = smem_base + kOffP;
+        mma_bf16_ss_halves(tmem_o, v_low, p_low, idesc_values, t > 0 ? 1u : 0u, elected);
 #pragma unroll
-        for (int kk = 0; kk < kKeys / 16; ++kk)
-          mma_bf16_ss(tmem_o, operand_descriptor_mn_major(a + (uint32_t)kk * 2048u, kHalf),
-                      operand_descriptor(b + (uint32_t)(kk >> 2) * kSmallHalf + (uint32_t)(kk & 3) * 32u), idesc_values,
-                      (t > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(bar(V_FREE));
+        for (int kk = 1; kk < kKeys / 16; ++kk)
+          mma_bf16_ss_halves<true>(tmem_o, v_low + (uint32_t)kk * (2048u >> 4),
+                                   p_low + (uint32_t)(kk >> 2) * (uint32_t)(kSmallHalf >> 4) + (uint32_t)(kk & 3) * 2u,
+                                   idesc_values, elected);
+        mma_commit_elected(bar(V_FREE), elected);
         // the next scores are issued behind this product, so that their barrier also says that O^T may be rescaled
         if (t + 1 < tiles) issue_scores(t + 1);
-        else mma_commit(bar(O_DONE));
+        else mma_commit_elected(bar(O_DONE), elected);
       }
     }
   } else {
