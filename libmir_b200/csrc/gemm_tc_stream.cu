@@ -148,26 +148,30 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ issuer: the whole warp stays converged, the
+    // products are predicated on the elected lane and take their descriptors as 32-bit halves (tcgen05.cuh); the
+    // stage and its parity are counted, not divided
+    {
       const uint32_t idesc = instruction_descriptor(128, tokens);
+      const uint32_t elected = elect_one();
+      const uint32_t a_low0 = operand_low(smem_base), b_low0 = operand_low(smem_base + weight_bytes);
+      const uint32_t stage_step = (uint32_t)stage_stride >> 4;
       bool alive = true;
+      uint32_t stage = 0, parity = 0;
       for (int i = 0; i < my_steps; ++i) {
-        const int stage = i % stages;
-        const uint32_t parity = (uint32_t)(i / stages) & 1u;
         if (alive && !wait_barrier(full0 + 8 * stage, parity)) { g_tc_stream_error = 2; alive = false; }
-        if (i == 0) MIR_TRACE_POINT(stream, 4);
-        if (i == my_steps - 1) MIR_TRACE_POINT(stream, 5);
+        if (elected && i == 0) MIR_TRACE_POINT(stream, 4);
+        if (elected && i == my_steps - 1) MIR_TRACE_POINT(stream, 5);
         tensor_fence_after_sync();
-        const uint32_t a_base = smem_base + (uint32_t)stage * (uint32_t)stage_stride;
-        const uint32_t b_base = a_base + weight_bytes;
+        const uint32_t a_low = a_low0 + stage * stage_step, b_low = b_low0 + stage * stage_step;
+        mma_bf16_ss_halves(tmem_base, a_low, b_low, idesc, i > 0 ? 1u : 0u, elected);
 #pragma unroll
-        for (int kk = 0; kk < kStepK / 16; ++kk)
-          mma_bf16_ss(tmem_base, operand_descriptor(a_base + kk * 32), operand_descriptor(b_base + kk * 32), idesc,
-                      (i > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(empty0 + 8 * stage);
+        for (int kk = 1; kk < kStepK / 16; ++kk)
+          mma_bf16_ss_halves<true>(tmem_base, a_low + 2u * kk, b_low + 2u * kk, idesc, elected);
+        mma_commit_elected(empty0 + 8 * stage, elected);
+        if (++stage == (uint32_t)stages) { stage = 0; parity ^= 1u; }
       }
-      mma_commit(done);
+      mma_commit_elected(done, elected);
     }
   }
   // ---------------------------------------------------------------------- the tile, transposed, into shared memory
