@@ -137,14 +137,17 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
         tma_load_2d(smem_base + (uint32_t)i * (uint32_t)stage_stride + weight_bytes, &x_map, full0 + 8 * i,
                     (step_begin + i) * kStepK, 0);
       MIR_TRACE_POINT(stream, 3);
+      // (the stage and its parity are counted, not divided: `ahead` stages are filled, so step `ahead` takes stage
+      // ahead % stages = 0 when the ring was filled, in its second turn)
+      int stage = ahead == stages ? 0 : ahead;
+      uint32_t parity = ahead == stages ? 1u : 0u;
       for (int i = ahead; i < my_steps; ++i) {
-        const int stage = i % stages;
-        const uint32_t parity = (uint32_t)(i / stages) & 1u;
         if (!wait_barrier(empty0 + 8 * stage, parity ^ 1u)) { g_tc_stream_error = 1; break; }
         const uint32_t barrier = full0 + 8 * stage;
         const uint32_t dst = smem_base + (uint32_t)stage * (uint32_t)stage_stride;
         load_weights(i, barrier, dst);
         tma_load_2d(dst + weight_bytes, &x_map, barrier, (step_begin + i) * kStepK, 0);
+        if (++stage == stages) { stage = 0; parity ^= 1u; }
       }
     }
   } else if (warp == 1) {
