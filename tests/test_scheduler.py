@@ -285,3 +285,59 @@ def test_a_preempted_request_finds_its_own_pages_again_unless_they_were_needed()
     assert len(by_name["old"].output) == 12 and len(by_name["young"].output) == 12
     assert manager.groups[0].pool.available == 6 and manager.prefix_evictions > 0
     manager.check()
+
+
+@pytest.mark.parametrize("seed", range(12))
+@pytest.mark.parametrize("policy", ["preempt", "finish"])
+def test_random_traffic_with_a_prefix_cache_feeds_every_token_once_in_order(seed, policy):
+    """Requests that share prefixes, a pool too small for all of them, both policies for running out of pages: every
+    request that finishes by length or stop has been fed, since its last (re)admission, exactly the tokens from where
+    its cached pages end up to its last token, in order and without a gap; cached starts are whole pages; nothing is
+    left held at the end."""
+    import random
+    rng = random.Random(seed)
+    page = 4
+    scheduler, runner, manager = build(pages=rng.choice([10, 14, 24]), page_size=page, prefix_cache=True,
+                                       out_of_pages=policy, max_batch_tokens=rng.choice([8, 16, 64]),
+                                       prefill_chunk_tokens=rng.choice([5, 8, 32]), max_batch_requests=4)
+    stems = [[rng.randrange(5, 9) for _ in range(rng.randrange(4, 20))] for _ in range(3)]
+    requests = []
+    for index in range(10):
+        stem = rng.choice(stems)
+        prompt = stem[:rng.randrange(1, len(stem) + 1)] + [rng.randrange(5, 9) for _ in range(rng.randrange(0, 6))]
+        settings = GenerationSettings(max_tokens=rng.randrange(1, 9))
+        requests.append(Request(f"r{index}", prompt, settings, RequestSampler()))
+    for item in requests[:5]:
+        scheduler.submit(item)
+    steps = 0
+    while scheduler.waiting or scheduler.running:
+        scheduler.step()
+        steps += 1
+        if steps == 3:
+            for item in requests[5:]:
+                scheduler.submit(item)
+        assert steps < 2000
+        manager.check()
+    fed = {item.request_id: [] for item in requests}
+    for step in runner.ran:
+        names = [rid for rid, _, _, _ in step]
+        assert len(names) == len(set(names))
+        for rid, start, count, _ in step:
+            fed[rid].append((start, count))
+    for item in requests:
+        assert item.state == "finished"
+        portions = fed[item.request_id]
+        if item.finish_reason in ("length", "stop"):
+            total = len(item.prompt) + len(item.output)
+            # walk back from the last portion to the start of the last (re)admission
+            end = total - 1                                    # the last generated token is never fed
+            cursor = len(portions) - 1
+            while cursor >= 0 and portions[cursor][0] + portions[cursor][1] == end:
+                end = portions[cursor][0]
+                cursor -= 1
+            assert end % page == 0 and end < len(item.prompt) + len(item.output), (item.request_id, portions)
+            assert item.cached_tokens >= end or end == 0
+        else:
+            assert item.finish_reason == "out_of_pages"
+    pool = manager.groups[0].pool
+    assert pool.available == pool.count and manager.free_slots == 4 and not manager.live
