@@ -10,7 +10,8 @@
 //              w box(es) with cp.async.bulk.tensor.2d into a ring of shared-memory stages laid out with the
 //              128-byte swizzle that tcgen05.mma reads.  Out-of-range rows and k arrive as zeros, so M, N and K
 //              need not be multiples of the tile.  An mbarrier per stage counts the bytes in.
-//   issuer     one thread.  When a stage is full it issues four tcgen05.mma (128 x width x 16 each, operands
+//   issuer     one warp that stays converged, the products predicated on its elected lane (tcgen05.cuh says why).
+//              When a stage is full it issues four tcgen05.mma (128 x width x 16 each, operands
 //              straight from shared memory through matrix descriptors, accumulator in tensor memory) and then
 //              tcgen05.commit, which arrives on the stage's "empty" barrier once the tensor cores have read the
 //              stage, so the producer can refill it.  After a tile's last step a commit arrives on the

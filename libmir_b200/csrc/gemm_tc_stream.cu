@@ -10,7 +10,8 @@
 //
 //   producer   one thread: per 64-wide step of K one TMA box of weights (128 rows x 64; with the SwiGLU epilogue 64
 //              gate rows and the 64 up rows that belong to them) and one of activations into a ring of stages.
-//   issuer     one thread: four tcgen05.mma (128 x tokens x 16) per stage, tcgen05.commit frees the stage.
+//   issuer     one warp that stays converged, the products predicated on its elected lane, the ring's stage counted
+//              (tcgen05.cuh says why): four tcgen05.mma (128 x tokens x 16) per stage, tcgen05.commit frees the stage.
 //   epilogue   four warps: read the accumulator (lane = feature), transpose it through shared memory.
 //
 // K is cut over a cluster of 1, 2, 4 or 8 CTAs so that up to 444 CTAs run whatever the shape (three fit on an SM;
